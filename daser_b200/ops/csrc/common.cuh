@@ -1,0 +1,112 @@
+// Shared device helpers for the sm_100a kernels of daser_b200.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define DASER_API extern "C" __attribute__((visibility("default")))
+
+// Error codes returned by the host entry points (0 = ok, >0 = cudaError_t).
+#define DASER_ERR_BAD_ARG (-1)
+#define DASER_ERR_UNSUPPORTED (-2)
+#define DASER_ERR_TOO_LARGE (-3)
+
+// Status words written by kernels whose waits ran out (see signals.cuh).
+#define DASER_STATUS_OK 0u
+#define DASER_STATUS_TIMEOUT 1u
+
+#define DASER_MAX_RANKS 8
+#define FP8_GROUP 16
+#define E4M3_MAX 448.0f
+
+namespace daser {
+
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+
+// Two e4m3 bytes (low 16 bits of v) -> two floats.
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+__device__ __forceinline__ uint16_t float2_to_e4m3x2(float lo, float hi) {
+  return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+
+// 16 floats -> 16 e4m3 bytes with one shared scale (absmax / 448; 1 for an all-zero group).
+// inv = 448 / absmax and the product x * inv are single IEEE fp32 operations so the
+// CPU oracle (kv/codec.py) reproduces the payload bit for bit.
+__device__ __forceinline__ void quant_group16(const float (&x)[16], uint4& payload, float& scale) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(x[i]));
+  float inv = 1.f;
+  scale = 1.f;
+  if (amax > 0.f) {
+    inv = __fdiv_rn(E4M3_MAX, amax);
+    scale = __fdiv_rn(amax, E4M3_MAX);
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float a = fminf(fmaxf(__fmul_rn(x[4 * i + 0], inv), -E4M3_MAX), E4M3_MAX);
+    float b = fminf(fmaxf(__fmul_rn(x[4 * i + 1], inv), -E4M3_MAX), E4M3_MAX);
+    float c = fminf(fmaxf(__fmul_rn(x[4 * i + 2], inv), -E4M3_MAX), E4M3_MAX);
+    float d = fminf(fmaxf(__fmul_rn(x[4 * i + 3], inv), -E4M3_MAX), E4M3_MAX);
+    w[i] = (uint32_t)float2_to_e4m3x2(a, b) | ((uint32_t)float2_to_e4m3x2(c, d) << 16);
+  }
+  payload = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ void dequant_group16(const uint4& payload, float scale, float (&x)[16]) {
+  const uint32_t w[4] = {payload.x, payload.y, payload.z, payload.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 a = e4m3x2_to_float2((uint16_t)(w[i] & 0xffffu));
+    float2 b = e4m3x2_to_float2((uint16_t)(w[i] >> 16));
+    x[4 * i + 0] = __fmul_rn(a.x, scale);
+    x[4 * i + 1] = __fmul_rn(a.y, scale);
+    x[4 * i + 2] = __fmul_rn(b.x, scale);
+    x[4 * i + 3] = __fmul_rn(b.y, scale);
+  }
+}
+
+__device__ __forceinline__ void load_bf16x16(const __nv_bfloat16* p, float (&x)[16]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint4 b = *reinterpret_cast<const uint4*>(p + 8);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    x[2 * i] = bf16_lo(w[i]);
+    x[2 * i + 1] = bf16_hi(w[i]);
+  }
+}
+
+__device__ __forceinline__ void store_bf16x16(__nv_bfloat16* p, const float (&x)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(p + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace daser

@@ -1,0 +1,336 @@
+// Bandwidth-bound serving-model kernels: fused residual-add + RMSNorm, RoPE fused with
+// the paged KV-cache write (bf16 or block-scaled fp8 pool), SwiGLU, embedding gather
+// and greedy sampling.  In the reference these all come from stock vLLM (its _C fused
+// add+rmsnorm, rotary and cache-write kernels); the reference itself has no GPU code.
+//
+// Inputs that come from a split-K / reduce-scatter GEMM are fp32 accumulators: the
+// consumer reads them and, when asked, writes zeros back so the next GEMM can
+// accumulate into the same buffer without a separate memset.
+#include "common.cuh"
+#include "kv_paged.h"
+
+namespace daser {
+
+template <typename T> struct Loader;
+template <> struct Loader<__nv_bfloat16> {
+  static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8], bool) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
+  }
+};
+template <> struct Loader<float> {
+  static __device__ __forceinline__ void load8(float* p, float (&v)[8], bool zero_after) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    if (zero_after) {
+      *reinterpret_cast<float4*>(p) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(p + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+};
+
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                            pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+
+struct OutList {
+  __nv_bfloat16* ptr[DASER_MAX_RANKS];  // normalised rows go to each of these (peers for the all-gather push)
+  int n;
+};
+
+// out = rmsnorm(x [+ residual]) * weight ; residual <- x + residual.
+// One CTA per row, the row stays in registers (hidden <= 8 * 4 * blockDim).
+template <typename TIn>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                   const __nv_bfloat16* __restrict__ weight, OutList out, int64_t out_row_offset,
+                   int hidden, float eps, int zero_after) {
+  __shared__ float s_part[32];
+  const int64_t row = blockIdx.x;
+  TIn* xr = x + row * hidden;
+  __nv_bfloat16* rr = residual ? residual + row * hidden : nullptr;
+  float v[4][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      Loader<TIn>::load8(const_cast<TIn*>(xr) + c, v[it], zero_after != 0);
+      if (rr) {
+        float r[8];
+        Loader<__nv_bfloat16>::load8(rr + c, r, false);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[it][i] += r[i];
+        // the residual stream is kept in bf16: normalise what the next layer will read
+        store8_bf16(rr + c, v[it]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[it][i] = __bfloat162float(__float2bfloat16(v[it][i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[it][i] * v[it][i];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_part[0] = rsqrtf(t / (float)hidden + eps);
+  }
+  __syncthreads();
+  const float inv = s_part[0];
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int c = (it * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      float w[8], o[8];
+      Loader<__nv_bfloat16>::load8(weight + c, w, false);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = v[it][i] * inv * w[i];
+      for (int k = 0; k < out.n; ++k) store8_bf16(out.ptr[k] + (out_row_offset + row) * hidden + c, o);
+    }
+  }
+}
+
+// RoPE on q and k, then k/v into the paged pool.  qkv row = [Hq*D | Hkv*D | Hkv*D].
+// slot_mapping[t] = block * block_tokens + offset inside the block, or < 0 to skip the write.
+template <typename TIn, bool POOL_FP8>
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* __restrict__ positions,
+                     const int64_t* __restrict__ slot_mapping, const float* __restrict__ cos_sin,
+                     int max_pos, __nv_bfloat16* __restrict__ q_out, int T, int Hq, int Hkv, int D,
+                     int block_tokens, DaserKVPool pool, int layer, int rank, int zero_after) {
+  const int half = D >> 1;
+  const int segs = half / FP8_GROUP;
+  const int heads = Hq + 2 * Hkv;
+  const int64_t total = (int64_t)T * heads * segs;
+  for (int64_t item = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; item < total;
+       item += (int64_t)gridDim.x * blockDim.x) {
+    const int j = item % segs;
+    const int hd = (item / segs) % heads;
+    const int t = item / ((int64_t)segs * heads);
+    TIn* src = qkv + (int64_t)t * qkv_stride + (int64_t)hd * D + j * FP8_GROUP;
+    float x1[16], x2[16];
+    {
+      float a[8], b[8];
+      Loader<TIn>::load8(src, a, zero_after != 0);
+      Loader<TIn>::load8(src + 8, b, zero_after != 0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x1[i] = a[i]; x1[8 + i] = b[i]; }
+      Loader<TIn>::load8(src + half, a, zero_after != 0);
+      Loader<TIn>::load8(src + half + 8, b, zero_after != 0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x2[i] = a[i]; x2[8 + i] = b[i]; }
+    }
+    const bool is_v = hd >= Hq + Hkv;
+    if (!is_v) {
+      int pos = positions[t];
+      pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+      const float* cs = cos_sin + (int64_t)pos * D + j * FP8_GROUP;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float c = cs[i], s = cs[half + i];
+        const float a = x1[i], b = x2[i];
+        x1[i] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+        x2[i] = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+      }
+    }
+    if (hd < Hq) {
+      __nv_bfloat16* dst = q_out + ((int64_t)t * Hq + hd) * D + j * FP8_GROUP;
+      store_bf16x16(dst, x1);
+      store_bf16x16(dst + half, x2);
+      continue;
+    }
+    const int64_t sm = slot_mapping[t];
+    if (sm < 0) continue;
+    const int block = (int)(sm / block_tokens), tok = (int)(sm % block_tokens);
+    if (block >= pool.num_blocks) continue;
+    const int kv = is_v ? 1 : 0;
+    const int hl = is_v ? hd - Hq - Hkv : hd - Hq;
+    const int64_t d1 = (int64_t)layer * pool.stride_layer + (int64_t)block * pool.stride_block +
+                       (int64_t)kv * pool.stride_kv + (int64_t)tok * pool.stride_tok +
+                       (int64_t)hl * pool.stride_head + j * FP8_GROUP;
+    const int64_t d2 = d1 + half;
+    if (POOL_FP8) {
+      uint4 q1, q2;
+      float s1, s2;
+      // quantise what a bf16 pool would have held, so both pool kinds see the same values
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        x1[i] = __bfloat162float(__float2bfloat16(x1[i]));
+        x2[i] = __bfloat162float(__float2bfloat16(x2[i]));
+      }
+      quant_group16(x1, q1, s1);
+      quant_group16(x2, q2, s2);
+      uint8_t* p = reinterpret_cast<uint8_t*>(pool.payload[rank]);
+      *reinterpret_cast<uint4*>(p + d1) = q1;
+      *reinterpret_cast<uint4*>(p + d2) = q2;
+      pool.scales[rank][d1 / FP8_GROUP] = s1;
+      pool.scales[rank][d2 / FP8_GROUP] = s2;
+    } else {
+      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(pool.payload[rank]);
+      store_bf16x16(p + d1, x1);
+      store_bf16x16(p + d2, x2);
+    }
+  }
+}
+
+// y[t, i] = silu(x[t, i]) * x[t, inter + i]
+template <typename TIn>
+__global__ void __launch_bounds__(256)
+swiglu_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ y, int64_t T, int inter, int zero_after) {
+  const int64_t total = T * (inter / 8);
+  for (int64_t item = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; item < total;
+       item += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = item / (inter / 8);
+    const int c = (int)(item % (inter / 8)) * 8;
+    float g[8], u[8], o[8];
+    Loader<TIn>::load8(x + t * 2 * inter + c, g, zero_after != 0);
+    Loader<TIn>::load8(x + t * 2 * inter + inter + c, u, zero_after != 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+    store8_bf16(y + t * inter + c, o);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+embedding_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                 __nv_bfloat16* __restrict__ out, int64_t T, int hidden, int vocab_begin, int vocab_count) {
+  const int64_t total = T * (hidden / 8);
+  for (int64_t item = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; item < total;
+       item += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = item / (hidden / 8);
+    const int c = (int)(item % (hidden / 8)) * 8;
+    const int id = ids[t] - vocab_begin;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (id >= 0 && id < vocab_count) v = *reinterpret_cast<const uint4*>(table + (int64_t)id * hidden + c);
+    *reinterpret_cast<uint4*>(out + t * hidden + c) = v;
+  }
+}
+
+// Greedy sampling: argmax over a row of logits; packs (value, index) so ties pick the lowest index.
+template <typename TIn>
+__global__ void __launch_bounds__(1024)
+argmax_kernel(TIn* __restrict__ logits, int64_t stride, int n, int index_offset,
+              float* __restrict__ best_val, int32_t* __restrict__ best_idx, int zero_after) {
+  __shared__ float s_v[32];
+  __shared__ int s_i[32];
+  TIn* row = logits + blockIdx.x * stride;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x * 8; c < n; c += blockDim.x * 8) {
+    float v[8];
+    Loader<TIn>::load8(row + c, v, zero_after != 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c + i < n && (v[i] > bv)) { bv = v[i]; bi = c + i; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int nw = blockDim.x >> 5;
+    bv = threadIdx.x < nw ? s_v[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? s_i[threadIdx.x] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) { best_val[blockIdx.x] = bv; best_idx[blockIdx.x] = bi + index_offset; }
+  }
+}
+
+static int ew_grid(int64_t items, int threads) {
+  int64_t b = (items + threads - 1) / threads;
+  const int64_t cap = 148 * 16;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace daser
+
+// x: bf16 (x_is_fp32 = 0) or fp32 accumulators (x_is_fp32 = 1, zeroed after the read when
+// zero_after != 0).  out_ptrs[0..n_out) each receive the normalised rows at row offset
+// out_row_offset (the all-gather push when they are peers' buffers).
+DASER_API int daser_add_rmsnorm(void* x, int x_is_fp32, void* residual, const void* weight,
+                                void* const* out_ptrs, int n_out, int64_t out_row_offset,
+                                int64_t rows, int hidden, float eps, int zero_after,
+                                cudaStream_t stream) {
+  using namespace daser;
+  if (rows < 0 || hidden <= 0 || hidden % 8 || n_out < 1 || n_out > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
+  if (rows == 0) return 0;
+  int threads = ((hidden / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (hidden > threads * 8 * 4) return DASER_ERR_TOO_LARGE;
+  OutList out;
+  out.n = n_out;
+  for (int i = 0; i < n_out; ++i) out.ptr[i] = (__nv_bfloat16*)out_ptrs[i];
+  if (x_is_fp32)
+    add_rmsnorm_kernel<float><<<(unsigned)rows, threads, 0, stream>>>(
+        (float*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, zero_after);
+  else
+    add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, stream>>>(
+        (__nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, 0);
+  return (int)cudaGetLastError();
+}
+
+DASER_API int daser_rope_kv_write(void* qkv, int qkv_is_fp32, int64_t qkv_stride, const int32_t* positions,
+                                  const int64_t* slot_mapping, const float* cos_sin, int max_pos,
+                                  void* q_out, int T, int Hq, int Hkv, int D, int block_tokens,
+                                  const DaserKVPool* pool, int layer, int rank, int zero_after,
+                                  cudaStream_t stream) {
+  using namespace daser;
+  if (!pool || T < 0 || D <= 0 || D % 32 || max_pos <= 0) return DASER_ERR_BAD_ARG;
+  if (rank < 0 || rank >= DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
+  if (T == 0) return 0;
+  const int64_t items = (int64_t)T * (Hq + 2 * Hkv) * (D / 32);
+  const int grid = ew_grid(items, 128);
+#define LAUNCH(TIN, FP8)                                                                         \
+  rope_kv_write_kernel<TIN, FP8><<<grid, 128, 0, stream>>>(                                      \
+      (TIN*)qkv, qkv_stride, positions, slot_mapping, cos_sin, max_pos, (__nv_bfloat16*)q_out, T, \
+      Hq, Hkv, D, block_tokens, *pool, layer, rank, zero_after)
+  if (qkv_is_fp32) { if (pool->pool_is_fp8) LAUNCH(float, true); else LAUNCH(float, false); }
+  else { if (pool->pool_is_fp8) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false); }
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+DASER_API int daser_swiglu(void* x, int x_is_fp32, void* y, int64_t T, int inter, int zero_after,
+                           cudaStream_t stream) {
+  using namespace daser;
+  if (T < 0 || inter <= 0 || inter % 8) return DASER_ERR_BAD_ARG;
+  if (T == 0) return 0;
+  const int grid = ew_grid(T * (inter / 8), 256);
+  if (x_is_fp32) swiglu_kernel<float><<<grid, 256, 0, stream>>>((float*)x, (__nv_bfloat16*)y, T, inter, zero_after);
+  else swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)x, (__nv_bfloat16*)y, T, inter, 0);
+  return (int)cudaGetLastError();
+}
+
+DASER_API int daser_embedding(const int32_t* ids, const void* table, void* out, int64_t T, int hidden,
+                              int vocab_begin, int vocab_count, cudaStream_t stream) {
+  using namespace daser;
+  if (T < 0 || hidden <= 0 || hidden % 8) return DASER_ERR_BAD_ARG;
+  if (T == 0) return 0;
+  embedding_kernel<<<ew_grid(T * (hidden / 8), 256), 256, 0, stream>>>(
+      ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, hidden, vocab_begin, vocab_count);
+  return (int)cudaGetLastError();
+}
+
+DASER_API int daser_argmax(void* logits, int is_fp32, int64_t stride, int rows, int n, int index_offset,
+                           float* best_val, int32_t* best_idx, int zero_after, cudaStream_t stream) {
+  using namespace daser;
+  if (rows < 0 || n <= 0 || stride % 8) return DASER_ERR_BAD_ARG;
+  if (rows == 0) return 0;
+  if (is_fp32) argmax_kernel<float><<<rows, 1024, 0, stream>>>((float*)logits, stride, n, index_offset, best_val, best_idx, zero_after);
+  else argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>((__nv_bfloat16*)logits, stride, n, index_offset, best_val, best_idx, 0);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,355 @@
+// tcgen05 GEMM for the serving model: C[M,N] (+)= A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate
+// in tensor memory.  A is the activation matrix (row-major), B a Linear weight as PyTorch
+// stores it ([out_features, in_features]), so both operands are K-major and go from global
+// memory to 128-byte-swizzled shared memory with plain (non-multicast) TMA tiled loads.
+//
+// In the reference's serving stack these GEMMs are cuBLAS/CUTLASS calls inside stock vLLM
+// (vllm/model_executor/layers/linear.py) followed, for the row-parallel layers, by a
+// separate all-reduce; here the reduce-scatter is the epilogue of the same kernel.
+//
+// Work decomposition: grid = (n_tiles, m_tiles, k_splits); one 128 x BN output tile and one
+// K range per CTA.  Serving GEMMs have few rows (a decode batch or a prompt tail), so the
+// time is set by how fast the weights stream from HBM: split-K keeps all 148 SMs pulling
+// even when N / BN is small.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = epilogue (TMEM lane quarter = warp % 4).
+//
+// Epilogues:
+//   EPI_STORE_BF16   C is bf16, k_splits must be 1.
+//   EPI_REDUCE_F32   C is fp32 and is accumulated with vector red.global.add; rows are
+//                    partitioned over n_owners buffers (rows_per_owner each).  With one owner
+//                    this is local split-K; with the owners being the tensor-parallel ranks'
+//                    peer-mapped buffers it is GEMM -> reduce-scatter: every partial tile goes
+//                    straight from TMEM over NVLink into the rank that owns those rows, and a
+//                    per-owner arrival counter is bumped (release, system scope) once the
+//                    CTA's contributions are out.
+//
+// Every wait is bounded; on a timeout the kernel records it in `status`, drains, frees its
+// TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace daser {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;  // 64 bf16 = 128 B = one swizzle row
+constexpr int GEMM_THREADS = 192;
+
+enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1 };
+
+struct GemmParams {
+  int M, N, K;
+  int k_splits;
+  int epilogue;
+  int n_owners;
+  int rows_per_owner;
+  int64_t ldc;
+  void* c[DASER_MAX_RANKS];
+  uint32_t* arrive[DASER_MAX_RANKS];  // per-owner arrival counters (may be null)
+  uint32_t* status;                   // [0] = timeout flag
+  // all-gather side: A rows [g*gate_rows, (g+1)*gate_rows) may be loaded once
+  // gate_flags[g] >= gate_target (null = no gating)
+  const uint32_t* gate_flags;
+  uint32_t gate_target;
+  int gate_rows;
+};
+
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full, then the TMEM base word and the abort flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16;
+  static constexpr int DYNAMIC = TOTAL + 1024;  // slack to align the tiles to 1024 B
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, (BN <= 128 ? 2 : 1))
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::BAR_OFFSET);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full_bar = empty_bar + STAGES;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * GEMM_BM;
+
+  const int kb_total = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int kb_per = (kb_total + p.k_splits - 1) / p.k_splits;
+  const int kb_begin = blockIdx.z * kb_per;
+  const int kb_end = min(kb_begin + kb_per, kb_total);
+  const int num_kb = kb_end - kb_begin;
+  if (num_kb <= 0) return;  // uniform across the CTA
+
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;  // power of two >= 32
+
+  if (warp == 0 && lane == 0) {
+    sm100::prefetch_tmap(&tmap_a);
+    sm100::prefetch_tmap(&tmap_b);
+    for (int s = 0; s < STAGES; ++s) {
+      sm100::mbar_init(&full_bar[s], 1);
+      sm100::mbar_init(&empty_bar[s], 1);
+    }
+    sm100::mbar_init(tmem_full_bar, 1);
+    *abort_flag = 0u;
+    sm100::mbar_init_fence();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(tmem_base_slot, TMEM_COLS);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      bool ok = true;
+      if (p.gate_flags != nullptr) {
+        // all-gather gating: the rows of this m-tile come from one or more peers' pushes
+        const int g0 = m0 / p.gate_rows;
+        const int g1 = min(m0 + GEMM_BM - 1, p.M - 1) / p.gate_rows;
+        for (int g = g0; g <= g1 && ok; ++g) {
+          uint32_t tries = 0;
+          while (ld_acquire_sys(p.gate_flags + g) < p.gate_target) {
+            if (++tries > (1u << 22) || *abort_flag) { ok = false; *abort_flag = 1u; break; }
+            __nanosleep(64);
+          }
+        }
+      }
+      int issued = 0;
+      for (int it = 0; it < num_kb && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+        if (!sm100::mbar_wait(&empty_bar[s], parity, abort_flag)) { ok = false; break; }
+        uint8_t* a_dst = smem + s * S::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + S::A_BYTES;
+        sm100::mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
+        const int k = (kb_begin + it) * GEMM_BK;
+        sm100::tma_load_2d(b_dst, &tmap_b, &full_bar[s], k, n0);
+        sm100::tma_load_2d(a_dst, &tmap_a, &full_bar[s], k, m0);
+        issued = it + 1;
+      }
+      if (!ok) {
+        // Aborting: give the loads already in flight a bounded chance to land before the
+        // CTA retires its shared memory.
+        const int first = issued > STAGES ? issued - STAGES : 0;
+        for (int it = first; it < issued; ++it) {
+          const int s = it % STAGES;
+          for (uint32_t i = 0; i < (1u << 16); ++i)
+            if (sm100::mbar_try_wait(&full_bar[s], (it / STAGES) & 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = sm100::make_idesc_f16(GEMM_BM, BN, 1u);
+      bool ok = true;
+      for (int it = 0; it < num_kb; ++it) {
+        const int s = it % STAGES;
+        if (!sm100::mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+        sm100::tc_fence_after();
+        const uint32_t a_addr = sm100::smem_u32(smem + s * S::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + S::A_BYTES;
+        const uint64_t da = sm100::make_desc_k_sw128(a_addr);
+        const uint64_t db = sm100::make_desc_k_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 16; ++k) {
+          // advancing 16 bf16 (32 B) along K inside the swizzle row: +2 in 16-byte units
+          sm100::umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        sm100::umma_commit(&empty_bar[s]);  // frees the stage once the MMAs have read it
+      }
+      if (ok) sm100::umma_commit(tmem_full_bar);
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;
+    const bool ok = sm100::mbar_wait(tmem_full_bar, 0, abort_flag);
+    sm100::tc_fence_after();
+    if (ok) {
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int owner = row_ok ? row / p.rows_per_owner : 0;
+      const int64_t local_row = row_ok ? row - (int64_t)owner * p.rows_per_owner : 0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
+        sm100::tmem_ld_wait();
+        if (!row_ok) continue;
+        const int col0 = n0 + c * 32;
+        if (p.epilogue == EPI_STORE_BF16) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + local_row * p.ldc + col0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + v * 8) = o;
+            }
+          }
+        } else {
+          float* dst = reinterpret_cast<float*>(p.c[owner]) + local_row * p.ldc + col0;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            if (col0 + v * 4 < p.N)
+              red_add_f32x4(dst + v * 4, __uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
+                            __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+          }
+        }
+      }
+      if (p.epilogue == EPI_REDUCE_F32 && p.arrive[0] != nullptr) {
+        // This warp's contributions are out: publish them, then bump every owner that its
+        // 32 rows touch.  (The host derives the expected count per owner from the same rule.)
+        __threadfence_system();
+        __syncwarp();
+        const int r_first = m0 + quarter * 32;
+        if (lane == 0 && r_first < p.M) {
+          const int o0 = r_first / p.rows_per_owner;
+          const int o1 = min(r_first + 31, p.M - 1) / p.rows_per_owner;
+          for (int o = o0; o <= o1; ++o)
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[o]) : "memory");
+        }
+      }
+    }
+  }
+
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tc_fence_after();
+    sm100::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, DASER_STATUS_TIMEOUT);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// bf16 [rows, cols] row-major with leading dimension ld (elements): box = [box_rows, 64 cols], 128 B swizzle.
+static int make_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return DASER_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return DASER_ERR_BAD_ARG;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : DASER_ERR_BAD_ARG;
+}
+
+template <int BN, int STAGES>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  using S = GemmSmem<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         S::DYNAMIC);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const dim3 grid((p.N + BN - 1) / BN, (p.M + GEMM_BM - 1) / GEMM_BM, p.k_splits);
+  gemm_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, S::DYNAMIC, stream>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace daser
+
+// C-callable description of one GEMM (mirrored with ctypes in daser_b200/ops/gemm.py).
+typedef struct {
+  const void* a;  // bf16 [M, K], leading dimension lda
+  const void* b;  // bf16 [N, K], leading dimension ldb
+  int64_t lda, ldb, ldc;
+  int32_t M, N, K;
+  int32_t block_n;   // 32, 64, 128 or 256
+  int32_t k_splits;  // >= 1
+  int32_t epilogue;  // 0 = bf16 store, 1 = fp32 red.add
+  int32_t n_owners;  // output row partitions (1 = plain)
+  int32_t rows_per_owner;
+  void* c[DASER_MAX_RANKS];
+  uint32_t* arrive[DASER_MAX_RANKS];
+  uint32_t* status;
+  const uint32_t* gate_flags;
+  uint32_t gate_target;
+  int32_t gate_rows;
+} DaserGemm;
+
+DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
+  using namespace daser;
+  if (!g || g->M <= 0 || g->N <= 0 || g->K <= 0 || g->k_splits < 1) return DASER_ERR_BAD_ARG;
+  if (g->K % 8 || g->N % 8) return DASER_ERR_UNSUPPORTED;
+  if (g->epilogue == EPI_STORE_BF16 && g->k_splits != 1) return DASER_ERR_BAD_ARG;
+  if (g->n_owners < 1 || g->n_owners > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
+  if (g->rows_per_owner <= 0 || (int64_t)g->rows_per_owner * g->n_owners < g->M) return DASER_ERR_BAD_ARG;
+  if (g->gate_flags && g->gate_rows <= 0) return DASER_ERR_BAD_ARG;
+  GemmParams p;
+  p.M = g->M; p.N = g->N; p.K = g->K;
+  p.k_splits = g->k_splits;
+  p.epilogue = g->epilogue;
+  p.n_owners = g->n_owners;
+  p.rows_per_owner = g->rows_per_owner;
+  p.ldc = g->ldc;
+  for (int i = 0; i < DASER_MAX_RANKS; ++i) { p.c[i] = g->c[i]; p.arrive[i] = g->arrive[i]; }
+  p.status = g->status;
+  p.gate_flags = g->gate_flags;
+  p.gate_target = g->gate_target;
+  p.gate_rows = g->gate_rows > 0 ? g->gate_rows : 1;
+  CUtensorMap ta, tb;
+  if (int e = make_tmap(&ta, g->a, g->M, g->K, g->lda, GEMM_BM)) return e;
+  if (int e = make_tmap(&tb, g->b, g->N, g->K, g->ldb, g->block_n)) return e;
+  switch (g->block_n) {
+    // stage counts keep two CTAs resident per SM for BN <= 128 (<= ~100 KB each)
+    case 32: return launch<32, 5>(ta, tb, p, stream);
+    case 64: return launch<64, 4>(ta, tb, p, stream);
+    case 128: return launch<128, 3>(ta, tb, p, stream);
+    case 256: return launch<256, 4>(ta, tb, p, stream);
+    default: return DASER_ERR_UNSUPPORTED;
+  }
+}

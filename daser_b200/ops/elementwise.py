@@ -1,0 +1,120 @@
+"""Entry points of the bandwidth-bound model kernels (``ops/csrc/elementwise.cu``)."""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from daser_b200.ops import _lib
+from daser_b200.ops.kv_ops import PagedKVPool
+
+
+def _is_f32(t: torch.Tensor) -> int:
+    assert t.dtype in (torch.float32, torch.bfloat16)
+    return int(t.dtype == torch.float32)
+
+
+def add_rmsnorm(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    residual: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    eps: float = 1e-5,
+    zero_after: bool = False,
+    out_ptrs: Optional[Sequence[int]] = None,
+    out_row_offset: int = 0,
+) -> Optional[torch.Tensor]:
+    """``out = rmsnorm(x + residual) * weight``; ``residual`` is updated in place.
+
+    ``x`` is bf16, or an fp32 accumulator that is zeroed after the read when
+    ``zero_after``.  ``out_ptrs`` (raw addresses, possibly peers') replaces ``out`` for the
+    all-gather push: each receives the rows at ``out_row_offset``.
+    """
+    rows, hidden = x.shape
+    if out_ptrs is None:
+        if out is None:
+            out = torch.empty((rows, hidden), dtype=torch.bfloat16, device=x.device)
+        out_ptrs = [out.data_ptr()]
+    arr = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+    _lib.check(
+        _lib.lib().daser_add_rmsnorm(
+            C.c_void_p(x.data_ptr()), _is_f32(x),
+            C.c_void_p(residual.data_ptr()) if residual is not None else None,
+            C.c_void_p(weight.data_ptr()), arr, len(out_ptrs), C.c_int64(out_row_offset),
+            C.c_int64(rows), hidden, C.c_float(eps), int(zero_after), _lib.stream_ptr(),
+        ),
+        "add_rmsnorm",
+    )
+    return out
+
+
+def rope_kv_write(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    cos_sin: torch.Tensor,
+    q_out: torch.Tensor,
+    num_q_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    block_tokens: int,
+    pool: PagedKVPool,
+    layer: int,
+    rank: int = 0,
+    zero_after: bool = False,
+) -> None:
+    """RoPE on q and k of ``qkv[T, (Hq + 2 Hkv) * D]``; q -> ``q_out``, k/v -> the paged pool."""
+    assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int64
+    pool_c = pool.c_struct()
+    _lib.check(
+        _lib.lib().daser_rope_kv_write(
+            C.c_void_p(qkv.data_ptr()), _is_f32(qkv), C.c_int64(qkv.stride(0)),
+            C.c_void_p(positions.data_ptr()), C.c_void_p(slot_mapping.data_ptr()),
+            C.c_void_p(cos_sin.data_ptr()), int(cos_sin.shape[0]), C.c_void_p(q_out.data_ptr()),
+            int(qkv.shape[0]), num_q_heads, num_kv_heads, head_dim, block_tokens,
+            C.byref(pool_c), layer, rank, int(zero_after), _lib.stream_ptr(),
+        ),
+        "rope_kv_write",
+    )
+
+
+def swiglu(x: torch.Tensor, out: Optional[torch.Tensor] = None, zero_after: bool = False) -> torch.Tensor:
+    """``silu(x[:, :I]) * x[:, I:]`` for ``x[T, 2I]`` (bf16 or fp32 accumulators)."""
+    T, two_i = x.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((T, inter), dtype=torch.bfloat16, device=x.device)
+    _lib.check(
+        _lib.lib().daser_swiglu(C.c_void_p(x.data_ptr()), _is_f32(x), C.c_void_p(out.data_ptr()),
+                                C.c_int64(T), inter, int(zero_after), _lib.stream_ptr()),
+        "swiglu",
+    )
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None,
+              vocab_begin: int = 0) -> torch.Tensor:
+    assert ids.dtype == torch.int32 and table.dtype == torch.bfloat16
+    T, hidden = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((T, hidden), dtype=torch.bfloat16, device=table.device)
+    _lib.check(
+        _lib.lib().daser_embedding(C.c_void_p(ids.data_ptr()), C.c_void_p(table.data_ptr()),
+                                   C.c_void_p(out.data_ptr()), C.c_int64(T), hidden, vocab_begin,
+                                   int(table.shape[0]), _lib.stream_ptr()),
+        "embedding",
+    )
+    return out
+
+
+def argmax(logits: torch.Tensor, best_val: torch.Tensor, best_idx: torch.Tensor,
+           index_offset: int = 0, zero_after: bool = False) -> None:
+    rows, n = logits.shape
+    _lib.check(
+        _lib.lib().daser_argmax(C.c_void_p(logits.data_ptr()), _is_f32(logits), C.c_int64(logits.stride(0)),
+                                rows, n, index_offset, C.c_void_p(best_val.data_ptr()),
+                                C.c_void_p(best_idx.data_ptr()), int(zero_after), _lib.stream_ptr()),
+        "argmax",
+    )

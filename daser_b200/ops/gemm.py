@@ -1,0 +1,124 @@
+"""tcgen05 GEMM entry points (``ops/csrc/gemm.cu``).
+
+``linear(x, w)`` computes ``x @ w.T`` for bf16 ``x[M, K]`` and a Linear weight
+``w[N, K]``.  Two output forms:
+
+* ``out`` bf16 ``[M, N]`` (no split-K), or
+* ``acc`` fp32 ``[M, N]`` accumulated with ``red.global.add`` (split-K and/or
+  reduce-scatter: ``owners`` lists per-rank accumulation buffers, each holding
+  ``rows_per_owner`` rows).
+
+``plan_tiles`` picks the N tile and the K split so that at least one CTA per SM streams
+weights when M is small.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from daser_b200.ops import _lib
+from daser_b200.ops._lib import Gemm
+
+NUM_SMS = 148
+EPI_STORE_BF16 = 0
+EPI_REDUCE_F32 = 1
+
+
+def plan_tiles(M: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int]:
+    """(block_n, k_splits) for a GEMM of this shape."""
+    m_tiles = -(-M // 128)
+    if m_tiles * -(-N // 256) >= 2 * NUM_SMS:
+        return 256, 1  # compute-bound: the biggest tile, no split
+    block_n = 128
+    tiles = m_tiles * -(-N // block_n)
+    if not allow_split or tiles >= NUM_SMS:
+        return block_n, 1
+    kb = -(-K // 64)
+    # aim for ~2 CTAs per SM, each with at least 4 K blocks
+    want = max(1, (2 * NUM_SMS) // tiles)
+    return block_n, max(1, min(want, kb // 4 if kb >= 4 else 1))
+
+
+def expected_arrivals(M: int, N: int, block_n: int, k_splits: int, rows_per_owner: int, n_owners: int,
+                      K: int) -> list[int]:
+    """Arrival-counter increments each owner receives from ONE rank's GEMM launch.
+
+    Mirrors the kernel: every epilogue warp (32 rows of a 128-row tile) with at least one
+    valid row bumps each owner its rows touch, once per (n tile, non-empty k split).
+    """
+    kb_total = -(-K // 64)
+    kb_per = -(-kb_total // k_splits)
+    live_splits = sum(1 for z in range(k_splits) if z * kb_per < kb_total)
+    n_tiles = -(-N // block_n)
+    counts = [0] * n_owners
+    for r0 in range(0, M, 32):
+        o0 = r0 // rows_per_owner
+        o1 = min(r0 + 31, M - 1) // rows_per_owner
+        for o in range(o0, o1 + 1):
+            counts[o] += n_tiles * live_splits
+    return counts
+
+
+def linear(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    out: Optional[torch.Tensor] = None,
+    acc: Optional[torch.Tensor] = None,
+    owners: Optional[Sequence[int]] = None,
+    rows_per_owner: Optional[int] = None,
+    arrive: Optional[Sequence[int]] = None,
+    block_n: Optional[int] = None,
+    k_splits: Optional[int] = None,
+    status: Optional[torch.Tensor] = None,
+    gate_flags: Optional[int] = None,
+    gate_target: int = 0,
+    gate_rows: int = 0,
+    ldc: Optional[int] = None,
+    stream=None,
+) -> torch.Tensor:
+    assert x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1]
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    M, K = x.shape
+    N = w.shape[0]
+    reduce = acc is not None or owners is not None
+    bn, ks = plan_tiles(M, N, K, allow_split=reduce)
+    bn = block_n or bn
+    ks = k_splits or ks
+    g = Gemm()
+    g.a, g.b = x.data_ptr(), w.data_ptr()
+    g.lda, g.ldb = x.stride(0), w.stride(0)
+    g.M, g.N, g.K = M, N, K
+    g.block_n, g.k_splits = bn, ks
+    g.status = status.data_ptr() if status is not None else None
+    g.gate_flags, g.gate_target, g.gate_rows = gate_flags, gate_target, gate_rows
+    if reduce:
+        g.epilogue = EPI_REDUCE_F32
+        if owners is None:
+            assert acc is not None and acc.dtype == torch.float32 and acc.stride(1) == 1
+            owners, rows_per_owner = [acc.data_ptr()], max(M, 1)
+            g.ldc = acc.stride(0)
+        else:
+            assert rows_per_owner is not None and ldc is not None
+            g.ldc = ldc
+        g.n_owners, g.rows_per_owner = len(owners), rows_per_owner
+        for i, ptr in enumerate(owners):
+            g.c[i] = ptr
+        if arrive is not None:
+            for i, ptr in enumerate(arrive):
+                g.arrive[i] = ptr
+        result = acc
+    else:
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+        g.epilogue = EPI_STORE_BF16
+        g.ldc = out.stride(0)
+        g.n_owners, g.rows_per_owner = 1, max(M, 1)
+        g.c[0] = out.data_ptr()
+        result = out
+    _lib.check(_lib.lib().daser_gemm(C.byref(g), _lib.stream_ptr(stream)), "gemm")
+    return result

@@ -1,0 +1,85 @@
+"""tcgen05 GEMM against an fp32 matmul of the same bf16 inputs."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(x, w):
+    return x.float() @ w.float().t()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 512), (64, 1280, 8192), (1, 384, 256),
+                                   (200, 136, 1000 * 8), (300, 512, 192)])
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+def test_store_epilogue(M, N, K, bn):
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = gemm.linear(x, w, block_n=bn, k_splits=1, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _ref(x, w)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-2, err
+
+
+@pytest.mark.parametrize("M,N,K,ks", [(64, 1280, 8192, 8), (128, 256, 1024, 3), (5, 128, 4096, 16), (130, 320, 640, 2)])
+def test_splitk_reduce_epilogue(M, N, K, ks):
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(1)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    acc = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    gemm.linear(x, w, acc=acc, k_splits=ks)
+    torch.cuda.synchronize()
+    ref = _ref(x, w)
+    assert (acc - ref).abs().max().item() <= 1e-3 * ref.abs().max().item() + 1e-3
+    # accumulates: a second launch doubles it
+    gemm.linear(x, w, acc=acc, k_splits=ks)
+    torch.cuda.synchronize()
+    assert (acc - 2 * ref).abs().max().item() <= 2e-3 * ref.abs().max().item() + 2e-3
+
+
+def test_reduce_scatter_epilogue_emulated_ranks():
+    """Two 'ranks' (K shards) on one device reduce into per-owner row buffers and bump the counters."""
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(2)
+    M, N, K, tp = 96, 256, 1024, 2
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    rows = M // tp
+    bufs = [torch.zeros(rows, N, dtype=torch.float32, device="cuda") for _ in range(tp)]
+    counters = torch.zeros(tp, dtype=torch.int32, device="cuda")
+    for r in range(tp):
+        ks = slice(r * K // tp, (r + 1) * K // tp)
+        gemm.linear(x[:, ks], w[:, ks], owners=[b.data_ptr() for b in bufs], rows_per_owner=rows,
+                    arrive=[counters.data_ptr() + 4 * i for i in range(tp)], ldc=N, block_n=128, k_splits=2)
+    torch.cuda.synchronize()
+    ref = _ref(x, w)
+    got = torch.cat(bufs)
+    assert (got - ref).abs().max().item() <= 1e-3 * ref.abs().max().item() + 1e-3
+    per_rank = gemm.expected_arrivals(M, N, 128, 2, rows, tp, K // tp)
+    assert counters.tolist() == [c * tp for c in per_rank]
+
+
+def test_gate_flags_release_the_loads():
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(3)
+    M, N, K = 256, 128, 256
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.5).to(torch.bfloat16)
+    flags = torch.full((2,), 5, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = gemm.linear(x, w, gate_flags=flags.data_ptr(), gate_target=5, gate_rows=128, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _ref(x, w)
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
