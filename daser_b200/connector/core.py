@@ -1,0 +1,613 @@
+"""Engine-agnostic connector: the scheduler half and the worker half.
+
+Capability parity: ``daser/connector/daser_connector.py:60-710`` — the metadata types
+(``ReqLoadSpec``, ``ReqStoreSpec``, per-step metadata), the scheduler-role hooks
+(``get_num_new_matched_tokens``, ``update_state_after_alloc``, ``build_connector_meta``,
+``request_finished``) and the worker-role hooks (``register_kv_caches``,
+``bind/clear_connector_metadata``, ``start_load_kv``, ``wait_for_layer_load``,
+``save_kv_layer``, ``wait_for_save``, ``shutdown``).  The vLLM adapter
+(:mod:`daser_b200.connector.daser_connector`) and the native engine both drive these
+classes; nothing here imports vLLM.
+
+What changed relative to the reference:
+
+* Loads and saves are ONE fused kernel launch per step (``ops/csrc/kv_paged.cu``) driven by
+  a device work list, instead of ``requests x slots x layers`` strided copies.
+* Chunk-level reuse: a request may carry ``chunk_placements`` — (chunk_key, token offset)
+  pairs — which are resolved with the batched ``lookup_chunks`` RPC and restored at their
+  new positions; the kernel rotates cached keys by ``new offset - stored pos_offset``.
+  The reference can only reuse exact prompt prefixes.
+* Partial prefix hits honour ``num_computed_tokens`` (``skip_slots``) instead of assuming 0.
+* A failed load is reported through ``take_load_errors`` so the engine recomputes; a
+  reservation whose request finishes without a store is aborted.
+* Staging memory is persistent (pinned host or device arena), never allocated per step.
+* An optional HBM tier (:mod:`daser_b200.kv.hbm_store`) serves hot chunks without IO.
+"""
+
+from __future__ import annotations
+
+import os
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional, Sequence
+
+import torch
+
+from daser_b200 import metrics
+from daser_b200.config import CODEC_FP8B16
+from daser_b200.connector.ipc_client import IPCClientSync
+from daser_b200.hashing import hash_tokens
+from daser_b200.io.engine import preallocate
+from daser_b200.kv import codec
+from daser_b200.kv.layout import KVGeometry, tp_head_range
+from daser_b200.logging import init_logger, init_perf_logger
+
+logger = init_logger(__name__)
+_perf = init_perf_logger("connector")
+
+
+@dataclass
+class ReqLoadSpec:
+    """One chunk to restore into a request's blocks."""
+
+    chunk_key: str
+    start_slot: int
+    num_slots: int
+    block_ids: list[int]
+    file_offset: int
+    token_count: int
+    # additions
+    pos_offset: int = 0  # position the stored keys are rotated to
+    dst_token_offset: int = 0  # position of the chunk's first token in this request
+    skip_slots: int = 0  # leading slots the engine already has (num_computed_tokens)
+    req_id: str = ""
+
+    @property
+    def delta(self) -> int:
+        return self.dst_token_offset - self.pos_offset
+
+
+@dataclass
+class ReqStoreSpec:
+    """One chunk to write from a request's blocks."""
+
+    chunk_key: str
+    start_slot: int
+    num_slots: int
+    block_ids: list[int]
+    file_offset: int
+    token_count: int
+    pos_offset: int = 0
+    first_block_digest: str = ""
+    req_id: str = ""
+
+
+@dataclass
+class ConnectorMeta:
+    """What the scheduler half hands to the worker half for one engine step."""
+
+    reqs_to_load: list[ReqLoadSpec] = field(default_factory=list)
+    reqs_to_store: list[ReqStoreSpec] = field(default_factory=list)
+
+
+# =========================================================================================
+# scheduler half
+# =========================================================================================
+
+
+class SchedulerHalf:
+    def __init__(self, socket_path: str, block_tokens: int = 16, model_id: str = "default",
+                 client: Optional[IPCClientSync] = None) -> None:
+        self.block_tokens = block_tokens
+        self.model_id = model_id
+        self._ipc = client or IPCClientSync(socket_path)
+        self._pending_loads: dict[str, list[ReqLoadSpec]] = {}
+        self._pending_stores: dict[str, ReqStoreSpec] = {}
+        self._pending_alloc: dict[str, dict[str, Any]] = {}
+        self._stored: set[str] = set()
+
+    # -- prefix reuse (reference behaviour) -----------------------------------------------
+    def get_num_new_matched_tokens(self, req_id: str, prompt_token_ids: Sequence[int],
+                                   num_computed_tokens: int) -> tuple[int, bool]:
+        """Tokens the connector can supply beyond ``num_computed_tokens`` (never asynchronous).
+
+        One ``match_and_alloc`` round trip: a hit remembers the chunk to load, a miss
+        remembers the server-side reservation to store into.  Repeated calls for the same
+        request are harmless (the server returns the same reservation).
+        """
+        bt = self.block_tokens
+        tokens = list(prompt_token_ids)
+        aligned = (len(tokens) // bt) * bt
+        if aligned == 0:
+            return 0, False
+        store_key = hash_tokens(tokens[:aligned])
+        t0 = time.perf_counter()
+        try:
+            chunks, alloc = self._ipc.match_and_alloc(tokens, store_key, self.model_id)
+        except RuntimeError as exc:
+            logger.warning("[CONNECTOR] lookup failed for %s (%s): treating as a miss", req_id, exc)
+            metrics.inc("connector.rpc_errors")
+            return 0, False
+        _perf.record("match_and_alloc_ms", (time.perf_counter() - t0) * 1e3, "ms")
+        if chunks:
+            best = chunks[0]
+            usable = min(best["token_count"], aligned)
+            # never claim the whole prompt: the engine must compute at least one token
+            if usable >= len(tokens):
+                usable = ((len(tokens) - 1) // bt) * bt
+            extra = usable - num_computed_tokens
+            if extra <= 0:
+                return 0, False
+            skip = num_computed_tokens // bt
+            self._pending_loads[req_id] = [
+                ReqLoadSpec(
+                    chunk_key=best["chunk_key"], start_slot=best["start_slot"], num_slots=best["num_slots"],
+                    block_ids=[], file_offset=best["file_offset"], token_count=usable,
+                    pos_offset=best.get("pos_offset", 0), dst_token_offset=best.get("pos_offset", 0),
+                    skip_slots=skip, req_id=req_id,
+                )
+            ]
+            metrics.inc("connector.prefix_hits")
+            return extra, False
+        if alloc is not None:
+            self._pending_alloc[req_id] = dict(alloc, first_block=hash_tokens(tokens[:bt]))
+        metrics.inc("connector.prefix_misses")
+        return 0, False
+
+    # -- chunk reuse at arbitrary offsets ----------------------------------------------------
+    def plan_chunk_loads(self, req_id: str, placements: Sequence[tuple[str, int]]) -> list[Optional[ReqLoadSpec]]:
+        """Resolve ``(chunk_key, token offset)`` pairs; returns one spec (or None) per pair.
+
+        Offsets must be block aligned.  Found chunks are queued for the request; the caller
+        assigns their blocks with :meth:`assign_chunk_blocks`.
+        """
+        bt = self.block_tokens
+        for _, off in placements:
+            if off % bt:
+                raise ValueError("chunk placements must be block aligned")
+        try:
+            found = self._ipc.lookup_chunks([k for k, _ in placements], self.model_id)
+        except RuntimeError as exc:
+            logger.warning("[CONNECTOR] lookup_chunks failed for %s (%s)", req_id, exc)
+            metrics.inc("connector.rpc_errors")
+            found = [None] * len(placements)
+        specs: list[Optional[ReqLoadSpec]] = []
+        for (key, off), meta in zip(placements, found):
+            if meta is None:
+                metrics.inc("connector.chunk_misses")
+                specs.append(None)
+                continue
+            metrics.inc("connector.chunk_hits")
+            specs.append(
+                ReqLoadSpec(
+                    chunk_key=key, start_slot=meta["start_slot"], num_slots=meta["num_slots"], block_ids=[],
+                    file_offset=meta["file_offset"], token_count=meta["token_count"],
+                    pos_offset=meta.get("pos_offset", 0), dst_token_offset=off, req_id=req_id,
+                )
+            )
+        self._pending_loads.setdefault(req_id, []).extend(s for s in specs if s is not None)
+        return specs
+
+    def assign_chunk_blocks(self, req_id: str, request_block_ids: Sequence[int]) -> None:
+        """Give every queued chunk load of ``req_id`` the request blocks its tokens fall into."""
+        bt = self.block_tokens
+        for spec in self._pending_loads.get(req_id, []):
+            first = spec.dst_token_offset // bt + spec.skip_slots
+            n = -(-spec.token_count // bt) - spec.skip_slots
+            spec.block_ids = list(request_block_ids[first : first + n])
+
+    def reserve_chunk_store(self, req_id: str, tokens: Sequence[int], block_ids: Sequence[int],
+                            pos_offset: int = 0) -> Optional[ReqStoreSpec]:
+        """Reserve slots for storing ``tokens`` (a whole number of blocks) keyed by their hash."""
+        bt = self.block_tokens
+        aligned = (len(tokens) // bt) * bt
+        if aligned == 0:
+            return None
+        key = hash_tokens(list(tokens[:aligned]))
+        try:
+            a = self._ipc.alloc_chunk(key, aligned, self.model_id, pos_offset=pos_offset)
+        except RuntimeError as exc:
+            logger.info("[CONNECTOR] no reservation for %s: %s", key, exc)
+            return None
+        spec = ReqStoreSpec(
+            chunk_key=key, start_slot=a["start_slot"], num_slots=a["num_slots"],
+            block_ids=list(block_ids[: a["num_slots"]]), file_offset=a["file_offset"], token_count=aligned,
+            pos_offset=pos_offset, first_block_digest=hash_tokens(list(tokens[:bt])), req_id=req_id,
+        )
+        self._pending_stores[req_id] = spec
+        return spec
+
+    # -- reference hooks -------------------------------------------------------------------------
+    def update_state_after_alloc(self, req_id: str, block_ids: Sequence[int], num_external_tokens: int) -> None:
+        bt = self.block_tokens
+        loads = self._pending_loads.get(req_id)
+        if loads and num_external_tokens > 0:
+            spec = loads[0]
+            first = spec.skip_slots
+            n = -(-spec.token_count // bt) - first
+            spec.block_ids = list(block_ids[first : first + n])
+            return
+        alloc = self._pending_alloc.pop(req_id, None)
+        if alloc is not None:
+            n = -(-alloc["token_count"] // bt)
+            self._pending_stores[req_id] = ReqStoreSpec(
+                chunk_key=alloc["chunk_key"], start_slot=alloc["start_slot"], num_slots=alloc["num_slots"],
+                block_ids=list(block_ids[:n]), file_offset=alloc["file_offset"],
+                token_count=alloc["token_count"], pos_offset=alloc.get("pos_offset", 0),
+                first_block_digest=alloc.get("first_block", ""), req_id=req_id,
+            )
+
+    def build_connector_meta(self, scheduled_req_ids: Sequence[str]) -> ConnectorMeta:
+        meta = ConnectorMeta()
+        for req_id in scheduled_req_ids:
+            loads = self._pending_loads.get(req_id)
+            if loads and all(s.block_ids for s in loads):
+                meta.reqs_to_load.extend(self._pending_loads.pop(req_id))
+            store = self._pending_stores.get(req_id)
+            if store is not None and store.block_ids:
+                meta.reqs_to_store.append(self._pending_stores.pop(req_id))
+                self._stored.add(store.chunk_key)
+        if meta.reqs_to_load or meta.reqs_to_store:
+            logger.debug("[CONNECTOR] step meta: %d loads, %d stores", len(meta.reqs_to_load),
+                         len(meta.reqs_to_store))
+        return meta
+
+    def request_finished(self, req_id: str) -> tuple[bool, Optional[dict]]:
+        self._pending_loads.pop(req_id, None)
+        leftovers = [self._pending_alloc.pop(req_id, None), self._pending_stores.pop(req_id, None)]
+        for item in leftovers:
+            key = item["chunk_key"] if isinstance(item, dict) else getattr(item, "chunk_key", None)
+            if key and key not in self._stored:
+                try:
+                    self._ipc.abort_chunk(key)
+                except RuntimeError:
+                    pass
+        return False, None
+
+    def close(self) -> None:
+        self._ipc.close()
+
+
+# =========================================================================================
+# KV backends: how slot images get into and out of a paged pool
+# =========================================================================================
+
+
+class TorchKVBackend:
+    """Pure-PyTorch restore/save on a ``[L, N, 2, H, B, D]`` pool (CPU engine and oracle)."""
+
+    device_kind = "cpu"
+
+    def __init__(self, geo: KVGeometry, pool_data: torch.Tensor, inv_freq: Sequence[float],
+                 tp: int = 1, rank: int = 0) -> None:
+        self.geo = geo
+        self.pool = pool_data
+        self.inv_freq = list(inv_freq)
+        self.tp, self.rank = tp, rank
+        self.h0, self.hn = tp_head_range(geo.num_kv_heads, tp, rank)
+
+    def _split(self, images: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """uint8 ``[n, slot_size]`` -> float32 K, V ``[n, L, B, H, D]`` (all heads)."""
+        g = self.geo
+        n = images.shape[0]
+        per_layer = images.reshape(n, g.num_layers, g.layer_size)
+        shape = (n, g.num_layers, 2, g.block_tokens, g.num_kv_heads, g.head_dim)
+        if g.codec == CODEC_FP8B16:
+            pay = per_layer[..., : g.payload_bytes_per_layer].reshape(shape)
+            sc = per_layer[..., g.payload_bytes_per_layer :].contiguous().view(torch.float32)
+            kv = codec.dequantize_fp8b16(pay, sc.reshape(*shape[:-1], g.head_dim // 16))
+        else:
+            dt = {2: torch.bfloat16, 4: torch.float32}[g.dtype_bytes]
+            kv = per_layer.contiguous().view(dt).reshape(shape).float()
+        return kv[:, :, 0], kv[:, :, 1]
+
+    def restore(self, images: torch.Tensor, block_ids: Sequence[int], deltas: Sequence[int]) -> None:
+        if len(block_ids) == 0:
+            return
+        k, v = self._split(images.cpu())
+        for i, d in enumerate(deltas):
+            if d:
+                k[i] = codec.rope_delta_rotate(k[i], int(d), self.inv_freq)
+        sl = slice(self.h0, self.h0 + self.hn)
+        idx = torch.as_tensor(list(block_ids), dtype=torch.long)
+        # [n, L, B, H, D] -> pool [L, N, kv, H, B, D]
+        self.pool[:, idx, 0] = k[..., sl, :].permute(1, 0, 3, 2, 4).to(self.pool.dtype).to(self.pool.device)
+        self.pool[:, idx, 1] = v[..., sl, :].permute(1, 0, 3, 2, 4).to(self.pool.dtype).to(self.pool.device)
+
+    def save(self, block_ids: Sequence[int], images: torch.Tensor) -> None:
+        """Write this rank's head slice of each block into ``images`` (uint8 ``[n, slot_size]``)."""
+        g = self.geo
+        idx = torch.as_tensor(list(block_ids), dtype=torch.long)
+        blk = self.pool[:, idx].cpu()  # [L, n, 2, H, B, D]
+        for i in range(len(block_ids)):
+            for layer in range(g.num_layers):
+                k_new = blk[layer, i, 0].permute(1, 0, 2)  # [B, Hloc, D]
+                v_new = blk[layer, i, 1].permute(1, 0, 2)
+                region = images[i, layer * g.layer_size : (layer + 1) * g.layer_size]
+                if self.tp == 1:
+                    k_full, v_full = k_new, v_new
+                else:
+                    k_full, v_full = codec.unpack_layer(g, region, torch.float32)
+                    k_full[:, self.h0 : self.h0 + self.hn] = k_new.float()
+                    v_full[:, self.h0 : self.h0 + self.hn] = v_new.float()
+                dt = {2: torch.bfloat16, 4: torch.float32}[g.dtype_bytes]
+                region.copy_(codec.pack_layer(g, k_full.to(dt), v_full.to(dt)))
+
+
+class CudaKVBackend:
+    """Fused sm_100a restore/save kernels on a :class:`~daser_b200.ops.kv_ops.PagedKVPool`."""
+
+    device_kind = "cuda"
+
+    def __init__(self, geo: KVGeometry, pool, inv_freq: Sequence[float], max_pos: int = 8192,
+                 rank: int = 0, max_slots: int = 4096, device: Optional[torch.device] = None) -> None:
+        from daser_b200.ops import kv_ops
+
+        self._ops = kv_ops
+        self.geo, self.pool, self.rank = geo, pool, rank
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.cos_sin = kv_ops.rope_table(max_pos, inv_freq, self.device)
+        self.status = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.max_slots = max_slots
+        # persistent work-list buffers: pinned host mirror + device copy
+        self._h = torch.empty((3, max_slots), dtype=torch.int64).pin_memory()
+        self._d_ptr = torch.empty(max_slots, dtype=torch.int64, device=self.device)
+        self._d_blk = torch.empty(max_slots, dtype=torch.int32, device=self.device)
+        self._d_dlt = torch.empty(max_slots, dtype=torch.int32, device=self.device)
+
+    def _worklist(self, ptrs: Sequence[int], block_ids: Sequence[int], deltas: Optional[Sequence[int]]):
+        n = len(block_ids)
+        if n > self.max_slots:
+            raise ValueError(f"{n} slots in one step exceeds max_slots={self.max_slots}")
+        h = self._h
+        h[0, :n] = torch.as_tensor(list(ptrs), dtype=torch.int64)
+        h[1, :n] = torch.as_tensor(list(block_ids), dtype=torch.int64)
+        h[2, :n] = torch.as_tensor(list(deltas) if deltas is not None else [0] * n, dtype=torch.int64)
+        self._d_ptr[:n].copy_(h[0, :n], non_blocking=True)
+        self._d_blk[:n].copy_(h[1, :n], non_blocking=True)
+        self._d_dlt[:n].copy_(h[2, :n], non_blocking=True)
+        return self._ops.KVWorkList(self._d_ptr[:n], self._d_blk[:n], self._d_dlt[:n] if deltas is not None else None)
+
+    def restore_ptrs(self, ptrs: Sequence[int], block_ids: Sequence[int], deltas: Sequence[int]) -> None:
+        if not block_ids:
+            return
+        self._ops.kv_restore(self._worklist(ptrs, block_ids, deltas), self.geo, self.pool, self.cos_sin, self.status)
+
+    def save_ptrs(self, ptrs: Sequence[int], block_ids: Sequence[int]) -> None:
+        if not block_ids:
+            return
+        self._ops.kv_save(self._worklist(ptrs, block_ids, None), self.geo, self.pool, self.rank, self.status)
+
+    def check_status(self) -> None:
+        code, slot = self.status.tolist()
+        if code:
+            self.status.zero_()
+            raise RuntimeError(f"KV kernel reported error {code} at work item {slot}")
+
+
+# =========================================================================================
+# worker half
+# =========================================================================================
+
+
+class WorkerHalf:
+    """Moves KV between the store file, the optional HBM tier and the paged pool."""
+
+    def __init__(self, socket_path: str, store_path: str, geo: KVGeometry, backend: Any,
+                 io_backend: str = "auto", tp: int = 1, rank: int = 0, hbm_store: Any = None,
+                 client: Optional[IPCClientSync] = None, staging_slots: int = 256,
+                 create_store_slots: int = 1024, commit: bool = True) -> None:
+        from daser_b200.connector.transfer import TransferLayer
+
+        self.geo = geo
+        self.kv = backend
+        self.tp, self.rank = tp, rank
+        self.hbm = hbm_store
+        self._ipc = client or IPCClientSync(socket_path)
+        self._commit = commit
+        if not os.path.exists(store_path):
+            # the reference zero-fills max(slot_size * 1024, 64 MiB) through user space
+            preallocate(store_path, max(geo.slot_size * create_store_slots, 64 << 20))
+        is_cuda = backend.device_kind == "cuda"
+        self._xfer = TransferLayer(store_path, backend=io_backend,
+                                   device=torch.cuda.current_device() if is_cuda else None)
+        # persistent staging: pinned host memory (readable by the kernels through UVA) for
+        # host IO backends, device memory for GDS
+        self._staging_slots = staging_slots
+        nbytes = staging_slots * geo.slot_size
+        if is_cuda and self._xfer.backend.name == "GDS":
+            self._staging = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        elif is_cuda:
+            self._staging = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+        else:
+            self._staging = torch.empty(nbytes, dtype=torch.uint8)
+        self._meta: Optional[ConnectorMeta] = None
+        self._load_errors: set[int] = set()
+        self._lock = threading.Lock()
+        self.last_load_bytes = 0
+        self.last_load_io_ms = 0.0
+
+    @property
+    def transfer(self):
+        return self._xfer
+
+    # -- metadata -------------------------------------------------------------------------------
+    def bind_connector_metadata(self, meta: ConnectorMeta) -> None:
+        self._meta = meta
+
+    def clear_connector_metadata(self) -> None:
+        self._meta = None
+
+    # -- load -------------------------------------------------------------------------------------
+    def start_load_kv(self) -> None:
+        """Restore every chunk named by the bound metadata (synchronous with the step)."""
+        meta = self._meta
+        if meta is None or not meta.reqs_to_load:
+            return
+        g = self.geo
+        jobs: list[tuple[ReqLoadSpec, int, int, int]] = []  # (spec, first staging slot, n slots, hbm base ptr)
+        used = 0
+        for spec in meta.reqs_to_load:
+            n = len(spec.block_ids)
+            if n == 0:
+                continue
+            hit = self.hbm.lookup(spec.chunk_key) if self.hbm is not None else None
+            if hit is not None:
+                jobs.append((spec, -1, n, hit + spec.skip_slots * g.slot_size))
+                metrics.inc("connector.hbm_hits")
+                continue
+            if used + n > self._staging_slots:
+                self._run_loads(jobs)  # staging full: flush what we have, then go on
+                jobs, used = [], 0
+            if n > self._staging_slots:
+                raise ValueError(f"chunk of {n} slots exceeds staging capacity {self._staging_slots}")
+            jobs.append((spec, used, n, 0))
+            used += n
+        self._run_loads(jobs)
+
+    def _run_loads(self, jobs) -> None:
+        if not jobs:
+            return
+        g = self.geo
+        t0 = time.perf_counter()
+        tickets = []
+        eng = self._xfer.engine
+        dev_staging = self._staging.is_cuda
+        nbytes_total = 0
+        for spec, first, n, hbm_ptr in jobs:
+            if first < 0:
+                continue
+            off = spec.file_offset + spec.skip_slots * g.slot_size
+            nbytes = n * g.slot_size
+            ptr = self._staging.data_ptr() + first * g.slot_size
+            try:
+                tickets.append((spec, eng.submit_read(ptr, off, nbytes, device=dev_staging)))
+            except OSError as exc:
+                logger.warning("[CONNECTOR] read submit failed for %s: %s", spec.chunk_key, exc)
+                tickets.append((spec, None))
+            nbytes_total += nbytes
+        failed: set[str] = set()
+        for spec, ticket in tickets:
+            try:
+                if ticket is None:
+                    raise OSError("submit failed")
+                eng.wait(ticket)
+            except (OSError, TimeoutError) as exc:
+                logger.warning("[CONNECTOR] load of %s failed: %s", spec.chunk_key, exc)
+                failed.add(spec.chunk_key)
+                self._load_errors.update(spec.block_ids)
+                metrics.inc("connector.load_errors")
+        io_ms = (time.perf_counter() - t0) * 1e3
+        self.last_load_bytes, self.last_load_io_ms = nbytes_total, io_ms
+        if nbytes_total:
+            _perf.record("load_io_ms", io_ms, "ms")
+            metrics.inc("connector.bytes_loaded", nbytes_total)
+        ptrs: list[int] = []
+        blocks: list[int] = []
+        deltas: list[int] = []
+        for spec, first, n, hbm_ptr in jobs:
+            if spec.chunk_key in failed:
+                continue
+            base = hbm_ptr if first < 0 else self._staging.data_ptr() + first * g.slot_size
+            for i in range(n):
+                ptrs.append(base + i * g.slot_size)
+                blocks.append(spec.block_ids[i])
+                deltas.append(spec.delta)
+        if self.kv.device_kind == "cuda":
+            self.kv.restore_ptrs(ptrs, blocks, deltas)
+            if self.hbm is not None:
+                for spec, first, n, _ in jobs:
+                    if first >= 0 and spec.chunk_key not in failed and spec.skip_slots == 0:
+                        self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+            torch.cuda.current_stream().synchronize()  # staging is reused by the next step
+            self.kv.check_status()
+        else:
+            base0 = self._staging.data_ptr()
+            rows = [(p - base0) // g.slot_size for p in ptrs]
+            images = self._staging.view(-1, g.slot_size)[torch.as_tensor(rows, dtype=torch.long)]
+            self.kv.restore(images, blocks, deltas)
+
+    def wait_for_layer_load(self, layer_name: str) -> None:
+        """Nothing to wait for: loads complete inside :meth:`start_load_kv`."""
+
+    def take_load_errors(self) -> set[int]:
+        """Block ids whose load failed since the last call (the engine recomputes them)."""
+        out, self._load_errors = self._load_errors, set()
+        return out
+
+    # -- save --------------------------------------------------------------------------------------
+    def save_kv_layer(self, layer_name: str, kv_layer: Any = None, attn_metadata: Any = None) -> None:
+        """Nothing per layer: the blocks stay in the pool until :meth:`wait_for_save`, which
+        gathers all layers with one launch."""
+
+    def wait_for_save(self, barrier: Optional[Callable[[], None]] = None) -> None:
+        meta = self._meta
+        if meta is None or not meta.reqs_to_store:
+            return
+        g = self.geo
+        pending = list(meta.reqs_to_store)
+        while pending:
+            batch, used = [], 0
+            while pending and used + len(pending[0].block_ids) <= self._staging_slots:
+                spec = pending.pop(0)
+                batch.append((spec, used))
+                used += len(spec.block_ids)
+            if not batch:
+                raise ValueError("chunk larger than the staging arena")
+            self._store_batch(batch, barrier)
+
+    def _store_batch(self, batch, barrier) -> None:
+        g = self.geo
+        ptrs, blocks = [], []
+        for spec, first in batch:
+            for i, b in enumerate(spec.block_ids):
+                ptrs.append(self._staging.data_ptr() + (first + i) * g.slot_size)
+                blocks.append(b)
+        if self.kv.device_kind == "cuda":
+            self.kv.save_ptrs(ptrs, blocks)
+            torch.cuda.current_stream().synchronize()  # images complete before the IO reads them
+            self.kv.check_status()
+        else:
+            n = len(blocks)
+            images = self._staging.view(-1, g.slot_size)[:n]
+            self.kv.save(blocks, images)
+        if barrier is not None:
+            barrier()  # every rank's head slice is in the owner's staging
+        if not self._commit:
+            return
+        eng = self._xfer.engine
+        dev_staging = self._staging.is_cuda
+        tickets = []
+        for spec, first in batch:
+            n = len(spec.block_ids)
+            ptr = self._staging.data_ptr() + first * g.slot_size
+            tickets.append((spec, first, n, eng.submit_write(ptr, spec.file_offset, n * g.slot_size, device=dev_staging)))
+        for spec, first, n, ticket in tickets:
+            try:
+                eng.wait(ticket)
+            except (OSError, TimeoutError) as exc:
+                logger.error("[CONNECTOR] store of %s failed: %s (reservation aborted)", spec.chunk_key, exc)
+                metrics.inc("connector.store_errors")
+                try:
+                    self._ipc.abort_chunk(spec.chunk_key)
+                except RuntimeError:
+                    pass
+                continue
+            metrics.inc("connector.bytes_stored", n * g.slot_size)
+            if self.hbm is not None and self.kv.device_kind == "cuda":
+                self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+            try:
+                extra = {"first_block": spec.first_block_digest} if spec.first_block_digest else {}
+                self._ipc.commit_chunk(spec.chunk_key, **extra)
+            except RuntimeError as exc:
+                logger.error("[CONNECTOR] commit of %s failed: %s", spec.chunk_key, exc)
+
+    def get_stats(self) -> dict[str, float]:
+        return {k: v for k, v in metrics.snapshot().items() if k.startswith(("connector.", "transfer."))}
+
+    def shutdown(self) -> None:
+        try:
+            self._xfer.close()
+        finally:
+            self._ipc.close()

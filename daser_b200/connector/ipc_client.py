@@ -97,15 +97,17 @@ class IPCClientSync:
         )
         return reply.get("chunks", []), reply.get("alloc")
 
-    def alloc_chunk(self, chunk_key: str, token_count: int, model_id: str) -> dict[str, Any]:
-        return self.call(
-            {
-                "op": frames.OP_ALLOC_CHUNK,
-                "chunk_key": chunk_key,
-                "token_count": token_count,
-                "model_id": model_id,
-            }
-        )
+    def alloc_chunk(self, chunk_key: str, token_count: int, model_id: str,
+                    pos_offset: Optional[int] = None) -> dict[str, Any]:
+        payload: dict[str, Any] = {
+            "op": frames.OP_ALLOC_CHUNK,
+            "chunk_key": chunk_key,
+            "token_count": token_count,
+            "model_id": model_id,
+        }
+        if pos_offset is not None:
+            payload["pos_offset"] = pos_offset
+        return self.call(payload)
 
     def commit_chunk(self, chunk_key: str, **extra: Any) -> None:
         self.call({"op": frames.OP_COMMIT_CHUNK, "chunk_key": chunk_key, **extra})

@@ -1,0 +1,164 @@
+"""CPU RAG engine: the toy decoder served through the connector with no GPU.
+
+This is the minimum end-to-end slice: control plane, io_uring/file storage engine,
+connector core, position re-encoding and a paged-KV decoder, all on CPU tensors.
+Document chunks are prefilled stand-alone at positions ``0..n-1`` and stored; a request
+``[prefix][chunk ...][query]`` restores each chunk at its new offset (keys rotated by the
+offset) and only computes the prefix and the query.
+
+The reference cannot do this: its service stores chunks keyed by their own hash but its
+only lookup matches whole prompt prefixes, and nothing applies ``pos_offset``
+(``daser/service/http_api.py:138-146``, ``daser/retrieval/prefix.py:63-72``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from daser_b200.connector.core import ConnectorMeta, SchedulerHalf, TorchKVBackend, WorkerHalf
+from daser_b200.hashing import hash_tokens
+from daser_b200.kv.layout import KVGeometry
+from daser_b200.models.llama import LlamaConfig, LlamaWeights, TorchPagedKV, reference_forward
+
+
+class BlockAllocator:
+    """Free-list allocator of pool blocks."""
+
+    def __init__(self, num_blocks: int) -> None:
+        self._free = list(range(num_blocks - 1, -1, -1))
+        self.num_blocks = num_blocks
+
+    def alloc(self, n: int) -> list[int]:
+        if n > len(self._free):
+            raise MemoryError(f"need {n} KV blocks, {len(self._free)} free")
+        return [self._free.pop() for _ in range(n)]
+
+    def free(self, blocks: Sequence[int]) -> None:
+        self._free.extend(blocks)
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+
+@dataclass
+class RequestResult:
+    logits: torch.Tensor
+    block_table: list[int]
+    chunk_offsets: list[int]
+    restored: list[bool]
+    total_tokens: int
+
+
+class CpuRagEngine:
+    def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 512,
+                 codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
+                 io_backend: str = "auto", model_id: str = "default") -> None:
+        self.cfg = cfg
+        self.weights = LlamaWeights.random(cfg, "cpu", dtype, seed=seed)
+        self.pool = TorchPagedKV(cfg, num_blocks, dtype)
+        self.blocks = BlockAllocator(num_blocks)
+        self.geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens,
+                              {torch.float32: 4, torch.bfloat16: 2}[dtype], codec_name)
+        self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id)
+        self.worker = WorkerHalf(socket_path, store_path, self.geo,
+                                 TorchKVBackend(self.geo, self.pool.data, cfg.inv_freq()), io_backend=io_backend)
+        self._req = 0
+
+    def _next_id(self) -> str:
+        self._req += 1
+        return f"req-{self._req}"
+
+    def _step(self, meta: ConnectorMeta, fn):
+        self.worker.bind_connector_metadata(meta)
+        try:
+            self.worker.start_load_kv()
+            out = fn()
+            self.worker.wait_for_save()
+        finally:
+            self.worker.clear_connector_metadata()
+        return out
+
+    # -- offline: fill the chunk store -----------------------------------------------------
+    def store_chunk(self, tokens: Sequence[int]) -> str:
+        """Prefill ``tokens`` alone at positions 0.. and store their KV; returns the chunk key."""
+        bt = self.cfg.block_tokens
+        tokens = list(tokens)
+        if len(tokens) % bt:
+            raise ValueError("chunks must be a whole number of blocks")
+        req = self._next_id()
+        table = self.blocks.alloc(len(tokens) // bt)
+        spec = self.sched.reserve_chunk_store(req, tokens, table, pos_offset=0)
+        meta = self.sched.build_connector_meta([req]) if spec is not None else ConnectorMeta()
+
+        def run():
+            t = torch.tensor(tokens)
+            reference_forward(self.weights, t, torch.arange(len(tokens)), self.pool, torch.tensor(table), 0,
+                              return_logits=False)
+
+        self._step(meta, run)
+        self.sched.request_finished(req)
+        self.blocks.free(table)
+        return hash_tokens(tokens)
+
+    # -- online: a RAG request -----------------------------------------------------------------
+    def run_request(self, prefix: Sequence[int], chunks: Sequence[Sequence[int]], query: Sequence[int],
+                    keep_blocks: bool = False) -> RequestResult:
+        bt = self.cfg.block_tokens
+        if len(prefix) % bt:
+            raise ValueError("the prefix must end on a block boundary")
+        req = self._next_id()
+        offsets, pos = [], len(prefix)
+        for c in chunks:
+            if len(c) % bt:
+                raise ValueError("chunks must be a whole number of blocks")
+            offsets.append(pos)
+            pos += len(c)
+        total = pos + len(query)
+        table = self.blocks.alloc(-(-total // bt))
+        tbl = torch.tensor(table)
+        placements = [(hash_tokens(list(c)), off) for c, off in zip(chunks, offsets)]
+        specs = self.sched.plan_chunk_loads(req, placements)
+        self.sched.assign_chunk_blocks(req, table)
+        meta = self.sched.build_connector_meta([req])
+
+        def run():
+            # the prefix is computed, then every chunk that could not be restored, then the query
+            ctx = 0
+            if prefix:
+                reference_forward(self.weights, torch.tensor(list(prefix)), torch.arange(len(prefix)), self.pool,
+                                  tbl, 0, return_logits=False)
+            ctx = len(prefix)
+            for c, off, spec in zip(chunks, offsets, specs):
+                if spec is None:
+                    reference_forward(self.weights, torch.tensor(list(c)), torch.arange(off, off + len(c)),
+                                      self.pool, tbl, ctx, return_logits=False)
+                ctx = off + len(c)
+            return reference_forward(self.weights, torch.tensor(list(query)), torch.arange(ctx, ctx + len(query)),
+                                     self.pool, tbl, ctx)
+
+        logits = self._step(meta, run)
+        self.sched.request_finished(req)
+        if not keep_blocks:
+            self.blocks.free(table)
+        return RequestResult(logits, table, offsets, [s is not None for s in specs], total)
+
+    def recompute_chunk_alone(self, chunk: Sequence[int], offset: int) -> tuple[list[int], int]:
+        """Run ``chunk`` alone at positions ``offset..``; returns its (fresh) blocks and length.
+
+        RoPE attention depends only on position differences, so the hidden states, the values
+        and the un-rotated keys equal those of the stand-alone prefill at 0: the restored,
+        re-rotated KV must match this recomputation.
+        """
+        bt = self.cfg.block_tokens
+        table = self.blocks.alloc(len(chunk) // bt)
+        reference_forward(self.weights, torch.tensor(list(chunk)), torch.arange(offset, offset + len(chunk)),
+                          self.pool, torch.tensor(table), 0, return_logits=False)
+        return table, len(chunk)
+
+    def close(self) -> None:
+        self.worker.shutdown()
+        self.sched.close()

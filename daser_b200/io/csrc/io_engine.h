@@ -1,0 +1,65 @@
+// Storage engine: asynchronous reads/writes between one pre-allocated store file and
+// host or device memory.
+//
+// Replaces what the reference gets from kvikio (daser/connector/gds_transfer.py:29-127:
+// CuFile.pread/pwrite futures, GDS when available, a POSIX thread pool with a CPU bounce
+// buffer otherwise).  The reference's documentation also names an io_uring fallback that its
+// code does not contain; this engine has one.
+//
+// Backends, chosen once at open and immutable afterwards:
+//   GDS       cuFile (libcufile.so loaded at run time): NVMe <-> GPU memory DMA.
+//   IO_URING  raw io_uring (io_uring_setup / io_uring_enter, no liburing), O_DIRECT when the
+//             request is 4 KiB aligned, requests split into pieces for queue depth.
+//   POSIX     pread/pwrite on a worker pool.
+// IO_URING and POSIX move host memory only; the caller stages device data through pinned
+// host buffers (daser_b200/connector/transfer.py does it on a dedicated copy stream).
+//
+// All functions are thread safe.  A submit returns a ticket; wait(ticket) returns 0, a
+// negative errno, or DASER_IO_TIMEOUT.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DASER_IO_AUTO 0
+#define DASER_IO_GDS 1
+#define DASER_IO_URING 2
+#define DASER_IO_POSIX 3
+
+#define DASER_IO_TIMEOUT 1
+
+#define DASER_IO_API __attribute__((visibility("default")))
+
+typedef struct daser_io daser_io;
+
+// Opens an existing file read/write.  Returns NULL and fills `err` on failure (a missing file
+// reports ENOENT in *err_no).  `backend` = DASER_IO_AUTO tries GDS (only if `want_device`),
+// then io_uring, then POSIX.
+DASER_IO_API daser_io* daser_io_open(const char* path, int backend, int want_device, int queue_depth,
+                                     int nthreads, char* err, int err_len, int* err_no);
+DASER_IO_API int daser_io_backend(const daser_io* io);
+DASER_IO_API int64_t daser_io_file_size(const daser_io* io);
+
+// `device` != 0: buf is a CUDA device pointer (GDS backend only).
+DASER_IO_API int64_t daser_io_submit(daser_io* io, int is_write, void* buf, int device, int64_t file_offset,
+                                     int64_t nbytes);
+DASER_IO_API int daser_io_wait(daser_io* io, int64_t ticket, int timeout_ms);
+DASER_IO_API int daser_io_close(daser_io* io);
+
+// Creates (or extends) a file of `size` bytes without writing zeros through user space.
+DASER_IO_API int daser_io_preallocate(const char* path, int64_t size);
+
+// Fault injection for tests (host side only): the next `count` pieces complete with -err_no
+// (err_no > 0), or are cut short to `short_bytes` once (err_no == 0, short_bytes >= 0; the
+// engine must then resubmit the remainder).
+DASER_IO_API void daser_io_inject(daser_io* io, int count, int err_no, int64_t short_bytes);
+
+// Counters: [0] pieces submitted, [1] bytes read, [2] bytes written, [3] resubmits after short IO,
+// [4] direct-IO pieces.
+DASER_IO_API void daser_io_stats(const daser_io* io, int64_t out[5]);
+
+#ifdef __cplusplus
+}
+#endif

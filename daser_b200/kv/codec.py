@@ -33,8 +33,11 @@ def quantize_fp8b16(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     absmax = g.abs().amax(dim=-1, keepdim=True)
     nz = absmax > 0
     safe = torch.where(nz, absmax, torch.ones_like(absmax))
-    inv = torch.where(nz, E4M3_MAX / safe, torch.ones_like(absmax))
-    scale = torch.where(nz, safe / E4M3_MAX, torch.ones_like(absmax))
+    # tensor / tensor so both are true IEEE divisions (scalar operands make torch multiply
+    # by a reciprocal, which rounds differently from the kernels' div.rn)
+    top = torch.full_like(safe, E4M3_MAX)
+    inv = torch.where(nz, torch.div(top, safe), torch.ones_like(absmax))
+    scale = torch.where(nz, torch.div(safe, top), torch.ones_like(absmax))
     q = (g * inv).clamp_(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
     return q.view(torch.uint8).reshape(x.shape), scale.squeeze(-1).contiguous()
 

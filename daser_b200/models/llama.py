@@ -1,0 +1,251 @@
+"""Llama-family decoder: configuration, (sharded) weights and a plain-PyTorch forward.
+
+The reference has no model code; its engine is stock vLLM
+(``vllm/model_executor/models/llama.py``).  This module defines the architecture once:
+
+* :class:`LlamaConfig` with presets for the toy decoder of the CPU plumbing check,
+  Llama-3-8B and Llama-3-70B;
+* :class:`LlamaWeights` — random-init weights, already laid out per tensor-parallel rank
+  (QKV and gate/up column-sharded by heads / intermediate size, O and down row-sharded);
+* :func:`reference_forward` — an fp32 PyTorch forward over a paged KV pool.  It is the
+  CPU engine for the plumbing check and the numerical oracle for the CUDA engine
+  (:mod:`daser_b200.engine.runner`), which runs the same graph with the hand-written kernels.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from daser_b200.kv import codec
+from daser_b200.position.rope_reencoder import inv_freq_table
+
+
+@dataclass(frozen=True)
+class LlamaConfig:
+    name: str = "toy"
+    vocab_size: int = 32000
+    hidden: int = 256
+    num_layers: int = 2
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 64
+    intermediate: int = 512
+    rope_theta: float = 10000.0
+    rope_scaling: tuple = ()  # items of the scaling dict; empty = plain RoPE
+    rms_eps: float = 1e-5
+    block_tokens: int = 16
+    max_position: int = 8192
+
+    def scaling_dict(self) -> dict[str, Any]:
+        return dict(self.rope_scaling)
+
+    def inv_freq(self) -> list[float]:
+        return inv_freq_table(self.head_dim, self.rope_theta, self.scaling_dict())
+
+    @property
+    def q_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    def param_count(self) -> int:
+        per_layer = (
+            (self.q_size + 2 * self.kv_size) * self.hidden
+            + self.hidden * self.q_size
+            + 3 * self.intermediate * self.hidden
+            + 2 * self.hidden
+        )
+        return self.num_layers * per_layer + 2 * self.vocab_size * self.hidden + self.hidden
+
+
+_LLAMA3_SCALING = (
+    ("factor", 8.0),
+    ("low_freq_factor", 1.0),
+    ("high_freq_factor", 4.0),
+    ("original_max_position_embeddings", 8192),
+)
+
+PRESETS = {
+    # the CPU plumbing check: 2 layers, 4 heads / 2 KV heads, head_dim 64, hidden 256, theta 1e4
+    "toy": LlamaConfig(),
+    "llama3-8b": LlamaConfig("llama3-8b", 128256, 4096, 32, 32, 8, 128, 14336, 500000.0, _LLAMA3_SCALING,
+                             1e-5, 16, 131072),
+    "llama3-70b": LlamaConfig("llama3-70b", 128256, 8192, 80, 64, 8, 128, 28672, 500000.0, _LLAMA3_SCALING,
+                              1e-5, 16, 131072),
+    # small GPU test model with the 70B head geometry
+    "tiny-gqa": LlamaConfig("tiny-gqa", 1024, 512, 2, 8, 2, 128, 1024, 500000.0, (), 1e-5, 16, 8192),
+}
+
+
+@dataclass
+class LayerWeights:
+    input_norm: torch.Tensor
+    wqkv: torch.Tensor  # [(Hq + 2 Hkv) / tp * D, hidden]
+    wo: torch.Tensor  # [hidden, Hq / tp * D]
+    post_norm: torch.Tensor
+    w_gate_up: torch.Tensor  # [2 * I / tp, hidden]: gate rows then up rows
+    w_down: torch.Tensor  # [hidden, I / tp]
+
+
+@dataclass
+class LlamaWeights:
+    cfg: LlamaConfig
+    tp: int
+    rank: int
+    embed: torch.Tensor  # [vocab, hidden] (replicated)
+    layers: list[LayerWeights]
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor  # [vocab / tp, hidden]
+    meta: dict = field(default_factory=dict)
+
+    @property
+    def heads_local(self) -> int:
+        return self.cfg.num_heads // self.tp
+
+    @property
+    def kv_heads_local(self) -> int:
+        return max(1, self.cfg.num_kv_heads // self.tp)
+
+    @property
+    def inter_local(self) -> int:
+        return self.cfg.intermediate // self.tp
+
+    @property
+    def vocab_local(self) -> int:
+        return self.cfg.vocab_size // self.tp
+
+    @classmethod
+    def random(cls, cfg: LlamaConfig, device: str | torch.device = "cpu", dtype: torch.dtype = torch.float32,
+               tp: int = 1, rank: int = 0, seed: int = 0, std: float = 0.02) -> "LlamaWeights":
+        """Random-init weights for ``rank`` of ``tp``.
+
+        Tensors are filled in place on ``device`` (no full-size temporaries), so the 70B
+        model initialises inside one 180 GB GPU.  Every rank seeds per tensor from
+        ``(seed, tensor index)`` and generates only its own shard.
+        """
+        if cfg.num_heads % tp or cfg.intermediate % tp or cfg.vocab_size % tp:
+            raise ValueError("heads, intermediate size and vocabulary must divide by tp")
+        if cfg.num_kv_heads % tp and tp % cfg.num_kv_heads:
+            raise ValueError("kv heads and tp must divide one another")
+        gen = torch.Generator(device=device)
+        counter = [0]
+
+        def mat(rows: int, cols: int, shard: bool = True) -> torch.Tensor:
+            counter[0] += 1
+            gen.manual_seed(seed * 1_000_003 + counter[0] * 97 + (rank if shard else 0))
+            t = torch.empty((rows, cols), dtype=dtype, device=device)
+            t.normal_(0.0, std, generator=gen)
+            return t
+
+        def ones(n: int) -> torch.Tensor:
+            return torch.ones(n, dtype=dtype, device=device)
+
+        D = cfg.head_dim
+        hq, hkv = cfg.num_heads // tp, max(1, cfg.num_kv_heads // tp)
+        inter = cfg.intermediate // tp
+        embed = mat(cfg.vocab_size, cfg.hidden, shard=False)
+        layers = []
+        for _ in range(cfg.num_layers):
+            layers.append(
+                LayerWeights(
+                    input_norm=ones(cfg.hidden),
+                    wqkv=mat((hq + 2 * hkv) * D, cfg.hidden),
+                    wo=mat(cfg.hidden, hq * D),
+                    post_norm=ones(cfg.hidden),
+                    w_gate_up=mat(2 * inter, cfg.hidden),
+                    w_down=mat(cfg.hidden, inter),
+                )
+            )
+        return cls(cfg, tp, rank, embed, layers, ones(cfg.hidden), mat(cfg.vocab_size // tp, cfg.hidden))
+
+
+class TorchPagedKV:
+    """Head-major paged pool ``[L, N, 2, H, B, D]`` in a torch dtype (the CPU engine's pool)."""
+
+    def __init__(self, cfg: LlamaConfig, num_blocks: int, dtype: torch.dtype = torch.float32,
+                 device: str | torch.device = "cpu", kv_heads: Optional[int] = None) -> None:
+        self.cfg = cfg
+        self.num_blocks = num_blocks
+        self.kv_heads = kv_heads or cfg.num_kv_heads
+        self.data = torch.zeros(
+            cfg.num_layers, num_blocks, 2, self.kv_heads, cfg.block_tokens, cfg.head_dim, dtype=dtype, device=device
+        )
+
+    def write(self, layer: int, block_ids: torch.Tensor, offsets: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+        """``k, v``: ``[T, H, D]`` go to ``(block_ids[t], offsets[t])``."""
+        self.data[layer, block_ids, 0, :, offsets] = k.to(self.data.dtype)
+        self.data[layer, block_ids, 1, :, offsets] = v.to(self.data.dtype)
+
+    def gather(self, layer: int, block_table: torch.Tensor, length: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """K and V ``[length, H, D]`` of a sequence whose blocks are ``block_table``."""
+        blk = self.data[layer, block_table]  # [nb, 2, H, B, D]
+        kv = blk.permute(1, 0, 3, 2, 4).reshape(2, -1, self.kv_heads, self.cfg.head_dim)
+        return kv[0, :length], kv[1, :length]
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+@torch.no_grad()
+def reference_forward(
+    weights: LlamaWeights,
+    tokens: torch.Tensor,
+    positions: torch.Tensor,
+    pool: TorchPagedKV,
+    block_table: torch.Tensor,
+    context_len: int,
+    return_logits: bool = True,
+) -> torch.Tensor:
+    """Run ``tokens`` (at ``positions``) of ONE sequence through the model.
+
+    The sequence already has ``context_len`` tokens cached in ``pool`` (written earlier or
+    restored by the connector); the new tokens occupy cache slots ``context_len ..``.
+    K/V of the new tokens are written to the pool, attention is causal over cache + new
+    tokens.  Returns logits ``[T, vocab]`` (or the final hidden states).  Single rank only
+    (``weights.tp == 1``): this is the oracle, not the parallel engine.
+    """
+    cfg = weights.cfg
+    assert weights.tp == 1
+    T = tokens.numel()
+    D, Hq, Hkv = cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    dev = weights.embed.device
+    cos, sin = codec.rope_cos_sin(positions.cpu(), cfg.inv_freq())
+    cos, sin = cos.to(dev), sin.to(dev)
+    slots = torch.arange(context_len, context_len + T, device=dev)
+    blk = block_table.to(dev)[slots // cfg.block_tokens]
+    off = slots % cfg.block_tokens
+    total = context_len + T
+    h = weights.embed[tokens.to(dev).long()].float()
+    for li, lw in enumerate(weights.layers):
+        x = rms_norm(h, lw.input_norm, cfg.rms_eps)
+        qkv = x @ lw.wqkv.float().t()
+        q = qkv[:, : Hq * D].reshape(T, Hq, D)
+        k = qkv[:, Hq * D : (Hq + Hkv) * D].reshape(T, Hkv, D)
+        v = qkv[:, (Hq + Hkv) * D :].reshape(T, Hkv, D)
+        q = codec.rope_rotate(q, cos, sin)
+        k = codec.rope_rotate(k, cos, sin)
+        pool.write(li, blk, off, k, v)
+        k_all, v_all = pool.gather(li, block_table.to(dev), total)
+        k_all = k_all.float().repeat_interleave(Hq // Hkv, dim=1)
+        v_all = v_all.float().repeat_interleave(Hq // Hkv, dim=1)
+        scores = torch.einsum("thd,shd->hts", q, k_all) / (D**0.5)
+        key_pos = torch.arange(total, device=dev)
+        mask = key_pos[None, :] > (context_len + torch.arange(T, device=dev))[:, None]
+        scores = scores.masked_fill(mask[None], float("-inf"))
+        attn = torch.einsum("hts,shd->thd", scores.softmax(-1), v_all).reshape(T, Hq * D)
+        h = h + attn @ lw.wo.float().t()
+        x = rms_norm(h, lw.post_norm, cfg.rms_eps)
+        gu = x @ lw.w_gate_up.float().t()
+        inter = gu.shape[1] // 2
+        h = h + (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]) @ lw.w_down.float().t()
+    h = rms_norm(h, weights.final_norm, cfg.rms_eps)
+    if not return_logits:
+        return h
+    return h @ weights.lm_head.float().t()

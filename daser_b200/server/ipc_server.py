@@ -187,17 +187,17 @@ class IPCServer:
         self._ri.discard(meta.chunk_key)
         self._dirty = True
 
-    def _reserve(self, chunk_key: str, token_count: int, model_id: str) -> ChunkMeta:
+    def _reserve(self, chunk_key: str, token_count: int, model_id: str,
+                 pos_offset: Optional[int] = None) -> ChunkMeta:
         if token_count <= 0:
             raise ProtocolError("token_count must be positive")
         existing = self._cm.store.get(chunk_key)
         if existing is not None and self._cm.store.is_committed(chunk_key):
             raise ProtocolError(f"chunk_key already exists: {chunk_key}")
-        pos_offset = (
-            existing.pos_offset
-            if existing is not None
-            else self._pe.assign_offset(chunk_key, token_count)
-        )
+        if existing is not None:
+            pos_offset = existing.pos_offset
+        elif pos_offset is None:
+            pos_offset = self._pe.assign_offset(chunk_key, token_count)
         try:
             self._cm.alloc(
                 chunk_key,
@@ -222,8 +222,12 @@ class IPCServer:
         return {"chunks": [self._chunk_dict(m) for m in found]}
 
     async def _handle_alloc_chunk(self, msg: dict[str, Any]) -> dict[str, Any]:
+        # optional "pos_offset": the position the chunk's first token had when its KV was
+        # computed (defaults to the position encoder's assignment)
+        pos = msg.get("pos_offset")
         meta = self._reserve(
-            msg["chunk_key"], int(msg["token_count"]), msg.get("model_id", "default")
+            msg["chunk_key"], int(msg["token_count"]), msg.get("model_id", "default"),
+            int(pos) if pos is not None else None,
         )
         return {
             "start_slot": meta.start_slot,
