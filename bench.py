@@ -1,0 +1,325 @@
+"""Headline benchmark: RAG time-to-first-token and KV-restore rate, Llama-3-70B, TP = #GPUs.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...            # the reference arm
+
+A *step* is one RAG request served up to its first token through the engine's public call
+(``GpuRagEngine.generate``): the control plane is asked for the request's chunks, the cached
+chunks are read from the store (NVMe file or HBM tier) and restored at their new offsets by
+the fused dequantise + RoPE-re-rotate + scatter kernel, the query is prefilled over the
+restored context with the tcgen05 GEMMs and the fp8 paged attention, and the first token is
+sampled and read back.
+
+Traffic (synthetic, random-init weights): a 64-token system prefix + k chunks drawn
+Zipf(s = 1.1) from a pool of lognormal-length chunks (median 300 tokens, sigma 0.6, clipped
+to 64..1024, padded to whole 16-token blocks) + a 64-token query.  The pool is smaller than
+the 20k chunks of the full workload so that filling it (real prefills through the save
+kernel) fits the benchmark's time and the box's disk; its size is printed in ``config``.
+
+Timing: W untimed warm-up steps, then exactly K timed steps between a barrier +
+``torch.cuda.synchronize()`` on both sides.  ``value`` is the p50 over the K steps of the
+device-timed TTFT (CUDA events on the launching stream, max over ranks); ``e2e.value`` is the
+p50 wall-clock TTFT of the same steps including the pinned-host -> device copy of each
+step's inputs and the device -> host read of the sampled token.  Weights (tens of GB per
+GPU) are far larger than L2, so no input of a step is served from cache.
+"""
+
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import math
+import os
+import random
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "rag_ttft_p50_ms (Llama-3-70B, TP=#GPUs, chunk-KV restore from fp8 store)"
+
+
+def reference_arm(args) -> None:
+    """The unmodified reference needs ``kvikio`` and ``cupy`` at import time
+    (``daser/connector/gds_transfer.py:10-13``, ``daser/connector/daser_connector.py:14``);
+    neither is installed and there is no package index, so its connector cannot be imported."""
+    why = "reference connector imports kvikio and cupy at module scope; neither is installed offline"
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import importlib
+
+        importlib.import_module("daser.connector.daser_connector")
+        why = "reference imported but its vLLM path was not wired in this build"
+    except Exception as exc:  # noqa: BLE001
+        why = f"reference connector cannot be imported here: {type(exc).__name__}: {str(exc)[:120]}"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = os.path.join(tempfile.gettempdir(), f"daser_clocks_{os.getpid()}.csv")
+
+    def start(self) -> None:
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_traffic(cfg, pool_size: int, k_chunks: int, n_requests: int, seed: int = 0):
+    rng = random.Random(seed)
+    bt = cfg.block_tokens
+    pad = 0
+
+    def tokens(n):
+        return [rng.randrange(1, cfg.vocab_size) for _ in range(n)]
+
+    def padded(n):
+        t = tokens(n)
+        return t + [pad] * (-len(t) % bt)
+
+    prefix = padded(64)
+    pool = []
+    for _ in range(pool_size):
+        n = int(round(math.exp(math.log(300.0) + 0.6 * rng.gauss(0, 1))))
+        pool.append(padded(max(64, min(1024, n))))
+    weights = [1.0 / (r + 1) ** 1.1 for r in range(pool_size)]
+    reqs = []
+    for _ in range(n_requests):
+        picks = rng.choices(range(pool_size), weights=weights, k=k_chunks)
+        reqs.append(([prefix] + [pool[i] for i in picks], tokens(64)))
+    return prefix, pool, reqs
+
+
+def percentile(vals, q):
+    v = sorted(vals)
+    return v[max(0, min(len(v) - 1, int(round(q / 100.0 * (len(v) - 1)))))]
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=24)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--model", default="llama3-70b")
+    ap.add_argument("--pool", type=int, default=64, help="chunks in the synthetic pool")
+    ap.add_argument("--k", type=int, default=8, help="chunks per request")
+    ap.add_argument("--hbm-frac", type=float, default=0.5, help="fraction of the pool the HBM tier can hold")
+    ap.add_argument("--store-dir", default="")
+    ap.add_argument("--io-backend", default="auto")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    from daser_b200.config import DaserConfig
+    from daser_b200.engine.rag_gpu import GpuRagEngine
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.ops import _lib
+    from daser_b200.server.__main__ import ControlPlane
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    cfg = PRESETS[args.model]
+    tp_ctx = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from daser_b200.parallel.tp import TPContext
+
+        tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=256)
+
+    store_dir = args.store_dir or tempfile.mkdtemp(prefix="daser_bench_")
+    if tp_ctx is not None:
+        store_dir = tp_ctx.broadcast_object(store_dir)
+    slot = cfg.num_layers * 2 * cfg.block_tokens * cfg.num_kv_heads * cfg.head_dim * 5 // 4
+    prefix, pool, reqs = make_traffic(cfg, args.pool, args.k, args.steps + args.warmup)
+    pool_slots = sum(len(c) // cfg.block_tokens for c in pool) + len(prefix) // cfg.block_tokens
+    total_slots = pool_slots + 64
+    dcfg = DaserConfig(store_path=os.path.join(store_dir, "daser.store"), index_path="", total_slots=total_slots,
+                       slot_size=slot, ipc_socket_path=os.path.join(store_dir, "daser.sock"),
+                       block_tokens=cfg.block_tokens, num_layers=cfg.num_layers, num_kv_heads=cfg.num_kv_heads,
+                       head_dim=cfg.head_dim, codec="fp8b16", log_level="WARNING")
+    os.environ.setdefault("DASER_LOG_LEVEL", "WARNING")
+
+    loop = None
+    if rank == 0:
+        plane = ControlPlane(dcfg)
+        loop = asyncio.new_event_loop()
+        ready = threading.Event()
+
+        def serve():
+            asyncio.set_event_loop(loop)
+            loop.run_until_complete(plane.start())
+            ready.set()
+            loop.run_forever()
+
+        threading.Thread(target=serve, daemon=True).start()
+        ready.wait(30)
+        from daser_b200.io.engine import preallocate
+
+        preallocate(dcfg.store_path, total_slots * slot)
+    if tp_ctx is not None:
+        tp_ctx.barrier()
+
+    max_ctx_tokens = (args.k * 1024 + 64 + 64 + 16)
+    blocks_per_req = -(-max_ctx_tokens // cfg.block_tokens)
+    t0 = time.time()
+    eng = GpuRagEngine(cfg, dcfg.ipc_socket_path, dcfg.store_path, num_blocks=blocks_per_req + 128, max_tokens=256,
+                       max_seqs=8, hbm_slots=max(64, int(pool_slots * args.hbm_frac)), io_backend=args.io_backend,
+                       tp_ctx=tp_ctx, staging_slots=max(blocks_per_req, 128))
+    t_init = time.time() - t0
+
+    # fill the store: real prefills through the save kernel (untimed)
+    t0 = time.time()
+    for c in [prefix] + pool:
+        eng.store_chunk(c)
+    torch.cuda.synchronize()
+    t_fill = time.time() - t0
+
+    def barrier():
+        if tp_ctx is not None:
+            tp_ctx.barrier()
+        torch.cuda.synchronize()
+
+    def run(req_spec):
+        chunks, query = req_spec
+        return eng.generate(chunks, query, max_new_tokens=1)
+
+    for spec in reqs[: args.warmup]:
+        run(spec)
+    eng.runner.check_status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count
+    barrier()
+    wall0 = time.perf_counter()
+    done = [run(spec) for spec in reqs[args.warmup : args.warmup + args.steps]]
+    barrier()
+    wall = time.perf_counter() - wall0
+    launches = _lib.launch_count - launches0
+    clocks = sampler.stop() if rank == 0 else {}
+    eng.runner.check_status()
+
+    dev_ms = [r.ttft_device_ms for r in done]
+    e2e_ms = [r.ttft_ms for r in done]
+    restore_ms = [r.timings["restore_ms"] for r in done]
+    restored_bytes = sum(r.restored_bytes for r in done)
+    prompt_tokens = sum(r.context_len for r in done)
+    stats = torch.tensor([percentile(dev_ms, 50), percentile(dev_ms, 99), percentile(e2e_ms, 50),
+                          percentile(e2e_ms, 99), wall * 1e3 / args.steps, sum(restore_ms)], dtype=torch.float64,
+                         device="cuda")
+    if tp_ctx is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    p50, p99, e50, e99, ms_per_step, restore_total_ms = stats.tolist()
+
+    if rank == 0:
+        from daser_b200 import metrics as M
+
+        snap = M.snapshot()
+        io_stats = eng.worker.transfer.engine.stats()
+        # per step: token ids, positions, slot mapping, block table, q_start/ctx_lens/sample rows of the
+        # query prefill + the restore work list (3 int64 per slot) + the slot images the restore kernel
+        # reads from pinned host memory when the chunk is not in the HBM tier
+        slots_per_step = sum(r.restored_bytes for r in done) / slot / len(done)
+        host_image_bytes = snap.get("connector.bytes_loaded", 0.0) / max(args.steps + args.warmup, 1)
+        h2d = int(64 * (4 + 4 + 8) + blocks_per_req * 4 + 3 * 4 + 8 + slots_per_step * 24 + host_image_bytes)
+        out = {
+            "metric": METRIC,
+            "value": round(p50, 3),
+            "unit": "ms",
+            "n_gpus": args.gpus,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 3),
+            "higher_is_better": False,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic RAG traffic, random-init weights",
+            "ttft_p99_ms": round(p99, 3),
+            "kv_restore_gbs": round(restored_bytes / max(restore_total_ms, 1e-9) / 1e6, 2),
+            "prompt_tok_s": round(prompt_tokens / wall, 1),
+            "e2e": {"value": round(e50, 3), "unit": "ms", "p99": round(e99, 3), "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "config": {
+                "model": cfg.name, "parallelism": f"tp{args.gpus}", "global_batch": 1,
+                "seq_len": int(prompt_tokens / len(done)), "chunks_per_request": args.k,
+                "chunk_pool": args.pool, "kv_codec": "fp8b16 (e4m3 + fp32 scale / 16)",
+                "io_backend": eng.worker.transfer.backend.name, "store": dcfg.store_path,
+                "hbm_tier_hit_rate": round(snap.get("hbm.hits", 0) / max(snap.get("hbm.hits", 0) + snap.get("hbm.misses", 0), 1), 3),
+                "l2": "inputs larger than L2 (weights stream from HBM every step)",
+                "init_s": round(t_init, 1), "fill_s": round(t_fill, 1),
+                "io_direct_pieces": io_stats["direct_pieces"],
+            },
+        }
+        print(json.dumps(out))
+    eng.close()
+    if rank == 0 and loop is not None:
+        asyncio.run_coroutine_threadsafe(plane.stop(save=False), loop).result(10)
+        loop.call_soon_threadsafe(loop.stop)
+    if tp_ctx is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

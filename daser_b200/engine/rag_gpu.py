@@ -1,0 +1,257 @@
+"""GPU RAG engine: the native serving engine behind the service and the benchmarks.
+
+The reference relies on a separately launched ``vllm serve`` for this part
+(``daser/service/vllm_client.py``); here the engine is in-process.  It combines
+
+* :class:`~daser_b200.engine.runner.GpuModelRunner` (model forward on the sm_100a kernels),
+* the connector halves (:mod:`daser_b200.connector.core`) with the fused restore / save
+  kernels, the native storage engine and the optional HBM tier,
+* an iteration-level scheduler: a waiting request is admitted with one *TTFT step*
+  (look up its chunks, restore them at their new offsets, prefill whatever was not cached
+  plus the query, sample the first token); otherwise all running sequences decode one token
+  as a batch.
+
+With ``tp > 1`` every rank runs the same engine object in lock step; rank 0 additionally
+owns the scheduler half and broadcasts each step's plan.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from daser_b200 import metrics
+from daser_b200.connector.core import ConnectorMeta, CudaKVBackend, SchedulerHalf, WorkerHalf
+from daser_b200.engine.rag_cpu import BlockAllocator
+from daser_b200.engine.runner import GpuModelRunner, make_step_inputs
+from daser_b200.hashing import hash_tokens
+from daser_b200.kv.hbm_store import HBMStore
+from daser_b200.models.llama import LlamaConfig, LlamaWeights
+from daser_b200.ops import kv_ops
+
+
+@dataclass
+class RagRequest:
+    chunks: list[list[int]]  # block-aligned token lists, concatenated in order (prefix first)
+    query: list[int]
+    max_new_tokens: int = 1
+    req_id: str = ""
+    arrival: float = 0.0
+    # filled by the engine
+    block_table: list[int] = field(default_factory=list)
+    generated: list[int] = field(default_factory=list)
+    context_len: int = 0
+    ttft_ms: float = 0.0
+    ttft_device_ms: float = 0.0
+    restored_chunks: int = 0
+    restored_bytes: int = 0
+    timings: dict = field(default_factory=dict)
+    done: bool = False
+
+
+class GpuRagEngine:
+    def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 4096,
+                 max_tokens: int = 256, max_seqs: int = 64, hbm_slots: int = 0, io_backend: str = "auto",
+                 seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
+                 staging_slots: int = 512) -> None:
+        self.cfg = cfg
+        self.tp = tp_ctx.tp if tp_ctx is not None else 1
+        self.rank = tp_ctx.rank if tp_ctx is not None else 0
+        self.tp_ctx = tp_ctx
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.weights = weights or LlamaWeights.random(cfg, self.device, torch.bfloat16, tp=self.tp,
+                                                      rank=self.rank, seed=seed)
+        self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device)
+        self.blocks = BlockAllocator(num_blocks)
+        self.geo = self.runner.geo
+        # the restore kernel of the IO owner scatters into every rank's pool
+        pool = tp_ctx.global_pool(self.runner) if tp_ctx is not None else self.runner.local_pool
+        self.kv_backend = CudaKVBackend(self.geo, pool, cfg.inv_freq(), max_pos=self.runner.cos_sin.shape[0],
+                                        rank=self.rank, max_slots=max(staging_slots, 1024), device=self.device)
+        self.kv_backend.cos_sin = self.runner.cos_sin
+        self.hbm = HBMStore(self.geo.slot_size, hbm_slots, self.device) if hbm_slots > 0 else None
+        self.is_io_rank = self.rank == 0
+        self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id) if self.rank == 0 else None
+        self.worker = (
+            WorkerHalf(socket_path, store_path, self.geo, self.kv_backend, io_backend=io_backend, tp=self.tp,
+                       rank=self.rank, hbm_store=self.hbm, staging_slots=staging_slots)
+            if self.is_io_rank else None
+        )
+        self.waiting: list[RagRequest] = []
+        self.running: list[RagRequest] = []
+        self._n = 0
+        self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+
+    # ------------------------------------------------------------------------------------------
+    def _next_id(self) -> str:
+        self._n += 1
+        return f"r{self._n}"
+
+    def _sync_ranks(self) -> None:
+        if self.tp_ctx is not None:
+            self.tp_ctx.barrier()
+
+    def _bcast(self, obj):
+        return self.tp_ctx.broadcast_object(obj) if self.tp_ctx is not None else obj
+
+    def _prefill_tokens(self, tokens: Sequence[int], start_pos: int, table: list[int]) -> torch.Tensor:
+        """Run ``tokens`` through the model in pieces of at most ``max_tokens``; returns the last sample."""
+        out = None
+        mt = self.runner.max_tokens
+        for i in range(0, len(tokens), mt):
+            piece = list(tokens[i : i + mt])
+            inp = make_step_inputs([{"tokens": piece, "start_pos": start_pos + i, "block_table": table}],
+                                   self.cfg.block_tokens, self.device)
+            out = self.runner.forward(inp)
+        return out
+
+    # -- offline fill ------------------------------------------------------------------------------
+    def store_chunk(self, tokens: Sequence[int]) -> str:
+        """Prefill ``tokens`` alone at positions 0.. and write their KV to the store."""
+        bt = self.cfg.block_tokens
+        tokens = list(tokens)
+        if len(tokens) % bt:
+            raise ValueError("chunks must be a whole number of blocks")
+        table = self.blocks.alloc(len(tokens) // bt)
+        req = self._next_id()
+        meta = ConnectorMeta()
+        if self.sched is not None:
+            if self.sched.reserve_chunk_store(req, tokens, table, pos_offset=0) is not None:
+                meta = self.sched.build_connector_meta([req])
+        meta = self._bcast(meta)
+        self._prefill_tokens(tokens, 0, table)
+        self._save(meta)
+        if self.sched is not None:
+            self.sched.request_finished(req)
+        self.blocks.free(table)
+        return hash_tokens(tokens)
+
+    def _save(self, meta: ConnectorMeta) -> None:
+        if self.tp_ctx is None:
+            self.worker.bind_connector_metadata(meta)
+            try:
+                self.worker.wait_for_save()
+            finally:
+                self.worker.clear_connector_metadata()
+            return
+        self.tp_ctx.save_step(self, meta)
+
+    def _restore(self, meta: ConnectorMeta) -> None:
+        if self.worker is not None:
+            self.worker.bind_connector_metadata(meta)
+            try:
+                self.worker.start_load_kv()
+            finally:
+                self.worker.clear_connector_metadata()
+        self._sync_ranks()  # peers' pools were written by the IO rank
+
+    # -- online ---------------------------------------------------------------------------------------
+    def submit(self, req: RagRequest) -> RagRequest:
+        req.req_id = req.req_id or self._next_id()
+        req.arrival = req.arrival or time.perf_counter()
+        self.waiting.append(req)
+        return req
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def step(self) -> None:
+        if self.waiting:
+            self._ttft_step(self.waiting.pop(0))
+        elif self.running:
+            self._decode_step()
+
+    def _ttft_step(self, req: RagRequest) -> None:
+        cfg, bt = self.cfg, self.cfg.block_tokens
+        t_start = time.perf_counter()
+        self._ev[0].record()
+        offsets, pos = [], 0
+        for c in req.chunks:
+            if len(c) % bt:
+                raise ValueError("chunks must be a whole number of blocks")
+            offsets.append(pos)
+            pos += len(c)
+        total = pos + len(req.query)
+        n_blocks = -(-(total + req.max_new_tokens) // bt)
+        req.block_table = self.blocks.alloc(n_blocks)
+        # 1. plan: which chunks are cached, where do they go
+        plan = None
+        if self.sched is not None:
+            placements = [(hash_tokens(c), off) for c, off in zip(req.chunks, offsets)]
+            specs = self.sched.plan_chunk_loads(req.req_id, placements)
+            self.sched.assign_chunk_blocks(req.req_id, req.block_table)
+            plan = (self.sched.build_connector_meta([req.req_id]), [s is not None for s in specs])
+        meta, found = self._bcast(plan)
+        t_plan = time.perf_counter()
+        # 2. restore cached chunks (IO + one fused kernel)
+        self._ev[1].record()
+        self._restore(meta)
+        self._ev[2].record()
+        t_restore = time.perf_counter()
+        failed_blocks = self.worker.take_load_errors() if self.worker is not None else set()
+        failed_blocks = self._bcast(failed_blocks)
+        # 3. compute what was not restored, then the query
+        ctx = 0
+        first = None
+        for c, off, ok in zip(req.chunks, offsets, found):
+            blocks_of_chunk = set(req.block_table[off // bt : (off + len(c)) // bt])
+            if not ok or (blocks_of_chunk & failed_blocks):
+                self._prefill_tokens(c, off, req.block_table)
+            else:
+                req.restored_chunks += 1
+                req.restored_bytes += (len(c) // bt) * self.geo.slot_size
+            ctx = off + len(c)
+        first = self._prefill_tokens(req.query, ctx, req.block_table)
+        self._ev[3].record()
+        token = int(first[0].item())  # device -> host read of the step's result
+        t_end = time.perf_counter()
+        req.generated.append(token)
+        req.context_len = total
+        req.ttft_ms = (t_end - t_start) * 1e3
+        req.ttft_device_ms = self._ev[0].elapsed_time(self._ev[3])
+        req.timings = {
+            "plan_ms": (t_plan - t_start) * 1e3,
+            "restore_ms": (t_restore - t_plan) * 1e3,
+            "restore_device_ms": self._ev[1].elapsed_time(self._ev[2]),
+            "compute_ms": (t_end - t_restore) * 1e3,
+        }
+        metrics.observe("engine.ttft_ms", req.ttft_ms)
+        if self.sched is not None:
+            self.sched.request_finished(req.req_id)
+        if len(req.generated) >= req.max_new_tokens:
+            self._finish(req)
+        else:
+            self.running.append(req)
+
+    def _decode_step(self) -> None:
+        batch = self.running[: self.runner.max_seqs]
+        seqs = [{"tokens": [r.generated[-1]], "start_pos": r.context_len + len(r.generated) - 1,
+                 "block_table": r.block_table} for r in batch]
+        inp = make_step_inputs(seqs, self.cfg.block_tokens, self.device)
+        out = self.runner.forward(inp).tolist()
+        for r, tok in zip(batch, out):
+            r.generated.append(int(tok))
+            if len(r.generated) >= r.max_new_tokens:
+                self._finish(r)
+
+    def _finish(self, req: RagRequest) -> None:
+        req.done = True
+        if req in self.running:
+            self.running.remove(req)
+        self.blocks.free(req.block_table)
+
+    def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1) -> RagRequest:
+        """Serve one request to completion (the call a user of the engine makes)."""
+        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens))
+        while not req.done:
+            self.step()
+        return req
+
+    def close(self) -> None:
+        if self.worker is not None:
+            self.worker.shutdown()
+        if self.sched is not None:
+            self.sched.close()

@@ -1,0 +1,207 @@
+"""CUDA model runner: the Llama forward on the hand-written sm_100a kernels.
+
+The reference has no engine (stock vLLM's ``GPUModelRunner`` plays this part).  One
+:class:`GpuModelRunner` lives in each process (one process per GPU).  It owns
+
+* this rank's weight shards (bf16),
+* this rank's slice of the paged KV pool: block-scaled fp8, head-major
+  ``[layer, block, k|v, head, token, dim]`` payload plus fp32 scales, which is what the fused
+  restore kernel writes into and the attention kernel reads from,
+* persistent activation buffers, so a step allocates nothing.
+
+Per layer the step is: tcgen05 GEMM (QKV) -> RoPE + KV write -> fp8 paged attention ->
+tcgen05 GEMM (O) -> add + RMSNorm -> tcgen05 GEMM (gate, up) -> SwiGLU -> tcgen05 GEMM (down)
+-> add + RMSNorm.  Skinny GEMMs run split-K into fp32 accumulators that the consuming kernel
+reads and hands back zeroed.
+
+Tensor parallelism (``tp > 1``) follows the sequence-parallel formulation: activations
+between blocks are sharded by rows.  The row-parallel GEMMs (O, down) reduce-scatter in their
+epilogue straight into the owning rank's accumulator over NVLink; the add + RMSNorm kernel
+waits for the arrivals, normalises its rows and pushes them into every rank's gathered
+activation buffer; the following column-parallel GEMM is gated on those pushes.  No NCCL call
+is made on that path (:mod:`daser_b200.parallel.tp` holds the symmetric buffers and counters).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from daser_b200.kv.layout import KVGeometry
+from daser_b200.models.llama import LlamaConfig, LlamaWeights
+from daser_b200.ops import attention, elementwise as ew, gemm, kv_ops
+
+
+@dataclass
+class StepInputs:
+    """Device tensors describing one engine step (all int32 unless noted)."""
+
+    tokens: torch.Tensor  # [T]
+    positions: torch.Tensor  # [T]
+    slot_mapping: torch.Tensor  # [T] int64: block * block_tokens + offset
+    block_tables: torch.Tensor  # [num_seqs, max_blocks]
+    q_start: torch.Tensor  # [num_seqs + 1]
+    ctx_lens: torch.Tensor  # [num_seqs]
+    sample_rows: torch.Tensor  # [num_seqs] row index of each sequence's last token
+    num_tokens: int
+    num_seqs: int
+    max_q_len: int
+    max_ctx: int
+
+
+class GpuModelRunner:
+    def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, num_blocks: int, max_tokens: int = 256,
+                 max_seqs: int = 64, tp_ctx=None, device: Optional[torch.device] = None) -> None:
+        self.cfg = cfg
+        self.w = weights
+        self.tp = weights.tp
+        self.rank = weights.rank
+        self.tp_ctx = tp_ctx
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs
+        self.num_blocks = num_blocks
+        D, B = cfg.head_dim, cfg.block_tokens
+        self.hq = weights.heads_local
+        self.hkv = weights.kv_heads_local
+        dev = self.device
+
+        # ---- paged KV pool (this rank's heads) ----
+        shape = (cfg.num_layers, num_blocks, 2, self.hkv, B, D)
+        if tp_ctx is not None:
+            self.kv_payload = tp_ctx.alloc("kv_payload", shape, torch.uint8)
+            self.kv_scales = tp_ctx.alloc("kv_scales", shape[:-1] + (D // 16,), torch.float32)
+        else:
+            self.kv_payload = torch.zeros(shape, dtype=torch.uint8, device=dev)
+            self.kv_scales = torch.ones(shape[:-1] + (D // 16,), dtype=torch.float32, device=dev)
+        self.local_pool = kv_ops.PagedKVPool.from_tensors([self.kv_payload], [self.kv_scales], "LNKHTD")
+        # geometry of a stored slot: ALL kv heads, fp8b16
+        self.geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, D, B, 2, "fp8b16")
+        self.cos_sin = kv_ops.rope_table(min(cfg.max_position, 32768), cfg.inv_freq(), dev)
+
+        # ---- activation buffers ----
+        T, H = max_tokens, cfg.hidden
+        qkv_n = (self.hq + 2 * self.hkv) * D
+        bf, f32 = torch.bfloat16, torch.float32
+        self.h = torch.zeros(T, H, dtype=bf, device=dev)  # residual stream
+        self.normed = torch.zeros(T, H, dtype=bf, device=dev)
+        self.qkv_acc = torch.zeros(T, qkv_n, dtype=f32, device=dev)
+        self.qkv_bf = torch.zeros(T, qkv_n, dtype=bf, device=dev)
+        self.q_rot = torch.zeros(T, self.hq, D, dtype=bf, device=dev)
+        self.attn_out = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
+        self.hid_acc = torch.zeros(T, H, dtype=f32, device=dev)
+        self.hid_bf = torch.zeros(T, H, dtype=bf, device=dev)
+        inter = weights.inter_local
+        self.gu_acc = torch.zeros(T, 2 * inter, dtype=f32, device=dev)
+        self.gu_bf = torch.zeros(T, 2 * inter, dtype=bf, device=dev)
+        self.act = torch.zeros(T, inter, dtype=bf, device=dev)
+        self.last_rows = torch.zeros(max_seqs, H, dtype=bf, device=dev)
+        self.logits_acc = torch.zeros(max_seqs, weights.vocab_local, dtype=f32, device=dev)
+        self.best_val = torch.zeros(max_seqs, dtype=f32, device=dev)
+        self.best_idx = torch.zeros(max_seqs, dtype=torch.int32, device=dev)
+        self.attn_ws = attention.AttentionWorkspace(dev)
+        self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.softmax_scale = D**-0.5
+
+    # -- helpers ---------------------------------------------------------------------------------
+    def _linear(self, x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, out_bf: torch.Tensor):
+        """``x @ w.T``; returns (tensor, is_fp32_accumulator)."""
+        M = x.shape[0]
+        bn, ks = gemm.plan_tiles(M, w.shape[0], w.shape[1], allow_split=True)
+        if ks > 1:
+            gemm.linear(x, w, acc=acc[:M], block_n=bn, k_splits=ks, status=self.status)
+            return acc[:M], True
+        gemm.linear(x, w, out=out_bf[:M], block_n=bn, k_splits=1, status=self.status)
+        return out_bf[:M], False
+
+    # -- one step -----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, inp: StepInputs) -> torch.Tensor:
+        """Run the model on the step's tokens; returns the greedy next token of every sequence
+        (int32 ``[num_seqs]``, on the device)."""
+        if self.tp > 1:
+            return self.tp_ctx.forward(self, inp)
+        cfg, w = self.cfg, self.w
+        T = inp.num_tokens
+        if T > self.max_tokens or inp.num_seqs > self.max_seqs:
+            raise ValueError("step exceeds the runner's buffers")
+        D, B = cfg.head_dim, cfg.block_tokens
+        h = self.h[:T]
+        normed = self.normed[:T]
+        ew.embedding(inp.tokens, w.embed, out=h)
+        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li, lw in enumerate(w.layers):
+            qkv, f32 = self._linear(normed, lw.wqkv, self.qkv_acc, self.qkv_bf)
+            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq,
+                             self.hkv, D, B, self.local_pool, li, 0, zero_after=f32)
+            attn = self.attn_out[:T].view(T, self.hq, D)
+            attention.paged_attention(self.q_rot[:T], attn, self.local_pool, li, inp.block_tables, inp.q_start,
+                                      inp.ctx_lens, inp.max_q_len, inp.max_ctx, self.hkv, self.softmax_scale,
+                                      self.attn_ws)
+            o, f32 = self._linear(self.attn_out[:T], lw.wo, self.hid_acc, self.hid_bf)
+            ew.add_rmsnorm(o, lw.post_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
+            gu, f32 = self._linear(normed, lw.w_gate_up, self.gu_acc, self.gu_bf)
+            ew.swiglu(gu, out=self.act[:T], zero_after=f32)
+            d, f32 = self._linear(self.act[:T], lw.w_down, self.hid_acc, self.hid_bf)
+            next_norm = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
+            ew.add_rmsnorm(d, next_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
+        return self.sample(normed, inp)
+
+    def sample(self, normed: torch.Tensor, inp: StepInputs) -> torch.Tensor:
+        n = inp.num_seqs
+        torch.index_select(normed, 0, inp.sample_rows[:n], out=self.last_rows[:n])
+        gemm.linear(self.last_rows[:n], self.w.lm_head, acc=self.logits_acc[:n], status=self.status)
+        ew.argmax(self.logits_acc[:n], self.best_val[:n], self.best_idx[:n],
+                  index_offset=self.rank * self.w.vocab_local, zero_after=True)
+        return self.best_idx[:n]
+
+    def logits(self, inp: StepInputs) -> torch.Tensor:
+        """Full forward returning fp32 logits of the sampled rows (tests; single rank)."""
+        assert self.tp == 1
+        self.forward(inp)  # leaves `normed` of the last layer in place
+        n = inp.num_seqs
+        gemm.linear(self.last_rows[:n], self.w.lm_head, acc=self.logits_acc[:n], status=self.status)
+        out = self.logits_acc[:n].clone()
+        self.logits_acc[:n].zero_()
+        return out
+
+    def check_status(self) -> None:
+        if int(self.status[0].item()) != 0:
+            self.status.zero_()
+            raise RuntimeError("a GEMM wait ran out (status word set); the step's output is invalid")
+
+
+def make_step_inputs(seqs: list[dict], block_tokens: int, device, max_blocks: Optional[int] = None) -> StepInputs:
+    """Build :class:`StepInputs` from ``[{tokens, start_pos, block_table}]``.
+
+    ``start_pos`` is the number of tokens already in the sequence's cache.  Host tensors are
+    assembled in pinned memory and copied once.
+    """
+    toks, pos, slots, q_start, ctx, rows = [], [], [], [0], [], []
+    for s in seqs:
+        n, p0, table = len(s["tokens"]), s["start_pos"], s["block_table"]
+        toks.extend(s["tokens"])
+        for i in range(n):
+            p = p0 + i
+            pos.append(p)
+            slots.append(table[p // block_tokens] * block_tokens + p % block_tokens)
+        q_start.append(q_start[-1] + n)
+        ctx.append(p0 + n)
+        rows.append(q_start[-1] - 1)
+    mb = max_blocks or max(len(s["block_table"]) for s in seqs)
+    tables = torch.zeros(len(seqs), mb, dtype=torch.int32)
+    for i, s in enumerate(seqs):
+        tables[i, : len(s["block_table"])] = torch.tensor(s["block_table"], dtype=torch.int32)
+
+    def dev(x, dt):
+        t = torch.tensor(x, dtype=dt).pin_memory()
+        return t.to(device, non_blocking=True)
+
+    return StepInputs(
+        tokens=dev(toks, torch.int32), positions=dev(pos, torch.int32), slot_mapping=dev(slots, torch.int64),
+        block_tables=tables.pin_memory().to(device, non_blocking=True), q_start=dev(q_start, torch.int32),
+        ctx_lens=dev(ctx, torch.int32), sample_rows=dev(rows, torch.int64), num_tokens=len(toks),
+        num_seqs=len(seqs), max_q_len=max(len(s["tokens"]) for s in seqs), max_ctx=max(ctx),
+    )

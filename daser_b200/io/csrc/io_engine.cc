@@ -370,7 +370,10 @@ daser_io* daser_io_open(const char* path, int backend, int want_device, int queu
   io->depth = (unsigned)queue_depth;
 
   int chosen = 0;
-  if ((backend == DASER_IO_AUTO && want_device > 0) || backend == DASER_IO_GDS) {
+  // AUTO only tries cuFile when the nvidia-fs kernel driver is loaded: without it
+  // cuFileDriverOpen can stall for a long time probing for the driver before it gives up.
+  const bool nvfs = access("/proc/driver/nvidia-fs/stats", R_OK) == 0;
+  if ((backend == DASER_IO_AUTO && want_device > 0 && nvfs) || backend == DASER_IO_GDS) {
     if (io->cf.load()) {
       if (io->cf.cuda_set_device && io->device >= 0) io->cf.cuda_set_device(io->device);
       CuFileApi::Error e = io->cf.driver_open();

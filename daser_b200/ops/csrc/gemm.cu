@@ -134,9 +134,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int g0 = m0 / p.gate_rows;
         const int g1 = min(m0 + GEMM_BM - 1, p.M - 1) / p.gate_rows;
         for (int g = g0; g <= g1 && ok; ++g) {
-          uint32_t tries = 0;
+          const uint64_t t0 = sm100::global_timer_ns();
           while (ld_acquire_sys(p.gate_flags + g) < p.gate_target) {
-            if (++tries > (1u << 22) || *abort_flag) { ok = false; *abort_flag = 1u; break; }
+            if (*abort_flag || sm100::global_timer_ns() - t0 > DASER_WAIT_NS) { ok = false; *abort_flag = 1u; break; }
             __nanosleep(64);
           }
         }
@@ -160,8 +160,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const int first = issued > STAGES ? issued - STAGES : 0;
         for (int it = first; it < issued; ++it) {
           const int s = it % STAGES;
-          for (uint32_t i = 0; i < (1u << 16); ++i)
-            if (sm100::mbar_try_wait(&full_bar[s], (it / STAGES) & 1)) break;
+          const uint64_t t0 = sm100::global_timer_ns();
+          while (!sm100::mbar_try_wait(&full_bar[s], (it / STAGES) & 1))
+            if (sm100::global_timer_ns() - t0 > 100000000ull) break;  // 100 ms
         }
       }
     }

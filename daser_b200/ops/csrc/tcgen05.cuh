@@ -50,16 +50,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait is bounded: try_wait suspends for a hardware-defined slice per attempt, so
-// the attempt budget below is seconds, not microseconds, yet it cannot spin for ever.
-// Returns false when the budget ran out; the caller records it and unwinds.
-#ifndef DASER_WAIT_ATTEMPTS
-#define DASER_WAIT_ATTEMPTS (1u << 20)
+// Every wait is bounded by wall time (%globaltimer): a healthy wait lasts microseconds, the
+// budget is DASER_WAIT_NS.  Returns false when the budget ran out; the caller records it and
+// unwinds (no trap, no endless spin).
+#ifndef DASER_WAIT_NS
+#define DASER_WAIT_NS 2000000000ull
 #endif
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < DASER_WAIT_ATTEMPTS; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > DASER_WAIT_NS) break;
+    }
   }
   *abort_flag = 1u;
   return false;

@@ -1,0 +1,34 @@
+"""HBM tier bookkeeping (runs on CPU memory: the arena is just a tensor)."""
+
+import torch
+
+from daser_b200.kv.hbm_store import HBMStore
+
+
+def test_lru_and_contiguity():
+    s = HBMStore(slot_size=64, capacity_slots=8, device=torch.device("cpu"))
+    src = torch.arange(64 * 8, dtype=torch.int64).to(torch.uint8)
+    assert s.admit("a", src, 0, 64 * 3) and s.admit("b", src, 64, 64 * 3)
+    assert s.lookup("zz") is None
+    pa = s.lookup("a")  # 'a' is now most recently used
+    assert pa == s.arena.data_ptr()
+    assert s.admit("c", src, 0, 64 * 4)  # needs eviction: 'b' is LRU, but freeing b gives 3+2=5 contiguous
+    assert "b" not in s and "a" in s and "c" in s
+    assert s.used_slots == 7
+    # contents survive
+    first = (s.lookup("c") - s.arena.data_ptr()) // 64
+    assert torch.equal(s.arena[first * 64 : first * 64 + 256], src[:256])
+    assert not s.admit("huge", src, 0, 64 * 9)
+    assert s.evict("a") and not s.evict("a")
+    assert s.admit("d", src, 0, 64 * 4)  # free runs are [0,3) and [7,8): 'c' has to go too
+    assert len(s) == 1 and s.stats()["used_slots"] == 4
+
+
+def test_fragmentation_evicts_until_a_run_fits():
+    s = HBMStore(32, 6, torch.device("cpu"))
+    src = torch.zeros(32 * 6, dtype=torch.uint8)
+    for k in "abc":
+        s.admit(k, src, 0, 64)
+    s.evict("b")  # hole of 2 in the middle
+    assert s.admit("d", src, 0, 32 * 4)  # must evict 'a' (LRU) to merge [0,4)
+    assert "a" not in s and "c" in s
