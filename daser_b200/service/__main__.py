@@ -1,0 +1,130 @@
+"""``python -m daser_b200.service`` — REST service with the control plane embedded.
+
+Capability parity: ``daser/service/__main__.py:26-213`` — flags ``--host`` (0.0.0.0),
+``--port`` (8080), ``--vllm-base-url``, ``--model``, ``--tokenizer``, ``--socket-path``,
+``--store-path``, ``--index-path``, ``--total-slots`` (1024), ``--slot-size`` (0 = derive),
+``--block-tokens``, ``--chunk-blocks``, the model-geometry flags and ``--model-id``; the
+control plane and uvicorn share one event loop, and a snapshot is written on shutdown.
+
+Added: ``--engine native`` serves from the in-process engine (``--native-model`` names a
+preset; ``cpu`` or ``cuda`` device) instead of a remote vLLM, in which case
+``--vllm-base-url`` and ``--model`` are optional.
+"""
+
+from __future__ import annotations
+
+import argparse
+import asyncio
+import signal
+from typing import Optional, Sequence
+
+from daser_b200.config import DaserConfig
+from daser_b200.logging import init_logger
+from daser_b200.server.__main__ import ControlPlane
+from daser_b200.service.http_api import ServiceConfig, build_service_app, load_tokenizer
+
+logger = init_logger(__name__)
+
+
+def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
+    p = argparse.ArgumentParser(prog="daser_b200.service", description=__doc__)
+    p.add_argument("--host", default="0.0.0.0")
+    p.add_argument("--port", type=int, default=8080)
+    p.add_argument("--engine", choices=("vllm", "native"), default="vllm")
+    p.add_argument("--vllm-base-url", default=None)
+    p.add_argument("--model", default=None)
+    p.add_argument("--tokenizer", required=True)
+    p.add_argument("--socket-path", default="/tmp/daser.sock")
+    p.add_argument("--store-path", default="/mnt/xfs/daser.store")
+    p.add_argument("--index-path", default="/mnt/xfs/daser.index")
+    p.add_argument("--total-slots", type=int, default=1024)
+    p.add_argument("--slot-size", type=int, default=0)
+    p.add_argument("--block-tokens", type=int, default=16)
+    p.add_argument("--chunk-blocks", type=int, default=16)
+    p.add_argument("--num-kv-heads", type=int, default=0)
+    p.add_argument("--head-dim", type=int, default=0)
+    p.add_argument("--num-layers", type=int, default=0)
+    p.add_argument("--dtype-bytes", type=int, default=2)
+    p.add_argument("--model-id", default="default")
+    p.add_argument("--native-model", default="toy")
+    p.add_argument("--native-device", choices=("cpu", "cuda"), default="cpu")
+    p.add_argument("--snapshot-interval", type=float, default=0.0)
+    args = p.parse_args(argv)
+    if args.engine == "vllm" and (not args.vllm_base_url or not args.model):
+        p.error("--vllm-base-url and --model are required with --engine vllm")
+    return args
+
+
+def _build_daser_config(args: argparse.Namespace) -> DaserConfig:
+    return DaserConfig(
+        store_path=args.store_path, index_path=args.index_path, total_slots=args.total_slots,
+        slot_size=args.slot_size, ipc_socket_path=args.socket_path, num_kv_heads=args.num_kv_heads,
+        head_dim=args.head_dim, num_layers=args.num_layers, block_tokens=args.block_tokens,
+        dtype_bytes=args.dtype_bytes, model_id=args.model_id,
+        snapshot_interval_s=getattr(args, "snapshot_interval", 0.0),
+    )
+
+
+def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    mcfg = PRESETS[args.native_model]
+    if args.native_device == "cuda":
+        from daser_b200.engine.rag_gpu import GpuRagEngine
+
+        engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
+                              hbm_slots=min(cfg.total_slots, 4096))
+    else:
+        from daser_b200.engine.rag_cpu import CpuRagEngine
+
+        engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id)
+    return NativeEngineClient(engine, tokenizer.decode, model=args.native_model), engine
+
+
+async def _run(args: argparse.Namespace) -> None:
+    import uvicorn
+
+    cfg = _build_daser_config(args)
+    tokenizer = load_tokenizer(args.tokenizer)
+    engine_client = engine = None
+    if args.engine == "native":
+        from daser_b200.models.llama import PRESETS
+
+        m = PRESETS[args.native_model]
+        if cfg.slot_size == 0 and cfg.num_layers == 0:
+            cfg.num_layers, cfg.num_kv_heads, cfg.head_dim = m.num_layers, m.num_kv_heads, m.head_dim
+            cfg.dtype_bytes = 4 if args.native_device == "cpu" else 2
+            cfg.codec = "raw" if args.native_device == "cpu" else "fp8b16"
+    plane = ControlPlane(cfg)
+    await plane.start()
+    if args.engine == "native":
+        engine_client, engine = _native_engine(args, cfg, tokenizer)
+    app = build_service_app(
+        ServiceConfig(vllm_base_url=args.vllm_base_url or "", model=args.model or args.native_model,
+                      tokenizer=args.tokenizer, socket_path=args.socket_path, block_tokens=args.block_tokens,
+                      chunk_blocks=args.chunk_blocks),
+        engine_client=engine_client, tokenizer=tokenizer,
+    )
+    server = uvicorn.Server(uvicorn.Config(app, host=args.host, port=args.port, loop="none", log_level="info"))
+    stop = asyncio.Event()
+    loop = asyncio.get_running_loop()
+    for sig in (signal.SIGTERM, signal.SIGINT):
+        loop.add_signal_handler(sig, stop.set)
+    http_task = asyncio.create_task(server.serve())
+    stop_task = asyncio.create_task(stop.wait())
+    await asyncio.wait({http_task, stop_task}, return_when=asyncio.FIRST_COMPLETED)
+    server.should_exit = True
+    await asyncio.gather(http_task, return_exceptions=True)
+    stop_task.cancel()
+    if engine is not None:
+        engine.close()
+    await plane.stop(save=True)
+
+
+def main(argv: Optional[Sequence[str]] = None) -> None:
+    asyncio.run(_run(_parse_args(argv)))
+
+
+if __name__ == "__main__":
+    main()

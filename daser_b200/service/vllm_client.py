@@ -1,0 +1,123 @@
+"""Engine clients used by the service.
+
+Capability parity: ``daser/service/vllm_client.py:15-146`` — :class:`VLLMClient` posts
+token-id prompts to an OpenAI-compatible ``/v1/completions`` (``prefill`` = one token at
+temperature 0, ``completion`` with defaults ``max_tokens=256, temperature=0.7`` overridden
+by the caller, ``health`` never raises, 300 s timeout).
+
+Added: :class:`NativeEngineClient` serves the same three calls from the in-process engine
+(:mod:`daser_b200.engine`), and additionally accepts *segments* so cached document chunks
+are restored at their offsets instead of being recomputed.
+"""
+
+from __future__ import annotations
+
+import asyncio
+from typing import Any, Optional, Sequence
+
+
+class VLLMClient:
+    def __init__(self, base_url: str, model: str, timeout_s: float = 300.0) -> None:
+        import httpx
+
+        self._base = base_url.rstrip("/")
+        self._model = model
+        self._http = httpx.AsyncClient(timeout=timeout_s)
+
+    async def __aenter__(self) -> "VLLMClient":
+        return self
+
+    async def __aexit__(self, *exc: Any) -> None:
+        await self.close()
+
+    @property
+    def model(self) -> str:
+        return self._model
+
+    async def close(self) -> None:
+        await self._http.aclose()
+
+    async def _post_completions(self, payload: dict[str, Any]) -> dict[str, Any]:
+        resp = await self._http.post(f"{self._base}/v1/completions", json=payload)
+        resp.raise_for_status()
+        return resp.json()
+
+    async def prefill(self, tokens: list[int]) -> None:
+        """Run the prompt through the engine so the connector stores its KV."""
+        await self._post_completions({"model": self._model, "prompt": tokens, "max_tokens": 1, "temperature": 0.0})
+
+    async def completion(self, tokens: list[int], gen_params: Optional[dict[str, Any]] = None,
+                         segments: Optional[Sequence[Sequence[int]]] = None) -> dict[str, Any]:
+        payload: dict[str, Any] = {"model": self._model, "prompt": tokens, "max_tokens": 256, "temperature": 0.7}
+        payload.update(gen_params or {})
+        return await self._post_completions(payload)
+
+    async def health(self) -> bool:
+        try:
+            resp = await self._http.get(f"{self._base}/health")
+            return resp.status_code == 200
+        except Exception:
+            return False
+
+
+class NativeEngineClient:
+    """The in-process engine behind the same interface.
+
+    ``engine`` is a :class:`~daser_b200.engine.rag_cpu.CpuRagEngine` or
+    :class:`~daser_b200.engine.rag_gpu.GpuRagEngine`; ``detokenize`` turns generated ids
+    into text.  Engine calls run in a worker thread so the event loop (which also serves
+    the control plane) stays responsive.
+    """
+
+    def __init__(self, engine: Any, detokenize, model: str = "native", pad_token: int = 0) -> None:
+        self._engine = engine
+        self._detok = detokenize
+        self._model = model
+        self._pad = pad_token
+        self._lock = asyncio.Lock()
+
+    @property
+    def model(self) -> str:
+        return self._model
+
+    async def close(self) -> None:
+        pass
+
+    async def health(self) -> bool:
+        return True
+
+    async def prefill(self, tokens: list[int]) -> None:
+        async with self._lock:
+            await asyncio.get_running_loop().run_in_executor(None, self._engine.store_chunk, list(tokens))
+
+    def _pad_block(self, tokens: Sequence[int]) -> list[int]:
+        bt = self._engine.cfg.block_tokens
+        t = list(tokens)
+        return t + [self._pad] * (-len(t) % bt)
+
+    def _generate(self, segments, query, max_new):
+        eng = self._engine
+        chunks = [self._pad_block(s) for s in segments if len(s)]
+        if hasattr(eng, "generate"):
+            req = eng.generate(chunks, list(query), max_new_tokens=max_new)
+            return req.generated, req.context_len
+        res = eng.run_request([], chunks, list(query))
+        return [int(res.logits[-1].argmax())], res.total_tokens
+
+    async def completion(self, tokens: list[int], gen_params: Optional[dict[str, Any]] = None,
+                         segments: Optional[Sequence[Sequence[int]]] = None) -> dict[str, Any]:
+        """``segments`` = cacheable token runs (document chunks) preceding the final query run;
+        without them the whole prompt is computed."""
+        params = gen_params or {}
+        max_new = int(params.get("max_tokens", 256))
+        if segments:
+            *cached, query = segments
+        else:
+            cached, query = [], tokens
+        async with self._lock:
+            gen, prompt_len = await asyncio.get_running_loop().run_in_executor(
+                None, self._generate, cached, query, max_new)
+        return {
+            "choices": [{"text": self._detok(gen), "token_ids": gen}],
+            "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)},
+        }

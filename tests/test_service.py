@@ -1,0 +1,157 @@
+"""REST service over a live control plane, with a fake engine and with the CPU engine."""
+
+import asyncio
+
+import pytest
+from fastapi.testclient import TestClient
+
+from conftest import LiveControlPlane
+from daser_b200.hashing import hash_tokens
+from daser_b200.service.chunker import Chunker
+from daser_b200.service.http_api import ByteTokenizer, ServiceConfig, build_service_app
+
+
+class FakeEngine:
+    """Stands in for vLLM: 'prefill' stores nothing, so chunks count as not cached."""
+
+    def __init__(self, plane=None, up=True):
+        self.prefills, self.completions, self.up, self.fail = [], [], up, False
+        self.plane = plane
+
+    @property
+    def model(self):
+        return "fake"
+
+    async def close(self):
+        pass
+
+    async def health(self):
+        return self.up
+
+    async def prefill(self, tokens):
+        if self.fail:
+            raise RuntimeError("engine down")
+        self.prefills.append(list(tokens))
+        if self.plane is not None:  # emulate the connector's store + commit
+            from daser_b200.connector.ipc_client import IPCClientSync
+
+            c = IPCClientSync(self.plane.socket_path)
+            key = hash_tokens(list(tokens))
+            await asyncio.get_running_loop().run_in_executor(None, c.alloc_chunk, key, len(tokens), "default")
+            await asyncio.get_running_loop().run_in_executor(None, c.commit_chunk, key)
+            c.close()
+
+    async def completion(self, tokens, gen_params=None, segments=None):
+        if self.fail:
+            raise RuntimeError("engine down")
+        self.completions.append((list(tokens), gen_params, segments))
+        return {"choices": [{"text": "answer"}], "usage": {"prompt_tokens": len(tokens), "completion_tokens": 3}}
+
+
+def test_chunker():
+    ch = Chunker(4, 2)
+    toks = list(range(19))
+    chunks = ch.chunk(toks)
+    assert [c.tokens for c in chunks] == [toks[0:8], toks[8:16]]  # trailing 3 dropped
+    assert chunks[1].chunk_key == hash_tokens(toks[8:16]) and ch.tail(toks) == toks[16:]
+    assert ch.chunk_tokens == 8 and ch.chunk(list(range(5))) == []
+    with pytest.raises(ValueError):
+        Chunker(0, 1)
+
+
+@pytest.fixture
+def svc(tmp_path):
+    lp = LiveControlPlane(tmp_path).start()
+    eng = FakeEngine(lp)
+    cfg = ServiceConfig("http://unused", "fake", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2)
+    app = build_service_app(cfg, engine_client=eng, tokenizer=ByteTokenizer())
+    with TestClient(app) as client:
+        yield client, eng
+    lp.stop()
+
+
+def test_document_lifecycle_and_infer(svc):
+    client, eng = svc
+    assert client.get("/health").json() == {"status": "ok", "vllm": True}
+    assert client.post("/documents", json={"title": "t", "text": "short"}).status_code == 400
+    text = "The quick brown fox jumps over the lazy dog. " * 3  # 135 bytes -> 4 chunks of 32
+    r = client.post("/documents", json={"title": "Doc A", "text": text})
+    assert r.status_code == 201
+    body = r.json()
+    assert body["status"] == "ready" and body["chunk_count"] == 4 and body["chunk_count_cached"] == 4
+    assert len(eng.prefills) == 4 and body["prefill_ms"] >= 0
+    doc_id = body["doc_id"]
+    listing = client.get("/documents").json()
+    assert listing[0]["doc_id"] == doc_id and listing[0]["chunk_count_total"] == 4
+    doc = client.get(f"/documents/{doc_id}").json()
+    assert "tokens" not in doc and doc["cached_mask"] == [True] * 4
+    assert client.get("/documents/nope").status_code == 404
+    assert client.post("/infer", json={"doc_ids": [], "task": "x"}).status_code == 400
+    assert client.post("/infer", json={"doc_ids": ["nope"], "task": "x"}).status_code == 404
+    r = client.post("/infer", json={"doc_ids": [doc_id], "task": "Summarise", "gen_params": {"max_tokens": 5}})
+    assert r.status_code == 200
+    out = r.json()
+    assert out["text"] == "answer" and out["completion_tokens"] == 3 and out["latency_ms"] >= 0
+    prompt, params, segments = eng.completions[-1]
+    assert params == {"max_tokens": 5}
+    assert [t for s in segments for t in s] == prompt
+    # the document's chunks appear as their own segments, so the engine can look them up by key
+    keys = {hash_tokens(s) for s in segments}
+    assert set(doc["chunk_keys"]) <= keys
+    assert "daser_ipc_register_doc" in client.get("/metrics").text
+    assert client.delete(f"/documents/{doc_id}").json() == {"ok": True, "chunks_evicted": 4}
+    assert client.delete(f"/documents/{doc_id}").status_code == 404
+    assert client.get("/documents").json() == []
+
+
+def test_engine_failures_map_to_502_and_health_degrades(svc):
+    client, eng = svc
+    eng.up = False
+    assert client.get("/health").json() == {"status": "degraded", "vllm": False}
+    eng.fail = True
+    assert client.post("/documents", json={"title": "t", "text": "x" * 100}).status_code == 502
+    eng.fail = False
+    doc_id = client.post("/documents", json={"title": "t", "text": "x" * 100}).json()["doc_id"]
+    eng.fail = True
+    assert client.post("/infer", json={"doc_ids": [doc_id], "task": "q"}).status_code == 502
+
+
+def test_service_cli_flags():
+    from daser_b200.service.__main__ import _build_daser_config, _parse_args
+
+    a = _parse_args(["--vllm-base-url", "http://x", "--model", "m", "--tokenizer", "byte"])
+    assert (a.host, a.port, a.total_slots, a.slot_size, a.chunk_blocks) == ("0.0.0.0", 8080, 1024, 0, 16)
+    assert a.store_path == "/mnt/xfs/daser.store" and a.index_path == "/mnt/xfs/daser.index"
+    cfg = _build_daser_config(a)
+    assert cfg.total_slots == 1024 and cfg.slot_size == 0
+    with pytest.raises(SystemExit):
+        _parse_args(["--tokenizer", "byte"])  # vllm engine needs url + model
+    assert _parse_args(["--engine", "native", "--tokenizer", "byte"]).native_model == "toy"
+
+
+def test_native_cpu_engine_serves_infer_with_restored_chunks(tmp_path):
+    from daser_b200.engine.rag_cpu import CpuRagEngine
+    from daser_b200.kv.layout import KVGeometry
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.vllm_client import NativeEngineClient
+    from daser_b200 import metrics
+
+    mcfg = PRESETS["toy"]
+    geo = KVGeometry(mcfg.num_layers, mcfg.num_kv_heads, mcfg.head_dim, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    engine = CpuRagEngine(mcfg, lp.socket_path, lp.cfg.store_path, num_blocks=128)
+    tok = ByteTokenizer()
+    client_obj = NativeEngineClient(engine, tok.decode)
+    cfg = ServiceConfig("", "toy", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2)
+    app = build_service_app(cfg, engine_client=client_obj, tokenizer=tok)
+    try:
+        with TestClient(app) as client:
+            doc_id = client.post("/documents", json={"title": "A", "text": "lorem ipsum dolor sit amet " * 5}).json()["doc_id"]
+            hits0 = metrics.snapshot().get("connector.chunk_hits", 0)
+            r = client.post("/infer", json={"doc_ids": [doc_id], "task": "why?", "gen_params": {"max_tokens": 1}})
+            assert r.status_code == 200 and r.json()["completion_tokens"] == 1
+            # uploaded chunks were found and restored inside a prompt that starts with the system prompt
+            assert metrics.snapshot().get("connector.chunk_hits", 0) - hits0 >= 4
+    finally:
+        engine.close()
+        lp.stop()
