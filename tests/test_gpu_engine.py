@@ -62,7 +62,7 @@ def test_gpu_rag_engine_restored_equals_recomputed(tmp_path):
         # restored + rotated KV equals KV recomputed at the new offset (up to fp8 requantisation)
         from daser_b200.engine.rag_gpu import RagRequest
 
-        r = eng.submit(RagRequest([chunks[2], chunks[0]], query, 1))
+        r = eng.submit(RagRequest([chunks[2], chunks[0]], query, 2))  # stays running: blocks are kept
         eng._ttft_step(eng.waiting.pop(0))
         off = len(chunks[2])
         blocks_restored = r.block_table[off // 16 : (off + 64) // 16]
