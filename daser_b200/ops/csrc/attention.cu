@@ -394,3 +394,43 @@ DASER_API int daser_paged_attention_fp8(const void* q, void* out, float* part_o,
   }
   return (int)e;
 }
+
+// ---- allocation-free variant (see attention_noalloc.h) ------------------------------------------
+#include "attention_noalloc.h"
+
+namespace daser {
+// Split-KV scratch that lives in the library image: partial outputs first, then the
+// log-sum-exp values.  In host code this name is only a handle for cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_scratch[(size_t)DASER_NOALLOC_MAX_ROW_SPLITS * (ATT_D + 1)];
+
+constexpr int kNoallocMaxDevices = 64;
+static float* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+}  // namespace daser
+
+DASER_API int daser_paged_attention_fp8_noalloc(const void* q, void* out, const DaserKVPool* pool, int layer,
+                                                int rank, const int32_t* block_tables, int max_blocks,
+                                                const int32_t* q_start, const int32_t* ctx_lens, int num_seqs,
+                                                int total_q, int max_q_len, int Hq, int Hkv, int head_dim,
+                                                int block_tokens, int nsplit, int split_tokens,
+                                                float softmax_scale, cudaStream_t stream) {
+  using namespace daser;
+  if (total_q < 0 || Hq <= 0 || nsplit < 1) return DASER_ERR_BAD_ARG;
+  if ((int64_t)total_q * Hq * nsplit > DASER_NOALLOC_MAX_ROW_SPLITS) return DASER_ERR_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoallocMaxDevices) return DASER_ERR_UNSUPPORTED;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // once per device, with that device current: the array's address on THIS device
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return DASER_ERR_UNSUPPORTED;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part_o = g_noalloc_ptr[dev];
+  float* part_lse = part_o + (size_t)DASER_NOALLOC_MAX_ROW_SPLITS * ATT_D;
+  return daser_paged_attention_fp8(q, out, part_o, part_lse, pool, layer, rank, block_tables, max_blocks, q_start,
+                                   ctx_lens, num_seqs, total_q, max_q_len, Hq, Hkv, head_dim, block_tokens, nsplit,
+                                   split_tokens, softmax_scale, stream);
+}
