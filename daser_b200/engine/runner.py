@@ -73,6 +73,8 @@ class GpuModelRunner:
         if tp_ctx is not None:
             self.kv_payload = tp_ctx.alloc("kv_payload", shape, torch.uint8)
             self.kv_scales = tp_ctx.alloc("kv_scales", shape[:-1] + (D // 16,), torch.float32)
+            self.kv_payload.zero_()
+            self.kv_scales.fill_(1.0)
         else:
             self.kv_payload = torch.zeros(shape, dtype=torch.uint8, device=dev)
             self.kv_scales = torch.ones(shape[:-1] + (D // 16,), dtype=torch.float32, device=dev)

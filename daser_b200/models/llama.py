@@ -164,6 +164,35 @@ class LlamaWeights:
         return cls(cfg, tp, rank, embed, layers, ones(cfg.hidden), mat(cfg.vocab_size // tp, cfg.hidden))
 
 
+def shard_weights(full: LlamaWeights, tp: int, rank: int) -> LlamaWeights:
+    """Rank ``rank``'s shard of single-rank weights (tests compare TP against TP=1 this way)."""
+    cfg = full.cfg
+    assert full.tp == 1 and cfg.num_kv_heads % tp == 0
+    D = cfg.head_dim
+    hq, hkv, inter = cfg.num_heads // tp, cfg.num_kv_heads // tp, cfg.intermediate // tp
+    q_end, k_end = cfg.num_heads * D, (cfg.num_heads + cfg.num_kv_heads) * D
+    layers = []
+    for lw in full.layers:
+        q = lw.wqkv[rank * hq * D : (rank + 1) * hq * D]
+        k = lw.wqkv[q_end + rank * hkv * D : q_end + (rank + 1) * hkv * D]
+        v = lw.wqkv[k_end + rank * hkv * D : k_end + (rank + 1) * hkv * D]
+        gate = lw.w_gate_up[rank * inter : (rank + 1) * inter]
+        up = lw.w_gate_up[cfg.intermediate + rank * inter : cfg.intermediate + (rank + 1) * inter]
+        layers.append(
+            LayerWeights(
+                input_norm=lw.input_norm,
+                wqkv=torch.cat([q, k, v]).contiguous(),
+                wo=lw.wo[:, rank * hq * D : (rank + 1) * hq * D].contiguous(),
+                post_norm=lw.post_norm,
+                w_gate_up=torch.cat([gate, up]).contiguous(),
+                w_down=lw.w_down[:, rank * inter : (rank + 1) * inter].contiguous(),
+            )
+        )
+    v_loc = cfg.vocab_size // tp
+    return LlamaWeights(cfg, tp, rank, full.embed, layers, full.final_norm,
+                        full.lm_head[rank * v_loc : (rank + 1) * v_loc].contiguous())
+
+
 class TorchPagedKV:
     """Head-major paged pool ``[L, N, 2, H, B, D]`` in a torch dtype (the CPU engine's pool)."""
 

@@ -6,6 +6,8 @@
 // Inputs that come from a split-K / reduce-scatter GEMM are fp32 accumulators: the
 // consumer reads them and, when asked, writes zeros back so the next GEMM can
 // accumulate into the same buffer without a separate memset.
+#include <string.h>
+
 #include "common.cuh"
 #include "kv_paged.h"
 
@@ -42,15 +44,63 @@ struct OutList {
   int n;
 };
 
+// Cross-rank ordering of the sequence-parallel add + RMSNorm (all pointers may be null):
+//   wait_counter / wait_target : arrivals of the reduce-scattered partials this rank must see
+//                                before it reads its accumulator rows (bumped by the GEMM epilogues
+//                                of every rank);
+//   done_counter / done_target : local count of finished CTAs; the CTA that completes it
+//   signal[0..n_signal)        : bumps each rank's "rows of rank r have landed" flag, which gates
+//                                the TMA loads of the next column-parallel GEMM there.
+struct TpSync {
+  const uint32_t* wait_counter;
+  uint32_t wait_target;
+  uint32_t* done_counter;
+  uint32_t done_target;
+  uint32_t* signal[DASER_MAX_RANKS];
+  int n_signal;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ uint64_t ew_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ew_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+#ifndef DASER_WAIT_NS
+#define DASER_WAIT_NS 2000000000ull
+#endif
+
 // out = rmsnorm(x [+ residual]) * weight ; residual <- x + residual.
 // One CTA per row, the row stays in registers (hidden <= 8 * 4 * blockDim).
 template <typename TIn>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ weight, OutList out, int64_t out_row_offset,
-                   int hidden, float eps, int zero_after) {
+                   int hidden, float eps, int zero_after, TpSync sync) {
   __shared__ float s_part[32];
+  __shared__ int s_ok;
   const int64_t row = blockIdx.x;
+  if (sync.wait_counter != nullptr) {
+    // bounded wait for the other ranks' partial sums (a second or two, never for ever)
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const uint64_t t0 = ew_timer_ns();
+      while (ew_ld_acquire_sys(sync.wait_counter) < sync.wait_target) {
+        if (ew_timer_ns() - t0 > DASER_WAIT_NS) { ok = 0; break; }
+        __nanosleep(32);
+      }
+      if (!ok && sync.status) atomicExch(sync.status, DASER_STATUS_TIMEOUT);
+      s_ok = ok;
+    }
+    __syncthreads();
+    // on a timeout the rows are still processed (from whatever arrived) so that peers are
+    // signalled and nobody downstream waits on this rank; the status word marks the step invalid
+  }
   TIn* xr = x + row * hidden;
   __nv_bfloat16* rr = residual ? residual + row * hidden : nullptr;
   float v[4][8];
@@ -93,6 +143,32 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] = v[it][i] * inv * w[i];
       for (int k = 0; k < out.n; ++k) store8_bf16(out.ptr[k] + (out_row_offset + row) * hidden + c, o);
+    }
+  }
+  if (sync.done_counter != nullptr) {
+    __threadfence_system();  // this CTA's pushes are visible system-wide before it is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(sync.done_counter, 1u);
+      if (prev + 1u == sync.done_target) {
+        __threadfence_system();
+        for (int k = 0; k < sync.n_signal; ++k)
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(sync.signal[k]) : "memory");
+      }
+    }
+  }
+}
+
+// Bounded wait until every flags[i] >= target (one thread); records a timeout in status.
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t target, uint32_t* status) {
+  const uint64_t t0 = ew_timer_ns();
+  for (int i = 0; i < n; ++i) {
+    while (ew_ld_acquire_sys(flags + i) < target) {
+      if (ew_timer_ns() - t0 > DASER_WAIT_NS) {
+        if (status) atomicExch(status, DASER_STATUS_TIMEOUT);
+        return;
+      }
+      __nanosleep(64);
     }
   }
 }
@@ -258,13 +334,21 @@ static int ew_grid(int64_t items, int threads) {
 
 }  // namespace daser
 
-// x: bf16 (x_is_fp32 = 0) or fp32 accumulators (x_is_fp32 = 1, zeroed after the read when
-// zero_after != 0).  out_ptrs[0..n_out) each receive the normalised rows at row offset
-// out_row_offset (the all-gather push when they are peers' buffers).
-DASER_API int daser_add_rmsnorm(void* x, int x_is_fp32, void* residual, const void* weight,
-                                void* const* out_ptrs, int n_out, int64_t out_row_offset,
-                                int64_t rows, int hidden, float eps, int zero_after,
-                                cudaStream_t stream) {
+// Mirrored with ctypes (ops/elementwise.py).
+typedef struct {
+  const uint32_t* wait_counter;
+  uint32_t wait_target;
+  uint32_t* done_counter;
+  uint32_t done_target;
+  uint32_t* signal[DASER_MAX_RANKS];
+  int32_t n_signal;
+  uint32_t* status;
+} DaserTpSync;
+
+DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const void* weight,
+                                   void* const* out_ptrs, int n_out, int64_t out_row_offset,
+                                   int64_t rows, int hidden, float eps, int zero_after,
+                                   const DaserTpSync* tp, cudaStream_t stream) {
   using namespace daser;
   if (rows < 0 || hidden <= 0 || hidden % 8 || n_out < 1 || n_out > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (rows == 0) return 0;
@@ -274,12 +358,39 @@ DASER_API int daser_add_rmsnorm(void* x, int x_is_fp32, void* residual, const vo
   OutList out;
   out.n = n_out;
   for (int i = 0; i < n_out; ++i) out.ptr[i] = (__nv_bfloat16*)out_ptrs[i];
+  TpSync sync;
+  memset(&sync, 0, sizeof(sync));
+  if (tp != nullptr) {
+    if (tp->n_signal < 0 || tp->n_signal > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
+    sync.wait_counter = tp->wait_counter; sync.wait_target = tp->wait_target;
+    sync.done_counter = tp->done_counter; sync.done_target = tp->done_target;
+    sync.n_signal = tp->n_signal; sync.status = tp->status;
+    for (int i = 0; i < tp->n_signal; ++i) sync.signal[i] = tp->signal[i];
+  }
   if (x_is_fp32)
     add_rmsnorm_kernel<float><<<(unsigned)rows, threads, 0, stream>>>(
-        (float*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, zero_after);
+        (float*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, zero_after, sync);
   else
     add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, stream>>>(
-        (__nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, 0);
+        (__nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, 0, sync);
+  return (int)cudaGetLastError();
+}
+
+// x: bf16 (x_is_fp32 = 0) or fp32 accumulators (x_is_fp32 = 1, zeroed after the read when
+// zero_after != 0).  out_ptrs[0..n_out) each receive the normalised rows at row offset
+// out_row_offset (the all-gather push when they are peers' buffers).
+DASER_API int daser_add_rmsnorm(void* x, int x_is_fp32, void* residual, const void* weight,
+                                void* const* out_ptrs, int n_out, int64_t out_row_offset,
+                                int64_t rows, int hidden, float eps, int zero_after,
+                                cudaStream_t stream) {
+  return daser_add_rmsnorm_tp(x, x_is_fp32, residual, weight, out_ptrs, n_out, out_row_offset, rows, hidden, eps,
+                              zero_after, nullptr, stream);
+}
+
+DASER_API int daser_wait_flags(const uint32_t* flags, int n, uint32_t target, uint32_t* status,
+                               cudaStream_t stream) {
+  if (!flags || n <= 0) return DASER_ERR_BAD_ARG;
+  daser::wait_flags_kernel<<<1, 1, 0, stream>>>(flags, n, target, status);
   return (int)cudaGetLastError();
 }
 

@@ -1,7 +1,7 @@
 // tcgen05 GEMM for the serving model: C[M,N] (+)= A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate
 // in tensor memory.  A is the activation matrix (row-major), B a Linear weight as PyTorch
 // stores it ([out_features, in_features]), so both operands are K-major and go from global
-// memory to 128-byte-swizzled shared memory with plain (non-multicast) TMA tiled loads.
+// memory to 128-byte-swizzled shared memory with plain TMA tiled loads (each CTA fetches its own tiles).
 //
 // In the reference's serving stack these GEMMs are cuBLAS/CUTLASS calls inside stock vLLM
 // (vllm/model_executor/layers/linear.py) followed, for the row-parallel layers, by a

@@ -1,5 +1,5 @@
 // Thin inline-PTX layer for the Blackwell (sm_100a) tensor path: mbarriers with bounded
-// waits, TMA tiled loads (never with cluster multicast), tcgen05 allocation, MMA issue,
+// waits, TMA tiled loads (one CTA, one destination), tcgen05 allocation, MMA issue,
 // commit and TMEM loads, and the shared-memory / instruction descriptors.
 #pragma once
 #include <cuda.h>

@@ -11,6 +11,30 @@ from daser_b200.ops import _lib
 from daser_b200.ops.kv_ops import PagedKVPool
 
 
+class TpSync(C.Structure):
+    """Mirror of ``DaserTpSync`` (``ops/csrc/elementwise.cu``)."""
+
+    _fields_ = [
+        ("wait_counter", C.c_void_p),
+        ("wait_target", C.c_uint32),
+        ("done_counter", C.c_void_p),
+        ("done_target", C.c_uint32),
+        ("signal", C.c_void_p * _lib.MAX_RANKS),
+        ("n_signal", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
+def wait_flags(flags_ptr: int, n: int, target: int, status: Optional[torch.Tensor] = None) -> None:
+    """Stream-ordered, bounded wait until ``flags[0..n) >= target`` (one-thread kernel)."""
+    _lib.check(
+        _lib.lib().daser_wait_flags(C.c_void_p(flags_ptr), n, C.c_uint32(target),
+                                    C.c_void_p(status.data_ptr()) if status is not None else None,
+                                    _lib.stream_ptr()),
+        "wait_flags",
+    )
+
+
 def _is_f32(t: torch.Tensor) -> int:
     assert t.dtype in (torch.float32, torch.bfloat16)
     return int(t.dtype == torch.float32)
@@ -25,6 +49,7 @@ def add_rmsnorm(
     zero_after: bool = False,
     out_ptrs: Optional[Sequence[int]] = None,
     out_row_offset: int = 0,
+    tp_sync: Optional[TpSync] = None,
 ) -> Optional[torch.Tensor]:
     """``out = rmsnorm(x + residual) * weight``; ``residual`` is updated in place.
 
@@ -39,11 +64,12 @@ def add_rmsnorm(
         out_ptrs = [out.data_ptr()]
     arr = (C.c_void_p * len(out_ptrs))(*out_ptrs)
     _lib.check(
-        _lib.lib().daser_add_rmsnorm(
+        _lib.lib().daser_add_rmsnorm_tp(
             C.c_void_p(x.data_ptr()), _is_f32(x),
             C.c_void_p(residual.data_ptr()) if residual is not None else None,
             C.c_void_p(weight.data_ptr()), arr, len(out_ptrs), C.c_int64(out_row_offset),
-            C.c_int64(rows), hidden, C.c_float(eps), int(zero_after), _lib.stream_ptr(),
+            C.c_int64(rows), hidden, C.c_float(eps), int(zero_after),
+            C.byref(tp_sync) if tp_sync is not None else None, _lib.stream_ptr(),
         ),
         "add_rmsnorm",
     )

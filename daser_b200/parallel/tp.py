@@ -1,0 +1,255 @@
+"""Tensor parallelism over NVLink peer memory: symmetric buffers, counters, fused forward.
+
+The reference has no tensor parallelism (its connector is not rank aware: every rank would
+write the same file offsets, ``daser/connector/daser_connector.py:150-156,652``); the stack it
+is benchmarked with (stock vLLM) runs row-parallel GEMMs followed by a separate NCCL /
+custom all-reduce (``vllm/model_executor/layers/linear.py``).  Here one process drives one
+GPU and the hot path makes no NCCL call:
+
+* **GEMM -> reduce-scatter** is the epilogue of the tcgen05 GEMM (``ops/csrc/gemm.cu``): every
+  partial tile leaves TMEM straight into the fp32 accumulator of the rank that owns those
+  rows (vector ``red.global.add`` on peer-mapped memory), then bumps that rank's arrival
+  counter.
+* **all-gather -> GEMM**: the add + RMSNorm kernel of the row owner waits for the arrivals,
+  normalises its rows and stores them into every rank's gathered-activation buffer (plain
+  16-byte peer stores), then bumps a per-source flag on every rank; the TMA producer of the
+  next column-parallel GEMM waits for exactly the flags of the rows its tile needs.
+* **chunk-KV restore** scatters from the IO rank into every rank's paged pool
+  (``ops/csrc/kv_paged.cu``); **save** has every rank compress and push its head slice into
+  the IO rank's staging buffer.
+
+NCCL is used for bootstrap, barriers between engine steps and the 8-byte-per-sequence
+exchange of greedy-sampling candidates.  Buffers that peers touch are allocated with
+``torch.distributed._symmetric_memory`` (VMM allocations exchanged between the processes).
+All device-side waits are bounded and report through a status word.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+from daser_b200.models.llama import LlamaConfig
+from daser_b200.ops import attention, elementwise as ew, gemm, kv_ops
+
+FLAG_RS = 0  # arrival counter of reduce-scattered partials
+FLAG_AG = 8  # first of tp per-source "rows landed" flags
+NUM_FLAGS = 16
+
+
+class TPContext:
+    def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._symm = symm_mem
+        self.cfg = cfg
+        self.group = group
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.group_name = group.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(self.group_name)
+        except Exception:
+            pass
+        self._cpu_group = dist.new_group(backend="gloo")
+        self._tensors: dict[str, torch.Tensor] = {}
+        self._handles: dict[str, Any] = {}
+        self.ptrs: dict[str, list[int]] = {}
+        self.max_tokens = max_tokens
+        self.rows_max = -(-max_tokens // self.tp)
+        H = cfg.hidden
+        # peers reduce into `acc`, push into `gathered`, and bump `flags`
+        self.acc = self.alloc("acc", (self.rows_max, H), torch.float32)
+        self.gathered = self.alloc("gathered", (self.rows_max * self.tp, H), torch.bfloat16)
+        self.flags = self.alloc("flags", (NUM_FLAGS,), torch.int32)
+        self.acc.zero_()
+        self.gathered.zero_()
+        self.flags.zero_()
+        # local only
+        self.h_local = torch.zeros(self.rows_max, H, dtype=torch.bfloat16, device=self.device)
+        self.done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.cand = torch.zeros(2, 64, dtype=torch.float32, device=self.device)
+        self.rs_target = 0
+        self.ag_epoch = 0
+        self.done_target = 0
+        self.save_staging: Optional[torch.Tensor] = None
+        torch.cuda.synchronize()
+        self.barrier()
+
+    # -- plumbing -------------------------------------------------------------------------
+    def alloc(self, name: str, shape, dtype) -> torch.Tensor:
+        """A tensor every rank can address: returns the local one, records all ranks' pointers."""
+        t = self._symm.empty(tuple(shape), dtype=dtype, device=self.device)
+        hdl = self._symm.rendezvous(t, self.group_name)
+        self._tensors[name], self._handles[name] = t, hdl
+        self.ptrs[name] = [int(p) for p in hdl.buffer_ptrs]
+        return t
+
+    def barrier(self) -> None:
+        dist.barrier(group=self.group, device_ids=[self.device.index])
+
+    def broadcast_object(self, obj: Any, src: int = 0) -> Any:
+        box = [obj]
+        dist.broadcast_object_list(box, src=src, group=self._cpu_group)
+        return box[0]
+
+    def global_pool(self, runner) -> kv_ops.PagedKVPool:
+        """The paged pool as the restore / save kernels see it: one base pointer per rank."""
+        local = runner.local_pool
+        return kv_ops.PagedKVPool(
+            payload_ptrs=self.ptrs["kv_payload"], scale_ptrs=self.ptrs["kv_scales"],
+            stride_layer=local.stride_layer, stride_block=local.stride_block, stride_kv=local.stride_kv,
+            stride_tok=local.stride_tok, stride_head=local.stride_head, num_blocks=local.num_blocks,
+            heads_per_rank=local.heads_per_rank, is_fp8=True, keepalive=[runner.kv_payload, runner.kv_scales],
+        )
+
+    def flag_ptr(self, rank: int, index: int) -> int:
+        return self.ptrs["flags"][rank] + 4 * index
+
+    # -- fused building blocks ---------------------------------------------------------------
+    def _maybe_reset_counters(self) -> None:
+        """Counters are 32-bit and only ever grow; restart them long before they wrap."""
+        if max(self.rs_target, self.done_target, self.ag_epoch) < (1 << 30):
+            return
+        torch.cuda.synchronize()
+        self.barrier()
+        self.flags.zero_()
+        self.done.zero_()
+        self.rs_target = self.ag_epoch = self.done_target = 0
+        torch.cuda.synchronize()
+        self.barrier()
+
+    def _norm_push(self, runner, x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor],
+                   rows: int, wait: bool) -> None:
+        """Add + RMSNorm on this rank's ``rows`` rows, pushed into every rank's ``gathered``."""
+        sync = ew.TpSync()
+        if wait:
+            sync.wait_counter = self.flag_ptr(self.rank, FLAG_RS)
+            sync.wait_target = self.rs_target
+        self.done_target += rows
+        sync.done_counter = self.done.data_ptr()
+        sync.done_target = self.done_target
+        for r in range(self.tp):
+            sync.signal[r] = self.flag_ptr(r, FLAG_AG + self.rank)
+        sync.n_signal = self.tp
+        sync.status = runner.status.data_ptr()
+        self.ag_epoch += 1
+        ew.add_rmsnorm(x[:rows], weight, residual=residual, eps=self.cfg.rms_eps, zero_after=wait,
+                       out_ptrs=self.ptrs["gathered"], out_row_offset=self.rank * rows, tp_sync=sync)
+
+    def _col_gemm(self, runner, w: torch.Tensor, acc: torch.Tensor, out_bf: torch.Tensor, T: int, rows: int):
+        """all-gather -> GEMM: A is the gathered activation, loads gated on the per-source flags."""
+        x = self.gathered[:T]
+        bn, ks = gemm.plan_tiles(T, w.shape[0], w.shape[1], allow_split=True)
+        gate = dict(gate_flags=self.flag_ptr(self.rank, FLAG_AG), gate_target=self.ag_epoch, gate_rows=rows)
+        if ks > 1:
+            gemm.linear(x, w, acc=acc[:T], block_n=bn, k_splits=ks, status=runner.status, **gate)
+            return acc[:T], True
+        gemm.linear(x, w, out=out_bf[:T], block_n=bn, k_splits=1, status=runner.status, **gate)
+        return out_bf[:T], False
+
+    def _row_gemm(self, runner, x: torch.Tensor, w: torch.Tensor, T: int, rows: int) -> None:
+        """GEMM -> reduce-scatter: partial tiles are added into the row owners' accumulators."""
+        N, K = w.shape
+        bn, ks = gemm.plan_tiles(T, N, K, allow_split=True)
+        counts = gemm.expected_arrivals(T, N, bn, ks, rows, self.tp, K)
+        self.rs_target += self.tp * counts[self.rank]
+        gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, k_splits=ks,
+                    arrive=[self.flag_ptr(r, FLAG_RS) for r in range(self.tp)], status=runner.status)
+
+    # -- the model step ---------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, runner, inp) -> torch.Tensor:
+        cfg, w = self.cfg, runner.w
+        T = inp.num_tokens
+        if T > self.max_tokens or T > runner.max_tokens:
+            raise ValueError("step exceeds the tensor-parallel buffers")
+        self._maybe_reset_counters()
+        D, B = cfg.head_dim, cfg.block_tokens
+        rows = -(-T // self.tp)
+        first = self.rank * rows
+        mine = max(0, min(rows, T - first))
+        h = self.h_local[:rows]
+        if mine < rows:
+            h[mine:].zero_()
+        if mine > 0:
+            ew.embedding(inp.tokens[first : first + mine], w.embed, out=h[:mine])
+        self._norm_push(runner, h, w.layers[0].input_norm, None, rows, wait=False)
+        for li, lw in enumerate(w.layers):
+            qkv, f32 = self._col_gemm(runner, lw.wqkv, runner.qkv_acc, runner.qkv_bf, T, rows)
+            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+            attn = runner.attn_out[:T].view(T, runner.hq, D)
+            attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
+                                      inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
+                                      runner.attn_ws)
+            self._row_gemm(runner, runner.attn_out[:T], lw.wo, T, rows)
+            self._norm_push(runner, self.acc, lw.post_norm, h, rows, wait=True)
+            gu, f32 = self._col_gemm(runner, lw.w_gate_up, runner.gu_acc, runner.gu_bf, T, rows)
+            ew.swiglu(gu, out=runner.act[:T], zero_after=f32)
+            self._row_gemm(runner, runner.act[:T], lw.w_down, T, rows)
+            nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
+            self._norm_push(runner, self.acc, nxt, h, rows, wait=True)
+        return self.sample(runner, inp)
+
+    def sample(self, runner, inp) -> torch.Tensor:
+        n = inp.num_seqs
+        # the last push must have landed from every rank before plain kernels read `gathered`
+        ew.wait_flags(self.flag_ptr(self.rank, FLAG_AG), self.tp, self.ag_epoch, runner.status)
+        torch.index_select(self.gathered, 0, inp.sample_rows[:n], out=runner.last_rows[:n])
+        gemm.linear(runner.last_rows[:n], runner.w.lm_head, acc=runner.logits_acc[:n], status=runner.status)
+        ew.argmax(runner.logits_acc[:n], runner.best_val[:n], runner.best_idx[:n],
+                  index_offset=self.rank * runner.w.vocab_local, zero_after=True)
+        cand = self.cand[:, :n]
+        cand[0].copy_(runner.best_val[:n])
+        cand[1].copy_(runner.best_idx[:n].to(torch.float32))
+        allc = torch.empty(self.tp, 2, n, dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(allc, cand.contiguous(), group=self.group)
+        winner = allc[:, 0].argmax(dim=0)
+        tok = allc[:, 1].gather(0, winner.unsqueeze(0)).squeeze(0).to(torch.int32)
+        runner.best_idx[:n].copy_(tok)
+        return runner.best_idx[:n]
+
+    # -- save: every rank pushes its heads into the IO rank's staging ---------------------------------
+    def save_step(self, engine, meta) -> None:
+        geo = engine.geo
+        specs = list(meta.reqs_to_store)
+        if not specs:
+            return
+        if self.save_staging is None:
+            self.staging_slots = 256
+            self.save_staging = self.alloc("save_staging", (self.staging_slots * geo.slot_size,), torch.uint8)
+        base0 = self.ptrs["save_staging"][0]
+        while specs:
+            batch, used = [], 0
+            while specs and used + len(specs[0].block_ids) <= self.staging_slots:
+                s = specs.pop(0)
+                batch.append((s, used))
+                used += len(s.block_ids)
+            if not batch:
+                raise ValueError("chunk larger than the save staging buffer")
+            ptrs, blocks = [], []
+            for s, first in batch:
+                for i, b in enumerate(s.block_ids):
+                    ptrs.append(base0 + (first + i) * geo.slot_size)
+                    blocks.append(b)
+            engine.kv_backend.save_ptrs(ptrs, blocks)
+            torch.cuda.synchronize()
+            engine.kv_backend.check_status()
+            self.barrier()  # every rank's head slice is in rank 0's staging
+            if self.rank == 0:
+                wk = engine.worker
+                for s, first in batch:
+                    n = len(s.block_ids)
+                    view = self.save_staging[first * geo.slot_size : (first + n) * geo.slot_size]
+                    wk.transfer.write(view, s.file_offset, n * geo.slot_size)
+                    if engine.hbm is not None:
+                        engine.hbm.admit(s.chunk_key, self.save_staging, first * geo.slot_size, n * geo.slot_size)
+                    extra = {"first_block": s.first_block_digest} if s.first_block_digest else {}
+                    wk._ipc.commit_chunk(s.chunk_key, **extra)
+                torch.cuda.synchronize()
+            self.barrier()  # staging may be overwritten again
