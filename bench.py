@@ -150,6 +150,7 @@ def main() -> None:
     ap.add_argument("--pool", type=int, default=64, help="chunks in the synthetic pool")
     ap.add_argument("--k", type=int, default=8, help="chunks per request")
     ap.add_argument("--hbm-frac", type=float, default=0.5, help="fraction of the pool the HBM tier can hold")
+    ap.add_argument("--host-frac", type=float, default=0.35, help="fraction of the pool the pinned host tier can hold")
     ap.add_argument("--store-dir", default="")
     ap.add_argument("--io-backend", default="auto")
     args = ap.parse_args()
@@ -221,7 +222,9 @@ def main() -> None:
     blocks_per_req = -(-max_ctx_tokens // cfg.block_tokens)
     t0 = time.time()
     eng = GpuRagEngine(cfg, dcfg.ipc_socket_path, dcfg.store_path, num_blocks=blocks_per_req + 128, max_tokens=256,
-                       max_seqs=8, hbm_slots=max(64, int(pool_slots * args.hbm_frac)), io_backend=args.io_backend,
+                       max_seqs=8, hbm_slots=max(64, int(pool_slots * args.hbm_frac)),
+                       host_slots=max(64, int(pool_slots * args.host_frac)) if args.host_frac > 0 else 0,
+                       io_backend=args.io_backend,
                        tp_ctx=tp_ctx, staging_slots=max(blocks_per_req, 128))
     t_init = time.time() - t0
 
@@ -306,7 +309,10 @@ def main() -> None:
                 "seq_len": int(prompt_tokens / len(done)), "chunks_per_request": args.k,
                 "chunk_pool": args.pool, "kv_codec": "fp8b16 (e4m3 + fp32 scale / 16)",
                 "io_backend": eng.worker.transfer.backend.name, "store": dcfg.store_path,
-                "hbm_tier_hit_rate": round(snap.get("hbm.hits", 0) / max(snap.get("hbm.hits", 0) + snap.get("hbm.misses", 0), 1), 3),
+                "tier_hits": {"hbm": int(snap.get("hbm.hits", 0)), "host": int(snap.get("host.hits", 0)),
+                              "file": int(snap.get("host.misses", snap.get("hbm.misses", 0)))},
+                "breakdown_ms_p50": {k: round(percentile([r.timings[k] for r in done], 50), 3)
+                                     for k in ("plan_ms", "restore_ms", "restore_device_ms", "compute_ms")},
                 "l2": "inputs larger than L2 (weights stream from HBM every step)",
                 "init_s": round(t_init, 1), "fill_s": round(t_fill, 1),
                 "io_direct_pieces": io_stats["direct_pieces"],

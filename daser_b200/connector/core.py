@@ -396,7 +396,7 @@ class WorkerHalf:
 
     def __init__(self, socket_path: str, store_path: str, geo: KVGeometry, backend: Any,
                  io_backend: str = "auto", tp: int = 1, rank: int = 0, hbm_store: Any = None,
-                 client: Optional[IPCClientSync] = None, staging_slots: int = 256,
+                 host_store: Any = None, client: Optional[IPCClientSync] = None, staging_slots: int = 256,
                  create_store_slots: int = 1024, commit: bool = True) -> None:
         from daser_b200.connector.transfer import TransferLayer
 
@@ -404,6 +404,7 @@ class WorkerHalf:
         self.kv = backend
         self.tp, self.rank = tp, rank
         self.hbm = hbm_store
+        self.host = host_store
         self._ipc = client or IPCClientSync(socket_path)
         self._commit = commit
         if not os.path.exists(store_path):
@@ -441,54 +442,73 @@ class WorkerHalf:
 
     # -- load -------------------------------------------------------------------------------------
     def start_load_kv(self) -> None:
-        """Restore every chunk named by the bound metadata (synchronous with the step)."""
+        """Restore every chunk named by the bound metadata (synchronous with the step).
+
+        Source of each chunk, first match wins: the HBM tier, the pinned host tier, the store
+        file.  A cold chunk is read straight into slots reserved in the host tier when there
+        is one (no staging copy), else into the staging arena.
+        """
         meta = self._meta
         if meta is None or not meta.reqs_to_load:
             return
         g = self.geo
-        jobs: list[tuple[ReqLoadSpec, int, int, int]] = []  # (spec, first staging slot, n slots, hbm base ptr)
+        # job = (spec, source address, n slots, IO destination address or 0, "hbm" | "host" | "host_fill" | "staging")
+        jobs: list[tuple[ReqLoadSpec, int, int, int, str]] = []
         used = 0
         for spec in meta.reqs_to_load:
             n = len(spec.block_ids)
             if n == 0:
                 continue
+            skip = spec.skip_slots * g.slot_size
             hit = self.hbm.lookup(spec.chunk_key) if self.hbm is not None else None
             if hit is not None:
-                jobs.append((spec, -1, n, hit + spec.skip_slots * g.slot_size))
-                metrics.inc("connector.hbm_hits")
+                jobs.append((spec, hit + skip, n, 0, "hbm"))
                 continue
+            hit = self.host.lookup(spec.chunk_key) if self.host is not None else None
+            if hit is not None:
+                jobs.append((spec, hit + skip, n, 0, "host"))
+                continue
+            if self.host is not None and spec.skip_slots == 0:
+                off = self.host.reserve(spec.chunk_key, n * g.slot_size)
+                if off is not None:
+                    ptr = self.host.arena.data_ptr() + off
+                    jobs.append((spec, ptr, n, ptr, "host_fill"))
+                    continue
             if used + n > self._staging_slots:
                 self._run_loads(jobs)  # staging full: flush what we have, then go on
                 jobs, used = [], 0
             if n > self._staging_slots:
                 raise ValueError(f"chunk of {n} slots exceeds staging capacity {self._staging_slots}")
-            jobs.append((spec, used, n, 0))
+            ptr = self._staging.data_ptr() + used * g.slot_size
+            jobs.append((spec, ptr, n, ptr, "staging"))
             used += n
         self._run_loads(jobs)
+        for tier in (self.hbm, self.host):
+            if tier is not None:
+                tier.end_step()
 
     def _run_loads(self, jobs) -> None:
         if not jobs:
             return
         g = self.geo
         t0 = time.perf_counter()
-        tickets = []
         eng = self._xfer.engine
         dev_staging = self._staging.is_cuda
+        tickets = []
         nbytes_total = 0
-        for spec, first, n, hbm_ptr in jobs:
-            if first < 0:
+        for spec, src, n, io_dst, kind in jobs:
+            if not io_dst:
                 continue
             off = spec.file_offset + spec.skip_slots * g.slot_size
             nbytes = n * g.slot_size
-            ptr = self._staging.data_ptr() + first * g.slot_size
             try:
-                tickets.append((spec, eng.submit_read(ptr, off, nbytes, device=dev_staging)))
+                tickets.append((spec, kind, eng.submit_read(io_dst, off, nbytes, device=dev_staging and kind == "staging")))
             except OSError as exc:
                 logger.warning("[CONNECTOR] read submit failed for %s: %s", spec.chunk_key, exc)
-                tickets.append((spec, None))
+                tickets.append((spec, kind, None))
             nbytes_total += nbytes
         failed: set[str] = set()
-        for spec, ticket in tickets:
+        for spec, kind, ticket in tickets:
             try:
                 if ticket is None:
                     raise OSError("submit failed")
@@ -498,6 +518,8 @@ class WorkerHalf:
                 failed.add(spec.chunk_key)
                 self._load_errors.update(spec.block_ids)
                 metrics.inc("connector.load_errors")
+                if kind == "host_fill":
+                    self.host.evict(spec.chunk_key)  # the reserved slots hold garbage
         io_ms = (time.perf_counter() - t0) * 1e3
         self.last_load_bytes, self.last_load_io_ms = nbytes_total, io_ms
         if nbytes_total:
@@ -506,27 +528,42 @@ class WorkerHalf:
         ptrs: list[int] = []
         blocks: list[int] = []
         deltas: list[int] = []
-        for spec, first, n, hbm_ptr in jobs:
+        for spec, src, n, io_dst, kind in jobs:
             if spec.chunk_key in failed:
                 continue
-            base = hbm_ptr if first < 0 else self._staging.data_ptr() + first * g.slot_size
             for i in range(n):
-                ptrs.append(base + i * g.slot_size)
+                ptrs.append(src + i * g.slot_size)
                 blocks.append(spec.block_ids[i])
                 deltas.append(spec.delta)
+            if kind != "hbm":
+                metrics.inc("connector.bytes_over_pcie", n * g.slot_size)
         if self.kv.device_kind == "cuda":
             self.kv.restore_ptrs(ptrs, blocks, deltas)
             if self.hbm is not None:
-                for spec, first, n, _ in jobs:
-                    if first >= 0 and spec.chunk_key not in failed and spec.skip_slots == 0:
-                        self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
-            torch.cuda.current_stream().synchronize()  # staging is reused by the next step
+                # promote what came from below; the copies are stream-ordered after the kernel
+                for spec, src, n, io_dst, kind in jobs:
+                    if kind == "hbm" or spec.chunk_key in failed or spec.skip_slots:
+                        continue
+                    arena = self.host.arena if kind in ("host", "host_fill") else self._staging
+                    self.hbm.admit(spec.chunk_key, arena, src - arena.data_ptr(), n * g.slot_size)
+            torch.cuda.current_stream().synchronize()  # sources may be reused by the next step
             self.kv.check_status()
         else:
-            base0 = self._staging.data_ptr()
-            rows = [(p - base0) // g.slot_size for p in ptrs]
-            images = self._staging.view(-1, g.slot_size)[torch.as_tensor(rows, dtype=torch.long)]
+            images = torch.empty((len(ptrs), g.slot_size), dtype=torch.uint8)
+            for row, ptr in enumerate(ptrs):
+                images[row] = self._image_at(ptr)
             self.kv.restore(images, blocks, deltas)
+
+    def _image_at(self, ptr: int) -> torch.Tensor:
+        """CPU path: the slot image at host address ``ptr`` (staging or host tier)."""
+        g = self.geo
+        for arena in (self._staging, self.host.arena if self.host is not None else None):
+            if arena is None or arena.is_cuda:
+                continue
+            base = arena.data_ptr()
+            if base <= ptr < base + arena.numel():
+                return arena[ptr - base : ptr - base + g.slot_size]
+        raise ValueError("slot image address outside the host arenas")
 
     def wait_for_layer_load(self, layer_name: str) -> None:
         """Nothing to wait for: loads complete inside :meth:`start_load_kv`."""
@@ -597,6 +634,10 @@ class WorkerHalf:
             metrics.inc("connector.bytes_stored", n * g.slot_size)
             if self.hbm is not None and self.kv.device_kind == "cuda":
                 self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+                self.hbm.end_step()
+            if self.host is not None:
+                self.host.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+                self.host.end_step()
             try:
                 extra = {"first_block": spec.first_block_digest} if spec.first_block_digest else {}
                 self._ipc.commit_chunk(spec.chunk_key, **extra)

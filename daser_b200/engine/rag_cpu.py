@@ -56,7 +56,7 @@ class RequestResult:
 class CpuRagEngine:
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 512,
                  codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
-                 io_backend: str = "auto", model_id: str = "default") -> None:
+                 io_backend: str = "auto", model_id: str = "default", host_slots: int = 0) -> None:
         self.cfg = cfg
         self.weights = LlamaWeights.random(cfg, "cpu", dtype, seed=seed)
         self.pool = TorchPagedKV(cfg, num_blocks, dtype)
@@ -64,8 +64,12 @@ class CpuRagEngine:
         self.geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens,
                               {torch.float32: 4, torch.bfloat16: 2}[dtype], codec_name)
         self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id)
+        from daser_b200.kv.hbm_store import HBMStore
+
+        self.host = HBMStore(self.geo.slot_size, host_slots, torch.device("cpu")) if host_slots > 0 else None
         self.worker = WorkerHalf(socket_path, store_path, self.geo,
-                                 TorchKVBackend(self.geo, self.pool.data, cfg.inv_freq()), io_backend=io_backend)
+                                 TorchKVBackend(self.geo, self.pool.data, cfg.inv_freq()), io_backend=io_backend,
+                                 host_store=self.host)
         self._req = 0
 
     def _next_id(self) -> str:

@@ -54,7 +54,8 @@ class RagRequest:
 
 class GpuRagEngine:
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 4096,
-                 max_tokens: int = 256, max_seqs: int = 64, hbm_slots: int = 0, io_backend: str = "auto",
+                 max_tokens: int = 256, max_seqs: int = 64, hbm_slots: int = 0, host_slots: int = 0,
+                 io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
                  staging_slots: int = 512) -> None:
         self.cfg = cfg
@@ -73,11 +74,14 @@ class GpuRagEngine:
                                         rank=self.rank, max_slots=max(staging_slots, 1024), device=self.device)
         self.kv_backend.cos_sin = self.runner.cos_sin
         self.hbm = HBMStore(self.geo.slot_size, hbm_slots, self.device) if hbm_slots > 0 else None
+        self.host = (
+            HBMStore(self.geo.slot_size, host_slots, torch.device("cpu")) if host_slots > 0 and self.rank == 0 else None
+        )
         self.is_io_rank = self.rank == 0
         self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id) if self.rank == 0 else None
         self.worker = (
             WorkerHalf(socket_path, store_path, self.geo, self.kv_backend, io_backend=io_backend, tp=self.tp,
-                       rank=self.rank, hbm_store=self.hbm, staging_slots=staging_slots)
+                       rank=self.rank, hbm_store=self.hbm, host_store=self.host, staging_slots=staging_slots)
             if self.is_io_rank else None
         )
         self.waiting: list[RagRequest] = []

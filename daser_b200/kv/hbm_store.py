@@ -1,4 +1,5 @@
-"""HBM tier: hot chunks kept compressed in GPU memory, in front of the NVMe store.
+"""Memory tiers: hot chunks kept compressed in GPU memory (and warm ones in pinned host
+memory), in front of the NVMe store.
 
 No counterpart in the reference (its roadmap mentions tiered prefetch only).  Chunks are
 kept in the on-disk slot format (fp8b16 images), so the restore kernel reads them exactly as
@@ -8,6 +9,11 @@ The arena is one device allocation of ``capacity_slots`` slots.  Chunks occupy c
 slot runs (the restore work list takes one base address per chunk); replacement is LRU with
 first-fit placement: least-recently-used chunks are evicted until a large enough free run
 exists.  Keys are content hashes, so an entry never goes stale.
+
+The same class is the **host tier** when its arena is pinned host memory
+(``HBMStore(..., device=torch.device("cpu"))``): pinned memory is addressable from the GPU, so
+the restore kernel reads a warm chunk straight over PCIe, and a cold chunk is read from the
+file directly into its reserved arena slots (``reserve``) with no staging copy.
 """
 
 from __future__ import annotations
@@ -27,7 +33,14 @@ class HBMStore:
         self.slot_size = slot_size
         self.capacity = capacity_slots
         self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.arena = torch.empty(slot_size * capacity_slots, dtype=torch.uint8, device=self.device)
+        if self.device.type == "cpu":
+            self.arena = torch.empty(slot_size * capacity_slots, dtype=torch.uint8)
+            if torch.cuda.is_available():
+                self.arena = self.arena.pin_memory()
+        else:
+            self.arena = torch.empty(slot_size * capacity_slots, dtype=torch.uint8, device=self.device)
+        self.kind = "host" if self.device.type == "cpu" else "hbm"
+        self._protected: set[str] = set()
         self._chunks: "OrderedDict[str, tuple[int, int]]" = OrderedDict()  # key -> (first slot, n)
         self._free: list[tuple[int, int]] = [(0, capacity_slots)]  # sorted (first slot, n) runs
 
@@ -46,11 +59,16 @@ class HBMStore:
         """Device address of the chunk's first slot image, or None."""
         hit = self._chunks.get(key)
         if hit is None:
-            metrics.inc("hbm.misses")
+            metrics.inc(f"{self.kind}.misses")
             return None
         self._chunks.move_to_end(key)
-        metrics.inc("hbm.hits")
+        self._protected.add(key)
+        metrics.inc(f"{self.kind}.hits")
         return self.arena.data_ptr() + hit[0] * self.slot_size
+
+    def end_step(self) -> None:
+        """Entries looked up or reserved since the last call may be evicted again."""
+        self._protected.clear()
 
     # -- placement -----------------------------------------------------------------------------
     def _take(self, n: int) -> Optional[int]:
@@ -79,8 +97,32 @@ class HBMStore:
         if hit is None:
             return False
         self._release(*hit)
-        metrics.inc("hbm.evictions")
+        self._protected.discard(key)
+        metrics.inc(f"{self.kind}.evictions")
         return True
+
+    def reserve(self, key: str, nbytes: int) -> Optional[int]:
+        """Claim room for ``key`` and return the arena byte offset to fill (None if it cannot fit
+        without evicting an entry that the current step still reads)."""
+        if key in self._chunks:
+            self._chunks.move_to_end(key)
+            self._protected.add(key)
+            return self._chunks[key][0] * self.slot_size
+        if nbytes % self.slot_size:
+            raise ValueError("chunk size is not a whole number of slots")
+        n = nbytes // self.slot_size
+        if n > self.capacity:
+            return None
+        first = self._take(n)
+        while first is None:
+            victim = next((k for k in self._chunks if k not in self._protected), None)
+            if victim is None:
+                return None
+            self.evict(victim)
+            first = self._take(n)
+        self._chunks[key] = (first, n)
+        self._protected.add(key)
+        return first * self.slot_size
 
     def admit(self, key: str, src: torch.Tensor, src_offset: int, nbytes: int) -> bool:
         """Copy ``nbytes`` of slot images from ``src`` (pinned host or device uint8 tensor).
@@ -91,22 +133,11 @@ class HBMStore:
         if key in self._chunks:
             self._chunks.move_to_end(key)
             return True
-        if nbytes % self.slot_size:
-            raise ValueError("chunk size is not a whole number of slots")
-        n = nbytes // self.slot_size
-        if n > self.capacity:
+        off = self.reserve(key, nbytes)
+        if off is None:
             return False
-        first = self._take(n)
-        while first is None:
-            if not self._chunks:
-                return False
-            victim = next(iter(self._chunks))
-            self.evict(victim)
-            first = self._take(n)
-        dst = self.arena[first * self.slot_size : first * self.slot_size + nbytes]
-        dst.copy_(src[src_offset : src_offset + nbytes], non_blocking=True)
-        self._chunks[key] = (first, n)
-        metrics.inc("hbm.admitted_bytes", nbytes)
+        self.arena[off : off + nbytes].copy_(src[src_offset : src_offset + nbytes], non_blocking=True)
+        metrics.inc(f"{self.kind}.admitted_bytes", nbytes)
         return True
 
     def stats(self) -> dict[str, float]:

@@ -51,10 +51,6 @@ class TPContext:
         self.rank = dist.get_rank(group)
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.group_name = group.group_name
-        try:
-            symm_mem.enable_symm_mem_for_group(self.group_name)
-        except Exception:
-            pass
         self._cpu_group = dist.new_group(backend="gloo")
         self._tensors: dict[str, torch.Tensor] = {}
         self._handles: dict[str, Any] = {}

@@ -106,3 +106,31 @@ def test_io_error_is_reported_as_load_error(rag):
     errs = eng.worker.take_load_errors()
     assert errs == set(res.block_table[1:3])
     assert eng.worker.take_load_errors() == set()
+
+
+def test_host_tier_serves_repeat_loads_without_io(tmp_path):
+    from daser_b200 import metrics
+
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=64, slot_size=geo.slot_size).start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=64, host_slots=6)
+    try:
+        rng = random.Random(4)
+        a, b = ([rng.randrange(32000) for _ in range(64)] for _ in range(2))  # 4 slots each, tier holds 6
+        eng.store_chunk(a)
+        eng.store_chunk(b)  # evicts 'a' from the tier (admitted at save time)
+        io0 = eng.worker.transfer.engine.stats()["bytes_read"]
+        r1 = eng.run_request([1] * 16, [b], [2] * 4, keep_blocks=True)   # tier hit: no file read
+        assert eng.worker.transfer.engine.stats()["bytes_read"] == io0
+        r2 = eng.run_request([1] * 16, [a], [2] * 4, keep_blocks=True)   # cold: read into the tier
+        assert eng.worker.transfer.engine.stats()["bytes_read"] == io0 + 4 * geo.slot_size
+        r3 = eng.run_request([1] * 16, [a], [2] * 4, keep_blocks=True)   # now warm
+        assert eng.worker.transfer.engine.stats()["bytes_read"] == io0 + 4 * geo.slot_size
+        # identical KV whichever tier served it
+        assert torch.equal(eng.pool.data[:, r2.block_table[1:5]], eng.pool.data[:, r3.block_table[1:5]])
+        assert metrics.snapshot().get("host.hits", 0) >= 2
+        assert r1.restored == [True]
+    finally:
+        eng.close()
+        lp.stop()

@@ -9,6 +9,7 @@ def test_lru_and_contiguity():
     s = HBMStore(slot_size=64, capacity_slots=8, device=torch.device("cpu"))
     src = torch.arange(64 * 8, dtype=torch.int64).to(torch.uint8)
     assert s.admit("a", src, 0, 64 * 3) and s.admit("b", src, 64, 64 * 3)
+    s.end_step()
     assert s.lookup("zz") is None
     pa = s.lookup("a")  # 'a' is now most recently used
     assert pa == s.arena.data_ptr()
@@ -19,6 +20,7 @@ def test_lru_and_contiguity():
     first = (s.lookup("c") - s.arena.data_ptr()) // 64
     assert torch.equal(s.arena[first * 64 : first * 64 + 256], src[:256])
     assert not s.admit("huge", src, 0, 64 * 9)
+    s.end_step()
     assert s.evict("a") and not s.evict("a")
     assert s.admit("d", src, 0, 64 * 4)  # free runs are [0,3) and [7,8): 'c' has to go too
     assert len(s) == 1 and s.stats()["used_slots"] == 4
@@ -29,6 +31,21 @@ def test_fragmentation_evicts_until_a_run_fits():
     src = torch.zeros(32 * 6, dtype=torch.uint8)
     for k in "abc":
         s.admit(k, src, 0, 64)
+    s.end_step()
     s.evict("b")  # hole of 2 in the middle
     assert s.admit("d", src, 0, 32 * 4)  # must evict 'a' (LRU) to merge [0,4)
     assert "a" not in s and "c" in s
+
+
+def test_entries_used_by_the_current_step_are_not_evicted():
+    s = HBMStore(16, 4, torch.device("cpu"))
+    src = torch.zeros(64, dtype=torch.uint8)
+    s.admit("a", src, 0, 32)
+    s.admit("b", src, 0, 32)
+    s.end_step()
+    assert s.lookup("a") is not None  # this step reads 'a'
+    off = s.reserve("c", 32)          # 'b' can go
+    assert off is not None and "b" not in s and "a" in s
+    assert s.reserve("d", 32) is None  # would need 'a' or 'c', both in use by this step
+    s.end_step()
+    assert s.reserve("d", 32) is not None
