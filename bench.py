@@ -150,7 +150,7 @@ def main() -> None:
     ap.add_argument("--pool", type=int, default=64, help="chunks in the synthetic pool")
     ap.add_argument("--k", type=int, default=8, help="chunks per request")
     ap.add_argument("--hbm-frac", type=float, default=0.5, help="fraction of the pool the HBM tier can hold")
-    ap.add_argument("--host-frac", type=float, default=0.35, help="fraction of the pool the pinned host tier can hold")
+    ap.add_argument("--host-frac", type=float, default=1.0, help="fraction of the pool the pinned host tier can hold")
     ap.add_argument("--store-dir", default="")
     ap.add_argument("--io-backend", default="auto")
     args = ap.parse_args()

@@ -424,6 +424,9 @@ class WorkerHalf:
         else:
             self._staging = torch.empty(nbytes, dtype=torch.uint8)
         self._meta: Optional[ConnectorMeta] = None
+        # (part, parts): this worker holds one of `parts` pieces of every chunk (per-rank store
+        # files under vLLM tensor parallelism); the server publishes a chunk when all arrived
+        self.commit_parts: Optional[tuple[int, int]] = None
         self._load_errors: set[int] = set()
         self._lock = threading.Lock()
         self.last_load_bytes = 0
@@ -640,6 +643,8 @@ class WorkerHalf:
                 self.host.end_step()
             try:
                 extra = {"first_block": spec.first_block_digest} if spec.first_block_digest else {}
+                if self.commit_parts is not None:
+                    extra.update(part=self.commit_parts[0], parts=self.commit_parts[1])
                 self._ipc.commit_chunk(spec.chunk_key, **extra)
             except RuntimeError as exc:
                 logger.error("[CONNECTOR] commit of %s failed: %s", spec.chunk_key, exc)

@@ -72,6 +72,7 @@ class IPCServer:
         self._geometry.setdefault("block_tokens", block_tokens)
         self._server: Optional[asyncio.AbstractServer] = None
         self._writers: set[asyncio.StreamWriter] = set()
+        self._parts: dict[str, set[int]] = {}
         self._dirty = False
         self._cm.add_eviction_listener(self._on_evicted)
         self._handlers: dict[str, Handler] = {
@@ -185,6 +186,7 @@ class IPCServer:
 
     def _on_evicted(self, meta: ChunkMeta) -> None:
         self._ri.discard(meta.chunk_key)
+        self._parts.pop(meta.chunk_key, None)
         self._dirty = True
 
     def _reserve(self, chunk_key: str, token_count: int, model_id: str,
@@ -266,6 +268,15 @@ class IPCServer:
         meta = self._cm.store.get(chunk_key)
         if meta is None:
             raise ProtocolError(f"commit_chunk: unknown chunk_key {chunk_key}")
+        parts = int(msg.get("parts", 1) or 1)
+        if parts > 1:
+            # several writers hold a piece each (tensor-parallel workers with their own files):
+            # the chunk becomes visible when the last piece is in
+            seen = self._parts.setdefault(chunk_key, set())
+            seen.add(int(msg.get("part", 0)))
+            if len(seen) < parts:
+                return {"ok": True, "pending_parts": parts - len(seen)}
+            self._parts.pop(chunk_key, None)
         self._cm.store.mark_committed(chunk_key, msg.get("checksum"))
         await self._ri.insert(meta)
         anchor = msg.get("first_block")

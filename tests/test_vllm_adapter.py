@@ -1,0 +1,122 @@
+"""The vLLM adapter driven by a fake engine: hooks are called in vLLM's order with CPU tensors.
+
+The reference has no unit coverage of these hooks (they only run under a GPU integration
+test); here a cold pass stores a prompt's KV and a warm pass restores it, for both KV layouts
+vLLM uses.
+"""
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from conftest import LiveControlPlane
+
+pytest.importorskip("vllm.distributed.kv_transfer.kv_connector.v1.base")
+pytestmark = pytest.mark.slow
+
+L, NB, B, H, D = 3, 12, 16, 2, 32
+
+
+def _vllm_config(lp, **extra):
+    cfg = {"socket_path": lp.socket_path, "store_path": lp.cfg.store_path, "block_tokens": B, **extra}
+    return SimpleNamespace(kv_transfer_config=SimpleNamespace(kv_connector_extra_config=cfg),
+                           parallel_config=SimpleNamespace(tensor_parallel_size=1, rank=0))
+
+
+def _caches(layout, seed):
+    """Evenly spaced per-layer views of one cross-layer allocation."""
+    g = torch.Generator().manual_seed(seed)
+    shape = (2, NB, B, H, D) if layout == "KNTHD" else (NB, 2, B, H, D)
+    big = torch.randn((L, *shape), generator=g).to(torch.bfloat16)
+    return {f"model.layers.{i}.attn": big[i] for i in range(L)}, big
+
+
+def _request(rid, tokens):
+    return SimpleNamespace(request_id=rid, prompt_token_ids=tokens)
+
+
+def _blocks(ids):
+    return SimpleNamespace(get_block_ids=lambda: (ids,))
+
+
+@pytest.mark.parametrize("layout", ["KNTHD", "NKTHD"])
+@pytest.mark.parametrize("codec_name", ["raw", "fp8b16"])
+def test_cold_store_then_warm_load(tmp_path, layout, codec_name):
+    from daser_b200.connector.daser_connector import DaserConnector, DaserConnectorMeta, describe_kv_caches
+    from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorRole
+
+    bytes_per = 2 if codec_name == "raw" else 1.25
+    slot = int(L * 2 * B * H * D * bytes_per)
+    lp = LiveControlPlane(tmp_path, total_slots=32, slot_size=slot).start()
+    cfg = _vllm_config(lp, codec=codec_name)
+    sched = DaserConnector(cfg, KVConnectorRole.SCHEDULER)
+    worker = DaserConnector(cfg, KVConnectorRole.WORKER)
+    try:
+        caches, big = _caches(layout, 1)
+        assert describe_kv_caches(caches)["layout"] == layout
+        worker.register_kv_caches(caches)
+        tokens = list(range(100, 100 + 50))  # 3 full blocks + 2 tokens
+        # ---- cold pass: miss -> reservation -> store ----
+        req = _request("r1", tokens)
+        assert sched.get_num_new_matched_tokens(req, 0) == (0, False)
+        assert sched.get_num_new_matched_tokens(req, 0) == (0, False)  # vLLM may ask twice
+        sched.update_state_after_alloc(req, _blocks([7, 2, 9, 4]), 0)
+        meta = sched.build_connector_meta(SimpleNamespace(num_scheduled_tokens={"r1": 50}))
+        assert isinstance(meta, DaserConnectorMeta) and len(meta.reqs_to_store) == 1
+        assert meta.reqs_to_store[0].block_ids == [7, 2, 9]
+        worker.bind_connector_metadata(meta)
+        worker.start_load_kv(None)
+        for name in caches:
+            worker.save_kv_layer(name, caches[name], None)
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+        assert sched.request_finished(req, [7, 2, 9, 4]) == (False, None)
+        # ---- warm pass in a fresh engine: hit -> load into other blocks ----
+        caches2, big2 = _caches(layout, 2)
+        worker2 = DaserConnector(cfg, KVConnectorRole.WORKER)
+        worker2.register_kv_caches(caches2)
+        req2 = _request("r2", tokens + [1, 2, 3])
+        n, is_async = sched.get_num_new_matched_tokens(req2, 0)
+        assert (n, is_async) == (48, False)
+        sched.update_state_after_alloc(req2, _blocks([1, 5, 3, 8]), 48)
+        meta2 = sched.build_connector_meta(SimpleNamespace(num_scheduled_tokens={"r2": 5}))
+        assert meta2.reqs_to_load[0].block_ids == [1, 5, 3] and not meta2.reqs_to_store
+        worker2.bind_connector_metadata(meta2)
+        worker2.start_load_kv(None)
+        worker2.wait_for_save()
+        worker2.clear_connector_metadata()
+        assert worker2.get_block_ids_with_load_errors() == set()
+        axis = 2 if layout == "KNTHD" else 1  # block axis of the stacked [L, ...] tensor
+        for src, dst in zip([7, 2, 9], [1, 5, 3]):
+            want = big.select(axis, src).float()
+            got = torch.stack([caches2[n] for n in caches2]).select(axis, dst).float()
+            if codec_name == "raw":
+                assert torch.equal(got, want)
+            else:
+                assert torch.allclose(got, want, atol=0.3, rtol=0.13)
+        untouched = torch.stack([caches2[n] for n in caches2]).select(axis, 8)
+        assert torch.equal(untouched, big2.select(axis, 8))
+        worker2.shutdown()
+    finally:
+        worker.shutdown()
+        sched.shutdown()
+        lp.stop()
+
+
+def test_partial_commits_publish_only_when_every_rank_arrived(tmp_path):
+    from daser_b200.connector.ipc_client import IPCClientSync
+
+    lp = LiveControlPlane(tmp_path).start()
+    try:
+        c = IPCClientSync(lp.socket_path)
+        c.alloc_chunk("k", 16, "default")
+        c.commit_chunk("k", part=0, parts=2)
+        assert c.lookup_chunks(["k"], "default") == [None]
+        c.commit_chunk("k", part=0, parts=2)  # a repeat does not count twice
+        assert c.lookup_chunks(["k"], "default") == [None]
+        c.commit_chunk("k", part=1, parts=2)
+        assert c.lookup_chunks(["k"], "default")[0]["chunk_key"] == "k"
+        c.close()
+    finally:
+        lp.stop()
