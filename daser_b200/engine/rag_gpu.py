@@ -50,6 +50,7 @@ class RagRequest:
     restored_bytes: int = 0
     timings: dict = field(default_factory=dict)
     done: bool = False
+    store_misses: bool = False  # write the KV of chunks that had to be computed (cold pass)
 
 
 class GpuRagEngine:
@@ -204,6 +205,8 @@ class GpuRagEngine:
             blocks_of_chunk = set(req.block_table[off // bt : (off + len(c)) // bt])
             if not ok or (blocks_of_chunk & failed_blocks):
                 self._prefill_tokens(c, off, req.block_table)
+                if req.store_misses and not ok:
+                    self._store_in_place(req, c, off)
             else:
                 req.restored_chunks += 1
                 req.restored_bytes += (len(c) // bt) * self.geo.slot_size
@@ -230,6 +233,20 @@ class GpuRagEngine:
         else:
             self.running.append(req)
 
+    def _store_in_place(self, req: RagRequest, chunk: Sequence[int], off: int) -> None:
+        """Save a chunk that was just computed inside the request (its keys sit at ``off``)."""
+        bt = self.cfg.block_tokens
+        blocks = req.block_table[off // bt : (off + len(chunk)) // bt]
+        meta = ConnectorMeta()
+        sub = f"{req.req_id}.s{off}"
+        if self.sched is not None:
+            if self.sched.reserve_chunk_store(sub, chunk, blocks, pos_offset=off) is not None:
+                meta = self.sched.build_connector_meta([sub])
+        meta = self._bcast(meta)
+        self._save(meta)
+        if self.sched is not None:
+            self.sched.request_finished(sub)
+
     def _decode_step(self) -> None:
         batch = self.running[: self.runner.max_seqs]
         seqs = [{"tokens": [r.generated[-1]], "start_pos": r.context_len + len(r.generated) - 1,
@@ -247,9 +264,11 @@ class GpuRagEngine:
             self.running.remove(req)
         self.blocks.free(req.block_table)
 
-    def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1) -> RagRequest:
+    def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
+                 store_misses: bool = False) -> RagRequest:
         """Serve one request to completion (the call a user of the engine makes)."""
-        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens))
+        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens,
+                                     store_misses=store_misses))
         while not req.done:
             self.step()
         return req
