@@ -76,9 +76,10 @@ __device__ __forceinline__ uint32_t ew_ld_acquire_sys(const uint32_t* p) {
 #endif
 
 // out = rmsnorm(x [+ residual]) * weight ; residual <- x + residual.
-// One CTA per row, the row stays in registers (hidden <= 8 * 4 * blockDim).
-template <typename TIn>
-__global__ void __launch_bounds__(1024)
+// One CTA of up to 256 threads per row; each thread keeps ITERS fragments of 8 values in
+// registers (hidden <= 8 * ITERS * blockDim), so the row is read from memory once.
+template <typename TIn, int ITERS>
+__global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ weight, OutList out, int64_t out_row_offset,
                    int hidden, float eps, int zero_after, TpSync sync) {
@@ -103,10 +104,10 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
   }
   TIn* xr = x + row * hidden;
   __nv_bfloat16* rr = residual ? residual + row * hidden : nullptr;
-  float v[4][8];
+  float v[ITERS][8];
   float ss = 0.f;
 #pragma unroll
-  for (int it = 0; it < 4; ++it) {
+  for (int it = 0; it < ITERS; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
       Loader<TIn>::load8(const_cast<TIn*>(xr) + c, v[it], zero_after != 0);
@@ -135,7 +136,7 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
   __syncthreads();
   const float inv = s_part[0];
 #pragma unroll
-  for (int it = 0; it < 4; ++it) {
+  for (int it = 0; it < ITERS; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
       float w[8], o[8];
@@ -353,8 +354,9 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
   if (rows < 0 || hidden <= 0 || hidden % 8 || n_out < 1 || n_out > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (rows == 0) return 0;
   int threads = ((hidden / 8 + 31) / 32) * 32;
-  if (threads > 1024) threads = 1024;
-  if (hidden > threads * 8 * 4) return DASER_ERR_TOO_LARGE;
+  if (threads > 256) threads = 256;
+  const int iters = (hidden / 8 + threads - 1) / threads;
+  if (iters > 16) return DASER_ERR_TOO_LARGE;
   OutList out;
   out.n = n_out;
   for (int i = 0; i < n_out; ++i) out.ptr[i] = (__nv_bfloat16*)out_ptrs[i];
@@ -367,12 +369,19 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
     sync.n_signal = tp->n_signal; sync.status = tp->status;
     for (int i = 0; i < tp->n_signal; ++i) sync.signal[i] = tp->signal[i];
   }
-  if (x_is_fp32)
-    add_rmsnorm_kernel<float><<<(unsigned)rows, threads, 0, stream>>>(
-        (float*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, zero_after, sync);
-  else
-    add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, threads, 0, stream>>>(
-        (__nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, 0, sync);
+#define NORM_LAUNCH(TIN, IT)                                                                          \
+  add_rmsnorm_kernel<TIN, IT><<<(unsigned)rows, threads, 0, stream>>>(                                  \
+      (TIN*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, \
+      x_is_fp32 ? zero_after : 0, sync)
+#define NORM_DISPATCH(TIN)                                   \
+  if (iters <= 1) NORM_LAUNCH(TIN, 1);                       \
+  else if (iters <= 2) NORM_LAUNCH(TIN, 2);                  \
+  else if (iters <= 4) NORM_LAUNCH(TIN, 4);                  \
+  else if (iters <= 8) NORM_LAUNCH(TIN, 8);                  \
+  else NORM_LAUNCH(TIN, 16)
+  if (x_is_fp32) { NORM_DISPATCH(float); } else { NORM_DISPATCH(__nv_bfloat16); }
+#undef NORM_DISPATCH
+#undef NORM_LAUNCH
   return (int)cudaGetLastError();
 }
 

@@ -231,10 +231,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (p.epilogue == EPI_REDUCE_F32 && p.arrive[0] != nullptr) {
         // This warp's contributions are out: publish them, then bump every owner that its
         // 32 rows touch.  (The host derives the expected count per owner from the same rule.)
-        __threadfence_system();
+        // The warp barrier orders every lane's reds before lane 0's fence, and a fence is
+        // cumulative, so one system-scope fence per warp is enough.
         __syncwarp();
         const int r_first = m0 + quarter * 32;
         if (lane == 0 && r_first < p.M) {
+          __threadfence_system();
           const int o0 = r_first / p.rows_per_owner;
           const int o1 = min(r_first + 31, p.M - 1) / p.rows_per_owner;
           for (int o = o0; o <= o1; ++o)

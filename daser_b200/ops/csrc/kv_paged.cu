@@ -30,7 +30,7 @@ __device__ __forceinline__ void report(uint32_t* status, uint32_t code, uint32_t
 template <bool IMG_FP8, bool POOL_FP8>
 __global__ void __launch_bounds__(256)
 kv_restore_kernel(const DaserKVJob job, const DaserKVPool pool) {
-  extern __shared__ float s_cs[];  // cos[D/2] then sin[D/2] for this slot's delta
+  extern __shared__ __align__(16) float s_cs[];  // cos[D/2] then sin[D/2] for this slot's delta
   const int slot = blockIdx.x / job.num_layers;
   const int layer = blockIdx.x % job.num_layers;
   const int D = job.head_dim, H = job.num_kv_heads, B = job.block_tokens;
@@ -96,12 +96,19 @@ kv_restore_kernel(const DaserKVJob job, const DaserKVPool pool) {
         dequant_group16(q2, sc2, x2);
       }
       if (rotate) {
+        float c[16], sn[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 cv = *reinterpret_cast<const float4*>(&s_cs[j * FP8_GROUP + 4 * i]);
+          const float4 sv = *reinterpret_cast<const float4*>(&s_cs[half + j * FP8_GROUP + 4 * i]);
+          c[4 * i] = cv.x; c[4 * i + 1] = cv.y; c[4 * i + 2] = cv.z; c[4 * i + 3] = cv.w;
+          sn[4 * i] = sv.x; sn[4 * i + 1] = sv.y; sn[4 * i + 2] = sv.z; sn[4 * i + 3] = sv.w;
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float c = s_cs[j * FP8_GROUP + i], s = s_cs[half + j * FP8_GROUP + i];
           const float a = x1[i], b = x2[i];
-          x1[i] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-          x2[i] = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+          x1[i] = __fsub_rn(__fmul_rn(a, c[i]), __fmul_rn(b, sn[i]));
+          x2[i] = __fadd_rn(__fmul_rn(b, c[i]), __fmul_rn(a, sn[i]));
         }
       }
       if (POOL_FP8) {
