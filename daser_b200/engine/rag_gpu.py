@@ -58,7 +58,7 @@ class GpuRagEngine:
                  max_tokens: int = 256, max_seqs: int = 64, hbm_slots: int = 0, host_slots: int = 0,
                  io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
-                 staging_slots: int = 512) -> None:
+                 staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True) -> None:
         self.cfg = cfg
         self.tp = tp_ctx.tp if tp_ctx is not None else 1
         self.rank = tp_ctx.rank if tp_ctx is not None else 0
@@ -66,7 +66,8 @@ class GpuRagEngine:
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.weights = weights or LlamaWeights.random(cfg, self.device, torch.bfloat16, tp=self.tp,
                                                       rank=self.rank, seed=seed)
-        self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device)
+        self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device,
+                                     max_blocks=max_blocks, use_graphs=use_graphs)
         self.blocks = BlockAllocator(num_blocks)
         self.geo = self.runner.geo
         # the restore kernel of the IO owner scatters into every rank's pool
@@ -108,8 +109,7 @@ class GpuRagEngine:
         mt = self.runner.max_tokens
         for i in range(0, len(tokens), mt):
             piece = list(tokens[i : i + mt])
-            inp = make_step_inputs([{"tokens": piece, "start_pos": start_pos + i, "block_table": table}],
-                                   self.cfg.block_tokens, self.device)
+            inp = self.runner.stage_inputs([{"tokens": piece, "start_pos": start_pos + i, "block_table": table}])
             out = self.runner.forward(inp)
         return out
 
@@ -251,7 +251,7 @@ class GpuRagEngine:
         batch = self.running[: self.runner.max_seqs]
         seqs = [{"tokens": [r.generated[-1]], "start_pos": r.context_len + len(r.generated) - 1,
                  "block_table": r.block_table} for r in batch]
-        inp = make_step_inputs(seqs, self.cfg.block_tokens, self.device)
+        inp = self.runner.stage_inputs(seqs)
         out = self.runner.forward(inp).tolist()
         for r, tok in zip(batch, out):
             r.generated.append(int(tok))

@@ -25,7 +25,7 @@ is made on that path (:mod:`daser_b200.parallel.tp` holds the symmetric buffers 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Any, Optional
 
 import torch
 
@@ -49,11 +49,13 @@ class StepInputs:
     num_seqs: int
     max_q_len: int
     max_ctx: int
+    persistent: bool = False  # tensors are the runner's own fixed buffers (graph replay is allowed)
 
 
 class GpuModelRunner:
     def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, num_blocks: int, max_tokens: int = 256,
-                 max_seqs: int = 64, tp_ctx=None, device: Optional[torch.device] = None) -> None:
+                 max_seqs: int = 64, tp_ctx=None, device: Optional[torch.device] = None,
+                 max_blocks: int = 512, use_graphs: bool = True) -> None:
         self.cfg = cfg
         self.w = weights
         self.tp = weights.tp
@@ -104,8 +106,26 @@ class GpuModelRunner:
         self.best_val = torch.zeros(max_seqs, dtype=f32, device=dev)
         self.best_idx = torch.zeros(max_seqs, dtype=torch.int32, device=dev)
         self.attn_ws = attention.AttentionWorkspace(dev)
+        self.attn_ws.ensure(attention.MAX_ROW_SPLITS, 1, D)  # sized once: captured graphs keep its address
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
         self.softmax_scale = D**-0.5
+        # ---- persistent step inputs (pinned host mirror + device copy) ----
+        self.max_blocks = max_blocks
+        i32, i64 = torch.int32, torch.int64
+        self._in_dev = {
+            "tokens": torch.zeros(T, dtype=i32, device=dev), "positions": torch.zeros(T, dtype=i32, device=dev),
+            "slot_mapping": torch.zeros(T, dtype=i64, device=dev),
+            "block_tables": torch.zeros(max_seqs, max_blocks, dtype=i32, device=dev),
+            "q_start": torch.zeros(max_seqs + 1, dtype=i32, device=dev),
+            "ctx_lens": torch.zeros(max_seqs, dtype=i32, device=dev),
+            "sample_rows": torch.zeros(max_seqs, dtype=i64, device=dev),
+        }
+        self._in_host = {k: torch.zeros_like(v, device="cpu").pin_memory() for k, v in self._in_dev.items()}
+        self._in_event: Optional[torch.cuda.Event] = None
+        # ---- CUDA graphs of the forward, one per step shape ----
+        self.use_graphs = use_graphs
+        self._graphs: dict[tuple, Any] = {}
+        self._seen: dict[tuple, int] = {}
 
     # -- helpers ---------------------------------------------------------------------------------
     def _linear(self, x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, out_bf: torch.Tensor):
@@ -119,16 +139,89 @@ class GpuModelRunner:
         return out_bf[:M], False
 
     # -- one step -----------------------------------------------------------------------------------
+    # -- step inputs ---------------------------------------------------------------------------------
+    def stage_inputs(self, seqs: list[dict]) -> StepInputs:
+        """Write one step's inputs into the runner's fixed buffers (pinned host -> device, one
+        copy each) and describe them.  ``seqs`` = ``[{tokens, start_pos, block_table}]``."""
+        bt = self.cfg.block_tokens
+        h = self._in_host
+        if self._in_event is not None:
+            self._in_event.synchronize()  # the previous step's copies have read the pinned mirror
+        t = 0
+        h["q_start"][0] = 0
+        max_q = max_ctx = 0
+        for i, s in enumerate(seqs):
+            n, p0, table = len(s["tokens"]), s["start_pos"], s["block_table"]
+            if t + n > self.max_tokens or i >= self.max_seqs or len(table) > self.max_blocks:
+                raise ValueError("step exceeds the runner's buffers")
+            h["tokens"][t : t + n] = torch.as_tensor(s["tokens"], dtype=torch.int32)
+            pos = torch.arange(p0, p0 + n, dtype=torch.int64)
+            h["positions"][t : t + n] = pos.to(torch.int32)
+            tbl = torch.as_tensor(table, dtype=torch.int64)
+            h["slot_mapping"][t : t + n] = tbl[pos // bt] * bt + pos % bt
+            h["block_tables"][i, : len(table)] = tbl.to(torch.int32)
+            t += n
+            h["q_start"][i + 1] = t
+            h["ctx_lens"][i] = p0 + n
+            h["sample_rows"][i] = t - 1
+            max_q, max_ctx = max(max_q, n), max(max_ctx, p0 + n)
+        ns = len(seqs)
+        d = self._in_dev
+        for name, count in (("tokens", t), ("positions", t), ("slot_mapping", t), ("q_start", ns + 1),
+                            ("ctx_lens", ns), ("sample_rows", ns)):
+            d[name][:count].copy_(h[name][:count], non_blocking=True)
+        d["block_tables"][:ns].copy_(h["block_tables"][:ns], non_blocking=True)
+        if self._in_event is None:
+            self._in_event = torch.cuda.Event()
+        self._in_event.record()
+        self.h2d_bytes = t * 16 + ns * (self.max_blocks * 4 + 20) + 4
+        return StepInputs(d["tokens"][:t], d["positions"][:t], d["slot_mapping"][:t], d["block_tables"][:ns],
+                          d["q_start"][: ns + 1], d["ctx_lens"][:ns], d["sample_rows"][:ns], t, ns, max_q, max_ctx,
+                          persistent=True)
+
+    # -- one step -----------------------------------------------------------------------------------
     @torch.no_grad()
     def forward(self, inp: StepInputs) -> torch.Tensor:
         """Run the model on the step's tokens; returns the greedy next token of every sequence
-        (int32 ``[num_seqs]``, on the device)."""
-        if self.tp > 1:
-            return self.tp_ctx.forward(self, inp)
-        cfg, w = self.cfg, self.w
+        (int32 ``[num_seqs]``, on the device).
+
+        The layer loop of a step shape seen before is replayed from a CUDA graph (captured on
+        the second occurrence): a forward is several hundred short kernels and the host
+        would otherwise be the bottleneck at small token counts.
+        """
         T = inp.num_tokens
         if T > self.max_tokens or inp.num_seqs > self.max_seqs:
             raise ValueError("step exceeds the runner's buffers")
+        group = self.hq // self.hkv
+        ctx_bucket = -(-inp.max_ctx // 2048) * 2048
+        nsplit, split_tokens = attention.plan_splits(inp.num_seqs, self.hkv, inp.max_q_len, group, ctx_bucket,
+                                                     self.cfg.block_tokens, rows=T * self.hq)
+        body = self._body if self.tp == 1 else (lambda i, a, b: self.tp_ctx.forward_body(self, i, a, b))
+        key = (T, inp.num_seqs, inp.max_q_len, nsplit, split_tokens)
+        if not (self.use_graphs and inp.persistent):
+            body(inp, nsplit, split_tokens)
+        elif key in self._graphs:
+            self._graphs[key].replay()
+        else:
+            seen = self._seen.get(key, 0)
+            self._seen[key] = seen + 1
+            if seen == 0 or len(self._graphs) >= 64:
+                body(inp, nsplit, split_tokens)  # first sight: eager (also loads every kernel)
+            else:
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    body(inp, nsplit, split_tokens)
+                self._graphs[key] = graph
+                graph.replay()
+        if self.tp > 1:
+            return self.tp_ctx.sample(self, inp)
+        return self.sample(self.normed[:T], inp)
+
+    def _body(self, inp: StepInputs, nsplit: int, split_tokens: int) -> None:
+        """Embedding, all layers and the final norm on one GPU; leaves ``self.normed`` ready to sample."""
+        cfg, w = self.cfg, self.w
+        T = inp.num_tokens
         D, B = cfg.head_dim, cfg.block_tokens
         h = self.h[:T]
         normed = self.normed[:T]
@@ -141,7 +234,7 @@ class GpuModelRunner:
             attn = self.attn_out[:T].view(T, self.hq, D)
             attention.paged_attention(self.q_rot[:T], attn, self.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, self.hkv, self.softmax_scale,
-                                      self.attn_ws)
+                                      self.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
             o, f32 = self._linear(self.attn_out[:T], lw.wo, self.hid_acc, self.hid_bf)
             ew.add_rmsnorm(o, lw.post_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
             gu, f32 = self._linear(normed, lw.w_gate_up, self.gu_acc, self.gu_bf)
@@ -149,7 +242,6 @@ class GpuModelRunner:
             d, f32 = self._linear(self.act[:T], lw.w_down, self.hid_acc, self.hid_bf)
             next_norm = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             ew.add_rmsnorm(d, next_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
-        return self.sample(normed, inp)
 
     def sample(self, normed: torch.Tensor, inp: StepInputs) -> torch.Tensor:
         n = inp.num_seqs

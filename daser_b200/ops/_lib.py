@@ -80,6 +80,7 @@ class Gemm(C.Structure):
         ("gate_flags", C.c_void_p),
         ("gate_target", C.c_uint32),
         ("gate_rows", C.c_int32),
+        ("gate_base", C.c_void_p),
     ]
 
 

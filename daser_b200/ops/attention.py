@@ -11,10 +11,11 @@ from daser_b200.ops import _lib
 from daser_b200.ops.kv_ops import PagedKVPool
 
 NUM_SMS = 148
+MAX_ROW_SPLITS = 262144  # (query rows x KV splits) the split-KV scratch is sized for (135 MB)
 
 
 def plan_splits(num_seqs: int, kv_heads: int, max_q_len: int, group: int, max_ctx: int,
-                block_tokens: int = 16) -> tuple[int, int]:
+                block_tokens: int = 16, rows: int = 0) -> tuple[int, int]:
     """(nsplit, split_tokens): enough warp-sized work items to fill the GPU."""
     row_tiles = -(-max_q_len * group // 16)
     base_items = num_seqs * kv_heads * row_tiles
@@ -26,6 +27,8 @@ def plan_splits(num_seqs: int, kv_heads: int, max_q_len: int, group: int, max_ct
     by_len = max(1, max_ctx // 1024)
     max_splits = max(1, max_ctx // 256)
     nsplit = max(1, min(max(want, by_len), max_splits, 128))
+    if rows > 0:
+        nsplit = max(1, min(nsplit, MAX_ROW_SPLITS // rows))
     per = -(-max_ctx // nsplit)
     split_tokens = -(-per // block_tokens) * block_tokens
     nsplit = -(-max_ctx // split_tokens)

@@ -53,9 +53,11 @@ struct OutList {
 //                                the TMA loads of the next column-parallel GEMM there.
 struct TpSync {
   const uint32_t* wait_counter;
-  uint32_t wait_target;
+  uint32_t wait_target;   // plus *wait_base when that is set
   uint32_t* done_counter;
-  uint32_t done_target;
+  uint32_t done_target;   // plus *done_base when that is set
+  const uint32_t* wait_base;
+  const uint32_t* done_base;
   uint32_t* signal[DASER_MAX_RANKS];
   int n_signal;
   uint32_t* status;
@@ -91,7 +93,8 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
     if (threadIdx.x == 0) {
       int ok = 1;
       const uint64_t t0 = ew_timer_ns();
-      while (ew_ld_acquire_sys(sync.wait_counter) < sync.wait_target) {
+      const uint32_t want = sync.wait_target + (sync.wait_base ? *sync.wait_base : 0u);
+      while ((int32_t)(ew_ld_acquire_sys(sync.wait_counter) - want) < 0) {
         if (ew_timer_ns() - t0 > DASER_WAIT_NS) { ok = 0; break; }
         __nanosleep(32);
       }
@@ -151,7 +154,7 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
     __syncthreads();
     if (threadIdx.x == 0) {
       const uint32_t prev = atomicAdd(sync.done_counter, 1u);
-      if (prev + 1u == sync.done_target) {
+      if (prev + 1u == sync.done_target + (sync.done_base ? *sync.done_base : 0u)) {
         __threadfence_system();
         for (int k = 0; k < sync.n_signal; ++k)
           asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(sync.signal[k]) : "memory");
@@ -160,11 +163,21 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
   }
 }
 
+// epochs[i] += delta[i]: run at the end of a tensor-parallel forward so that the next
+// forward (or the next replay of the same captured graph) waits for fresh arrivals.
+__global__ void advance_epochs_kernel(uint32_t* epochs, uint32_t d0, uint32_t d1, uint32_t d2) {
+  epochs[0] += d0;
+  epochs[1] += d1;
+  epochs[2] += d2;
+}
+
 // Bounded wait until every flags[i] >= target (one thread); records a timeout in status.
-__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t target, uint32_t* status) {
+__global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t target, const uint32_t* base,
+                                  uint32_t* status) {
   const uint64_t t0 = ew_timer_ns();
+  const uint32_t want = target + (base ? *base : 0u);
   for (int i = 0; i < n; ++i) {
-    while (ew_ld_acquire_sys(flags + i) < target) {
+    while ((int32_t)(ew_ld_acquire_sys(flags + i) - want) < 0) {
       if (ew_timer_ns() - t0 > DASER_WAIT_NS) {
         if (status) atomicExch(status, DASER_STATUS_TIMEOUT);
         return;
@@ -344,6 +357,8 @@ typedef struct {
   uint32_t* signal[DASER_MAX_RANKS];
   int32_t n_signal;
   uint32_t* status;
+  const uint32_t* wait_base;
+  const uint32_t* done_base;
 } DaserTpSync;
 
 DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const void* weight,
@@ -367,6 +382,7 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
     sync.wait_counter = tp->wait_counter; sync.wait_target = tp->wait_target;
     sync.done_counter = tp->done_counter; sync.done_target = tp->done_target;
     sync.n_signal = tp->n_signal; sync.status = tp->status;
+    sync.wait_base = tp->wait_base; sync.done_base = tp->done_base;
     for (int i = 0; i < tp->n_signal; ++i) sync.signal[i] = tp->signal[i];
   }
 #define NORM_LAUNCH(TIN, IT)                                                                          \
@@ -396,10 +412,16 @@ DASER_API int daser_add_rmsnorm(void* x, int x_is_fp32, void* residual, const vo
                               zero_after, nullptr, stream);
 }
 
-DASER_API int daser_wait_flags(const uint32_t* flags, int n, uint32_t target, uint32_t* status,
-                               cudaStream_t stream) {
+DASER_API int daser_wait_flags(const uint32_t* flags, int n, uint32_t target, const uint32_t* base,
+                               uint32_t* status, cudaStream_t stream) {
   if (!flags || n <= 0) return DASER_ERR_BAD_ARG;
-  daser::wait_flags_kernel<<<1, 1, 0, stream>>>(flags, n, target, status);
+  daser::wait_flags_kernel<<<1, 1, 0, stream>>>(flags, n, target, base, status);
+  return (int)cudaGetLastError();
+}
+
+DASER_API int daser_advance_epochs(uint32_t* epochs, uint32_t d0, uint32_t d1, uint32_t d2, cudaStream_t stream) {
+  if (!epochs) return DASER_ERR_BAD_ARG;
+  daser::advance_epochs_kernel<<<1, 1, 0, stream>>>(epochs, d0, d1, d2);
   return (int)cudaGetLastError();
 }
 

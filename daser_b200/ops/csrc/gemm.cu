@@ -51,8 +51,11 @@ struct GemmParams {
   uint32_t* arrive[DASER_MAX_RANKS];  // per-owner arrival counters (may be null)
   uint32_t* status;                   // [0] = timeout flag
   // all-gather side: A rows [g*gate_rows, (g+1)*gate_rows) may be loaded once
-  // gate_flags[g] >= gate_target (null = no gating)
+  // gate_flags[g] >= gate_target + *gate_base (null flags = no gating; null base = 0).
+  // The base lives in device memory so that a captured CUDA graph can be replayed while the
+  // counters keep growing.
   const uint32_t* gate_flags;
+  const uint32_t* gate_base;
   uint32_t gate_target;
   int gate_rows;
 };
@@ -133,9 +136,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // all-gather gating: the rows of this m-tile come from one or more peers' pushes
         const int g0 = m0 / p.gate_rows;
         const int g1 = min(m0 + GEMM_BM - 1, p.M - 1) / p.gate_rows;
+        const uint32_t want = p.gate_target + (p.gate_base ? *p.gate_base : 0u);
         for (int g = g0; g <= g1 && ok; ++g) {
           const uint64_t t0 = sm100::global_timer_ns();
-          while (ld_acquire_sys(p.gate_flags + g) < p.gate_target) {
+          while ((int32_t)(ld_acquire_sys(p.gate_flags + g) - want) < 0) {
             if (*abort_flag || sm100::global_timer_ns() - t0 > DASER_WAIT_NS) { ok = false; *abort_flag = 1u; break; }
             __nanosleep(64);
           }
@@ -322,6 +326,7 @@ typedef struct {
   const uint32_t* gate_flags;
   uint32_t gate_target;
   int32_t gate_rows;
+  const uint32_t* gate_base;
 } DaserGemm;
 
 DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
@@ -343,6 +348,7 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   p.status = g->status;
   p.gate_flags = g->gate_flags;
   p.gate_target = g->gate_target;
+  p.gate_base = g->gate_base;
   p.gate_rows = g->gate_rows > 0 ? g->gate_rows : 1;
   CUtensorMap ta, tb;
   if (int e = make_tmap(&ta, g->a, g->M, g->K, g->lda, GEMM_BM)) return e;

@@ -22,16 +22,28 @@ class TpSync(C.Structure):
         ("signal", C.c_void_p * _lib.MAX_RANKS),
         ("n_signal", C.c_int32),
         ("status", C.c_void_p),
+        ("wait_base", C.c_void_p),
+        ("done_base", C.c_void_p),
     ]
 
 
-def wait_flags(flags_ptr: int, n: int, target: int, status: Optional[torch.Tensor] = None) -> None:
-    """Stream-ordered, bounded wait until ``flags[0..n) >= target`` (one-thread kernel)."""
+def wait_flags(flags_ptr: int, n: int, target: int, status: Optional[torch.Tensor] = None,
+               base_ptr: Optional[int] = None) -> None:
+    """Stream-ordered, bounded wait until ``flags[0..n) >= target (+ *base)`` (one-thread kernel)."""
     _lib.check(
-        _lib.lib().daser_wait_flags(C.c_void_p(flags_ptr), n, C.c_uint32(target),
+        _lib.lib().daser_wait_flags(C.c_void_p(flags_ptr), n, C.c_uint32(target), C.c_void_p(base_ptr),
                                     C.c_void_p(status.data_ptr()) if status is not None else None,
                                     _lib.stream_ptr()),
         "wait_flags",
+    )
+
+
+def advance_epochs(epochs: torch.Tensor, d0: int, d1: int, d2: int) -> None:
+    """``epochs[0:3] += (d0, d1, d2)`` on the stream (see ``parallel/tp.py``)."""
+    _lib.check(
+        _lib.lib().daser_advance_epochs(C.c_void_p(epochs.data_ptr()), C.c_uint32(d0), C.c_uint32(d1),
+                                        C.c_uint32(d2), _lib.stream_ptr()),
+        "advance_epochs",
     )
 
 

@@ -76,6 +76,7 @@ def linear(
     gate_flags: Optional[int] = None,
     gate_target: int = 0,
     gate_rows: int = 0,
+    gate_base: Optional[int] = None,
     ldc: Optional[int] = None,
     stream=None,
 ) -> torch.Tensor:
@@ -94,7 +95,7 @@ def linear(
     g.M, g.N, g.K = M, N, K
     g.block_n, g.k_splits = bn, ks
     g.status = status.data_ptr() if status is not None else None
-    g.gate_flags, g.gate_target, g.gate_rows = gate_flags, gate_target, gate_rows
+    g.gate_flags, g.gate_target, g.gate_rows, g.gate_base = gate_flags, gate_target, gate_rows, gate_base
     if reduce:
         g.epilogue = EPI_REDUCE_F32
         if owners is None:

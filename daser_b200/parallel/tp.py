@@ -69,9 +69,11 @@ class TPContext:
         self.h_local = torch.zeros(self.rows_max, H, dtype=torch.bfloat16, device=self.device)
         self.done = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.cand = torch.zeros(2, 64, dtype=torch.float32, device=self.device)
-        self.rs_target = 0
-        self.ag_epoch = 0
-        self.done_target = 0
+        # device-resident bases of the three growing counters (reduce-scatter arrivals, pushes
+        # per source rank, finished norm CTAs): kernels wait for base + offset, and the last
+        # kernel of a forward advances the bases, so a captured forward can be replayed
+        self.epochs = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._rs_off = self._ag_off = self._done_off = 0
         self.save_staging: Optional[torch.Tensor] = None
         torch.cuda.synchronize()
         self.barrier()
@@ -107,33 +109,24 @@ class TPContext:
         return self.ptrs["flags"][rank] + 4 * index
 
     # -- fused building blocks ---------------------------------------------------------------
-    def _maybe_reset_counters(self) -> None:
-        """Counters are 32-bit and only ever grow; restart them long before they wrap."""
-        if max(self.rs_target, self.done_target, self.ag_epoch) < (1 << 30):
-            return
-        torch.cuda.synchronize()
-        self.barrier()
-        self.flags.zero_()
-        self.done.zero_()
-        self.rs_target = self.ag_epoch = self.done_target = 0
-        torch.cuda.synchronize()
-        self.barrier()
-
     def _norm_push(self, runner, x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor],
                    rows: int, wait: bool) -> None:
         """Add + RMSNorm on this rank's ``rows`` rows, pushed into every rank's ``gathered``."""
         sync = ew.TpSync()
+        ep = self.epochs.data_ptr()
         if wait:
             sync.wait_counter = self.flag_ptr(self.rank, FLAG_RS)
-            sync.wait_target = self.rs_target
-        self.done_target += rows
+            sync.wait_target = self._rs_off
+            sync.wait_base = ep
+        self._done_off += rows
         sync.done_counter = self.done.data_ptr()
-        sync.done_target = self.done_target
+        sync.done_target = self._done_off
+        sync.done_base = ep + 8
         for r in range(self.tp):
             sync.signal[r] = self.flag_ptr(r, FLAG_AG + self.rank)
         sync.n_signal = self.tp
         sync.status = runner.status.data_ptr()
-        self.ag_epoch += 1
+        self._ag_off += 1
         ew.add_rmsnorm(x[:rows], weight, residual=residual, eps=self.cfg.rms_eps, zero_after=wait,
                        out_ptrs=self.ptrs["gathered"], out_row_offset=self.rank * rows, tp_sync=sync)
 
@@ -141,7 +134,8 @@ class TPContext:
         """all-gather -> GEMM: A is the gathered activation, loads gated on the per-source flags."""
         x = self.gathered[:T]
         bn, ks = gemm.plan_tiles(T, w.shape[0], w.shape[1], allow_split=True)
-        gate = dict(gate_flags=self.flag_ptr(self.rank, FLAG_AG), gate_target=self.ag_epoch, gate_rows=rows)
+        gate = dict(gate_flags=self.flag_ptr(self.rank, FLAG_AG), gate_target=self._ag_off, gate_rows=rows,
+                    gate_base=self.epochs.data_ptr() + 4)
         if ks > 1:
             gemm.linear(x, w, acc=acc[:T], block_n=bn, k_splits=ks, status=runner.status, **gate)
             return acc[:T], True
@@ -153,18 +147,24 @@ class TPContext:
         N, K = w.shape
         bn, ks = gemm.plan_tiles(T, N, K, allow_split=True)
         counts = gemm.expected_arrivals(T, N, bn, ks, rows, self.tp, K)
-        self.rs_target += self.tp * counts[self.rank]
+        self._rs_off += self.tp * counts[self.rank]
         gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, k_splits=ks,
                     arrive=[self.flag_ptr(r, FLAG_RS) for r in range(self.tp)], status=runner.status)
 
     # -- the model step ---------------------------------------------------------------------------
     @torch.no_grad()
-    def forward(self, runner, inp) -> torch.Tensor:
+    def forward_body(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+        """Embedding, all layers and the final norm push; ends by advancing the epoch bases.
+
+        Every launch depends only on the step's shape (offsets are relative to the bases), so
+        the runner may capture this body in a CUDA graph and replay it.  Counter comparisons
+        are wrap-safe (signed difference), so the 32-bit counters may grow for ever.
+        """
         cfg, w = self.cfg, runner.w
         T = inp.num_tokens
         if T > self.max_tokens or T > runner.max_tokens:
             raise ValueError("step exceeds the tensor-parallel buffers")
-        self._maybe_reset_counters()
+        self._rs_off = self._ag_off = self._done_off = 0
         D, B = cfg.head_dim, cfg.block_tokens
         rows = -(-T // self.tp)
         first = self.rank * rows
@@ -182,7 +182,7 @@ class TPContext:
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
-                                      runner.attn_ws)
+                                      runner.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
             self._row_gemm(runner, runner.attn_out[:T], lw.wo, T, rows)
             self._norm_push(runner, self.acc, lw.post_norm, h, rows, wait=True)
             gu, f32 = self._col_gemm(runner, lw.w_gate_up, runner.gu_acc, runner.gu_bf, T, rows)
@@ -190,12 +190,14 @@ class TPContext:
             self._row_gemm(runner, runner.act[:T], lw.w_down, T, rows)
             nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             self._norm_push(runner, self.acc, nxt, h, rows, wait=True)
-        return self.sample(runner, inp)
+        ew.advance_epochs(self.epochs, self._rs_off, self._ag_off, self._done_off)
 
     def sample(self, runner, inp) -> torch.Tensor:
         n = inp.num_seqs
         # the last push must have landed from every rank before plain kernels read `gathered`
-        ew.wait_flags(self.flag_ptr(self.rank, FLAG_AG), self.tp, self.ag_epoch, runner.status)
+        # (the bases were advanced by the forward: the last push is at base + 0)
+        ew.wait_flags(self.flag_ptr(self.rank, FLAG_AG), self.tp, 0, runner.status,
+                      base_ptr=self.epochs.data_ptr() + 4)
         torch.index_select(self.gathered, 0, inp.sample_rows[:n], out=runner.last_rows[:n])
         gemm.linear(runner.last_rows[:n], runner.w.lm_head, acc=runner.logits_acc[:n], status=runner.status)
         ew.argmax(runner.logits_acc[:n], runner.best_val[:n], runner.best_idx[:n],
@@ -243,8 +245,10 @@ class TPContext:
                     n = len(s.block_ids)
                     view = self.save_staging[first * geo.slot_size : (first + n) * geo.slot_size]
                     wk.transfer.write(view, s.file_offset, n * geo.slot_size)
-                    if engine.hbm is not None:
-                        engine.hbm.admit(s.chunk_key, self.save_staging, first * geo.slot_size, n * geo.slot_size)
+                    for tier in (engine.hbm, engine.host):
+                        if tier is not None:
+                            tier.admit(s.chunk_key, self.save_staging, first * geo.slot_size, n * geo.slot_size)
+                            tier.end_step()
                     extra = {"first_block": s.first_block_digest} if s.first_block_digest else {}
                     wk._ipc.commit_chunk(s.chunk_key, **extra)
                 torch.cuda.synchronize()
