@@ -31,7 +31,7 @@ import torch
 
 from daser_b200.kv.layout import KVGeometry
 from daser_b200.models.llama import LlamaConfig, LlamaWeights
-from daser_b200.ops import attention, elementwise as ew, gemm, kv_ops
+from daser_b200.ops import _lib, attention, elementwise as ew, gemm, kv_ops
 
 
 @dataclass
@@ -201,7 +201,9 @@ class GpuModelRunner:
         if not (self.use_graphs and inp.persistent):
             body(inp, nsplit, split_tokens)
         elif key in self._graphs:
-            self._graphs[key].replay()
+            graph, n_kernels = self._graphs[key]
+            graph.replay()
+            _lib.launch_count += n_kernels  # kernels of ours that the replay launched
         else:
             seen = self._seen.get(key, 0)
             self._seen[key] = seen + 1
@@ -210,9 +212,10 @@ class GpuModelRunner:
             else:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
+                before = _lib.launch_count
                 with torch.cuda.graph(graph):
                     body(inp, nsplit, split_tokens)
-                self._graphs[key] = graph
+                self._graphs[key] = (graph, _lib.launch_count - before)
                 graph.replay()
         if self.tp > 1:
             return self.tp_ctx.sample(self, inp)

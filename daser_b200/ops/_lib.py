@@ -74,6 +74,7 @@ class Gemm(C.Structure):
         ("epilogue", C.c_int32),
         ("n_owners", C.c_int32),
         ("rows_per_owner", C.c_int32),
+        ("dst_row_offset", C.c_int32),
         ("c", C.c_void_p * MAX_RANKS),
         ("arrive", C.c_void_p * MAX_RANKS),
         ("status", C.c_void_p),

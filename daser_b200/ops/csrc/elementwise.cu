@@ -84,7 +84,7 @@ template <typename TIn, int ITERS>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ weight, OutList out, int64_t out_row_offset,
-                   int hidden, float eps, int zero_after, TpSync sync) {
+                   int hidden, float eps, int zero_after, TpSync sync, int n_partials, int64_t partial_stride) {
   __shared__ float s_part[32];
   __shared__ int s_ok;
   const int64_t row = blockIdx.x;
@@ -114,6 +114,13 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
     const int c = (it * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
       Loader<TIn>::load8(const_cast<TIn*>(xr) + c, v[it], zero_after != 0);
+      // reduce-scatter, bf16 form: x holds one slot of partial rows per source rank
+      for (int pt = 1; pt < n_partials; ++pt) {
+        float t[8];
+        Loader<TIn>::load8(const_cast<TIn*>(xr) + pt * partial_stride + c, t, false);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[it][i] += t[i];
+      }
       if (rr) {
         float r[8];
         Loader<__nv_bfloat16>::load8(rr + c, r, false);
@@ -364,7 +371,8 @@ typedef struct {
 DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const void* weight,
                                    void* const* out_ptrs, int n_out, int64_t out_row_offset,
                                    int64_t rows, int hidden, float eps, int zero_after,
-                                   const DaserTpSync* tp, cudaStream_t stream) {
+                                   const DaserTpSync* tp, int n_partials, int64_t partial_stride,
+                                   cudaStream_t stream) {
   using namespace daser;
   if (rows < 0 || hidden <= 0 || hidden % 8 || n_out < 1 || n_out > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (rows == 0) return 0;
@@ -388,7 +396,7 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
 #define NORM_LAUNCH(TIN, IT)                                                                          \
   add_rmsnorm_kernel<TIN, IT><<<(unsigned)rows, threads, 0, stream>>>(                                  \
       (TIN*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, \
-      x_is_fp32 ? zero_after : 0, sync)
+      x_is_fp32 ? zero_after : 0, sync, n_partials < 1 ? 1 : n_partials, partial_stride)
 #define NORM_DISPATCH(TIN)                                   \
   if (iters <= 1) NORM_LAUNCH(TIN, 1);                       \
   else if (iters <= 2) NORM_LAUNCH(TIN, 2);                  \
@@ -409,7 +417,7 @@ DASER_API int daser_add_rmsnorm(void* x, int x_is_fp32, void* residual, const vo
                                 int64_t rows, int hidden, float eps, int zero_after,
                                 cudaStream_t stream) {
   return daser_add_rmsnorm_tp(x, x_is_fp32, residual, weight, out_ptrs, n_out, out_row_offset, rows, hidden, eps,
-                              zero_after, nullptr, stream);
+                              zero_after, nullptr, 1, 0, stream);
 }
 
 DASER_API int daser_wait_flags(const uint32_t* flags, int n, uint32_t target, const uint32_t* base,

@@ -16,7 +16,12 @@
 // warps 2..5 = epilogue (TMEM lane quarter = warp % 4).
 //
 // Epilogues:
-//   EPI_STORE_BF16   C is bf16, k_splits must be 1.
+//   EPI_STORE_BF16   C is bf16, k_splits must be 1.  With several owners this is the
+//                    reduce-scatter's scatter half in bf16: rank s stores its partial rows
+//                    into slot s of the owner's receive buffer ([slot][rows_per_owner][N],
+//                    dst_row_offset = s * rows_per_owner) with plain 64-byte stores and bumps the
+//                    owner's arrival counter; the owner's add + RMSNorm kernel sums the slots.
+//                    Half the NVLink bytes of the fp32 form and no atomics.
 //   EPI_REDUCE_F32   C is fp32 and is accumulated with vector red.global.add; rows are
 //                    partitioned over n_owners buffers (rows_per_owner each).  With one owner
 //                    this is local split-K; with the owners being the tensor-parallel ranks'
@@ -47,6 +52,7 @@ struct GemmParams {
   int n_owners;
   int rows_per_owner;
   int64_t ldc;
+  int64_t dst_row_offset;  // added to the row inside the owner's buffer (bf16 store epilogue)
   void* c[DASER_MAX_RANKS];
   uint32_t* arrive[DASER_MAX_RANKS];  // per-owner arrival counters (may be null)
   uint32_t* status;                   // [0] = timeout flag
@@ -210,7 +216,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!row_ok) continue;
         const int col0 = n0 + c * 32;
         if (p.epilogue == EPI_STORE_BF16) {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + local_row * p.ldc + col0;
+          __nv_bfloat16* dst =
+              reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + (local_row + p.dst_row_offset) * p.ldc + col0;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col0 + v * 8 < p.N) {
@@ -232,7 +239,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
-      if (p.epilogue == EPI_REDUCE_F32 && p.arrive[0] != nullptr) {
+      if (p.arrive[0] != nullptr) {
         // This warp's contributions are out: publish them, then bump every owner that its
         // 32 rows touch.  (The host derives the expected count per owner from the same rule.)
         // The warp barrier orders every lane's reds before lane 0's fence, and a fence is
@@ -320,6 +327,7 @@ typedef struct {
   int32_t epilogue;  // 0 = bf16 store, 1 = fp32 red.add
   int32_t n_owners;  // output row partitions (1 = plain)
   int32_t rows_per_owner;
+  int32_t dst_row_offset;
   void* c[DASER_MAX_RANKS];
   uint32_t* arrive[DASER_MAX_RANKS];
   uint32_t* status;
@@ -344,6 +352,7 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   p.n_owners = g->n_owners;
   p.rows_per_owner = g->rows_per_owner;
   p.ldc = g->ldc;
+  p.dst_row_offset = g->dst_row_offset;
   for (int i = 0; i < DASER_MAX_RANKS; ++i) { p.c[i] = g->c[i]; p.arrive[i] = g->arrive[i]; }
   p.status = g->status;
   p.gate_flags = g->gate_flags;

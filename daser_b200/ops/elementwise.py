@@ -62,6 +62,8 @@ def add_rmsnorm(
     out_ptrs: Optional[Sequence[int]] = None,
     out_row_offset: int = 0,
     tp_sync: Optional[TpSync] = None,
+    n_partials: int = 1,
+    partial_stride: int = 0,
 ) -> Optional[torch.Tensor]:
     """``out = rmsnorm(x + residual) * weight``; ``residual`` is updated in place.
 
@@ -81,7 +83,8 @@ def add_rmsnorm(
             C.c_void_p(residual.data_ptr()) if residual is not None else None,
             C.c_void_p(weight.data_ptr()), arr, len(out_ptrs), C.c_int64(out_row_offset),
             C.c_int64(rows), hidden, C.c_float(eps), int(zero_after),
-            C.byref(tp_sync) if tp_sync is not None else None, _lib.stream_ptr(),
+            C.byref(tp_sync) if tp_sync is not None else None, n_partials, C.c_int64(partial_stride),
+            _lib.stream_ptr(),
         ),
         "add_rmsnorm",
     )

@@ -77,6 +77,8 @@ def linear(
     gate_target: int = 0,
     gate_rows: int = 0,
     gate_base: Optional[int] = None,
+    scatter_bf16: bool = False,
+    dst_row_offset: int = 0,
     ldc: Optional[int] = None,
     stream=None,
 ) -> torch.Tensor:
@@ -85,6 +87,23 @@ def linear(
     assert x.stride(1) == 1 and w.stride(1) == 1
     M, K = x.shape
     N = w.shape[0]
+    if scatter_bf16:
+        # reduce-scatter, bf16 form: plain stores into slot `dst_row_offset / rows_per_owner` of
+        # every owner's receive buffer; no split-K (stores cannot accumulate)
+        assert owners is not None and rows_per_owner is not None and ldc is not None
+        g = Gemm()
+        g.a, g.b = x.data_ptr(), w.data_ptr()
+        g.lda, g.ldb, g.ldc = x.stride(0), w.stride(0), ldc
+        g.M, g.N, g.K = x.shape[0], w.shape[0], x.shape[1]
+        g.block_n, g.k_splits, g.epilogue = block_n or 64, 1, EPI_STORE_BF16
+        g.n_owners, g.rows_per_owner, g.dst_row_offset = len(owners), rows_per_owner, dst_row_offset
+        for i, ptr in enumerate(owners):
+            g.c[i] = ptr
+        for i, ptr in enumerate(arrive or []):
+            g.arrive[i] = ptr
+        g.status = status.data_ptr() if status is not None else None
+        _lib.check(_lib.lib().daser_gemm(C.byref(g), _lib.stream_ptr(stream)), "gemm")
+        return None  # type: ignore[return-value]
     reduce = acc is not None or owners is not None
     bn, ks = plan_tiles(M, N, K, allow_split=reduce)
     bn = block_n or bn

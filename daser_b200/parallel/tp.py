@@ -59,7 +59,7 @@ class TPContext:
         self.rows_max = -(-max_tokens // self.tp)
         H = cfg.hidden
         # peers reduce into `acc`, push into `gathered`, and bump `flags`
-        self.acc = self.alloc("acc", (self.rows_max, H), torch.float32)
+        self.acc = self.alloc("acc", (self.tp * self.rows_max, H), torch.bfloat16)  # [source rank][row][H]
         self.gathered = self.alloc("gathered", (self.rows_max * self.tp, H), torch.bfloat16)
         self.flags = self.alloc("flags", (NUM_FLAGS,), torch.int32)
         self.acc.zero_()
@@ -127,8 +127,10 @@ class TPContext:
         sync.n_signal = self.tp
         sync.status = runner.status.data_ptr()
         self._ag_off += 1
-        ew.add_rmsnorm(x[:rows], weight, residual=residual, eps=self.cfg.rms_eps, zero_after=wait,
-                       out_ptrs=self.ptrs["gathered"], out_row_offset=self.rank * rows, tp_sync=sync)
+        # after a reduce-scatter, x is the receive buffer: tp slots of `rows` partial rows each
+        ew.add_rmsnorm(x[:rows], weight, residual=residual, eps=self.cfg.rms_eps, zero_after=False,
+                       out_ptrs=self.ptrs["gathered"], out_row_offset=self.rank * rows, tp_sync=sync,
+                       n_partials=self.tp if wait else 1, partial_stride=rows * self.cfg.hidden)
 
     def _col_gemm(self, runner, w: torch.Tensor, acc: torch.Tensor, out_bf: torch.Tensor, T: int, rows: int):
         """all-gather -> GEMM: A is the gathered activation, loads gated on the per-source flags."""
@@ -143,12 +145,14 @@ class TPContext:
         return out_bf[:T], False
 
     def _row_gemm(self, runner, x: torch.Tensor, w: torch.Tensor, T: int, rows: int) -> None:
-        """GEMM -> reduce-scatter: partial tiles are added into the row owners' accumulators."""
+        """GEMM -> reduce-scatter: every partial tile is stored (bf16) into this rank's slot of
+        the row owner's receive buffer; the owner's norm kernel sums the slots."""
         N, K = w.shape
-        bn, ks = gemm.plan_tiles(T, N, K, allow_split=True)
-        counts = gemm.expected_arrivals(T, N, bn, ks, rows, self.tp, K)
+        bn = 64 if -(-T // 128) * -(-N // 128) < 148 else 128
+        counts = gemm.expected_arrivals(T, N, bn, 1, rows, self.tp, K)
         self._rs_off += self.tp * counts[self.rank]
-        gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, k_splits=ks,
+        gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, scatter_bf16=True,
+                    dst_row_offset=self.rank * rows,
                     arrive=[self.flag_ptr(r, FLAG_RS) for r in range(self.tp)], status=runner.status)
 
     # -- the model step ---------------------------------------------------------------------------

@@ -83,3 +83,38 @@ def test_gate_flags_release_the_loads():
     assert status.item() == 0
     ref = _ref(x, w)
     assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-2
+
+
+def test_bf16_scatter_epilogue_and_partial_sum_norm():
+    """Reduce-scatter in its bf16 form, two 'ranks' on one device: each K shard stores its partial
+    rows into its slot of the owners' receive buffers; the norm kernel sums the slots."""
+    from daser_b200.ops import elementwise as ew
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(4)
+    M, N, K, tp = 48, 512, 1024, 2
+    rows = M // tp
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    recv = [torch.zeros(tp * rows, N, dtype=torch.bfloat16, device="cuda") for _ in range(tp)]  # per owner
+    counters = torch.zeros(tp, dtype=torch.int32, device="cuda")
+    for r in range(tp):
+        ks = slice(r * K // tp, (r + 1) * K // tp)
+        gemm.linear(x[:, ks], w[:, ks], owners=[b.data_ptr() for b in recv], rows_per_owner=rows, ldc=N,
+                    scatter_bf16=True, dst_row_offset=r * rows, block_n=64,
+                    arrive=[counters.data_ptr() + 4 * i for i in range(tp)])
+    torch.cuda.synchronize()
+    ref = x.float() @ w.float().t()
+    per_rank = gemm.expected_arrivals(M, N, 64, 1, rows, tp, K // tp)
+    assert counters.tolist() == [c * tp for c in per_rank]
+    nw = torch.ones(N, dtype=torch.bfloat16, device="cuda")
+    for owner in range(tp):
+        summed = recv[owner].view(tp, rows, N).float().sum(0)
+        want = ref[owner * rows : (owner + 1) * rows]
+        assert (summed - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 2e-2
+        res = torch.zeros(rows, N, dtype=torch.bfloat16, device="cuda")
+        out = ew.add_rmsnorm(recv[owner][:rows], nw, residual=res, n_partials=tp, partial_stride=rows * N)
+        torch.cuda.synchronize()
+        h = summed.to(torch.bfloat16).float()
+        assert torch.allclose(res.float(), h, atol=2e-2, rtol=2e-2)
+        assert torch.allclose(out.float(), h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5), atol=3e-2, rtol=3e-2)
