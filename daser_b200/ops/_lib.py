@@ -82,6 +82,9 @@ class Gemm(C.Structure):
         ("gate_target", C.c_uint32),
         ("gate_rows", C.c_int32),
         ("gate_base", C.c_void_p),
+        ("work", C.c_void_p),
+        ("work_ld", C.c_int64),
+        ("tile_counters", C.c_void_p),
     ]
 
 

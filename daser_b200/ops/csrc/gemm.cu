@@ -30,6 +30,12 @@
 //                    per-owner arrival counter is bumped (release, system scope) once the
 //                    CTA's contributions are out.
 //
+//   EPI_SPLITK_SCATTER  split-K and the bf16 scatter in one kernel: every K split adds its
+//                    partial tile into a local fp32 work buffer; the CTA that finishes a tile
+//                    last (per-tile counter) reads the sum back, hands the work buffer back
+//                    zeroed, and does the bf16 slot stores + arrival bumps of EPI_STORE_BF16.
+//                    All SMs stream weights, yet only one bf16 copy of the tile crosses NVLink.
+//
 // Every wait is bounded; on a timeout the kernel records it in `status`, drains, frees its
 // TMEM and returns.
 #include <cuda.h>
@@ -43,7 +49,7 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;  // 64 bf16 = 128 B = one swizzle row
 constexpr int GEMM_THREADS = 192;
 
-enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1 };
+enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1, EPI_SPLITK_SCATTER = 2 };
 
 struct GemmParams {
   int M, N, K;
@@ -56,6 +62,9 @@ struct GemmParams {
   void* c[DASER_MAX_RANKS];
   uint32_t* arrive[DASER_MAX_RANKS];  // per-owner arrival counters (may be null)
   uint32_t* status;                   // [0] = timeout flag
+  float* work;                        // EPI_SPLITK_SCATTER: local fp32 [M][work_ld], zero between GEMMs
+  int64_t work_ld;
+  uint32_t* tile_counters;            // EPI_SPLITK_SCATTER: one per output tile, zero between GEMMs
   // all-gather side: A rows [g*gate_rows, (g+1)*gate_rows) may be loaded once
   // gate_flags[g] >= gate_target + *gate_base (null flags = no gating; null base = 0).
   // The base lives in device memory so that a captured CUDA graph can be replayed while the
@@ -230,7 +239,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
           }
         } else {
-          float* dst = reinterpret_cast<float*>(p.c[owner]) + local_row * p.ldc + col0;
+          float* dst = p.epilogue == EPI_SPLITK_SCATTER
+                           ? p.work + (int64_t)row * p.work_ld + col0
+                           : reinterpret_cast<float*>(p.c[owner]) + local_row * p.ldc + col0;
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             if (col0 + v * 4 < p.N)
@@ -239,10 +250,54 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
-      if (p.arrive[0] != nullptr) {
+      bool signal = p.arrive[0] != nullptr;
+      if (p.epilogue == EPI_SPLITK_SCATTER) {
+        // Which CTA completes this tile?  (uniform over the 128 epilogue threads: a named
+        // barrier is safe here because `ok` is true for all of them or for none)
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t* s_last = tmem_base_slot + 2;
+        if (threadIdx.x == 64) {
+          const int live = (kb_total + kb_per - 1) / kb_per;
+          uint32_t* ctr = p.tile_counters + blockIdx.y * gridDim.x + blockIdx.x;
+          const uint32_t old = atomicAdd(ctr, 1u);
+          const bool last = old + 1u == (uint32_t)live;
+          if (last) atomicExch(ctr, 0u);
+          *s_last = last ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        signal = signal && (*s_last != 0u);
+        if (*s_last != 0u && row_ok) {
+          __threadfence();
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col0 = n0 + c * 32;
+            float* src = p.work + (int64_t)row * p.work_ld + col0;
+            __nv_bfloat16* dst =
+                reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + (local_row + p.dst_row_offset) * p.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 < p.N) {
+                float4 a, b;
+                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "l"(src + v * 8) : "memory");
+                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(src + v * 8 + 4) : "memory");
+                *reinterpret_cast<float4*>(src + v * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(src + v * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                uint4 o;
+                o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
+                o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
+                *reinterpret_cast<uint4*>(dst + v * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      if (signal) {
         // This warp's contributions are out: publish them, then bump every owner that its
         // 32 rows touch.  (The host derives the expected count per owner from the same rule.)
-        // The warp barrier orders every lane's reds before lane 0's fence, and a fence is
+        // The warp barrier orders every lane's stores before lane 0's fence, and a fence is
         // cumulative, so one system-scope fence per warp is enough.
         __syncwarp();
         const int r_first = m0 + quarter * 32;
@@ -335,6 +390,9 @@ typedef struct {
   uint32_t gate_target;
   int32_t gate_rows;
   const uint32_t* gate_base;
+  float* work;
+  int64_t work_ld;
+  uint32_t* tile_counters;
 } DaserGemm;
 
 DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
@@ -355,6 +413,10 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   p.dst_row_offset = g->dst_row_offset;
   for (int i = 0; i < DASER_MAX_RANKS; ++i) { p.c[i] = g->c[i]; p.arrive[i] = g->arrive[i]; }
   p.status = g->status;
+  p.work = g->work;
+  p.work_ld = g->work_ld;
+  p.tile_counters = g->tile_counters;
+  if (g->epilogue == EPI_SPLITK_SCATTER && (!g->work || !g->tile_counters)) return DASER_ERR_BAD_ARG;
   p.gate_flags = g->gate_flags;
   p.gate_target = g->gate_target;
   p.gate_base = g->gate_base;

@@ -25,6 +25,7 @@ from daser_b200.ops._lib import Gemm
 NUM_SMS = 148
 EPI_STORE_BF16 = 0
 EPI_REDUCE_F32 = 1
+EPI_SPLITK_SCATTER = 2
 
 
 def plan_tiles(M: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int]:
@@ -79,6 +80,8 @@ def linear(
     gate_base: Optional[int] = None,
     scatter_bf16: bool = False,
     dst_row_offset: int = 0,
+    work: Optional[torch.Tensor] = None,
+    tile_counters: Optional[torch.Tensor] = None,
     ldc: Optional[int] = None,
     stream=None,
 ) -> torch.Tensor:
@@ -96,6 +99,11 @@ def linear(
         g.lda, g.ldb, g.ldc = x.stride(0), w.stride(0), ldc
         g.M, g.N, g.K = x.shape[0], w.shape[0], x.shape[1]
         g.block_n, g.k_splits, g.epilogue = block_n or 64, 1, EPI_STORE_BF16
+        if work is not None and (k_splits or 1) > 1:
+            # split-K into the local fp32 work buffer; the last CTA of a tile scatters the sum
+            assert tile_counters is not None and work.dtype == torch.float32
+            g.k_splits, g.epilogue = k_splits, EPI_SPLITK_SCATTER
+            g.work, g.work_ld, g.tile_counters = work.data_ptr(), work.stride(0), tile_counters.data_ptr()
         g.n_owners, g.rows_per_owner, g.dst_row_offset = len(owners), rows_per_owner, dst_row_offset
         for i, ptr in enumerate(owners):
             g.c[i] = ptr

@@ -68,6 +68,7 @@ class TPContext:
         # local only
         self.h_local = torch.zeros(self.rows_max, H, dtype=torch.bfloat16, device=self.device)
         self.done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
         self.cand = torch.zeros(2, 64, dtype=torch.float32, device=self.device)
         # device-resident bases of the three growing counters (reduce-scatter arrivals, pushes
         # per source rank, finished norm CTAs): kernels wait for base + offset, and the last
@@ -148,11 +149,12 @@ class TPContext:
         """GEMM -> reduce-scatter: every partial tile is stored (bf16) into this rank's slot of
         the row owner's receive buffer; the owner's norm kernel sums the slots."""
         N, K = w.shape
-        bn = 64 if -(-T // 128) * -(-N // 128) < 148 else 128
-        counts = gemm.expected_arrivals(T, N, bn, 1, rows, self.tp, K)
+        bn, ks = gemm.plan_tiles(T, N, K, allow_split=True)
+        counts = gemm.expected_arrivals(T, N, bn, 1, rows, self.tp, K)  # one arrival per tile, whatever ks
         self._rs_off += self.tp * counts[self.rank]
-        gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, scatter_bf16=True,
-                    dst_row_offset=self.rank * rows,
+        gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, k_splits=ks,
+                    scatter_bf16=True, dst_row_offset=self.rank * rows, work=runner.hid_acc[:T],
+                    tile_counters=self.tile_counters,
                     arrive=[self.flag_ptr(r, FLAG_RS) for r in range(self.tp)], status=runner.status)
 
     # -- the model step ---------------------------------------------------------------------------

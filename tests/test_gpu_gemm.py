@@ -118,3 +118,37 @@ def test_bf16_scatter_epilogue_and_partial_sum_norm():
         h = summed.to(torch.bfloat16).float()
         assert torch.allclose(res.float(), h, atol=2e-2, rtol=2e-2)
         assert torch.allclose(out.float(), h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("M,N,K,ks", [(48, 512, 2048, 4), (130, 320, 1024, 3), (64, 8192, 4096, 4)])
+def test_splitk_scatter_epilogue(M, N, K, ks):
+    """Split-K partials meet in a local fp32 buffer; the last CTA of each tile scatters the bf16 sum
+    into the owners' slots, zeroes the buffer and its tile counter, and bumps the arrival counters."""
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(5)
+    tp = 2
+    rows = -(-M // tp)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    recv = [torch.zeros(tp * rows, N, dtype=torch.bfloat16, device="cuda") for _ in range(tp)]
+    work = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    tiles = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    counters = torch.zeros(tp, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):  # the second launch must find the work buffer and counters clean
+        gemm.linear(x, w, owners=[b.data_ptr() for b in recv], rows_per_owner=rows, ldc=N, scatter_bf16=True,
+                    dst_row_offset=1 * rows, block_n=128, k_splits=ks, work=work, tile_counters=tiles,
+                    arrive=[counters.data_ptr() + 4 * i for i in range(tp)], status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert work.abs().max().item() == 0 and tiles.abs().max().item() == 0
+    ref = x.float() @ w.float().t()
+    for owner in range(tp):
+        n = min(rows, M - owner * rows)
+        got = recv[owner].view(tp, rows, N)[1, :n].float()  # slot 1 = this "rank"
+        want = ref[owner * rows : owner * rows + n]
+        assert (got - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-2
+        assert recv[owner].view(tp, rows, N)[0].abs().max().item() == 0
+    per = gemm.expected_arrivals(M, N, 128, 1, rows, tp, K)
+    assert counters.tolist() == [2 * c for c in per]
