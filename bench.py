@@ -235,6 +235,8 @@ def main() -> None:
     torch.cuda.synchronize()
     t_fill = time.time() - t0
 
+    eng.warm_up(token_counts=(64,), context_lens=(2048, 4096, 8192))
+
     def barrier():
         if tp_ctx is not None:
             tp_ctx.barrier()

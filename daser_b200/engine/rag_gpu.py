@@ -113,6 +113,25 @@ class GpuRagEngine:
             out = self.runner.forward(inp)
         return out
 
+    def warm_up(self, token_counts: Sequence[int] = (64,), context_lens: Sequence[int] = (2048, 4096, 8192)) -> None:
+        """Run (and capture) the forward for the step shapes a workload will use, on scratch blocks.
+
+        A shape's first run is eager and its second run captures a CUDA graph, which costs
+        tens of milliseconds; serving code calls this once at start-up so that no request pays it.
+        """
+        bt = self.cfg.block_tokens
+        for ctx in context_lens:
+            for t in token_counts:
+                n_blocks = -(-ctx // bt)
+                if n_blocks > self.blocks.num_free or n_blocks > self.runner.max_blocks or t > self.runner.max_tokens:
+                    continue
+                table = self.blocks.alloc(n_blocks)
+                for _ in range(3):
+                    inp = self.runner.stage_inputs([{"tokens": [1] * t, "start_pos": ctx - t, "block_table": table}])
+                    self.runner.forward(inp)
+                torch.cuda.synchronize()
+                self.blocks.free(table)
+
     # -- offline fill ------------------------------------------------------------------------------
     def store_chunk(self, tokens: Sequence[int]) -> str:
         """Prefill ``tokens`` alone at positions 0.. and write their KV to the store."""

@@ -193,7 +193,7 @@ class GpuModelRunner:
         if T > self.max_tokens or inp.num_seqs > self.max_seqs:
             raise ValueError("step exceeds the runner's buffers")
         group = self.hq // self.hkv
-        ctx_bucket = -(-inp.max_ctx // 2048) * 2048
+        ctx_bucket = max(2048, 1 << (max(inp.max_ctx, 1) - 1).bit_length())  # powers of two: few graph shapes
         nsplit, split_tokens = attention.plan_splits(inp.num_seqs, self.hkv, inp.max_q_len, group, ctx_bucket,
                                                      self.cfg.block_tokens, rows=T * self.hq)
         body = self._body if self.tp == 1 else (lambda i, a, b: self.tp_ctx.forward_body(self, i, a, b))

@@ -28,7 +28,7 @@
 //                    peer-mapped buffers it is GEMM -> reduce-scatter: every partial tile goes
 //                    straight from TMEM over NVLink into the rank that owns those rows, and a
 //                    per-owner arrival counter is bumped (release, system scope) once the
-//                    CTA's contributions are out.
+//                    CTA's contributions are out (one bump per CTA and owner).
 //
 //   EPI_SPLITK_SCATTER  split-K and the bf16 scatter in one kernel: every K split adds its
 //                    partial tile into a local fp32 work buffer; the CTA that finishes a tile
@@ -275,36 +275,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             float* src = p.work + (int64_t)row * p.work_ld + col0;
             __nv_bfloat16* dst =
                 reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + (local_row + p.dst_row_offset) * p.ldc + col0;
+            // all loads of the chunk first (one L2 round trip), then the stores
+            float4 t[8];
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              t[v] = (col0 + v * 4 < p.N) ? __ldcg(reinterpret_cast<const float4*>(src + v * 4))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               if (col0 + v * 8 < p.N) {
-                float4 a, b;
-                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "l"(src + v * 8) : "memory");
-                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(src + v * 8 + 4) : "memory");
                 *reinterpret_cast<float4*>(src + v * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
                 *reinterpret_cast<float4*>(src + v * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
                 uint4 o;
-                o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
-                o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
+                o.x = pack_bf16x2(t[2 * v].x, t[2 * v].y); o.y = pack_bf16x2(t[2 * v].z, t[2 * v].w);
+                o.z = pack_bf16x2(t[2 * v + 1].x, t[2 * v + 1].y); o.w = pack_bf16x2(t[2 * v + 1].z, t[2 * v + 1].w);
                 *reinterpret_cast<uint4*>(dst + v * 8) = o;
               }
             }
           }
         }
       }
-      if (signal) {
-        // This warp's contributions are out: publish them, then bump every owner that its
-        // 32 rows touch.  (The host derives the expected count per owner from the same rule.)
-        // The warp barrier orders every lane's stores before lane 0's fence, and a fence is
-        // cumulative, so one system-scope fence per warp is enough.
-        __syncwarp();
-        const int r_first = m0 + quarter * 32;
-        if (lane == 0 && r_first < p.M) {
+      if (p.arrive[0] != nullptr) {
+        // The CTA's contributions are out: publish them, then bump every owner that the tile's
+        // rows touch, once per CTA.  The barrier orders every epilogue thread's stores before
+        // thread 64's fence, and a fence is cumulative, so one system-scope fence per CTA is
+        // enough.  (The host derives the expected count per owner from the same rule.)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64 && signal) {
           __threadfence_system();
-          const int o0 = r_first / p.rows_per_owner;
-          const int o1 = min(r_first + 31, p.M - 1) / p.rows_per_owner;
+          const int o0 = m0 / p.rows_per_owner;
+          const int o1 = min(m0 + GEMM_BM - 1, p.M - 1) / p.rows_per_owner;
           for (int o = o0; o <= o1; ++o)
             asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[o]) : "memory");
         }

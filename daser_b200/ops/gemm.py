@@ -47,17 +47,18 @@ def expected_arrivals(M: int, N: int, block_n: int, k_splits: int, rows_per_owne
                       K: int) -> list[int]:
     """Arrival-counter increments each owner receives from ONE rank's GEMM launch.
 
-    Mirrors the kernel: every epilogue warp (32 rows of a 128-row tile) with at least one
-    valid row bumps each owner its rows touch, once per (n tile, non-empty k split).
+    Mirrors the kernel: every CTA (one 128-row tile) bumps each owner its rows touch, once
+    per (n tile, non-empty k split).  The split-K scatter epilogue signals only from the CTA
+    that completes a tile: pass ``k_splits=1`` for it.
     """
     kb_total = -(-K // 64)
     kb_per = -(-kb_total // k_splits)
     live_splits = sum(1 for z in range(k_splits) if z * kb_per < kb_total)
     n_tiles = -(-N // block_n)
     counts = [0] * n_owners
-    for r0 in range(0, M, 32):
-        o0 = r0 // rows_per_owner
-        o1 = min(r0 + 31, M - 1) // rows_per_owner
+    for m0 in range(0, M, 128):
+        o0 = m0 // rows_per_owner
+        o1 = min(m0 + 127, M - 1) // rows_per_owner
         for o in range(o0, o1 + 1):
             counts[o] += n_tiles * live_splits
     return counts

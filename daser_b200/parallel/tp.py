@@ -149,7 +149,11 @@ class TPContext:
         """GEMM -> reduce-scatter: every partial tile is stored (bf16) into this rank's slot of
         the row owner's receive buffer; the owner's norm kernel sums the slots."""
         N, K = w.shape
-        bn, ks = gemm.plan_tiles(T, N, K, allow_split=True)
+        # measured (M = 64, N = 8192): plain bf16 stores from 64-wide tiles win up to K ~ 4k per rank,
+        # split-K with the last-CTA scatter wins beyond
+        bn, ks = (128, 4) if K >= 8192 and T <= 128 else (64, 1)
+        if -(-T // 128) * -(-N // 128) >= 148:
+            bn, ks = 128, 1
         counts = gemm.expected_arrivals(T, N, bn, 1, rows, self.tp, K)  # one arrival per tile, whatever ks
         self._rs_off += self.tp * counts[self.rank]
         gemm.linear(x, w, owners=self.ptrs["acc"], rows_per_owner=rows, ldc=N, block_n=bn, k_splits=ks,
