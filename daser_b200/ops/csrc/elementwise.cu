@@ -162,9 +162,9 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
     if (threadIdx.x == 0) {
       const uint32_t prev = atomicAdd(sync.done_counter, 1u);
       if (prev + 1u == sync.done_target + (sync.done_base ? *sync.done_base : 0u)) {
-        __threadfence_system();
+        __threadfence_system();  // acquire side of the CTA count, release side of the signals
         for (int k = 0; k < sync.n_signal; ++k)
-          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(sync.signal[k]) : "memory");
+          asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(sync.signal[k]) : "memory");
       }
     }
   }

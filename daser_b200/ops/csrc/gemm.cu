@@ -302,11 +302,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // enough.  (The host derives the expected count per owner from the same rule.)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64 && signal) {
-          __threadfence_system();
+          __threadfence_system();  // one release fence, then relaxed bumps (a release per bump would pay it again)
           const int o0 = m0 / p.rows_per_owner;
           const int o1 = min(m0 + GEMM_BM - 1, p.M - 1) / p.rows_per_owner;
           for (int o = o0; o <= o1; ++o)
-            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[o]) : "memory");
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[o]) : "memory");
         }
       }
     }
