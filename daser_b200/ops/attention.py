@@ -23,6 +23,10 @@ def plan_splits(num_seqs: int, kv_heads: int, max_q_len: int, group: int, max_ct
     # bandwidth, 2048 -> 0.78, 8192 -> 0.53, 256 -> 0.69.  So: splits of about 1024 tokens
     # whenever that still yields several waves of warps, never shorter than 256.
     target_items = NUM_SMS * 8 * 4
+    if row_tiles > 1:
+        # prefill kernel: the work unit is a CTA of four row tiles, three CTAs fit an SM
+        base_items = num_seqs * kv_heads * -(-row_tiles // 4)
+        target_items = NUM_SMS * 3 * 2
     want = max(1, -(-target_items // max(base_items, 1)))
     by_len = max(1, max_ctx // 1024)
     max_splits = max(1, max_ctx // 256)

@@ -312,6 +312,244 @@ paged_attn_fp8_kernel(const AttnParams p) {
   }
 }
 
+// ---- prefill variant: one CTA = four row tiles sharing one dequantised KV stream ----------------
+//
+// With many query tokens the per-warp kernel above converts the same fp8 page to f16 once per
+// row tile.  Here the four warps of a CTA take four consecutive row tiles (64 query rows) of
+// the same KV head, the CTA streams the pages once (cp.async ring of raw pages), all 128
+// threads dequantise a page into f16 tiles in shared memory (one 16-dim scale group per
+// thread), and every warp reads its MMA operands from there with ldmatrix (K as the "col"
+// operand directly, V through ldmatrix.trans).  f16 tiles are double buffered: one CTA
+// barrier per page.  Rows are in the standard m16n8k16 layout (no permutation tricks needed).
+constexpr int PF_STAGES = 4;
+constexpr int PF_RAW_BYTES = ATT_STAGE_BYTES;                 // 5120: K, V payload + scales
+constexpr int PF_F16_BYTES = 2 * ATT_B * ATT_D * 2;           // 8192: K and V tiles in f16
+constexpr int PF_SMEM = PF_STAGES * PF_RAW_BYTES + 2 * PF_F16_BYTES;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(128, 3)
+paged_attn_fp8_prefill_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t pf_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int kvh = blockIdx.x, seq = blockIdx.y;
+  const int grp = blockIdx.z / p.nsplit, sp = blockIdx.z % p.nsplit;
+  const int q0 = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - q0;
+  const int ctx = p.ctx_lens[seq];
+  const int G = p.G;
+  const int toks_per_tile = 16 / G;
+  const int grp_tok_first = grp * 4 * toks_per_tile;
+  if (grp_tok_first >= q_len) return;  // uniform over the CTA
+  const int grp_tok_last = min(grp_tok_first + 4 * toks_per_tile, q_len) - 1;
+  const int grp_limit = ctx - q_len + grp_tok_last + 1;
+  const int key_begin = sp * p.split_tokens;
+  const int key_end = min(key_begin + p.split_tokens, grp_limit);
+
+  // this warp's row tile
+  const int tok_first = grp_tok_first + warp * toks_per_tile;
+  const bool tile_live = tok_first < q_len;
+  const int tq0 = tok_first + g / G, tq1 = tok_first + (g + 8) / G;
+  const int hq0 = kvh * G + g % G, hq1 = kvh * G + (g + 8) % G;
+  const bool v0 = tile_live && tq0 < q_len, v1 = tile_live && tq1 < q_len;
+  const int pos0 = ctx - q_len + tq0, pos1 = ctx - q_len + tq1;
+  const int my_limit = tile_live ? ctx - q_len + min(tok_first + toks_per_tile, q_len) : 0;  // keys this tile can see
+
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  if (key_begin < key_end) {
+    // Q fragments, standard layout: [kk][0]=(row g, dims 16kk+2t,+1) [1]=(row g+8) [2]=(row g, +8) [3]=(row g+8, +8)
+    uint32_t qa[8][4];
+    {
+      const __nv_bfloat16* q0p = p.q + ((int64_t)(q0 + tq0) * p.Hq + hq0) * ATT_D;
+      const __nv_bfloat16* q1p = p.q + ((int64_t)(q0 + tq1) * p.Hq + hq1) * ATT_D;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int d = 16 * kk + 8 * h + 2 * t;
+          const uint32_t a = v0 ? *reinterpret_cast<const uint32_t*>(q0p + d) : 0u;
+          const uint32_t b = v1 ? *reinterpret_cast<const uint32_t*>(q1p + d) : 0u;
+          qa[kk][2 * h] = pack_half2(bf16_lo(a) * p.scale_log2, bf16_hi(a) * p.scale_log2);
+          qa[kk][2 * h + 1] = pack_half2(bf16_lo(b) * p.scale_log2, bf16_hi(b) * p.scale_log2);
+        }
+      }
+    }
+    uint8_t* raw = pf_smem;
+    uint8_t* f16 = pf_smem + PF_STAGES * PF_RAW_BYTES;
+    const uint32_t raw_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(raw));
+    const uint32_t f16_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(f16));
+    const int32_t* table = p.block_tables + (int64_t)seq * p.max_blocks;
+    const int page_begin = key_begin / ATT_B;
+    const int n_pages = (key_end + ATT_B - 1) / ATT_B - page_begin;
+
+    auto issue = [&](int pi) {  // 320 pieces of 16 B per page, 128 threads
+      const uint32_t sbase = raw_u32 + (pi % PF_STAGES) * PF_RAW_BYTES;
+      int blk = table[min(page_begin + pi, p.max_blocks - 1)];
+      blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+      const int64_t base_k = (int64_t)blk * p.stride_block + (int64_t)kvh * p.stride_head;
+      const int64_t base_v = base_k + p.stride_kv;
+      for (int piece = threadIdx.x; piece < 320; piece += 128) {
+        if (piece < 256) {
+          const int which = piece >> 7, q = piece & 127, tok = q >> 3, slot = q & 7;
+          const int64_t src = (which ? base_v : base_k) + (int64_t)tok * p.stride_tok + slot * 16;
+          cp_async16(sbase + which * 2048 + q * 16, p.kv_payload + src);
+        } else {
+          const int q = piece - 256, which = q >> 5, r = q & 31, tok = r >> 1, hf = r & 1;
+          const int64_t soff = ((which ? base_v : base_k) + (int64_t)tok * p.stride_tok) / 16 + hf * 4;
+          cp_async16(sbase + 4096 + which * 512 + r * 16, p.kv_scales + soff);
+        }
+      }
+    };
+#pragma unroll
+    for (int s = 0; s < PF_STAGES - 1; ++s) {
+      if (s < n_pages) issue(s);
+      cp_async_commit();
+    }
+    for (int pi = 0; pi < n_pages; ++pi) {
+      cp_async_wait<PF_STAGES - 2>();
+      __syncthreads();  // raw page pi has landed for everyone; f16 buffer (pi & 1) is free (read at pi - 2)
+      {
+        // dequantise: thread -> (which = K|V, token, 16-dim chunk); 256 chunks per page, 2 per thread
+        const uint8_t* st = raw + (pi % PF_STAGES) * PF_RAW_BYTES;
+        uint8_t* dstb = f16 + (pi & 1) * PF_F16_BYTES;
+#pragma unroll
+        for (int rep = 0; rep < 2; ++rep) {
+          const int item = threadIdx.x + rep * 128;
+          const int which = item >> 7, q = item & 127, tok = q >> 3, chunk = q & 7;
+          const uint4 w = *reinterpret_cast<const uint4*>(st + which * 2048 + q * 16);
+          const float sc = reinterpret_cast<const float*>(st + 4096 + which * 512)[tok * 8 + chunk];
+          const uint32_t sc2 = pack_half2(sc, sc);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+          uint32_t h[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            h[2 * i] = hmul2_u32(cvt_e4m3x2_f16x2((uint16_t)(ww[i] & 0xffffu)), sc2);
+            h[2 * i + 1] = hmul2_u32(cvt_e4m3x2_f16x2((uint16_t)(ww[i] >> 16)), sc2);
+          }
+          uint8_t* row = dstb + which * 4096 + tok * 256;
+          *reinterpret_cast<uint4*>(row + (((2 * chunk) ^ (tok & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<uint4*>(row + (((2 * chunk + 1) ^ (tok & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+        }
+      }
+      // the next raw page may be fetched now (its stage was consumed by the dequant of page pi - 1)
+      if (pi + PF_STAGES - 1 < n_pages) issue(pi + PF_STAGES - 1);
+      cp_async_commit();
+      __syncthreads();  // f16 tiles of page pi are complete
+      const int key0 = (page_begin + pi) * ATT_B;
+      if (tile_live && key0 < my_limit) {
+        const uint32_t kt = f16_u32 + (pi & 1) * PF_F16_BYTES, vt = kt + 4096;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        {
+          const int mi = lane >> 3, r = lane & 7;
+          const int tok = r + 8 * (mi >> 1);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            uint32_t b[4];
+            ldmatrix_x4(b, kt + tok * 256 + (((2 * kk + (mi & 1)) ^ (tok & 7)) << 4));
+            mma_16816(s[0], qa[kk], b[0], b[1]);
+            mma_16816(s[1], qa[kk], b[2], b[3]);
+          }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + nt * 8 + 2 * t + e;
+            const bool in = key < key_end;
+            if (!(in && v0 && key <= pos0)) s[nt][e] = -INFINITY;
+            if (!(in && v1 && key <= pos1)) s[nt][2 + e] = -INFINITY;
+            mx0 = fmaxf(mx0, s[nt][e]);
+            mx1 = fmaxf(mx1, s[nt][2 + e]);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float al0 = exp2f(m0 - base0), al1 = exp2f(m1 - base1);
+        const bool rescale = (mn0 != m0) || (mn1 != m1);
+        m0 = mn0;
+        m1 = mn1;
+        uint32_t pa[4];
+        {
+          const float p00 = exp2f(s[0][0] - base0), p01 = exp2f(s[0][1] - base0);
+          const float p02 = exp2f(s[0][2] - base1), p03 = exp2f(s[0][3] - base1);
+          const float p10 = exp2f(s[1][0] - base0), p11 = exp2f(s[1][1] - base0);
+          const float p12 = exp2f(s[1][2] - base1), p13 = exp2f(s[1][3] - base1);
+          l0 = l0 * al0 + (p00 + p01 + p10 + p11);
+          l1 = l1 * al1 + (p02 + p03 + p12 + p13);
+          pa[0] = pack_half2(p00, p01);
+          pa[1] = pack_half2(p02, p03);
+          pa[2] = pack_half2(p10, p11);
+          pa[3] = pack_half2(p12, p13);
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1;
+          }
+        }
+        {
+          const int mi = lane >> 3, r = lane & 7;
+          const int tok = r + 8 * (mi & 1);
+#pragma unroll
+          for (int j2 = 0; j2 < 8; ++j2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, vt + tok * 256 + (((2 * j2 + (mi >> 1)) ^ (tok & 7)) << 4));
+            mma_16816(o[2 * j2], pa, b[0], b[1]);
+            mma_16816(o[2 * j2 + 1], pa, b[2], b[3]);
+          }
+        }
+      }
+    }
+    cp_async_wait<0>();
+  }
+  if (!tile_live) return;
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (!(r ? v1 : v0)) continue;
+    const int tq = r ? tq1 : tq0, hq = r ? hq1 : hq0;
+    const float inv = r ? inv1 : inv0;
+    const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
+    if (p.nsplit == 1) {
+      __nv_bfloat16* dst = p.out + row * ATT_D + 2 * t;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        *reinterpret_cast<uint32_t*>(dst + 8 * j) = pack_bf16x2(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+    } else {
+      float* dst = p.part_o + (row * p.nsplit + sp) * ATT_D + 2 * t;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        *reinterpret_cast<float2*>(dst + 8 * j) = make_float2(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+      if (t == 0) {
+        const float l = r ? l1 : l0, m = r ? m1 : m0;
+        p.part_lse[row * p.nsplit + sp] = l > 0.f ? m + log2f(l) : -INFINITY;
+      }
+    }
+  }
+}
+
 // One warp per (query token, head): out = sum_s w_s O_s / sum_s w_s, w_s = 2^(lse_s - max).
 __global__ void __launch_bounds__(128)
 attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
@@ -382,9 +620,18 @@ DASER_API int daser_paged_attention_fp8(const void* q, void* out, float* part_o,
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(paged_attn_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(paged_attn_fp8_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+    if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  paged_attn_fp8_kernel<<<grid, ATT_WARPS * 32, smem, stream>>>(p);
+  if (p.row_tiles_max > 1) {
+    // several row tiles per KV head: the CTA-shared dequantisation pays off
+    const int groups = (p.row_tiles_max + 3) / 4;
+    const dim3 pgrid(Hkv, num_seqs, groups * nsplit);
+    paged_attn_fp8_prefill_kernel<<<pgrid, 128, PF_SMEM, stream>>>(p);
+  } else {
+    paged_attn_fp8_kernel<<<grid, ATT_WARPS * 32, smem, stream>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (nsplit > 1) {
