@@ -39,6 +39,7 @@
 // Every wait is bounded; on a timeout the kernel records it in `status`, drains, frees its
 // TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "tcgen05.cuh"
@@ -147,6 +148,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       bool ok = true;
+      // Weights do not depend on the previous kernel (nor on the peers): start streaming the
+      // first stages' B tiles at once, then wait for whatever produces A.
+      const int pre = num_kb < STAGES ? num_kb : STAGES;
+      for (int it = 0; it < pre; ++it) {
+        uint8_t* b_dst = smem + it * S::STAGE_BYTES + S::A_BYTES;
+        sm100::mbar_expect_tx(&full_bar[it], S::STAGE_BYTES);
+        sm100::tma_load_2d(b_dst, &tmap_b, &full_bar[it], (kb_begin + it) * GEMM_BK, n0);
+      }
+      // Programmatic dependent launch: this grid may have started while the previous kernel
+      // on the stream was still draining; its results are visible after this returns
+      // (a no-op when launched without the attribute).
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       if (p.gate_flags != nullptr) {
         // all-gather gating: the rows of this m-tile come from one or more peers' pushes
         const int g0 = m0 / p.gate_rows;
@@ -160,15 +173,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
-      int issued = 0;
+      int issued = pre;  // their B halves are in flight either way
       for (int it = 0; it < num_kb && ok; ++it) {
         const int s = it % STAGES;
-        const uint32_t parity = ((it / STAGES) & 1) ^ 1;
-        if (!sm100::mbar_wait(&empty_bar[s], parity, abort_flag)) { ok = false; break; }
         uint8_t* a_dst = smem + s * S::STAGE_BYTES;
         uint8_t* b_dst = a_dst + S::A_BYTES;
-        sm100::mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
         const int k = (kb_begin + it) * GEMM_BK;
+        if (it < pre) {
+          sm100::tma_load_2d(a_dst, &tmap_a, &full_bar[s], k, m0);
+          continue;
+        }
+        const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+        if (!sm100::mbar_wait(&empty_bar[s], parity, abort_flag)) { ok = false; break; }
+        sm100::mbar_expect_tx(&full_bar[s], S::STAGE_BYTES);
         sm100::tma_load_2d(b_dst, &tmap_b, &full_bar[s], k, n0);
         sm100::tma_load_2d(a_dst, &tmap_a, &full_bar[s], k, m0);
         issued = it + 1;
@@ -187,6 +204,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (lane == 0) {
       constexpr uint32_t idesc = sm100::make_idesc_f16(GEMM_BM, BN, 1u);
       bool ok = true;
@@ -209,6 +227,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int quarter = warp & 3;
     const bool ok = sm100::mbar_wait(tmem_full_bar, 0, abort_flag);
     sm100::tc_fence_after();
@@ -354,6 +373,15 @@ static int make_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t c
   return r == CUDA_SUCCESS ? 0 : DASER_ERR_BAD_ARG;
 }
 
+static bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DASER_PDL");
+    v = (e == nullptr || e[0] != '0') ? 1 : 0;
+  }
+  return v == 1;
+}
+
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
@@ -365,8 +393,20 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     configured = true;
   }
   const dim3 grid((p.N + BN - 1) / BN, (p.M + GEMM_BM - 1) / GEMM_BM, p.k_splits);
-  gemm_tcgen05_kernel<BN, STAGES><<<grid, GEMM_THREADS, S::DYNAMIC, stream>>>(ta, tb, p);
-  return (int)cudaGetLastError();
+  // Programmatic dependent launch: CTAs of this grid may be scheduled while the previous
+  // kernel's last CTAs drain; every role executes griddepcontrol.wait before it touches
+  // anything the previous kernel wrote, and the weight prefetch runs ahead of that wait.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = S::DYNAMIC;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, STAGES>, ta, tb, p);
 }
 
 }  // namespace daser
