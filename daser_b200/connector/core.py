@@ -407,6 +407,13 @@ class WorkerHalf:
         self.host = host_store
         self._ipc = client or IPCClientSync(socket_path)
         self._commit = commit
+        # geometry handshake: a store written with another slot size or codec must not be read
+        try:
+            self._ipc.hello({"slot_size": geo.slot_size, "block_tokens": geo.block_tokens})
+        except RuntimeError as exc:
+            if "geometry mismatch" in str(exc):
+                raise ValueError(f"connector and control plane disagree: {exc}") from exc
+            logger.warning("[CONNECTOR] geometry handshake skipped: %s", exc)
         if not os.path.exists(store_path):
             # the reference zero-fills max(slot_size * 1024, 64 MiB) through user space
             preallocate(store_path, max(geo.slot_size * create_store_slots, 64 << 20))

@@ -124,3 +124,19 @@ def test_periodic_snapshot(tmp_path):
         c.close()
     finally:
         lp.stop()
+
+
+def test_worker_refuses_a_control_plane_with_another_geometry(tmp_path):
+    import torch
+
+    from daser_b200.connector.core import TorchKVBackend, WorkerHalf
+    from daser_b200.kv.layout import KVGeometry
+
+    geo = KVGeometry(2, 2, 32, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, slot_size=geo.slot_size * 2).start()  # server configured for other slots
+    try:
+        pool = torch.zeros(2, 8, 2, 2, 16, 32)
+        with pytest.raises(ValueError, match="disagree"):
+            WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool, [1.0] * 16))
+    finally:
+        lp.stop()
