@@ -538,24 +538,28 @@ class WorkerHalf:
         ptrs: list[int] = []
         blocks: list[int] = []
         deltas: list[int] = []
+        cuda = self.kv.device_kind == "cuda"
         for spec, src, n, io_dst, kind in jobs:
             if spec.chunk_key in failed:
                 continue
+            if kind != "hbm":
+                metrics.inc("connector.bytes_over_pcie", n * g.slot_size)
+                if cuda and self.hbm is not None and spec.skip_slots == 0:
+                    # Promote first, restore from the promoted copy: the images cross PCIe once,
+                    # by DMA at full rate, instead of being read by the kernel and copied again.
+                    off = self.hbm.reserve(spec.chunk_key, n * g.slot_size)
+                    if off is not None:
+                        arena = self.host.arena if kind in ("host", "host_fill") else self._staging
+                        a0 = src - arena.data_ptr()
+                        self.hbm.arena[off : off + n * g.slot_size].copy_(arena[a0 : a0 + n * g.slot_size],
+                                                                         non_blocking=True)
+                        src = self.hbm.arena.data_ptr() + off
             for i in range(n):
                 ptrs.append(src + i * g.slot_size)
                 blocks.append(spec.block_ids[i])
                 deltas.append(spec.delta)
-            if kind != "hbm":
-                metrics.inc("connector.bytes_over_pcie", n * g.slot_size)
-        if self.kv.device_kind == "cuda":
+        if cuda:
             self.kv.restore_ptrs(ptrs, blocks, deltas)
-            if self.hbm is not None:
-                # promote what came from below; the copies are stream-ordered after the kernel
-                for spec, src, n, io_dst, kind in jobs:
-                    if kind == "hbm" or spec.chunk_key in failed or spec.skip_slots:
-                        continue
-                    arena = self.host.arena if kind in ("host", "host_fill") else self._staging
-                    self.hbm.admit(spec.chunk_key, arena, src - arena.data_ptr(), n * g.slot_size)
             torch.cuda.current_stream().synchronize()  # sources may be reused by the next step
             self.kv.check_status()
         else:
