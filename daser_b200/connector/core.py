@@ -42,6 +42,7 @@ from daser_b200.io.engine import preallocate
 from daser_b200.kv import codec
 from daser_b200.kv.layout import KVGeometry, tp_head_range
 from daser_b200.logging import init_logger, init_perf_logger
+from daser_b200.utils import trace
 
 logger = init_logger(__name__)
 _perf = init_perf_logger("connector")
@@ -124,7 +125,8 @@ class SchedulerHalf:
         store_key = hash_tokens(tokens[:aligned])
         t0 = time.perf_counter()
         try:
-            chunks, alloc = self._ipc.match_and_alloc(tokens, store_key, self.model_id)
+            with trace.span("rpc.match_and_alloc", "connector", req=req_id, tokens=len(tokens)):
+                chunks, alloc = self._ipc.match_and_alloc(tokens, store_key, self.model_id)
         except RuntimeError as exc:
             logger.warning("[CONNECTOR] lookup failed for %s (%s): treating as a miss", req_id, exc)
             metrics.inc("connector.rpc_errors")
@@ -167,7 +169,8 @@ class SchedulerHalf:
             if off % bt:
                 raise ValueError("chunk placements must be block aligned")
         try:
-            found = self._ipc.lookup_chunks([k for k, _ in placements], self.model_id)
+            with trace.span("rpc.lookup_chunks", "connector", req=req_id, chunks=len(placements)):
+                found = self._ipc.lookup_chunks([k for k, _ in placements], self.model_id)
         except RuntimeError as exc:
             logger.warning("[CONNECTOR] lookup_chunks failed for %s (%s)", req_id, exc)
             metrics.inc("connector.rpc_errors")
@@ -461,6 +464,10 @@ class WorkerHalf:
         meta = self._meta
         if meta is None or not meta.reqs_to_load:
             return
+        with trace.span("start_load_kv", "connector", chunks=len(meta.reqs_to_load)):
+            self._start_load_kv(meta)
+
+    def _start_load_kv(self, meta: ConnectorMeta) -> None:
         g = self.geo
         # job = (spec, source address, n slots, IO destination address or 0, "hbm" | "host" | "host_fill" | "staging")
         jobs: list[tuple[ReqLoadSpec, int, int, int, str]] = []
@@ -518,6 +525,7 @@ class WorkerHalf:
                 tickets.append((spec, kind, None))
             nbytes_total += nbytes
         failed: set[str] = set()
+        trace.instant("io.reads_submitted", n=len(tickets), bytes=nbytes_total)
         for spec, kind, ticket in tickets:
             try:
                 if ticket is None:
@@ -596,6 +604,10 @@ class WorkerHalf:
         meta = self._meta
         if meta is None or not meta.reqs_to_store:
             return
+        with trace.span("wait_for_save", "connector", chunks=len(meta.reqs_to_store)):
+            self._wait_for_save(meta, barrier)
+
+    def _wait_for_save(self, meta: ConnectorMeta, barrier: Optional[Callable[[], None]]) -> None:
         g = self.geo
         pending = list(meta.reqs_to_store)
         while pending:

@@ -30,7 +30,8 @@ from daser_b200.engine.runner import GpuModelRunner, make_step_inputs
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.hbm_store import HBMStore
 from daser_b200.models.llama import LlamaConfig, LlamaWeights
-from daser_b200.ops import kv_ops
+from daser_b200.ops import kv_ops  # noqa: F401
+from daser_b200.utils import trace
 
 
 @dataclass
@@ -184,9 +185,11 @@ class GpuRagEngine:
 
     def step(self) -> None:
         if self.waiting:
-            self._ttft_step(self.waiting.pop(0))
+            with trace.span("engine.ttft_step", "engine"):
+                self._ttft_step(self.waiting.pop(0))
         elif self.running:
-            self._decode_step()
+            with trace.span("engine.decode_step", "engine", batch=len(self.running)):
+                self._decode_step()
 
     def _ttft_step(self, req: RagRequest) -> None:
         cfg, bt = self.cfg, self.cfg.block_tokens

@@ -172,6 +172,7 @@ struct daser_io {
   std::deque<Piece*> backlog;
   unsigned inflight = 0;
   unsigned depth = 64;
+  std::condition_variable_any ring_idle_cv;  // signalled when inflight and backlog both reach zero
   std::thread reaper;
 
   // cuFile
@@ -340,6 +341,7 @@ struct daser_io {
         backlog.pop_front();
         ring_submit_locked(q);
       }
+      if (inflight == 0 && backlog.empty()) ring_idle_cv.notify_all();
     }
   }
 };
@@ -477,7 +479,10 @@ int daser_io_close(daser_io* io) {
   for (auto& t : io->workers) t.join();
   if (io->reaper.joinable()) {
     {
-      std::lock_guard<std::mutex> g(io->ring_mu);
+      // Every submitted piece completes before the sentinel goes in: the caller's buffers are
+      // not written after this function returns, and no piece is left behind un-freed.
+      std::unique_lock<std::mutex> g(io->ring_mu);
+      io->ring_idle_cv.wait_for(g, std::chrono::seconds(30), [&] { return io->inflight == 0 && io->backlog.empty(); });
       io->ring.push(IORING_OP_NOP, -1, nullptr, 0, 0, 0);
     }
     io->reaper.join();

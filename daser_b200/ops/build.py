@@ -77,7 +77,7 @@ def build_ops(verbose: bool = False, force: bool = False) -> Path:
 
 
 def build_io(force: bool = False) -> Path:
-    sources = sorted(IO_SRC.glob("*.cc"))
+    sources = sorted(p for p in IO_SRC.glob("*.cc") if not p.name.endswith("_selftest.cc"))
     headers = sorted(IO_SRC.glob("*.h"))
     if not sources:
         return IO_LIB
@@ -92,6 +92,17 @@ def build_io(force: bool = False) -> Path:
         cmd += ["-o", str(IO_LIB), *map(str, sources), "-ldl"]
         _run(cmd)
     return IO_LIB
+
+
+def build_io_selftest(sanitize: str = "address,undefined") -> Path:
+    """The storage engine's stand-alone exerciser, instrumented with ``-fsanitize=<sanitize>``."""
+    BUILD_DIR.mkdir(exist_ok=True)
+    out = BUILD_DIR / f"io_selftest_{sanitize.replace(',', '_')}"
+    srcs = [IO_SRC / "io_engine.cc", IO_SRC / "io_engine_selftest.cc"]
+    if _stale(out, srcs + sorted(IO_SRC.glob("*.h"))):
+        _run(["g++", "-O1", "-g", "-std=c++17", f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-pthread",
+              "-I", str(IO_SRC), "-o", str(out), *map(str, srcs), "-ldl"])
+    return out
 
 
 def build_all(verbose: bool = False, force: bool = False) -> None:
