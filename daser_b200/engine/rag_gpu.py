@@ -184,6 +184,8 @@ class GpuRagEngine:
         return bool(self.waiting or self.running)
 
     def step(self) -> None:
+        if self.tp_ctx is not None:
+            self.tp_ctx.check_peers()  # host-side: a lost peer ends the step before any launch
         if self.waiting:
             with trace.span("engine.ttft_step", "engine"):
                 self._ttft_step(self.waiting.pop(0))
@@ -300,3 +302,5 @@ class GpuRagEngine:
             self.worker.shutdown()
         if self.sched is not None:
             self.sched.close()
+        if self.tp_ctx is not None:
+            self.tp_ctx.close()

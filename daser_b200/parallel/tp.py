@@ -19,7 +19,11 @@ GPU and the hot path makes no NCCL call:
   the IO rank's staging buffer.
 
 NCCL is used for bootstrap, barriers between engine steps and the 8-byte-per-sequence
-exchange of greedy-sampling candidates.  Buffers that peers touch are allocated with
+exchange of greedy-sampling candidates.  No kernel here uses ``multimem``, so the symmetric
+allocations are made without an NVLink multicast object bound to them
+(``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` unless the caller set it): a process that dies while its
+memory is bound to one raises NVLink faults on its peers' GPUs.  Peer liveness is checked on the
+host between steps (:mod:`daser_b200.parallel.health`).  Buffers that peers touch are allocated with
 ``torch.distributed._symmetric_memory`` (VMM allocations exchanged between the processes).
 All device-side waits are bounded and report through a status word.
 """
@@ -27,6 +31,7 @@ All device-side waits are bounded and report through a status word.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Any, Optional
 
 import torch
@@ -34,6 +39,7 @@ import torch.distributed as dist
 
 from daser_b200.models.llama import LlamaConfig
 from daser_b200.ops import attention, elementwise as ew, gemm, kv_ops
+from daser_b200.parallel.health import PeerMonitor
 
 FLAG_RS = 0  # arrival counter of reduce-scattered partials
 FLAG_AG = 8  # first of tp per-source "rows landed" flags
@@ -42,6 +48,7 @@ NUM_FLAGS = 16
 
 class TPContext:
     def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256) -> None:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         self._symm = symm_mem
@@ -76,6 +83,11 @@ class TPContext:
         self.epochs = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._rs_off = self._ag_off = self._done_off = 0
         self.save_staging: Optional[torch.Tensor] = None
+        self.health: Optional[PeerMonitor] = None
+        if os.environ.get("DASER_TP_HEALTH", "1") != "0":
+            store = dist.distributed_c10d._get_default_store()
+            self.health = PeerMonitor(dist.PrefixStore(f"daser/{self.group_name}", store), self.rank, self.tp,
+                                      timeout_s=float(os.environ.get("DASER_TP_HEALTH_TIMEOUT", "10")))
         torch.cuda.synchronize()
         self.barrier()
 
@@ -90,6 +102,27 @@ class TPContext:
 
     def barrier(self) -> None:
         dist.barrier(group=self.group, device_ids=[self.device.index])
+
+    def check_peers(self) -> None:
+        """Raise :class:`~daser_b200.parallel.health.PeerLost` if a peer left or stopped beating.
+
+        Called between engine steps, before anything that waits on a peer is launched."""
+        if self.health is not None:
+            self.health.check()
+
+    def multicast_bound(self) -> bool:
+        """True if any symmetric allocation of this context has an NVLink multicast mapping."""
+        return any(int(getattr(h, "multicast_ptr", 0) or 0) != 0 for h in self._handles.values())
+
+    def leave(self) -> None:
+        """Orderly exit of this rank: between steps, after its own work has drained."""
+        torch.cuda.synchronize()
+        if self.health is not None:
+            self.health.leave()
+
+    def close(self) -> None:
+        if self.health is not None:
+            self.health.close()
 
     def broadcast_object(self, obj: Any, src: int = 0) -> Any:
         box = [obj]

@@ -1,0 +1,193 @@
+"""CPU ranks for the multi-process tests (``gloo`` backend, no GPU).
+
+Scenarios, chosen by ``argv[1]``; RANK / WORLD_SIZE / MASTER_PORT come from the environment:
+
+``parts``   two tensor-parallel workers in the per-rank-file arrangement used under vLLM: rank 0
+            also runs the control plane and the scheduler half and broadcasts each step's plan;
+            every rank stores its head slice into its own file and commits its part.  A chunk
+            must be visible only after both parts are in, restore must give every rank its
+            heads back, and a chunk whose second part never arrives must stay invisible.
+``health``  three ranks with a :class:`PeerMonitor`: rank 2 leaves in an orderly way after
+            step 1, rank 1 exits without a word after step 2; rank 0 must learn of both on the
+            host, before its next step.
+``late``    rank 0 alone of a two-rank world: the rendezvous must end with an error inside
+            its time limit instead of waiting for ever.
+"""
+
+import asyncio
+import datetime
+import os
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from daser_b200.config import DaserConfig  # noqa: E402
+from daser_b200.connector.core import ConnectorMeta, SchedulerHalf, TorchKVBackend, WorkerHalf  # noqa: E402
+from daser_b200.connector.ipc_client import IPCClientSync  # noqa: E402
+from daser_b200.kv.layout import KVGeometry, tp_head_range  # noqa: E402
+from daser_b200.parallel.health import PeerLost, PeerMonitor  # noqa: E402
+
+
+def _init(timeout_s: float = 60.0) -> tuple[int, int]:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['MASTER_PORT']}", rank=rank,
+                            world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+    return rank, world
+
+
+def _bcast(obj, src=0):
+    box = [obj]
+    dist.broadcast_object_list(box, src=src)
+    return box[0]
+
+
+def scenario_parts() -> int:
+    rank, world = _init()
+    L, H, D, B = 2, 4, 32, 16
+    h0, hn = tp_head_range(H, world, rank)
+    geo = KVGeometry(num_layers=L, num_kv_heads=hn, head_dim=D, block_tokens=B, dtype_bytes=2, codec="raw")
+    tmp = _bcast(tempfile.mkdtemp(prefix="daser_gloo_") if rank == 0 else None)
+    sock = f"{tmp}/d.sock"
+    loop = plane = None
+    if rank == 0:
+        from daser_b200.server.__main__ import ControlPlane
+
+        cfg = DaserConfig(store_path=f"{tmp}/unused.store", index_path="", total_slots=64, slot_size=geo.slot_size,
+                          ipc_socket_path=sock)
+        plane = ControlPlane(cfg)
+        loop = asyncio.new_event_loop()
+        ready = threading.Event()
+
+        def serve():
+            asyncio.set_event_loop(loop)
+            loop.run_until_complete(plane.start())
+            ready.set()
+            loop.run_forever()
+
+        threading.Thread(target=serve, daemon=True).start()
+        ready.wait(20)
+    dist.barrier()
+
+    torch.manual_seed(7)  # same "model output" on every rank; each keeps its heads
+    full = torch.randn(L, 8, 2, H, B, D).to(torch.bfloat16)
+    pool = full[:, :, :, h0 : h0 + hn].clone()
+    backend = TorchKVBackend(geo, pool, [1.0] * (D // 2))
+    worker = WorkerHalf(sock, f"{tmp}/rank{rank}.store", geo, backend, io_backend="posix", staging_slots=8,
+                        create_store_slots=64)
+    worker.commit_parts = (rank, world)
+    sched = SchedulerHalf(sock, B, "m") if rank == 0 else None
+    probe = IPCClientSync(sock)
+    ok = True
+
+    # step 1: store a 3-block chunk from blocks 5,1,6
+    tokens = list(range(100, 100 + 3 * B))
+    if rank == 0:
+        sched.reserve_chunk_store("r1", tokens, [5, 1, 6])
+        meta = sched.build_connector_meta(["r1"])
+    else:
+        meta = None
+    meta = _bcast(meta)
+    assert isinstance(meta, ConnectorMeta) and len(meta.reqs_to_store) == 1
+    key = meta.reqs_to_store[0].chunk_key
+    worker.bind_connector_metadata(meta)
+    if rank == 1:
+        # rank 0 commits its part first; the chunk must still be invisible
+        dist.barrier()
+        ok = ok and probe.lookup_chunks([key], "m") == [None]
+        worker.wait_for_save()
+        dist.barrier()
+    else:
+        worker.wait_for_save()
+        dist.barrier()
+        dist.barrier()
+    worker.clear_connector_metadata()
+    ok = ok and probe.lookup_chunks([key], "m")[0] is not None
+
+    # step 2: restore it into other blocks on every rank; each gets its own heads back
+    if rank == 0:
+        sched.plan_chunk_loads("r2", [(key, 0)])
+        sched.assign_chunk_blocks("r2", [2, 3, 4])
+        meta = sched.build_connector_meta(["r2"])
+    meta = _bcast(meta if rank == 0 else None)
+    pool[:, [2, 3, 4]] = 0
+    worker.bind_connector_metadata(meta)
+    worker.start_load_kv()
+    worker.clear_connector_metadata()
+    ok = ok and torch.equal(pool[:, [2, 3, 4]], full[:, [5, 1, 6]][:, :, :, h0 : h0 + hn])
+    ok = ok and not worker.take_load_errors()
+
+    # step 3: a chunk whose second part never arrives (rank 1 "crashed" between write and commit)
+    tokens2 = list(range(500, 500 + B))
+    if rank == 0:
+        sched.reserve_chunk_store("r3", tokens2, [7])
+        meta = sched.build_connector_meta(["r3"])
+    meta = _bcast(meta if rank == 0 else None)
+    key2 = meta.reqs_to_store[0].chunk_key
+    if rank == 0:
+        worker.bind_connector_metadata(meta)
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+    dist.barrier()
+    ok = ok and probe.lookup_chunks([key2], "m") == [None]
+
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(ok))
+    worker.shutdown()
+    probe.close()
+    dist.barrier()
+    if rank == 0:
+        asyncio.run_coroutine_threadsafe(plane.stop(save=False), loop).result(10)
+        loop.call_soon_threadsafe(loop.stop)
+        print("PARTS_OK" if all(flags) else f"PARTS_FAIL {flags}", flush=True)
+    dist.destroy_process_group()
+    return 0 if all(flags) else 1
+
+
+def scenario_health() -> int:
+    rank, world = _init()
+    store = dist.distributed_c10d._get_default_store()
+    mon = PeerMonitor(store, rank, world, timeout_s=1.5, interval_s=0.2)
+    seen = []
+    for step in range(6):
+        try:
+            mon.check()
+        except PeerLost as exc:
+            seen.append((step, exc.ranks))
+            if exc.ranks == [1, 2]:
+                break
+        if rank == 2 and step == 1:
+            mon.leave()  # between steps, nothing in flight
+            os._exit(0)
+        if rank == 1 and step == 2:
+            os._exit(0)  # no notice at all
+        time.sleep(0.2 if step < 3 else 1.0)  # a "step"
+    mon.close()
+    if rank == 0:
+        first_left = next((s for s, r in seen if 2 in r), None)
+        both = next((s for s, r in seen if r == [1, 2]), None)
+        print(f"seen={seen}", flush=True)
+        good = first_left == 2 and both is not None
+        print("HEALTH_OK" if good else "HEALTH_FAIL", flush=True)
+        os._exit(0 if good else 1)  # peers are gone: skip the collective teardown
+    return 0
+
+
+def scenario_late() -> int:
+    t0 = time.time()
+    try:
+        _init(timeout_s=3.0)
+    except Exception as exc:  # DistStoreError / DistNetworkError / RuntimeError by version
+        print(f"RENDEZVOUS_FAILED after {time.time() - t0:.1f}s: {type(exc).__name__}", flush=True)
+        return 7
+    print("RENDEZVOUS_UNEXPECTEDLY_OK", flush=True)
+    return 1
+
+
+if __name__ == "__main__":
+    sys.exit({"parts": scenario_parts, "health": scenario_health, "late": scenario_late}[sys.argv[1]]())

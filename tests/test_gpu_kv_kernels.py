@@ -172,3 +172,41 @@ def test_save_then_restore_roundtrip(img_codec, pool_fp8, tp):
     if img_codec == "raw" and not pool_fp8 and tp == 1:
         k0 = truth[0, blocks[0], 0].permute(1, 0, 2).contiguous()
         assert torch.equal(img[: k0.numel() * 2], k0.view(torch.uint8).reshape(-1))
+
+
+@pytest.mark.parametrize("pool_fp8", [False, True])
+def test_restore_and_save_stay_inside_their_buffers(pool_fp8):
+    """Guard bytes on both sides of the pool, the scale table and the staging area survive a
+    restore into the first and last block and a save of the same blocks."""
+    kv_ops = _ops()
+    torch.manual_seed(3)
+    geo = KVGeometry(2, 2, 64, 16, 2, "fp8b16")
+    n_blocks, guard = 5, 4096
+    elems = geo.num_layers * n_blocks * 2 * 2 * 16 * 64
+    pool_bytes = elems * (1 if pool_fp8 else 2)
+    raw_pool = torch.full((guard + pool_bytes + guard,), 0xA5, dtype=torch.uint8, device="cuda")
+    raw_scales = torch.full((guard + elems // 16 * 4 + guard,), 0xA5, dtype=torch.uint8, device="cuda")
+    shape = [geo.num_layers, n_blocks, 2, 2, 16, 64]
+    body = raw_pool[guard : guard + pool_bytes]
+    payload = (body if pool_fp8 else body.view(torch.bfloat16)).view(shape)
+    scales = raw_scales[guard:-guard].view(torch.float32).view(shape[:-1] + [4]) if pool_fp8 else None
+    pool = kv_ops.PagedKVPool.from_tensors([payload], [scales] if pool_fp8 else None, "LNKHTD")
+    n = 2
+    raw_staging = torch.full((guard + n * geo.slot_size + guard,), 0xA5, dtype=torch.uint8, device="cuda")
+    ks = [(torch.randn(16, 2, 64) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    vs = [(torch.randn(16, 2, 64) * 0.5).to(torch.bfloat16) for _ in range(2)]
+    image = codec.pack_slot(geo, ks, vs).cuda()
+    for i in range(n):
+        raw_staging[guard + i * geo.slot_size : guard + (i + 1) * geo.slot_size] = image
+    ptrs = torch.tensor([raw_staging.data_ptr() + guard + i * geo.slot_size for i in range(n)], dtype=torch.int64,
+                        device="cuda")
+    work = kv_ops.KVWorkList(ptrs, torch.tensor([0, n_blocks - 1], dtype=torch.int32, device="cuda"),
+                             torch.tensor([3, -7], dtype=torch.int32, device="cuda"))
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    kv_ops.kv_restore(work, geo, pool, kv_ops.rope_table(64, inv_freq_table(64, 10000.0), "cuda"), status)
+    kv_ops.kv_save(kv_ops.KVWorkList(ptrs, work.block_ids), geo, pool, 0, status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0]
+    for buf in (raw_pool, raw_scales, raw_staging):
+        assert bool((buf[:guard] == 0xA5).all()) and bool((buf[-guard:] == 0xA5).all())
+    assert bool((payload.view(torch.uint8) != 0xA5).any())  # the kernels did write

@@ -17,3 +17,18 @@ def test_tp2_forward_and_engine_match_single_gpu():
     tail = (proc.stdout + proc.stderr)[-3000:]
     assert proc.returncode == 0, tail
     assert "TP_OK" in proc.stdout, tail
+
+
+def test_tp2_rank_leaves_between_steps_and_the_other_learns_on_the_host():
+    """No GPU is faulted: the leaving rank has nothing in flight, NVLS and multicast are off,
+    and the surviving rank finds out from the store before it launches its next step."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", DASER_TP_HEALTH_TIMEOUT="3")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29519", os.path.join(here, "tp_leave_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=200, env=env)
+    tail = (proc.stdout + proc.stderr)[-3000:]
+    assert proc.returncode == 0, tail
+    if "TP_LEAVE_SKIPPED" in proc.stdout:
+        pytest.skip("symmetric buffers carry a multicast mapping on this box")
+    assert "TP_LEAVE_OK" in proc.stdout, tail

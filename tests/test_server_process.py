@@ -1,0 +1,116 @@
+"""The control plane as a real process: start from the command line, talk to it over the
+Unix socket, stop it with SIGTERM, start it again and find the state it saved.
+
+Reference behaviour covered: daser/server/__main__.py (signal-driven shutdown that writes the
+index, restore at start-up, refusal to load an index written for another geometry is not trusted).
+"""
+
+import os
+import signal
+import subprocess
+import sys
+import time
+
+import pytest
+
+from daser_b200.connector.ipc_client import IPCClientSync
+from daser_b200.hashing import hash_tokens
+
+SLOT = 16 * 1024
+
+
+def _spawn(tmp_path, *extra):
+    sock = str(tmp_path / "d.sock")
+    cmd = [sys.executable, "-m", "daser_b200.server", "--store-path", str(tmp_path / "d.store"),
+           "--store-size", str(64 * SLOT), "--socket-path", sock, "--index-path", str(tmp_path / "d.index"),
+           "--slot-size", str(SLOT), "--block-tokens", "16", "--model-id", "m", *extra]
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            env=dict(os.environ, PYTHONUNBUFFERED="1"))
+    deadline = time.time() + 60
+    while time.time() < deadline:
+        if os.path.exists(sock):
+            try:
+                client = IPCClientSync(sock)
+                client.stats()
+                return proc, client
+            except (OSError, RuntimeError):
+                pass
+        if proc.poll() is not None:
+            raise AssertionError("server exited early:\n" + proc.stdout.read())
+        time.sleep(0.1)
+    proc.kill()
+    raise AssertionError("server did not come up")
+
+
+def _stop(proc, sig=signal.SIGTERM):
+    proc.send_signal(sig)
+    try:
+        out, _ = proc.communicate(timeout=30)
+    except subprocess.TimeoutExpired:
+        proc.kill()
+        raise
+    return out
+
+
+def test_sigterm_saves_and_restart_restores(tmp_path):
+    proc, client = _spawn(tmp_path)
+    tokens = list(range(48))
+    key = hash_tokens(tokens)
+    got = client.alloc_chunk(key, len(tokens), "m")
+    assert got["num_slots"] == 3
+    client.commit_chunk(key)
+    client.call({"op": "register_doc", "doc_id": "d1", "title": "t", "token_count": 48, "chunk_keys": [key]})
+    client.close()
+    out = _stop(proc)
+    assert proc.returncode == 0, out
+    assert (tmp_path / "d.index").exists()
+
+    proc2, client2 = _spawn(tmp_path)
+    try:
+        hit = client2.lookup(tokens, "m")
+        assert len(hit) == 1 and hit[0]["chunk_key"] == key and hit[0]["start_slot"] == got["start_slot"]
+        docs = client2.call({"op": "list_docs"})["docs"]
+        assert [d["doc_id"] for d in docs] == ["d1"] and docs[0]["status"] == "ready"
+        fresh = client2.alloc_chunk(hash_tokens(list(range(100, 116))), 16, "m")
+        assert fresh["start_slot"] == got["start_slot"] + 3  # the ring head came back too
+    finally:
+        client2.close()
+        out2 = _stop(proc2, signal.SIGINT)
+    assert proc2.returncode == 0, out2
+
+
+def test_restart_with_other_geometry_starts_cold(tmp_path):
+    """An index written for another slot count is not trusted: warning, empty ring, no stale hits."""
+    proc, client = _spawn(tmp_path)
+    toks = list(range(16))
+    client.alloc_chunk(hash_tokens(toks), 16, "m")
+    client.commit_chunk(hash_tokens(toks))
+    client.close()
+    _stop(proc)
+    proc2, client2 = _spawn(tmp_path, "--slot-size", str(2 * SLOT))  # later flag wins: 32 slots instead of 64
+    try:
+        assert client2.lookup(toks, "m") == []
+        assert client2.stats()["ring"]["used_slots"] == 0
+    finally:
+        client2.close()
+        out = _stop(proc2)
+    assert "cold start" in out
+
+
+def test_periodic_snapshot_survives_sigkill(tmp_path):
+    proc, client = _spawn(tmp_path, "--snapshot-interval", "0.2")
+    client.alloc_chunk(hash_tokens(list(range(32))), 32, "m")
+    client.commit_chunk(hash_tokens(list(range(32))))
+    client.close()
+    deadline = time.time() + 20
+    while not (tmp_path / "d.index").exists() and time.time() < deadline:
+        time.sleep(0.1)
+    time.sleep(0.5)
+    proc.kill()  # no chance to save on the way out
+    proc.wait(timeout=30)
+    proc2, client2 = _spawn(tmp_path)
+    try:
+        assert len(client2.lookup(list(range(32)), "m")) == 1
+    finally:
+        client2.close()
+        _stop(proc2)
