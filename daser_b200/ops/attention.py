@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -14,9 +15,39 @@ NUM_SMS = 148
 MAX_ROW_SPLITS = 262144  # (query rows x KV splits) the split-KV scratch is sized for (135 MB)
 
 
+TC_MIN_ROWS = 64  # query rows per KV head from which chunked prefill runs on the tcgen05 kernel
+TC_KEY_TILE = 64
+_tc_enabled = os.environ.get("DASER_ATTN_TC", "1") != "0"
+
+
+def set_tensor_core_prefill(enabled: bool) -> None:
+    """Route chunked prefill to the tcgen05 kernel (default) or to the mma.sync one."""
+    global _tc_enabled
+    _tc_enabled = bool(enabled)
+    _lib.lib().daser_attention_set_tc(1 if enabled else 0)
+
+
+def tc_status() -> int:
+    """Non-zero if a tcgen05 attention CTA ever gave up on a bounded wait (synchronises)."""
+    out = C.c_uint32(0)
+    _lib.check(_lib.lib().daser_attention_tc_status(C.byref(out)), "attention_tc_status")
+    return int(out.value)
+
+
 def plan_splits(num_seqs: int, kv_heads: int, max_q_len: int, group: int, max_ctx: int,
                 block_tokens: int = 16, rows: int = 0) -> tuple[int, int]:
-    """(nsplit, split_tokens): enough warp-sized work items to fill the GPU."""
+    """(nsplit, split_tokens): enough work items to fill the GPU."""
+    if _tc_enabled and max_q_len * group >= TC_MIN_ROWS and 128 % group == 0:
+        # tcgen05 kernel: the unit is a CTA of 128 query rows, two per SM, 64 keys per tile
+        base_items = num_seqs * kv_heads * -(-max_q_len * group // 128)
+        want = max(1, (NUM_SMS * 2) // max(base_items, 1))
+        max_splits = max(1, max_ctx // (2 * TC_KEY_TILE))
+        nsplit = max(1, min(want, max_splits, 64))
+        if rows > 0:
+            nsplit = max(1, min(nsplit, MAX_ROW_SPLITS // rows))
+        per = -(-max_ctx // nsplit)
+        split_tokens = -(-per // TC_KEY_TILE) * TC_KEY_TILE
+        return -(-max_ctx // split_tokens), split_tokens
     row_tiles = -(-max_q_len * group // 16)
     base_items = num_seqs * kv_heads * row_tiles
     # Measured on the batch-64, 4k-32k decode case: 1024-token splits reach 0.80 of the copy

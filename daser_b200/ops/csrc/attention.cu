@@ -21,56 +21,12 @@
 //   O = P V   : lane (g, t) supplies dims [16g, 16g+16) (one scale group) of tokens
 //               2t, 2t+1, 2t+8, 2t+9; MMA n-tile j uses dim 16g + j.  The lane therefore
 //               accumulates output dims [32t, 32t+32) of rows g and g+8.
-#include "common.cuh"
-#include "kv_paged.h"
+#include <stdlib.h>
+
+#include "attention_params.cuh"
 
 namespace daser {
 
-constexpr int ATT_D = 128;          // head dim
-constexpr int ATT_B = 16;           // tokens per page
-constexpr int ATT_STAGES = 4;       // cp.async ring depth per warp
-constexpr int ATT_WARPS = 4;
-constexpr int ATT_STAGE_BYTES = 2 * ATT_B * ATT_D + 2 * ATT_B * (ATT_D / 16) * 4;  // K, V payload + K, V scales = 5120
-
-struct AttnParams {
-  const __nv_bfloat16* q;    // [Tq, Hq, D]
-  __nv_bfloat16* out;        // [Tq, Hq, D]
-  float* part_o;             // [Tq, Hq, nsplit, D]  (nsplit > 1)
-  float* part_lse;           // [Tq, Hq, nsplit]
-  const uint8_t* kv_payload; // layer base of the fp8 pool
-  const float* kv_scales;
-  int64_t stride_block, stride_kv, stride_head, stride_tok;  // payload strides (elements = bytes)
-  const int32_t* block_tables;  // [num_seqs, max_blocks]
-  int max_blocks;
-  const int32_t* q_start;    // [num_seqs + 1] prefix sums of query lengths
-  const int32_t* ctx_lens;   // [num_seqs] total length including the new tokens
-  int num_seqs, Hq, Hkv, G;
-  int nsplit, split_tokens, row_tiles_max;
-  float scale_log2;          // softmax scale * log2(e)
-  int num_blocks;
-};
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint16_t v) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
-  return r;
-}
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
-  __half2 h = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -578,6 +534,17 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
 
 }  // namespace daser
 
+// Chunked prefill goes to the tcgen05 kernel unless DASER_ATTN_TC=0 (or the setter) says otherwise.
+static int g_attn_tc_mode = -1;
+static bool attention_tc_enabled() {
+  if (g_attn_tc_mode < 0) {
+    const char* v = getenv("DASER_ATTN_TC");
+    g_attn_tc_mode = (v && v[0] == '0') ? 0 : 1;
+  }
+  return g_attn_tc_mode != 0;
+}
+DASER_API void daser_attention_set_tc(int enabled) { g_attn_tc_mode = enabled ? 1 : 0; }
+
 // Paged attention over an fp8b16 pool.  `pool` gives the layout; only this rank's base
 // pointers (index `rank`) are used.  part_o / part_lse are scratch of
 // Tq*Hq*nsplit*(128+1) floats, needed when nsplit > 1.
@@ -624,7 +591,11 @@ DASER_API int daser_paged_attention_fp8(const void* q, void* out, float* part_o,
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  if (p.row_tiles_max > 1) {
+  if (attention_tc_enabled() && max_q_len * G >= 64 && 128 % G == 0) {
+    // at least half of a 128-row MMA tile per KV head: the tcgen05 kernel
+    const int rc = daser_launch_attention_tc(p, max_q_len, stream);
+    if (rc != 0) return rc;
+  } else if (p.row_tiles_max > 1) {
     // several row tiles per KV head: the CTA-shared dequantisation pays off
     const int groups = (p.row_tiles_max + 3) / 4;
     const dim3 pgrid(Hkv, num_seqs, groups * nsplit);

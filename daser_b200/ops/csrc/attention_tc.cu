@@ -1,0 +1,382 @@
+// Chunked-prefill paged attention on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// In the reference's serving stack the prefill of a RAG query over restored chunk KV is stock
+// vLLM's FlashAttention kernel over a bf16 cache (vllm/v1/attention/backends/flash_attn.py).
+// Here the cache is block-scaled fp8 and the query block is small (tens of tokens) while the
+// context is thousands of keys, so the kernel is organised around one 128-row MMA tile:
+//
+//   * one CTA = 128 query rows of one KV head (128 / G query tokens x the G heads that share
+//     the KV head) and one contiguous range of keys (split-KV; partials are merged by
+//     attn_merge_kernel);
+//   * keys are streamed in tiles of 64 (four 16-token pages): the raw fp8 pages and their
+//     scales arrive through a two-stage cp.async ring, all 128 threads dequantise them to f16
+//     straight into the 128-byte-swizzled K-major layout the MMA descriptors expect: K as
+//     [key][dim], V transposed to [dim][key] so that both MMAs take K-major operands;
+//   * S = Q K^T (M 128, N 64, K 128) is issued by one thread as eight tcgen05.mma into TMEM;
+//     every thread then owns one row of S (tcgen05.ld 32x32b: lane = row), so the online
+//     softmax needs no shuffles; P goes back to shared memory as f16 (over the K tile, which
+//     is dead by then) and O_tile = P V (M 128, N 128, K 64) is four more tcgen05.mma;
+//   * the running output lives in registers (one row of 128 floats per thread) and is
+//     updated from TMEM after each tile, so no TMEM store is needed for the rescale.
+//
+// Two CTAs fit one SM (about 105 KB of shared memory, 256 TMEM columns and 128 threads each),
+// which is what overlaps one CTA's softmax with the other's MMAs and copies.
+// Every mbarrier wait is bounded; on expiry the CTA records it in a status word, frees its
+// TMEM and returns.
+#include "attention_params.cuh"
+#include "tcgen05.cuh"
+
+namespace daser {
+using namespace sm100;
+
+constexpr int TC_NK = 64;                        // keys per tile
+constexpr int TC_PAGES = TC_NK / ATT_B;          // 4
+constexpr int TC_Q_BYTES = 128 * ATT_D * 2;      // 32768: two sub-tiles [128 rows][64 dims]
+constexpr int TC_KP_BYTES = 16384;               // K: two sub-tiles [64 keys][64 dims]; later P: [128 rows][64 keys]
+constexpr int TC_VT_BYTES = 16384;               // V^T: [128 dims][64 keys]
+constexpr int TC_RAW_PAYLOAD = TC_PAGES * 4096;  // per page: K 2048 B, V 2048 B
+constexpr int TC_RAW_KSCALE = TC_PAGES * 512;
+constexpr int TC_RAW_VSCALE = TC_NK * 8 * 4;
+constexpr int TC_RAW_BYTES = TC_RAW_PAYLOAD + TC_RAW_KSCALE + TC_RAW_VSCALE;  // 20480
+constexpr int TC_SMEM = 1024 + TC_Q_BYTES + TC_KP_BYTES + TC_VT_BYTES + 2 * TC_RAW_BYTES + 64;
+constexpr uint32_t TC_TMEM_COLS = 256;           // S in columns [0, 64), O tile in [128, 256)
+
+__device__ uint32_t g_attn_tc_status = 0;        // bit 0: a bounded wait ran out
+
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+__global__ void __launch_bounds__(128, 2)
+paged_attn_fp8_tc_kernel(const AttnParams p) {
+  extern __shared__ uint8_t tc_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* kp_s = q_s + TC_Q_BYTES;
+  uint8_t* vt_s = kp_s + TC_KP_BYTES;
+  uint8_t* raw_s = vt_s + TC_VT_BYTES;
+  uint64_t* bar_s = reinterpret_cast<uint64_t*>(raw_s + 2 * TC_RAW_BYTES);
+  uint64_t* bar_o = bar_s + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int kvh = blockIdx.x, seq = blockIdx.y;
+  const int grp = blockIdx.z / p.nsplit, sp = blockIdx.z % p.nsplit;
+  const int q0 = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - q0;
+  const int ctx = p.ctx_lens[seq];
+  const int G = p.G;
+  const int toks_per_cta = 128 / G;
+  const int grp_tok_first = grp * toks_per_cta;
+  if (grp_tok_first >= q_len) return;  // uniform over the CTA
+  const int grp_tok_last = min(grp_tok_first + toks_per_cta, q_len) - 1;
+  const int grp_limit = ctx - q_len + grp_tok_last + 1;  // keys visible to the last row
+  const int key_begin = sp * p.split_tokens;
+  const int key_end = min(key_begin + p.split_tokens, grp_limit);
+  const int n_tiles = key_begin < key_end ? (key_end - key_begin + TC_NK - 1) / TC_NK : 0;
+
+  // this thread's row
+  const int tq = grp_tok_first + tid / G;
+  const int hq = kvh * G + tid % G;
+  const bool valid = tq < q_len;
+  const int pos = ctx - q_len + tq;  // last key this row may see
+
+  float o[ATT_D];
+#pragma unroll
+  for (int i = 0; i < ATT_D; ++i) o[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+
+  if (n_tiles > 0) {
+    const uint32_t q_u32 = smem_u32(q_s), kp_u32 = smem_u32(kp_s), vt_u32 = smem_u32(vt_s), raw_u32 = smem_u32(raw_s);
+    if (tid == 0) {
+      mbar_init(bar_s, 1);
+      mbar_init(bar_o, 1);
+      *abort_flag = 0u;
+      mbar_init_fence();
+    }
+    if (warp == 0) {
+      tmem_alloc(tmem_slot, TC_TMEM_COLS);
+      tmem_relinquish();
+    }
+    const int32_t* table = p.block_tables + (int64_t)seq * p.max_blocks;
+    const int page_begin = key_begin / ATT_B;
+
+    auto issue = [&](int ti) {
+      const uint32_t st = raw_u32 + (ti & 1) * TC_RAW_BYTES;
+      const int key0 = key_begin + ti * TC_NK;
+      int64_t base[TC_PAGES];
+      bool live[TC_PAGES];
+#pragma unroll
+      for (int pg = 0; pg < TC_PAGES; ++pg) {
+        live[pg] = key0 + pg * ATT_B < key_end;
+        int blk = table[min(page_begin + ti * TC_PAGES + pg, p.max_blocks - 1)];
+        blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
+        base[pg] = (int64_t)blk * p.stride_block + (int64_t)kvh * p.stride_head;
+      }
+      // payload: 4 pages x (K, V) x 128 pieces of 16 B.  The 16-byte chunk c of a token row is
+      // stored at chunk (c ^ tok%8) for K and (c ^ key/8) for V, so that the dequantisation
+      // below reads shared memory without bank conflicts.
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int idx = tid + 128 * it;
+        const int pg = idx >> 8, which = (idx >> 7) & 1, tok = (idx >> 3) & 15, c = idx & 7;
+        if (!live[pg]) continue;
+        const int kt = pg * ATT_B + tok;
+        const int at = which ? (c ^ ((kt >> 3) & 7)) : (c ^ (tok & 7));
+        const int64_t src = base[pg] + (which ? p.stride_kv : 0) + (int64_t)tok * p.stride_tok + c * 16;
+        cp_async16(st + pg * 4096 + which * 2048 + tok * 128 + at * 16, p.kv_payload + src);
+      }
+      {  // K scales: [page][tok][8] as stored
+        const int pg = tid >> 5, r = tid & 31, tok = r >> 1, hf = r & 1;
+        int64_t b = base[0];
+        bool lv = live[0];
+#pragma unroll
+        for (int x = 1; x < TC_PAGES; ++x)
+          if (x == pg) { b = base[x]; lv = live[x]; }
+        if (lv) {
+          const int64_t soff = (b + (int64_t)tok * p.stride_tok) / 16 + hf * 4;
+          cp_async16(st + TC_RAW_PAYLOAD + pg * 512 + r * 16, p.kv_scales + soff);
+        }
+      }
+      // V scales: one word each, laid out [key % 8][group][key / 8]
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int idx = tid + 128 * it;
+        const int kt = idx >> 3, c = idx & 7, pg = kt >> 4, tok = kt & 15;
+        if (!live[pg]) continue;
+        const int64_t soff = (base[pg] + p.stride_kv + (int64_t)tok * p.stride_tok) / 16 + c;
+        cp_async4(st + TC_RAW_PAYLOAD + TC_RAW_KSCALE + (((kt & 7) * 64 + c * 8 + (kt >> 3)) << 2), p.kv_scales + soff);
+      }
+    };
+    issue(0);
+    cp_async_commit();
+
+    {  // Q row -> f16, pre-multiplied by scale * log2(e), into the swizzled A tile
+      const __nv_bfloat16* qp = p.q + ((int64_t)(q0 + tq) * p.Hq + hq) * ATT_D;
+#pragma unroll
+      for (int ck = 0; ck < 16; ++ck) {
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) w = *reinterpret_cast<const uint4*>(qp + ck * 8);
+        uint4 h;
+        h.x = pack_half2(bf16_lo(w.x) * p.scale_log2, bf16_hi(w.x) * p.scale_log2);
+        h.y = pack_half2(bf16_lo(w.y) * p.scale_log2, bf16_hi(w.y) * p.scale_log2);
+        h.z = pack_half2(bf16_lo(w.z) * p.scale_log2, bf16_hi(w.z) * p.scale_log2);
+        h.w = pack_half2(bf16_lo(w.w) * p.scale_log2, bf16_hi(w.w) * p.scale_log2);
+        *reinterpret_cast<uint4*>(q_s + (ck >> 3) * 16384 + tid * 128 + ((((ck & 7) ^ (tid & 7))) << 4)) = h;
+      }
+    }
+    tc_fence_before();
+    __syncthreads();  // barriers initialised, TMEM address published
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
+    constexpr uint32_t idesc_s = make_idesc_f16(128, TC_NK, 0);
+    constexpr uint32_t idesc_o = make_idesc_f16(128, ATT_D, 0);
+    int fail = 0;
+
+    for (int ti = 0; ti < n_tiles; ++ti) {
+      cp_async_wait<0>();
+      if (__syncthreads_or(fail)) break;  // raw tile ti is in; K/P and V^T are free (PV of ti - 1 has completed)
+      if (ti + 1 < n_tiles) issue(ti + 1);
+      cp_async_commit();
+      const uint8_t* st = raw_s + (ti & 1) * TC_RAW_BYTES;
+      const int key0 = key_begin + ti * TC_NK;
+
+      // ---- K: (key, 16-dim group) items, four per thread ----
+#pragma unroll
+      for (int rep = 0; rep < 4; ++rep) {
+        const int item = tid + 128 * rep;
+        const int kt = (item & 7) + 8 * (item >> 6), c = (item >> 3) & 7;
+        const int pg = kt >> 4, tok = kt & 15;
+        uint32_t h[8];
+        if (key0 + kt < key_end) {
+          const uint4 w = *reinterpret_cast<const uint4*>(st + pg * 4096 + tok * 128 + ((c ^ (tok & 7)) << 4));
+          const float sc = reinterpret_cast<const float*>(st + TC_RAW_PAYLOAD + pg * 512)[tok * 8 + c];
+          const uint32_t sc2 = pack_half2(sc, sc);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            h[2 * i] = hmul2_u32(cvt_e4m3x2_f16x2((uint16_t)(ww[i] & 0xffffu)), sc2);
+            h[2 * i + 1] = hmul2_u32(cvt_e4m3x2_f16x2((uint16_t)(ww[i] >> 16)), sc2);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) h[i] = 0u;
+        }
+        uint8_t* row = kp_s + (c >> 2) * 8192 + kt * 128;
+        *reinterpret_cast<uint4*>(row + (((2 * (c & 3)) ^ (kt & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(row + (((2 * (c & 3) + 1) ^ (kt & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+      }
+      // ---- V^T: (8 keys, 4 dims) items, two per thread ----
+#pragma unroll
+      for (int rep = 0; rep < 2; ++rep) {
+        const int item = tid + 128 * rep;
+        const int ko = item & 7, dq = item >> 3, c = dq >> 2;
+        const int pg = ko >> 1;
+        uint32_t h01[8], h23[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int tok = 8 * (ko & 1) + i;
+          if (key0 + 8 * ko + i < key_end) {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(st + pg * 4096 + 2048 + tok * 128 + ((c ^ ko) << 4) + (dq & 3) * 4);
+            const float sc = reinterpret_cast<const float*>(st + TC_RAW_PAYLOAD + TC_RAW_KSCALE)[i * 64 + c * 8 + ko];
+            const uint32_t sc2 = pack_half2(sc, sc);
+            h01[i] = hmul2_u32(cvt_e4m3x2_f16x2((uint16_t)(w & 0xffffu)), sc2);
+            h23[i] = hmul2_u32(cvt_e4m3x2_f16x2((uint16_t)(w >> 16)), sc2);
+          } else {
+            h01[i] = 0u;
+            h23[i] = 0u;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t* src = (j < 2) ? h01 : h23;
+          const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+          const int d = 4 * dq + j;
+          uint4 v;
+          v.x = prmt(src[0], src[1], sel);
+          v.y = prmt(src[2], src[3], sel);
+          v.z = prmt(src[4], src[5], sel);
+          v.w = prmt(src[6], src[7], sel);
+          *reinterpret_cast<uint4*>(vt_s + d * 128 + ((ko ^ (d & 7)) << 4)) = v;
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0 && !*abort_flag) {
+        tc_fence_after();
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          const uint64_t da = make_desc_k_sw128(q_u32 + sub * 16384);
+          const uint64_t db = make_desc_k_sw128(kp_u32 + sub * 8192);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16(tmem, da + 2 * k, db + 2 * k, idesc_s, (sub | k) ? 1u : 0u);
+        }
+        umma_commit(bar_s);
+      }
+      if (!mbar_wait(bar_s, ti & 1, abort_flag)) fail = 1;
+      tc_fence_after();
+
+      // ---- softmax on this thread's row ----
+      float alpha;
+      {
+        uint32_t sr[2][32];
+        tmem_ld_32x32(tmem_row, sr[0]);
+        tmem_ld_32x32(tmem_row + 32, sr[1]);
+        tmem_ld_wait();
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < TC_NK; ++j) {
+          const int key = key0 + j;
+          float s = __uint_as_float(sr[j >> 5][j & 31]);
+          if (!(valid && key < key_end && key <= pos)) s = -INFINITY;
+          sr[j >> 5][j & 31] = __float_as_uint(s);
+          mx = fmaxf(mx, s);
+        }
+        const float mn = fmaxf(m, mx);
+        const float base = mn == -INFINITY ? 0.f : mn;
+        alpha = exp2f(m - base);
+        m = mn;
+        float sum = 0.f;
+#pragma unroll
+        for (int ck = 0; ck < 8; ++ck) {
+          float pv[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = ck * 8 + e;
+            pv[e] = exp2f(__uint_as_float(sr[j >> 5][j & 31]) - base);
+            sum += pv[e];
+          }
+          const uint4 h = make_uint4(pack_half2(pv[0], pv[1]), pack_half2(pv[2], pv[3]), pack_half2(pv[4], pv[5]),
+                                     pack_half2(pv[6], pv[7]));
+          *reinterpret_cast<uint4*>(kp_s + tid * 128 + ((ck ^ (tid & 7)) << 4)) = h;
+        }
+        l = l * alpha + sum;
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0 && !*abort_flag) {
+        tc_fence_after();
+        const uint64_t da = make_desc_k_sw128(kp_u32);
+        const uint64_t db = make_desc_k_sw128(vt_u32);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem + 128, da + 2 * k, db + 2 * k, idesc_o, k ? 1u : 0u);
+        umma_commit(bar_o);
+      }
+      if (!mbar_wait(bar_o, ti & 1, abort_flag)) fail = 1;
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_row + 128 + 32 * cc, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) o[32 * cc + x] = o[32 * cc + x] * alpha + __uint_as_float(r[x]);
+      }
+      tc_fence_before();
+    }
+    cp_async_wait<0>();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, TC_TMEM_COLS);
+    if (*abort_flag) {
+      if (tid == 0) atomicOr(&g_attn_tc_status, 1u);
+      return;
+    }
+  }
+  if (!valid) return;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
+  if (p.nsplit == 1) {
+    __nv_bfloat16* dst = p.out + row * ATT_D;
+#pragma unroll
+    for (int ck = 0; ck < 16; ++ck) {
+      uint4 w;
+      w.x = pack_bf16x2(o[8 * ck] * inv, o[8 * ck + 1] * inv);
+      w.y = pack_bf16x2(o[8 * ck + 2] * inv, o[8 * ck + 3] * inv);
+      w.z = pack_bf16x2(o[8 * ck + 4] * inv, o[8 * ck + 5] * inv);
+      w.w = pack_bf16x2(o[8 * ck + 6] * inv, o[8 * ck + 7] * inv);
+      *reinterpret_cast<uint4*>(dst + 8 * ck) = w;
+    }
+  } else {
+    float* dst = p.part_o + (row * p.nsplit + sp) * ATT_D;
+#pragma unroll
+    for (int ck = 0; ck < 32; ++ck)
+      *reinterpret_cast<float4*>(dst + 4 * ck) =
+          make_float4(o[4 * ck] * inv, o[4 * ck + 1] * inv, o[4 * ck + 2] * inv, o[4 * ck + 3] * inv);
+    p.part_lse[row * p.nsplit + sp] = l > 0.f ? m + log2f(l) : -INFINITY;
+  }
+}
+
+}  // namespace daser
+
+int daser_launch_attention_tc(const daser::AttnParams& p, int max_q_len, cudaStream_t stream) {
+  using namespace daser;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(paged_attn_fp8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int groups = (max_q_len * p.G + 127) / 128;
+  const dim3 grid(p.Hkv, p.num_seqs, groups * p.nsplit);
+  paged_attn_fp8_tc_kernel<<<grid, 128, TC_SMEM, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// Non-zero once any tensor-core attention CTA gave up on a bounded wait (synchronises the device).
+DASER_API int daser_attention_tc_status(uint32_t* out) {
+  uint32_t v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, daser::g_attn_tc_status, sizeof(v));
+  if (out) *out = v;
+  return (int)e;
+}
