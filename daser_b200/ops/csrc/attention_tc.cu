@@ -16,8 +16,12 @@
 //     every thread then owns one row of S (tcgen05.ld 32x32b: lane = row), so the online
 //     softmax needs no shuffles; P goes back to shared memory as f16 (over the K tile, which
 //     is dead by then) and O_tile = P V (M 128, N 128, K 64) is four more tcgen05.mma;
-//   * the running output lives in registers (one row of 128 floats per thread) and is
-//     updated from TMEM after each tile, so no TMEM store is needed for the rescale.
+//   * P = 2^(S - m) is computed two at a time in f16 (ex2.approx.f16x2) and is the MMA operand
+//     as is; V^T carries one extra row of ones, so column 128 of the output accumulates the row
+//     sums of exactly the P that was multiplied (no separate summation);
+//   * the output accumulates in TMEM across tiles.  The running maximum m is only raised when
+//     a tile exceeds it by more than 2^8 (the f16 P has the head-room), and only then is the
+//     accumulator rescaled (tcgen05.ld / st); most tiles do not touch it.
 //
 // Two CTAs fit one SM (about 105 KB of shared memory, 256 TMEM columns and 128 threads each),
 // which is what overlaps one CTA's softmax with the other's MMAs and copies.
@@ -33,13 +37,16 @@ constexpr int TC_NK = 64;                        // keys per tile
 constexpr int TC_PAGES = TC_NK / ATT_B;          // 4
 constexpr int TC_Q_BYTES = 128 * ATT_D * 2;      // 32768: two sub-tiles [128 rows][64 dims]
 constexpr int TC_KP_BYTES = 16384;               // K: two sub-tiles [64 keys][64 dims]; later P: [128 rows][64 keys]
-constexpr int TC_VT_BYTES = 16384;               // V^T: [128 dims][64 keys]
+constexpr int TC_ON = ATT_D + 16;                // output columns: 128 dims, the row sum, 15 unused
+constexpr int TC_VT_BYTES = TC_ON * 128;         // V^T: [128 dims + 16][64 keys] = 18432
 constexpr int TC_RAW_PAYLOAD = TC_PAGES * 4096;  // per page: K 2048 B, V 2048 B
 constexpr int TC_RAW_KSCALE = TC_PAGES * 512;
 constexpr int TC_RAW_VSCALE = TC_NK * 8 * 4;
 constexpr int TC_RAW_BYTES = TC_RAW_PAYLOAD + TC_RAW_KSCALE + TC_RAW_VSCALE;  // 20480
 constexpr int TC_SMEM = 1024 + TC_Q_BYTES + TC_KP_BYTES + TC_VT_BYTES + 2 * TC_RAW_BYTES + 64;
-constexpr uint32_t TC_TMEM_COLS = 256;           // S in columns [0, 64), O tile in [128, 256)
+constexpr uint32_t TC_TMEM_COLS = 256;           // S in columns [0, 64), O in [64, 208)
+constexpr uint32_t TC_O_COL = 64;
+constexpr float TC_RESCALE_AT = 8.f;             // raise the running maximum only beyond this (log2)
 
 __device__ uint32_t g_attn_tc_status = 0;        // bit 0: a bounded wait ran out
 
@@ -47,6 +54,32 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// {2^lo, 2^hi} as packed f16 (lo in the low half).
+__device__ __forceinline__ uint32_t ex2_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 t;\n\t"
+      "cvt.rn.f16x2.f32 t, %2, %1;\n\t"
+      "ex2.approx.f16x2 %0, t;\n\t}\n"
+      : "=r"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ float ex2_f32(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t r;
   asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -88,10 +121,8 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
   const bool valid = tq < q_len;
   const int pos = ctx - q_len + tq;  // last key this row may see
 
-  float o[ATT_D];
-#pragma unroll
-  for (int i = 0; i < ATT_D; ++i) o[i] = 0.f;
-  float m = -INFINITY, l = 0.f;
+  float m = -INFINITY;  // the maximum the accumulated P are relative to
+  float l = 0.f;
 
   if (n_tiles > 0) {
     const uint32_t q_u32 = smem_u32(q_s), kp_u32 = smem_u32(kp_s), vt_u32 = smem_u32(vt_s), raw_u32 = smem_u32(raw_s);
@@ -172,13 +203,18 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
         *reinterpret_cast<uint4*>(q_s + (ck >> 3) * 16384 + tid * 128 + ((((ck & 7) ^ (tid & 7))) << 4)) = h;
       }
     }
+    {  // rows 128..143 of V^T: row 128 all ones (it accumulates the row sums of P), the rest zero
+      const uint32_t one2 = 0x3c003c00u;
+      const uint32_t v = tid < 8 ? one2 : 0u;
+      *reinterpret_cast<uint4*>(vt_s + ATT_D * 128 + tid * 16) = make_uint4(v, v, v, v);
+    }
     tc_fence_before();
     __syncthreads();  // barriers initialised, TMEM address published
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
     constexpr uint32_t idesc_s = make_idesc_f16(128, TC_NK, 0);
-    constexpr uint32_t idesc_o = make_idesc_f16(128, ATT_D, 0);
+    constexpr uint32_t idesc_o = make_idesc_f16(128, TC_ON, 0);
     int fail = 0;
 
     for (int ti = 0; ti < n_tiles; ++ti) {
@@ -263,43 +299,58 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
         umma_commit(bar_s);
       }
       if (!mbar_wait(bar_s, ti & 1, abort_flag)) fail = 1;
+      __syncwarp();
       tc_fence_after();
 
       // ---- softmax on this thread's row ----
-      float alpha;
       {
         uint32_t sr[2][32];
         tmem_ld_32x32(tmem_row, sr[0]);
         tmem_ld_32x32(tmem_row + 32, sr[1]);
         tmem_ld_wait();
-        float mx = -INFINITY;
+        if (!(valid && key0 + TC_NK - 1 <= pos && key0 + TC_NK <= key_end)) {
+          // the causal edge or the end of the range runs through this tile
 #pragma unroll
-        for (int j = 0; j < TC_NK; ++j) {
-          const int key = key0 + j;
-          float s = __uint_as_float(sr[j >> 5][j & 31]);
-          if (!(valid && key < key_end && key <= pos)) s = -INFINITY;
-          sr[j >> 5][j & 31] = __float_as_uint(s);
-          mx = fmaxf(mx, s);
+          for (int j = 0; j < TC_NK; ++j) {
+            const int key = key0 + j;
+            if (!(valid && key < key_end && key <= pos)) sr[j >> 5][j & 31] = 0xff800000u;  // -inf
+          }
         }
-        const float mn = fmaxf(m, mx);
-        const float base = mn == -INFINITY ? 0.f : mn;
-        alpha = exp2f(m - base);
-        m = mn;
-        float sum = 0.f;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[0][j]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[1][j]));
+        }
+        const float mx = fmaxf(mx0, mx1);
+        // Raise m only when this tile is far above it: P then stays below 2^8, well inside f16.
+        const bool raise = mx > m + TC_RESCALE_AT || (m == -INFINITY && mx > -INFINITY);
+        if (ti > 0 && __any_sync(0xffffffffu, raise)) {
+          // the previous P V has completed (its barrier was waited for before this tile's K was written)
+          const float alpha = raise ? ex2_f32(m - mx) : 1.f;
+#pragma unroll
+          for (int cc = 0; cc < 5; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_row + TC_O_COL + 32 * cc, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * alpha);
+            tmem_st_32x32(tmem_row + TC_O_COL + 32 * cc, r);
+          }
+          tmem_st_wait();
+        }
+        if (raise) m = mx;
+        const float base = m == -INFINITY ? 0.f : m;
 #pragma unroll
         for (int ck = 0; ck < 8; ++ck) {
-          float pv[8];
+          uint32_t h[4];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int j = ck * 8 + e;
-            pv[e] = exp2f(__uint_as_float(sr[j >> 5][j & 31]) - base);
-            sum += pv[e];
+          for (int e = 0; e < 4; ++e) {
+            const int j = ck * 8 + 2 * e;
+            h[e] = ex2_f16x2(__uint_as_float(sr[j >> 5][j & 31]) - base, __uint_as_float(sr[(j + 1) >> 5][(j + 1) & 31]) - base);
           }
-          const uint4 h = make_uint4(pack_half2(pv[0], pv[1]), pack_half2(pv[2], pv[3]), pack_half2(pv[4], pv[5]),
-                                     pack_half2(pv[6], pv[7]));
-          *reinterpret_cast<uint4*>(kp_s + tid * 128 + ((ck ^ (tid & 7)) << 4)) = h;
+          *reinterpret_cast<uint4*>(kp_s + tid * 128 + ((ck ^ (tid & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
         }
-        l = l * alpha + sum;
       }
       fence_async_smem();
       tc_fence_before();
@@ -309,51 +360,72 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
         const uint64_t da = make_desc_k_sw128(kp_u32);
         const uint64_t db = make_desc_k_sw128(vt_u32);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f16(tmem + 128, da + 2 * k, db + 2 * k, idesc_o, k ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) umma_f16(tmem + TC_O_COL, da + 2 * k, db + 2 * k, idesc_o, (ti | k) ? 1u : 0u);
         umma_commit(bar_o);
       }
       if (!mbar_wait(bar_o, ti & 1, abort_flag)) fail = 1;
+      __syncwarp();
       tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_row + 128 + 32 * cc, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int x = 0; x < 32; ++x) o[32 * cc + x] = o[32 * cc + x] * alpha + __uint_as_float(r[x]);
-      }
-      tc_fence_before();
     }
     cp_async_wait<0>();
+    const bool aborted = __syncthreads_or(fail) != 0;
+    if (!aborted) {
+      // ---- epilogue: O / l from TMEM (column 128 holds l).  The TMEM loads are warp-wide
+      // (.sync.aligned): every thread executes them, only the global stores depend on `valid`.
+      const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_32x32(tmem_row + TC_O_COL + ATT_D, r);
+      tmem_ld_wait();
+      l = __uint_as_float(r[0]);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        __syncwarp();  // reconverge after the predicated stores of the previous chunk
+        tmem_ld_32x32(tmem_row + TC_O_COL + 32 * cc, r);
+        tmem_ld_wait();
+        if (!valid) continue;
+        if (p.nsplit == 1) {
+          __nv_bfloat16* dst = p.out + row * ATT_D + 32 * cc;
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(r[8 * x]) * inv, __uint_as_float(r[8 * x + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(r[8 * x + 2]) * inv, __uint_as_float(r[8 * x + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(r[8 * x + 4]) * inv, __uint_as_float(r[8 * x + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(r[8 * x + 6]) * inv, __uint_as_float(r[8 * x + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 8 * x) = w;
+          }
+        } else {
+          float* dst = p.part_o + (row * p.nsplit + sp) * ATT_D + 32 * cc;
+#pragma unroll
+          for (int x = 0; x < 8; ++x)
+            *reinterpret_cast<float4*>(dst + 4 * x) =
+                make_float4(__uint_as_float(r[4 * x]) * inv, __uint_as_float(r[4 * x + 1]) * inv,
+                            __uint_as_float(r[4 * x + 2]) * inv, __uint_as_float(r[4 * x + 3]) * inv);
+        }
+      }
+      if (valid && p.nsplit > 1) p.part_lse[row * p.nsplit + sp] = l > 0.f ? m + log2f(l) : -INFINITY;
+      __syncwarp();
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, TC_TMEM_COLS);
-    if (*abort_flag) {
-      if (tid == 0) atomicOr(&g_attn_tc_status, 1u);
-      return;
-    }
+    if (aborted && tid == 0) atomicOr(&g_attn_tc_status, 1u);
+    return;
   }
+  // no keys in this split: an empty partial
   if (!valid) return;
-  const float inv = l > 0.f ? 1.f / l : 0.f;
   const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
   if (p.nsplit == 1) {
     __nv_bfloat16* dst = p.out + row * ATT_D;
 #pragma unroll
-    for (int ck = 0; ck < 16; ++ck) {
-      uint4 w;
-      w.x = pack_bf16x2(o[8 * ck] * inv, o[8 * ck + 1] * inv);
-      w.y = pack_bf16x2(o[8 * ck + 2] * inv, o[8 * ck + 3] * inv);
-      w.z = pack_bf16x2(o[8 * ck + 4] * inv, o[8 * ck + 5] * inv);
-      w.w = pack_bf16x2(o[8 * ck + 6] * inv, o[8 * ck + 7] * inv);
-      *reinterpret_cast<uint4*>(dst + 8 * ck) = w;
-    }
+    for (int ck = 0; ck < 16; ++ck) *reinterpret_cast<uint4*>(dst + 8 * ck) = make_uint4(0u, 0u, 0u, 0u);
   } else {
     float* dst = p.part_o + (row * p.nsplit + sp) * ATT_D;
 #pragma unroll
-    for (int ck = 0; ck < 32; ++ck)
-      *reinterpret_cast<float4*>(dst + 4 * ck) =
-          make_float4(o[4 * ck] * inv, o[4 * ck + 1] * inv, o[4 * ck + 2] * inv, o[4 * ck + 3] * inv);
-    p.part_lse[row * p.nsplit + sp] = l > 0.f ? m + log2f(l) : -INFINITY;
+    for (int ck = 0; ck < 32; ++ck) *reinterpret_cast<float4*>(dst + 4 * ck) = make_float4(0.f, 0.f, 0.f, 0.f);
+    p.part_lse[row * p.nsplit + sp] = -INFINITY;
   }
 }
 
