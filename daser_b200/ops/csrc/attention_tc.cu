@@ -139,6 +139,14 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
     const int32_t* table = p.block_tables + (int64_t)seq * p.max_blocks;
     const int page_begin = key_begin / ATT_B;
 
+    // Block ids are fetched one tile ahead of the copies that need them, so that the table
+    // read (a dependent global load) is never on the critical path of a tile.
+    int blk_next[TC_PAGES];
+    auto fetch_blocks = [&](int ti) {
+#pragma unroll
+      for (int pg = 0; pg < TC_PAGES; ++pg)
+        blk_next[pg] = __ldg(table + min(page_begin + ti * TC_PAGES + pg, p.max_blocks - 1));
+    };
     auto issue = [&](int ti) {
       const uint32_t st = raw_u32 + (ti & 1) * TC_RAW_BYTES;
       const int key0 = key_begin + ti * TC_NK;
@@ -147,7 +155,7 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
 #pragma unroll
       for (int pg = 0; pg < TC_PAGES; ++pg) {
         live[pg] = key0 + pg * ATT_B < key_end;
-        int blk = table[min(page_begin + ti * TC_PAGES + pg, p.max_blocks - 1)];
+        int blk = blk_next[pg];
         blk = blk < 0 ? 0 : (blk >= p.num_blocks ? p.num_blocks - 1 : blk);
         base[pg] = (int64_t)blk * p.stride_block + (int64_t)kvh * p.stride_head;
       }
@@ -186,8 +194,10 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
         cp_async4(st + TC_RAW_PAYLOAD + TC_RAW_KSCALE + (((kt & 7) * 64 + c * 8 + (kt >> 3)) << 2), p.kv_scales + soff);
       }
     };
+    fetch_blocks(0);
     issue(0);
     cp_async_commit();
+    fetch_blocks(1);
 
     {  // Q row -> f16, pre-multiplied by scale * log2(e), into the swizzled A tile
       const __nv_bfloat16* qp = p.q + ((int64_t)(q0 + tq) * p.Hq + hq) * ATT_D;
@@ -222,6 +232,7 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
       if (__syncthreads_or(fail)) break;  // raw tile ti is in; K/P and V^T are free (PV of ti - 1 has completed)
       if (ti + 1 < n_tiles) issue(ti + 1);
       cp_async_commit();
+      fetch_blocks(ti + 2);  // clamped to the table; used by the next iteration
       const uint8_t* st = raw_s + (ti & 1) * TC_RAW_BYTES;
       const int key0 = key_begin + ti * TC_NK;
 
@@ -412,20 +423,19 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, TC_TMEM_COLS);
     if (aborted && tid == 0) atomicOr(&g_attn_tc_status, 1u);
-    return;
-  }
-  // no keys in this split: an empty partial
-  if (!valid) return;
-  const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
-  if (p.nsplit == 1) {
-    __nv_bfloat16* dst = p.out + row * ATT_D;
+  } else if (valid) {
+    // no keys in this split: an empty partial
+    const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
+    if (p.nsplit == 1) {
+      __nv_bfloat16* dst = p.out + row * ATT_D;
 #pragma unroll
-    for (int ck = 0; ck < 16; ++ck) *reinterpret_cast<uint4*>(dst + 8 * ck) = make_uint4(0u, 0u, 0u, 0u);
-  } else {
-    float* dst = p.part_o + (row * p.nsplit + sp) * ATT_D;
+      for (int ck = 0; ck < 16; ++ck) *reinterpret_cast<uint4*>(dst + 8 * ck) = make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      float* dst = p.part_o + (row * p.nsplit + sp) * ATT_D;
 #pragma unroll
-    for (int ck = 0; ck < 32; ++ck) *reinterpret_cast<float4*>(dst + 4 * ck) = make_float4(0.f, 0.f, 0.f, 0.f);
-    p.part_lse[row * p.nsplit + sp] = -INFINITY;
+      for (int ck = 0; ck < 32; ++ck) *reinterpret_cast<float4*>(dst + 4 * ck) = make_float4(0.f, 0.f, 0.f, 0.f);
+      p.part_lse[row * p.nsplit + sp] = -INFINITY;
+    }
   }
 }
 

@@ -78,10 +78,13 @@ __device__ __forceinline__ uint32_t ew_ld_acquire_sys(const uint32_t* p) {
 #endif
 
 // out = rmsnorm(x [+ residual]) * weight ; residual <- x + residual.
-// One CTA of up to 256 threads per row; each thread keeps ITERS fragments of 8 values in
-// registers (hidden <= 8 * ITERS * blockDim), so the row is read from memory once.
-template <typename TIn, int ITERS>
-__global__ void __launch_bounds__(256)
+// One CTA per row; each thread keeps ITERS fragments of 8 values in registers
+// (hidden <= 8 * ITERS * blockDim), so the row is read from memory once.  Two shapes: 256
+// threads with several fragments each when there are rows enough to fill the GPU (bandwidth
+// bound), and up to 1024 threads with one fragment each when there are only a few rows (a
+// token block of a serving step: latency bound, so every load of the row is in flight at once).
+template <typename TIn, int ITERS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ weight, OutList out, int64_t out_row_offset,
                    int hidden, float eps, int zero_after, TpSync sync, int n_partials, int64_t partial_stride) {
@@ -377,7 +380,9 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
   if (rows < 0 || hidden <= 0 || hidden % 8 || n_out < 1 || n_out > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (rows == 0) return 0;
   int threads = ((hidden / 8 + 31) / 32) * 32;
-  if (threads > 256) threads = 256;
+  const bool few_rows = rows <= 4 * 148;
+  const int max_threads = few_rows ? 1024 : 256;
+  if (threads > max_threads) threads = max_threads;
   const int iters = (hidden / 8 + threads - 1) / threads;
   if (iters > 16) return DASER_ERR_TOO_LARGE;
   OutList out;
@@ -393,16 +398,18 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
     sync.wait_base = tp->wait_base; sync.done_base = tp->done_base;
     for (int i = 0; i < tp->n_signal; ++i) sync.signal[i] = tp->signal[i];
   }
-#define NORM_LAUNCH(TIN, IT)                                                                          \
-  add_rmsnorm_kernel<TIN, IT><<<(unsigned)rows, threads, 0, stream>>>(                                  \
+#define NORM_LAUNCH(TIN, IT, MAXT)                                                                    \
+  add_rmsnorm_kernel<TIN, IT, MAXT><<<(unsigned)rows, threads, 0, stream>>>(                            \
       (TIN*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, \
       x_is_fp32 ? zero_after : 0, sync, n_partials < 1 ? 1 : n_partials, partial_stride)
-#define NORM_DISPATCH(TIN)                                   \
-  if (iters <= 1) NORM_LAUNCH(TIN, 1);                       \
-  else if (iters <= 2) NORM_LAUNCH(TIN, 2);                  \
-  else if (iters <= 4) NORM_LAUNCH(TIN, 4);                  \
-  else if (iters <= 8) NORM_LAUNCH(TIN, 8);                  \
-  else NORM_LAUNCH(TIN, 16)
+#define NORM_DISPATCH(TIN)                                                  \
+  if (few_rows && iters <= 1) NORM_LAUNCH(TIN, 1, 1024);                    \
+  else if (few_rows && iters <= 2) NORM_LAUNCH(TIN, 2, 1024);               \
+  else if (iters <= 1) NORM_LAUNCH(TIN, 1, 256);                            \
+  else if (iters <= 2) NORM_LAUNCH(TIN, 2, 256);                            \
+  else if (iters <= 4) NORM_LAUNCH(TIN, 4, 256);                            \
+  else if (iters <= 8) NORM_LAUNCH(TIN, 8, 256);                            \
+  else NORM_LAUNCH(TIN, 16, 256)
   if (x_is_fp32) { NORM_DISPATCH(float); } else { NORM_DISPATCH(__nv_bfloat16); }
 #undef NORM_DISPATCH
 #undef NORM_LAUNCH
