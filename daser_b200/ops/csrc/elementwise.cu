@@ -8,6 +8,8 @@
 // accumulate into the same buffer without a separate memset.
 #include <string.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kv_paged.h"
 
@@ -380,7 +382,9 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
   if (rows < 0 || hidden <= 0 || hidden % 8 || n_out < 1 || n_out > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (rows == 0) return 0;
   int threads = ((hidden / 8 + 31) / 32) * 32;
-  const bool few_rows = rows <= 4 * 148;
+  // measured kernel time, hidden 8192, fp32 input: 64 rows 10.7 us wide / 13.3 us narrow,
+  // 128 rows 12.4 / 19.4, 512 rows 47 / 40: wide while one wave of CTAs covers the rows
+  const bool few_rows = rows <= 148;
   const int max_threads = few_rows ? 1024 : 256;
   if (threads > max_threads) threads = max_threads;
   const int iters = (hidden / 8 + threads - 1) / threads;
