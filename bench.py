@@ -148,6 +148,9 @@ def main() -> None:
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default="llama3-70b")
     ap.add_argument("--pool", type=int, default=64, help="chunks in the synthetic pool")
+    ap.add_argument("--tp-impl", choices=("fused", "nccl"), default="fused",
+                    help="fused: GEMM epilogue reduce-scatter + gated all-gather over peer memory; "
+                         "nccl: the unfused baseline (same kernels, NCCL all-reduce)")
     ap.add_argument("--k", type=int, default=8, help="chunks per request")
     ap.add_argument("--hbm-frac", type=float, default=0.5, help="fraction of the pool the HBM tier can hold")
     ap.add_argument("--host-frac", type=float, default=1.0, help="fraction of the pool the pinned host tier can hold")
@@ -183,7 +186,7 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         from daser_b200.parallel.tp import TPContext
 
-        tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=256)
+        tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=256, impl=args.tp_impl)
 
     store_dir = args.store_dir or tempfile.mkdtemp(prefix="daser_bench_")
     if tp_ctx is not None:
@@ -310,7 +313,8 @@ def main() -> None:
             "gpu_launches": int(launches),
             "clocks": clocks,
             "config": {
-                "model": cfg.name, "parallelism": f"tp{args.gpus}", "global_batch": 1,
+                "model": cfg.name, "parallelism": f"tp{args.gpus}", "tp_impl": args.tp_impl if args.gpus > 1 else "none",
+                "global_batch": 1,
                 "seq_len": int(prompt_tokens / len(done)), "chunks_per_request": args.k,
                 "chunk_pool": args.pool, "kv_codec": "fp8b16 (e4m3 + fp32 scale / 16)",
                 "io_backend": eng.worker.transfer.backend.name, "store": dcfg.store_path,

@@ -268,6 +268,8 @@ class GpuModelRunner:
         if int(self.status[0].item()) != 0:
             self.status.zero_()
             raise RuntimeError("a GEMM wait ran out (status word set); the step's output is invalid")
+        if attention.tc_status() != 0:
+            raise RuntimeError("an attention CTA gave up on a bounded wait; the step's output is invalid")
 
 
 def make_step_inputs(seqs: list[dict], block_tokens: int, device, max_blocks: Optional[int] = None) -> StepInputs:

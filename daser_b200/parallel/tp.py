@@ -47,7 +47,12 @@ NUM_FLAGS = 16
 
 
 class TPContext:
-    def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256) -> None:
+    def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256, impl: Optional[str] = None) -> None:
+        # "fused": the path this module is about.  "nccl": the unfused arrangement it is measured
+        # against (same kernels, replicated activations, NCCL all-reduce after the row-parallel GEMMs).
+        self.impl = impl or os.environ.get("DASER_TP_IMPL", "fused")
+        if self.impl not in ("fused", "nccl"):
+            raise ValueError(f"unknown tensor-parallel implementation {self.impl!r}")
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -207,6 +212,8 @@ class TPContext:
         T = inp.num_tokens
         if T > self.max_tokens or T > runner.max_tokens:
             raise ValueError("step exceeds the tensor-parallel buffers")
+        if self.impl == "nccl":
+            return self._forward_body_nccl(runner, inp, nsplit, split_tokens)
         self._rs_off = self._ag_off = self._done_off = 0
         D, B = cfg.head_dim, cfg.block_tokens
         rows = -(-T // self.tp)
@@ -234,6 +241,38 @@ class TPContext:
             nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             self._norm_push(runner, self.acc, nxt, h, rows, wait=True)
         ew.advance_epochs(self.epochs, self._rs_off, self._ag_off, self._done_off)
+
+    def _forward_body_nccl(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+        """The baseline: what stock tensor parallelism does (``vllm/model_executor/layers/linear.py``,
+        ``RowParallelLinear`` with ``reduce_results``): every rank keeps the whole residual stream,
+        column- and row-parallel GEMMs run on the local shards (the same tcgen05 kernels as the
+        fused path), and the row-parallel outputs are summed by a NCCL all-reduce (on the fp32
+        split-K accumulator when the GEMM was split, else on its bf16 output) before the
+        add + RMSNorm, which every rank repeats on all rows.  No peer memory, no flags."""
+        cfg, w = self.cfg, runner.w
+        T = inp.num_tokens
+        D, B = cfg.head_dim, cfg.block_tokens
+        h, normed = runner.h[:T], runner.normed[:T]
+        ew.embedding(inp.tokens, w.embed, out=h)
+        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li, lw in enumerate(w.layers):
+            qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
+            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+            attn = runner.attn_out[:T].view(T, runner.hq, D)
+            attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
+                                      inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
+                                      runner.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
+            o, f32 = runner._linear(runner.attn_out[:T], lw.wo, runner.hid_acc, runner.hid_bf)
+            dist.all_reduce(o, group=self.group)
+            ew.add_rmsnorm(o, lw.post_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
+            gu, f32 = runner._linear(normed, lw.w_gate_up, runner.gu_acc, runner.gu_bf)
+            ew.swiglu(gu, out=runner.act[:T], zero_after=f32)
+            d, f32 = runner._linear(runner.act[:T], lw.w_down, runner.hid_acc, runner.hid_bf)
+            dist.all_reduce(d, group=self.group)
+            nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
+            ew.add_rmsnorm(d, nxt, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
+        self.gathered[:T].copy_(normed)  # where `sample` looks for the last layer's output
 
     def sample(self, runner, inp) -> torch.Tensor:
         n = inp.num_seqs

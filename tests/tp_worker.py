@@ -46,6 +46,20 @@ def main() -> None:
         hidden_tp = ctx.gathered[: hi - lo].float().clone()
     runner.check_status()
     ok = True
+    # the unfused NCCL arrangement of the same shards must sample the same tokens
+    ctx.impl = "nccl"
+    base_runner = GpuModelRunner(cfg, shard_weights(full, tp, rank), 64, 128, 8, ctx, use_graphs=False)
+    got_nccl = []
+    for lo, hi in ((0, 33), (33, 45)):
+        inp = make_step_inputs([{"tokens": tokens[lo:hi], "start_pos": lo, "block_table": table}], 16, "cuda")
+        got_nccl.append(int(base_runner.forward(inp)[0].item()))
+        hidden_nccl = ctx.gathered[: hi - lo].float().clone()
+    ctx.impl = "fused"
+    rel_nccl = (hidden_nccl - hidden_tp).abs().max().item() / hidden_tp.abs().max().item()
+    if rank == 0:
+        print(f"tokens nccl={got_nccl} fused={got} hidden rel diff={rel_nccl:.4f}", flush=True)
+    ok = ok and rel_nccl < 0.06
+    del base_runner
     if rank == 0:
         single = GpuModelRunner(cfg, full, 64, 128, 8)
         want = []
