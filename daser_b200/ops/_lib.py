@@ -85,6 +85,7 @@ class Gemm(C.Structure):
         ("work", C.c_void_p),
         ("work_ld", C.c_int64),
         ("tile_counters", C.c_void_p),
+        ("bcast", C.c_int32),
     ]
 
 

@@ -21,6 +21,10 @@
 //                    into slot s of the owner's receive buffer ([slot][rows_per_owner][N],
 //                    dst_row_offset = s * rows_per_owner) with plain 64-byte stores and bumps the
 //                    owner's arrival counter; the owner's add + RMSNorm kernel sums the slots.
+//                    With `bcast` the rows are not partitioned: every rank receives the whole
+//                    partial (one-shot all-reduce; each rank then sums and normalises all rows
+//                    itself, so no all-gather follows).  One NVLink hop instead of two, tp - 1
+//                    times the bytes: the form for the few rows of a serving step.
 //                    Half the NVLink bytes of the fp32 form and no atomics.
 //   EPI_REDUCE_F32   C is fp32 and is accumulated with vector red.global.add; rows are
 //                    partitioned over n_owners buffers (rows_per_owner each).  With one owner
@@ -60,6 +64,7 @@ struct GemmParams {
   int rows_per_owner;
   int64_t ldc;
   int64_t dst_row_offset;  // added to the row inside the owner's buffer (bf16 store epilogue)
+  int bcast;               // bf16 epilogues: store every row to ALL n_owners buffers (one-shot all-reduce)
   void* c[DASER_MAX_RANKS];
   uint32_t* arrive[DASER_MAX_RANKS];  // per-owner arrival counters (may be null)
   uint32_t* status;                   // [0] = timeout flag
@@ -244,18 +249,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!row_ok) continue;
         const int col0 = n0 + c * 32;
         if (p.epilogue == EPI_STORE_BF16) {
-          __nv_bfloat16* dst =
-              reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + (local_row + p.dst_row_offset) * p.ldc + col0;
+          uint4 o[4];
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            if (col0 + v * 8 < p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + v * 8) = o;
-            }
+            o[v].x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+            o[v].y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            o[v].z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            o[v].w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+          }
+          // one destination (the row's owner), or every rank's copy when broadcasting
+          const int n_dst = p.bcast ? p.n_owners : 1;
+          for (int d = 0; d < n_dst; ++d) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[p.bcast ? d : owner]) +
+                                 ((p.bcast ? (int64_t)row : local_row) + p.dst_row_offset) * p.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              if (col0 + v * 8 < p.N) *reinterpret_cast<uint4*>(dst + v * 8) = o[v];
           }
         } else {
           float* dst = p.epilogue == EPI_SPLITK_SCATTER
@@ -292,24 +301,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int c = 0; c < BN / 32; ++c) {
             const int col0 = n0 + c * 32;
             float* src = p.work + (int64_t)row * p.work_ld + col0;
-            __nv_bfloat16* dst =
-                reinterpret_cast<__nv_bfloat16*>(p.c[owner]) + (local_row + p.dst_row_offset) * p.ldc + col0;
             // all loads of the chunk first (one L2 round trip), then the stores
             float4 t[8];
 #pragma unroll
             for (int v = 0; v < 8; ++v)
               t[v] = (col0 + v * 4 < p.N) ? __ldcg(reinterpret_cast<const float4*>(src + v * 4))
                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+            uint4 o[4];
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               if (col0 + v * 8 < p.N) {
                 *reinterpret_cast<float4*>(src + v * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
                 *reinterpret_cast<float4*>(src + v * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-                uint4 o;
-                o.x = pack_bf16x2(t[2 * v].x, t[2 * v].y); o.y = pack_bf16x2(t[2 * v].z, t[2 * v].w);
-                o.z = pack_bf16x2(t[2 * v + 1].x, t[2 * v + 1].y); o.w = pack_bf16x2(t[2 * v + 1].z, t[2 * v + 1].w);
-                *reinterpret_cast<uint4*>(dst + v * 8) = o;
               }
+              o[v].x = pack_bf16x2(t[2 * v].x, t[2 * v].y); o[v].y = pack_bf16x2(t[2 * v].z, t[2 * v].w);
+              o[v].z = pack_bf16x2(t[2 * v + 1].x, t[2 * v + 1].y); o[v].w = pack_bf16x2(t[2 * v + 1].z, t[2 * v + 1].w);
+            }
+            const int n_dst = p.bcast ? p.n_owners : 1;
+            for (int d = 0; d < n_dst; ++d) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[p.bcast ? d : owner]) +
+                                   ((p.bcast ? (int64_t)row : local_row) + p.dst_row_offset) * p.ldc + col0;
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                if (col0 + v * 8 < p.N) *reinterpret_cast<uint4*>(dst + v * 8) = o[v];
             }
           }
         }
@@ -322,8 +336,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64 && signal) {
           __threadfence_system();  // one release fence, then relaxed bumps (a release per bump would pay it again)
-          const int o0 = m0 / p.rows_per_owner;
-          const int o1 = min(m0 + GEMM_BM - 1, p.M - 1) / p.rows_per_owner;
+          const int o0 = p.bcast ? 0 : m0 / p.rows_per_owner;
+          const int o1 = p.bcast ? p.n_owners - 1 : min(m0 + GEMM_BM - 1, p.M - 1) / p.rows_per_owner;
           for (int o = o0; o <= o1; ++o)
             asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.arrive[o]) : "memory");
         }
@@ -433,6 +447,7 @@ typedef struct {
   float* work;
   int64_t work_ld;
   uint32_t* tile_counters;
+  int32_t bcast;  // 1: the bf16 epilogues store to every c[i] (row + dst_row_offset) and bump every arrive[i]
 } DaserGemm;
 
 DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
@@ -451,6 +466,8 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   p.rows_per_owner = g->rows_per_owner;
   p.ldc = g->ldc;
   p.dst_row_offset = g->dst_row_offset;
+  p.bcast = g->bcast ? 1 : 0;
+  if (p.bcast && g->epilogue == EPI_REDUCE_F32) return DASER_ERR_BAD_ARG;
   for (int i = 0; i < DASER_MAX_RANKS; ++i) { p.c[i] = g->c[i]; p.arrive[i] = g->arrive[i]; }
   p.status = g->status;
   p.work = g->work;

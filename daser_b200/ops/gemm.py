@@ -84,6 +84,7 @@ def linear(
     work: Optional[torch.Tensor] = None,
     tile_counters: Optional[torch.Tensor] = None,
     ldc: Optional[int] = None,
+    broadcast: bool = False,
     stream=None,
 ) -> torch.Tensor:
     assert x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -106,6 +107,9 @@ def linear(
             g.k_splits, g.epilogue = k_splits, EPI_SPLITK_SCATTER
             g.work, g.work_ld, g.tile_counters = work.data_ptr(), work.stride(0), tile_counters.data_ptr()
         g.n_owners, g.rows_per_owner, g.dst_row_offset = len(owners), rows_per_owner, dst_row_offset
+        # broadcast: the one-shot all-reduce form.  Every rank receives this rank's whole partial
+        # (rows are not partitioned: row r lands at dst_row_offset + r of every owner's buffer)
+        g.bcast = 1 if broadcast else 0
         for i, ptr in enumerate(owners):
             g.c[i] = ptr
         for i, ptr in enumerate(arrive or []):

@@ -14,6 +14,9 @@ GPU and the hot path makes no NCCL call:
   normalises its rows and stores them into every rank's gathered-activation buffer (plain
   16-byte peer stores), then bumps a per-source flag on every rank; the TMA producer of the
   next column-parallel GEMM waits for exactly the flags of the rows its tile needs.
+* **steps of few tokens** (the serving case) use the one-shot form instead: the GEMM epilogue
+  writes its partial into every peer's receive buffer and each rank sums and normalises all rows
+  itself: one NVLink hop per sync point, no all-gather (``_forward_body_oneshot``).
 * **chunk-KV restore** scatters from the IO rank into every rank's paged pool
   (``ops/csrc/kv_paged.cu``); **save** has every rank compress and push its head slice into
   the IO rank's staging buffer.
@@ -42,6 +45,7 @@ from daser_b200.ops import attention, elementwise as ew, gemm, kv_ops
 from daser_b200.parallel.health import PeerMonitor
 
 FLAG_RS = 0  # arrival counter of reduce-scattered partials
+FLAG_OS = 1  # and 2: arrival counters of the two one-shot all-reduce receive buffers
 FLAG_AG = 8  # first of tp per-source "rows landed" flags
 NUM_FLAGS = 16
 
@@ -50,8 +54,9 @@ class TPContext:
     def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256, impl: Optional[str] = None) -> None:
         # "fused": the path this module is about.  "nccl": the unfused arrangement it is measured
         # against (same kernels, replicated activations, NCCL all-reduce after the row-parallel GEMMs).
+        # "twoshot" forces the reduce-scatter / all-gather form at every step size.
         self.impl = impl or os.environ.get("DASER_TP_IMPL", "fused")
-        if self.impl not in ("fused", "nccl"):
+        if self.impl not in ("fused", "twoshot", "nccl"):
             raise ValueError(f"unknown tensor-parallel implementation {self.impl!r}")
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
@@ -87,6 +92,11 @@ class TPContext:
         # kernel of a forward advances the bases, so a captured forward can be replayed
         self.epochs = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._rs_off = self._ag_off = self._done_off = 0
+        # one-shot all-reduce (steps of few tokens): two alternating receive buffers of tp slots
+        # x os_cap rows, their arrival counters and the bases those counters are read against
+        self.os_cap = min(max_tokens, int(os.environ.get("DASER_TP_ONESHOT_MAX", "256")))
+        self.os_buf = [self.alloc(f"os_{i}", (self.tp * self.os_cap, H), torch.bfloat16) for i in range(2)]
+        self.epochs_os = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.save_staging: Optional[torch.Tensor] = None
         self.health: Optional[PeerMonitor] = None
         if os.environ.get("DASER_TP_HEALTH", "1") != "0":
@@ -214,6 +224,8 @@ class TPContext:
             raise ValueError("step exceeds the tensor-parallel buffers")
         if self.impl == "nccl":
             return self._forward_body_nccl(runner, inp, nsplit, split_tokens)
+        if self.impl == "fused" and T <= self.os_cap:
+            return self._forward_body_oneshot(runner, inp, nsplit, split_tokens)
         self._rs_off = self._ag_off = self._done_off = 0
         D, B = cfg.head_dim, cfg.block_tokens
         rows = -(-T // self.tp)
@@ -241,6 +253,70 @@ class TPContext:
             nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             self._norm_push(runner, self.acc, nxt, h, rows, wait=True)
         ew.advance_epochs(self.epochs, self._rs_off, self._ag_off, self._done_off)
+
+    # -- one-shot form: GEMM -> all-reduce in the epilogue, one NVLink hop per sync point -----------
+    def _row_gemm_bcast(self, runner, x: torch.Tensor, w: torch.Tensor, T: int, which: int, offs: list[int]) -> None:
+        """Row-parallel GEMM whose epilogue stores the bf16 partial into this rank's slot of EVERY
+        rank's receive buffer ``which`` and bumps every rank's arrival counter once per tile."""
+        N, K = w.shape
+        bn, ks = (128, 4) if K >= 8192 and T <= 128 else (64, 1)
+        if -(-T // 128) * -(-N // 128) >= 148:
+            bn, ks = 128, 1
+        offs[which] += self.tp * -(-T // 128) * -(-N // bn)
+        gemm.linear(x, w, owners=self.ptrs[f"os_{which}"], rows_per_owner=self.os_cap, ldc=N, block_n=bn,
+                    k_splits=ks, scatter_bf16=True, dst_row_offset=self.rank * self.os_cap, broadcast=True,
+                    work=runner.hid_acc[:T], tile_counters=self.tile_counters,
+                    arrive=[self.flag_ptr(r, FLAG_OS + which) for r in range(self.tp)], status=runner.status)
+
+    def _norm_sum(self, runner, which: int, weight: torch.Tensor, h: torch.Tensor, out: torch.Tensor, T: int,
+                  offs: list[int]) -> None:
+        """Wait for every rank's partial in buffer ``which``, sum the tp slots, add the residual and
+        normalise all T rows locally (every rank sums the same values in the same order, so the
+        replicated residual streams stay bit-identical)."""
+        sync = ew.TpSync()
+        sync.wait_counter = self.flag_ptr(self.rank, FLAG_OS + which)
+        sync.wait_target = offs[which]
+        sync.wait_base = self.epochs_os.data_ptr() + 4 * which
+        sync.status = runner.status.data_ptr()
+        ew.add_rmsnorm(self.os_buf[which][:T], weight, residual=h, out=out, eps=self.cfg.rms_eps, zero_after=False,
+                       tp_sync=sync, n_partials=self.tp, partial_stride=self.os_cap * self.cfg.hidden)
+
+    def _forward_body_oneshot(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+        """The fused forward for steps of few tokens (a RAG query block, a decode batch).
+
+        At this size a sync point costs latency, not bandwidth, so each of the two per-layer
+        reductions is ONE hop: the row-parallel GEMM's epilogue writes its bf16 partial tile
+        straight into every peer's receive buffer while the other tiles still compute, and each
+        rank's add + RMSNorm waits for the arrivals, sums the tp slots from its own HBM and
+        normalises all rows; the next column-parallel GEMM then reads local memory and needs no
+        gate.  The price is tp - 1 times the reduce-scatter's NVLink bytes (7 MB per GEMM at 64
+        tokens and tp = 8), spread over the GEMM.  The two receive buffers alternate: a peer can
+        only overwrite a buffer after it has passed the other one's sync point, which needs this
+        rank's next partial, which this rank issues after it has read the first."""
+        cfg, w = self.cfg, runner.w
+        T = inp.num_tokens
+        D, B = cfg.head_dim, cfg.block_tokens
+        h, normed = runner.h[:T], runner.normed[:T]
+        offs = [0, 0]
+        ew.embedding(inp.tokens, w.embed, out=h)
+        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li, lw in enumerate(w.layers):
+            qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
+            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+            attn = runner.attn_out[:T].view(T, runner.hq, D)
+            attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
+                                      inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
+                                      runner.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
+            self._row_gemm_bcast(runner, runner.attn_out[:T], lw.wo, T, 0, offs)
+            self._norm_sum(runner, 0, lw.post_norm, h, normed, T, offs)
+            gu, f32 = runner._linear(normed, lw.w_gate_up, runner.gu_acc, runner.gu_bf)
+            ew.swiglu(gu, out=runner.act[:T], zero_after=f32)
+            self._row_gemm_bcast(runner, runner.act[:T], lw.w_down, T, 1, offs)
+            last = li + 1 == len(w.layers)
+            nxt = w.final_norm if last else w.layers[li + 1].input_norm
+            self._norm_sum(runner, 1, nxt, h, self.gathered[:T] if last else normed, T, offs)
+        ew.advance_epochs(self.epochs_os, offs[0], offs[1], 0)
 
     def _forward_body_nccl(self, runner, inp, nsplit: int, split_tokens: int) -> None:
         """The baseline: what stock tensor parallelism does (``vllm/model_executor/layers/linear.py``,

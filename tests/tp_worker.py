@@ -46,20 +46,23 @@ def main() -> None:
         hidden_tp = ctx.gathered[: hi - lo].float().clone()
     runner.check_status()
     ok = True
-    # the unfused NCCL arrangement of the same shards must sample the same tokens
-    ctx.impl = "nccl"
-    base_runner = GpuModelRunner(cfg, shard_weights(full, tp, rank), 64, 128, 8, ctx, use_graphs=False)
-    got_nccl = []
-    for lo, hi in ((0, 33), (33, 45)):
-        inp = make_step_inputs([{"tokens": tokens[lo:hi], "start_pos": lo, "block_table": table}], 16, "cuda")
-        got_nccl.append(int(base_runner.forward(inp)[0].item()))
-        hidden_nccl = ctx.gathered[: hi - lo].float().clone()
+    # the other arrangements of the same shards (reduce-scatter + all-gather at every size; plain
+    # NCCL all-reduce) must agree with the default one (one-shot all-reduce at this step size)
+    for other in ("twoshot", "nccl"):
+        ctx.impl = other
+        other_runner = GpuModelRunner(cfg, shard_weights(full, tp, rank), 64, 128, 8, ctx, use_graphs=False)
+        got_other = []
+        for lo, hi in ((0, 33), (33, 45)):
+            inp = make_step_inputs([{"tokens": tokens[lo:hi], "start_pos": lo, "block_table": table}], 16, "cuda")
+            got_other.append(int(other_runner.forward(inp)[0].item()))
+            hidden_other = ctx.gathered[: hi - lo].float().clone()
+        other_runner.check_status()
+        rel_other = (hidden_other - hidden_tp).abs().max().item() / hidden_tp.abs().max().item()
+        if rank == 0:
+            print(f"tokens {other}={got_other} fused={got} hidden rel diff={rel_other:.4f}", flush=True)
+        ok = ok and rel_other < 0.06
+        del other_runner
     ctx.impl = "fused"
-    rel_nccl = (hidden_nccl - hidden_tp).abs().max().item() / hidden_tp.abs().max().item()
-    if rank == 0:
-        print(f"tokens nccl={got_nccl} fused={got} hidden rel diff={rel_nccl:.4f}", flush=True)
-    ok = ok and rel_nccl < 0.06
-    del base_runner
     if rank == 0:
         single = GpuModelRunner(cfg, full, 64, 128, 8)
         want = []
