@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--hq", type=int, default=64)
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--check", type=int, default=1)
+    ap.add_argument("--plans", default="", help="extra split plans for the tcgen05 kernel, e.g. 26x128,9x384")
     args = ap.parse_args()
     D, B, dev = 128, 16, "cuda"
     nb = -(-args.ctx // B)
@@ -53,9 +54,11 @@ def main():
         sc = sc.masked_fill((torch.arange(args.ctx)[None, :] > lim)[None], float("-inf"))
         ref = torch.einsum("hts,shd->thd", sc.softmax(-1), v)
     flops = 4.0 * args.q * args.hq * args.ctx * D
-    for name, tc in (("tcgen05", True), ("mma.sync", False)):
+    arms = [("tcgen05", True, None), ("mma.sync", False, None)]
+    arms += [("tcgen05", True, tuple(int(v) for v in pl.split("x"))) for pl in args.plans.split(",") if pl]
+    for name, tc, plan in arms:
         attention.set_tensor_core_prefill(tc)
-        ns, st = attention.plan_splits(1, args.hkv, args.q, args.hq // args.hkv, args.ctx, B)
+        ns, st = plan or attention.plan_splits(1, args.hkv, args.q, args.hq // args.hkv, args.ctx, B)
         fn = lambda: attention.paged_attention(q, out, pool, 0, tables, q_start, ctx_t, args.q, args.ctx, args.hkv,
                                                D**-0.5, ws, nsplit=ns, split_tokens=st)
         med, best = time_cuda(fn, iters=20, warmup=3, flush=True)

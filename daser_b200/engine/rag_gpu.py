@@ -31,6 +31,7 @@ from daser_b200.hashing import hash_tokens
 from daser_b200.kv.hbm_store import HBMStore
 from daser_b200.models.llama import LlamaConfig, LlamaWeights
 from daser_b200.ops import kv_ops  # noqa: F401
+from daser_b200.ops import gemm as gemm_ops
 from daser_b200.utils import trace
 
 
@@ -67,6 +68,10 @@ class GpuRagEngine:
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.weights = weights or LlamaWeights.random(cfg, self.device, torch.bfloat16, tp=self.tp,
                                                       rank=self.rank, seed=seed)
+        # the engine owns its weights: put gate/up rows in the order that lets SwiGLU run as the
+        # GEMM's epilogue (in place, one layer-sized temporary)
+        if self.weights.gate_up_block == 0 and self.weights.inter_local % gemm_ops.GATE_UP_BLOCK == 0:
+            self.weights.interleave_gate_up_(gemm_ops.GATE_UP_BLOCK)
         self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device,
                                      max_blocks=max_blocks, use_graphs=use_graphs)
         self.blocks = BlockAllocator(num_blocks)

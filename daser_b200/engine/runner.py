@@ -138,6 +138,21 @@ class GpuModelRunner:
         gemm.linear(x, w, out=out_bf[:M], block_n=bn, k_splits=1, status=self.status)
         return out_bf[:M], False
 
+    def mlp_up(self, x: torch.Tensor, lw, T: int, **gate) -> torch.Tensor:
+        """``silu(x Wg^T) * (x Wu^T)`` into ``self.act[:T]``: one GEMM with the activation as its
+        epilogue when the weights are interleaved and the shape runs unsplit, else GEMM + kernel."""
+        w = self.w
+        if w.gate_up_block == gemm.GATE_UP_BLOCK and gemm.can_fuse_swiglu(T, lw.w_gate_up.shape[0], lw.w_gate_up.shape[1]):
+            return gemm.linear_swiglu(x, lw.w_gate_up, self.act[:T], status=self.status, **gate)
+        bn, ks = gemm.plan_tiles(T, lw.w_gate_up.shape[0], lw.w_gate_up.shape[1], allow_split=True)
+        if ks > 1:
+            gemm.linear(x, lw.w_gate_up, acc=self.gu_acc[:T], block_n=bn, k_splits=ks, status=self.status, **gate)
+            gu, f32 = self.gu_acc[:T], True
+        else:
+            gemm.linear(x, lw.w_gate_up, out=self.gu_bf[:T], block_n=bn, k_splits=1, status=self.status, **gate)
+            gu, f32 = self.gu_bf[:T], False
+        return ew.swiglu(gu, out=self.act[:T], zero_after=f32, block=w.gate_up_block)
+
     # -- one step -----------------------------------------------------------------------------------
     # -- step inputs ---------------------------------------------------------------------------------
     def stage_inputs(self, seqs: list[dict]) -> StepInputs:
@@ -240,8 +255,7 @@ class GpuModelRunner:
                                       self.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
             o, f32 = self._linear(self.attn_out[:T], lw.wo, self.hid_acc, self.hid_bf)
             ew.add_rmsnorm(o, lw.post_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
-            gu, f32 = self._linear(normed, lw.w_gate_up, self.gu_acc, self.gu_bf)
-            ew.swiglu(gu, out=self.act[:T], zero_after=f32)
+            self.mlp_up(normed, lw, T)
             d, f32 = self._linear(self.act[:T], lw.w_down, self.hid_acc, self.hid_bf)
             next_norm = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             ew.add_rmsnorm(d, next_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)

@@ -102,6 +102,30 @@ class LlamaWeights:
     final_norm: torch.Tensor
     lm_head: torch.Tensor  # [vocab / tp, hidden]
     meta: dict = field(default_factory=dict)
+    # 0: w_gate_up rows are [gate | up].  b > 0: blocks of b gate rows followed by the matching up
+    # rows (the order in which a GEMM tile holds both halves, so SwiGLU can be its epilogue).
+    gate_up_block: int = 0
+
+    def interleave_gate_up_(self, block: int = 64) -> "LlamaWeights":
+        """Reorder every layer's gate/up rows in place (one layer-sized temporary at a time)."""
+        if self.gate_up_block == block:
+            return self
+        if self.gate_up_block != 0 or self.inter_local % block:
+            raise ValueError("gate/up rows cannot be interleaved in blocks of %d" % block)
+        for lw in self.layers:
+            two_i, hidden = lw.w_gate_up.shape
+            src = lw.w_gate_up.view(2, two_i // 2 // block, block, hidden).transpose(0, 1)
+            lw.w_gate_up.copy_(src.reshape(two_i, hidden).clone())
+        self.gate_up_block = block
+        return self
+
+    def gate_up_plain(self, lw: "LayerWeights") -> torch.Tensor:
+        """``lw.w_gate_up`` as [gate | up] whatever the stored order (oracles; copies when interleaved)."""
+        b = self.gate_up_block
+        if b == 0:
+            return lw.w_gate_up
+        two_i, hidden = lw.w_gate_up.shape
+        return lw.w_gate_up.view(two_i // 2 // b, 2, b, hidden).transpose(0, 1).reshape(two_i, hidden)
 
     @property
     def heads_local(self) -> int:
@@ -168,6 +192,7 @@ def shard_weights(full: LlamaWeights, tp: int, rank: int) -> LlamaWeights:
     """Rank ``rank``'s shard of single-rank weights (tests compare TP against TP=1 this way)."""
     cfg = full.cfg
     assert full.tp == 1 and cfg.num_kv_heads % tp == 0
+    assert full.gate_up_block == 0, "shard the plain layout, then interleave the shard"
     D = cfg.head_dim
     hq, hkv, inter = cfg.num_heads // tp, cfg.num_kv_heads // tp, cfg.intermediate // tp
     q_end, k_end = cfg.num_heads * D, (cfg.num_heads + cfg.num_kv_heads) * D
@@ -271,7 +296,7 @@ def reference_forward(
         attn = torch.einsum("hts,shd->thd", scores.softmax(-1), v_all).reshape(T, Hq * D)
         h = h + attn @ lw.wo.float().t()
         x = rms_norm(h, lw.post_norm, cfg.rms_eps)
-        gu = x @ lw.w_gate_up.float().t()
+        gu = x @ weights.gate_up_plain(lw).float().t()
         inter = gu.shape[1] // 2
         h = h + (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]) @ lw.w_down.float().t()
     h = rms_norm(h, weights.final_norm, cfg.rms_eps)

@@ -282,18 +282,21 @@ rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* _
   }
 }
 
-// y[t, i] = silu(x[t, i]) * x[t, inter + i]
+// y[t, i] = silu(gate[t, i]) * up[t, i].  x rows are [gate | up] (block = 0), or blocks of `block`
+// gate values followed by the matching up values (the row order the fused GEMM epilogue uses).
 template <typename TIn>
 __global__ void __launch_bounds__(256)
-swiglu_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ y, int64_t T, int inter, int zero_after) {
+swiglu_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ y, int64_t T, int inter, int zero_after, int block) {
   const int64_t total = T * (inter / 8);
   for (int64_t item = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; item < total;
        item += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = item / (inter / 8);
     const int c = (int)(item % (inter / 8)) * 8;
     float g[8], u[8], o[8];
-    Loader<TIn>::load8(x + t * 2 * inter + c, g, zero_after != 0);
-    Loader<TIn>::load8(x + t * 2 * inter + inter + c, u, zero_after != 0);
+    const int gcol = block ? (c / block) * 2 * block + c % block : c;
+    const int ucol = block ? gcol + block : inter + c;
+    Loader<TIn>::load8(x + t * 2 * inter + gcol, g, zero_after != 0);
+    Loader<TIn>::load8(x + t * 2 * inter + ucol, u, zero_after != 0);
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
     store8_bf16(y + t * inter + c, o);
@@ -466,13 +469,14 @@ DASER_API int daser_rope_kv_write(void* qkv, int qkv_is_fp32, int64_t qkv_stride
 }
 
 DASER_API int daser_swiglu(void* x, int x_is_fp32, void* y, int64_t T, int inter, int zero_after,
-                           cudaStream_t stream) {
+                           int block, cudaStream_t stream) {
   using namespace daser;
   if (T < 0 || inter <= 0 || inter % 8) return DASER_ERR_BAD_ARG;
+  if (block < 0 || (block && (block % 8 || inter % block))) return DASER_ERR_BAD_ARG;
   if (T == 0) return 0;
   const int grid = ew_grid(T * (inter / 8), 256);
-  if (x_is_fp32) swiglu_kernel<float><<<grid, 256, 0, stream>>>((float*)x, (__nv_bfloat16*)y, T, inter, zero_after);
-  else swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)x, (__nv_bfloat16*)y, T, inter, 0);
+  if (x_is_fp32) swiglu_kernel<float><<<grid, 256, 0, stream>>>((float*)x, (__nv_bfloat16*)y, T, inter, zero_after, block);
+  else swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)x, (__nv_bfloat16*)y, T, inter, 0, block);
   return (int)cudaGetLastError();
 }
 

@@ -34,6 +34,10 @@
 //                    per-owner arrival counter is bumped (release, system scope) once the
 //                    CTA's contributions are out (one bump per CTA and owner).
 //
+//   EPI_SWIGLU_BF16  the gate/up projection with its activation: the weight rows of every BN-row
+//                    tile are BN/2 gate rows followed by the BN/2 up rows of the same outputs
+//                    (the loader interleaves them), so one CTA holds both halves in TMEM and
+//                    stores silu(gate) * up as bf16 [M, N/2]; k_splits must be 1.
 //   EPI_SPLITK_SCATTER  split-K and the bf16 scatter in one kernel: every K split adds its
 //                    partial tile into a local fp32 work buffer; the CTA that finishes a tile
 //                    last (per-tile counter) reads the sum back, hands the work buffer back
@@ -54,7 +58,7 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;  // 64 bf16 = 128 B = one swizzle row
 constexpr int GEMM_THREADS = 192;
 
-enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1, EPI_SPLITK_SCATTER = 2 };
+enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1, EPI_SPLITK_SCATTER = 2, EPI_SWIGLU_BF16 = 3 };
 
 struct GemmParams {
   int M, N, K;
@@ -241,8 +245,39 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < p.M;
       const int owner = row_ok ? row / p.rows_per_owner : 0;
       const int64_t local_row = row_ok ? row - (int64_t)owner * p.rows_per_owner : 0;
+      if (p.epilogue == EPI_SWIGLU_BF16) {
+        if constexpr (BN >= 64) {
+          // columns [0, BN/2) of the tile are gate, [BN/2, BN) the matching up values
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t g[32], u[32];
+            sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), g);
+            sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(BN / 2 + c * 32), u);
+            sm100::tmem_ld_wait();
+            if (!row_ok) continue;
+            const int col0 = (n0 >> 1) + c * 32;  // output column
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[0]) + (int64_t)row * p.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (2 * (col0 + v * 8) < p.N) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float gv = __uint_as_float(g[v * 8 + i]);
+                  o[i] = gv / (1.f + __expf(-gv)) * __uint_as_float(u[v * 8 + i]);
+                }
+                uint4 w;
+                w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]);
+                w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+                *reinterpret_cast<uint4*>(dst + v * 8) = w;
+              }
+            }
+          }
+        }
+      }
+      const int n_chunks = p.epilogue == EPI_SWIGLU_BF16 ? 0 : BN / 32;  // (the activation epilogue is done)
+#pragma unroll 1
+      for (int c = 0; c < n_chunks; ++c) {
         uint32_t r[32];
         sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
         sm100::tmem_ld_wait();
@@ -455,6 +490,8 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   if (!g || g->M <= 0 || g->N <= 0 || g->K <= 0 || g->k_splits < 1) return DASER_ERR_BAD_ARG;
   if (g->K % 8 || g->N % 8) return DASER_ERR_UNSUPPORTED;
   if (g->epilogue == EPI_STORE_BF16 && g->k_splits != 1) return DASER_ERR_BAD_ARG;
+  if (g->epilogue == EPI_SWIGLU_BF16 &&
+      (g->k_splits != 1 || g->block_n < 64 || g->N % g->block_n || g->n_owners != 1)) return DASER_ERR_BAD_ARG;
   if (g->n_owners < 1 || g->n_owners > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (g->rows_per_owner <= 0 || (int64_t)g->rows_per_owner * g->n_owners < g->M) return DASER_ERR_BAD_ARG;
   if (g->gate_flags && g->gate_rows <= 0) return DASER_ERR_BAD_ARG;

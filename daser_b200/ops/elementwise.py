@@ -121,15 +121,17 @@ def rope_kv_write(
     )
 
 
-def swiglu(x: torch.Tensor, out: Optional[torch.Tensor] = None, zero_after: bool = False) -> torch.Tensor:
-    """``silu(x[:, :I]) * x[:, I:]`` for ``x[T, 2I]`` (bf16 or fp32 accumulators)."""
+def swiglu(x: torch.Tensor, out: Optional[torch.Tensor] = None, zero_after: bool = False,
+           block: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` for ``x[T, 2I]`` (bf16 or fp32 accumulators): ``x = [gate | up]``, or with
+    ``block`` > 0 blocks of ``block`` gate columns followed by the matching up columns."""
     T, two_i = x.shape
     inter = two_i // 2
     if out is None:
         out = torch.empty((T, inter), dtype=torch.bfloat16, device=x.device)
     _lib.check(
         _lib.lib().daser_swiglu(C.c_void_p(x.data_ptr()), _is_f32(x), C.c_void_p(out.data_ptr()),
-                                C.c_int64(T), inter, int(zero_after), _lib.stream_ptr()),
+                                C.c_int64(T), inter, int(zero_after), int(block), _lib.stream_ptr()),
         "swiglu",
     )
     return out

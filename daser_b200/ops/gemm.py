@@ -26,6 +26,8 @@ NUM_SMS = 148
 EPI_STORE_BF16 = 0
 EPI_REDUCE_F32 = 1
 EPI_SPLITK_SCATTER = 2
+EPI_SWIGLU_BF16 = 3
+GATE_UP_BLOCK = 64  # gate/up rows are interleaved in blocks of this many (half of a 128-row tile)
 
 
 def plan_tiles(M: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int]:
@@ -155,3 +157,43 @@ def linear(
         result = out
     _lib.check(_lib.lib().daser_gemm(C.byref(g), _lib.stream_ptr(stream)), "gemm")
     return result
+
+
+def interleave_gate_up(w_gate_up: torch.Tensor, block: int = GATE_UP_BLOCK) -> torch.Tensor:
+    """``[gate rows | up rows]`` -> blocks of ``block`` gate rows followed by the matching up rows.
+
+    With this row order every ``2 * block``-row GEMM tile holds the gate and the up values of
+    the same outputs, which is what lets the activation run in the GEMM epilogue.
+    """
+    two_i, hidden = w_gate_up.shape
+    inter = two_i // 2
+    assert inter % block == 0
+    return (w_gate_up.view(2, inter // block, block, hidden).transpose(0, 1).reshape(two_i, hidden).contiguous())
+
+
+def can_fuse_swiglu(M: int, two_i: int, K: int) -> bool:
+    """True when the gate/up GEMM of this shape runs unsplit with 128-row tiles (one CTA per tile
+    sees the whole K range, so a nonlinearity may follow in the epilogue)."""
+    bn, ks = plan_tiles(M, two_i, K, allow_split=True)
+    return ks == 1 and two_i % 128 == 0
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up_il: torch.Tensor, out: torch.Tensor,
+                  status: Optional[torch.Tensor] = None, gate_flags: Optional[int] = None, gate_target: int = 0,
+                  gate_rows: int = 0, gate_base: Optional[int] = None, stream=None) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` in one kernel; ``w_gate_up_il`` is :func:`interleave_gate_up` order."""
+    assert x.dtype == torch.bfloat16 and w_gate_up_il.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    M, K = x.shape
+    N = w_gate_up_il.shape[0]
+    assert out.shape[0] >= M and out.shape[1] == N // 2 and out.stride(1) == 1
+    g = Gemm()
+    g.a, g.b = x.data_ptr(), w_gate_up_il.data_ptr()
+    g.lda, g.ldb, g.ldc = x.stride(0), w_gate_up_il.stride(0), out.stride(0)
+    g.M, g.N, g.K = M, N, K
+    g.block_n, g.k_splits, g.epilogue = 2 * GATE_UP_BLOCK, 1, EPI_SWIGLU_BF16
+    g.n_owners, g.rows_per_owner = 1, max(M, 1)
+    g.c[0] = out.data_ptr()
+    g.status = status.data_ptr() if status is not None else None
+    g.gate_flags, g.gate_target, g.gate_rows, g.gate_base = gate_flags, gate_target, gate_rows, gate_base
+    _lib.check(_lib.lib().daser_gemm(C.byref(g), _lib.stream_ptr(stream)), "gemm_swiglu")
+    return out

@@ -247,8 +247,8 @@ class TPContext:
                                       runner.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
             self._row_gemm(runner, runner.attn_out[:T], lw.wo, T, rows)
             self._norm_push(runner, self.acc, lw.post_norm, h, rows, wait=True)
-            gu, f32 = self._col_gemm(runner, lw.w_gate_up, runner.gu_acc, runner.gu_bf, T, rows)
-            ew.swiglu(gu, out=runner.act[:T], zero_after=f32)
+            runner.mlp_up(self.gathered[:T], lw, T, gate_flags=self.flag_ptr(self.rank, FLAG_AG),
+                          gate_target=self._ag_off, gate_rows=rows, gate_base=self.epochs.data_ptr() + 4)
             self._row_gemm(runner, runner.act[:T], lw.w_down, T, rows)
             nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             self._norm_push(runner, self.acc, nxt, h, rows, wait=True)
@@ -310,8 +310,7 @@ class TPContext:
                                       runner.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
             self._row_gemm_bcast(runner, runner.attn_out[:T], lw.wo, T, 0, offs)
             self._norm_sum(runner, 0, lw.post_norm, h, normed, T, offs)
-            gu, f32 = runner._linear(normed, lw.w_gate_up, runner.gu_acc, runner.gu_bf)
-            ew.swiglu(gu, out=runner.act[:T], zero_after=f32)
+            runner.mlp_up(normed, lw, T)
             self._row_gemm_bcast(runner, runner.act[:T], lw.w_down, T, 1, offs)
             last = li + 1 == len(w.layers)
             nxt = w.final_norm if last else w.layers[li + 1].input_norm
@@ -342,8 +341,7 @@ class TPContext:
             o, f32 = runner._linear(runner.attn_out[:T], lw.wo, runner.hid_acc, runner.hid_bf)
             dist.all_reduce(o, group=self.group)
             ew.add_rmsnorm(o, lw.post_norm, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
-            gu, f32 = runner._linear(normed, lw.w_gate_up, runner.gu_acc, runner.gu_bf)
-            ew.swiglu(gu, out=runner.act[:T], zero_after=f32)
+            runner.mlp_up(normed, lw, T)
             d, f32 = runner._linear(runner.act[:T], lw.w_down, runner.hid_acc, runner.hid_bf)
             dist.all_reduce(d, group=self.group)
             nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm

@@ -11,11 +11,14 @@ from daser_b200.models.llama import PRESETS, LlamaWeights, TorchPagedKV, referen
 pytestmark = pytest.mark.gpu
 
 
-def test_runner_matches_reference_forward():
+@pytest.mark.parametrize("interleave", [False, True])
+def test_runner_matches_reference_forward(interleave):
     from daser_b200.engine.runner import GpuModelRunner, make_step_inputs
 
     cfg = PRESETS["tiny-gqa"]
     w = LlamaWeights.random(cfg, "cuda", torch.bfloat16, seed=3, std=0.05)
+    if interleave:
+        w.interleave_gate_up_()  # the row order the engine uses (SwiGLU as the GEMM epilogue)
     runner = GpuModelRunner(cfg, w, num_blocks=64, max_tokens=64)
     rng = random.Random(0)
     tokens = [rng.randrange(cfg.vocab_size) for _ in range(40)]
@@ -28,7 +31,8 @@ def test_runner_matches_reference_forward():
     # reference: same weights in fp32 on the CPU, bf16 pool emulated in fp32
     wf = LlamaWeights(cfg, 1, 0, w.embed.float().cpu(),
                       [type(l)(*(t.float().cpu() for t in (l.input_norm, l.wqkv, l.wo, l.post_norm, l.w_gate_up, l.w_down)))
-                       for l in w.layers], w.final_norm.float().cpu(), w.lm_head.float().cpu())
+                       for l in w.layers], w.final_norm.float().cpu(), w.lm_head.float().cpu(),
+                      gate_up_block=w.gate_up_block)
     pool = TorchPagedKV(cfg, 64)
     reference_forward(wf, torch.tensor(tokens[:33]), torch.arange(33), pool, torch.tensor(table), 0, return_logits=False)
     ref = reference_forward(wf, torch.tensor(tokens[33:]), torch.arange(33, 40), pool, torch.tensor(table), 33)
