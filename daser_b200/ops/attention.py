@@ -41,7 +41,7 @@ def plan_splits(num_seqs: int, kv_heads: int, max_q_len: int, group: int, max_ct
         # tcgen05 kernel: the unit is a CTA of 128 query rows, two per SM, 64 keys per tile
         base_items = num_seqs * kv_heads * -(-max_q_len * group // 128)
         want = max(1, (NUM_SMS * 2) // max(base_items, 1))
-        max_splits = max(1, max_ctx // (2 * TC_KEY_TILE))
+        max_splits = max(1, -(-max_ctx // (2 * TC_KEY_TILE)))  # splits of two key tiles at the shortest
         nsplit = max(1, min(want, max_splits, 64))
         if rows > 0:
             nsplit = max(1, min(nsplit, MAX_ROW_SPLITS // rows))
