@@ -75,6 +75,7 @@ class NativeEngineClient:
         self._model = model
         self._pad = pad_token
         self._lock = asyncio.Lock()
+        self._failed: Optional[str] = None  # set once the engine lost a tensor-parallel peer
 
     @property
     def model(self) -> str:
@@ -84,11 +85,23 @@ class NativeEngineClient:
         pass
 
     async def health(self) -> bool:
-        return True
+        """False once a step failed with a lost peer or an invalid device status: the group has
+        to be restarted, `/health` degrades and `/infer` answers 502 until then."""
+        return self._failed is None
+
+    def _guard(self, fn, *args):
+        if self._failed is not None:
+            raise RuntimeError(f"engine unavailable: {self._failed}")
+        try:
+            return fn(*args)
+        except Exception as exc:
+            if type(exc).__name__ == "PeerLost":
+                self._failed = str(exc)
+            raise
 
     async def prefill(self, tokens: list[int]) -> None:
         async with self._lock:
-            await asyncio.get_running_loop().run_in_executor(None, self._engine.store_chunk, list(tokens))
+            await asyncio.get_running_loop().run_in_executor(None, self._guard, self._engine.store_chunk, list(tokens))
 
     def _pad_block(self, tokens: Sequence[int]) -> list[int]:
         bt = self._engine.cfg.block_tokens
@@ -116,7 +129,7 @@ class NativeEngineClient:
             cached, query = [], tokens
         async with self._lock:
             gen, prompt_len = await asyncio.get_running_loop().run_in_executor(
-                None, self._generate, cached, query, max_new)
+                None, self._guard, self._generate, cached, query, max_new)
         return {
             "choices": [{"text": self._detok(gen), "token_ids": gen}],
             "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)},

@@ -155,3 +155,36 @@ def test_native_cpu_engine_serves_infer_with_restored_chunks(tmp_path):
     finally:
         engine.close()
         lp.stop()
+
+
+def test_native_client_degrades_after_a_lost_peer():
+    """A step that ends with PeerLost marks the in-process engine unavailable: health turns false
+    and later calls fail at once instead of launching work that would wait for the dead rank."""
+    import asyncio
+
+    from daser_b200.parallel.health import PeerLost
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    class Engine:
+        class cfg:
+            block_tokens = 16
+
+        calls = 0
+
+        def generate(self, chunks, query, max_new_tokens=1):
+            Engine.calls += 1
+            raise PeerLost([3], "left the group")
+
+    client = NativeEngineClient(Engine(), lambda ids: "")
+
+    async def run():
+        assert await client.health()
+        for _ in range(2):
+            try:
+                await client.completion([1, 2, 3], {"max_tokens": 1})
+            except RuntimeError:
+                pass
+        return await client.health()
+
+    assert asyncio.run(run()) is False
+    assert Engine.calls == 1
