@@ -14,9 +14,10 @@ GPU and the hot path makes no NCCL call:
   normalises its rows and stores them into every rank's gathered-activation buffer (plain
   16-byte peer stores), then bumps a per-source flag on every rank; the TMA producer of the
   next column-parallel GEMM waits for exactly the flags of the rows its tile needs.
-* **steps of few tokens** (the serving case) use the one-shot form instead: the GEMM epilogue
-  writes its partial into every peer's receive buffer and each rank sums and normalises all rows
-  itself: one NVLink hop per sync point, no all-gather (``_forward_body_oneshot``).
+* **steps of few tokens at tp <= 2** use the one-shot form instead: the GEMM epilogue writes its
+  partial into every peer's receive buffer and each rank sums and normalises all rows itself: one
+  NVLink hop per sync point, no all-gather (``_forward_body_oneshot``).  At higher degrees the
+  tp - 1 copies cost more than the second hop saves (measured), so the two-hop form stays.
 * **chunk-KV restore** scatters from the IO rank into every rank's paged pool
   (``ops/csrc/kv_paged.cu``); **save** has every rank compress and push its head slice into
   the IO rank's staging buffer.
@@ -46,6 +47,11 @@ from daser_b200.parallel.health import PeerMonitor
 
 FLAG_RS = 0  # arrival counter of reduce-scattered partials
 FLAG_OS = 1  # and 2: arrival counters of the two one-shot all-reduce receive buffers
+# Largest degree at which "fused" picks the one-shot form for small steps.  Measured on the 70B
+# 64-token step (compute part, ms): tp = 2: one-shot 21.7, two-hop 22.4, NCCL 21.7; tp = 8: one-shot
+# 19.9, two-hop 14.3, NCCL 15.2.  The one-shot epilogue sends tp - 1 copies of every tile; at 8
+# ranks those stores dominate the GEMM's epilogue.
+ONESHOT_MAX_TP = 2
 FLAG_AG = 8  # first of tp per-source "rows landed" flags
 NUM_FLAGS = 16
 
@@ -54,9 +60,9 @@ class TPContext:
     def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256, impl: Optional[str] = None) -> None:
         # "fused": the path this module is about.  "nccl": the unfused arrangement it is measured
         # against (same kernels, replicated activations, NCCL all-reduce after the row-parallel GEMMs).
-        # "twoshot" forces the reduce-scatter / all-gather form at every step size.
+        # "twoshot" / "oneshot" force one form of the fused reduction at every size and degree.
         self.impl = impl or os.environ.get("DASER_TP_IMPL", "fused")
-        if self.impl not in ("fused", "twoshot", "nccl"):
+        if self.impl not in ("fused", "twoshot", "oneshot", "nccl"):
             raise ValueError(f"unknown tensor-parallel implementation {self.impl!r}")
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
@@ -224,7 +230,7 @@ class TPContext:
             raise ValueError("step exceeds the tensor-parallel buffers")
         if self.impl == "nccl":
             return self._forward_body_nccl(runner, inp, nsplit, split_tokens)
-        if self.impl == "fused" and T <= self.os_cap:
+        if self.impl == "oneshot" or (self.impl == "fused" and self.tp <= ONESHOT_MAX_TP and T <= self.os_cap):
             return self._forward_body_oneshot(runner, inp, nsplit, split_tokens)
         self._rs_off = self._ag_off = self._done_off = 0
         D, B = cfg.head_dim, cfg.block_tokens
