@@ -33,16 +33,39 @@ def hash_tokens(tokens: Sequence[int]) -> str:
     return xxhash.xxh3_128(_token_bytes(tokens)).hexdigest()
 
 
+def _native():
+    from daser_b200.server import native_index
+
+    return native_index if native_index.available() else None
+
+
+def block_digests(tokens: Sequence[int], block_tokens: int) -> list[str]:
+    """Digest of every aligned block ``tokens[i * b : (i + 1) * b]`` (anchor candidates of a scan)."""
+    if block_tokens <= 0:
+        raise ValueError("block_tokens must be positive")
+    nat = _native()
+    if nat is not None:
+        return nat.block_digests(tokens, block_tokens)
+    nblocks = len(tokens) // block_tokens
+    raw = memoryview(_token_bytes(tokens[: nblocks * block_tokens]))
+    step = block_tokens * 4
+    return [xxhash.xxh3_128(raw[i * step : (i + 1) * step]).hexdigest() for i in range(nblocks)]
+
+
 def prefix_digests(tokens: Sequence[int], block_tokens: int) -> list[str]:
     """Digests of ``tokens[:b]`` for ``b = block_tokens, 2*block_tokens, ...``.
 
-    Entry ``i`` equals ``hash_tokens(tokens[:(i + 1) * block_tokens])``.
+    Entry ``i`` equals ``hash_tokens(tokens[:(i + 1) * block_tokens])``.  One streaming pass, in
+    the native library when it is built.
     """
     if block_tokens <= 0:
         raise ValueError("block_tokens must be positive")
     nblocks = len(tokens) // block_tokens
     if nblocks == 0:
         return []
+    nat = _native()
+    if nat is not None:
+        return nat.prefix_digests(tokens, block_tokens)
     raw = memoryview(_token_bytes(tokens[: nblocks * block_tokens]))
     step = block_tokens * 4
     state = xxhash.xxh3_128()

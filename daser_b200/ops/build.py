@@ -20,6 +20,8 @@ OPS_SRC = PKG / "ops" / "csrc"
 IO_SRC = PKG / "io" / "csrc"
 OPS_LIB = PKG / "ops" / "libdaser_ops.so"
 IO_LIB = PKG / "io" / "libdaser_io.so"
+INDEX_SRC = PKG / "server" / "csrc"
+INDEX_LIB = PKG / "server" / "libdaser_index.so"
 BUILD_DIR = PKG.parent / "build"
 
 NVCC_FLAGS = [
@@ -105,11 +107,21 @@ def build_io_selftest(sanitize: str = "address,undefined") -> Path:
     return out
 
 
+def build_index(force: bool = False) -> Path:
+    """The control plane's native token index (hashing through the system's libxxhash)."""
+    src = INDEX_SRC / "token_index.cc"
+    if force or _stale(INDEX_LIB, [src]):
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread",
+              "-o", str(INDEX_LIB), str(src), "-ldl"])
+    return INDEX_LIB
+
+
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_io(force=force)
+    build_index(force=force)
     build_ops(verbose=verbose, force=force)
 
 
 if __name__ == "__main__":
     build_all(verbose="-v" in sys.argv, force="--force" in sys.argv)
-    print(OPS_LIB, IO_LIB)
+    print(OPS_LIB, IO_LIB, INDEX_LIB)

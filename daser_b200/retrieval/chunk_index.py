@@ -22,7 +22,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from daser_b200.hashing import hash_tokens
+from daser_b200.hashing import block_digests, hash_tokens
 from daser_b200.retrieval.prefix import PrefixHashIndex
 from daser_b200.server.metadata_store import ChunkMeta
 
@@ -36,8 +36,8 @@ class ChunkHit:
 
 
 class ChunkOffsetIndex(PrefixHashIndex):
-    def __init__(self, block_tokens: int = 16) -> None:
-        super().__init__(block_tokens)
+    def __init__(self, block_tokens: int = 16, native: bool | None = None) -> None:
+        super().__init__(block_tokens, native)
         self._anchors: dict[str, set[str]] = {}
         self._anchor_of: dict[str, str] = {}
 
@@ -61,9 +61,13 @@ class ChunkOffsetIndex(PrefixHashIndex):
         hits: list[ChunkHit] = []
         pos = 0
         n = len(tokens)
+        if not self._anchors:
+            return hits
+        # every aligned block is hashed once, in one pass (native when built)
+        anchors = block_digests(tokens, bt)
         while pos + bt <= n:
             best: ChunkMeta | None = None
-            keys = self._anchors.get(hash_tokens(tokens[pos : pos + bt]))
+            keys = self._anchors.get(anchors[pos // bt])
             if keys:
                 for key in keys:
                     meta = self._by_key.get(key)
