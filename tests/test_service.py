@@ -108,10 +108,13 @@ def test_engine_failures_map_to_502_and_health_degrades(svc):
     client, eng = svc
     eng.up = False
     assert client.get("/health").json() == {"status": "degraded", "vllm": False}
+    text = "".join(chr(97 + (i * 7) % 26) for i in range(100))  # three distinct 32-byte chunks
     eng.fail = True
-    assert client.post("/documents", json={"title": "t", "text": "x" * 100}).status_code == 502
+    assert client.post("/documents", json={"title": "t", "text": text}).status_code == 502
     eng.fail = False
-    doc_id = client.post("/documents", json={"title": "t", "text": "x" * 100}).json()["doc_id"]
+    r = client.post("/documents", json={"title": "t", "text": text})
+    assert r.status_code == 201, r.text
+    doc_id = r.json()["doc_id"]
     eng.fail = True
     assert client.post("/infer", json={"doc_ids": [doc_id], "task": "q"}).status_code == 502
 
