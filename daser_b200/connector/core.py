@@ -433,6 +433,18 @@ class WorkerHalf:
             self._staging = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
         else:
             self._staging = torch.empty(nbytes, dtype=torch.uint8)
+        # Plain host arenas the IO lands in are registered with the ring once (fixed-buffer IO: no
+        # page pinning per read); a refusal (memlock limit) just leaves plain IO in place.
+        # Arenas pinned by the CUDA driver are left alone: they are driver mappings, already
+        # resident, and whether the kernel accepts them for long-term pinning differs by driver.
+        regions = []
+        for arena in (self._staging, host_store.arena if host_store is not None else None):
+            if arena is not None and not arena.is_cuda and not arena.is_pinned():
+                regions.append((arena.data_ptr(), arena.numel()))
+        try:
+            self.registered_regions = self._xfer.engine.register_buffers(regions)
+        except (OSError, AttributeError):
+            self.registered_regions = 0
         self._meta: Optional[ConnectorMeta] = None
         # (part, parts): this worker holds one of `parts` pieces of every chunk (per-rank store
         # files under vLLM tensor parallelism); the server publishes a chunk when all arrived

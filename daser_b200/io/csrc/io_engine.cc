@@ -113,6 +113,13 @@ struct Uring {
     return true;
   }
 
+  // Pin and map `n` buffers once (IORING_REGISTER_BUFFERS): fixed reads / writes into them skip
+  // the per-IO page lookup.  One registration per ring; returns 0 or -errno.
+  int register_buffers(const iovec* iov, unsigned n) {
+    const long r = syscall(__NR_io_uring_register, fd, IORING_REGISTER_BUFFERS, iov, n);
+    return r < 0 ? -errno : 0;
+  }
+
   void teardown() {
     if (sq_ring != MAP_FAILED) munmap(sq_ring, sq_ring_sz);
     if (cq_ring != MAP_FAILED) munmap(cq_ring, cq_ring_sz);
@@ -124,7 +131,7 @@ struct Uring {
   }
 
   // Caller holds the submit lock and has checked that a slot is free.
-  bool push(int opcode, int file_fd, void* buf, unsigned len, int64_t off, uint64_t user_data) {
+  bool push(int opcode, int file_fd, void* buf, unsigned len, int64_t off, uint64_t user_data, int buf_index = -1) {
     const unsigned tail = *sq_tail;
     const unsigned idx = tail & *sq_mask;
     io_uring_sqe* e = &sqes[idx];
@@ -135,6 +142,7 @@ struct Uring {
     e->len = len;
     e->off = (uint64_t)off;
     e->user_data = user_data;
+    if (buf_index >= 0) e->buf_index = (uint16_t)buf_index;  // READ_FIXED / WRITE_FIXED
     sq_array[idx] = idx;
     __atomic_store_n(sq_tail, tail + 1, __ATOMIC_RELEASE);
     for (;;) {
@@ -172,6 +180,9 @@ struct daser_io {
   std::deque<Piece*> backlog;
   unsigned inflight = 0;
   unsigned depth = 64;
+  struct Region { uintptr_t base; size_t len; int index; };
+  std::vector<Region> fixed;  // registered buffers (written once, before any IO that uses them)
+  std::atomic<int64_t> st_fixed{0};
   std::condition_variable_any ring_idle_cv;  // signalled when inflight and backlog both reach zero
   std::thread reaper;
 
@@ -269,12 +280,22 @@ struct daser_io {
 
   // ---- io_uring -----------------------------------------------------------------------------------
   // ring_mu held.
+  int fixed_index(const Piece& p) const {
+    const uintptr_t a = (uintptr_t)p.buf;
+    for (const Region& r : fixed)
+      if (a >= r.base && a + (size_t)p.len <= r.base + r.len) return r.index;
+    return -1;
+  }
+
   void ring_submit_locked(Piece* p) {
     const bool direct = direct_ok(*p);
     if (direct) st_direct++;
     const unsigned len = (unsigned)p->len;
-    if (!ring.push(p->write ? IORING_OP_WRITE : IORING_OP_READ, direct ? fd_direct : fd, p->buf, len, p->off,
-                   (uint64_t)(uintptr_t)p)) {
+    const int bi = fixed_index(*p);
+    if (bi >= 0) st_fixed++;
+    const int op = bi >= 0 ? (p->write ? IORING_OP_WRITE_FIXED : IORING_OP_READ_FIXED)
+                           : (p->write ? IORING_OP_WRITE : IORING_OP_READ);
+    if (!ring.push(op, direct ? fd_direct : fd, p->buf, len, p->off, (uint64_t)(uintptr_t)p, bi)) {
       const int e = errno ? errno : EIO;
       finish(p->ticket, -e);
       delete p;
@@ -418,6 +439,35 @@ daser_io* daser_io_open(const char* path, int backend, int want_device, int queu
 }
 
 int daser_io_backend(const daser_io* io) { return io ? io->backend : -1; }
+
+// Register host buffers with the ring (io_uring backend only; call once, before IO into them).
+// Buffers larger than 1 GiB are registered as consecutive 1 GiB regions.  Returns the number
+// of regions registered, 0 when the backend has no use for it, or -errno (the engine keeps
+// working with plain reads and writes in that case).
+int64_t daser_io_register_buffers(daser_io* io, void* const* bufs, const int64_t* lens, int n) {
+  if (!io || n < 0 || (n && (!bufs || !lens))) return -EINVAL;
+  if (io->backend != DASER_IO_URING) return 0;
+  std::lock_guard<std::mutex> g(io->ring_mu);
+  if (!io->fixed.empty()) return -EBUSY;
+  const size_t kMax = (size_t)1 << 30;
+  std::vector<iovec> iov;
+  for (int i = 0; i < n; ++i) {
+    if (!bufs[i] || lens[i] <= 0) return -EINVAL;
+    for (size_t off = 0; off < (size_t)lens[i]; off += kMax) {
+      iovec v;
+      v.iov_base = (char*)bufs[i] + off;
+      v.iov_len = (size_t)lens[i] - off < kMax ? (size_t)lens[i] - off : kMax;
+      iov.push_back(v);
+    }
+  }
+  if (iov.empty()) return 0;
+  if (iov.size() > 1024) return -E2BIG;
+  const int rc = io->ring.register_buffers(iov.data(), (unsigned)iov.size());
+  if (rc != 0) return rc;
+  for (size_t i = 0; i < iov.size(); ++i)
+    io->fixed.push_back({(uintptr_t)iov[i].iov_base, iov[i].iov_len, (int)i});
+  return (int64_t)iov.size();
+}
 int64_t daser_io_file_size(const daser_io* io) { return io ? io->file_size : -1; }
 
 int64_t daser_io_submit(daser_io* io, int is_write, void* buf, int device, int64_t file_offset, int64_t nbytes) {
@@ -510,6 +560,8 @@ void daser_io_inject(daser_io* io, int count, int err_no, int64_t short_bytes) {
   io->inject_short = short_bytes;
   io->inject_count = count;
 }
+
+int64_t daser_io_fixed_pieces(const daser_io* io) { return io ? io->st_fixed.load() : 0; }
 
 void daser_io_stats(const daser_io* io, int64_t out[5]) {
   out[0] = io->st_pieces;

@@ -40,6 +40,14 @@ typedef struct daser_io daser_io;
 DASER_IO_API daser_io* daser_io_open(const char* path, int backend, int want_device, int queue_depth,
                                      int nthreads, char* err, int err_len, int* err_no);
 DASER_IO_API int daser_io_backend(const daser_io* io);
+
+/* Register host buffers with the io_uring ring so that IO into them uses READ_FIXED /
+ * WRITE_FIXED (no per-IO page pinning).  Call once, before IO into the buffers; buffers above
+ * 1 GiB are split.  Returns the number of regions, 0 on other backends, or -errno (plain IO
+ * keeps working). */
+DASER_IO_API int64_t daser_io_register_buffers(daser_io* io, void* const* bufs, const int64_t* lens, int n);
+/* Pieces submitted as fixed-buffer operations so far. */
+DASER_IO_API int64_t daser_io_fixed_pieces(const daser_io* io);
 DASER_IO_API int64_t daser_io_file_size(const daser_io* io);
 
 // `device` != 0: buf is a CUDA device pointer (GDS backend only).

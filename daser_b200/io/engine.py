@@ -6,7 +6,7 @@ import ctypes as C
 import enum
 import os
 from pathlib import Path
-from typing import Optional
+from typing import Optional, Sequence
 
 _LIB_PATH = Path(__file__).resolve().parent / "libdaser_io.so"
 _lib: Optional[C.CDLL] = None
@@ -44,6 +44,10 @@ def lib() -> C.CDLL:
         L.daser_io_preallocate.argtypes = [C.c_char_p, C.c_int64]
         L.daser_io_inject.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64]
         L.daser_io_stats.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]
+        L.daser_io_register_buffers.restype = C.c_int64
+        L.daser_io_register_buffers.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int64), C.c_int]
+        L.daser_io_fixed_pieces.restype = C.c_int64
+        L.daser_io_fixed_pieces.argtypes = [C.c_void_p]
         _lib = L
     return _lib
 
@@ -104,10 +108,25 @@ class IOEngine:
     def inject_fault(self, count: int, err_no: int = 0, short_bytes: int = -1) -> None:
         lib().daser_io_inject(self._h, count, err_no, short_bytes)
 
+    def register_buffers(self, regions: Sequence[tuple[int, int]]) -> int:
+        """Register host buffers ``(address, bytes)`` with the io_uring ring: IO into them then
+        runs as fixed-buffer operations (no page pinning per IO).  Once per engine, before IO into
+        them.  Returns the number of registered regions; 0 on other backends or when the kernel
+        refuses (memlock limit, too many regions): plain IO keeps working either way."""
+        regions = [(p, n) for p, n in regions if p and n > 0]
+        if not regions:
+            return 0
+        ptrs = (C.c_void_p * len(regions))(*[p for p, _ in regions])
+        lens = (C.c_int64 * len(regions))(*[n for _, n in regions])
+        rc = int(lib().daser_io_register_buffers(self._h, ptrs, lens, len(regions)))
+        return max(rc, 0)
+
     def stats(self) -> dict[str, int]:
         out = (C.c_int64 * 5)()
         lib().daser_io_stats(self._h, out)
-        return dict(zip(("pieces", "bytes_read", "bytes_written", "resubmits", "direct_pieces"), out))
+        d = dict(zip(("pieces", "bytes_read", "bytes_written", "resubmits", "direct_pieces"), out))
+        d["fixed_pieces"] = int(lib().daser_io_fixed_pieces(self._h))
+        return d
 
     def close(self) -> None:
         if self._h is not None:

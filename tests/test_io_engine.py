@@ -122,3 +122,43 @@ def test_device_buffers_rejected_on_host_backends(store):
         with pytest.raises(OSError) as ei:
             io.submit_read(buf.ctypes.data, 0, 4096, device=True)
         assert ei.value.errno == errno.ENOTSUP
+
+
+def test_registered_buffers_use_fixed_operations(tmp_path):
+    """IO into a registered region goes out as READ_FIXED / WRITE_FIXED; IO that leaves the region
+    falls back to plain operations; the data is the same either way."""
+    import ctypes
+
+    import torch
+
+    path = str(tmp_path / "fixed.store")
+    preallocate(path, 16 << 20)
+    buf = torch.empty(9 << 20, dtype=torch.uint8)
+    base = (buf.data_ptr() + 4095) // 4096 * 4096
+    try:
+        eng = IOEngine(path, IOBackend.IO_URING)
+    except OSError:
+        pytest.skip("io_uring unavailable")
+    with eng:
+        n = eng.register_buffers([(base, 4 << 20)])
+        if n == 0:
+            pytest.skip("the kernel refused to register buffers (memlock limit)")
+        assert n == 1
+        assert eng.register_buffers([(base, 4096)]) == 0  # one registration per ring
+        src = (ctypes.c_uint8 * (4 << 20)).from_address(base)
+        for i in range(0, 4 << 20, 997):
+            src[i] = i % 251
+        eng.wait(eng.submit_write(base, 0, 4 << 20))           # inside the region: fixed
+        fixed_after_write = eng.stats()["fixed_pieces"]
+        assert fixed_after_write >= 1
+        out = base + (4 << 20)                                  # outside the region: plain
+        eng.wait(eng.submit_read(out, 0, 4 << 20))
+        assert eng.stats()["fixed_pieces"] == fixed_after_write
+        dst = (ctypes.c_uint8 * (4 << 20)).from_address(out)
+        assert all(dst[i] == src[i] for i in range(0, 4 << 20, 997))
+        eng.wait(eng.submit_read(base + (3 << 20), 1 << 20, 2 << 20))  # crosses the region's end: plain
+        assert eng.stats()["fixed_pieces"] == fixed_after_write
+        eng.inject_fault(1, 0, 4096)                            # a short fixed read is resubmitted inside the region
+        eng.wait(eng.submit_read(base, 0, 1 << 20))
+        st = eng.stats()
+        assert st["fixed_pieces"] > fixed_after_write and st["resubmits"] >= 1
