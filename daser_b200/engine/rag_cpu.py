@@ -14,7 +14,7 @@ only lookup matches whole prompt prefixes, and nothing applies ``pos_offset``
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 

@@ -26,7 +26,7 @@ import torch
 from daser_b200 import metrics
 from daser_b200.connector.core import ConnectorMeta, CudaKVBackend, SchedulerHalf, WorkerHalf
 from daser_b200.engine.rag_cpu import BlockAllocator
-from daser_b200.engine.runner import GpuModelRunner, make_step_inputs
+from daser_b200.engine.runner import GpuModelRunner
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.hbm_store import HBMStore
 from daser_b200.models.llama import LlamaConfig, LlamaWeights

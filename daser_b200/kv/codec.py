@@ -18,7 +18,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from daser_b200.config import CODEC_FP8B16, CODEC_RAW, FP8_GROUP
+from daser_b200.config import CODEC_RAW, FP8_GROUP
 from daser_b200.kv.layout import KVGeometry
 
 E4M3_MAX = 448.0

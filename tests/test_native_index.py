@@ -9,7 +9,6 @@ import xxhash
 
 from daser_b200 import hashing
 from daser_b200.retrieval.chunk_index import ChunkOffsetIndex
-from daser_b200.retrieval.prefix import PrefixHashIndex
 from daser_b200.server import native_index
 from daser_b200.server.metadata_store import ChunkMeta
 

@@ -11,7 +11,6 @@ import subprocess
 import sys
 import time
 
-import pytest
 
 from daser_b200.connector.ipc_client import IPCClientSync
 from daser_b200.hashing import hash_tokens
