@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+import os
 import signal
 from typing import Optional, Sequence
 
@@ -65,6 +66,50 @@ def _build_daser_config(args: argparse.Namespace) -> DaserConfig:
     )
 
 
+def _world() -> tuple[int, int]:
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+_TP_CTX = None
+
+
+def _tp_context(mcfg):
+    """The tensor-parallel context when the service was started under torchrun with several
+    ranks (one per GPU); None for a single process."""
+    global _TP_CTX
+    rank, world = _world()
+    if world <= 1:
+        return None
+    if _TP_CTX is None:
+        import torch
+        import torch.distributed as dist
+
+        from daser_b200.parallel.tp import TPContext
+
+        local = int(os.environ.get("LOCAL_RANK", str(rank)))
+        torch.cuda.set_device(local)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        _TP_CTX = TPContext(mcfg, dist.group.WORLD, max_tokens=256)
+    return _TP_CTX
+
+
+def _run_follower(args: argparse.Namespace) -> None:
+    """Ranks above 0: build the same engine shard and replay the leader's calls until told to stop."""
+    from daser_b200.engine.rag_gpu import GpuRagEngine
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.tp_serving import follower_loop
+
+    cfg = _build_daser_config(args)
+    mcfg = PRESETS[args.native_model]
+    tp_ctx = _tp_context(mcfg)
+    tp_ctx.barrier()  # the leader's control plane is up
+    engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
+                          hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx)
+    steps = follower_loop(engine, tp_ctx.broadcast_object)
+    logger.info("[SERVICE] follower rank %d leaves after %d engine calls", tp_ctx.rank, steps)
+
+
 def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
     from daser_b200.models.llama import PRESETS
     from daser_b200.service.vllm_client import NativeEngineClient
@@ -73,8 +118,14 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
     if args.native_device == "cuda":
         from daser_b200.engine.rag_gpu import GpuRagEngine
 
+        tp_ctx = _tp_context(mcfg)
         engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
-                              hbm_slots=min(cfg.total_slots, 4096))
+                              hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx)
+        if tp_ctx is not None:
+            from daser_b200.service.tp_serving import TPLeaderEngine
+
+            # rank 0 leads: every engine call is announced to the followers first
+            engine = TPLeaderEngine(engine, tp_ctx.broadcast_object)
     else:
         from daser_b200.engine.rag_cpu import CpuRagEngine
 
@@ -99,6 +150,10 @@ async def _run(args: argparse.Namespace) -> None:
     plane = ControlPlane(cfg)
     await plane.start()
     if args.engine == "native":
+        if args.native_device == "cuda" and _world()[1] > 1:
+            from daser_b200.models.llama import PRESETS as _P
+
+            _tp_context(_P[args.native_model]).barrier()  # followers may connect to the control plane now
         engine_client, engine = _native_engine(args, cfg, tokenizer)
     app = build_service_app(
         ServiceConfig(vllm_base_url=args.vllm_base_url or "", model=args.model or args.native_model,
@@ -123,7 +178,14 @@ async def _run(args: argparse.Namespace) -> None:
 
 
 def main(argv: Optional[Sequence[str]] = None) -> None:
-    asyncio.run(_run(_parse_args(argv)))
+    args = _parse_args(argv)
+    rank, world = _world()
+    if world > 1 and rank > 0:
+        if args.engine != "native" or args.native_device != "cuda":
+            return  # nothing to do on extra ranks of a single-process configuration
+        _run_follower(args)
+        return
+    asyncio.run(_run(args))
 
 
 if __name__ == "__main__":

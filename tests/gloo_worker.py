@@ -10,6 +10,9 @@ Scenarios, chosen by ``argv[1]``; RANK / WORLD_SIZE / MASTER_PORT come from the 
 ``health``  three ranks with a :class:`PeerMonitor`: rank 2 leaves in an orderly way after
             step 1, rank 1 exits without a word after step 2; rank 0 must learn of both on the
             host, before its next step.
+``serve``   the leader / follower layer that puts a tensor-parallel engine behind one HTTP front
+            end: rank 0 announces every engine call, the other ranks replay it; all ranks must
+            have executed the same calls with the same arguments, in the same order.
 ``late``    rank 0 alone of a two-rank world: the rendezvous must end with an error inside
             its time limit instead of waiting for ever.
 """
@@ -179,6 +182,57 @@ def scenario_health() -> int:
     return 0
 
 
+def scenario_serve() -> int:
+    from daser_b200.service.tp_serving import TPLeaderEngine, follower_loop
+
+    rank, world = _init()
+
+    class Engine:
+        class cfg:
+            block_tokens = 16
+
+        def __init__(self):
+            self.calls = []
+
+        def store_chunk(self, tokens):
+            self.calls.append(("store", tuple(tokens)))
+            return "key"
+
+        def generate(self, chunks, query, max_new_tokens=1, **kw):
+            self.calls.append(("generate", tuple(map(tuple, chunks)), tuple(query), max_new_tokens, tuple(sorted(kw.items()))))
+            return len(self.calls)
+
+        def warm_up(self, *a, **kw):
+            self.calls.append(("warm_up", a, tuple(sorted(kw.items()))))
+
+        def close(self):
+            self.calls.append(("close",))
+
+    eng = Engine()
+    if rank == 0:
+        lead = TPLeaderEngine(eng, _bcast)
+        lead.warm_up(token_counts=(64,))
+        assert lead.store_chunk(range(32)) == "key"
+        lead.generate([list(range(16)), list(range(16, 48))], [1, 2, 3], max_new_tokens=4)
+        lead.generate([], [9], max_new_tokens=1, store_misses=True)
+        lead.close()
+        try:
+            lead.store_chunk([1] * 16)
+            refused = False
+        except RuntimeError:
+            refused = True
+    else:
+        steps = follower_loop(eng, _bcast)
+        refused = steps == 4
+    logs = [None] * world
+    dist.all_gather_object(logs, (eng.calls, refused))
+    good = all(log == logs[0][0] for log, _ in logs) and all(r for _, r in logs) and len(logs[0][0]) == 5
+    if rank == 0:
+        print("SERVE_OK" if good else f"SERVE_FAIL {logs}", flush=True)
+    dist.destroy_process_group()
+    return 0 if good else 1
+
+
 def scenario_late() -> int:
     t0 = time.time()
     try:
@@ -191,4 +245,5 @@ def scenario_late() -> int:
 
 
 if __name__ == "__main__":
-    sys.exit({"parts": scenario_parts, "health": scenario_health, "late": scenario_late}[sys.argv[1]]())
+    sys.exit({"parts": scenario_parts, "health": scenario_health, "serve": scenario_serve,
+              "late": scenario_late}[sys.argv[1]]())

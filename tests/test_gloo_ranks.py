@@ -47,6 +47,12 @@ def test_peer_that_leaves_and_peer_that_dies_are_noticed_between_steps():
     assert "HEALTH_OK" in outs[0][1]
 
 
+def test_followers_replay_the_leaders_engine_calls():
+    outs = _launch("serve", 3)
+    assert all(rc == 0 for rc, _ in outs), "\n".join(o[-2000:] for _, o in outs)
+    assert "SERVE_OK" in outs[0][1]
+
+
 def test_rank_missing_at_rendezvous_fails_within_the_time_limit():
     outs = _launch("late", 2, ranks=[0], timeout=60)
     assert outs[0][0] == 7, outs[0][1][-2000:]
