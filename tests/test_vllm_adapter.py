@@ -120,3 +120,22 @@ def test_partial_commits_publish_only_when_every_rank_arrived(tmp_path):
         c.close()
     finally:
         lp.stop()
+
+
+def test_vllm_factory_resolves_the_connector_by_module_path():
+    """What `vllm serve --kv-transfer-config '{"kv_connector": "DaserConnector",
+    "kv_connector_module_path": "daser_b200.connector.daser_connector", ...}'` does first."""
+    pytest.importorskip("vllm")
+    from vllm.config import KVTransferConfig
+    from vllm.distributed.kv_transfer.kv_connector.factory import KVConnectorFactory
+    from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorBase_V1
+
+    from daser_b200.connector.daser_connector import DaserConnector
+
+    ktc = KVTransferConfig(kv_connector="DaserConnector", kv_role="kv_both",
+                           kv_connector_module_path="daser_b200.connector.daser_connector",
+                           kv_connector_extra_config={"socket_path": "/tmp/x.sock", "block_tokens": 16})
+    cls = KVConnectorFactory.get_connector_class(ktc)
+    assert cls is DaserConnector and issubclass(cls, KVConnectorBase_V1)
+    # every abstract hook of the installed vLLM's base class is implemented
+    assert not getattr(cls, "__abstractmethods__", None)
