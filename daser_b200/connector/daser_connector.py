@@ -19,7 +19,8 @@ Differences from the reference adapter:
   ``kv[:, block_id]`` and breaks on the FlashInfer layout that compute capability 10.x selects.
 * Additional extra-config keys: ``codec`` (``raw`` keeps the reference's container byte for
   byte, ``fp8b16`` compresses), ``io_backend``, ``hbm_slots``, ``host_slots``.
-* Hooks the reference leaves at their defaults are implemented: ``get_block_ids_with_load_errors``,
+* Hooks the reference leaves at their defaults are implemented: ``register_cross_layers_kv_cache``,
+  ``reset_cache``, ``get_block_ids_with_load_errors``,
   ``get_kv_connector_stats``, ``prefer_cross_layer_blocks``.
 * Tensor parallel workers each keep their own store file (``<store_path>.tp<rank>``) holding
   their head slice, and a chunk becomes visible only after every rank has committed its part.
@@ -185,6 +186,22 @@ class DaserConnector(KVConnectorBase_V1):
         return False, None
 
     # ------------------------------------------------------------------ worker role
+    def register_cross_layers_kv_cache(self, kv_cache: torch.Tensor, attn_backend: Any) -> None:
+        """vLLM's answer to ``prefer_cross_layer_blocks``: ONE tensor for all layers, handed over
+        in its physical dimension order (FlashAttention: ``(blocks, layers, 2, block, heads, dim)``
+        for the NHD layout, ``(blocks, heads, layers, 2, block, dim)`` for HND).  vLLM calls this
+        INSTEAD of :meth:`register_kv_caches`.  The backend's stride order turns it back into
+        per-layer views (strides kept), which is what the stride-driven registration consumes;
+        with the NHD order a block's slot image is one contiguous run of the tensor."""
+        try:
+            order = tuple(attn_backend.get_kv_cache_stride_order(include_num_layers_dimension=True))
+        except (AttributeError, NotImplementedError, TypeError):
+            order = tuple(range(kv_cache.dim()))
+        if sorted(order) != list(range(kv_cache.dim())):
+            raise ValueError(f"stride order {order} does not match a {kv_cache.dim()}-D KV tensor")
+        logical = kv_cache.permute(*[order.index(i) for i in range(len(order))])  # (layers, per-layer shape)
+        self.register_kv_caches({f"layer.{i}": logical[i] for i in range(logical.shape[0])})
+
     def register_kv_caches(self, kv_caches: dict[str, torch.Tensor]) -> None:
         info = describe_kv_caches(kv_caches)
         first = kv_caches[info["names"][0]]
@@ -252,6 +269,15 @@ class DaserConnector(KVConnectorBase_V1):
 
     def get_block_ids_with_load_errors(self) -> set[int]:
         return self._worker.take_load_errors() if self._worker is not None else set()
+
+    def reset_cache(self) -> bool:
+        """Drop what this connector caches itself (the HBM and pinned-host tiers).  The store file
+        and the control plane's index are shared with other engines and are left alone."""
+        if self._worker is not None:
+            for tier in (self._worker.hbm, self._worker.host):
+                if tier is not None:
+                    tier.clear()
+        return True
 
     def get_kv_connector_stats(self) -> Any:
         return None  # counters are served by get_stats(); vLLM's stats object is optional

@@ -101,6 +101,16 @@ class HBMStore:
         metrics.inc(f"{self.kind}.evictions")
         return True
 
+    def clear(self) -> int:
+        """Forget every entry (the arena stays allocated); returns how many there were."""
+        n = len(self._chunks)
+        self._chunks.clear()
+        self._protected.clear()
+        self._free = [(0, self.capacity)]
+        if n:
+            metrics.inc(f"{self.kind}.evictions", n)
+        return n
+
     def reserve(self, key: str, nbytes: int) -> Optional[int]:
         """Claim room for ``key`` and return the arena byte offset to fill (None if it cannot fit
         without evicting an entry that the current step still reads)."""

@@ -49,3 +49,18 @@ def test_entries_used_by_the_current_step_are_not_evicted():
     assert s.reserve("d", 32) is None  # would need 'a' or 'c', both in use by this step
     s.end_step()
     assert s.reserve("d", 32) is not None
+
+
+def test_clear_forgets_everything_and_frees_the_arena():
+    import torch
+
+    from daser_b200.kv.hbm_store import HBMStore
+
+    tier = HBMStore(64, 8, torch.device("cpu"))
+    src = torch.arange(64 * 8, dtype=torch.uint8)
+    for i in range(4):
+        assert tier.admit(f"k{i}", src, 0, 128)
+    assert tier.used_slots == 8 and len(tier) == 4
+    assert tier.clear() == 4
+    assert len(tier) == 0 and tier.used_slots == 0 and tier.lookup("k0") is None
+    assert tier.reserve("big", 64 * 8) == 0  # the whole arena is one free run again

@@ -139,3 +139,78 @@ def test_vllm_factory_resolves_the_connector_by_module_path():
     assert cls is DaserConnector and issubclass(cls, KVConnectorBase_V1)
     # every abstract hook of the installed vLLM's base class is implemented
     assert not getattr(cls, "__abstractmethods__", None)
+
+
+class _FlashAttnLike:
+    """The stride-order hook of vLLM's FlashAttention backend (per-layer shape (2, N, T, H, D))."""
+
+    order = (2, 0, 1, 3, 4, 5)  # NHD: physical (blocks, layers, 2, block, heads, dim)
+
+    @classmethod
+    def get_kv_cache_stride_order(cls, include_num_layers_dimension=False):
+        assert include_num_layers_dimension
+        return cls.order
+
+
+class _FlashAttnLikeHND(_FlashAttnLike):
+    order = (2, 4, 0, 1, 3, 5)  # HND: physical (blocks, heads, layers, 2, block, dim)
+
+
+@pytest.mark.parametrize("backend", [_FlashAttnLike, _FlashAttnLikeHND])
+def test_cross_layer_tensor_registration_store_and_load(tmp_path, backend):
+    """vLLM answers prefer_cross_layer_blocks with ONE tensor in physical order and calls
+    register_cross_layers_kv_cache instead of register_kv_caches."""
+    from daser_b200.connector.daser_connector import DaserConnector
+    from vllm.distributed.kv_transfer.kv_connector.v1.base import KVConnectorRole
+
+    slot = L * 2 * B * H * D * 2
+    lp = LiveControlPlane(tmp_path, total_slots=32, slot_size=slot).start()
+    cfg = _vllm_config(lp)
+    sched = DaserConnector(cfg, KVConnectorRole.SCHEDULER)
+
+    def physical(seed):
+        g = torch.Generator().manual_seed(seed)
+        logical_shape = (L, 2, NB, B, H, D)
+        phys_shape = tuple(logical_shape[i] for i in backend.order)
+        return torch.randn(phys_shape, generator=g).to(torch.bfloat16)
+
+    def logical(t):  # (L, 2, N, T, H, D) view of the physical tensor
+        return t.permute(*[backend.order.index(i) for i in range(6)])
+
+    worker = DaserConnector(cfg, KVConnectorRole.WORKER)
+    worker2 = DaserConnector(cfg, KVConnectorRole.WORKER)
+    try:
+        assert worker.prefer_cross_layer_blocks
+        cache1 = physical(1)
+        worker.register_cross_layers_kv_cache(cache1, backend)
+        tokens = list(range(200, 200 + 48))
+        req = _request("r1", tokens + [5])
+        assert sched.get_num_new_matched_tokens(req, 0) == (0, False)
+        sched.update_state_after_alloc(req, _blocks([7, 2, 9, 4]), 0)
+        meta = sched.build_connector_meta(SimpleNamespace(num_scheduled_tokens={"r1": 49}))
+        worker.bind_connector_metadata(meta)
+        worker.start_load_kv(None)
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+        sched.request_finished(req, [7, 2, 9, 4])
+
+        cache2 = physical(2)
+        before = cache2.clone()
+        worker2.register_cross_layers_kv_cache(cache2, backend)
+        req2 = _request("r2", tokens + [1, 2, 3])
+        assert sched.get_num_new_matched_tokens(req2, 0) == (48, False)
+        sched.update_state_after_alloc(req2, _blocks([1, 5, 3, 8]), 48)
+        meta2 = sched.build_connector_meta(SimpleNamespace(num_scheduled_tokens={"r2": 3}))
+        worker2.bind_connector_metadata(meta2)
+        worker2.start_load_kv(None)
+        worker2.clear_connector_metadata()
+        assert worker2.get_block_ids_with_load_errors() == set()
+        for src, dst in zip([7, 2, 9], [1, 5, 3]):
+            assert torch.equal(logical(cache2)[:, :, dst], logical(cache1)[:, :, src])
+        assert torch.equal(logical(cache2)[:, :, 8], logical(before)[:, :, 8])
+        assert worker2.reset_cache() is True
+    finally:
+        worker.shutdown()
+        worker2.shutdown()
+        sched.shutdown()
+        lp.stop()
