@@ -1,5 +1,6 @@
 """HBM tier bookkeeping (runs on CPU memory: the arena is just a tensor)."""
 
+import pytest
 import torch
 
 from daser_b200.kv.hbm_store import HBMStore
@@ -64,3 +65,78 @@ def test_clear_forgets_everything_and_frees_the_arena():
     assert tier.clear() == 4
     assert len(tier) == 0 and tier.used_slots == 0 and tier.lookup("k0") is None
     assert tier.reserve("big", 64 * 8) == 0  # the whole arena is one free run again
+
+
+def test_tier_invariants_under_random_operations():
+    """Random reserve / admit / lookup / evict / end_step sequences: entries never overlap, free
+    runs and entries tile the arena exactly, and nothing looked up in the current step is evicted."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    import torch
+
+    from daser_b200.kv.hbm_store import HBMStore
+
+    CAP, SLOT = 16, 32
+    op = st.one_of(
+        st.tuples(st.just("reserve"), st.integers(0, 11), st.integers(1, 6)),
+        st.tuples(st.just("admit"), st.integers(0, 11), st.integers(1, 6)),
+        st.tuples(st.just("lookup"), st.integers(0, 11)),
+        st.tuples(st.just("evict"), st.integers(0, 11)),
+        st.tuples(st.just("end_step")),
+        st.tuples(st.just("clear")),
+    )
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(op, min_size=1, max_size=80))
+    def run(sequence):
+        tier = HBMStore(SLOT, CAP, torch.device("cpu"))
+        src = torch.arange(SLOT * CAP, dtype=torch.int64).to(torch.uint8)
+        pinned_this_step: set[str] = set()
+        sizes: dict[str, int] = {}
+        for o in sequence:
+            kind = o[0]
+            if kind in ("reserve", "admit"):
+                key, n = f"k{o[1]}", o[2]
+                n = sizes.get(key, n) if key in tier else n
+                if kind == "reserve":
+                    off = tier.reserve(key, n * SLOT)
+                    ok = off is not None
+                else:
+                    ok = tier.admit(key, src, 0, n * SLOT)
+                if ok:
+                    sizes[key] = n
+                    pinned_this_step.add(key)
+                    assert key in tier
+            elif kind == "lookup":
+                key = f"k{o[1]}"
+                ptr = tier.lookup(key)
+                assert (ptr is not None) == (key in tier)
+                if ptr is not None:
+                    pinned_this_step.add(key)
+                    assert (ptr - tier.arena.data_ptr()) % SLOT == 0
+            elif kind == "evict":
+                key = f"k{o[1]}"
+                had = key in tier
+                assert tier.evict(key) == had
+                pinned_this_step.discard(key)
+            elif kind == "end_step":
+                tier.end_step()
+                pinned_this_step.clear()
+            else:
+                tier.clear()
+                pinned_this_step.clear()
+            # whatever was touched in this step is still there
+            for key in pinned_this_step:
+                assert key in tier, (key, sequence)
+            # entries and free runs tile the arena exactly once
+            spans = sorted([(f, n) for f, n in tier._chunks.values()] + list(tier._free))
+            pos = 0
+            for first, n in spans:
+                assert first == pos and n > 0
+                pos += n
+            assert pos == CAP
+            assert tier.used_slots == sum(n for _, n in tier._chunks.values()) <= CAP
+
+    run()
