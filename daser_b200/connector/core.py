@@ -107,6 +107,7 @@ class SchedulerHalf:
         self._pending_stores: dict[str, ReqStoreSpec] = {}
         self._pending_alloc: dict[str, dict[str, Any]] = {}
         self._stored: set[str] = set()
+        self._negotiated = False
 
     # -- prefix reuse (reference behaviour) -----------------------------------------------
     def get_num_new_matched_tokens(self, req_id: str, prompt_token_ids: Sequence[int],
@@ -123,6 +124,10 @@ class SchedulerHalf:
         if aligned == 0:
             return 0, False
         store_key = hash_tokens(tokens[:aligned])
+        if not self._negotiated:  # once the server answers: packed token ids if it takes them
+            self._negotiated = True
+            if hasattr(self._ipc, "negotiate"):
+                self._ipc.negotiate()
         t0 = time.perf_counter()
         try:
             with trace.span("rpc.match_and_alloc", "connector", req=req_id, tokens=len(tokens)):

@@ -17,6 +17,8 @@ Capability parity: ``daser/connector/ipc_client.py:53-317``.
 from __future__ import annotations
 
 import asyncio
+import sys
+from array import array
 import socket
 import threading
 from typing import Any, Optional
@@ -32,6 +34,28 @@ class IPCClientSync:
         self._timeout = timeout
         self._sock: Optional[socket.socket] = None
         self._lock = threading.Lock()
+        # token ids travel as a msgpack list (the reference's wire form) until `negotiate` finds
+        # a server that also takes them as packed int32 (one bin field instead of n integers)
+        self.binary_tokens = False
+
+    def negotiate(self) -> bool:
+        """Ask the server what it supports; enables packed token ids when it does.  A server
+        without the ``hello`` operation (the reference's) leaves everything as it is."""
+        try:
+            reply = self.call({"op": frames.OP_HELLO, "geometry": {}})
+        except RuntimeError:
+            return False
+        self.binary_tokens = "tokens_bin" in (reply.get("features") or [])
+        return self.binary_tokens
+
+    def _tok(self, tokens) -> dict[str, Any]:
+        if self.binary_tokens:
+            buf = tokens if isinstance(tokens, array) and tokens.typecode == "i" else array("i", tokens)
+            if sys.byteorder != "little":  # pragma: no cover
+                buf = array("i", buf)
+                buf.byteswap()
+            return {"tokens_bin": buf.tobytes()}
+        return {"tokens": list(tokens)}
 
     def _connect(self) -> socket.socket:
         if self._sock is None:
@@ -80,7 +104,7 @@ class IPCClientSync:
 
     # reference operations
     def lookup(self, tokens: list[int], model_id: str) -> list[dict[str, Any]]:
-        return self.call({"op": frames.OP_LOOKUP, "tokens": tokens, "model_id": model_id})[
+        return self.call({"op": frames.OP_LOOKUP, **self._tok(tokens), "model_id": model_id})[
             "chunks"
         ]
 
@@ -90,7 +114,7 @@ class IPCClientSync:
         reply = self.call(
             {
                 "op": frames.OP_MATCH_AND_ALLOC,
-                "tokens": tokens,
+                **self._tok(tokens),
                 "chunk_key": chunk_key,
                 "model_id": model_id,
             }
@@ -125,7 +149,7 @@ class IPCClientSync:
 
     def scan_chunks(self, tokens: list[int], model_id: str) -> list[dict[str, Any]]:
         return self.call(
-            {"op": frames.OP_LOOKUP_CHUNKS, "tokens": tokens, "model_id": model_id}
+            {"op": frames.OP_LOOKUP_CHUNKS, **self._tok(tokens), "model_id": model_id}
         )["hits"]
 
     def abort_chunk(self, chunk_key: str) -> bool:

@@ -142,6 +142,7 @@ class HBMStore:
         """
         if key in self._chunks:
             self._chunks.move_to_end(key)
+            self._protected.add(key)  # like every other touch: stays until the step ends
             return True
         off = self.reserve(key, nbytes)
         if off is None:

@@ -26,6 +26,8 @@ Differences:
 from __future__ import annotations
 
 import asyncio
+import sys
+from array import array
 import os
 from typing import Any, Awaitable, Callable, Optional
 
@@ -218,8 +220,23 @@ class IPCServer:
 
     # -- reference operations -------------------------------------------------------
 
+    @staticmethod
+    def _tokens_of(msg: dict[str, Any]):
+        """The request's token ids: ``tokens`` (a list, the reference's form) or ``tokens_bin``
+        (the same ids as packed little-endian int32: no per-token msgpack object on either side)."""
+        raw = msg.get("tokens_bin")
+        if raw is not None:
+            if len(raw) % 4:
+                raise ProtocolError("tokens_bin is not a whole number of int32")
+            arr = array("i")
+            arr.frombytes(bytes(raw))
+            if sys.byteorder != "little":  # pragma: no cover
+                arr.byteswap()
+            return arr
+        return list(msg["tokens"])
+
     async def _handle_lookup(self, msg: dict[str, Any]) -> dict[str, Any]:
-        found = await self._ri.lookup(list(msg["tokens"]), msg.get("model_id", "default"))
+        found = await self._ri.lookup(self._tokens_of(msg), msg.get("model_id", "default"))
         metrics.inc("lookup.hit" if found else "lookup.miss")
         return {"chunks": [self._chunk_dict(m) for m in found]}
 
@@ -239,7 +256,7 @@ class IPCServer:
         }
 
     async def _handle_match_and_alloc(self, msg: dict[str, Any]) -> dict[str, Any]:
-        tokens = list(msg["tokens"])
+        tokens = self._tokens_of(msg)
         model_id = msg.get("model_id", "default")
         chunk_key = msg.get("chunk_key", "")
         found = await self._ri.lookup(tokens, model_id)
@@ -402,7 +419,7 @@ class IPCServer:
         if "tokens" in msg:
             if not hasattr(self._ri, "scan"):
                 raise ProtocolError("retrieval index does not support offset scans")
-            hits = self._ri.scan(list(msg["tokens"]), model_id)  # type: ignore[attr-defined]
+            hits = self._ri.scan(self._tokens_of(msg), model_id)  # type: ignore[attr-defined]
             out["hits"] = [
                 {**self._chunk_dict(h.meta), "offset": h.offset} for h in hits
             ]
@@ -417,7 +434,8 @@ class IPCServer:
         bad = geometry_mismatch(self._geometry, dict(msg.get("geometry") or {}))
         if bad:
             raise ProtocolError("geometry mismatch: " + "; ".join(bad))
-        return {"ok": True, "geometry": self._geometry, "ops": sorted(self._handlers)}
+        return {"ok": True, "geometry": self._geometry, "ops": sorted(self._handlers),
+                "features": ["tokens_bin"]}
 
     async def _handle_stats(self, msg: dict[str, Any]) -> dict[str, Any]:
         return {

@@ -88,7 +88,7 @@ def test_tier_invariants_under_random_operations():
         st.tuples(st.just("clear")),
     )
 
-    @settings(max_examples=200, deadline=None)
+    @settings(max_examples=200, deadline=None, derandomize=True)
     @given(st.lists(op, min_size=1, max_size=80))
     def run(sequence):
         tier = HBMStore(SLOT, CAP, torch.device("cpu"))

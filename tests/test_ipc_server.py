@@ -194,3 +194,27 @@ def test_async_client(live_plane):
         s.close()
 
     asyncio.run(go())
+
+
+def test_packed_token_ids_are_negotiated_and_equivalent(live_plane):
+    """`hello` advertises `tokens_bin`; lookups with packed int32 ids answer like lists do, and a
+    client that never negotiates keeps the reference's wire form."""
+    from daser_b200.connector.ipc_client import IPCClientSync
+
+    p = live_plane.socket_path
+    plain, packed = IPCClientSync(p), IPCClientSync(p)
+    try:
+        assert packed.negotiate() is True and packed.binary_tokens and not plain.binary_tokens
+        toks = list(range(1000, 1000 + 70))
+        key = hash_tokens(toks[:64])
+        chunks, alloc = packed.match_and_alloc(toks, key, "m")
+        assert chunks == [] and alloc["token_count"] == 64
+        packed.commit_chunk(key)
+        for c in (plain, packed):
+            got = c.lookup(toks + [1, 2, 3], "m")
+            assert len(got) == 1 and got[0]["chunk_key"] == key
+            assert c.lookup(toks[:10], "m") == []
+        assert rpc(p, {"op": "lookup", "tokens_bin": b"\x01\x02\x03", "model_id": "m"}).get("error")
+    finally:
+        plain.close()
+        packed.close()

@@ -51,7 +51,7 @@ def _check(cm: ChunkManager, evicted: list[str], live_expected: set[str]) -> Non
         assert cm.store.get_slot_entry(c.start_slot).chunk_key == c.chunk_key
 
 
-@settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@settings(max_examples=150, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
 @given(ops)
 def test_ring_invariants_hold_under_mixed_operations(tmp_path_factory, sequence):
     cm = ChunkManager(TOTAL, MetadataStore(TOTAL))
