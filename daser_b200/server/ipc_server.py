@@ -416,7 +416,7 @@ class IPCServer:
                 metrics.inc("lookup_chunks.hit" if ok else "lookup_chunks.miss")
                 chunks.append(self._chunk_dict(meta) if ok else None)  # type: ignore[arg-type]
             out["chunks"] = chunks
-        if "tokens" in msg:
+        if "tokens" in msg or "tokens_bin" in msg:
             if not hasattr(self._ri, "scan"):
                 raise ProtocolError("retrieval index does not support offset scans")
             hits = self._ri.scan(self._tokens_of(msg), model_id)  # type: ignore[attr-defined]

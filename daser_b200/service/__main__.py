@@ -161,6 +161,13 @@ async def _run(args: argparse.Namespace) -> None:
                       chunk_blocks=args.chunk_blocks),
         engine_client=engine_client, tokenizer=tokenizer,
     )
+    if args.engine == "native":
+        # the in-process engine also answers vLLM's completions API (token-id prompts), with the
+        # stored chunks of a prompt found by a scan: a client written for vLLM can point here
+        from daser_b200.service.openai_api import mount_openai_routes
+
+        mount_openai_routes(app, engine_client, tokenizer, args.socket_path, args.native_model, cfg.model_id,
+                            args.block_tokens)
     server = uvicorn.Server(uvicorn.Config(app, host=args.host, port=args.port, loop="none", log_level="info"))
     stop = asyncio.Event()
     loop = asyncio.get_running_loop()

@@ -1,0 +1,113 @@
+"""A minimal OpenAI-compatible completions endpoint in front of the in-process engine.
+
+The reference's service (and its benchmarks) drive a remote stock vLLM through
+``POST /v1/completions`` with token-id prompts (``daser/service/vllm_client.py:62-126``).  With
+these routes mounted, the native engine answers the same calls, so that client (or this
+repository's :class:`~daser_b200.service.vllm_client.VLLMClient`) can point at it unchanged:
+
+* ``POST /v1/completions``  ``{"model", "prompt": [token ids] | "text", "max_tokens", ...}``
+* ``GET  /v1/models``, ``GET /health``
+
+Cache reuse needs no cooperation from the caller: the prompt's token ids are scanned against the
+control plane (``lookup_chunks`` with tokens: every stored chunk that appears at a block-aligned
+offset), the prompt is cut at the hits, and the pieces go to the engine as segments: hits are
+restored (keys re-rotated to their new positions), the gaps and the tail are computed.  Sampling is
+greedy; ``temperature`` and the other sampling fields are accepted and ignored.
+"""
+
+from __future__ import annotations
+
+import time
+import uuid
+from typing import Any, Optional, Sequence
+
+from fastapi import FastAPI, HTTPException
+from pydantic import BaseModel
+
+from daser_b200 import metrics
+from daser_b200.connector.ipc_client import IPCClientAsync
+from daser_b200.logging import init_logger
+
+logger = init_logger(__name__)
+
+
+class CompletionRequest(BaseModel):
+    model: Optional[str] = None
+    prompt: Any
+    max_tokens: int = 16
+    temperature: float = 0.0
+    stream: bool = False
+
+    model_config = {"extra": "allow"}
+
+
+def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_tokens: int) -> list[list[int]]:
+    """Cut ``tokens`` into segments at the stored chunks found in it.
+
+    Every segment but the last is a whole number of blocks (a stored chunk, or the gap before
+    one); the last one is the query the engine computes and is never empty.
+    """
+    segments: list[list[int]] = []
+    pos = 0
+    n = len(tokens)
+    for hit in sorted(hits, key=lambda h: h["offset"]):
+        off, count = int(hit["offset"]), int(hit["token_count"])
+        if off < pos or off % block_tokens or off + count >= n:
+            continue  # overlaps the previous hit, or would leave no token to compute
+        if off > pos:
+            segments.append(list(tokens[pos:off]))
+        segments.append(list(tokens[off : off + count]))
+        pos = off + count
+    segments.append(list(tokens[pos:]))
+    return segments
+
+
+def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket_path: str, model_name: str,
+                        model_id: str = "default", block_tokens: int = 16) -> None:
+    ipc = IPCClientAsync(socket_path)
+
+    @app.get("/v1/models")
+    async def models() -> dict[str, Any]:
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "daser_b200"}]}
+
+    @app.post("/v1/completions")
+    async def completions(req: CompletionRequest) -> dict[str, Any]:
+        if req.stream:
+            raise HTTPException(400, "streaming is not supported")
+        prompt = req.prompt
+        if isinstance(prompt, str):
+            tokens = list(tokenizer(prompt, add_special_tokens=False)["input_ids"])
+        elif isinstance(prompt, list) and prompt and all(isinstance(t, int) for t in prompt):
+            tokens = list(prompt)
+        elif isinstance(prompt, list) and len(prompt) == 1 and isinstance(prompt[0], list):
+            tokens = [int(t) for t in prompt[0]]
+        else:
+            raise HTTPException(400, "prompt must be a string or a list of token ids")
+        if not tokens:
+            raise HTTPException(400, "empty prompt")
+        if req.max_tokens < 1:
+            raise HTTPException(400, "max_tokens must be at least 1")  # as vLLM
+        t0 = time.time()
+        try:
+            reply = await ipc.call({"op": "lookup_chunks", "tokens": tokens, "model_id": model_id})
+            hits = reply.get("hits", [])
+        except RuntimeError as exc:  # the control plane is optional for correctness: compute everything
+            logger.warning("[SERVICE] scan failed (%s): computing the whole prompt", exc)
+            hits = []
+        segments = split_at_hits(tokens, hits, block_tokens)
+        try:
+            out = await engine_client.completion(tokens, {"max_tokens": req.max_tokens}, segments=segments)
+        except Exception as exc:
+            raise HTTPException(502, f"engine failed: {exc}") from exc
+        metrics.observe("service.completion_ms", (time.time() - t0) * 1e3)
+        metrics.inc("service.completion_hits", len(segments) - 1 if hits else 0)
+        choice = out["choices"][0]
+        usage = out.get("usage", {})
+        n_out = int(usage.get("completion_tokens", len(choice.get("token_ids", []))))
+        return {
+            "id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": int(t0),
+            "model": req.model or model_name,
+            "choices": [{"index": 0, "text": choice.get("text", ""), "token_ids": choice.get("token_ids"),
+                         "logprobs": None, "finish_reason": "length"}],
+            "usage": {"prompt_tokens": len(tokens), "completion_tokens": n_out, "total_tokens": len(tokens) + n_out},
+        }

@@ -191,3 +191,63 @@ def test_native_client_degrades_after_a_lost_peer():
 
     assert asyncio.run(run()) is False
     assert Engine.calls == 1
+
+
+def test_split_at_hits():
+    from daser_b200.service.openai_api import split_at_hits
+
+    toks = list(range(100))
+    hits = [{"offset": 32, "token_count": 32}, {"offset": 16, "token_count": 32},  # the second overlaps: dropped
+            {"offset": 80, "token_count": 20}]                                      # would leave no query: dropped
+    segs = split_at_hits(toks, hits, 16)
+    assert segs == [toks[0:16], toks[16:48], toks[48:]]
+    assert split_at_hits(toks, [], 16) == [toks]
+    assert [t for s in segs for t in s] == toks and segs[-1]
+
+
+def test_openai_completions_reuse_stored_chunks_found_by_scan(tmp_path):
+    """The native engine behind vLLM's completions API: a prompt that contains an uploaded chunk
+    behind an unrelated prefix gets it restored, and the reference's kind of client (token-id
+    prompt, max_tokens) gets the usual response shape."""
+    from daser_b200 import metrics
+    from daser_b200.engine.rag_cpu import CpuRagEngine
+    from daser_b200.kv.layout import KVGeometry
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.openai_api import mount_openai_routes
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    mcfg = PRESETS["toy"]
+    geo = KVGeometry(mcfg.num_layers, mcfg.num_kv_heads, mcfg.head_dim, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    engine = CpuRagEngine(mcfg, lp.socket_path, lp.cfg.store_path, num_blocks=128)
+    tok = ByteTokenizer()
+    client_obj = NativeEngineClient(engine, tok.decode)
+    cfg = ServiceConfig("", "toy", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2)
+    app = build_service_app(cfg, engine_client=client_obj, tokenizer=tok)
+    mount_openai_routes(app, client_obj, tok, lp.socket_path, "toy", "default", 16)
+    try:
+        with TestClient(app) as client:
+            text = "the quick brown fox jumps over the lazy dog and keeps running "  # 62 bytes -> one 32-token chunk
+            assert client.post("/documents", json={"title": "A", "text": text}).status_code == 201
+            enc = lambda t: tok(t)["input_ids"]  # noqa: E731
+            chunk = enc(text)[:32]
+            prompt = list(range(1, 17)) + chunk + enc("and then?")
+            assert client.get("/v1/models").json()["data"][0]["id"] == "toy"
+            hits0 = metrics.snapshot().get("connector.chunk_hits", 0)
+            r = client.post("/v1/completions", json={"model": "toy", "prompt": prompt, "max_tokens": 1, "temperature": 0})
+            assert r.status_code == 200, r.text
+            body = r.json()
+            assert body["object"] == "text_completion" and len(body["choices"][0]["token_ids"]) == 1
+            assert body["usage"] == {"prompt_tokens": len(prompt), "completion_tokens": 1, "total_tokens": len(prompt) + 1}
+            assert metrics.snapshot().get("connector.chunk_hits", 0) - hits0 >= 1  # the chunk was restored, not recomputed
+            # the same prompt with nothing cached computes the same first token
+            cold = client.post("/v1/completions", json={"prompt": [7] * 16 + prompt[16:], "max_tokens": 1})
+            assert cold.status_code == 200
+            # bad requests
+            assert client.post("/v1/completions", json={"prompt": [], "max_tokens": 1}).status_code == 400
+            assert client.post("/v1/completions", json={"prompt": prompt, "max_tokens": 0}).status_code == 400
+            assert client.post("/v1/completions", json={"prompt": prompt, "stream": True}).status_code == 400
+            assert client.post("/v1/completions", json={"prompt": "plain text works too", "max_tokens": 1}).status_code == 200
+    finally:
+        engine.close()
+        lp.stop()
