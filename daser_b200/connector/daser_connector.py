@@ -127,6 +127,38 @@ def describe_kv_caches(kv_caches: dict[str, torch.Tensor]) -> dict[str, Any]:
     }
 
 
+_STAT_KEYS = ("connector.bytes_loaded", "connector.bytes_stored", "connector.bytes_over_pcie",
+              "connector.load_errors", "connector.store_errors")
+
+try:  # vLLM's container for connector telemetry (worker -> logger process); absent in old versions
+    from vllm.distributed.kv_transfer.kv_connector.v1.metrics import KVConnectorStats as _KVConnectorStats
+except Exception:  # pragma: no cover
+    _KVConnectorStats = None
+
+if _KVConnectorStats is not None:
+    from dataclasses import dataclass as _dataclass
+
+    @_dataclass
+    class DaserKVConnectorStats(_KVConnectorStats):  # type: ignore[misc,valid-type]
+        """Byte and error counters of one interval; all fields are sums, so aggregation adds."""
+
+        def reset(self) -> None:
+            self.data = {}
+
+        def aggregate(self, other: "DaserKVConnectorStats") -> "DaserKVConnectorStats":
+            for k, v in other.data.items():
+                self.data[k] = self.data.get(k, 0) + v
+            return self
+
+        def reduce(self) -> dict[str, int | float]:
+            return dict(self.data)
+
+        def is_empty(self) -> bool:
+            return not any(self.data.values())
+else:  # pragma: no cover
+    DaserKVConnectorStats = None  # type: ignore[assignment,misc]
+
+
 class DaserConnector(KVConnectorBase_V1):
     def __init__(self, vllm_config: Any, role: Any, kv_cache_config: Any = None) -> None:
         try:
@@ -150,6 +182,7 @@ class DaserConnector(KVConnectorBase_V1):
         self._sched: Optional[SchedulerHalf] = None
         self._worker: Optional[WorkerHalf] = None
         self._req_tokens: dict[str, int] = {}
+        self._stats_seen: dict[str, float] = {}
         if self._is_scheduler:
             self._sched = SchedulerHalf(self._socket_path, self._block_tokens, self._model_id)
 
@@ -280,7 +313,22 @@ class DaserConnector(KVConnectorBase_V1):
         return True
 
     def get_kv_connector_stats(self) -> Any:
-        return None  # counters are served by get_stats(); vLLM's stats object is optional
+        """What this worker moved since the last call, in vLLM's stats container (None when
+        nothing happened, or when the installed vLLM has no such container)."""
+        if self._worker is None or DaserKVConnectorStats is None:
+            return None
+        now = self._worker.get_stats()
+        delta = {k: now.get(k, 0) - self._stats_seen.get(k, 0) for k in _STAT_KEYS}
+        self._stats_seen = {k: now.get(k, 0) for k in _STAT_KEYS}
+        if not any(delta.values()):
+            return None
+        return DaserKVConnectorStats(data={k.split(".", 1)[1]: v for k, v in delta.items()})
+
+    @classmethod
+    def build_kv_connector_stats(cls, data: Optional[dict[str, Any]] = None) -> Any:
+        if DaserKVConnectorStats is None:
+            return None
+        return DaserKVConnectorStats(data=dict(data)) if data is not None else DaserKVConnectorStats()
 
     def get_stats(self) -> dict[str, float]:
         return self._worker.get_stats() if self._worker is not None else {}

@@ -69,8 +69,12 @@ def test_cold_store_then_warm_load(tmp_path, layout, codec_name):
         worker.start_load_kv(None)
         for name in caches:
             worker.save_kv_layer(name, caches[name], None)
+        worker.get_kv_connector_stats()  # start a fresh interval
         worker.wait_for_save()
         worker.clear_connector_metadata()
+        stats = worker.get_kv_connector_stats()
+        assert stats is not None and stats.data["bytes_stored"] == 3 * slot and not stats.is_empty()
+        assert worker.get_kv_connector_stats() is None  # nothing moved since
         assert sched.request_finished(req, [7, 2, 9, 4]) == (False, None)
         # ---- warm pass in a fresh engine: hit -> load into other blocks ----
         caches2, big2 = _caches(layout, 2)
@@ -214,3 +218,14 @@ def test_cross_layer_tensor_registration_store_and_load(tmp_path, backend):
         worker2.shutdown()
         sched.shutdown()
         lp.stop()
+
+
+def test_connector_stats_container():
+    from daser_b200.connector.daser_connector import DaserConnector, DaserKVConnectorStats
+
+    a = DaserConnector.build_kv_connector_stats({"bytes_loaded": 10, "load_errors": 0})
+    b = DaserKVConnectorStats(data={"bytes_loaded": 5, "bytes_stored": 7})
+    assert not a.is_empty() and DaserConnector.build_kv_connector_stats().is_empty()
+    assert a.aggregate(b).reduce() == {"bytes_loaded": 15, "load_errors": 0, "bytes_stored": 7}
+    a.reset()
+    assert a.is_empty()
