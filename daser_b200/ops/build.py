@@ -116,6 +116,17 @@ def build_index(force: bool = False) -> Path:
     return INDEX_LIB
 
 
+def build_index_selftest(sanitize: str = "address,undefined") -> Path:
+    """The token index's stand-alone exerciser, instrumented with ``-fsanitize=<sanitize>``."""
+    BUILD_DIR.mkdir(exist_ok=True)
+    out = BUILD_DIR / f"index_selftest_{sanitize.replace(',', '_')}"
+    srcs = [INDEX_SRC / "token_index.cc", INDEX_SRC / "token_index_selftest.cc"]
+    if _stale(out, srcs):
+        _run(["g++", "-O1", "-g", "-std=c++17", f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-pthread",
+              "-o", str(out), *map(str, srcs), "-ldl"])
+    return out
+
+
 def build_all(verbose: bool = False, force: bool = False) -> None:
     build_io(force=force)
     build_index(force=force)
