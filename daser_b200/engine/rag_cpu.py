@@ -24,6 +24,13 @@ from daser_b200.kv.layout import KVGeometry
 from daser_b200.models.llama import LlamaConfig, LlamaWeights, TorchPagedKV, reference_forward
 
 
+@dataclass
+class GenerateResult:
+    generated: list[int]
+    context_len: int
+    restored_chunks: int
+
+
 class BlockAllocator:
     """Free-list allocator of pool blocks."""
 
@@ -149,6 +156,28 @@ class CpuRagEngine:
         if not keep_blocks:
             self.blocks.free(table)
         return RequestResult(logits, table, offsets, [s is not None for s in specs], total)
+
+    def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
+                 store_misses: bool = False) -> "GenerateResult":
+        """Serve one request to completion with greedy sampling: the same call the GPU engine
+        offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
+        for signature parity; chunks are only stored through :meth:`store_chunk` here."""
+        res = self.run_request([], chunks, query, keep_blocks=True)
+        bt = self.cfg.block_tokens
+        table = list(res.block_table)
+        generated = [int(res.logits[-1].argmax())]
+        pos = res.total_tokens
+        try:
+            while len(generated) < max_new_tokens:
+                if pos // bt >= len(table):
+                    table.extend(self.blocks.alloc(1))
+                logits = reference_forward(self.weights, torch.tensor([generated[-1]]), torch.tensor([pos]), self.pool,
+                                           torch.tensor(table), pos)
+                generated.append(int(logits[-1].argmax()))
+                pos += 1
+        finally:
+            self.blocks.free(table)
+        return GenerateResult(generated, res.total_tokens, sum(res.restored))
 
     def recompute_chunk_alone(self, chunk: Sequence[int], offset: int) -> tuple[list[int], int]:
         """Run ``chunk`` alone at positions ``offset..``; returns its (fresh) blocks and length.

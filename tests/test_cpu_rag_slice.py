@@ -134,3 +134,30 @@ def test_host_tier_serves_repeat_loads_without_io(tmp_path):
     finally:
         eng.close()
         lp.stop()
+
+
+def test_generate_decodes_over_restored_chunks(rag):
+    """Multi-token greedy generation: restored chunks are used (their KV was computed with each
+    chunk alone, so the tokens may differ from a run that lets chunks attend to one another; what
+    must hold is that the restored run is reproducible, decodes past a block boundary, and
+    returns every block)."""
+    eng, _ = rag
+    rng = random.Random(5)
+    chunks = [[rng.randrange(eng.cfg.vocab_size) for _ in range(64)] for _ in range(2)]
+    query = [rng.randrange(eng.cfg.vocab_size) for _ in range(9)]
+    free0 = eng.blocks.num_free
+    cold = eng.generate(chunks, query, max_new_tokens=12)  # nothing stored yet: all computed
+    assert cold.restored_chunks == 0 and len(cold.generated) == 12 and cold.context_len == 137
+    assert eng.generate(chunks, query, max_new_tokens=12).generated == cold.generated
+    for c in chunks:
+        eng.store_chunk(c)
+    warm = eng.generate(chunks, query, max_new_tokens=12)
+    again = eng.generate(chunks, query, max_new_tokens=12)
+    assert warm.restored_chunks == 2 and again.restored_chunks == 2
+    assert warm.generated == again.generated and len(warm.generated) == 12
+    # a single stored chunk at offset 0 has nothing before it to attend to: restoring it changes nothing
+    one_cold = eng.generate([[7] * 32], query, max_new_tokens=6)
+    eng.store_chunk([7] * 32)
+    one_warm = eng.generate([[7] * 32], query, max_new_tokens=6)
+    assert one_warm.restored_chunks == 1 and one_warm.generated == one_cold.generated
+    assert eng.blocks.num_free == free0

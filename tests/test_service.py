@@ -234,11 +234,11 @@ def test_openai_completions_reuse_stored_chunks_found_by_scan(tmp_path):
             prompt = list(range(1, 17)) + chunk + enc("and then?")
             assert client.get("/v1/models").json()["data"][0]["id"] == "toy"
             hits0 = metrics.snapshot().get("connector.chunk_hits", 0)
-            r = client.post("/v1/completions", json={"model": "toy", "prompt": prompt, "max_tokens": 1, "temperature": 0})
+            r = client.post("/v1/completions", json={"model": "toy", "prompt": prompt, "max_tokens": 3, "temperature": 0})
             assert r.status_code == 200, r.text
             body = r.json()
-            assert body["object"] == "text_completion" and len(body["choices"][0]["token_ids"]) == 1
-            assert body["usage"] == {"prompt_tokens": len(prompt), "completion_tokens": 1, "total_tokens": len(prompt) + 1}
+            assert body["object"] == "text_completion" and len(body["choices"][0]["token_ids"]) == 3
+            assert body["usage"] == {"prompt_tokens": len(prompt), "completion_tokens": 3, "total_tokens": len(prompt) + 3}
             assert metrics.snapshot().get("connector.chunk_hits", 0) - hits0 >= 1  # the chunk was restored, not recomputed
             # the same prompt with nothing cached computes the same first token
             cold = client.post("/v1/completions", json={"prompt": [7] * 16 + prompt[16:], "max_tokens": 1})
