@@ -154,7 +154,9 @@ async def _run(args: argparse.Namespace) -> None:
             from daser_b200.models.llama import PRESETS as _P
 
             _tp_context(_P[args.native_model]).barrier()  # followers may connect to the control plane now
-        engine_client, engine = _native_engine(args, cfg, tokenizer)
+        # built off the loop: the engine's connector talks to the control plane, which this loop serves
+        engine_client, engine = await asyncio.get_running_loop().run_in_executor(
+            None, _native_engine, args, cfg, tokenizer)
     app = build_service_app(
         ServiceConfig(vllm_base_url=args.vllm_base_url or "", model=args.model or args.native_model,
                       tokenizer=args.tokenizer, socket_path=args.socket_path, block_tokens=args.block_tokens,

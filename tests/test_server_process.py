@@ -113,3 +113,44 @@ def test_periodic_snapshot_survives_sigkill(tmp_path):
     finally:
         client2.close()
         _stop(proc2)
+
+
+def test_service_process_with_native_engine_starts_quickly_and_answers(tmp_path):
+    """`python -m daser_b200.service --engine native`: control plane, CPU engine and REST front end
+    in one process.  The engine is built off the event loop (its connector talks to the control
+    plane that the same loop serves), so start-up must not wait for an RPC timeout."""
+    import json
+    import socket
+    import urllib.request
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "daser_b200.service", "--engine", "native", "--tokenizer", "byte",
+           "--store-path", str(tmp_path / "s.store"), "--index-path", str(tmp_path / "s.index"),
+           "--socket-path", str(tmp_path / "s.sock"), "--total-slots", "256", "--host", "127.0.0.1", "--port", str(port)]
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            env=dict(os.environ, PYTHONUNBUFFERED="1"))
+    base = f"http://127.0.0.1:{port}"
+    try:
+        t0 = time.time()
+        up = False
+        while time.time() - t0 < 25:
+            if proc.poll() is not None:
+                raise AssertionError("service exited early:\n" + proc.stdout.read())
+            try:
+                with urllib.request.urlopen(base + "/health", timeout=2) as r:
+                    up = json.load(r)["status"] == "ok"
+                    break
+            except OSError:
+                time.sleep(0.3)
+        assert up, "service did not come up within 25 s"
+        body = json.dumps({"prompt": "what does the fox say? nobody knows for sure", "max_tokens": 2}).encode()
+        req = urllib.request.Request(base + "/v1/completions", data=body, headers={"content-type": "application/json"})
+        with urllib.request.urlopen(req, timeout=30) as r:
+            out = json.load(r)
+        assert out["usage"]["completion_tokens"] == 2 and out["object"] == "text_completion"
+    finally:
+        out_text = _stop(proc)
+    assert proc.returncode == 0, out_text[-2000:]
+    assert (tmp_path / "s.index").exists()  # state saved on the way out
