@@ -530,7 +530,8 @@ class WorkerHalf:
         dev_staging = self._staging.is_cuda
         tickets = []
         nbytes_total = 0
-        for spec, src, n, io_dst, kind in jobs:
+        # reads go out in file order: neighbouring chunks become one sequential sweep of the device
+        for spec, src, n, io_dst, kind in sorted(jobs, key=lambda j: j[0].file_offset):
             if not io_dst:
                 continue
             off = spec.file_offset + spec.skip_slots * g.slot_size
