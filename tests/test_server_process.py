@@ -154,3 +154,31 @@ def test_service_process_with_native_engine_starts_quickly_and_answers(tmp_path)
         out_text = _stop(proc)
     assert proc.returncode == 0, out_text[-2000:]
     assert (tmp_path / "s.index").exists()  # state saved on the way out
+
+
+def test_operator_cli_reads_and_evicts(tmp_path, capsys):
+    import json
+
+    from daser_b200.server import ctl
+
+    proc, client = _spawn(tmp_path)
+    try:
+        key = hash_tokens(list(range(32)))
+        client.alloc_chunk(key, 32, "m")
+        client.commit_chunk(key)
+        sock = str(tmp_path / "d.sock")
+        assert ctl.main(["--socket-path", sock, "stats"]) == 0
+        assert json.loads(capsys.readouterr().out)["ring"]["used_slots"] == 2
+        assert ctl.main(["--socket-path", sock, "lookup", key, "nope", "--model-id", "m"]) == 0
+        found = json.loads(capsys.readouterr().out)["chunks"]
+        assert found[0]["chunk_key"] == key and found[1] is None
+        assert ctl.main(["--socket-path", sock, "evict-chunk", key]) == 0
+        capsys.readouterr()
+        assert ctl.main(["--socket-path", sock, "lookup", key, "--model-id", "m"]) == 0
+        assert json.loads(capsys.readouterr().out)["chunks"] == [None]
+        assert "tokens_bin" in json.loads((ctl.main(["--socket-path", sock, "hello"]), capsys.readouterr().out)[1])["features"]
+        assert ctl.main(["--socket-path", sock, "doc", "missing"]) == 1  # server-side error -> exit code 1
+        assert ctl.main(["--socket-path", str(tmp_path / "absent.sock"), "--timeout", "1", "stats"]) == 1
+    finally:
+        client.close()
+        _stop(proc)
