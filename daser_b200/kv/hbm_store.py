@@ -69,6 +69,8 @@ class HBMStore:
     def end_step(self) -> None:
         """Entries looked up or reserved since the last call may be evicted again."""
         self._protected.clear()
+        metrics.set_gauge(f"{self.kind}.used_slots", self.used_slots)
+        metrics.set_gauge(f"{self.kind}.capacity_slots", self.capacity)
 
     # -- placement -----------------------------------------------------------------------------
     def _take(self, n: int) -> Optional[int]:

@@ -16,11 +16,18 @@ from typing import Iterable
 _lock = threading.Lock()
 _counters: dict[str, float] = defaultdict(float)
 _samples: dict[str, deque] = defaultdict(lambda: deque(maxlen=4096))
+_gauges: dict[str, float] = {}
 
 
 def inc(name: str, value: float = 1.0) -> None:
     with _lock:
         _counters[name] += value
+
+
+def set_gauge(name: str, value: float) -> None:
+    """A value that is replaced, not accumulated (ring occupancy, tier fill)."""
+    with _lock:
+        _gauges[name] = float(value)
 
 
 def observe(name: str, value: float) -> None:
@@ -42,6 +49,7 @@ def percentile(values: Iterable[float], q: float) -> float:
 def snapshot() -> dict[str, float]:
     with _lock:
         out = dict(_counters)
+        out.update(_gauges)
         for name, dq in _samples.items():
             vals = list(dq)
             out[name + ".p50"] = percentile(vals, 50)
@@ -53,6 +61,7 @@ def reset() -> None:
     with _lock:
         _counters.clear()
         _samples.clear()
+        _gauges.clear()
 
 
 def prometheus_text(prefix: str = "daser") -> str:

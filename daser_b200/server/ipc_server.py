@@ -163,7 +163,12 @@ class IPCServer:
             return {"error": f"unknown op: {op}"}
         metrics.inc(f"ipc.{op}")
         try:
-            return await handler(msg)
+            reply = await handler(msg)
+            if self._dirty:  # occupancy gauges for /metrics and the stats of embedding processes
+                metrics.set_gauge("ring.used_slots", self._cm.used_slots)
+                metrics.set_gauge("ring.total_slots", self._cm.total_slots)
+                metrics.set_gauge("ring.chunks", len(self._cm.store))
+            return reply
         except ProtocolError as exc:
             return {"error": str(exc)}
         except (KeyError, ValueError, TypeError) as exc:

@@ -218,3 +218,16 @@ def test_packed_token_ids_are_negotiated_and_equivalent(live_plane):
     finally:
         plain.close()
         packed.close()
+
+
+def test_ring_occupancy_gauges_follow_the_ring(live_plane):
+    from daser_b200 import metrics
+
+    p = live_plane.socket_path
+    rpc(p, {"op": "alloc_chunk", "chunk_key": "g1", "token_count": 40, "model_id": "m"})
+    snap = metrics.snapshot()
+    assert snap["ring.used_slots"] == 3 and snap["ring.chunks"] == 1 and snap["ring.total_slots"] >= 3
+    rpc(p, {"op": "commit_chunk", "chunk_key": "g1"})
+    rpc(p, {"op": "evict_chunk", "chunk_key": "g1"})
+    assert metrics.snapshot()["ring.chunks"] == 0
+    assert "daser_ring_used_slots" in metrics.prometheus_text()
