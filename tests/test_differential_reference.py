@@ -125,3 +125,66 @@ def test_same_replies_over_the_wire_from_both_servers(tmp_path):
     finally:
         ref.stop()
         mine.stop()
+
+
+def test_reference_clients_talk_to_this_server(tmp_path):
+    """The unmodified reference clients (sync and async) against this control plane: the wire
+    protocol is the reference's, so its connector and its service can be pointed here."""
+    from daser.connector.ipc_client import IPCClientAsync as RefAsync
+    from daser.connector.ipc_client import IPCClientSync as RefSync
+
+    tokens = list(range(700, 740))
+    ref = _RefPlane(str(tmp_path / "ref.sock"))
+    mine = LiveControlPlane(tmp_path).start()
+    try:
+        # same scripted session through the reference's own sync client, on both servers
+        def session(client):
+            key = hash_tokens(tokens[:32])
+            out = [client.call({"op": "lookup", "tokens": tokens, "model_id": "m"})]
+            out.append(client.call({"op": "match_and_alloc", "tokens": tokens, "chunk_key": key, "model_id": "m"}))
+            out.append(client.call({"op": "commit_chunk", "chunk_key": key}))
+            out.append(client.call({"op": "lookup", "tokens": tokens + [9], "model_id": "m"}))
+            out.append(client.call({"op": "alloc_chunk", "chunk_key": "other", "token_count": 40, "model_id": "m"}))
+            out.append(client.call({"op": "evict_chunk", "chunk_key": key}))
+            out.append(client.call({"op": "lookup", "tokens": tokens, "model_id": "m"}))
+            return out
+
+        a, b = RefSync(str(tmp_path / "ref.sock")), RefSync(mine.socket_path)
+        try:
+            got_a, got_b = session(a), session(b)
+        finally:
+            a.close(), b.close()
+        # this server adds fields the reference's replies do not have; what the reference sends must match
+        for ra, rb in zip(got_a, got_b):
+            assert set(ra) <= set(rb), (ra, rb)  # every field of the reference's reply is present here
+            for k in ra:
+                va, vb = ra[k], rb[k]
+                if isinstance(va, list) and va and isinstance(va[0], dict):
+                    assert [{f: d[f] for f in va[i]} for i, d in enumerate(vb)] == va
+                elif isinstance(va, dict):
+                    assert {f: vb[f] for f in va} == va
+                else:
+                    assert va == vb
+
+        async def docs(path):
+            c = RefAsync(path)
+            key = hash_tokens(list(range(16)))
+            sync = IPCClientSync(path)
+            sync.alloc_chunk(key, 16, "m")
+            await c.commit_chunk(key)
+            r = await c.register_doc("d1", "Title", [key, "missing"], 32, list(range(32)))
+            listing = await c.list_docs()
+            doc = await c.get_doc("d1")
+            gone = await c.evict_doc("d1")
+            after = await c.list_docs()
+            sync.close()
+            for d in listing + [doc]:
+                d.pop("created_at", None)
+            return r, listing, doc, gone, after
+
+        got_ref = asyncio.run(docs(str(tmp_path / "ref.sock")))
+        got_mine = asyncio.run(docs(mine.socket_path))
+        assert got_ref == got_mine
+    finally:
+        ref.stop()
+        mine.stop()
