@@ -8,6 +8,11 @@ repository's :class:`~daser_b200.service.vllm_client.VLLMClient`) can point at i
 * ``POST /v1/completions``  ``{"model", "prompt": [token ids] | "text", "max_tokens", ...}``
 * ``GET  /v1/models``, ``GET /health``
 
+A request with ``max_tokens == 1`` is what the reference's service uses as "prefill this chunk so
+that the cache holds it" (vLLM's connector stores the KV of every prompt it has not seen); the same
+side effect happens here: when the prompt's block-aligned prefix is not stored yet, it is stored as
+a chunk keyed by the hash of its tokens, which is the key the reference's chunker registers.
+
 Cache reuse needs no cooperation from the caller: the prompt's token ids are scanned against the
 control plane (``lookup_chunks`` with tokens: every stored chunk that appears at a block-aligned
 offset), the prompt is cut at the hits, and the pieces go to the engine as segments: hits are
@@ -97,6 +102,11 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
         segments = split_at_hits(tokens, hits, block_tokens)
         try:
             out = await engine_client.completion(tokens, {"max_tokens": req.max_tokens}, segments=segments)
+            aligned = len(tokens) // block_tokens * block_tokens
+            covered = any(int(h["offset"]) == 0 and int(h["token_count"]) >= aligned for h in hits)
+            if req.max_tokens == 1 and aligned and not covered:
+                await engine_client.prefill(tokens[:aligned])  # a prefill request leaves its KV in the store
+                metrics.inc("service.completion_stores")
         except Exception as exc:
             raise HTTPException(502, f"engine failed: {exc}") from exc
         metrics.observe("service.completion_ms", (time.time() - t0) * 1e3)
