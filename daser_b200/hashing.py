@@ -52,6 +52,21 @@ def block_digests(tokens: Sequence[int], block_tokens: int) -> list[str]:
     return [xxhash.xxh3_128(raw[i * step : (i + 1) * step]).hexdigest() for i in range(nblocks)]
 
 
+def window_digests(tokens: Sequence[int], block_tokens: int) -> list[str]:
+    """Digest of ``tokens[i : i + b]`` at every token offset ``i`` (anchors at unaligned offsets)."""
+    if block_tokens <= 0:
+        raise ValueError("block_tokens must be positive")
+    nat = _native()
+    if nat is not None:
+        return nat.window_digests(tokens, block_tokens)
+    n = len(tokens) - block_tokens + 1
+    if n <= 0:
+        return []
+    raw = memoryview(_token_bytes(tokens))
+    step = block_tokens * 4
+    return [xxhash.xxh3_128(raw[4 * i : 4 * i + step]).hexdigest() for i in range(n)]
+
+
 def prefix_digests(tokens: Sequence[int], block_tokens: int) -> list[str]:
     """Digests of ``tokens[:b]`` for ``b = block_tokens, 2*block_tokens, ...``.
 

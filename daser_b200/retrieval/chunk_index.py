@@ -22,7 +22,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from daser_b200.hashing import block_digests, hash_tokens
+from daser_b200.hashing import block_digests, hash_tokens, window_digests
 from daser_b200.retrieval.prefix import PrefixHashIndex
 from daser_b200.server.metadata_store import ChunkMeta
 
@@ -55,19 +55,22 @@ class ChunkOffsetIndex(PrefixHashIndex):
             out.append(meta if meta is not None and meta.model_id == model_id else None)
         return out
 
-    def scan(self, tokens: list[int], model_id: str) -> list[ChunkHit]:
-        """Non-overlapping stored chunks at block-aligned offsets, left to right."""
+    def scan(self, tokens: list[int], model_id: str, any_offset: bool = False) -> list[ChunkHit]:
+        """Non-overlapping stored chunks, left to right: at block-aligned offsets, or with
+        ``any_offset`` at every token offset (a caller that pads what precedes a hit can then
+        still place the chunk on a block boundary)."""
         bt = self._block_tokens
         hits: list[ChunkHit] = []
         pos = 0
         n = len(tokens)
         if not self._anchors:
             return hits
-        # every aligned block is hashed once, in one pass (native when built)
-        anchors = block_digests(tokens, bt)
+        # every candidate first block is hashed once, in one pass (native when built)
+        step = 1 if any_offset else bt
+        anchors = window_digests(tokens, bt) if any_offset else block_digests(tokens, bt)
         while pos + bt <= n:
             best: ChunkMeta | None = None
-            keys = self._anchors.get(anchors[pos // bt])
+            keys = self._anchors.get(anchors[pos // step])
             if keys:
                 for key in keys:
                     meta = self._by_key.get(key)
@@ -80,9 +83,9 @@ class ChunkOffsetIndex(PrefixHashIndex):
                         best = meta
             if best is not None:
                 hits.append(ChunkHit(best, pos))
-                pos += -(-best.token_count // bt) * bt
+                pos += best.token_count if any_offset else -(-best.token_count // bt) * bt
             else:
-                pos += bt
+                pos += step
         return hits
 
     def _forget(self, chunk_key: str) -> None:

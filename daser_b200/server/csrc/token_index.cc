@@ -184,6 +184,15 @@ DASER_API int64_t daser_block_digests(const int32_t* tokens, int64_t n, int32_t 
   return nb;
 }
 
+// out: 16 bytes per window tokens[i : i + block], i = 0 .. n - block (every token offset: anchors
+// of chunks that sit at offsets which are not multiples of the block size); returns their number.
+DASER_API int64_t daser_window_digests(const int32_t* tokens, int64_t n, int32_t block, uint8_t* out) {
+  if (!xxh().ok || block <= 0 || n < 0 || (!tokens && n) || !out) return -1;
+  const int64_t nw = n >= block ? n - block + 1 : 0;
+  for (int64_t i = 0; i < nw; ++i) canonical(xxh().oneshot(tokens + i, (size_t)block * 4), out + 16 * i);
+  return nw;
+}
+
 DASER_API daser_table* daser_table_new(int64_t capacity_hint) { return new daser_table(capacity_hint < 0 ? 0 : capacity_hint); }
 DASER_API void daser_table_free(daser_table* t) { delete t; }
 DASER_API int64_t daser_table_size(daser_table* t) {

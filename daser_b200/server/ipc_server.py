@@ -424,7 +424,8 @@ class IPCServer:
         if "tokens" in msg or "tokens_bin" in msg:
             if not hasattr(self._ri, "scan"):
                 raise ProtocolError("retrieval index does not support offset scans")
-            hits = self._ri.scan(self._tokens_of(msg), model_id)  # type: ignore[attr-defined]
+            hits = self._ri.scan(self._tokens_of(msg), model_id,  # type: ignore[attr-defined]
+                                 any_offset=bool(msg.get("any_offset", False)))
             out["hits"] = [
                 {**self._chunk_dict(h.meta), "offset": h.offset} for h in hits
             ]

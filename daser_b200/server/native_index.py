@@ -31,7 +31,7 @@ def _load() -> Optional[C.CDLL]:
     p, i64, i32, u64 = C.c_void_p, C.c_int64, C.c_int32, C.c_uint64
     lib.daser_index_available.restype = C.c_int
     lib.daser_hash_tokens.argtypes = [p, i64, p]
-    for fn in (lib.daser_prefix_digests, lib.daser_block_digests):
+    for fn in (lib.daser_prefix_digests, lib.daser_block_digests, lib.daser_window_digests):
         fn.argtypes, fn.restype = [p, i64, i32, p], i64
     lib.daser_table_new.argtypes, lib.daser_table_new.restype = [i64], p
     lib.daser_table_free.argtypes = [p]
@@ -84,6 +84,19 @@ def prefix_digests(tokens: Sequence[int], block: int) -> list[str]:
 
 def block_digests(tokens: Sequence[int], block: int) -> list[str]:
     return _digests(_load().daser_block_digests, tokens, block)
+
+
+def window_digests(tokens: Sequence[int], block: int) -> list[str]:
+    """Digest of ``tokens[i : i + block]`` for every offset ``i``."""
+    buf, ptr, n = _tokens(tokens)
+    nw = n - block + 1 if n >= block else 0
+    if nw == 0:
+        return []
+    out = C.create_string_buffer(16 * nw)
+    if _load().daser_window_digests(ptr, n, block, out) != nw:
+        raise RuntimeError("native digest pass failed")
+    raw = out.raw
+    return [raw[16 * i : 16 * i + 16].hex() for i in range(nw)]
 
 
 class DigestTable:

@@ -46,18 +46,21 @@ class CompletionRequest(BaseModel):
     model_config = {"extra": "allow"}
 
 
-def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_tokens: int) -> list[list[int]]:
+def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_tokens: int,
+                  aligned_only: bool = False) -> list[list[int]]:
     """Cut ``tokens`` into segments at the stored chunks found in it.
 
-    Every segment but the last is a whole number of blocks (a stored chunk, or the gap before
-    one); the last one is the query the engine computes and is never empty.
+    Every segment but the last is a stored chunk or the gap before one; the last one is the
+    query the engine computes and is never empty.  The engine client pads every segment but the
+    last to a block boundary, which is what puts a chunk found at an odd offset back on one (at
+    the price of pad tokens in the context); ``aligned_only`` keeps only hits that need no padding.
     """
     segments: list[list[int]] = []
     pos = 0
     n = len(tokens)
     for hit in sorted(hits, key=lambda h: h["offset"]):
         off, count = int(hit["offset"]), int(hit["token_count"])
-        if off < pos or off % block_tokens or off + count >= n:
+        if off < pos or off + count >= n or (aligned_only and off % block_tokens):
             continue  # overlaps the previous hit, or would leave no token to compute
         if off > pos:
             segments.append(list(tokens[pos:off]))
@@ -94,7 +97,8 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             raise HTTPException(400, "max_tokens must be at least 1")  # as vLLM
         t0 = time.time()
         try:
-            reply = await ipc.call({"op": "lookup_chunks", "tokens": tokens, "model_id": model_id})
+            reply = await ipc.call({"op": "lookup_chunks", "tokens": tokens, "model_id": model_id,
+                                    "any_offset": True})
             hits = reply.get("hits", [])
         except RuntimeError as exc:  # the control plane is optional for correctness: compute everything
             logger.warning("[SERVICE] scan failed (%s): computing the whole prompt", exc)

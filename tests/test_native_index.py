@@ -98,3 +98,24 @@ def test_indexes_answer_like_the_python_path():
     py.discard(stored[1][0])
     assert same(prompt, "m")[0].token_count == 3 * 16
     loop.close()
+
+
+def test_scan_at_any_offset_matches_between_native_and_python():
+    rng = random.Random(3)
+    nat, py = ChunkOffsetIndex(16, native=True), ChunkOffsetIndex(16, native=False)
+    prompt = [rng.randrange(50000) for _ in range(400)]
+    loop = asyncio.new_event_loop()
+    placed = [(21, 64), (100, 32), (133, 48)]  # offsets that are not multiples of 16
+    for off, n in placed:
+        toks = prompt[off : off + n]
+        key = hashing.hash_tokens(toks)
+        for ix in (nat, py):
+            loop.run_until_complete(ix.insert(_meta(key, n)))
+            ix.register_anchor(key, hashing.hash_tokens(toks[:16]))
+    loop.close()
+    for ix in (nat, py):
+        assert ix.scan(prompt, "m") == []  # none of them sits on a block boundary
+        got = [(h.offset, h.meta.token_count) for h in ix.scan(prompt, "m", any_offset=True)]
+        assert got == placed
+    assert native_index.window_digests(prompt[:40], 16) == [hashing.hash_tokens(prompt[i : i + 16]) for i in range(25)]
+    assert native_index.window_digests(prompt[:10], 16) == []

@@ -74,8 +74,9 @@ def test_reference_service_uses_this_engine_and_gets_chunk_hits(tmp_path):
             return 0.0
 
         cfg = RefConfig(vllm_base_url=base, model="toy", tokenizer=_char_tokenizer(str(tmp_path / "tok")),
-                        socket_path=sock, block_tokens=16, chunk_blocks=2,
-                        system_prompt="S" * 32, task_separator="|task: ")  # 32 characters = 2 whole blocks
+                        socket_path=sock, block_tokens=16, chunk_blocks=2)
+        # the reference's default system prompt is 81 characters: the document's chunks sit at an
+        # odd offset of the /infer prompt; the scan finds them at any offset and the engine pads
         with TestClient(ref_app(cfg)) as client:
             assert client.get("/health").json()["vllm"] is True
             text = "the quick brown fox jumps over the lazy dog, twice over and then once more for luck"

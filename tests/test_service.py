@@ -201,6 +201,9 @@ def test_split_at_hits():
             {"offset": 80, "token_count": 20}]                                      # would leave no query: dropped
     segs = split_at_hits(toks, hits, 16)
     assert segs == [toks[0:16], toks[16:48], toks[48:]]
+    odd = [{"offset": 21, "token_count": 32}]
+    assert split_at_hits(toks, odd, 16) == [toks[:21], toks[21:53], toks[53:]]  # the engine client pads the gap
+    assert split_at_hits(toks, odd, 16, aligned_only=True) == [toks]
     assert split_at_hits(toks, [], 16) == [toks]
     assert [t for s in segs for t in s] == toks and segs[-1]
 
