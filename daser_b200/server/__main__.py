@@ -81,7 +81,8 @@ def _build_daser_config(args: argparse.Namespace) -> DaserConfig:
             f"store_size={args.store_size} must be a positive multiple of "
             f"slot_size={slot}"
         )
-    cfg.slot_size = slot
+    # slot_size stays as given (0 = derived from the model parameters, through
+    # resolved_slot_size(), which is what every consumer calls): the reference's behaviour
     cfg.total_slots = args.store_size // slot
     return cfg
 
