@@ -150,6 +150,26 @@ def test_service_process_with_native_engine_starts_quickly_and_answers(tmp_path)
         with urllib.request.urlopen(req, timeout=30) as r:
             out = json.load(r)
         assert out["usage"]["completion_tokens"] == 2 and out["object"] == "text_completion"
+
+        # this repository's client for a remote vLLM, pointed at the native engine instead
+        import asyncio
+
+        from daser_b200.service.vllm_client import VLLMClient
+
+        async def through_the_vllm_client():
+            async with VLLMClient(base, "toy") as c:
+                assert await c.health()
+                chunk = list(range(10, 42))
+                await c.prefill(chunk)  # max_tokens = 1: leaves the chunk in the store
+                reply = await c.completion([5] * 16 + chunk + [7, 8, 9], {"max_tokens": 2, "temperature": 0})
+                return reply["usage"], reply["choices"][0]["text"]
+
+        usage, _ = asyncio.run(through_the_vllm_client())
+        assert usage["completion_tokens"] == 2 and usage["prompt_tokens"] == 51
+        with urllib.request.urlopen(base + "/metrics", timeout=5) as r:
+            text = r.read().decode()
+        hits = [float(l.split()[1]) for l in text.splitlines() if l.startswith("daser_connector_chunk_hits ")]
+        assert hits and hits[0] >= 1  # the prefilled chunk was found behind the 16-token lead and restored
     finally:
         out_text = _stop(proc)
     assert proc.returncode == 0, out_text[-2000:]
