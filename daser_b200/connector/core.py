@@ -27,6 +27,7 @@ What changed relative to the reference:
 from __future__ import annotations
 
 import os
+from collections import OrderedDict
 import threading
 import time
 from dataclasses import dataclass, field
@@ -37,7 +38,7 @@ import torch
 from daser_b200 import metrics
 from daser_b200.config import CODEC_FP8B16
 from daser_b200.connector.ipc_client import IPCClientSync
-from daser_b200.hashing import hash_tokens
+from daser_b200.hashing import hash_tokens, prefix_digests
 from daser_b200.io.engine import preallocate
 from daser_b200.kv import codec
 from daser_b200.kv.layout import KVGeometry, tp_head_range
@@ -108,6 +109,7 @@ class SchedulerHalf:
         self._pending_alloc: dict[str, dict[str, Any]] = {}
         self._stored: set[str] = set()
         self._negotiated = False
+        self._compositions: "OrderedDict[str, int]" = OrderedDict()  # sightings of ordered chunk prefixes
 
     # -- prefix reuse (reference behaviour) -----------------------------------------------
     def get_num_new_matched_tokens(self, req_id: str, prompt_token_ids: Sequence[int],
@@ -196,6 +198,64 @@ class SchedulerHalf:
             )
         self._pending_loads.setdefault(req_id, []).extend(s for s in specs if s is not None)
         return specs
+
+    # -- composed chunks: the KV of an ordered combination, with its cross-attention --------------
+    def composition_keys(self, chunks: Sequence[Sequence[int]]) -> list[str]:
+        """Key of ``chunks[0] + ... + chunks[k]`` for every k (one streaming hash pass).  A
+        combination is stored like any chunk, under the hash of its concatenated tokens: what
+        makes it "composed" is that its KV was computed with the chunks attending to one another."""
+        bt = self.block_tokens
+        flat: list[int] = []
+        ends = []
+        for c in chunks:
+            if len(c) % bt:
+                raise ValueError("chunks must be a whole number of blocks")
+            flat.extend(c)
+            ends.append(len(flat) // bt)
+        digests = prefix_digests(flat, bt)
+        return [digests[e - 1] for e in ends]
+
+    def merge_composed(self, chunks: Sequence[Sequence[int]]) -> list[list[int]]:
+        """Replace the longest stored combination prefix ``chunks[:k]`` (k >= 2) by one chunk.
+
+        The merged chunk sits at offset 0, so it is restored without re-rotation and is exact;
+        the chunks after it are handled one by one as before.  One ``lookup_chunks`` round trip;
+        on any error the list comes back unchanged."""
+        chunks = [list(c) for c in chunks]
+        if len(chunks) < 2:
+            return chunks
+        keys = self.composition_keys(chunks)
+        try:
+            found = self._ipc.lookup_chunks(keys[1:], self.model_id)
+        except RuntimeError:
+            return chunks
+        for k in range(len(chunks), 1, -1):
+            if found[k - 2] is not None:
+                metrics.inc("connector.composed_hits")
+                merged = [t for c in chunks[:k] for t in c]
+                return [merged] + chunks[k:]
+        return chunks
+
+    def note_composition(self, chunks: Sequence[Sequence[int]], threshold: int, max_tracked: int = 4096) -> Optional[list[int]]:
+        """Count sightings of the ordered pair-or-longer prefixes of ``chunks``; returns the
+        concatenated tokens of the longest prefix that has now been seen ``threshold`` times and
+        is not stored yet (the caller computes and stores it), else None."""
+        if threshold <= 0 or len(chunks) < 2:
+            return None
+        keys = self.composition_keys(chunks)
+        best = None
+        for k in range(2, len(chunks) + 1):
+            key = keys[k - 1]
+            n = self._compositions.get(key, 0) + 1
+            self._compositions[key] = n
+            self._compositions.move_to_end(key)
+            if n == threshold:
+                best = k
+        while len(self._compositions) > max_tracked:
+            self._compositions.popitem(last=False)
+        if best is None:
+            return None
+        return [t for c in chunks[:best] for t in c]
 
     def assign_chunk_blocks(self, req_id: str, request_block_ids: Sequence[int]) -> None:
         """Give every queued chunk load of ``req_id`` the request blocks its tokens fall into."""

@@ -63,8 +63,12 @@ class RequestResult:
 class CpuRagEngine:
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 512,
                  codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
-                 io_backend: str = "auto", model_id: str = "default", host_slots: int = 0) -> None:
+                 io_backend: str = "auto", model_id: str = "default", host_slots: int = 0,
+                 compose_after: int = 0) -> None:
         self.cfg = cfg
+        # > 0: an ordered combination of chunks seen this many times is computed once with full
+        # cross-attention and stored; later requests that start with it restore it as one chunk
+        self.compose_after = compose_after
         self.weights = LlamaWeights.random(cfg, "cpu", dtype, seed=seed)
         self.pool = TorchPagedKV(cfg, num_blocks, dtype)
         self.blocks = BlockAllocator(num_blocks)
@@ -162,6 +166,9 @@ class CpuRagEngine:
         """Serve one request to completion with greedy sampling: the same call the GPU engine
         offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
         for signature parity; chunks are only stored through :meth:`store_chunk` here."""
+        asked = [list(c) for c in chunks]
+        if self.compose_after > 0:
+            chunks = self.sched.merge_composed(asked)
         res = self.run_request([], chunks, query, keep_blocks=True)
         bt = self.cfg.block_tokens
         table = list(res.block_table)
@@ -177,6 +184,10 @@ class CpuRagEngine:
                 pos += 1
         finally:
             self.blocks.free(table)
+        if self.compose_after > 0:
+            combo = self.sched.note_composition(asked, self.compose_after)
+            if combo is not None:
+                self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
         return GenerateResult(generated, res.total_tokens, sum(res.restored))
 
     def recompute_chunk_alone(self, chunk: Sequence[int], offset: int) -> tuple[list[int], int]:

@@ -60,8 +60,12 @@ class GpuRagEngine:
                  max_tokens: int = 256, max_seqs: int = 64, hbm_slots: int = 0, host_slots: int = 0,
                  io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
-                 staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True) -> None:
+                 staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True,
+                 compose_after: int = 0) -> None:
         self.cfg = cfg
+        # > 0: an ordered combination of chunks seen this many times is computed once with full
+        # cross-attention and stored; later requests that start with it restore it as one chunk
+        self.compose_after = compose_after
         self.tp = tp_ctx.tp if tp_ctx is not None else 1
         self.rank = tp_ctx.rank if tp_ctx is not None else 0
         self.tp_ctx = tp_ctx
@@ -296,10 +300,18 @@ class GpuRagEngine:
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
                  store_misses: bool = False) -> RagRequest:
         """Serve one request to completion (the call a user of the engine makes)."""
-        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens,
-                                     store_misses=store_misses))
+        asked = [list(c) for c in chunks]
+        merged = asked
+        if self.compose_after > 0:
+            # the rank that owns the scheduler half decides; every rank must serve the same list
+            merged = self._bcast(self.sched.merge_composed(asked) if self.sched is not None else None)
+        req = self.submit(RagRequest(merged, list(query), max_new_tokens, store_misses=store_misses))
         while not req.done:
             self.step()
+        if self.compose_after > 0:
+            combo = self._bcast(self.sched.note_composition(asked, self.compose_after) if self.sched is not None else None)
+            if combo is not None:
+                self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
         return req
 
     def close(self) -> None:

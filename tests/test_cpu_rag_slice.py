@@ -161,3 +161,58 @@ def test_generate_decodes_over_restored_chunks(rag):
     one_warm = eng.generate([[7] * 32], query, max_new_tokens=6)
     assert one_warm.restored_chunks == 1 and one_warm.generated == one_cold.generated
     assert eng.blocks.num_free == free0
+
+
+def test_composed_chunks_are_stored_after_repeats_and_restored_exactly(tmp_path):
+    """With ``compose_after=2`` the second sighting of an ordered chunk pair stores its composed KV
+    (computed with cross-attention); from then on a request that starts with the pair restores
+    it as ONE chunk and produces exactly the tokens of a run that computes everything."""
+    from daser_b200 import metrics
+
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=256, slot_size=geo.slot_size, num_layers=cfg.num_layers,
+                          num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, dtype_bytes=4)
+    lp.plane.position = RopeReencoder(cfg.head_dim, cfg.rope_theta)
+    lp.start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=256, compose_after=2)
+    try:
+        rng = random.Random(9)
+        a, b, c = ([rng.randrange(cfg.vocab_size) for _ in range(32)] for _ in range(3))
+        query = [rng.randrange(cfg.vocab_size) for _ in range(7)]
+        exact = eng.generate([a, b, c], query, max_new_tokens=5)          # nothing stored: all computed (sighting 1)
+        assert exact.restored_chunks == 0
+        second = eng.generate([a, b, c], query, max_new_tokens=5)         # sighting 2: composed [a,b,c] gets stored
+        assert second.generated == exact.generated
+        hits0 = metrics.snapshot().get("connector.composed_hits", 0)
+        third = eng.generate([a, b, c], query, max_new_tokens=5)          # restored as one exact chunk
+        assert metrics.snapshot().get("connector.composed_hits", 0) == hits0 + 1
+        assert third.restored_chunks == 1 and third.generated == exact.generated
+        # a request that shares only the stored prefix [a, b]: also stored at sighting 2 (as part of the longest)?
+        # the longest prefix that reached the threshold was [a, b, c]; [a, b] reached it at the same time and is
+        # covered by it only when c follows, so [a, b, x] falls back to independent chunks
+        other = eng.generate([a, b, list(reversed(c))], query, max_new_tokens=2)
+        assert len(other.generated) == 2
+        # order matters: [b, a, c] is another combination
+        assert eng.sched.merge_composed([b, a, c]) == [b, a, c]
+        assert eng.sched.merge_composed([a, b, c, a])[0] == a + b + c
+    finally:
+        eng.close()
+        lp.stop()
+
+
+def test_composition_counting_and_keys():
+    from daser_b200.connector.core import SchedulerHalf
+    from daser_b200.hashing import hash_tokens
+
+    s = SchedulerHalf("/nonexistent.sock", 16, "m")
+    a, b, c = [1] * 16, [2] * 32, [3] * 16
+    assert s.composition_keys([a, b, c]) == [hash_tokens(a), hash_tokens(a + b), hash_tokens(a + b + c)]
+    assert s.note_composition([a, b, c], 2) is None
+    assert s.note_composition([a, b], 2) == a + b          # [a, b] seen twice now
+    assert s.note_composition([a, b, c], 2) == a + b + c   # and now [a, b, c] too
+    assert s.note_composition([a, b, c], 2) is None        # reported once
+    assert s.note_composition([a], 2) is None and s.note_composition([a, b], 0) is None
+    assert s.merge_composed([a, b]) == [a, b]              # control plane unreachable: unchanged
+    with pytest.raises(ValueError):
+        s.composition_keys([[1] * 5])
