@@ -148,9 +148,10 @@ def main() -> None:
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default="llama3-70b")
     ap.add_argument("--pool", type=int, default=64, help="chunks in the synthetic pool")
-    ap.add_argument("--tp-impl", choices=("fused", "twoshot", "oneshot", "nccl"), default="fused",
+    ap.add_argument("--tp-impl", choices=("fused", "twoshot", "oneshot", "nvls", "nccl"), default="fused",
                     help="fused: GEMM-epilogue reduction over peer memory (one-shot all-reduce for few tokens at "
                          "tp <= 2, reduce-scatter + gated all-gather otherwise); twoshot / oneshot: force one form; "
+                         "nvls: partials stay local, each rank reads the sum through the NVLink multicast mapping; "
                          "nccl: the unfused baseline (same kernels, NCCL all-reduce)")
     ap.add_argument("--k", type=int, default=8, help="chunks per request")
     ap.add_argument("--hbm-frac", type=float, default=0.5, help="fraction of the pool the HBM tier can hold")

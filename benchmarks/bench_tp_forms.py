@@ -9,6 +9,8 @@ token; no store, no restore) with each arrangement in turn:
 
 * ``twoshot``  GEMM epilogue reduce-scatter into the owner's slots + all-gather push gated on flags
 * ``oneshot``  GEMM epilogue stores the partial into every rank's slot, each rank sums locally
+* ``nvls``     (only when named in ``--forms``) the partial stays in the rank's own buffer, every
+               rank reads the sum through the NVLink multicast mapping (``multimem.ld_reduce``)
 * ``nccl``     the unfused baseline: same kernels, NCCL all-reduce of the row-parallel outputs
 
 Every arrangement is warmed up until its CUDA graph is captured, then timed with CUDA events
@@ -52,7 +54,8 @@ def main():
     bt = cfg.block_tokens
     ctx_tokens = -(-args.ctx // bt) * bt
     n_blocks = ctx_tokens // bt
-    ctx = TPContext(cfg, dist.group.WORLD, max_tokens=max(256, args.tokens))
+    forms = [f for f in args.forms.split(",") if f]
+    ctx = TPContext(cfg, dist.group.WORLD, max_tokens=max(256, args.tokens), multicast="nvls" in forms)
     weights = LlamaWeights.random(cfg, "cuda", torch.bfloat16, tp=tp, rank=rank, seed=1)
     if weights.inter_local % gemm.GATE_UP_BLOCK == 0:
         weights.interleave_gate_up_(gemm.GATE_UP_BLOCK)
@@ -60,7 +63,7 @@ def main():
     table = list(range(n_blocks))
     step_tokens = [rng.randrange(cfg.vocab_size) for _ in range(args.tokens)]
     results = {}
-    for form in [f for f in args.forms.split(",") if f]:
+    for form in forms:
         ctx.impl = form
         runner = GpuModelRunner(cfg, weights, n_blocks + 8, max(256, args.tokens), 8, ctx,
                                 max_blocks=max(512, n_blocks + 8))

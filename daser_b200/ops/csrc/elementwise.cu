@@ -63,7 +63,24 @@ struct TpSync {
   uint32_t* signal[DASER_MAX_RANKS];
   int n_signal;
   uint32_t* status;
+  // NVLink multicast alias of x (bf16 only, may be null): when set, the row's values are the SUM
+  // over every rank's buffer at the same offset, fetched with multimem.ld_reduce (the switch
+  // adds the ranks' partials in flight); x itself is not read and n_partials is ignored
+  const __nv_bfloat16* mc_x;
 };
+
+// Sum over all ranks of the 8 bf16 values at the same offset of a multicast-bound buffer, added in
+// fp32 inside the switch.  Only after the arrival counter said that every rank's partial is in its
+// own memory (acquire by thread 0, then the CTA barrier).
+__device__ __forceinline__ void multimem_sum8(const __nv_bfloat16* mc, float (&v)[8]) {
+  uint32_t w[4];
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+               : "l"(mc)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = bf16_lo(w[i]); v[2 * i + 1] = bf16_hi(w[i]); }
+}
 
 __device__ __forceinline__ uint64_t ew_timer_ns() {
   uint64_t t;
@@ -85,7 +102,8 @@ __device__ __forceinline__ uint32_t ew_ld_acquire_sys(const uint32_t* p) {
 // threads with several fragments each when there are rows enough to fill the GPU (bandwidth
 // bound), and up to 1024 threads with one fragment each when there are only a few rows (a
 // token block of a serving step: latency bound, so every load of the row is in flight at once).
-template <typename TIn, int ITERS, int MAXT>
+// MC: the row is read as the in-switch sum over ranks (sync.mc_x) instead of from x.
+template <typename TIn, int ITERS, int MAXT, bool MC = false>
 __global__ void __launch_bounds__(MAXT)
 add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                    const __nv_bfloat16* __restrict__ weight, OutList out, int64_t out_row_offset,
@@ -118,9 +136,10 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
   for (int it = 0; it < ITERS; ++it) {
     const int c = (it * blockDim.x + threadIdx.x) * 8;
     if (c < hidden) {
-      Loader<TIn>::load8(const_cast<TIn*>(xr) + c, v[it], zero_after != 0);
+      if (MC) multimem_sum8(sync.mc_x + row * hidden + c, v[it]);
+      else Loader<TIn>::load8(const_cast<TIn*>(xr) + c, v[it], zero_after != 0);
       // reduce-scatter, bf16 form: x holds one slot of partial rows per source rank
-      for (int pt = 1; pt < n_partials; ++pt) {
+      for (int pt = 1; pt < (MC ? 1 : n_partials); ++pt) {
         float t[8];
         Loader<TIn>::load8(const_cast<TIn*>(xr) + pt * partial_stride + c, t, false);
 #pragma unroll
@@ -374,6 +393,7 @@ typedef struct {
   uint32_t* status;
   const uint32_t* wait_base;
   const uint32_t* done_base;
+  const void* mc_x;  // multicast alias of x: rows are read as the sum over ranks (bf16 x only)
 } DaserTpSync;
 
 DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const void* weight,
@@ -403,6 +423,8 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
     sync.done_counter = tp->done_counter; sync.done_target = tp->done_target;
     sync.n_signal = tp->n_signal; sync.status = tp->status;
     sync.wait_base = tp->wait_base; sync.done_base = tp->done_base;
+    if (tp->mc_x != nullptr && (x_is_fp32 || ((uintptr_t)tp->mc_x & 15))) return DASER_ERR_BAD_ARG;
+    sync.mc_x = (const __nv_bfloat16*)tp->mc_x;
     for (int i = 0; i < tp->n_signal; ++i) sync.signal[i] = tp->signal[i];
   }
 #define NORM_LAUNCH(TIN, IT, MAXT)                                                                    \
@@ -417,7 +439,19 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
   else if (iters <= 4) NORM_LAUNCH(TIN, 4, 256);                            \
   else if (iters <= 8) NORM_LAUNCH(TIN, 8, 256);                            \
   else NORM_LAUNCH(TIN, 16, 256)
-  if (x_is_fp32) { NORM_DISPATCH(float); } else { NORM_DISPATCH(__nv_bfloat16); }
+  if (sync.mc_x != nullptr) {
+    // in-switch sum: bf16 only, and only the shapes a serving step has (rows of up to 16k values)
+    if (iters > 2) return DASER_ERR_TOO_LARGE;
+#define NORM_LAUNCH_MC(IT, MAXT)                                                                             \
+  add_rmsnorm_kernel<__nv_bfloat16, IT, MAXT, true><<<(unsigned)rows, threads, 0, stream>>>(                   \
+      (__nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, \
+      eps, 0, sync, 1, 0)
+    if (few_rows && iters <= 1) NORM_LAUNCH_MC(1, 1024);
+    else if (few_rows) NORM_LAUNCH_MC(2, 1024);
+    else if (iters <= 1) NORM_LAUNCH_MC(1, 256);
+    else NORM_LAUNCH_MC(2, 256);
+#undef NORM_LAUNCH_MC
+  } else if (x_is_fp32) { NORM_DISPATCH(float); } else { NORM_DISPATCH(__nv_bfloat16); }
 #undef NORM_DISPATCH
 #undef NORM_LAUNCH
   return (int)cudaGetLastError();

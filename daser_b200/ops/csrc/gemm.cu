@@ -68,7 +68,9 @@ struct GemmParams {
   int rows_per_owner;
   int64_t ldc;
   int64_t dst_row_offset;  // added to the row inside the owner's buffer (bf16 store epilogue)
-  int bcast;               // bf16 epilogues: store every row to ALL n_owners buffers (one-shot all-reduce)
+  int bcast;               // bf16 epilogues.  1: store every row to ALL n_owners buffers (one-shot all-reduce);
+                           // 2: store every row to c[0] only (this rank's own buffer, which peers read
+                           // through the switch) but still bump all n_owners arrival counters
   void* c[DASER_MAX_RANKS];
   uint32_t* arrive[DASER_MAX_RANKS];  // per-owner arrival counters (may be null)
   uint32_t* status;                   // [0] = timeout flag
@@ -293,9 +295,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             o[v].w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
           }
           // one destination (the row's owner), or every rank's copy when broadcasting
-          const int n_dst = p.bcast ? p.n_owners : 1;
+          const int n_dst = p.bcast == 1 ? p.n_owners : 1;
           for (int d = 0; d < n_dst; ++d) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[p.bcast ? d : owner]) +
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[p.bcast == 1 ? d : (p.bcast ? 0 : owner)]) +
                                  ((p.bcast ? (int64_t)row : local_row) + p.dst_row_offset) * p.ldc + col0;
 #pragma unroll
             for (int v = 0; v < 4; ++v)
@@ -352,9 +354,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               o[v].x = pack_bf16x2(t[2 * v].x, t[2 * v].y); o[v].y = pack_bf16x2(t[2 * v].z, t[2 * v].w);
               o[v].z = pack_bf16x2(t[2 * v + 1].x, t[2 * v + 1].y); o[v].w = pack_bf16x2(t[2 * v + 1].z, t[2 * v + 1].w);
             }
-            const int n_dst = p.bcast ? p.n_owners : 1;
+            const int n_dst = p.bcast == 1 ? p.n_owners : 1;
             for (int d = 0; d < n_dst; ++d) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[p.bcast ? d : owner]) +
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[p.bcast == 1 ? d : (p.bcast ? 0 : owner)]) +
                                    ((p.bcast ? (int64_t)row : local_row) + p.dst_row_offset) * p.ldc + col0;
 #pragma unroll
               for (int v = 0; v < 4; ++v)
@@ -482,7 +484,9 @@ typedef struct {
   float* work;
   int64_t work_ld;
   uint32_t* tile_counters;
-  int32_t bcast;  // 1: the bf16 epilogues store to every c[i] (row + dst_row_offset) and bump every arrive[i]
+  int32_t bcast;  // 1: the bf16 epilogues store to every c[i] (row + dst_row_offset) and bump every arrive[i];
+                  // 2: they store to c[0] only and bump every arrive[i] (the partial stays in this rank's
+                  //    memory; peers fetch the sum with multimem.ld_reduce once all counters are up)
 } DaserGemm;
 
 DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
@@ -503,7 +507,7 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   p.rows_per_owner = g->rows_per_owner;
   p.ldc = g->ldc;
   p.dst_row_offset = g->dst_row_offset;
-  p.bcast = g->bcast ? 1 : 0;
+  p.bcast = g->bcast < 0 || g->bcast > 2 ? 1 : g->bcast;
   if (p.bcast && g->epilogue == EPI_REDUCE_F32) return DASER_ERR_BAD_ARG;
   for (int i = 0; i < DASER_MAX_RANKS; ++i) { p.c[i] = g->c[i]; p.arrive[i] = g->arrive[i]; }
   p.status = g->status;

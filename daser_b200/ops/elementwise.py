@@ -24,6 +24,7 @@ class TpSync(C.Structure):
         ("status", C.c_void_p),
         ("wait_base", C.c_void_p),
         ("done_base", C.c_void_p),
+        ("mc_x", C.c_void_p),
     ]
 
 

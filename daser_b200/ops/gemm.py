@@ -87,6 +87,7 @@ def linear(
     tile_counters: Optional[torch.Tensor] = None,
     ldc: Optional[int] = None,
     broadcast: bool = False,
+    signal_all: bool = False,
     stream=None,
 ) -> torch.Tensor:
     assert x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -112,6 +113,11 @@ def linear(
         # broadcast: the one-shot all-reduce form.  Every rank receives this rank's whole partial
         # (rows are not partitioned: row r lands at dst_row_offset + r of every owner's buffer)
         g.bcast = 1 if broadcast else 0
+        # signal_all: the partial stays in this rank's own buffer (owners[0]); every rank's arrival
+        # counter is bumped, after which peers read the sum through the NVLink multicast mapping
+        if signal_all:
+            assert not broadcast
+            g.bcast = 2
         for i, ptr in enumerate(owners):
             g.c[i] = ptr
         for i, ptr in enumerate(arrive or []):

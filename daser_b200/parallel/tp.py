@@ -18,15 +18,19 @@ GPU and the hot path makes no NCCL call:
   partial into every peer's receive buffer and each rank sums and normalises all rows itself: one
   NVLink hop per sync point, no all-gather (``_forward_body_oneshot``).  At higher degrees the
   tp - 1 copies cost more than the second hop saves (measured), so the two-hop form stays.
+* **in-switch form** (``impl="nvls"``, opt-in): the GEMM keeps its partial in its own memory and only
+  signals; each rank's add + RMSNorm reads the sum of all ranks' partials through the NVLink
+  multicast mapping (``multimem.ld_reduce``: the switch adds in flight).  One hop, T x hidden x 2
+  bytes in per rank whatever tp is.  Needs multicast-mapped buffers (below).
 * **chunk-KV restore** scatters from the IO rank into every rank's paged pool
   (``ops/csrc/kv_paged.cu``); **save** has every rank compress and push its head slice into
   the IO rank's staging buffer.
 
 NCCL is used for bootstrap, barriers between engine steps and the 8-byte-per-sequence
-exchange of greedy-sampling candidates.  No kernel here uses ``multimem``, so the symmetric
-allocations are made without an NVLink multicast object bound to them
-(``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` unless the caller set it): a process that dies while its
-memory is bound to one raises NVLink faults on its peers' GPUs.  Peer liveness is checked on the
+exchange of greedy-sampling candidates.  Only the opt-in in-switch form uses ``multimem``, so by
+default the symmetric allocations are made without an NVLink multicast object bound to them
+(``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` unless the caller set it, or asked for ``multicast``): a
+process that dies while its memory is bound to one raises NVLink faults on its peers' GPUs.  Peer liveness is checked on the
 host between steps (:mod:`daser_b200.parallel.health`).  Buffers that peers touch are allocated with
 ``torch.distributed._symmetric_memory`` (VMM allocations exchanged between the processes).
 All device-side waits are bounded and report through a status word.
@@ -52,19 +56,33 @@ FLAG_OS = 1  # and 2: arrival counters of the two one-shot all-reduce receive bu
 # 19.9, two-hop 14.3, NCCL 15.2.  The one-shot epilogue sends tp - 1 copies of every tile; at 8
 # ranks those stores dominate the GEMM's epilogue.
 ONESHOT_MAX_TP = 2
+FLAG_NV = 3  # and 4: arrival counters of the two in-switch all-reduce buffers
 FLAG_AG = 8  # first of tp per-source "rows landed" flags
 NUM_FLAGS = 16
+IMPLS = ("fused", "twoshot", "oneshot", "nvls", "nccl")
 
 
 class TPContext:
-    def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256, impl: Optional[str] = None) -> None:
+    def __init__(self, cfg: LlamaConfig, group: Any, max_tokens: int = 256, impl: Optional[str] = None,
+                 multicast: Optional[bool] = None) -> None:
         # "fused": the path this module is about.  "nccl": the unfused arrangement it is measured
         # against (same kernels, replicated activations, NCCL all-reduce after the row-parallel GEMMs).
         # "twoshot" / "oneshot" force one form of the fused reduction at every size and degree.
+        # "nvls": the in-switch form (needs `multicast`); opt-in, see `_forward_body_nvls`.
         self.impl = impl or os.environ.get("DASER_TP_IMPL", "fused")
-        if self.impl not in ("fused", "twoshot", "oneshot", "nccl"):
+        if self.impl not in IMPLS:
             raise ValueError(f"unknown tensor-parallel implementation {self.impl!r}")
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        # Symmetric allocations get an NVLink multicast mapping only on request: a process that dies
+        # while its memory is bound to one raises NVLink faults on its peers' GPUs, so deployments
+        # that must survive a lost rank keep it off.
+        if multicast is None:
+            multicast = self.impl == "nvls" or os.environ.get("DASER_TP_MULTICAST", "0") == "1"
+        self.multicast = bool(multicast)
+        if self.multicast:
+            if os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST") == "1":
+                raise ValueError("multicast requested but TORCH_SYMM_MEM_DISABLE_MULTICAST=1 is set")
+        else:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         self._symm = symm_mem
@@ -103,6 +121,20 @@ class TPContext:
         self.os_cap = min(max_tokens, int(os.environ.get("DASER_TP_ONESHOT_MAX", "256")))
         self.os_buf = [self.alloc(f"os_{i}", (self.tp * self.os_cap, H), torch.bfloat16) for i in range(2)]
         self.epochs_os = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # in-switch all-reduce: two alternating buffers that hold this rank's own partial (os_cap rows);
+        # peers read the sum of all ranks' buffers through the multicast alias of the same range
+        self.nv_buf: list[torch.Tensor] = []
+        self.nv_mc: list[int] = []
+        self.epochs_nv = torch.zeros(4, dtype=torch.int32, device=self.device)
+        if self.multicast:
+            for i in range(2):
+                self.nv_buf.append(self.alloc(f"nv_{i}", (self.os_cap, H), torch.bfloat16))
+                self.nv_buf[i].zero_()
+                self.nv_mc.append(int(getattr(self._handles[f"nv_{i}"], "multicast_ptr", 0) or 0))
+            if not all(self.nv_mc):
+                if self.impl == "nvls":
+                    raise RuntimeError("no NVLink multicast mapping for the symmetric buffers (NVLS unavailable)")
+                self.nv_buf, self.nv_mc = [], []
         self.save_staging: Optional[torch.Tensor] = None
         self.health: Optional[PeerMonitor] = None
         if os.environ.get("DASER_TP_HEALTH", "1") != "0":
@@ -230,6 +262,8 @@ class TPContext:
             raise ValueError("step exceeds the tensor-parallel buffers")
         if self.impl == "nccl":
             return self._forward_body_nccl(runner, inp, nsplit, split_tokens)
+        if self.impl == "nvls":
+            return self._forward_body_nvls(runner, inp, nsplit, split_tokens)
         if self.impl == "oneshot" or (self.impl == "fused" and self.tp <= ONESHOT_MAX_TP and T <= self.os_cap):
             return self._forward_body_oneshot(runner, inp, nsplit, split_tokens)
         self._rs_off = self._ag_off = self._done_off = 0
@@ -322,6 +356,72 @@ class TPContext:
             nxt = w.final_norm if last else w.layers[li + 1].input_norm
             self._norm_sum(runner, 1, nxt, h, self.gathered[:T] if last else normed, T, offs)
         ew.advance_epochs(self.epochs_os, offs[0], offs[1], 0)
+
+    # -- in-switch form: partial stays local, the reader sums through the NVLink multicast mapping ----
+    def _forward_body_nvls(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+        """The one-shot form with the NVSwitch doing the sum.
+
+        Each row-parallel GEMM stores its bf16 partial into this rank's OWN buffer (local stores
+        only: nothing crosses NVLink in the epilogue) and bumps every rank's arrival counter; each
+        rank's add + RMSNorm waits for the tp x tiles arrivals and then reads every row through
+        the multicast alias with ``multimem.ld_reduce`` (the switch fetches the tp partials and adds
+        them in fp32 on the way), adds the residual and normalises all rows.  Per sync point and
+        rank: T x hidden x 2 bytes come in over NVLink, whatever tp is, against tp - 1 times that
+        going out in the store form; one hop, no all-gather, two sync points per layer.  Buffer
+        reuse follows the one-shot form's argument (two alternating buffers; a rank can only pass
+        sync point k + 1 after every peer has finished reading at sync point k).
+
+        Needs symmetric buffers with a multicast mapping (``multicast=True``), which a deployment
+        that must survive a lost rank keeps off: hence opt-in.
+        """
+        if not self.nv_mc:
+            raise RuntimeError("the in-switch form needs a context built with multicast=True")
+        cfg, w = self.cfg, runner.w
+        T = inp.num_tokens
+        if T > self.os_cap:
+            raise ValueError("step exceeds the in-switch all-reduce buffers")
+        D, B = cfg.head_dim, cfg.block_tokens
+        h, normed = runner.h[:T], runner.normed[:T]
+        offs = [0, 0]
+
+        def row_gemm(x: torch.Tensor, wt: torch.Tensor, which: int) -> None:
+            N, K = wt.shape
+            bn, ks = (128, 4) if K >= 8192 and T <= 128 else (64, 1)
+            if -(-T // 128) * -(-N // 128) >= 148:
+                bn, ks = 128, 1
+            offs[which] += self.tp * -(-T // 128) * -(-N // bn)
+            gemm.linear(x, wt, owners=[self.nv_buf[which].data_ptr()] * self.tp, rows_per_owner=self.os_cap, ldc=N,
+                        block_n=bn, k_splits=ks, scatter_bf16=True, dst_row_offset=0, signal_all=True,
+                        work=runner.hid_acc[:T], tile_counters=self.tile_counters,
+                        arrive=[self.flag_ptr(r, FLAG_NV + which) for r in range(self.tp)], status=runner.status)
+
+        def norm_sum(which: int, weight: torch.Tensor, out: torch.Tensor) -> None:
+            sync = ew.TpSync()
+            sync.wait_counter = self.flag_ptr(self.rank, FLAG_NV + which)
+            sync.wait_target = offs[which]
+            sync.wait_base = self.epochs_nv.data_ptr() + 4 * which
+            sync.status = runner.status.data_ptr()
+            sync.mc_x = self.nv_mc[which]
+            ew.add_rmsnorm(self.nv_buf[which][:T], weight, residual=h, out=out, eps=cfg.rms_eps, zero_after=False,
+                           tp_sync=sync)
+
+        ew.embedding(inp.tokens, w.embed, out=h)
+        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li, lw in enumerate(w.layers):
+            qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
+            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+            attn = runner.attn_out[:T].view(T, runner.hq, D)
+            attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
+                                      inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
+                                      runner.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
+            row_gemm(runner.attn_out[:T], lw.wo, 0)
+            norm_sum(0, lw.post_norm, normed)
+            runner.mlp_up(normed, lw, T)
+            row_gemm(runner.act[:T], lw.w_down, 1)
+            last = li + 1 == len(w.layers)
+            norm_sum(1, w.final_norm if last else w.layers[li + 1].input_norm, self.gathered[:T] if last else normed)
+        ew.advance_epochs(self.epochs_nv, offs[0], offs[1], 0)
 
     def _forward_body_nccl(self, runner, inp, nsplit: int, split_tokens: int) -> None:
         """The baseline: what stock tensor parallelism does (``vllm/model_executor/layers/linear.py``,

@@ -48,7 +48,8 @@ def main() -> None:
     ok = True
     # the other arrangements of the same shards (reduce-scatter + all-gather at every size; plain
     # NCCL all-reduce) must agree with the default one (one-shot all-reduce at this step size)
-    for other in ("twoshot", "nccl"):
+    # (with DASER_TP_MULTICAST=1 the context has multicast-mapped buffers and the in-switch form joins)
+    for other in ("twoshot", "nccl") + (("nvls",) if ctx.nv_mc else ()):
         ctx.impl = other
         other_runner = GpuModelRunner(cfg, shard_weights(full, tp, rank), 64, 128, 8, ctx, use_graphs=False)
         got_other = []
