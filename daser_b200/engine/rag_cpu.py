@@ -14,7 +14,7 @@ only lookup matches whole prompt prefixes, and nothing applies ``pos_offset``
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Sequence
+from typing import Optional, Sequence
 
 import torch
 
@@ -83,6 +83,19 @@ class CpuRagEngine:
                                  host_store=self.host)
         self._req = 0
 
+    # -- hooks a multi-process arrangement overrides (pipeline stages: parallel/pp.py) ------------
+    def _lead(self, fn):
+        """Run ``fn`` where the scheduler half lives; every process gets its result."""
+        return fn()
+
+    def _forward(self, tokens: Sequence[int], positions: torch.Tensor, table: torch.Tensor, context_len: int,
+                 return_logits: bool = True) -> Optional[torch.Tensor]:
+        return reference_forward(self.weights, torch.tensor(list(tokens)), positions, self.pool, table, context_len,
+                                 return_logits=return_logits)
+
+    def _sample(self, logits: Optional[torch.Tensor]) -> int:
+        return int(logits[-1].argmax())
+
     def _next_id(self) -> str:
         self._req += 1
         return f"req-{self._req}"
@@ -106,16 +119,15 @@ class CpuRagEngine:
             raise ValueError("chunks must be a whole number of blocks")
         req = self._next_id()
         table = self.blocks.alloc(len(tokens) // bt)
-        spec = self.sched.reserve_chunk_store(req, tokens, table, pos_offset=0)
-        meta = self.sched.build_connector_meta([req]) if spec is not None else ConnectorMeta()
 
-        def run():
-            t = torch.tensor(tokens)
-            reference_forward(self.weights, t, torch.arange(len(tokens)), self.pool, torch.tensor(table), 0,
-                              return_logits=False)
+        def plan():
+            spec = self.sched.reserve_chunk_store(req, tokens, table, pos_offset=0)
+            return self.sched.build_connector_meta([req]) if spec is not None else ConnectorMeta()
 
-        self._step(meta, run)
-        self.sched.request_finished(req)
+        meta = self._lead(plan)
+        self._step(meta, lambda: self._forward(tokens, torch.arange(len(tokens)), torch.tensor(table), 0,
+                                               return_logits=False))
+        self._lead(lambda: self.sched.request_finished(req))
         self.blocks.free(table)
         return hash_tokens(tokens)
 
@@ -136,27 +148,28 @@ class CpuRagEngine:
         table = self.blocks.alloc(-(-total // bt))
         tbl = torch.tensor(table)
         placements = [(hash_tokens(list(c)), off) for c, off in zip(chunks, offsets)]
-        specs = self.sched.plan_chunk_loads(req, placements)
-        self.sched.assign_chunk_blocks(req, table)
-        meta = self.sched.build_connector_meta([req])
+
+        def plan():
+            found = self.sched.plan_chunk_loads(req, placements)
+            self.sched.assign_chunk_blocks(req, table)
+            return found, self.sched.build_connector_meta([req])
+
+        specs, meta = self._lead(plan)
 
         def run():
             # the prefix is computed, then every chunk that could not be restored, then the query
             ctx = 0
             if prefix:
-                reference_forward(self.weights, torch.tensor(list(prefix)), torch.arange(len(prefix)), self.pool,
-                                  tbl, 0, return_logits=False)
+                self._forward(prefix, torch.arange(len(prefix)), tbl, 0, return_logits=False)
             ctx = len(prefix)
             for c, off, spec in zip(chunks, offsets, specs):
                 if spec is None:
-                    reference_forward(self.weights, torch.tensor(list(c)), torch.arange(off, off + len(c)),
-                                      self.pool, tbl, ctx, return_logits=False)
+                    self._forward(c, torch.arange(off, off + len(c)), tbl, ctx, return_logits=False)
                 ctx = off + len(c)
-            return reference_forward(self.weights, torch.tensor(list(query)), torch.arange(ctx, ctx + len(query)),
-                                     self.pool, tbl, ctx)
+            return self._forward(query, torch.arange(ctx, ctx + len(query)), tbl, ctx)
 
         logits = self._step(meta, run)
-        self.sched.request_finished(req)
+        self._lead(lambda: self.sched.request_finished(req))
         if not keep_blocks:
             self.blocks.free(table)
         return RequestResult(logits, table, offsets, [s is not None for s in specs], total)
@@ -168,24 +181,23 @@ class CpuRagEngine:
         for signature parity; chunks are only stored through :meth:`store_chunk` here."""
         asked = [list(c) for c in chunks]
         if self.compose_after > 0:
-            chunks = self.sched.merge_composed(asked)
+            chunks = self._lead(lambda: self.sched.merge_composed(asked))
         res = self.run_request([], chunks, query, keep_blocks=True)
         bt = self.cfg.block_tokens
         table = list(res.block_table)
-        generated = [int(res.logits[-1].argmax())]
+        generated = [self._sample(res.logits)]
         pos = res.total_tokens
         try:
             while len(generated) < max_new_tokens:
                 if pos // bt >= len(table):
                     table.extend(self.blocks.alloc(1))
-                logits = reference_forward(self.weights, torch.tensor([generated[-1]]), torch.tensor([pos]), self.pool,
-                                           torch.tensor(table), pos)
-                generated.append(int(logits[-1].argmax()))
+                logits = self._forward([generated[-1]], torch.tensor([pos]), torch.tensor(table), pos)
+                generated.append(self._sample(logits))
                 pos += 1
         finally:
             self.blocks.free(table)
         if self.compose_after > 0:
-            combo = self.sched.note_composition(asked, self.compose_after)
+            combo = self._lead(lambda: self.sched.note_composition(asked, self.compose_after))
             if combo is not None:
                 self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
         return GenerateResult(generated, res.total_tokens, sum(res.restored))
@@ -199,8 +211,7 @@ class CpuRagEngine:
         """
         bt = self.cfg.block_tokens
         table = self.blocks.alloc(len(chunk) // bt)
-        reference_forward(self.weights, torch.tensor(list(chunk)), torch.arange(offset, offset + len(chunk)),
-                          self.pool, torch.tensor(table), 0, return_logits=False)
+        self._forward(chunk, torch.arange(offset, offset + len(chunk)), torch.tensor(table), 0, return_logits=False)
         return table, len(chunk)
 
     def close(self) -> None:

@@ -222,12 +222,14 @@ class TorchPagedKV:
     """Head-major paged pool ``[L, N, 2, H, B, D]`` in a torch dtype (the CPU engine's pool)."""
 
     def __init__(self, cfg: LlamaConfig, num_blocks: int, dtype: torch.dtype = torch.float32,
-                 device: str | torch.device = "cpu", kv_heads: Optional[int] = None) -> None:
+                 device: str | torch.device = "cpu", kv_heads: Optional[int] = None,
+                 num_layers: Optional[int] = None) -> None:
         self.cfg = cfg
         self.num_blocks = num_blocks
         self.kv_heads = kv_heads or cfg.num_kv_heads
+        # num_layers: a pipeline stage keeps only its own layers' KV
         self.data = torch.zeros(
-            cfg.num_layers, num_blocks, 2, self.kv_heads, cfg.block_tokens, cfg.head_dim, dtype=dtype, device=device
+            num_layers or cfg.num_layers, num_blocks, 2, self.kv_heads, cfg.block_tokens, cfg.head_dim, dtype=dtype, device=device
         )
 
     def write(self, layer: int, block_ids: torch.Tensor, offsets: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
@@ -256,8 +258,16 @@ def reference_forward(
     block_table: torch.Tensor,
     context_len: int,
     return_logits: bool = True,
+    layers: Optional[range] = None,
+    hidden_in: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Run ``tokens`` (at ``positions``) of ONE sequence through the model.
+
+    ``layers`` restricts the pass to a contiguous range of decoder layers (a pipeline stage):
+    a range that does not start at 0 takes its input from ``hidden_in`` instead of the
+    embedding, a range that does not end at the last layer returns the residual stream
+    ``[T, hidden]`` (fp32) without the final norm, and ``pool`` then holds only the stage's own
+    layers (layer ``i`` of the model is pool layer ``i - layers.start``).
 
     The sequence already has ``context_len`` tokens cached in ``pool`` (written earlier or
     restored by the connector); the new tokens occupy cache slots ``context_len ..``.
@@ -276,8 +286,13 @@ def reference_forward(
     blk = block_table.to(dev)[slots // cfg.block_tokens]
     off = slots % cfg.block_tokens
     total = context_len + T
-    h = weights.embed[tokens.to(dev).long()].float()
-    for li, lw in enumerate(weights.layers):
+    stage = layers if layers is not None else range(len(weights.layers))
+    if stage.start == 0:
+        h = weights.embed[tokens.to(dev).long()].float()
+    else:
+        assert hidden_in is not None and hidden_in.shape == (T, cfg.hidden)
+        h = hidden_in.to(dev).float()
+    for li, lw in ((i - stage.start, weights.layers[i]) for i in stage):
         x = rms_norm(h, lw.input_norm, cfg.rms_eps)
         qkv = x @ lw.wqkv.float().t()
         q = qkv[:, : Hq * D].reshape(T, Hq, D)
@@ -299,6 +314,8 @@ def reference_forward(
         gu = x @ weights.gate_up_plain(lw).float().t()
         inter = gu.shape[1] // 2
         h = h + (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]) @ lw.w_down.float().t()
+    if stage.stop != len(weights.layers):
+        return h
     h = rms_norm(h, weights.final_norm, cfg.rms_eps)
     if not return_logits:
         return h

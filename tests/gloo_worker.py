@@ -13,6 +13,9 @@ Scenarios, chosen by ``argv[1]``; RANK / WORLD_SIZE / MASTER_PORT come from the 
 ``serve``   the leader / follower layer that puts a tensor-parallel engine behind one HTTP front
             end: rank 0 announces every engine call, the other ranks replay it; all ranks must
             have executed the same calls with the same arguments, in the same order.
+``pipeline`` every rank one pipeline stage of the oracle engine (layer ranges, per-stage store
+            files, multi-part commits, activations over point-to-point sends); tokens and logits must
+            equal those of a single process with all layers.
 ``late``    rank 0 alone of a two-rank world: the rendezvous must end with an error inside
             its time limit instead of waiting for ever.
 """
@@ -244,6 +247,96 @@ def scenario_late() -> int:
     return 1
 
 
+def _start_plane(tmp: str, name: str, slot_size: int, position=None):
+    from daser_b200.server.__main__ import ControlPlane
+
+    cfg = DaserConfig(store_path=f"{tmp}/{name}.unused", index_path="", total_slots=256, slot_size=slot_size,
+                      ipc_socket_path=f"{tmp}/{name}.sock")
+    plane = ControlPlane(cfg, position_encoder=position)
+    loop = asyncio.new_event_loop()
+    ready = threading.Event()
+
+    def serve():
+        asyncio.set_event_loop(loop)
+        loop.run_until_complete(plane.start())
+        ready.set()
+        loop.run_forever()
+
+    threading.Thread(target=serve, daemon=True).start()
+    ready.wait(20)
+    return plane, loop
+
+
+def scenario_pipeline() -> int:
+    """Every rank is one pipeline stage of the oracle engine (5 layers over WORLD_SIZE stages, so
+    the split is uneven); rank 0 also runs the control plane, and a lone single-process engine on
+    a control plane of its own to compare with."""
+    import dataclasses
+    import random
+
+    from daser_b200.engine.rag_cpu import CpuRagEngine
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.parallel.pp import PipelineCpuEngine, partition_layers, stage_geometry
+    from daser_b200.position import RopeReencoder
+
+    rank, world = _init()
+    cfg = dataclasses.replace(PRESETS["toy"], num_layers=5)
+    tmp = _bcast(tempfile.mkdtemp(prefix="daser_pp_") if rank == 0 else None)
+    geo = stage_geometry(cfg, world)
+    planes = []
+    if rank == 0:
+        planes.append(_start_plane(tmp, "pp", geo.slot_size, RopeReencoder(cfg.head_dim, cfg.rope_theta)))
+    dist.barrier()
+    eng = PipelineCpuEngine(cfg, f"{tmp}/pp.sock", f"{tmp}/pp.store", num_blocks=128, io_backend="posix")
+    ok = eng.layers == partition_layers(5, world)[rank] and geo.num_layers == -(-5 // world)
+    rng = random.Random(4)
+    chunks = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (32, 48, 32)]
+    query = [rng.randrange(cfg.vocab_size) for _ in range(7)]
+    probe = IPCClientSync(f"{tmp}/pp.sock")
+
+    keys = [eng.store_chunk(c) for c in chunks[:2]]                      # chunk 2 stays unknown: computed
+    ok = ok and all(m is not None for m in probe.lookup_chunks(keys, "default"))
+    res = eng.run_request([], [chunks[1], chunks[2], chunks[0]], query)   # restored, computed, restored
+    ok = ok and res.restored == [True, False, True]
+    ok = ok and (res.logits is not None) == (rank == world - 1)
+    gen = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=4)
+    ok = ok and gen.restored_chunks == 2 and len(gen.generated) == 4
+
+    if rank == 0:
+        # the same calls on one process with all layers
+        from daser_b200.kv.layout import KVGeometry as G
+
+        g1 = G(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+        planes.append(_start_plane(tmp, "one", g1.slot_size, RopeReencoder(cfg.head_dim, cfg.rope_theta)))
+        lone = CpuRagEngine(cfg, f"{tmp}/one.sock", f"{tmp}/one.store", num_blocks=128, io_backend="posix")
+        for c in chunks[:2]:
+            lone.store_chunk(c)
+        want = lone.run_request([], [chunks[1], chunks[2], chunks[0]], query)
+        want_gen = lone.generate([chunks[1], chunks[0]], query, max_new_tokens=4)
+        lone.close()
+        ok = ok and want_gen.generated == gen.generated
+        want_logits = want.logits
+    else:
+        want_logits = None
+    want_logits = _bcast(want_logits)
+    if rank == world - 1:
+        err = (res.logits - want_logits).abs().max().item()
+        print(f"pipeline logits max abs diff {err:.2e}", flush=True)
+        ok = ok and err < 1e-3
+
+    flags = [None] * world
+    dist.all_gather_object(flags, bool(ok))
+    eng.close()
+    probe.close()
+    dist.barrier()
+    for plane, loop in planes:
+        asyncio.run_coroutine_threadsafe(plane.stop(save=False), loop).result(10)
+        loop.call_soon_threadsafe(loop.stop)
+    if rank == 0:
+        print("PIPELINE_OK" if all(flags) else f"PIPELINE_FAIL {flags}", flush=True)
+    return 0 if all(flags) else 1
+
+
 if __name__ == "__main__":
     sys.exit({"parts": scenario_parts, "health": scenario_health, "serve": scenario_serve,
-              "late": scenario_late}[sys.argv[1]]())
+              "late": scenario_late, "pipeline": scenario_pipeline}[sys.argv[1]]())

@@ -53,6 +53,13 @@ def test_followers_replay_the_leaders_engine_calls():
     assert "SERVE_OK" in outs[0][1]
 
 
+def test_pipeline_stages_match_a_single_process():
+    for world in (2, 3):
+        outs = _launch("pipeline", world, timeout=180)
+        assert all(rc == 0 for rc, _ in outs), "\n".join(o[-2000:] for _, o in outs)
+        assert "PIPELINE_OK" in outs[0][1]
+
+
 def test_rank_missing_at_rendezvous_fails_within_the_time_limit():
     outs = _launch("late", 2, ranks=[0], timeout=60)
     assert outs[0][0] == 7, outs[0][1][-2000:]
