@@ -30,7 +30,6 @@ from daser_b200.engine.runner import GpuModelRunner
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.hbm_store import HBMStore
 from daser_b200.models.llama import LlamaConfig, LlamaWeights
-from daser_b200.ops import kv_ops  # noqa: F401
 from daser_b200.ops import gemm as gemm_ops
 from daser_b200.utils import trace
 

@@ -38,7 +38,6 @@ All device-side waits are bounded and report through a status word.
 
 from __future__ import annotations
 
-import ctypes as C
 import os
 from typing import Any, Optional
 
