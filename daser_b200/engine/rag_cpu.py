@@ -175,10 +175,11 @@ class CpuRagEngine:
         return RequestResult(logits, table, offsets, [s is not None for s in specs], total)
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
-                 store_misses: bool = False) -> "GenerateResult":
+                 store_misses: bool = False, on_token=None) -> "GenerateResult":
         """Serve one request to completion with greedy sampling: the same call the GPU engine
         offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
-        for signature parity; chunks are only stored through :meth:`store_chunk` here."""
+        for signature parity; chunks are only stored through :meth:`store_chunk` here.
+        ``on_token(token_id)`` is called as each token is sampled (streaming front ends)."""
         asked = [list(c) for c in chunks]
         if self.compose_after > 0:
             chunks = self._lead(lambda: self.sched.merge_composed(asked))
@@ -186,6 +187,8 @@ class CpuRagEngine:
         bt = self.cfg.block_tokens
         table = list(res.block_table)
         generated = [self._sample(res.logits)]
+        if on_token is not None:
+            on_token(generated[-1])
         pos = res.total_tokens
         try:
             while len(generated) < max_new_tokens:
@@ -193,6 +196,8 @@ class CpuRagEngine:
                     table.extend(self.blocks.alloc(1))
                 logits = self._forward([generated[-1]], torch.tensor([pos]), torch.tensor(table), pos)
                 generated.append(self._sample(logits))
+                if on_token is not None:
+                    on_token(generated[-1])
                 pos += 1
         finally:
             self.blocks.free(table)

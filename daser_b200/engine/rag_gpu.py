@@ -297,16 +297,24 @@ class GpuRagEngine:
         self.blocks.free(req.block_table)
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
-                 store_misses: bool = False) -> RagRequest:
-        """Serve one request to completion (the call a user of the engine makes)."""
+                 store_misses: bool = False, on_token=None) -> RagRequest:
+        """Serve one request to completion (the call a user of the engine makes).
+
+        ``on_token(token_id)`` is called after each engine step with every token the step added
+        (a streaming front end sends the first one on as soon as the prefill step has ended)."""
         asked = [list(c) for c in chunks]
         merged = asked
         if self.compose_after > 0:
             # the rank that owns the scheduler half decides; every rank must serve the same list
             merged = self._bcast(self.sched.merge_composed(asked) if self.sched is not None else None)
         req = self.submit(RagRequest(merged, list(query), max_new_tokens, store_misses=store_misses))
+        sent = 0
         while not req.done:
             self.step()
+            if on_token is not None:
+                for tok in req.generated[sent:]:
+                    on_token(int(tok))
+                sent = len(req.generated)
         if self.compose_after > 0:
             combo = self._bcast(self.sched.note_composition(asked, self.compose_after) if self.sched is not None else None)
             if combo is not None:

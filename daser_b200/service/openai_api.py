@@ -18,15 +18,20 @@ control plane (``lookup_chunks`` with tokens: every stored chunk that appears at
 offset), the prompt is cut at the hits, and the pieces go to the engine as segments: hits are
 restored (keys re-rotated to their new positions), the gaps and the tail are computed.  Sampling is
 greedy; ``temperature`` and the other sampling fields are accepted and ignored.
+
+``"stream": true`` answers with server-sent events, one per sampled token (vLLM's shape), so a
+client sees the first token when the prefill step ends rather than when the request does.
 """
 
 from __future__ import annotations
 
+import json
 import time
 import uuid
 from typing import Any, Optional, Sequence
 
 from fastapi import FastAPI, HTTPException
+from fastapi.responses import StreamingResponse
 from pydantic import BaseModel
 
 from daser_b200 import metrics
@@ -70,6 +75,38 @@ def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_t
     return segments
 
 
+async def _sse(engine_client: Any, req: CompletionRequest, tokens: list[int], segments: list[list[int]],
+               model_name: str, t0: float):
+    """Server-sent events in vLLM's shape: one ``text_completion`` object per token, a last one with
+    ``finish_reason`` and ``usage``, then ``data: [DONE]``.  The first event is the time to first
+    token as an HTTP client sees it (recorded as ``service.stream_ttft_ms``)."""
+    rid = "cmpl-" + uuid.uuid4().hex
+    base = {"id": rid, "object": "text_completion", "created": int(t0), "model": req.model or model_name}
+    first = True
+    try:
+        async for item in engine_client.completion_stream(tokens, {"max_tokens": req.max_tokens}, segments=segments):
+            if item.get("done"):
+                usage = item["usage"]
+                n_out = int(usage.get("completion_tokens", 0))
+                last = dict(base, choices=[{"index": 0, "text": "", "token_ids": [], "logprobs": None,
+                                            "finish_reason": "length"}],
+                            usage={"prompt_tokens": len(tokens), "completion_tokens": n_out,
+                                   "total_tokens": len(tokens) + n_out})
+                yield f"data: {json.dumps(last)}\n\n"
+                break
+            if first:
+                metrics.observe("service.stream_ttft_ms", (time.time() - t0) * 1e3)
+                first = False
+            event = dict(base, choices=[{"index": 0, "text": item["text"], "token_ids": item["token_ids"],
+                                         "logprobs": None, "finish_reason": None}])
+            yield f"data: {json.dumps(event)}\n\n"
+    except Exception as exc:  # the status line has gone out already: report in-band, as vLLM does
+        logger.warning("[SERVICE] streamed completion failed: %s", exc)
+        yield f"data: {json.dumps({'error': {'message': f'engine failed: {exc}', 'code': 502}})}\n\n"
+    metrics.observe("service.completion_ms", (time.time() - t0) * 1e3)
+    yield "data: [DONE]\n\n"
+
+
 def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket_path: str, model_name: str,
                         model_id: str = "default", block_tokens: int = 16) -> None:
     ipc = IPCClientAsync(socket_path)
@@ -79,9 +116,7 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
         return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "daser_b200"}]}
 
     @app.post("/v1/completions")
-    async def completions(req: CompletionRequest) -> dict[str, Any]:
-        if req.stream:
-            raise HTTPException(400, "streaming is not supported")
+    async def completions(req: CompletionRequest) -> Any:
         prompt = req.prompt
         if isinstance(prompt, str):
             tokens = list(tokenizer(prompt, add_special_tokens=False)["input_ids"])
@@ -104,6 +139,11 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             logger.warning("[SERVICE] scan failed (%s): computing the whole prompt", exc)
             hits = []
         segments = split_at_hits(tokens, hits, block_tokens)
+        if req.stream:
+            if not hasattr(engine_client, "completion_stream"):
+                raise HTTPException(400, "streaming is not supported by this engine client")
+            return StreamingResponse(_sse(engine_client, req, tokens, segments, model_name, t0),
+                                     media_type="text/event-stream")
         try:
             out = await engine_client.completion(tokens, {"max_tokens": req.max_tokens}, segments=segments)
             aligned = len(tokens) // block_tokens * block_tokens

@@ -57,10 +57,13 @@ class TPLeaderEngine:
         self._announce(CMD_STORE, tokens)
         return self._engine.store_chunk(tokens)
 
-    def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1, **kw: Any):
+    def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
+                 on_token: Optional[Callable[[int], None]] = None, **kw: Any):
         chunks = [list(c) for c in chunks]
         query = list(query)
         self._announce(CMD_GENERATE, chunks, query, int(max_new_tokens), dict(kw))
+        if on_token is not None:  # a local observer: the followers neither need nor could receive it
+            kw = dict(kw, on_token=on_token)
         return self._engine.generate(chunks, query, max_new_tokens=max_new_tokens, **kw)
 
     def warm_up(self, *args: Any, **kw: Any) -> None:

@@ -108,11 +108,12 @@ class NativeEngineClient:
         t = list(tokens)
         return t + [self._pad] * (-len(t) % bt)
 
-    def _generate(self, segments, query, max_new):
+    def _generate(self, segments, query, max_new, on_token=None):
         eng = self._engine
         chunks = [self._pad_block(s) for s in segments if len(s)]
         if hasattr(eng, "generate"):
-            req = eng.generate(chunks, list(query), max_new_tokens=max_new)
+            kw = {"on_token": on_token} if on_token is not None else {}
+            req = eng.generate(chunks, list(query), max_new_tokens=max_new, **kw)
             return req.generated, req.context_len
         res = eng.run_request([], chunks, list(query))
         return [int(res.logits[-1].argmax())], res.total_tokens
@@ -134,3 +135,39 @@ class NativeEngineClient:
             "choices": [{"text": self._detok(gen), "token_ids": gen}],
             "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)},
         }
+
+    async def completion_stream(self, tokens: list[int], gen_params: Optional[dict[str, Any]] = None,
+                                segments: Optional[Sequence[Sequence[int]]] = None):
+        """Async generator over the request's tokens as the engine samples them: yields
+        ``{"token_ids": [id], "text": piece}`` per token and a last item
+        ``{"done": True, "usage": {...}}``.  The first item leaves as soon as the prefill step has
+        ended, which is what makes the time to first token visible to an HTTP client."""
+        params = gen_params or {}
+        max_new = int(params.get("max_tokens", 256))
+        if segments:
+            *cached, query = segments
+        else:
+            cached, query = [], tokens
+        loop = asyncio.get_running_loop()
+        queue: asyncio.Queue = asyncio.Queue()
+        async with self._lock:
+            fut = loop.run_in_executor(None, self._guard, self._generate, cached, query, max_new,
+                                       lambda tok: loop.call_soon_threadsafe(queue.put_nowait, int(tok)))
+            fut.add_done_callback(lambda _f: queue.put_nowait(None))  # runs on the loop: after every token
+            sent: list[int] = []
+            text = ""
+            while True:
+                tok = await queue.get()
+                if tok is None:
+                    break
+                sent.append(tok)
+                # detokenise the whole run and send the new suffix: pieces of one token can change
+                # with what follows (byte-level merges)
+                full = self._detok(sent)
+                piece, text = (full[len(text):], full) if full.startswith(text) else (full, full)
+                yield {"token_ids": [tok], "text": piece}
+            gen, prompt_len = await fut  # raises here if the engine failed
+            if len(sent) < len(gen):  # an engine without token callbacks: everything at the end
+                rest = gen[len(sent):]
+                yield {"token_ids": rest, "text": self._detok(gen)[len(text):]}
+        yield {"done": True, "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)}}

@@ -249,7 +249,20 @@ def test_openai_completions_reuse_stored_chunks_found_by_scan(tmp_path):
             # bad requests
             assert client.post("/v1/completions", json={"prompt": [], "max_tokens": 1}).status_code == 400
             assert client.post("/v1/completions", json={"prompt": prompt, "max_tokens": 0}).status_code == 400
-            assert client.post("/v1/completions", json={"prompt": prompt, "stream": True}).status_code == 400
+            # streaming: one event per token, the same tokens as the plain call, usage at the end
+            with client.stream("POST", "/v1/completions", json={"prompt": prompt, "max_tokens": 3, "stream": True}) as sr:
+                assert sr.status_code == 200 and sr.headers["content-type"].startswith("text/event-stream")
+                events = [line[6:] for line in sr.iter_lines() if line.startswith("data: ")]
+            assert events[-1] == "[DONE]"
+            import json as _json
+
+            objs = [_json.loads(e) for e in events[:-1]]
+            streamed = [t for o in objs for t in o["choices"][0]["token_ids"]]
+            assert streamed == body["choices"][0]["token_ids"]
+            assert [len(o["choices"][0]["token_ids"]) for o in objs] == [1, 1, 1, 0]
+            assert "".join(o["choices"][0]["text"] for o in objs) == body["choices"][0]["text"]
+            assert objs[-1]["choices"][0]["finish_reason"] == "length" and objs[-1]["usage"] == body["usage"]
+            assert metrics.snapshot().get("service.stream_ttft_ms.count", 0) >= 1
             assert client.post("/v1/completions", json={"prompt": "plain text works too", "max_tokens": 1}).status_code == 200
     finally:
         engine.close()
