@@ -60,8 +60,10 @@ def test_gpu_rag_engine_restored_equals_recomputed(tmp_path):
         query = [rng.randrange(cfg.vocab_size) for _ in range(20)]
         # cold: from the store file; warm: from the HBM tier; both must restore all chunks
         for attempt in range(2):
-            req = eng.generate([chunks[2], chunks[0], chunks[1]], query, max_new_tokens=4)
+            seen = []
+            req = eng.generate([chunks[2], chunks[0], chunks[1]], query, max_new_tokens=4, on_token=seen.append)
             assert req.restored_chunks == 3 and len(req.generated) == 4
+            assert seen == [int(t) for t in req.generated]  # reported token by token, as sampled
             assert req.ttft_ms > 0 and req.ttft_device_ms > 0
         # restored + rotated KV equals KV recomputed at the new offset (up to fp8 requantisation)
         from daser_b200.engine.rag_gpu import RagRequest
