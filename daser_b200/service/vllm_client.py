@@ -52,6 +52,34 @@ class VLLMClient:
         payload.update(gen_params or {})
         return await self._post_completions(payload)
 
+    async def completion_stream(self, tokens: list[int], gen_params: Optional[dict[str, Any]] = None,
+                                segments: Optional[Sequence[Sequence[int]]] = None):
+        """The same request with ``"stream": true``: yields ``{"token_ids", "text"}`` per
+        server-sent event and a last ``{"done": True, "usage": ...}`` (the shape of
+        :meth:`NativeEngineClient.completion_stream`)."""
+        import json
+
+        payload: dict[str, Any] = {"model": self._model, "prompt": tokens, "max_tokens": 256, "temperature": 0.7}
+        payload.update(gen_params or {})
+        payload["stream"] = True
+        usage: dict[str, Any] = {}
+        async with self._http.stream("POST", f"{self._base}/v1/completions", json=payload) as resp:
+            resp.raise_for_status()
+            async for line in resp.aiter_lines():
+                if not line.startswith("data: "):
+                    continue
+                data = line[6:].strip()
+                if data == "[DONE]":
+                    break
+                obj = json.loads(data)
+                if "error" in obj:
+                    raise RuntimeError(str(obj["error"].get("message", obj["error"])))
+                usage = obj.get("usage") or usage
+                choice = (obj.get("choices") or [{}])[0]
+                if choice.get("text") or choice.get("token_ids"):
+                    yield {"token_ids": list(choice.get("token_ids") or []), "text": choice.get("text", "")}
+        yield {"done": True, "usage": usage}
+
     async def health(self) -> bool:
         try:
             resp = await self._http.get(f"{self._base}/health")

@@ -161,11 +161,17 @@ def test_service_process_with_native_engine_starts_quickly_and_answers(tmp_path)
                 assert await c.health()
                 chunk = list(range(10, 42))
                 await c.prefill(chunk)  # max_tokens = 1: leaves the chunk in the store
-                reply = await c.completion([5] * 16 + chunk + [7, 8, 9], {"max_tokens": 2, "temperature": 0})
-                return reply["usage"], reply["choices"][0]["text"]
+                prompt = [5] * 16 + chunk + [7, 8, 9]
+                reply = await c.completion(prompt, {"max_tokens": 2, "temperature": 0})
+                streamed = [item async for item in c.completion_stream(prompt, {"max_tokens": 2, "temperature": 0})]
+                return reply, streamed
 
-        usage, _ = asyncio.run(through_the_vllm_client())
+        reply, streamed = asyncio.run(through_the_vllm_client())
+        usage = reply["usage"]
         assert usage["completion_tokens"] == 2 and usage["prompt_tokens"] == 51
+        # the same request over server-sent events: token by token, the same tokens, usage at the end
+        assert [t for item in streamed[:-1] for t in item["token_ids"]] == reply["choices"][0]["token_ids"]
+        assert len(streamed) == 3 and streamed[-1] == {"done": True, "usage": usage}
         with urllib.request.urlopen(base + "/metrics", timeout=5) as r:
             text = r.read().decode()
         hits = [float(l.split()[1]) for l in text.splitlines() if l.startswith("daser_connector_chunk_hits ")]
