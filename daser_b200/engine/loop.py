@@ -1,0 +1,146 @@
+"""One thread that owns the engine and keeps it stepping, so that concurrent callers share steps.
+
+``engine.generate`` serves one request from its prefill to its last token; callers that arrive
+meanwhile wait for the whole of it.  The engines schedule per iteration, though
+(``submit`` / ``step``: the prefill of the oldest waiting request first, else one decode step for
+every running request together), so a front end that hands requests over as they arrive gets
+continuous batching: a new request's prefill slips in between two decode steps of the others, and
+the decode steps carry every running request at once.
+
+:class:`EngineLoop` is that hand-over.  Any thread may call :meth:`submit` (returns a
+``concurrent.futures.Future`` of the finished request; ``on_token`` is called from the loop thread
+as tokens are sampled) or :meth:`call` (runs an engine method such as ``store_chunk`` between two
+steps).  The engine itself is only ever touched by the loop thread, which matters for the GPU
+engine: CUDA graphs, its streams and the tensor-parallel announcements all assume one caller.
+
+The reference has no engine of its own (it forwards to a remote vLLM, which has such a loop
+inside: ``daser/service/vllm_client.py:62-126``).
+"""
+
+from __future__ import annotations
+
+import queue
+import threading
+from concurrent.futures import Future
+from typing import Any, Callable, Optional, Sequence
+
+from daser_b200 import metrics
+from daser_b200.engine.request import RagRequest
+from daser_b200.logging import init_logger
+
+logger = init_logger(__name__)
+
+
+class _Tracked:
+    __slots__ = ("req", "future", "on_token", "sent")
+
+    def __init__(self, req: RagRequest, future: Future, on_token: Optional[Callable[[int], None]]) -> None:
+        self.req, self.future, self.on_token, self.sent = req, future, on_token, 0
+
+
+class EngineLoop:
+    def __init__(self, engine: Any, idle_wait_s: float = 0.05) -> None:
+        if not (hasattr(engine, "submit") and hasattr(engine, "step") and hasattr(engine, "has_work")):
+            raise TypeError("the engine has no submit / step / has_work: it cannot be stepped by a loop")
+        self.engine = engine
+        self._idle_wait = idle_wait_s
+        self._inbox: queue.Queue = queue.Queue()
+        self._tracked: list[_Tracked] = []
+        self._stop = False
+        self.failed: Optional[BaseException] = None
+        self.steps = 0
+        self.max_batch = 0  # most requests in flight at once (prefilled, still decoding)
+        self._thread = threading.Thread(target=self._run, name="daser-engine", daemon=True)
+        self._thread.start()
+
+    # -- any thread ----------------------------------------------------------------------------------
+    def submit(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
+               on_token: Optional[Callable[[int], None]] = None, **fields: Any) -> Future:
+        fut: Future = Future()
+        if self._stop or self.failed is not None:
+            fut.set_exception(RuntimeError(f"engine loop is not running: {self.failed or 'closed'}"))
+            return fut
+        req = RagRequest([list(c) for c in chunks], list(query), int(max_new_tokens), **fields)
+        self._inbox.put(("submit", _Tracked(req, fut, on_token)))
+        return fut
+
+    def call(self, method: str, *args: Any, **kw: Any) -> Future:
+        """Run ``engine.<method>(*args, **kw)`` on the loop thread, between two steps."""
+        fut: Future = Future()
+        if self._stop or self.failed is not None:
+            fut.set_exception(RuntimeError(f"engine loop is not running: {self.failed or 'closed'}"))
+            return fut
+        self._inbox.put(("call", (fut, method, args, kw)))
+        return fut
+
+    def close(self, timeout_s: float = 60.0) -> None:
+        """Finish what is in flight, then stop the thread (the engine is left open)."""
+        self._stop = True
+        self._inbox.put(("wake", None))
+        self._thread.join(timeout_s)
+
+    # -- the loop thread ---------------------------------------------------------------------------
+    def _take(self, block: bool) -> bool:
+        try:
+            kind, item = self._inbox.get(timeout=self._idle_wait) if block else self._inbox.get_nowait()
+        except queue.Empty:
+            return False
+        if kind == "submit":
+            self.engine.submit(item.req)
+            self._tracked.append(item)
+        elif kind == "call":
+            fut, method, args, kw = item
+            try:
+                fut.set_result(getattr(self.engine, method)(*args, **kw))
+            except Exception as exc:  # the caller's error, not the loop's
+                fut.set_exception(exc)
+        return True
+
+    def _report(self) -> None:
+        for t in list(self._tracked):
+            if t.on_token is not None:
+                for tok in t.req.generated[t.sent:]:
+                    try:
+                        t.on_token(int(tok))
+                    except Exception as exc:  # a closed client must not stop the others
+                        logger.warning("[ENGINE] token callback failed: %r", exc)
+                        t.on_token = None
+                        break
+            t.sent = len(t.req.generated)
+            if t.req.done:
+                self._tracked.remove(t)
+                t.future.set_result(t.req)
+
+    def _fail(self, exc: BaseException) -> None:
+        self.failed = exc
+        for t in self._tracked:
+            if not t.future.done():
+                t.future.set_exception(exc)
+        self._tracked.clear()
+        while True:  # whoever queued meanwhile
+            try:
+                kind, item = self._inbox.get_nowait()
+            except queue.Empty:
+                break
+            fut = item.future if kind == "submit" else (item[0] if kind == "call" else None)
+            if fut is not None and not fut.done():
+                fut.set_exception(exc)
+
+    def _run(self) -> None:
+        try:
+            while True:
+                while self._take(block=False):  # everything that arrived since the last step
+                    pass
+                if self.engine.has_work():
+                    self.engine.step()
+                    self.steps += 1
+                    self.max_batch = max(self.max_batch, len(self._tracked))
+                    metrics.set_gauge("engine.loop_in_flight", len(self._tracked))
+                    self._report()
+                elif self._stop:
+                    return
+                else:
+                    self._take(block=True)
+        except BaseException as exc:  # a failed step invalidates every request in flight
+            logger.error("[ENGINE] loop stopped: %r", exc)
+            self._fail(exc)

@@ -19,6 +19,7 @@ from typing import Optional, Sequence
 import torch
 
 from daser_b200.connector.core import ConnectorMeta, SchedulerHalf, TorchKVBackend, WorkerHalf
+from daser_b200.engine.request import RagRequest
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.layout import KVGeometry
 from daser_b200.models.llama import LlamaConfig, LlamaWeights, TorchPagedKV, reference_forward
@@ -82,6 +83,8 @@ class CpuRagEngine:
                                  TorchKVBackend(self.geo, self.pool.data, cfg.inv_freq()), io_backend=io_backend,
                                  host_store=self.host)
         self._req = 0
+        self.waiting: list[RagRequest] = []
+        self.running: list[RagRequest] = []
 
     # -- hooks a multi-process arrangement overrides (pipeline stages: parallel/pp.py) ------------
     def _lead(self, fn):
@@ -183,29 +186,52 @@ class CpuRagEngine:
         asked = [list(c) for c in chunks]
         if self.compose_after > 0:
             chunks = self._lead(lambda: self.sched.merge_composed(asked))
-        res = self.run_request([], chunks, query, keep_blocks=True)
-        bt = self.cfg.block_tokens
-        table = list(res.block_table)
-        generated = [self._sample(res.logits)]
-        if on_token is not None:
-            on_token(generated[-1])
-        pos = res.total_tokens
-        try:
-            while len(generated) < max_new_tokens:
-                if pos // bt >= len(table):
-                    table.extend(self.blocks.alloc(1))
-                logits = self._forward([generated[-1]], torch.tensor([pos]), torch.tensor(table), pos)
-                generated.append(self._sample(logits))
-                if on_token is not None:
-                    on_token(generated[-1])
-                pos += 1
-        finally:
-            self.blocks.free(table)
+        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens))
+        sent = 0
+        while not req.done:
+            self.step()
+            if on_token is not None:
+                for tok in req.generated[sent:]:
+                    on_token(tok)
+                sent = len(req.generated)
         if self.compose_after > 0:
             combo = self._lead(lambda: self.sched.note_composition(asked, self.compose_after))
             if combo is not None:
                 self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
-        return GenerateResult(generated, res.total_tokens, sum(res.restored))
+        return GenerateResult(req.generated, req.context_len, req.restored_chunks)
+
+    # -- iteration-level scheduling: the calls GpuRagEngine offers, on the oracle model ----------
+    def submit(self, req: RagRequest) -> RagRequest:
+        req.req_id = req.req_id or self._next_id()
+        self.waiting.append(req)
+        return req
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def step(self) -> None:
+        """One engine iteration: the prefill of the oldest waiting request (restore, compute
+        what is missing, first token), else one more token for every running request."""
+        bt = self.cfg.block_tokens
+        if self.waiting:
+            req = self.waiting.pop(0)
+            res = self.run_request([], req.chunks, req.query, keep_blocks=True)
+            req.block_table, req.context_len = list(res.block_table), res.total_tokens
+            req.restored_chunks = sum(res.restored)
+            req.generated.append(self._sample(res.logits))
+            self.running.append(req)
+        else:
+            for req in list(self.running):
+                pos = req.context_len + len(req.generated) - 1
+                if pos // bt >= len(req.block_table):
+                    req.block_table.extend(self.blocks.alloc(1))
+                logits = self._forward([req.generated[-1]], torch.tensor([pos]), torch.tensor(req.block_table), pos)
+                req.generated.append(self._sample(logits))
+        for req in list(self.running):
+            if len(req.generated) >= req.max_new_tokens:
+                req.done = True
+                self.running.remove(req)
+                self.blocks.free(req.block_table)
 
     def recompute_chunk_alone(self, chunk: Sequence[int], offset: int) -> tuple[list[int], int]:
         """Run ``chunk`` alone at positions ``offset..``; returns its (fresh) blocks and length.

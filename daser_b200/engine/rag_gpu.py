@@ -18,7 +18,6 @@ owns the scheduler half and broadcasts each step's plan.
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
 import torch
@@ -26,32 +25,13 @@ import torch
 from daser_b200 import metrics
 from daser_b200.connector.core import ConnectorMeta, CudaKVBackend, SchedulerHalf, WorkerHalf
 from daser_b200.engine.rag_cpu import BlockAllocator
+from daser_b200.engine.request import RagRequest
 from daser_b200.engine.runner import GpuModelRunner
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.hbm_store import HBMStore
 from daser_b200.models.llama import LlamaConfig, LlamaWeights
 from daser_b200.ops import gemm as gemm_ops
 from daser_b200.utils import trace
-
-
-@dataclass
-class RagRequest:
-    chunks: list[list[int]]  # block-aligned token lists, concatenated in order (prefix first)
-    query: list[int]
-    max_new_tokens: int = 1
-    req_id: str = ""
-    arrival: float = 0.0
-    # filled by the engine
-    block_table: list[int] = field(default_factory=list)
-    generated: list[int] = field(default_factory=list)
-    context_len: int = 0
-    ttft_ms: float = 0.0
-    ttft_device_ms: float = 0.0
-    restored_chunks: int = 0
-    restored_bytes: int = 0
-    timings: dict = field(default_factory=dict)
-    done: bool = False
-    store_misses: bool = False  # write the KV of chunks that had to be computed (cold pass)
 
 
 class GpuRagEngine:

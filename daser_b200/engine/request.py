@@ -1,0 +1,25 @@
+"""The request record both engines schedule: what was asked, and what the engine filled in."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+
+@dataclass
+class RagRequest:
+    chunks: list[list[int]]  # block-aligned token lists, concatenated in order (prefix first)
+    query: list[int]
+    max_new_tokens: int = 1
+    req_id: str = ""
+    arrival: float = 0.0
+    # filled by the engine
+    block_table: list[int] = field(default_factory=list)
+    generated: list[int] = field(default_factory=list)
+    context_len: int = 0
+    ttft_ms: float = 0.0
+    ttft_device_ms: float = 0.0
+    restored_chunks: int = 0
+    restored_bytes: int = 0
+    timings: dict = field(default_factory=dict)
+    done: bool = False
+    store_misses: bool = False  # write the KV of chunks that had to be computed (cold pass)

@@ -128,6 +128,7 @@ class PipelineCpuEngine(CpuRagEngine):
         if n > 1:
             self.worker.commit_parts = (st, n)
         self._req = 0
+        self.waiting, self.running = [], []
 
     # -- the hooks of CpuRagEngine --------------------------------------------------------------------
     def _lead(self, fn):

@@ -49,6 +49,9 @@ def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
     p.add_argument("--model-id", default="default")
     p.add_argument("--native-model", default="toy")
     p.add_argument("--native-device", choices=("cpu", "cuda"), default="cpu")
+    p.add_argument("--native-batching", action="store_true",
+                   help="one thread keeps the native engine stepping and concurrent requests share its steps "
+                        "(continuous batching); without it requests are served one after the other")
     p.add_argument("--snapshot-interval", type=float, default=0.0)
     args = p.parse_args(argv)
     if args.engine == "vllm" and (not args.vllm_base_url or not args.model):
@@ -130,7 +133,8 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
         from daser_b200.engine.rag_cpu import CpuRagEngine
 
         engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id)
-    return NativeEngineClient(engine, tokenizer.decode, model=args.native_model), engine
+    return NativeEngineClient(engine, tokenizer.decode, model=args.native_model,
+                              batching=bool(getattr(args, "native_batching", False))), engine
 
 
 async def _run(args: argparse.Namespace) -> None:
@@ -181,6 +185,8 @@ async def _run(args: argparse.Namespace) -> None:
     server.should_exit = True
     await asyncio.gather(http_task, return_exceptions=True)
     stop_task.cancel()
+    if engine_client is not None and engine is not None:
+        await engine_client.close()  # drains the engine loop, if there is one, before the engine goes
     if engine is not None:
         engine.close()
     await plane.stop(save=True)

@@ -13,6 +13,10 @@ the other ranks sit in :func:`follower_loop` and replay what they are told.
 The reference's service talks to a remote stock vLLM and leaves tensor parallelism to it
 (``daser/service/vllm_client.py:15-146``); its own connector is not rank aware at all.
 
+An engine loop (``engine/loop.py``) on the leader drives ``submit`` / ``step`` instead of
+``generate``; both are announced the same way, so the followers' queues mirror the leader's and a
+step batches the same requests on every rank.
+
 Failure handling: a follower that cannot be reached makes the announcement itself fail (the
 gloo broadcast times out or raises); the leader then marks the engine unavailable, which the
 front end reports through ``/health`` (see ``NativeEngineClient``).  ``shutdown`` tells the
@@ -32,6 +36,8 @@ Broadcast = Callable[[Any], Any]  # leader: sends and returns its argument; foll
 CMD_STORE = "store_chunk"
 CMD_GENERATE = "generate"
 CMD_WARM_UP = "warm_up"
+CMD_SUBMIT = "submit"
+CMD_STEP = "step"
 CMD_STOP = "stop"
 
 
@@ -66,6 +72,19 @@ class TPLeaderEngine:
             kw = dict(kw, on_token=on_token)
         return self._engine.generate(chunks, query, max_new_tokens=max_new_tokens, **kw)
 
+    # iteration-level calls (an engine loop drives these instead of `generate`)
+    def submit(self, req: Any) -> Any:
+        self._announce(CMD_SUBMIT, [list(c) for c in req.chunks], list(req.query), int(req.max_new_tokens),
+                       bool(req.store_misses))
+        return self._engine.submit(req)
+
+    def has_work(self) -> bool:
+        return self._engine.has_work()  # the same on every rank: they hold the same queues
+
+    def step(self) -> None:
+        self._announce(CMD_STEP)
+        self._engine.step()
+
     def warm_up(self, *args: Any, **kw: Any) -> None:
         self._announce(CMD_WARM_UP, list(args), dict(kw))
         self._engine.warm_up(*args, **kw)
@@ -99,6 +118,13 @@ def follower_loop(engine: Any, broadcast: Broadcast, on_step: Optional[Callable[
         elif op == CMD_GENERATE:
             _, chunks, query, max_new, kw = cmd
             engine.generate(chunks, query, max_new_tokens=max_new, **kw)
+        elif op == CMD_SUBMIT:
+            from daser_b200.engine.request import RagRequest
+
+            _, chunks, query, max_new, store_misses = cmd
+            engine.submit(RagRequest(chunks, query, max_new, store_misses=store_misses))
+        elif op == CMD_STEP:
+            engine.step()
         elif op == CMD_WARM_UP:
             engine.warm_up(*cmd[1], **cmd[2])
         else:

@@ -88,6 +88,14 @@ class VLLMClient:
             return False
 
 
+class _NoLock:
+    async def __aenter__(self) -> None:
+        return None
+
+    async def __aexit__(self, *exc: Any) -> None:
+        return None
+
+
 class NativeEngineClient:
     """The in-process engine behind the same interface.
 
@@ -97,24 +105,35 @@ class NativeEngineClient:
     the control plane) stays responsive.
     """
 
-    def __init__(self, engine: Any, detokenize, model: str = "native", pad_token: int = 0) -> None:
+    def __init__(self, engine: Any, detokenize, model: str = "native", pad_token: int = 0,
+                 batching: bool = False) -> None:
         self._engine = engine
         self._detok = detokenize
         self._model = model
         self._pad = pad_token
         self._lock = asyncio.Lock()
         self._failed: Optional[str] = None  # set once the engine lost a tensor-parallel peer
+        # batching: one thread keeps the engine stepping and concurrent requests share its steps
+        # (continuous batching); without it requests are served one after the other
+        self._loop = None
+        if batching:
+            from daser_b200.engine.loop import EngineLoop
+
+            self._loop = EngineLoop(engine)
 
     @property
     def model(self) -> str:
         return self._model
 
     async def close(self) -> None:
-        pass
+        if self._loop is not None:
+            await asyncio.get_running_loop().run_in_executor(None, self._loop.close)
 
     async def health(self) -> bool:
         """False once a step failed with a lost peer or an invalid device status: the group has
         to be restarted, `/health` degrades and `/infer` answers 502 until then."""
+        if self._loop is not None and self._loop.failed is not None:
+            return False
         return self._failed is None
 
     def _guard(self, fn, *args):
@@ -128,6 +147,9 @@ class NativeEngineClient:
             raise
 
     async def prefill(self, tokens: list[int]) -> None:
+        if self._loop is not None:
+            await asyncio.wrap_future(self._loop.call("store_chunk", list(tokens)))
+            return
         async with self._lock:
             await asyncio.get_running_loop().run_in_executor(None, self._guard, self._engine.store_chunk, list(tokens))
 
@@ -156,9 +178,14 @@ class NativeEngineClient:
             *cached, query = segments
         else:
             cached, query = [], tokens
-        async with self._lock:
-            gen, prompt_len = await asyncio.get_running_loop().run_in_executor(
-                None, self._guard, self._generate, cached, query, max_new)
+        if self._loop is not None:
+            chunks = [self._pad_block(s) for s in cached if len(s)]
+            req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new))
+            gen, prompt_len = req.generated, req.context_len
+        else:
+            async with self._lock:
+                gen, prompt_len = await asyncio.get_running_loop().run_in_executor(
+                    None, self._guard, self._generate, cached, query, max_new)
         return {
             "choices": [{"text": self._detok(gen), "token_ids": gen}],
             "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)},
@@ -178,9 +205,18 @@ class NativeEngineClient:
             cached, query = [], tokens
         loop = asyncio.get_running_loop()
         queue: asyncio.Queue = asyncio.Queue()
-        async with self._lock:
-            fut = loop.run_in_executor(None, self._guard, self._generate, cached, query, max_new,
-                                       lambda tok: loop.call_soon_threadsafe(queue.put_nowait, int(tok)))
+        push = lambda tok: loop.call_soon_threadsafe(queue.put_nowait, int(tok))  # noqa: E731
+        async with (self._lock if self._loop is None else _NoLock()):
+            if self._loop is not None:
+                chunks = [self._pad_block(s) for s in cached if len(s)]
+
+                async def stepped():
+                    req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new, on_token=push))
+                    return req.generated, req.context_len
+
+                fut = asyncio.ensure_future(stepped())
+            else:
+                fut = loop.run_in_executor(None, self._guard, self._generate, cached, query, max_new, push)
             fut.add_done_callback(lambda _f: queue.put_nowait(None))  # runs on the loop: after every token
             sent: list[int] = []
             text = ""

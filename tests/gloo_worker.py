@@ -208,6 +208,17 @@ def scenario_serve() -> int:
         def warm_up(self, *a, **kw):
             self.calls.append(("warm_up", a, tuple(sorted(kw.items()))))
 
+        def submit(self, req):
+            self.calls.append(("submit", tuple(map(tuple, req.chunks)), tuple(req.query), req.max_new_tokens,
+                               req.store_misses))
+            return req
+
+        def has_work(self):
+            return False
+
+        def step(self):
+            self.calls.append(("step",))
+
         def close(self):
             self.calls.append(("close",))
 
@@ -218,6 +229,15 @@ def scenario_serve() -> int:
         assert lead.store_chunk(range(32)) == "key"
         lead.generate([list(range(16)), list(range(16, 48))], [1, 2, 3], max_new_tokens=4)
         lead.generate([], [9], max_new_tokens=1, store_misses=True)
+        # a local observer is not announced (followers log the same call without it)
+        lead.generate([], [8], max_new_tokens=2, on_token=lambda t: None)
+        eng.calls[-1] = eng.calls[-1][:4] + ((),)
+        # the iteration-level calls an engine loop makes
+        from daser_b200.engine.request import RagRequest
+
+        lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True))
+        lead.step()
+        lead.step()
         lead.close()
         try:
             lead.store_chunk([1] * 16)
@@ -226,10 +246,10 @@ def scenario_serve() -> int:
             refused = True
     else:
         steps = follower_loop(eng, _bcast)
-        refused = steps == 4
+        refused = steps == 8
     logs = [None] * world
     dist.all_gather_object(logs, (eng.calls, refused))
-    good = all(log == logs[0][0] for log, _ in logs) and all(r for _, r in logs) and len(logs[0][0]) == 5
+    good = all(log == logs[0][0] for log, _ in logs) and all(r for _, r in logs) and len(logs[0][0]) == 9
     if rank == 0:
         print("SERVE_OK" if good else f"SERVE_FAIL {logs}", flush=True)
     dist.destroy_process_group()

@@ -1,0 +1,121 @@
+"""The engine loop: concurrent callers share the engine's steps (continuous batching)."""
+
+import random
+import threading
+import time
+
+import pytest
+
+from conftest import LiveControlPlane
+from daser_b200.engine.loop import EngineLoop
+from daser_b200.engine.rag_cpu import CpuRagEngine
+from daser_b200.kv.layout import KVGeometry
+from daser_b200.models.llama import PRESETS
+from daser_b200.position import RopeReencoder
+
+
+@pytest.fixture
+def engine(tmp_path):
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=256, slot_size=geo.slot_size, num_layers=cfg.num_layers,
+                          num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, dtype_bytes=4)
+    lp.plane.position = RopeReencoder(cfg.head_dim, cfg.rope_theta)
+    lp.start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=256)
+    yield eng
+    eng.close()
+    lp.stop()
+
+
+def test_concurrent_requests_share_steps_and_match_sequential_results(engine):
+    cfg = engine.cfg
+    rng = random.Random(0)
+    chunks = [[rng.randrange(cfg.vocab_size) for _ in range(32)] for _ in range(4)]
+    for c in chunks:
+        engine.store_chunk(c)
+    reqs = [([rng.choice(chunks), rng.choice(chunks)], [rng.randrange(cfg.vocab_size) for _ in range(6)])
+            for _ in range(6)]
+    want = [engine.generate(c, q, max_new_tokens=5).generated for c, q in reqs]
+    free_before = engine.blocks.num_free
+
+    loop = EngineLoop(engine)
+    try:
+        streams = [[] for _ in reqs]
+        futs = [loop.submit(c, q, 5, on_token=streams[i].append) for i, (c, q) in enumerate(reqs)]
+        # an engine call from another thread is slotted in between two steps
+        key = loop.call("store_chunk", [rng.randrange(cfg.vocab_size) for _ in range(16)]).result(60)
+        done = [f.result(60) for f in futs]
+    finally:
+        loop.close()
+    assert [r.generated for r in done] == want            # batching changes the schedule, not the tokens
+    assert streams == want                                 # every token was reported, in order
+    assert all(r.restored_chunks == 2 for r in done)
+    assert loop.max_batch > 1                              # requests really overlapped
+    assert loop.steps < sum(len(w) for w in want)          # fewer steps than one request at a time needs
+    assert isinstance(key, str) and engine.blocks.num_free == free_before
+
+
+def test_requests_arriving_while_others_decode_join_the_batch(engine):
+    cfg = engine.cfg
+    loop = EngineLoop(engine)
+    try:
+        first = loop.submit([], [1, 2, 3], 40)
+        started = threading.Event()
+        got = []
+        second = None
+
+        def late():
+            nonlocal second
+            time.sleep(0.05)
+            second = loop.submit([], [4, 5, 6], 3, on_token=lambda t: (got.append(t), started.set()))
+
+        t = threading.Thread(target=late)
+        t.start()
+        t.join()
+        r2 = second.result(60)
+        assert not first.done() or len(first.result().generated) == 40   # the short one did not wait for the long one
+        r1 = first.result(60)
+    finally:
+        loop.close()
+    assert len(r1.generated) == 40 and len(r2.generated) == 3 and got == r2.generated
+    assert r2.generated == engine.generate([], [4, 5, 6], max_new_tokens=3).generated
+    assert cfg.block_tokens == 16
+
+
+def test_a_failing_step_fails_everything_in_flight_and_later_calls():
+    class Broken:
+        def __init__(self):
+            self.q = []
+
+        def submit(self, req):
+            self.q.append(req)
+
+        def has_work(self):
+            return bool(self.q)
+
+        def step(self):
+            raise RuntimeError("device status word set")
+
+    loop = EngineLoop(Broken())
+    fut = loop.submit([], [1], 2)
+    with pytest.raises(RuntimeError, match="status word"):
+        fut.result(10)
+    assert loop.failed is not None
+    with pytest.raises(RuntimeError, match="not running"):
+        loop.submit([], [1], 1).result(1)
+    with pytest.raises(RuntimeError, match="not running"):
+        loop.call("store_chunk", [1]).result(1)
+    loop.close()
+    with pytest.raises(TypeError):
+        EngineLoop(object())
+
+
+def test_a_callers_error_in_call_does_not_stop_the_loop(engine):
+    loop = EngineLoop(engine)
+    try:
+        with pytest.raises(ValueError):
+            loop.call("store_chunk", [1, 2, 3]).result(30)   # not a whole number of blocks
+        assert len(loop.submit([], [9, 9], 2).result(60).generated) == 2
+    finally:
+        loop.close()

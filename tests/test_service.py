@@ -267,3 +267,46 @@ def test_openai_completions_reuse_stored_chunks_found_by_scan(tmp_path):
     finally:
         engine.close()
         lp.stop()
+
+
+def test_batching_engine_client_serves_concurrent_and_streamed_requests(tmp_path):
+    """With ``batching`` the engine client hands requests to an engine loop: concurrent HTTP calls share
+    the engine's steps, answers equal those of the one-at-a-time client, streaming still works."""
+    import json
+    from concurrent.futures import ThreadPoolExecutor
+
+    from daser_b200.engine.rag_cpu import CpuRagEngine
+    from daser_b200.kv.layout import KVGeometry
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.openai_api import mount_openai_routes
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    mcfg = PRESETS["toy"]
+    geo = KVGeometry(mcfg.num_layers, mcfg.num_kv_heads, mcfg.head_dim, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    engine = CpuRagEngine(mcfg, lp.socket_path, lp.cfg.store_path, num_blocks=256)
+    tok = ByteTokenizer()
+    client_obj = NativeEngineClient(engine, tok.decode, batching=True)
+    cfg = ServiceConfig("", "toy", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2)
+    app = build_service_app(cfg, engine_client=client_obj, tokenizer=tok)
+    mount_openai_routes(app, client_obj, tok, lp.socket_path, "toy", "default", 16)
+    prompts = [[(7 * i + j) % 250 + 1 for j in range(20 + i)] for i in range(6)]
+    try:
+        with TestClient(app) as client:
+            assert client.post("/documents", json={"title": "A", "text": "lorem ipsum dolor sit amet " * 5}).status_code == 201
+            post = lambda p: client.post("/v1/completions", json={"prompt": p, "max_tokens": 6}).json()  # noqa: E731
+            with ThreadPoolExecutor(6) as pool:
+                together = list(pool.map(post, prompts))
+            alone = [post(p) for p in prompts]
+            assert [r["choices"][0]["token_ids"] for r in together] == [r["choices"][0]["token_ids"] for r in alone]
+            assert client_obj._loop.max_batch > 1
+            with client.stream("POST", "/v1/completions", json={"prompt": prompts[0], "max_tokens": 6, "stream": True}) as sr:
+                events = [json.loads(l[6:]) for l in sr.iter_lines() if l.startswith("data: {")]
+            assert [t for e in events for t in e["choices"][0]["token_ids"]] == alone[0]["choices"][0]["token_ids"]
+            assert client.get("/health").json()["status"] in ("ok", "healthy", "degraded")
+    finally:
+        import asyncio
+
+        asyncio.run(client_obj.close())
+        engine.close()
+        lp.stop()
