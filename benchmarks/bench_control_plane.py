@@ -8,7 +8,8 @@ A control plane is started as a separate process (``python -m daser_b200.server`
 * one client: latency of ``lookup`` (longest-prefix over a ``--prompt-tokens`` prompt),
   ``lookup_chunks`` (8 keys, the RAG plan of one request) and an ``alloc_chunk`` + ``commit_chunk``
   pair; p50 / p99 over ``--iters`` calls;
-* ``--clients`` concurrent clients (threads, one socket each): ``lookup_chunks`` calls per second.
+* ``--clients`` concurrent client processes: ``lookup_chunks`` calls per second, against the Python
+  server and against the native lookup thread (``server/csrc/fast_lookup.cc``).
 
 In-process figures for comparison: the longest-prefix lookup with the native index and with the
 pure-Python path (what the reference's algorithm costs is the third line: re-hashing every
@@ -99,6 +100,14 @@ def main():
         lat = _timed(plan, args.iters)
         emit({"bench": "control_plane", "what": "lookup_chunks RPC, 8 keys", "p50_us": percentile(lat, 50),
               "p99_us": percentile(lat, 99)})
+        native = IPCClientSync(sock)
+        native.negotiate()
+        has_native = getattr(native, "_fast", None) is not None
+        if has_native:
+            lat = _timed(lambda: native.lookup_chunks(rng.sample(keys, 8), "m"), args.iters)
+            emit({"bench": "control_plane", "what": "lookup_chunks RPC, 8 keys, native lookup thread",
+                  "p50_us": percentile(lat, 50), "p99_us": percentile(lat, 99)})
+        native.close()
         n = [0]
 
         def alloc_commit():
@@ -111,25 +120,33 @@ def main():
         emit({"bench": "control_plane", "what": "alloc_chunk + commit_chunk RPC pair", "p50_us": percentile(lat, 50),
               "p99_us": percentile(lat, 99)})
 
-        counts = [0] * args.clients
-        stop = time.time() + 3.0
-
-        def worker(i):
-            c = IPCClientSync(sock)
-            r = random.Random(i)
-            while time.time() < stop:
-                c.lookup_chunks(r.sample(keys, 8), "m")
-                counts[i] += 1
-            c.close()
-
-        threads = [threading.Thread(target=worker, args=(i,)) for i in range(args.clients)]
-        t0 = time.perf_counter()
-        for t in threads:
-            t.start()
-        for t in threads:
-            t.join()
-        emit({"bench": "control_plane", "what": f"lookup_chunks RPC, {args.clients} concurrent clients",
-              "calls_per_s": sum(counts) / (time.perf_counter() - t0)})
+        # concurrent clients are processes (threads of one interpreter would measure its lock)
+        for label, use_native in (("python server", False), ("native lookup thread", True)):
+            if use_native and not has_native:
+                continue
+            code = (
+                "import sys, time, random\n"
+                "from daser_b200.connector.ipc_client import IPCClientSync\n"
+                "sock, seed, native = sys.argv[1], int(sys.argv[2]), sys.argv[3] == '1'\n"
+                "keys = sys.stdin.read().split()\n"
+                "c = IPCClientSync(sock)\n"
+                "if native: c.negotiate()\n"
+                "r = random.Random(seed); n = 0; stop = time.time() + 3.0\n"
+                "while time.time() < stop:\n"
+                "    c.lookup_chunks(r.sample(keys, 8), 'm'); n += 1\n"
+                "print(n)\n"
+            )
+            procs = [subprocess.Popen([sys.executable, "-c", code, sock, str(i), "1" if use_native else "0"],
+                                      stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, cwd=ROOT)
+                     for i in range(args.clients)]
+            for p in procs:
+                p.stdin.write(" ".join(keys))
+                p.stdin.close()
+            total = sum(int(p.stdout.read().strip() or 0) for p in procs)
+            for p in procs:
+                p.wait()
+            emit({"bench": "control_plane", "what": f"lookup_chunks RPC, {args.clients} concurrent client "
+                  f"processes, {label}", "calls_per_s": total / 3.0})
         client.close()
     finally:
         proc.send_signal(signal.SIGTERM)

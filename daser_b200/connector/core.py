@@ -126,10 +126,7 @@ class SchedulerHalf:
         if aligned == 0:
             return 0, False
         store_key = hash_tokens(tokens[:aligned])
-        if not self._negotiated:  # once the server answers: packed token ids if it takes them
-            self._negotiated = True
-            if hasattr(self._ipc, "negotiate"):
-                self._ipc.negotiate()
+        self._negotiate_once()
         t0 = time.perf_counter()
         try:
             with trace.span("rpc.match_and_alloc", "connector", req=req_id, tokens=len(tokens)):
@@ -165,6 +162,13 @@ class SchedulerHalf:
         return 0, False
 
     # -- chunk reuse at arbitrary offsets ----------------------------------------------------
+    def _negotiate_once(self) -> None:
+        """First contact: packed token ids and the native lookup socket, if the server has them."""
+        if not self._negotiated:
+            self._negotiated = True
+            if hasattr(self._ipc, "negotiate"):
+                self._ipc.negotiate()
+
     def plan_chunk_loads(self, req_id: str, placements: Sequence[tuple[str, int]]) -> list[Optional[ReqLoadSpec]]:
         """Resolve ``(chunk_key, token offset)`` pairs; returns one spec (or None) per pair.
 
@@ -175,6 +179,7 @@ class SchedulerHalf:
         for _, off in placements:
             if off % bt:
                 raise ValueError("chunk placements must be block aligned")
+        self._negotiate_once()
         try:
             with trace.span("rpc.lookup_chunks", "connector", req=req_id, chunks=len(placements)):
                 found = self._ipc.lookup_chunks([k for k, _ in placements], self.model_id)

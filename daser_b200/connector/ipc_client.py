@@ -37,6 +37,7 @@ class IPCClientSync:
         # token ids travel as a msgpack list (the reference's wire form) until `negotiate` finds
         # a server that also takes them as packed int32 (one bin field instead of n integers)
         self.binary_tokens = False
+        self._fast: Optional["IPCClientSync"] = None  # client of the server's native lookup socket
 
     def negotiate(self) -> bool:
         """Ask the server what it supports; enables packed token ids when it does.  A server
@@ -46,6 +47,10 @@ class IPCClientSync:
         except RuntimeError:
             return False
         self.binary_tokens = "tokens_bin" in (reply.get("features") or [])
+        # lookups by key may go to the server's native thread, on a socket of its own
+        fast = reply.get("fast_lookup")
+        if isinstance(fast, str) and fast and fast != self._path:
+            self._fast = IPCClientSync(fast, timeout=self._timeout)
         return self.binary_tokens
 
     def _tok(self, tokens) -> dict[str, Any]:
@@ -101,6 +106,9 @@ class IPCClientSync:
     def close(self) -> None:
         with self._lock:
             self._reset()
+        if self._fast is not None:
+            self._fast.close()
+            self._fast = None
 
     # reference operations
     def lookup(self, tokens: list[int], model_id: str) -> list[dict[str, Any]]:
@@ -143,9 +151,14 @@ class IPCClientSync:
     def lookup_chunks(
         self, keys: list[str], model_id: str
     ) -> list[Optional[dict[str, Any]]]:
-        return self.call(
-            {"op": frames.OP_LOOKUP_CHUNKS, "keys": keys, "model_id": model_id}
-        )["chunks"]
+        msg = {"op": frames.OP_LOOKUP_CHUNKS, "keys": keys, "model_id": model_id}
+        if self._fast is not None:
+            try:
+                return self._fast.call(msg)["chunks"]
+            except (RuntimeError, OSError, KeyError):  # the thread went away: the main socket still answers
+                self._fast.close()
+                self._fast = None
+        return self.call(msg)["chunks"]
 
     def scan_chunks(self, tokens: list[int], model_id: str) -> list[dict[str, Any]]:
         return self.call(

@@ -108,11 +108,12 @@ def build_io_selftest(sanitize: str = "address,undefined") -> Path:
 
 
 def build_index(force: bool = False) -> Path:
-    """The control plane's native token index (hashing through the system's libxxhash)."""
-    src = INDEX_SRC / "token_index.cc"
-    if force or _stale(INDEX_LIB, [src]):
+    """The control plane's native parts: the token index (hashing through the system's libxxhash)
+    and the lookup-by-key server thread."""
+    srcs = [INDEX_SRC / "token_index.cc", INDEX_SRC / "fast_lookup.cc"]
+    if force or _stale(INDEX_LIB, srcs):
         _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-pthread",
-              "-o", str(INDEX_LIB), str(src), "-ldl"])
+              "-o", str(INDEX_LIB), *map(str, srcs), "-ldl"])
     return INDEX_LIB
 
 
@@ -120,7 +121,7 @@ def build_index_selftest(sanitize: str = "address,undefined") -> Path:
     """The token index's stand-alone exerciser, instrumented with ``-fsanitize=<sanitize>``."""
     BUILD_DIR.mkdir(exist_ok=True)
     out = BUILD_DIR / f"index_selftest_{sanitize.replace(',', '_')}"
-    srcs = [INDEX_SRC / "token_index.cc", INDEX_SRC / "token_index_selftest.cc"]
+    srcs = [INDEX_SRC / "token_index.cc", INDEX_SRC / "fast_lookup.cc", INDEX_SRC / "token_index_selftest.cc"]
     if _stale(out, srcs):
         _run(["g++", "-O1", "-g", "-std=c++17", f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-pthread",
               "-o", str(out), *map(str, srcs), "-ldl"])

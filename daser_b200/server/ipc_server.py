@@ -61,7 +61,14 @@ class IPCServer:
         block_tokens: int = 16,
         doc_registry: Optional[DocRegistry] = None,
         geometry: Optional[dict[str, Any]] = None,
+        fast_lookup: Optional[bool] = None,
     ) -> None:
+        # lookups by key are also served by a native thread on `<socket>.fast` (no interpreter on
+        # that path); off with fast_lookup=False or DASER_FAST_LOOKUP=0
+        if fast_lookup is None:
+            fast_lookup = os.environ.get("DASER_FAST_LOOKUP", "1") != "0"
+        self._fast_enabled = bool(fast_lookup)
+        self._fast: Any = None
         self._socket_path = socket_path
         self._cm = chunk_manager
         self._ri = retrieval_index
@@ -114,8 +121,32 @@ class IPCServer:
             self._handle_connection, path=self._socket_path
         )
         logger.info("[IPC] listening on %s", self._socket_path)
+        self._start_fast()
+
+    def _start_fast(self) -> None:
+        from daser_b200.server.native_index import FastLookupServer
+
+        if not self._fast_enabled or not FastLookupServer.supported():
+            return
+        try:
+            self._fast = FastLookupServer(self._socket_path + ".fast", self._slot_size)
+        except (OSError, RuntimeError) as exc:
+            logger.warning("[IPC] no native lookup thread (%s): lookups stay on the main socket", exc)
+            return
+        for meta in self._cm.store.iter_chunks():  # what a snapshot brought back
+            if self._cm.store.is_committed(meta.chunk_key):
+                self._fast_put(meta)
+        logger.info("[IPC] native lookup thread on %s", self._fast.socket_path)
+
+    def _fast_put(self, meta: ChunkMeta) -> None:
+        if self._fast is not None:
+            self._fast.put(meta.chunk_key, meta.model_id, meta.start_slot, meta.num_slots, meta.token_count,
+                           int(self._pe.get_offset(meta)))
 
     async def stop(self) -> None:
+        if self._fast is not None:
+            self._fast.stop()
+            self._fast = None
         if self._server is not None:
             self._server.close()
             # wait_closed() also waits for live connections: hang up on them.
@@ -168,6 +199,9 @@ class IPCServer:
                 metrics.set_gauge("ring.used_slots", self._cm.used_slots)
                 metrics.set_gauge("ring.total_slots", self._cm.total_slots)
                 metrics.set_gauge("ring.chunks", len(self._cm.store))
+                if self._fast is not None:
+                    for name, value in self._fast.stats().items():
+                        metrics.set_gauge(f"fast_lookup.{name}", value)
             return reply
         except ProtocolError as exc:
             return {"error": str(exc)}
@@ -192,6 +226,8 @@ class IPCServer:
         return -(-token_count // self._block_tokens)
 
     def _on_evicted(self, meta: ChunkMeta) -> None:
+        if self._fast is not None:
+            self._fast.delete(meta.chunk_key)
         self._ri.discard(meta.chunk_key)
         self._parts.pop(meta.chunk_key, None)
         self._dirty = True
@@ -301,6 +337,7 @@ class IPCServer:
             self._parts.pop(chunk_key, None)
         self._cm.store.mark_committed(chunk_key, msg.get("checksum"))
         await self._ri.insert(meta)
+        self._fast_put(meta)  # visible on the native lookup socket before this commit is acknowledged
         anchor = msg.get("first_block")
         if anchor and hasattr(self._ri, "register_anchor"):
             self._ri.register_anchor(chunk_key, anchor)  # type: ignore[attr-defined]
@@ -440,8 +477,11 @@ class IPCServer:
         bad = geometry_mismatch(self._geometry, dict(msg.get("geometry") or {}))
         if bad:
             raise ProtocolError("geometry mismatch: " + "; ".join(bad))
-        return {"ok": True, "geometry": self._geometry, "ops": sorted(self._handlers),
-                "features": ["tokens_bin"]}
+        reply = {"ok": True, "geometry": self._geometry, "ops": sorted(self._handlers),
+                 "features": ["tokens_bin"]}
+        if self._fast is not None:
+            reply["fast_lookup"] = self._fast.socket_path
+        return reply
 
     async def _handle_stats(self, msg: dict[str, Any]) -> dict[str, Any]:
         return {
@@ -454,4 +494,5 @@ class IPCServer:
             },
             "docs": len(self._docs) if self._docs is not None else 0,
             "counters": metrics.snapshot(),
+            **({"fast_lookup": self._fast.stats()} if self._fast is not None else {}),
         }

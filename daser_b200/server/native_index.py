@@ -14,11 +14,12 @@ from typing import Optional, Sequence
 
 _LIB_PATH = Path(__file__).resolve().parent / "libdaser_index.so"
 _lib: Optional[C.CDLL] = None
+_raw: Optional[C.CDLL] = None  # the library whether or not libxxhash was found (the lookup server needs none)
 _checked = False
 
 
 def _load() -> Optional[C.CDLL]:
-    global _lib, _checked
+    global _lib, _raw, _checked
     if _checked:
         return _lib
     _checked = True
@@ -42,6 +43,15 @@ def _load() -> Optional[C.CDLL]:
     lib.daser_table_longest_prefix.argtypes = [p, u64, p, i64, i32, i64, C.POINTER(i64)]
     lib.daser_table_longest_prefix.restype = i64
     lib.daser_table_scan_blocks.argtypes, lib.daser_table_scan_blocks.restype = [p, u64, p, i64, i32, p, p, i64], i64
+    if hasattr(lib, "daser_fast_start"):
+        cs = C.c_char_p
+        lib.daser_fast_start.argtypes, lib.daser_fast_start.restype = [cs, i64], p
+        lib.daser_fast_stop.argtypes = [p]
+        lib.daser_fast_put.argtypes = [p, cs, cs, i64, i64, i64, i64]
+        lib.daser_fast_del.argtypes = [p, cs]
+        lib.daser_fast_clear.argtypes = [p]
+        lib.daser_fast_stats.argtypes = [p, p]
+        _raw = lib
     if lib.daser_index_available() != 1:
         return None
     _lib = lib
@@ -142,3 +152,54 @@ class DigestTable:
         val = (C.c_int64 * cap)()
         hits = int(self._lib.daser_table_scan_blocks(self._t, tag, ptr, n, block, idx, val, cap))
         return [(int(idx[i]), int(val[i])) for i in range(min(hits, cap))]
+
+
+class FastLookupServer:
+    """The native thread that answers ``lookup_chunks {keys}`` on a socket of its own
+    (``server/csrc/fast_lookup.cc``).  The Python server keeps its records in step: :meth:`put`
+    when a chunk becomes visible, :meth:`delete` when it is evicted or aborted."""
+
+    def __init__(self, socket_path: str, slot_size: int) -> None:
+        _load()
+        if _raw is None:
+            raise RuntimeError("the native library was not built")
+        self.socket_path = socket_path
+        self._lib = _raw
+        self._h = self._lib.daser_fast_start(socket_path.encode(), slot_size)
+        if not self._h:
+            raise OSError(f"cannot listen on {socket_path}")
+
+    @staticmethod
+    def supported() -> bool:
+        _load()
+        return _raw is not None
+
+    def put(self, key: str, model_id: str, start_slot: int, num_slots: int, token_count: int, pos_offset: int) -> None:
+        if self._h:
+            self._lib.daser_fast_put(self._h, key.encode(), model_id.encode(), start_slot, num_slots, token_count,
+                                     pos_offset)
+
+    def delete(self, key: str) -> None:
+        if self._h:
+            self._lib.daser_fast_del(self._h, key.encode())
+
+    def clear(self) -> None:
+        if self._h:
+            self._lib.daser_fast_clear(self._h)
+
+    def stats(self) -> dict[str, int]:
+        out = (C.c_int64 * 5)()
+        if self._h:
+            self._lib.daser_fast_stats(self._h, out)
+        return dict(zip(("records", "calls", "hits", "misses", "refused"), (int(v) for v in out)))
+
+    def stop(self) -> None:
+        if self._h:
+            self._lib.daser_fast_stop(self._h)
+            self._h = None
+
+    def __del__(self) -> None:
+        try:
+            self.stop()
+        except Exception:
+            pass
