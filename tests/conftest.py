@@ -33,7 +33,7 @@ def pytest_collection_modifyitems(config, items):
 class LiveControlPlane:
     """A real control plane on a temp socket, on its own thread and event loop."""
 
-    def __init__(self, tmp_path, total_slots=64, slot_size=4096, block_tokens=16, **cfg_kw):
+    def __init__(self, tmp_path, total_slots=64, slot_size=4096, block_tokens=16, position_encoder=None, **cfg_kw):
         from daser_b200.config import DaserConfig
         from daser_b200.server.__main__ import ControlPlane
 
@@ -46,7 +46,7 @@ class LiveControlPlane:
             block_tokens=block_tokens,
             **cfg_kw,
         )
-        self.plane = ControlPlane(self.cfg, position_encoder=cfg_kw.get("_pe"))
+        self.plane = ControlPlane(self.cfg, position_encoder=position_encoder)
         self.loop = asyncio.new_event_loop()
         self._ready = threading.Event()
         self.thread = threading.Thread(target=self._run, daemon=True)
