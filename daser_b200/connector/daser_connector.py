@@ -158,6 +158,47 @@ if _KVConnectorStats is not None:
 else:  # pragma: no cover
     DaserKVConnectorStats = None  # type: ignore[assignment,misc]
 
+try:  # vLLM's hook for per-connector Prometheus metrics (logger process); absent in old versions
+    from vllm.distributed.kv_transfer.kv_connector.v1.metrics import KVConnectorPromMetrics as _PromBase
+except Exception:  # pragma: no cover
+    _PromBase = None
+
+_PROM_HELP = {
+    "bytes_loaded": "Bytes of chunk KV restored into the paged cache",
+    "bytes_stored": "Bytes of chunk KV written to the store",
+    "bytes_over_pcie": "Bytes of chunk KV that crossed PCIe on the way in (store file or host tier)",
+    "load_errors": "Blocks whose restore failed and were handed back to vLLM for recomputation",
+    "store_errors": "Chunks whose write failed (left uncommitted)",
+}
+
+if _PromBase is not None:
+
+    class DaserPromMetrics(_PromBase):  # type: ignore[misc,valid-type]
+        """One counter per field of :class:`DaserKVConnectorStats`, labelled per engine:
+        ``vllm:daser_<field>_total`` grows by what each stats interval reports."""
+
+        def __init__(self, vllm_config: Any, metric_types: Any, labelnames: list[str],
+                     per_engine_labelvalues: dict[int, list[object]]) -> None:
+            super().__init__(vllm_config, metric_types, labelnames, per_engine_labelvalues)
+            self._counters = {
+                field: self._counter_cls(name=f"vllm:daser_{field}", documentation=doc, labelnames=labelnames)
+                for field, doc in _PROM_HELP.items()
+            }
+            self._children: dict[tuple[int, str], Any] = {}
+
+        def observe(self, transfer_stats_data: dict[str, Any], engine_idx: int = 0) -> None:
+            for field, value in transfer_stats_data.items():
+                counter = self._counters.get(field)
+                if counter is None or not value or value < 0:
+                    continue
+                child = self._children.get((engine_idx, field))
+                if child is None:
+                    child = counter.labels(*self.per_engine_labelvalues[engine_idx])
+                    self._children[(engine_idx, field)] = child
+                child.inc(value)
+else:  # pragma: no cover
+    DaserPromMetrics = None  # type: ignore[assignment,misc]
+
 
 class DaserConnector(KVConnectorBase_V1):
     def __init__(self, vllm_config: Any, role: Any, kv_cache_config: Any = None) -> None:
@@ -329,6 +370,14 @@ class DaserConnector(KVConnectorBase_V1):
         if DaserKVConnectorStats is None:
             return None
         return DaserKVConnectorStats(data=dict(data)) if data is not None else DaserKVConnectorStats()
+
+    @classmethod
+    def build_prom_metrics(cls, vllm_config: Any, metric_types: Any, labelnames: list[str],
+                           per_engine_labelvalues: dict[int, list[object]]) -> Any:
+        """vLLM's logger process calls this once and then feeds it every reduced stats interval."""
+        if DaserPromMetrics is None:
+            return None
+        return DaserPromMetrics(vllm_config, metric_types, labelnames, per_engine_labelvalues)
 
     def get_stats(self) -> dict[str, float]:
         return self._worker.get_stats() if self._worker is not None else {}

@@ -229,3 +229,30 @@ def test_connector_stats_container():
     assert a.aggregate(b).reduce() == {"bytes_loaded": 15, "load_errors": 0, "bytes_stored": 7}
     a.reset()
     assert a.is_empty()
+
+
+def test_prometheus_metrics_hook_counts_per_engine():
+    """vLLM's logger process builds the connector's Prometheus metrics once and feeds it the reduced
+    stats of every interval: counters per field, labelled per engine."""
+    from types import SimpleNamespace
+
+    from prometheus_client import CollectorRegistry, Counter, Gauge, Histogram
+
+    from daser_b200.connector.daser_connector import DaserConnector
+
+    reg = CollectorRegistry()
+
+    def bound(cls):
+        return lambda **kw: cls(registry=reg, **kw)
+
+    prom = DaserConnector.build_prom_metrics(
+        SimpleNamespace(kv_transfer_config=None), {Gauge: bound(Gauge), Counter: bound(Counter), Histogram: bound(Histogram)},
+        ["model_name", "engine"], {0: ["toy", "0"], 1: ["toy", "1"]})
+    assert prom is not None
+    prom.observe({"bytes_loaded": 100, "bytes_stored": 0, "load_errors": 2, "unknown_field": 5}, engine_idx=0)
+    prom.observe({"bytes_loaded": 50}, engine_idx=0)
+    prom.observe({"bytes_loaded": 7}, engine_idx=1)
+    get = lambda name, eng: reg.get_sample_value(name, {"model_name": "toy", "engine": eng})  # noqa: E731
+    assert get("vllm:daser_bytes_loaded_total", "0") == 150 and get("vllm:daser_bytes_loaded_total", "1") == 7
+    assert get("vllm:daser_load_errors_total", "0") == 2
+    assert get("vllm:daser_bytes_stored_total", "0") is None   # nothing stored: no child yet
