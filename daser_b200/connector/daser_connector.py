@@ -331,6 +331,14 @@ class DaserConnector(KVConnectorBase_V1):
         if self._worker is not None:
             self._worker.start_load_kv()
 
+    @classmethod
+    def requires_piecewise_for_cudagraph(cls, extra_config: dict[str, Any]) -> bool:
+        """No: nothing happens in the per-layer hooks (restore completes in :meth:`start_load_kv`,
+        save gathers all layers in :meth:`wait_for_save`), so a full-graph replay that skips them
+        loses nothing.  The reference had to make its loads synchronous for the same reason
+        (``docs/design/architecture.md:48-52`` there)."""
+        return False
+
     def wait_for_layer_load(self, layer_name: str) -> None:
         """Loads finish inside :meth:`start_load_kv`; a full CUDA-graph replay skips Python hooks."""
 
