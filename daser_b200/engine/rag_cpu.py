@@ -65,8 +65,12 @@ class CpuRagEngine:
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 512,
                  codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
                  io_backend: str = "auto", model_id: str = "default", host_slots: int = 0,
-                 compose_after: int = 0) -> None:
+                 compose_after: int = 0, repair_tokens: int = 0) -> None:
         self.cfg = cfg
+        # > 0: after a chunk was restored behind other context, its first `repair_tokens` tokens are
+        # recomputed in place with attention over everything before them (the tokens whose stored KV
+        # is furthest from what the full context would have produced: they saw nothing when stored)
+        self.repair_tokens = repair_tokens
         # > 0: an ordered combination of chunks seen this many times is computed once with full
         # cross-attention and stored; later requests that start with it restore it as one chunk
         self.compose_after = compose_after
@@ -168,6 +172,9 @@ class CpuRagEngine:
             for c, off, spec in zip(chunks, offsets, specs):
                 if spec is None:
                     self._forward(c, torch.arange(off, off + len(c)), tbl, ctx, return_logits=False)
+                elif self.repair_tokens > 0 and off > 0:
+                    r = min(self.repair_tokens, len(c))
+                    self._forward(c[:r], torch.arange(off, off + r), tbl, off, return_logits=False)
                 ctx = off + len(c)
             return self._forward(query, torch.arange(ctx, ctx + len(query)), tbl, ctx)
 

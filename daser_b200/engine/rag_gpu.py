@@ -40,8 +40,12 @@ class GpuRagEngine:
                  io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
                  staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True,
-                 compose_after: int = 0) -> None:
+                 compose_after: int = 0, repair_tokens: int = 0) -> None:
         self.cfg = cfg
+        # > 0: after a chunk was restored behind other context, its first `repair_tokens` tokens are
+        # recomputed in place with attention over everything before them (the tokens whose stored KV
+        # is furthest from what the full context would have produced: they saw nothing when stored)
+        self.repair_tokens = repair_tokens
         # > 0: an ordered combination of chunks seen this many times is computed once with full
         # cross-attention and stored; later requests that start with it restore it as one chunk
         self.compose_after = compose_after
@@ -222,6 +226,8 @@ class GpuRagEngine:
             else:
                 req.restored_chunks += 1
                 req.restored_bytes += (len(c) // bt) * self.geo.slot_size
+                if self.repair_tokens > 0 and off > 0:
+                    self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table)
             ctx = off + len(c)
         first = self._prefill_tokens(req.query, ctx, req.block_table)
         self._ev[3].record()

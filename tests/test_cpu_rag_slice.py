@@ -216,3 +216,35 @@ def test_composition_counting_and_keys():
     assert s.merge_composed([a, b]) == [a, b]              # control plane unreachable: unchanged
     with pytest.raises(ValueError):
         s.composition_keys([[1] * 5])
+
+
+def test_repairing_the_head_of_restored_chunks_moves_the_output_towards_the_exact_one(tmp_path):
+    """``repair_tokens=r`` recomputes the first r tokens of every chunk restored behind other
+    context, in place, with attention over all that precedes them.  The error against a run that
+    computes everything shrinks with r and vanishes when r covers the chunks."""
+    import dataclasses
+
+    cfg = dataclasses.replace(PRESETS["toy"], num_layers=3)
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=256, slot_size=geo.slot_size, num_layers=cfg.num_layers,
+                          num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, dtype_bytes=4)
+    lp.plane.position = RopeReencoder(cfg.head_dim, cfg.rope_theta)
+    lp.start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=256)
+    try:
+        rng = random.Random(0)
+        chunks = [[rng.randrange(cfg.vocab_size) for _ in range(48)] for _ in range(3)]
+        query = [rng.randrange(cfg.vocab_size) for _ in range(8)]
+        exact = eng.run_request([], chunks, query).logits           # nothing stored yet: all computed
+        for c in chunks:
+            eng.store_chunk(c)
+        errs = []
+        for r in (0, 16, 48):
+            eng.repair_tokens = r
+            res = eng.run_request([], chunks, query)
+            assert res.restored == [True, True, True]
+            errs.append((res.logits - exact).abs().max().item())
+        assert errs[0] > errs[1] > errs[2] and errs[2] < 1e-4
+    finally:
+        eng.close()
+        lp.stop()
