@@ -115,6 +115,52 @@ def test_periodic_snapshot_survives_sigkill(tmp_path):
         _stop(proc2)
 
 
+def test_service_process_with_batching_serves_concurrent_clients(tmp_path):
+    """`--native-batching`: the engine loop behind the HTTP front end.  Eight clients at once get
+    the answers a lone client gets, the process shuts down cleanly with the loop drained."""
+    import json
+    import socket
+    import urllib.request
+    from concurrent.futures import ThreadPoolExecutor
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "daser_b200.service", "--engine", "native", "--native-batching", "--tokenizer", "byte",
+           "--store-path", str(tmp_path / "s.store"), "--index-path", str(tmp_path / "s.index"),
+           "--socket-path", str(tmp_path / "s.sock"), "--total-slots", "256", "--host", "127.0.0.1", "--port", str(port)]
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            env=dict(os.environ, PYTHONUNBUFFERED="1"))
+    base = f"http://127.0.0.1:{port}"
+
+    def post(prompt):
+        body = json.dumps({"prompt": prompt, "max_tokens": 4}).encode()
+        req = urllib.request.Request(base + "/v1/completions", data=body, headers={"content-type": "application/json"})
+        with urllib.request.urlopen(req, timeout=60) as r:
+            return json.load(r)["choices"][0]["token_ids"]
+
+    try:
+        t0 = time.time()
+        while True:
+            assert proc.poll() is None, "service exited early"
+            assert time.time() - t0 < 25, "service did not come up within 25 s"
+            try:
+                with urllib.request.urlopen(base + "/health", timeout=2) as r:
+                    if json.load(r)["status"] == "ok":
+                        break
+            except OSError:
+                time.sleep(0.3)
+        prompts = [[(3 * i + j) % 200 + 1 for j in range(24 + i)] for i in range(8)]
+        with ThreadPoolExecutor(8) as pool:
+            together = list(pool.map(post, prompts))
+        assert together == [post(p) for p in prompts] and all(len(t) == 4 for t in together)
+        with urllib.request.urlopen(base + "/metrics", timeout=5) as r:
+            assert "daser_engine_loop_in_flight" in r.read().decode()
+    finally:
+        out_text = _stop(proc)
+    assert proc.returncode == 0, out_text[-2000:]
+
+
 def test_service_process_with_native_engine_starts_quickly_and_answers(tmp_path):
     """`python -m daser_b200.service --engine native`: control plane, CPU engine and REST front end
     in one process.  The engine is built off the event loop (its connector talks to the control
