@@ -1,0 +1,1 @@
+"""Storage engine binding: cuFile, io_uring and POSIX back ends behind one asynchronous interface."""

@@ -1,0 +1,1 @@
+"""Multi-process arrangements: tensor parallelism over peer memory, pipeline stages, peer liveness."""

@@ -1,0 +1,1 @@
+"""Small helpers shared by the package: Chrome-trace spans and NVTX ranges."""
