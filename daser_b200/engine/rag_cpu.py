@@ -62,6 +62,10 @@ class RequestResult:
 
 
 class CpuRagEngine:
+    # defaults of the optional behaviours, also for subclasses that build themselves differently
+    compose_after = 0
+    repair_tokens = 0
+
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 512,
                  codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
                  io_backend: str = "auto", model_id: str = "default", host_slots: int = 0,

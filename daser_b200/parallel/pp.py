@@ -106,9 +106,11 @@ class PipelineCpuEngine(CpuRagEngine):
 
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, group: Any = None,
                  num_blocks: int = 512, codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
-                 io_backend: str = "auto", model_id: str = "default", compose_after: int = 0) -> None:
+                 io_backend: str = "auto", model_id: str = "default", compose_after: int = 0,
+                 repair_tokens: int = 0) -> None:
         self.cfg = cfg
         self.compose_after = compose_after
+        self.repair_tokens = repair_tokens
         self.link = StageLink(group)
         st, n = self.link.stage, self.link.stages
         self.layers = partition_layers(cfg.num_layers, n)[st]
