@@ -138,6 +138,12 @@ class GpuModelRunner:
         gemm.linear(x, w, out=out_bf[:M], block_n=bn, k_splits=1, status=self.status)
         return out_bf[:M], False
 
+    def qk_norm(self, lw):
+        """The per-head norm of models that have one, as ``ops.elementwise.rope_kv_write`` takes it."""
+        if not self.cfg.qk_norm:
+            return None
+        return (lw.q_norm, lw.k_norm, self.cfg.rms_eps)
+
     def mlp_up(self, x: torch.Tensor, lw, T: int, **gate) -> torch.Tensor:
         """``silu(x Wg^T) * (x Wu^T)`` into ``self.act[:T]``: one GEMM with the activation as its
         epilogue when the weights are interleaved and the shape runs unsplit, else GEMM + kernel."""
@@ -248,7 +254,7 @@ class GpuModelRunner:
         for li, lw in enumerate(w.layers):
             qkv, f32 = self._linear(normed, lw.wqkv, self.qkv_acc, self.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq,
-                             self.hkv, D, B, self.local_pool, li, 0, zero_after=f32)
+                             self.hkv, D, B, self.local_pool, li, 0, zero_after=f32, qk_norm=self.qk_norm(lw))
             attn = self.attn_out[:T].view(T, self.hq, D)
             attention.paged_attention(self.q_rot[:T], attn, self.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, self.hkv, self.softmax_scale,

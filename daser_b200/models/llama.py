@@ -38,6 +38,9 @@ class LlamaConfig:
     rms_eps: float = 1e-5
     block_tokens: int = 16
     max_position: int = 8192
+    # Qwen3 family: RMSNorm over head_dim on every query and key head (one weight vector each per
+    # layer, shared by the heads) between the QKV projection and RoPE
+    qk_norm: bool = False
 
     def scaling_dict(self) -> dict[str, Any]:
         return dict(self.rope_scaling)
@@ -79,6 +82,11 @@ PRESETS = {
                               1e-5, 16, 131072),
     # small GPU test model with the 70B head geometry
     "tiny-gqa": LlamaConfig("tiny-gqa", 1024, 512, 2, 8, 2, 128, 1024, 500000.0, (), 1e-5, 16, 8192),
+    # the model of the reference's own end-to-end runs (tests/integration/conftest.py:30 there:
+    # 36 layers x 8 KV heads x 128 x 16 tokens x bf16 x 2 = 2 359 296 bytes per slot)
+    "qwen3-8b": LlamaConfig("qwen3-8b", 151936, 4096, 36, 32, 8, 128, 12288, 1000000.0, (), 1e-6, 16, 40960, True),
+    "toy-qk": LlamaConfig("toy-qk", 32000, 256, 2, 4, 2, 64, 512, 10000.0, (), 1e-6, 16, 8192, True),
+    "tiny-gqa-qk": LlamaConfig("tiny-gqa-qk", 1024, 512, 2, 8, 2, 128, 1024, 1000000.0, (), 1e-6, 16, 8192, True),
 }
 
 
@@ -90,6 +98,8 @@ class LayerWeights:
     post_norm: torch.Tensor
     w_gate_up: torch.Tensor  # [2 * I / tp, hidden]: gate rows then up rows
     w_down: torch.Tensor  # [hidden, I / tp]
+    q_norm: Optional[torch.Tensor] = None  # [head_dim], models with qk_norm only (replicated)
+    k_norm: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -174,6 +184,14 @@ class LlamaWeights:
         inter = cfg.intermediate // tp
         embed = mat(cfg.vocab_size, cfg.hidden, shard=False)
         layers = []
+
+        def head_norm() -> torch.Tensor:  # near one, not one: a misapplied weight must show in tests
+            counter[0] += 1
+            gen.manual_seed(seed * 1_000_003 + counter[0] * 97)
+            t = torch.empty(D, dtype=dtype, device=device)
+            t.normal_(1.0, 0.1, generator=gen)
+            return t
+
         for _ in range(cfg.num_layers):
             layers.append(
                 LayerWeights(
@@ -183,6 +201,8 @@ class LlamaWeights:
                     post_norm=ones(cfg.hidden),
                     w_gate_up=mat(2 * inter, cfg.hidden),
                     w_down=mat(cfg.hidden, inter),
+                    q_norm=head_norm() if cfg.qk_norm else None,
+                    k_norm=head_norm() if cfg.qk_norm else None,
                 )
             )
         return cls(cfg, tp, rank, embed, layers, ones(cfg.hidden), mat(cfg.vocab_size // tp, cfg.hidden))
@@ -211,6 +231,7 @@ def shard_weights(full: LlamaWeights, tp: int, rank: int) -> LlamaWeights:
                 post_norm=lw.post_norm,
                 w_gate_up=torch.cat([gate, up]).contiguous(),
                 w_down=lw.w_down[:, rank * inter : (rank + 1) * inter].contiguous(),
+                q_norm=lw.q_norm, k_norm=lw.k_norm,
             )
         )
     v_loc = cfg.vocab_size // tp
@@ -298,6 +319,9 @@ def reference_forward(
         q = qkv[:, : Hq * D].reshape(T, Hq, D)
         k = qkv[:, Hq * D : (Hq + Hkv) * D].reshape(T, Hkv, D)
         v = qkv[:, (Hq + Hkv) * D :].reshape(T, Hkv, D)
+        if cfg.qk_norm:
+            q = rms_norm(q, lw.q_norm, cfg.rms_eps)
+            k = rms_norm(k, lw.k_norm, cfg.rms_eps)
         q = codec.rope_rotate(q, cos, sin)
         k = codec.rope_rotate(k, cos, sin)
         pool.write(li, blk, off, k, v)

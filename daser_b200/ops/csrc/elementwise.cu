@@ -220,12 +220,18 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t target,
 
 // RoPE on q and k, then k/v into the paged pool.  qkv row = [Hq*D | Hkv*D | Hkv*D].
 // slot_mapping[t] = block * block_tokens + offset inside the block, or < 0 to skip the write.
-template <typename TIn, bool POOL_FP8>
+// QKNORM (Qwen3 family): every query and key head is RMS-normalised over head_dim and scaled by
+// q_norm_w / k_norm_w before the rotation.  A head's `segs` items sit on consecutive lanes of one
+// warp (segs is a power of two <= 32, the item stride is a multiple of the block size), so the sum
+// of squares is a butterfly over those lanes only; all of them are inside the loop together.
+template <typename TIn, bool POOL_FP8, bool QKNORM = false>
 __global__ void __launch_bounds__(128)
 rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* __restrict__ positions,
                      const int64_t* __restrict__ slot_mapping, const float* __restrict__ cos_sin,
                      int max_pos, __nv_bfloat16* __restrict__ q_out, int T, int Hq, int Hkv, int D,
-                     int block_tokens, DaserKVPool pool, int layer, int rank, int zero_after) {
+                     int block_tokens, DaserKVPool pool, int layer, int rank, int zero_after,
+                     const __nv_bfloat16* __restrict__ q_norm_w = nullptr,
+                     const __nv_bfloat16* __restrict__ k_norm_w = nullptr, float norm_eps = 0.f) {
   const int half = D >> 1;
   const int segs = half / FP8_GROUP;
   const int heads = Hq + 2 * Hkv;
@@ -249,6 +255,22 @@ rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* _
       for (int i = 0; i < 8; ++i) { x2[i] = a[i]; x2[8 + i] = b[i]; }
     }
     const bool is_v = hd >= Hq + Hkv;
+    if (QKNORM && !is_v) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
+      const unsigned lane = threadIdx.x & 31u;
+      const unsigned group = (segs >= 32 ? 0xFFFFFFFFu : ((1u << segs) - 1u) << (lane & ~(unsigned)(segs - 1)));
+      for (int m = segs >> 1; m > 0; m >>= 1) ss += __shfl_xor_sync(group, ss, m);
+      const float inv = rsqrtf(ss / (float)D + norm_eps);
+      const __nv_bfloat16* w = (hd < Hq ? q_norm_w : k_norm_w) + j * FP8_GROUP;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        // the normalised head is a bf16 tensor in the models this follows: round before rotating
+        x1[i] = __bfloat162float(__float2bfloat16(x1[i] * inv * __bfloat162float(w[i])));
+        x2[i] = __bfloat162float(__float2bfloat16(x2[i] * inv * __bfloat162float(w[half + i])));
+      }
+    }
     if (!is_v) {
       int pos = positions[t];
       pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
@@ -478,6 +500,33 @@ DASER_API int daser_wait_flags(const uint32_t* flags, int n, uint32_t target, co
 DASER_API int daser_advance_epochs(uint32_t* epochs, uint32_t d0, uint32_t d1, uint32_t d2, cudaStream_t stream) {
   if (!epochs) return DASER_ERR_BAD_ARG;
   daser::advance_epochs_kernel<<<1, 1, 0, stream>>>(epochs, d0, d1, d2);
+  return (int)cudaGetLastError();
+}
+
+// The same with RMSNorm over head_dim on every query and key head before the rotation
+// (q_norm_w, k_norm_w: bf16 [D]).
+DASER_API int daser_rope_kv_write_qknorm(void* qkv, int qkv_is_fp32, int64_t qkv_stride, const int32_t* positions,
+                                         const int64_t* slot_mapping, const float* cos_sin, int max_pos,
+                                         void* q_out, int T, int Hq, int Hkv, int D, int block_tokens,
+                                         const DaserKVPool* pool, int layer, int rank, int zero_after,
+                                         const void* q_norm_w, const void* k_norm_w, float eps,
+                                         cudaStream_t stream) {
+  using namespace daser;
+  if (!pool || !q_norm_w || !k_norm_w || T < 0 || D <= 0 || D % 32 || max_pos <= 0) return DASER_ERR_BAD_ARG;
+  const int segs = D / 32;
+  if (segs > 32 || (segs & (segs - 1))) return DASER_ERR_UNSUPPORTED;  // the lane butterfly needs a power of two
+  if (rank < 0 || rank >= DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
+  if (T == 0) return 0;
+  const int64_t items = (int64_t)T * (Hq + 2 * Hkv) * segs;
+  const int grid = ew_grid(items, 128);
+#define LAUNCH_QK(TIN, FP8)                                                                        \
+  rope_kv_write_kernel<TIN, FP8, true><<<grid, 128, 0, stream>>>(                                  \
+      (TIN*)qkv, qkv_stride, positions, slot_mapping, cos_sin, max_pos, (__nv_bfloat16*)q_out, T,  \
+      Hq, Hkv, D, block_tokens, *pool, layer, rank, zero_after, (const __nv_bfloat16*)q_norm_w,    \
+      (const __nv_bfloat16*)k_norm_w, eps)
+  if (qkv_is_fp32) { if (pool->pool_is_fp8) LAUNCH_QK(float, true); else LAUNCH_QK(float, false); }
+  else { if (pool->pool_is_fp8) LAUNCH_QK(__nv_bfloat16, true); else LAUNCH_QK(__nv_bfloat16, false); }
+#undef LAUNCH_QK
   return (int)cudaGetLastError();
 }
 

@@ -106,10 +106,29 @@ def rope_kv_write(
     layer: int,
     rank: int = 0,
     zero_after: bool = False,
+    qk_norm: Optional[tuple[torch.Tensor, torch.Tensor, float]] = None,
 ) -> None:
-    """RoPE on q and k of ``qkv[T, (Hq + 2 Hkv) * D]``; q -> ``q_out``, k/v -> the paged pool."""
+    """RoPE on q and k of ``qkv[T, (Hq + 2 Hkv) * D]``; q -> ``q_out``, k/v -> the paged pool.
+
+    ``qk_norm = (q_weight[D], k_weight[D], eps)``: RMSNorm over head_dim on every query and key
+    head before the rotation (Qwen3 family)."""
     assert positions.dtype == torch.int32 and slot_mapping.dtype == torch.int64
     pool_c = pool.c_struct()
+    if qk_norm is not None:
+        qw, kw, eps = qk_norm
+        assert qw.dtype == torch.bfloat16 and kw.dtype == torch.bfloat16 and qw.numel() == head_dim == kw.numel()
+        _lib.check(
+            _lib.lib().daser_rope_kv_write_qknorm(
+                C.c_void_p(qkv.data_ptr()), _is_f32(qkv), C.c_int64(qkv.stride(0)),
+                C.c_void_p(positions.data_ptr()), C.c_void_p(slot_mapping.data_ptr()),
+                C.c_void_p(cos_sin.data_ptr()), int(cos_sin.shape[0]), C.c_void_p(q_out.data_ptr()),
+                int(qkv.shape[0]), num_q_heads, num_kv_heads, head_dim, block_tokens,
+                C.byref(pool_c), layer, rank, int(zero_after), C.c_void_p(qw.data_ptr()),
+                C.c_void_p(kw.data_ptr()), C.c_float(eps), _lib.stream_ptr(),
+            ),
+            "rope_kv_write_qknorm",
+        )
+        return
     _lib.check(
         _lib.lib().daser_rope_kv_write(
             C.c_void_p(qkv.data_ptr()), _is_f32(qkv), C.c_int64(qkv.stride(0)),

@@ -279,7 +279,7 @@ class TPContext:
         for li, lw in enumerate(w.layers):
             qkv, f32 = self._col_gemm(runner, lw.wqkv, runner.qkv_acc, runner.qkv_bf, T, rows)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
@@ -342,7 +342,7 @@ class TPContext:
         for li, lw in enumerate(w.layers):
             qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
@@ -409,7 +409,7 @@ class TPContext:
         for li, lw in enumerate(w.layers):
             qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
@@ -438,7 +438,7 @@ class TPContext:
         for li, lw in enumerate(w.layers):
             qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32)
+                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,

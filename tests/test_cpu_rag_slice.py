@@ -248,3 +248,30 @@ def test_repairing_the_head_of_restored_chunks_moves_the_output_towards_the_exac
     finally:
         eng.close()
         lp.stop()
+
+
+def test_qk_norm_model_restores_and_rotates_like_the_plain_one(tmp_path):
+    """Qwen3-style per-head query / key norm sits before the rotation, so stored keys are still
+    re-rotated by position difference alone: restored KV equals KV recomputed at the new offset."""
+    cfg = PRESETS["toy-qk"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size, num_layers=cfg.num_layers,
+                          num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, dtype_bytes=4)
+    lp.plane.position = RopeReencoder(cfg.head_dim, cfg.rope_theta)
+    lp.start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=128)
+    try:
+        assert eng.weights.layers[0].q_norm is not None and not torch.equal(
+            eng.weights.layers[0].q_norm, torch.ones(cfg.head_dim))
+        rng = random.Random(5)
+        a, b = ([rng.randrange(cfg.vocab_size) for _ in range(32)] for _ in range(2))
+        eng.store_chunk(a)
+        eng.store_chunk(b)
+        res = eng.run_request([], [b, a], [1, 2, 3], keep_blocks=True)
+        assert res.restored == [True, True]
+        fresh, n = eng.recompute_chunk_alone(a, 32)
+        got = eng.pool.data[:, res.block_table[2:4]]
+        assert (got - eng.pool.data[:, fresh]).abs().max().item() <= 1e-4
+    finally:
+        eng.close()
+        lp.stop()
