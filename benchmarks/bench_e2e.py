@@ -9,7 +9,9 @@ every prompt is restored from the store and only the tail is computed.  Reports 
 tokens/s of both passes, the warm/cold speed-up and how many first tokens differ between the
 passes.  The reference's published run (H800, Qwen3-8B, 200 IMDB prompts of ~303 tokens) gave
 8 940 tok/s cold and 28 772 tok/s warm; prompts here are synthetic token ids of the same
-length distribution because no dataset is available offline.
+length distribution because no dataset is available offline.  ``--model qwen3-8b`` runs the
+reference's own architecture (random-init weights); the default stays the Llama-3-8B shape that
+the recorded figures were taken with.
 """
 
 from __future__ import annotations
