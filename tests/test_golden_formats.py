@@ -117,3 +117,15 @@ def test_a_snapshot_in_the_references_format_loads(tmp_path):
         c.close()
     finally:
         lp.stop()
+
+
+def test_slot_sizes_of_the_models_the_reference_names():
+    """``heads * hd * 2 * L * B * dtype_bytes`` (``daser/config.py:68-75``): 2 359 296 bytes for
+    Qwen3-8B (``tests/integration/conftest.py:30`` there), 2 MiB for the Llama-3-8B-like geometry
+    of its storage benchmark (``benchmarks/bench_storage_imdb.py:47-48``)."""
+    from daser_b200.models.llama import PRESETS
+
+    q = PRESETS["qwen3-8b"]
+    assert KVGeometry(q.num_layers, q.num_kv_heads, q.head_dim, q.block_tokens, 2, "raw").slot_size == 2_359_296
+    m = PRESETS["llama3-8b"]
+    assert KVGeometry(m.num_layers, m.num_kv_heads, m.head_dim, m.block_tokens, 2, "raw").slot_size == 2_097_152
