@@ -69,7 +69,7 @@ class CpuRagEngine:
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 512,
                  codec_name: str = "raw", dtype: torch.dtype = torch.float32, seed: int = 0,
                  io_backend: str = "auto", model_id: str = "default", host_slots: int = 0,
-                 compose_after: int = 0, repair_tokens: int = 0) -> None:
+                 compose_after: int = 0, repair_tokens: int = 0, weights: Optional[LlamaWeights] = None) -> None:
         self.cfg = cfg
         # > 0: after a chunk was restored behind other context, its first `repair_tokens` tokens are
         # recomputed in place with attention over everything before them (the tokens whose stored KV
@@ -78,7 +78,7 @@ class CpuRagEngine:
         # > 0: an ordered combination of chunks seen this many times is computed once with full
         # cross-attention and stored; later requests that start with it restore it as one chunk
         self.compose_after = compose_after
-        self.weights = LlamaWeights.random(cfg, "cpu", dtype, seed=seed)
+        self.weights = weights if weights is not None else LlamaWeights.random(cfg, "cpu", dtype, seed=seed)
         self.pool = TorchPagedKV(cfg, num_blocks, dtype)
         self.blocks = BlockAllocator(num_blocks)
         self.geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens,

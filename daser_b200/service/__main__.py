@@ -49,6 +49,10 @@ def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
     p.add_argument("--model-id", default="default")
     p.add_argument("--native-model", default="toy")
     p.add_argument("--native-device", choices=("cpu", "cuda"), default="cpu")
+    p.add_argument("--native-checkpoint", default=None,
+                   help="directory of a Hugging Face checkpoint (config.json + *.safetensors; Llama-3 and Qwen3 "
+                        "families): architecture and weights of the native engine instead of --native-model "
+                        "with random weights")
     p.add_argument("--native-batching", action="store_true",
                    help="one thread keeps the native engine stepping and concurrent requests share its steps "
                         "(continuous batching); without it requests are served one after the other")
@@ -97,33 +101,63 @@ def _tp_context(mcfg):
     return _TP_CTX
 
 
+def _model_config(args: argparse.Namespace):
+    """The native engine's architecture: a preset name, or the ``config.json`` of ``--native-checkpoint``."""
+    from daser_b200.models.llama import PRESETS
+
+    if getattr(args, "native_checkpoint", None):
+        import json
+
+        from daser_b200.models.hf import config_from_hf
+
+        with open(os.path.join(args.native_checkpoint, "config.json")) as f:
+            return config_from_hf(json.load(f), name=os.path.basename(os.path.normpath(args.native_checkpoint)),
+                                  block_tokens=args.block_tokens)
+    return PRESETS[args.native_model]
+
+
+def _model_weights(args: argparse.Namespace, device, dtype, tp: int = 1, rank: int = 0):
+    """This rank's shard of the checkpoint, or None (the engine then draws random weights)."""
+    if not getattr(args, "native_checkpoint", None):
+        return None
+    from daser_b200.models.hf import load_checkpoint
+
+    return load_checkpoint(args.native_checkpoint, tp=tp, rank=rank, dtype=dtype, device=device,
+                           block_tokens=args.block_tokens)
+
+
 def _run_follower(args: argparse.Namespace) -> None:
     """Ranks above 0: build the same engine shard and replay the leader's calls until told to stop."""
+    import torch
+
     from daser_b200.engine.rag_gpu import GpuRagEngine
-    from daser_b200.models.llama import PRESETS
     from daser_b200.service.tp_serving import follower_loop
 
     cfg = _build_daser_config(args)
-    mcfg = PRESETS[args.native_model]
+    mcfg = _model_config(args)
     tp_ctx = _tp_context(mcfg)
     tp_ctx.barrier()  # the leader's control plane is up
     engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
-                          hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx)
+                          hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx,
+                          weights=_model_weights(args, "cuda", torch.bfloat16, tp_ctx.tp, tp_ctx.rank))
     steps = follower_loop(engine, tp_ctx.broadcast_object)
     logger.info("[SERVICE] follower rank %d leaves after %d engine calls", tp_ctx.rank, steps)
 
 
 def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
-    from daser_b200.models.llama import PRESETS
+    import torch
+
     from daser_b200.service.vllm_client import NativeEngineClient
 
-    mcfg = PRESETS[args.native_model]
+    mcfg = _model_config(args)
     if args.native_device == "cuda":
         from daser_b200.engine.rag_gpu import GpuRagEngine
 
         tp_ctx = _tp_context(mcfg)
+        shard = (tp_ctx.tp, tp_ctx.rank) if tp_ctx is not None else (1, 0)
         engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
-                              hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx)
+                              hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx,
+                              weights=_model_weights(args, "cuda", torch.bfloat16, *shard))
         if tp_ctx is not None:
             from daser_b200.service.tp_serving import TPLeaderEngine
 
@@ -132,7 +166,8 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
     else:
         from daser_b200.engine.rag_cpu import CpuRagEngine
 
-        engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id)
+        engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
+                              weights=_model_weights(args, "cpu", torch.float32))
     return NativeEngineClient(engine, tokenizer.decode, model=args.native_model,
                               batching=bool(getattr(args, "native_batching", False))), engine
 
@@ -144,9 +179,7 @@ async def _run(args: argparse.Namespace) -> None:
     tokenizer = load_tokenizer(args.tokenizer)
     engine_client = engine = None
     if args.engine == "native":
-        from daser_b200.models.llama import PRESETS
-
-        m = PRESETS[args.native_model]
+        m = _model_config(args)
         if cfg.slot_size == 0 and cfg.num_layers == 0:
             cfg.num_layers, cfg.num_kv_heads, cfg.head_dim = m.num_layers, m.num_kv_heads, m.head_dim
             cfg.dtype_bytes = 4 if args.native_device == "cpu" else 2
@@ -155,9 +188,7 @@ async def _run(args: argparse.Namespace) -> None:
     await plane.start()
     if args.engine == "native":
         if args.native_device == "cuda" and _world()[1] > 1:
-            from daser_b200.models.llama import PRESETS as _P
-
-            _tp_context(_P[args.native_model]).barrier()  # followers may connect to the control plane now
+            _tp_context(_model_config(args)).barrier()  # followers may connect to the control plane now
         # built off the loop: the engine's connector talks to the control plane, which this loop serves
         engine_client, engine = await asyncio.get_running_loop().run_in_executor(
             None, _native_engine, args, cfg, tokenizer)
