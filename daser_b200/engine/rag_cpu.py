@@ -104,8 +104,15 @@ class CpuRagEngine:
         return reference_forward(self.weights, torch.tensor(list(tokens)), positions, self.pool, table, context_len,
                                  return_logits=return_logits)
 
-    def _sample(self, logits: Optional[torch.Tensor]) -> int:
-        return int(logits[-1].argmax())
+    def _sample(self, logits: Optional[torch.Tensor], req: Optional[RagRequest] = None) -> int:
+        """Greedy, or (request with a temperature) a draw from softmax(logits / T) by the Gumbel-max
+        rule, reproducible from the request's seed and the step."""
+        row = logits[-1].float()
+        if req is not None and req.temperature > 0:
+            gen = torch.Generator().manual_seed(req.step_seed())
+            u = torch.rand(row.shape, generator=gen).clamp_(1e-9, 1.0 - 1e-9)
+            row = row / req.temperature - torch.log(-torch.log(u))
+        return int(row.argmax())
 
     def _next_id(self) -> str:
         self._req += 1
@@ -189,7 +196,8 @@ class CpuRagEngine:
         return RequestResult(logits, table, offsets, [s is not None for s in specs], total)
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
-                 store_misses: bool = False, on_token=None) -> "GenerateResult":
+                 store_misses: bool = False, on_token=None, temperature: float = 0.0,
+                 seed: int = 0) -> "GenerateResult":
         """Serve one request to completion with greedy sampling: the same call the GPU engine
         offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
         for signature parity; chunks are only stored through :meth:`store_chunk` here.
@@ -197,7 +205,8 @@ class CpuRagEngine:
         asked = [list(c) for c in chunks]
         if self.compose_after > 0:
             chunks = self._lead(lambda: self.sched.merge_composed(asked))
-        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens))
+        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens,
+                                     temperature=float(temperature), seed=int(seed)))
         sent = 0
         while not req.done:
             self.step()
@@ -229,7 +238,7 @@ class CpuRagEngine:
             res = self.run_request([], req.chunks, req.query, keep_blocks=True)
             req.block_table, req.context_len = list(res.block_table), res.total_tokens
             req.restored_chunks = sum(res.restored)
-            req.generated.append(self._sample(res.logits))
+            req.generated.append(self._sample(res.logits, req))
             self.running.append(req)
         else:
             for req in list(self.running):
@@ -237,7 +246,7 @@ class CpuRagEngine:
                 if pos // bt >= len(req.block_table):
                     req.block_table.extend(self.blocks.alloc(1))
                 logits = self._forward([req.generated[-1]], torch.tensor([pos]), torch.tensor(req.block_table), pos)
-                req.generated.append(self._sample(logits))
+                req.generated.append(self._sample(logits, req))
         for req in list(self.running):
             if len(req.generated) >= req.max_new_tokens:
                 req.done = True

@@ -96,13 +96,16 @@ class GpuRagEngine:
     def _bcast(self, obj):
         return self.tp_ctx.broadcast_object(obj) if self.tp_ctx is not None else obj
 
-    def _prefill_tokens(self, tokens: Sequence[int], start_pos: int, table: list[int]) -> torch.Tensor:
-        """Run ``tokens`` through the model in pieces of at most ``max_tokens``; returns the last sample."""
+    def _prefill_tokens(self, tokens: Sequence[int], start_pos: int, table: list[int],
+                        sample: Optional[dict] = None) -> torch.Tensor:
+        """Run ``tokens`` through the model in pieces of at most ``max_tokens``; returns the last sample
+        (greedy, or drawn with ``sample = {"temperature", "seed"}``)."""
         out = None
         mt = self.runner.max_tokens
         for i in range(0, len(tokens), mt):
             piece = list(tokens[i : i + mt])
-            inp = self.runner.stage_inputs([{"tokens": piece, "start_pos": start_pos + i, "block_table": table}])
+            inp = self.runner.stage_inputs([{"tokens": piece, "start_pos": start_pos + i, "block_table": table,
+                                             **(sample or {})}])
             out = self.runner.forward(inp)
         return out
 
@@ -229,7 +232,8 @@ class GpuRagEngine:
                 if self.repair_tokens > 0 and off > 0:
                     self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table)
             ctx = off + len(c)
-        first = self._prefill_tokens(req.query, ctx, req.block_table)
+        sample = {"temperature": req.temperature, "seed": req.step_seed()} if req.temperature > 0 else None
+        first = self._prefill_tokens(req.query, ctx, req.block_table, sample)
         self._ev[3].record()
         token = int(first[0].item())  # device -> host read of the step's result
         t_end = time.perf_counter()
@@ -268,7 +272,7 @@ class GpuRagEngine:
     def _decode_step(self) -> None:
         batch = self.running[: self.runner.max_seqs]
         seqs = [{"tokens": [r.generated[-1]], "start_pos": r.context_len + len(r.generated) - 1,
-                 "block_table": r.block_table} for r in batch]
+                 "block_table": r.block_table, "temperature": r.temperature, "seed": r.step_seed()} for r in batch]
         inp = self.runner.stage_inputs(seqs)
         out = self.runner.forward(inp).tolist()
         for r, tok in zip(batch, out):
@@ -283,7 +287,7 @@ class GpuRagEngine:
         self.blocks.free(req.block_table)
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
-                 store_misses: bool = False, on_token=None) -> RagRequest:
+                 store_misses: bool = False, on_token=None, temperature: float = 0.0, seed: int = 0) -> RagRequest:
         """Serve one request to completion (the call a user of the engine makes).
 
         ``on_token(token_id)`` is called after each engine step with every token the step added
@@ -293,7 +297,8 @@ class GpuRagEngine:
         if self.compose_after > 0:
             # the rank that owns the scheduler half decides; every rank must serve the same list
             merged = self._bcast(self.sched.merge_composed(asked) if self.sched is not None else None)
-        req = self.submit(RagRequest(merged, list(query), max_new_tokens, store_misses=store_misses))
+        req = self.submit(RagRequest(merged, list(query), max_new_tokens, store_misses=store_misses,
+                                     temperature=float(temperature), seed=int(seed)))
         sent = 0
         while not req.done:
             self.step()

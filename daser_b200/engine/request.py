@@ -23,3 +23,10 @@ class RagRequest:
     timings: dict = field(default_factory=dict)
     done: bool = False
     store_misses: bool = False  # write the KV of chunks that had to be computed (cold pass)
+    # sampling: 0 = greedy; > 0 draws from softmax(logits / temperature), reproducibly from `seed`
+    temperature: float = 0.0
+    seed: int = 0
+
+    def step_seed(self) -> int:
+        """The seed of the token about to be sampled (one stream of noise per request and step)."""
+        return (self.seed * 1_000_003 + len(self.generated) + 1) & 0x7FFFFFFFFFFFFFFF

@@ -50,6 +50,9 @@ class StepInputs:
     max_q_len: int
     max_ctx: int
     persistent: bool = False  # tensors are the runner's own fixed buffers (graph replay is allowed)
+    # (inv_temp float32[num_seqs], seeds int64[num_seqs]) when a sequence of the step samples with a
+    # temperature; None = every sequence is greedy
+    sampling: Optional[tuple] = None
 
 
 class GpuModelRunner:
@@ -196,9 +199,17 @@ class GpuModelRunner:
             self._in_event = torch.cuda.Event()
         self._in_event.record()
         self.h2d_bytes = t * 16 + ns * (self.max_blocks * 4 + 20) + 4
+        sampling = None
+        if any(s.get("temperature", 0.0) > 0.0 for s in seqs):
+            # sampling runs outside the captured layer loop, so these need no fixed buffers
+            inv = torch.tensor([1.0 / s["temperature"] if s.get("temperature", 0.0) > 0.0 else 0.0 for s in seqs],
+                               dtype=torch.float32)
+            seeds = torch.tensor([int(s.get("seed", 0)) & 0x7FFFFFFFFFFFFFFF for s in seqs], dtype=torch.int64)
+            sampling = (inv.to(self.device), seeds.to(self.device))
+            self.h2d_bytes += ns * 12
         return StepInputs(d["tokens"][:t], d["positions"][:t], d["slot_mapping"][:t], d["block_tables"][:ns],
                           d["q_start"][: ns + 1], d["ctx_lens"][:ns], d["sample_rows"][:ns], t, ns, max_q, max_ctx,
-                          persistent=True)
+                          persistent=True, sampling=sampling)
 
     # -- one step -----------------------------------------------------------------------------------
     @torch.no_grad()
@@ -271,7 +282,7 @@ class GpuModelRunner:
         torch.index_select(normed, 0, inp.sample_rows[:n], out=self.last_rows[:n])
         gemm.linear(self.last_rows[:n], self.w.lm_head, acc=self.logits_acc[:n], status=self.status)
         ew.argmax(self.logits_acc[:n], self.best_val[:n], self.best_idx[:n],
-                  index_offset=self.rank * self.w.vocab_local, zero_after=True)
+                  index_offset=self.rank * self.w.vocab_local, zero_after=True, sampling=inp.sampling)
         return self.best_idx[:n]
 
     def logits(self, inp: StepInputs) -> torch.Tensor:

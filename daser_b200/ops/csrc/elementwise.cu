@@ -359,19 +359,42 @@ embedding_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restric
   }
 }
 
+// Standard Gumbel noise from a counter-based hash of (seed, vocabulary index): the same index gets
+// the same noise on whichever rank holds it, and no generator state is kept.
+__device__ __forceinline__ float gumbel_noise(uint64_t seed, uint32_t index) {
+  uint64_t z = seed + 0x9E3779B97F4A7C15ull * ((uint64_t)index + 1ull);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  z ^= z >> 31;
+  // 23 random bits + 0.5: every value is exact in fp32 and strictly inside (0, 1), so both logs are finite
+  const float u = ((float)(uint32_t)(z >> 41) + 0.5f) * (1.0f / 8388608.0f);
+  return -__logf(-__logf(u));
+}
+
 // Greedy sampling: argmax over a row of logits; packs (value, index) so ties pick the lowest index.
-template <typename TIn>
+// GUMBEL: temperature sampling by the Gumbel-max rule.  argmax_i(logit_i / T + g_i) with independent
+// standard Gumbel g_i is a draw from softmax(logits / T), and a maximum composes across vocabulary
+// shards, so tensor-parallel ranks sample exactly by exchanging their (value, index) candidates as
+// they do for greedy.  inv_temp[row] == 0 leaves that row greedy.
+template <typename TIn, bool GUMBEL = false>
 __global__ void __launch_bounds__(1024)
 argmax_kernel(TIn* __restrict__ logits, int64_t stride, int n, int index_offset,
-              float* __restrict__ best_val, int32_t* __restrict__ best_idx, int zero_after) {
+              float* __restrict__ best_val, int32_t* __restrict__ best_idx, int zero_after,
+              const float* __restrict__ inv_temp = nullptr, const uint64_t* __restrict__ seeds = nullptr) {
   __shared__ float s_v[32];
   __shared__ int s_i[32];
   TIn* row = logits + blockIdx.x * stride;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
+  const float it = GUMBEL ? inv_temp[blockIdx.x] : 0.f;
+  const uint64_t seed = GUMBEL ? seeds[blockIdx.x] : 0ull;
   for (int c = threadIdx.x * 8; c < n; c += blockDim.x * 8) {
     float v[8];
     Loader<TIn>::load8(row + c, v, zero_after != 0);
+    if (GUMBEL && it > 0.f) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * it + gumbel_noise(seed, (uint32_t)(c + i + index_offset));
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (c + i < n && (v[i] > bv)) { bv = v[i]; bi = c + i; }
@@ -570,6 +593,19 @@ DASER_API int daser_embedding(const int32_t* ids, const void* table, void* out, 
   if (T == 0) return 0;
   embedding_kernel<<<ew_grid(T * (hidden / 8), 256), 256, 0, stream>>>(
       ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, hidden, vocab_begin, vocab_count);
+  return (int)cudaGetLastError();
+}
+
+// Temperature sampling (Gumbel-max): inv_temp[rows] = 1 / temperature (0 = greedy for that row),
+// seeds[rows] = one 64-bit seed per row and step.
+DASER_API int daser_argmax_sample(void* logits, int is_fp32, int64_t stride, int rows, int n, int index_offset,
+                                  float* best_val, int32_t* best_idx, int zero_after, const float* inv_temp,
+                                  const uint64_t* seeds, cudaStream_t stream) {
+  using namespace daser;
+  if (rows < 0 || n <= 0 || stride % 8 || !inv_temp || !seeds) return DASER_ERR_BAD_ARG;
+  if (rows == 0) return 0;
+  if (is_fp32) argmax_kernel<float, true><<<rows, 1024, 0, stream>>>((float*)logits, stride, n, index_offset, best_val, best_idx, zero_after, inv_temp, seeds);
+  else argmax_kernel<__nv_bfloat16, true><<<rows, 1024, 0, stream>>>((__nv_bfloat16*)logits, stride, n, index_offset, best_val, best_idx, 0, inv_temp, seeds);
   return (int)cudaGetLastError();
 }
 

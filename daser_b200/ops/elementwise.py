@@ -173,8 +173,27 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor
 
 
 def argmax(logits: torch.Tensor, best_val: torch.Tensor, best_idx: torch.Tensor,
-           index_offset: int = 0, zero_after: bool = False) -> None:
+           index_offset: int = 0, zero_after: bool = False,
+           sampling: Optional[tuple[torch.Tensor, torch.Tensor]] = None) -> None:
+    """Per row: the index (plus ``index_offset``) and value of the largest logit.
+
+    ``sampling = (inv_temp float32[rows], seeds int64[rows])`` draws from ``softmax(logits * inv_temp)``
+    instead, by the Gumbel-max rule (``best_val`` is then the perturbed maximum, which is what
+    tensor-parallel ranks compare); rows with ``inv_temp == 0`` stay greedy."""
     rows, n = logits.shape
+    if sampling is not None:
+        inv_temp, seeds = sampling
+        assert inv_temp.dtype == torch.float32 and seeds.dtype == torch.int64
+        assert inv_temp.numel() >= rows and seeds.numel() >= rows
+        _lib.check(
+            _lib.lib().daser_argmax_sample(C.c_void_p(logits.data_ptr()), _is_f32(logits), C.c_int64(logits.stride(0)),
+                                           rows, n, index_offset, C.c_void_p(best_val.data_ptr()),
+                                           C.c_void_p(best_idx.data_ptr()), int(zero_after),
+                                           C.c_void_p(inv_temp.data_ptr()), C.c_void_p(seeds.data_ptr()),
+                                           _lib.stream_ptr()),
+            "argmax_sample",
+        )
+        return
     _lib.check(
         _lib.lib().daser_argmax(C.c_void_p(logits.data_ptr()), _is_f32(logits), C.c_int64(logits.stride(0)),
                                 rows, n, index_offset, C.c_void_p(best_val.data_ptr()),

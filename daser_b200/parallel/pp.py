@@ -158,8 +158,8 @@ class PipelineCpuEngine(CpuRagEngine):
         self.link.send_next(out)  # asynchronous: this stage moves on to the next piece
         return None
 
-    def _sample(self, logits: Optional[torch.Tensor]) -> int:
-        token = self.link.token_from_last(int(logits[-1].argmax()) if self.link.last else None)
+    def _sample(self, logits: Optional[torch.Tensor], req=None) -> int:
+        token = self.link.token_from_last(super()._sample(logits, req) if self.link.last else None)
         self.link.drain()  # the token exists, so every hand-over that led to it has completed
         return token
 

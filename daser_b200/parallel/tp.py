@@ -461,8 +461,10 @@ class TPContext:
                       base_ptr=self.epochs.data_ptr() + 4)
         torch.index_select(self.gathered, 0, inp.sample_rows[:n], out=runner.last_rows[:n])
         gemm.linear(runner.last_rows[:n], runner.w.lm_head, acc=runner.logits_acc[:n], status=runner.status)
+        # (with a temperature the values are Gumbel-perturbed: their maximum over the ranks' shards
+        # is the sample, the noise being a function of the seed and the global vocabulary index)
         ew.argmax(runner.logits_acc[:n], runner.best_val[:n], runner.best_idx[:n],
-                  index_offset=self.rank * runner.w.vocab_local, zero_after=True)
+                  index_offset=self.rank * runner.w.vocab_local, zero_after=True, sampling=inp.sampling)
         cand = self.cand[:, :n]
         cand[0].copy_(runner.best_val[:n])
         cand[1].copy_(runner.best_idx[:n].to(torch.float32))

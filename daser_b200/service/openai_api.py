@@ -17,7 +17,8 @@ Cache reuse needs no cooperation from the caller: the prompt's token ids are sca
 control plane (``lookup_chunks`` with tokens: every stored chunk that appears at a block-aligned
 offset), the prompt is cut at the hits, and the pieces go to the engine as segments: hits are
 restored (keys re-rotated to their new positions), the gaps and the tail are computed.  Sampling is
-greedy; ``temperature`` and the other sampling fields are accepted and ignored.
+greedy by default (``temperature`` 0); a positive ``temperature`` draws from the softmax, reproducibly
+when ``seed`` is given.  ``top_p`` / ``top_k`` and the other sampling fields are accepted and ignored.
 
 ``"stream": true`` answers with server-sent events, one per sampled token (vLLM's shape), so a
 client sees the first token when the prefill step ends rather than when the request does.
@@ -46,6 +47,7 @@ class CompletionRequest(BaseModel):
     prompt: Any
     max_tokens: int = 16
     temperature: float = 0.0
+    seed: Optional[int] = None
     stream: bool = False
 
     model_config = {"extra": "allow"}
@@ -75,6 +77,13 @@ def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_t
     return segments
 
 
+def _gen_params(req: CompletionRequest) -> dict[str, Any]:
+    params: dict[str, Any] = {"max_tokens": req.max_tokens, "temperature": req.temperature}
+    if req.seed is not None:
+        params["seed"] = req.seed
+    return params
+
+
 async def _sse(engine_client: Any, req: CompletionRequest, tokens: list[int], segments: list[list[int]],
                model_name: str, t0: float):
     """Server-sent events in vLLM's shape: one ``text_completion`` object per token, a last one with
@@ -84,7 +93,7 @@ async def _sse(engine_client: Any, req: CompletionRequest, tokens: list[int], se
     base = {"id": rid, "object": "text_completion", "created": int(t0), "model": req.model or model_name}
     first = True
     try:
-        async for item in engine_client.completion_stream(tokens, {"max_tokens": req.max_tokens}, segments=segments):
+        async for item in engine_client.completion_stream(tokens, _gen_params(req), segments=segments):
             if item.get("done"):
                 usage = item["usage"]
                 n_out = int(usage.get("completion_tokens", 0))
@@ -145,7 +154,7 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             return StreamingResponse(_sse(engine_client, req, tokens, segments, model_name, t0),
                                      media_type="text/event-stream")
         try:
-            out = await engine_client.completion(tokens, {"max_tokens": req.max_tokens}, segments=segments)
+            out = await engine_client.completion(tokens, _gen_params(req), segments=segments)
             aligned = len(tokens) // block_tokens * block_tokens
             covered = any(int(h["offset"]) == 0 and int(h["token_count"]) >= aligned for h in hits)
             if req.max_tokens == 1 and aligned and not covered:

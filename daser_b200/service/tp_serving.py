@@ -75,7 +75,7 @@ class TPLeaderEngine:
     # iteration-level calls (an engine loop drives these instead of `generate`)
     def submit(self, req: Any) -> Any:
         self._announce(CMD_SUBMIT, [list(c) for c in req.chunks], list(req.query), int(req.max_new_tokens),
-                       bool(req.store_misses))
+                       bool(req.store_misses), float(req.temperature), int(req.seed))
         return self._engine.submit(req)
 
     def has_work(self) -> bool:
@@ -121,8 +121,9 @@ def follower_loop(engine: Any, broadcast: Broadcast, on_step: Optional[Callable[
         elif op == CMD_SUBMIT:
             from daser_b200.engine.request import RagRequest
 
-            _, chunks, query, max_new, store_misses = cmd
-            engine.submit(RagRequest(chunks, query, max_new, store_misses=store_misses))
+            _, chunks, query, max_new, store_misses, temperature, seed = cmd
+            engine.submit(RagRequest(chunks, query, max_new, store_misses=store_misses, temperature=temperature,
+                                     seed=seed))
         elif op == CMD_STEP:
             engine.step()
         elif op == CMD_WARM_UP:

@@ -13,6 +13,7 @@ are restored at their offsets instead of being recomputed.
 from __future__ import annotations
 
 import asyncio
+import random
 from typing import Any, Optional, Sequence
 
 
@@ -158,11 +159,23 @@ class NativeEngineClient:
         t = list(tokens)
         return t + [self._pad] * (-len(t) % bt)
 
-    def _generate(self, segments, query, max_new, on_token=None):
+    @staticmethod
+    def _sampling(params: dict[str, Any]) -> dict[str, Any]:
+        """``temperature`` / ``seed`` of a request as the engines take them.  Greedy unless a positive
+        temperature is asked for; an unseeded sampling request gets a fresh seed here, once, so that
+        every tensor-parallel rank draws with the same one."""
+        t = float(params.get("temperature") or 0.0)
+        if t <= 0.0:
+            return {}
+        seed = params.get("seed")
+        return {"temperature": t, "seed": int(seed) if seed is not None else random.getrandbits(62)}
+
+    def _generate(self, segments, query, max_new, on_token=None, sampling=None):
         eng = self._engine
         chunks = [self._pad_block(s) for s in segments if len(s)]
         if hasattr(eng, "generate"):
             kw = {"on_token": on_token} if on_token is not None else {}
+            kw.update(sampling or {})
             req = eng.generate(chunks, list(query), max_new_tokens=max_new, **kw)
             return req.generated, req.context_len
         res = eng.run_request([], chunks, list(query))
@@ -178,14 +191,15 @@ class NativeEngineClient:
             *cached, query = segments
         else:
             cached, query = [], tokens
+        sampling = self._sampling(params)
         if self._loop is not None:
             chunks = [self._pad_block(s) for s in cached if len(s)]
-            req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new))
+            req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new, **sampling))
             gen, prompt_len = req.generated, req.context_len
         else:
             async with self._lock:
                 gen, prompt_len = await asyncio.get_running_loop().run_in_executor(
-                    None, self._guard, self._generate, cached, query, max_new)
+                    None, self._guard, self._generate, cached, query, max_new, None, sampling)
         return {
             "choices": [{"text": self._detok(gen), "token_ids": gen}],
             "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)},
@@ -203,6 +217,7 @@ class NativeEngineClient:
             *cached, query = segments
         else:
             cached, query = [], tokens
+        sampling = self._sampling(params)
         loop = asyncio.get_running_loop()
         queue: asyncio.Queue = asyncio.Queue()
         push = lambda tok: loop.call_soon_threadsafe(queue.put_nowait, int(tok))  # noqa: E731
@@ -211,12 +226,13 @@ class NativeEngineClient:
                 chunks = [self._pad_block(s) for s in cached if len(s)]
 
                 async def stepped():
-                    req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new, on_token=push))
+                    req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new, on_token=push,
+                                                                      **sampling))
                     return req.generated, req.context_len
 
                 fut = asyncio.ensure_future(stepped())
             else:
-                fut = loop.run_in_executor(None, self._guard, self._generate, cached, query, max_new, push)
+                fut = loop.run_in_executor(None, self._guard, self._generate, cached, query, max_new, push, sampling)
             fut.add_done_callback(lambda _f: queue.put_nowait(None))  # runs on the loop: after every token
             sent: list[int] = []
             text = ""

@@ -210,7 +210,7 @@ def scenario_serve() -> int:
 
         def submit(self, req):
             self.calls.append(("submit", tuple(map(tuple, req.chunks)), tuple(req.query), req.max_new_tokens,
-                               req.store_misses))
+                               req.store_misses, req.temperature, req.seed))
             return req
 
         def has_work(self):
@@ -235,7 +235,7 @@ def scenario_serve() -> int:
         # the iteration-level calls an engine loop makes
         from daser_b200.engine.request import RagRequest
 
-        lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True))
+        lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True, temperature=0.5, seed=42))
         lead.step()
         lead.step()
         lead.close()

@@ -1,0 +1,70 @@
+"""Temperature sampling (Gumbel-max) on the oracle engine and through the HTTP front end."""
+
+import random
+
+import torch
+
+from conftest import LiveControlPlane
+from daser_b200.engine.rag_cpu import CpuRagEngine
+from daser_b200.engine.request import RagRequest
+from daser_b200.kv.layout import KVGeometry
+from daser_b200.models.llama import PRESETS
+
+
+def test_draws_follow_the_softmax_and_repeat_with_the_seed():
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5]])
+    temp = 0.7
+    eng = CpuRagEngine.__new__(CpuRagEngine)                  # _sample needs no engine state
+    counts = torch.zeros(5)
+    for seed in range(6000):
+        counts[eng._sample(logits, RagRequest([], [1], 4, temperature=temp, seed=seed))] += 1
+    want = torch.softmax(logits[0] / temp, 0)
+    assert (counts / counts.sum() - want).abs().max().item() < 0.02
+    req = RagRequest([], [1], 4, temperature=temp, seed=11)
+    assert eng._sample(logits, req) == eng._sample(logits, req)                       # same seed and step
+    assert eng._sample(logits, RagRequest([], [1], 4)) == 2                           # temperature 0: greedy
+    seen = set()
+    for step in range(40):                                                            # steps draw differently
+        req.generated = [0] * step
+        seen.add(eng._sample(logits, req))
+    assert len(seen) > 1
+
+
+def test_engine_and_http_sampling_are_reproducible_per_seed(tmp_path):
+    from fastapi.testclient import TestClient
+
+    from daser_b200.service.http_api import ByteTokenizer, ServiceConfig, build_service_app
+    from daser_b200.service.openai_api import mount_openai_routes
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=128)
+    try:
+        rng = random.Random(0)
+        query = [rng.randrange(cfg.vocab_size) for _ in range(12)]
+        greedy = eng.generate([], query, max_new_tokens=8).generated
+        a = eng.generate([], query, max_new_tokens=8, temperature=1.5, seed=3).generated
+        b = eng.generate([], query, max_new_tokens=8, temperature=1.5, seed=3).generated
+        c = eng.generate([], query, max_new_tokens=8, temperature=1.5, seed=4).generated
+        assert a == b and a != c and a != greedy
+        tok = ByteTokenizer()
+        client_obj = NativeEngineClient(eng, tok.decode)
+        app = build_service_app(ServiceConfig("", "toy", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2),
+                                engine_client=client_obj, tokenizer=tok)
+        mount_openai_routes(app, client_obj, tok, lp.socket_path, "toy", "default", 16)
+        with TestClient(app) as client:
+            def post(**kw):
+                r = client.post("/v1/completions", json={"prompt": query, "max_tokens": 8, **kw})
+                assert r.status_code == 200, r.text
+                return r.json()["choices"][0]["token_ids"]
+
+            assert post() == greedy == post(temperature=0)
+            assert post(temperature=1.5, seed=3) == a                       # the engine's draw, over HTTP
+            assert post(temperature=1.5, seed=3) == post(temperature=1.5, seed=3)
+            draws = {tuple(post(temperature=1.5)) for _ in range(4)}        # unseeded: a fresh seed per request
+            assert len(draws) > 1
+    finally:
+        eng.close()
+        lp.stop()

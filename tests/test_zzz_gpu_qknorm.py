@@ -46,3 +46,41 @@ def test_runner_with_qk_norm_matches_reference_forward():
     reference_forward(plain, torch.tensor(tokens[:33]), torch.arange(33), pool2, torch.tensor(table), 0, return_logits=False)
     other = reference_forward(plain, torch.tensor(tokens[33:]), torch.arange(33, 40), pool2, torch.tensor(table), 33)[-1]
     assert torch.nn.functional.cosine_similarity(other, want, dim=0).item() < 0.97
+
+
+def test_gumbel_max_sampling_kernel_is_exact_across_vocabulary_shards_and_follows_the_softmax():
+    """Temperature sampling as an argmax over Gumbel-perturbed logits: the noise depends on (seed,
+    global vocabulary index) only, so two shards that exchange their best (value, index) pick what one
+    rank holding the whole row picks; over many seeds the picks follow softmax(logits / T)."""
+    from daser_b200.ops import elementwise as ew
+
+    torch.manual_seed(0)
+    n, rows, temp = 64, 8192, 0.8
+    base = torch.randn(n) * 1.5
+    logits = base.repeat(rows, 1).to("cuda", torch.float32).contiguous()
+    inv = torch.full((rows,), 1.0 / temp, dtype=torch.float32, device="cuda")
+    inv[0] = 0.0                                                   # row 0 stays greedy
+    seeds = torch.arange(rows, dtype=torch.int64, device="cuda") * 7919 + 13
+    val = torch.empty(rows, dtype=torch.float32, device="cuda")
+    idx = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ew.argmax(logits, val, idx, sampling=(inv, seeds))
+    torch.cuda.synchronize()
+    assert int(idx[0]) == int(base.argmax())
+    # two shards of 32 with their global offsets, combined by the larger perturbed value
+    v = [torch.empty_like(val) for _ in range(2)]
+    i = [torch.empty_like(idx) for _ in range(2)]
+    for s in range(2):
+        ew.argmax(logits[:, 32 * s : 32 * (s + 1)].contiguous(), v[s], i[s], index_offset=32 * s, sampling=(inv, seeds))
+    torch.cuda.synchronize()
+    combined = torch.where(v[1] > v[0], i[1], i[0])
+    assert torch.equal(combined, idx)
+    freq = torch.bincount(idx[1:].long().cpu(), minlength=n).float() / (rows - 1)
+    want = torch.softmax(base / temp, 0)
+    assert (freq - want).abs().max().item() < 0.02, (freq - want).abs().max().item()
+    # same seeds, same draw; other seeds, another draw
+    idx2 = torch.empty_like(idx)
+    ew.argmax(logits, val, idx2, sampling=(inv, seeds))
+    idx3 = torch.empty_like(idx)
+    ew.argmax(logits, val, idx3, sampling=(inv, seeds + 1))
+    torch.cuda.synchronize()
+    assert torch.equal(idx2, idx) and not torch.equal(idx3, idx)
