@@ -1,7 +1,6 @@
-"""Qwen3-style per-head query / key norm on the CUDA runner against the fp32 PyTorch model.
-
-Runs last (file name) on purpose: the norm lives in a variant of the RoPE + cache-write kernel
-that the Llama models never launch."""
+"""Kernel variants that the Llama models with greedy decoding never launch: the Qwen3-style per-head
+query / key norm inside the RoPE + cache-write kernel, and temperature sampling inside the argmax
+kernel.  Runs last (file name) on purpose."""
 
 import random
 
