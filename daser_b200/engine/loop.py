@@ -109,7 +109,10 @@ class EngineLoop:
             t.sent = len(t.req.generated)
             if t.req.done:
                 self._tracked.remove(t)
-                t.future.set_result(t.req)
+                if t.req.error is not None:  # given up alone (it can never fit): the others go on
+                    t.future.set_exception(MemoryError(t.req.error))
+                else:
+                    t.future.set_result(t.req)
 
     def _fail(self, exc: BaseException) -> None:
         self.failed = exc

@@ -214,6 +214,8 @@ class CpuRagEngine:
                 for tok in req.generated[sent:]:
                     on_token(tok)
                 sent = len(req.generated)
+        if req.error is not None:
+            raise MemoryError(req.error)
         if self.compose_after > 0:
             combo = self._lead(lambda: self.sched.note_composition(asked, self.compose_after))
             if combo is not None:
@@ -234,17 +236,26 @@ class CpuRagEngine:
         what is missing, first token), else one more token for every running request."""
         bt = self.cfg.block_tokens
         if self.waiting:
+            # admission as in the GPU engine: all blocks of the request up front, or wait for the
+            # running requests to finish, or (idle engine, still too large) give this one up alone
+            req = self.waiting[0]
+            need = req.blocks_needed(bt)
+            if need > self.blocks.num_free and not self.running:
+                self.waiting.pop(0)
+                req.error = f"{need} KV blocks needed, the pool has {self.blocks.num_free} free of {self.blocks.num_blocks}"
+                req.done = True
+                return
+        if self.waiting and self.waiting[0].blocks_needed(bt) <= self.blocks.num_free:
             req = self.waiting.pop(0)
             res = self.run_request([], req.chunks, req.query, keep_blocks=True)
             req.block_table, req.context_len = list(res.block_table), res.total_tokens
+            req.block_table.extend(self.blocks.alloc(req.blocks_needed(bt) - len(req.block_table)))
             req.restored_chunks = sum(res.restored)
             req.generated.append(self._sample(res.logits, req))
             self.running.append(req)
         else:
             for req in list(self.running):
                 pos = req.context_len + len(req.generated) - 1
-                if pos // bt >= len(req.block_table):
-                    req.block_table.extend(self.blocks.alloc(1))
                 logits = self._forward([req.generated[-1]], torch.tensor([pos]), torch.tensor(req.block_table), pos)
                 req.generated.append(self._sample(logits, req))
         for req in list(self.running):

@@ -181,12 +181,37 @@ class GpuRagEngine:
     def step(self) -> None:
         if self.tp_ctx is not None:
             self.tp_ctx.check_peers()  # host-side: a lost peer ends the step before any launch
+        if self.waiting and not self._admit():
+            return
         if self.waiting:
             with trace.span("engine.ttft_step", "engine"):
                 self._ttft_step(self.waiting.pop(0))
         elif self.running:
             with trace.span("engine.decode_step", "engine", batch=len(self.running)):
                 self._decode_step()
+
+    def _admit(self) -> bool:
+        """May the oldest waiting request start now?  If the pool lacks the blocks, the running
+        requests get a decode step instead (they free theirs when they finish); a request that
+        cannot fit even an idle engine is given up alone (``error``), the others go on.  The answer
+        depends on queue and pool state only, which every tensor-parallel rank shares."""
+        req = self.waiting[0]
+        need = req.blocks_needed(self.cfg.block_tokens)
+        why = None
+        if need > self.runner.max_blocks:
+            why = f"{need} KV blocks exceed the runner's limit of {self.runner.max_blocks} per sequence"
+        elif need > self.blocks.num_free and not self.running:
+            why = f"{need} KV blocks needed, the pool has {self.blocks.num_free} free of {self.blocks.num_blocks}"
+        if why is not None:
+            self.waiting.pop(0)
+            req.error, req.done = why, True
+            metrics.inc("engine.requests_rejected")
+            return False
+        if need > self.blocks.num_free:
+            with trace.span("engine.decode_step", "engine", batch=len(self.running)):
+                self._decode_step()
+            return False
+        return True
 
     def _ttft_step(self, req: RagRequest) -> None:
         cfg, bt = self.cfg, self.cfg.block_tokens
@@ -306,6 +331,8 @@ class GpuRagEngine:
                 for tok in req.generated[sent:]:
                     on_token(int(tok))
                 sent = len(req.generated)
+        if req.error is not None:
+            raise MemoryError(req.error)
         if self.compose_after > 0:
             combo = self._bcast(self.sched.note_composition(asked, self.compose_after) if self.sched is not None else None)
             if combo is not None:

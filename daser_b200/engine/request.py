@@ -3,6 +3,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from typing import Optional
 
 
 @dataclass
@@ -26,6 +27,15 @@ class RagRequest:
     # sampling: 0 = greedy; > 0 draws from softmax(logits / temperature), reproducibly from `seed`
     temperature: float = 0.0
     seed: int = 0
+    # set (with done) when the engine gave the request up without touching the others: it can never
+    # fit the KV pool or the runner's buffers
+    error: Optional[str] = None
+
+    def blocks_needed(self, block_tokens: int) -> int:
+        """KV blocks of the whole request, generation included (reserved up front, so that a running
+        request can never be starved of blocks by later arrivals)."""
+        total = sum(len(c) for c in self.chunks) + len(self.query) + self.max_new_tokens
+        return -(-total // block_tokens)
 
     def step_seed(self) -> int:
         """The seed of the token about to be sampled (one stream of noise per request and step)."""

@@ -160,6 +160,8 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             if req.max_tokens == 1 and aligned and not covered:
                 await engine_client.prefill(tokens[:aligned])  # a prefill request leaves its KV in the store
                 metrics.inc("service.completion_stores")
+        except MemoryError as exc:  # the request can never fit the KV pool: the caller's problem, as in vLLM
+            raise HTTPException(400, f"request too large: {exc}") from exc
         except Exception as exc:
             raise HTTPException(502, f"engine failed: {exc}") from exc
         metrics.observe("service.completion_ms", (time.time() - t0) * 1e3)

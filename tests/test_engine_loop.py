@@ -119,3 +119,31 @@ def test_a_callers_error_in_call_does_not_stop_the_loop(engine):
         assert len(loop.submit([], [9, 9], 2).result(60).generated) == 2
     finally:
         loop.close()
+
+
+def test_a_request_that_cannot_fit_is_given_up_alone_and_one_that_must_wait_waits(tmp_path):
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=64, slot_size=geo.slot_size, num_layers=cfg.num_layers,
+                          num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim, dtype_bytes=4)
+    lp.start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=8)     # 128 tokens of KV in all
+    loop = EngineLoop(eng)
+    try:
+        a = loop.submit([], list(range(1, 60)), 30)          # 89 tokens: 6 blocks
+        b = loop.submit([], list(range(1, 50)), 20)          # 69 tokens: 5 blocks, does not fit beside a
+        huge = loop.submit([], list(range(1, 120)), 40)      # 159 tokens: 10 blocks, never fits
+        ra = a.result(120)
+        rb = b.result(120)                                   # waited for a's blocks, then ran
+        with pytest.raises(MemoryError, match="KV blocks"):
+            huge.result(120)
+        assert len(ra.generated) == 30 and len(rb.generated) == 20
+        assert loop.failed is None and eng.blocks.num_free == 8
+        assert len(loop.submit([], [5, 6, 7], 2).result(60).generated) == 2      # the loop lives on
+    finally:
+        loop.close()
+    with pytest.raises(MemoryError):
+        eng.generate([], list(range(1, 120)), max_new_tokens=40)
+    assert eng.blocks.num_free == 8
+    eng.close()
+    lp.stop()
