@@ -64,6 +64,13 @@ class EngineLoop:
         self._inbox.put(("submit", _Tracked(req, fut, on_token)))
         return fut
 
+    def cancel(self, fut: Future) -> None:
+        """Stop working on the request behind ``fut`` (as returned by :meth:`submit`): it leaves the
+        engine between two steps and the future fails with ``CancelledError``-like ``RuntimeError``.
+        Harmless when the request has finished."""
+        if not fut.done():
+            self._inbox.put(("cancel", fut))
+
     def call(self, method: str, *args: Any, **kw: Any) -> Future:
         """Run ``engine.<method>(*args, **kw)`` on the loop thread, between two steps."""
         fut: Future = Future()
@@ -88,6 +95,18 @@ class EngineLoop:
         if kind == "submit":
             self.engine.submit(item.req)
             self._tracked.append(item)
+        elif kind == "cancel":
+            for t in self._tracked:
+                if t.future is item:
+                    if hasattr(self.engine, "abort"):
+                        self.engine.abort(t.req.req_id)
+                    else:
+                        t.on_token = None  # an engine without abort runs the request out, unobserved
+                        break
+                    self._tracked.remove(t)
+                    if not t.future.done():
+                        t.future.set_exception(RuntimeError("request cancelled"))
+                    break
         elif kind == "call":
             fut, method, args, kw = item
             try:
@@ -125,7 +144,7 @@ class EngineLoop:
                 kind, item = self._inbox.get_nowait()
             except queue.Empty:
                 break
-            fut = item.future if kind == "submit" else (item[0] if kind == "call" else None)
+            fut = item.future if kind == "submit" else (item[0] if kind == "call" else None)  # cancels: nothing to tell
             if fut is not None and not fut.done():
                 fut.set_exception(exc)
 

@@ -231,6 +231,19 @@ class CpuRagEngine:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def abort(self, req_id: str) -> bool:
+        """Drop a waiting or running request between two steps (a client that went away); its blocks
+        go back to the pool.  False when the request is unknown or already finished."""
+        for queue in (self.waiting, self.running):
+            for req in queue:
+                if req.req_id == req_id:
+                    queue.remove(req)
+                    if req.block_table:
+                        self.blocks.free(req.block_table)
+                    req.error, req.done = "aborted", True
+                    return True
+        return False
+
     def step(self) -> None:
         """One engine iteration: the prefill of the oldest waiting request (restore, compute
         what is missing, first token), else one more token for every running request."""

@@ -178,6 +178,20 @@ class GpuRagEngine:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def abort(self, req_id: str) -> bool:
+        """Drop a waiting or running request between two steps (a client that went away); its blocks
+        go back to the pool.  False when the request is unknown or already finished."""
+        for queue in (self.waiting, self.running):
+            for req in queue:
+                if req.req_id == req_id:
+                    queue.remove(req)
+                    if req.block_table:
+                        self.blocks.free(req.block_table)
+                    req.error, req.done = "aborted", True
+                    metrics.inc("engine.requests_aborted")
+                    return True
+        return False
+
     def step(self) -> None:
         if self.tp_ctx is not None:
             self.tp_ctx.check_peers()  # host-side: a lost peer ends the step before any launch

@@ -38,6 +38,7 @@ CMD_GENERATE = "generate"
 CMD_WARM_UP = "warm_up"
 CMD_SUBMIT = "submit"
 CMD_STEP = "step"
+CMD_ABORT = "abort"
 CMD_STOP = "stop"
 
 
@@ -85,6 +86,10 @@ class TPLeaderEngine:
         self._announce(CMD_STEP)
         self._engine.step()
 
+    def abort(self, req_id: str) -> bool:
+        self._announce(CMD_ABORT, req_id)  # request ids are assigned in submit order: the same on every rank
+        return self._engine.abort(req_id)
+
     def warm_up(self, *args: Any, **kw: Any) -> None:
         self._announce(CMD_WARM_UP, list(args), dict(kw))
         self._engine.warm_up(*args, **kw)
@@ -126,6 +131,8 @@ def follower_loop(engine: Any, broadcast: Broadcast, on_step: Optional[Callable[
                                      seed=seed))
         elif op == CMD_STEP:
             engine.step()
+        elif op == CMD_ABORT:
+            engine.abort(cmd[1])
         elif op == CMD_WARM_UP:
             engine.warm_up(*cmd[1], **cmd[2])
         else:

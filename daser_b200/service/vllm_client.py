@@ -225,9 +225,10 @@ class NativeEngineClient:
             if self._loop is not None:
                 chunks = [self._pad_block(s) for s in cached if len(s)]
 
+                ticket = self._loop.submit(chunks, query, max_new, on_token=push, **sampling)
+
                 async def stepped():
-                    req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new, on_token=push,
-                                                                      **sampling))
+                    req = await asyncio.wrap_future(ticket)
                     return req.generated, req.context_len
 
                 fut = asyncio.ensure_future(stepped())
@@ -236,16 +237,23 @@ class NativeEngineClient:
             fut.add_done_callback(lambda _f: queue.put_nowait(None))  # runs on the loop: after every token
             sent: list[int] = []
             text = ""
-            while True:
-                tok = await queue.get()
-                if tok is None:
-                    break
-                sent.append(tok)
-                # detokenise the whole run and send the new suffix: pieces of one token can change
-                # with what follows (byte-level merges)
-                full = self._detok(sent)
-                piece, text = (full[len(text):], full) if full.startswith(text) else (full, full)
-                yield {"token_ids": [tok], "text": piece}
+            try:
+                while True:
+                    tok = await queue.get()
+                    if tok is None:
+                        break
+                    sent.append(tok)
+                    # detokenise the whole run and send the new suffix: pieces of one token can change
+                    # with what follows (byte-level merges)
+                    full = self._detok(sent)
+                    piece, text = (full[len(text):], full) if full.startswith(text) else (full, full)
+                    yield {"token_ids": [tok], "text": piece}
+            finally:
+                # the consumer went away mid-stream (client disconnect closes this generator): take the
+                # request out of the engine instead of generating the rest for nobody
+                if self._loop is not None and not fut.done():
+                    self._loop.cancel(ticket)
+                    fut.cancel()
             gen, prompt_len = await fut  # raises here if the engine failed
             if len(sent) < len(gen):  # an engine without token callbacks: everything at the end
                 rest = gen[len(sent):]

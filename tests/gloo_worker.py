@@ -219,6 +219,10 @@ def scenario_serve() -> int:
         def step(self):
             self.calls.append(("step",))
 
+        def abort(self, req_id):
+            self.calls.append(("abort", req_id))
+            return True
+
         def close(self):
             self.calls.append(("close",))
 
@@ -238,6 +242,7 @@ def scenario_serve() -> int:
         lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True, temperature=0.5, seed=42))
         lead.step()
         lead.step()
+        lead.abort("req-7")
         lead.close()
         try:
             lead.store_chunk([1] * 16)
@@ -246,10 +251,10 @@ def scenario_serve() -> int:
             refused = True
     else:
         steps = follower_loop(eng, _bcast)
-        refused = steps == 8
+        refused = steps == 9
     logs = [None] * world
     dist.all_gather_object(logs, (eng.calls, refused))
-    good = all(log == logs[0][0] for log, _ in logs) and all(r for _, r in logs) and len(logs[0][0]) == 9
+    good = all(log == logs[0][0] for log, _ in logs) and all(r for _, r in logs) and len(logs[0][0]) == 10
     if rank == 0:
         print("SERVE_OK" if good else f"SERVE_FAIL {logs}", flush=True)
     dist.destroy_process_group()

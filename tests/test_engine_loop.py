@@ -147,3 +147,49 @@ def test_a_request_that_cannot_fit_is_given_up_alone_and_one_that_must_wait_wait
     assert eng.blocks.num_free == 8
     eng.close()
     lp.stop()
+
+
+def test_cancelled_requests_leave_the_engine_and_return_their_blocks(engine):
+    import asyncio
+
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    loop = EngineLoop(engine)
+    free = engine.blocks.num_free
+    try:
+        got = []
+        long_one = loop.submit([], [1, 2, 3], 400, on_token=got.append)
+        other = loop.submit([], [4, 5, 6], 5)
+        while len(got) < 3:
+            time.sleep(0.01)
+        loop.cancel(long_one)
+        with pytest.raises(RuntimeError, match="cancelled"):
+            long_one.result(30)
+        assert len(other.result(60).generated) == 5            # the neighbour was not disturbed
+        assert len(got) < 400
+        loop.cancel(other)                                     # finished already: nothing happens
+        assert loop.call("has_work").result(10) is False and engine.blocks.num_free == free
+        assert engine.abort("no-such-request") is False
+    finally:
+        loop.close()
+
+    # the same through the streaming client: a consumer that stops reading cancels the request
+    client = NativeEngineClient(engine, lambda ids: "".join(chr(65 + i % 26) for i in ids), batching=True)
+
+    async def read_three():
+        agen = client.completion_stream([1, 2, 3], {"max_tokens": 400})
+        seen = []
+        async for item in agen:
+            seen.append(item)
+            if len(seen) == 3:
+                break
+        await agen.aclose()
+        for _ in range(200):                                   # the abort happens between two steps
+            if not engine.has_work():
+                break
+            await asyncio.sleep(0.01)
+        await client.close()
+        return seen
+
+    seen = asyncio.run(read_three())
+    assert len(seen) == 3 and not engine.has_work() and engine.blocks.num_free == free
