@@ -6,6 +6,8 @@ these routes mounted, the native engine answers the same calls, so that client (
 repository's :class:`~daser_b200.service.vllm_client.VLLMClient`) can point at it unchanged:
 
 * ``POST /v1/completions``  ``{"model", "prompt": [token ids] | "text", "max_tokens", ...}``
+* ``POST /v1/chat/completions``  ``{"model", "messages": [{"role", "content"}], "max_tokens", ...}`` (the
+  tokenizer's chat template when it has one)
 * ``GET  /v1/models``, ``GET /health``
 
 A request with ``max_tokens == 1`` is what the reference's service uses as "prefill this chunk so
@@ -53,6 +55,28 @@ class CompletionRequest(BaseModel):
     model_config = {"extra": "allow"}
 
 
+class ChatRequest(BaseModel):
+    model: Optional[str] = None
+    messages: list[dict[str, Any]]
+    max_tokens: int = 16
+    temperature: float = 0.0
+    seed: Optional[int] = None
+    stream: bool = False
+
+    model_config = {"extra": "allow"}
+
+
+def chat_prompt_tokens(tokenizer: Any, messages: list[dict[str, Any]]) -> list[int]:
+    """Token ids of a chat: the tokenizer's own template when it has one (``transformers``
+    tokenizers of chat models), else ``role: content`` lines and an open assistant line."""
+    if hasattr(tokenizer, "apply_chat_template") and getattr(tokenizer, "chat_template", None):
+        out = tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=True)
+        ids = out["input_ids"] if isinstance(out, dict) else out
+        return [int(t) for t in ids]
+    text = "".join(f"{m.get('role', 'user')}: {m.get('content', '')}\n" for m in messages) + "assistant:"
+    return list(tokenizer(text, add_special_tokens=False)["input_ids"])
+
+
 def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_tokens: int,
                   aligned_only: bool = False) -> list[list[int]]:
     """Cut ``tokens`` into segments at the stored chunks found in it.
@@ -77,28 +101,37 @@ def split_at_hits(tokens: Sequence[int], hits: Sequence[dict[str, Any]], block_t
     return segments
 
 
-def _gen_params(req: CompletionRequest) -> dict[str, Any]:
+def _gen_params(req: Any) -> dict[str, Any]:
     params: dict[str, Any] = {"max_tokens": req.max_tokens, "temperature": req.temperature}
     if req.seed is not None:
         params["seed"] = req.seed
     return params
 
 
-async def _sse(engine_client: Any, req: CompletionRequest, tokens: list[int], segments: list[list[int]],
-               model_name: str, t0: float):
+def _choice(chat: bool, text: str, token_ids: Any, finish: Optional[str], delta: bool) -> dict[str, Any]:
+    """One ``choices`` entry in the completions or the chat shape (``delta`` in stream events)."""
+    if not chat:
+        return {"index": 0, "text": text, "token_ids": token_ids, "logprobs": None, "finish_reason": finish}
+    body = {"role": "assistant", "content": text}
+    return {"index": 0, ("delta" if delta else "message"): body, "token_ids": token_ids, "logprobs": None,
+            "finish_reason": finish}
+
+
+async def _sse(engine_client: Any, req: Any, tokens: list[int], segments: list[list[int]],
+               model_name: str, t0: float, chat: bool = False):
     """Server-sent events in vLLM's shape: one ``text_completion`` object per token, a last one with
     ``finish_reason`` and ``usage``, then ``data: [DONE]``.  The first event is the time to first
     token as an HTTP client sees it (recorded as ``service.stream_ttft_ms``)."""
-    rid = "cmpl-" + uuid.uuid4().hex
-    base = {"id": rid, "object": "text_completion", "created": int(t0), "model": req.model or model_name}
+    rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex
+    base = {"id": rid, "object": "chat.completion.chunk" if chat else "text_completion", "created": int(t0),
+            "model": req.model or model_name}
     first = True
     try:
         async for item in engine_client.completion_stream(tokens, _gen_params(req), segments=segments):
             if item.get("done"):
                 usage = item["usage"]
                 n_out = int(usage.get("completion_tokens", 0))
-                last = dict(base, choices=[{"index": 0, "text": "", "token_ids": [], "logprobs": None,
-                                            "finish_reason": "length"}],
+                last = dict(base, choices=[_choice(chat, "", [], "length", True)],
                             usage={"prompt_tokens": len(tokens), "completion_tokens": n_out,
                                    "total_tokens": len(tokens) + n_out})
                 yield f"data: {json.dumps(last)}\n\n"
@@ -106,8 +139,7 @@ async def _sse(engine_client: Any, req: CompletionRequest, tokens: list[int], se
             if first:
                 metrics.observe("service.stream_ttft_ms", (time.time() - t0) * 1e3)
                 first = False
-            event = dict(base, choices=[{"index": 0, "text": item["text"], "token_ids": item["token_ids"],
-                                         "logprobs": None, "finish_reason": None}])
+            event = dict(base, choices=[_choice(chat, item["text"], item["token_ids"], None, True)])
             yield f"data: {json.dumps(event)}\n\n"
     except Exception as exc:  # the status line has gone out already: report in-band, as vLLM does
         logger.warning("[SERVICE] streamed completion failed: %s", exc)
@@ -135,6 +167,15 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             tokens = [int(t) for t in prompt[0]]
         else:
             raise HTTPException(400, "prompt must be a string or a list of token ids")
+        return await serve(req, tokens, chat=False)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(req: ChatRequest) -> Any:
+        if not req.messages:
+            raise HTTPException(400, "messages must not be empty")
+        return await serve(req, chat_prompt_tokens(tokenizer, req.messages), chat=True)
+
+    async def serve(req: Any, tokens: list[int], chat: bool) -> Any:
         if not tokens:
             raise HTTPException(400, "empty prompt")
         if req.max_tokens < 1:
@@ -151,7 +192,7 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
         if req.stream:
             if not hasattr(engine_client, "completion_stream"):
                 raise HTTPException(400, "streaming is not supported by this engine client")
-            return StreamingResponse(_sse(engine_client, req, tokens, segments, model_name, t0),
+            return StreamingResponse(_sse(engine_client, req, tokens, segments, model_name, t0, chat),
                                      media_type="text/event-stream")
         try:
             out = await engine_client.completion(tokens, _gen_params(req), segments=segments)
@@ -170,9 +211,9 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
         usage = out.get("usage", {})
         n_out = int(usage.get("completion_tokens", len(choice.get("token_ids", []))))
         return {
-            "id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": int(t0),
+            "id": ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex,
+            "object": "chat.completion" if chat else "text_completion", "created": int(t0),
             "model": req.model or model_name,
-            "choices": [{"index": 0, "text": choice.get("text", ""), "token_ids": choice.get("token_ids"),
-                         "logprobs": None, "finish_reason": "length"}],
+            "choices": [_choice(chat, choice.get("text", ""), choice.get("token_ids"), "length", False)],
             "usage": {"prompt_tokens": len(tokens), "completion_tokens": n_out, "total_tokens": len(tokens) + n_out},
         }

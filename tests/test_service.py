@@ -310,3 +310,46 @@ def test_batching_engine_client_serves_concurrent_and_streamed_requests(tmp_path
         asyncio.run(client_obj.close())
         engine.close()
         lp.stop()
+
+
+def test_chat_completions_route(tmp_path):
+    import json
+
+    from daser_b200.engine.rag_cpu import CpuRagEngine
+    from daser_b200.kv.layout import KVGeometry
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.openai_api import chat_prompt_tokens, mount_openai_routes
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    mcfg = PRESETS["toy"]
+    geo = KVGeometry(mcfg.num_layers, mcfg.num_kv_heads, mcfg.head_dim, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    engine = CpuRagEngine(mcfg, lp.socket_path, lp.cfg.store_path, num_blocks=128)
+    tok = ByteTokenizer()
+    client_obj = NativeEngineClient(engine, tok.decode)
+    app = build_service_app(ServiceConfig("", "toy", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2),
+                            engine_client=client_obj, tokenizer=tok)
+    mount_openai_routes(app, client_obj, tok, lp.socket_path, "toy", "default", 16)
+    messages = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "why is the sky blue?"}]
+    try:
+        with TestClient(app) as client:
+            ids = chat_prompt_tokens(tok, messages)
+            assert tok.decode(ids) == "system: be brief\nuser: why is the sky blue?\nassistant:"
+            plain = client.post("/v1/completions", json={"prompt": ids, "max_tokens": 4}).json()
+            r = client.post("/v1/chat/completions", json={"model": "toy", "messages": messages, "max_tokens": 4})
+            assert r.status_code == 200, r.text
+            body = r.json()
+            assert body["object"] == "chat.completion" and body["id"].startswith("chatcmpl-")
+            msg = body["choices"][0]["message"]
+            assert msg["role"] == "assistant" and msg["content"] == plain["choices"][0]["text"]
+            assert body["usage"]["prompt_tokens"] == len(ids) and body["usage"]["completion_tokens"] == 4
+            with client.stream("POST", "/v1/chat/completions",
+                               json={"messages": messages, "max_tokens": 4, "stream": True}) as sr:
+                events = [json.loads(l[6:]) for l in sr.iter_lines() if l.startswith("data: {")]
+            assert all(e["object"] == "chat.completion.chunk" for e in events)
+            assert "".join(e["choices"][0]["delta"]["content"] for e in events) == msg["content"]
+            assert events[-1]["choices"][0]["finish_reason"] == "length"
+            assert client.post("/v1/chat/completions", json={"messages": [], "max_tokens": 1}).status_code == 400
+    finally:
+        engine.close()
+        lp.stop()
