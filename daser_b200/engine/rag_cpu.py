@@ -30,6 +30,7 @@ class GenerateResult:
     generated: list[int]
     context_len: int
     restored_chunks: int
+    finish_reason: str = "length"
 
 
 class BlockAllocator:
@@ -197,7 +198,7 @@ class CpuRagEngine:
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
                  store_misses: bool = False, on_token=None, temperature: float = 0.0,
-                 seed: int = 0) -> "GenerateResult":
+                 seed: int = 0, stop_token_ids: Sequence[int] = ()) -> "GenerateResult":
         """Serve one request to completion with greedy sampling: the same call the GPU engine
         offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
         for signature parity; chunks are only stored through :meth:`store_chunk` here.
@@ -206,7 +207,8 @@ class CpuRagEngine:
         if self.compose_after > 0:
             chunks = self._lead(lambda: self.sched.merge_composed(asked))
         req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens,
-                                     temperature=float(temperature), seed=int(seed)))
+                                     temperature=float(temperature), seed=int(seed),
+                                     stop_token_ids=tuple(int(t) for t in stop_token_ids)))
         sent = 0
         while not req.done:
             self.step()
@@ -220,7 +222,7 @@ class CpuRagEngine:
             combo = self._lead(lambda: self.sched.note_composition(asked, self.compose_after))
             if combo is not None:
                 self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
-        return GenerateResult(req.generated, req.context_len, req.restored_chunks)
+        return GenerateResult(req.generated, req.context_len, req.restored_chunks, req.finish_reason)
 
     # -- iteration-level scheduling: the calls GpuRagEngine offers, on the oracle model ----------
     def submit(self, req: RagRequest) -> RagRequest:
@@ -272,7 +274,7 @@ class CpuRagEngine:
                 logits = self._forward([req.generated[-1]], torch.tensor([pos]), torch.tensor(req.block_table), pos)
                 req.generated.append(self._sample(logits, req))
         for req in list(self.running):
-            if len(req.generated) >= req.max_new_tokens:
+            if req.finished():
                 req.done = True
                 self.running.remove(req)
                 self.blocks.free(req.block_table)

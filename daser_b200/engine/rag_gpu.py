@@ -289,7 +289,7 @@ class GpuRagEngine:
         metrics.observe("engine.ttft_ms", req.ttft_ms)
         if self.sched is not None:
             self.sched.request_finished(req.req_id)
-        if len(req.generated) >= req.max_new_tokens:
+        if req.finished():
             self._finish(req)
         else:
             self.running.append(req)
@@ -316,7 +316,7 @@ class GpuRagEngine:
         out = self.runner.forward(inp).tolist()
         for r, tok in zip(batch, out):
             r.generated.append(int(tok))
-            if len(r.generated) >= r.max_new_tokens:
+            if r.finished():
                 self._finish(r)
 
     def _finish(self, req: RagRequest) -> None:
@@ -326,7 +326,8 @@ class GpuRagEngine:
         self.blocks.free(req.block_table)
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
-                 store_misses: bool = False, on_token=None, temperature: float = 0.0, seed: int = 0) -> RagRequest:
+                 store_misses: bool = False, on_token=None, temperature: float = 0.0, seed: int = 0,
+                 stop_token_ids: Sequence[int] = ()) -> RagRequest:
         """Serve one request to completion (the call a user of the engine makes).
 
         ``on_token(token_id)`` is called after each engine step with every token the step added
@@ -337,7 +338,8 @@ class GpuRagEngine:
             # the rank that owns the scheduler half decides; every rank must serve the same list
             merged = self._bcast(self.sched.merge_composed(asked) if self.sched is not None else None)
         req = self.submit(RagRequest(merged, list(query), max_new_tokens, store_misses=store_misses,
-                                     temperature=float(temperature), seed=int(seed)))
+                                     temperature=float(temperature), seed=int(seed),
+                                     stop_token_ids=tuple(int(t) for t in stop_token_ids)))
         sent = 0
         while not req.done:
             self.step()

@@ -30,6 +30,20 @@ class RagRequest:
     # set (with done) when the engine gave the request up without touching the others: it can never
     # fit the KV pool or the runner's buffers
     error: Optional[str] = None
+    # generation also ends when one of these is sampled (end-of-sequence ids); the token stays in
+    # `generated`, as in vLLM's token_ids
+    stop_token_ids: tuple = ()
+    finish_reason: str = ""  # "length" | "stop", set when generation ends
+
+    def finished(self) -> bool:
+        """Has the token just appended ended the generation?  Records why."""
+        if self.generated and self.stop_token_ids and self.generated[-1] in self.stop_token_ids:
+            self.finish_reason = "stop"
+            return True
+        if len(self.generated) >= self.max_new_tokens:
+            self.finish_reason = "length"
+            return True
+        return False
 
     def blocks_needed(self, block_tokens: int) -> int:
         """KV blocks of the whole request, generation included (reserved up front, so that a running

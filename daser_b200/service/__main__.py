@@ -126,6 +126,25 @@ def _model_weights(args: argparse.Namespace, device, dtype, tp: int = 1, rank: i
                            block_tokens=args.block_tokens)
 
 
+def _eos_ids(args: argparse.Namespace) -> tuple:
+    """End-of-sequence ids of a checkpoint (``generation_config.json``, else ``config.json``); none for
+    the presets with random weights, whose generations run to ``max_tokens``."""
+    if not getattr(args, "native_checkpoint", None):
+        return ()
+    import json
+
+    ids: list[int] = []
+    for name in ("generation_config.json", "config.json"):
+        path = os.path.join(args.native_checkpoint, name)
+        if os.path.exists(path):
+            with open(path) as f:
+                eos = json.load(f).get("eos_token_id")
+            if eos is not None:
+                ids = [int(t) for t in (eos if isinstance(eos, list) else [eos])]
+                break
+    return tuple(ids)
+
+
 def _run_follower(args: argparse.Namespace) -> None:
     """Ranks above 0: build the same engine shard and replay the leader's calls until told to stop."""
     import torch
@@ -169,7 +188,7 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
         engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
                               weights=_model_weights(args, "cpu", torch.float32))
     return NativeEngineClient(engine, tokenizer.decode, model=args.native_model,
-                              batching=bool(getattr(args, "native_batching", False))), engine
+                              batching=bool(getattr(args, "native_batching", False)), eos_token_ids=_eos_ids(args)), engine
 
 
 async def _run(args: argparse.Namespace) -> None:

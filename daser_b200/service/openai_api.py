@@ -105,6 +105,10 @@ def _gen_params(req: Any) -> dict[str, Any]:
     params: dict[str, Any] = {"max_tokens": req.max_tokens, "temperature": req.temperature}
     if req.seed is not None:
         params["seed"] = req.seed
+    extra = getattr(req, "model_extra", None) or {}  # vLLM's extensions, passed as plain fields
+    for name in ("stop_token_ids", "ignore_eos"):
+        if extra.get(name) is not None:
+            params[name] = extra[name]
     return params
 
 
@@ -131,7 +135,7 @@ async def _sse(engine_client: Any, req: Any, tokens: list[int], segments: list[l
             if item.get("done"):
                 usage = item["usage"]
                 n_out = int(usage.get("completion_tokens", 0))
-                last = dict(base, choices=[_choice(chat, "", [], "length", True)],
+                last = dict(base, choices=[_choice(chat, "", [], item.get("finish_reason", "length"), True)],
                             usage={"prompt_tokens": len(tokens), "completion_tokens": n_out,
                                    "total_tokens": len(tokens) + n_out})
                 yield f"data: {json.dumps(last)}\n\n"
@@ -214,6 +218,7 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             "id": ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex,
             "object": "chat.completion" if chat else "text_completion", "created": int(t0),
             "model": req.model or model_name,
-            "choices": [_choice(chat, choice.get("text", ""), choice.get("token_ids"), "length", False)],
+            "choices": [_choice(chat, choice.get("text", ""), choice.get("token_ids"),
+                                choice.get("finish_reason", "length"), False)],
             "usage": {"prompt_tokens": len(tokens), "completion_tokens": n_out, "total_tokens": len(tokens) + n_out},
         }

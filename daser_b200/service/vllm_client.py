@@ -107,8 +107,9 @@ class NativeEngineClient:
     """
 
     def __init__(self, engine: Any, detokenize, model: str = "native", pad_token: int = 0,
-                 batching: bool = False) -> None:
+                 batching: bool = False, eos_token_ids: Sequence[int] = ()) -> None:
         self._engine = engine
+        self.eos_token_ids = tuple(int(t) for t in eos_token_ids)  # generation stops at these
         self._detok = detokenize
         self._model = model
         self._pad = pad_token
@@ -159,16 +160,22 @@ class NativeEngineClient:
         t = list(tokens)
         return t + [self._pad] * (-len(t) % bt)
 
-    @staticmethod
-    def _sampling(params: dict[str, Any]) -> dict[str, Any]:
-        """``temperature`` / ``seed`` of a request as the engines take them.  Greedy unless a positive
-        temperature is asked for; an unseeded sampling request gets a fresh seed here, once, so that
-        every tensor-parallel rank draws with the same one."""
+    def _sampling(self, params: dict[str, Any]) -> dict[str, Any]:
+        """Sampling and stopping fields of a request as the engines take them.  Greedy unless a
+        positive temperature is asked for; an unseeded sampling request gets a fresh seed here, once,
+        so that every tensor-parallel rank draws with the same one.  Generation stops at the model's
+        end-of-sequence ids (unless ``ignore_eos``) and at the request's ``stop_token_ids``."""
+        out: dict[str, Any] = {}
+        stops = set(int(t) for t in (params.get("stop_token_ids") or []))
+        if not params.get("ignore_eos"):
+            stops.update(self.eos_token_ids)
+        if stops:
+            out["stop_token_ids"] = tuple(sorted(stops))
         t = float(params.get("temperature") or 0.0)
-        if t <= 0.0:
-            return {}
-        seed = params.get("seed")
-        return {"temperature": t, "seed": int(seed) if seed is not None else random.getrandbits(62)}
+        if t > 0.0:
+            seed = params.get("seed")
+            out.update(temperature=t, seed=int(seed) if seed is not None else random.getrandbits(62))
+        return out
 
     def _generate(self, segments, query, max_new, on_token=None, sampling=None):
         eng = self._engine
@@ -177,9 +184,9 @@ class NativeEngineClient:
             kw = {"on_token": on_token} if on_token is not None else {}
             kw.update(sampling or {})
             req = eng.generate(chunks, list(query), max_new_tokens=max_new, **kw)
-            return req.generated, req.context_len
+            return req.generated, req.context_len, getattr(req, "finish_reason", "") or "length"
         res = eng.run_request([], chunks, list(query))
-        return [int(res.logits[-1].argmax())], res.total_tokens
+        return [int(res.logits[-1].argmax())], res.total_tokens, "length"
 
     async def completion(self, tokens: list[int], gen_params: Optional[dict[str, Any]] = None,
                          segments: Optional[Sequence[Sequence[int]]] = None) -> dict[str, Any]:
@@ -195,13 +202,13 @@ class NativeEngineClient:
         if self._loop is not None:
             chunks = [self._pad_block(s) for s in cached if len(s)]
             req = await asyncio.wrap_future(self._loop.submit(chunks, query, max_new, **sampling))
-            gen, prompt_len = req.generated, req.context_len
+            gen, prompt_len, why = req.generated, req.context_len, req.finish_reason or "length"
         else:
             async with self._lock:
-                gen, prompt_len = await asyncio.get_running_loop().run_in_executor(
+                gen, prompt_len, why = await asyncio.get_running_loop().run_in_executor(
                     None, self._guard, self._generate, cached, query, max_new, None, sampling)
         return {
-            "choices": [{"text": self._detok(gen), "token_ids": gen}],
+            "choices": [{"text": self._detok(gen), "token_ids": gen, "finish_reason": why}],
             "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)},
         }
 
@@ -229,7 +236,7 @@ class NativeEngineClient:
 
                 async def stepped():
                     req = await asyncio.wrap_future(ticket)
-                    return req.generated, req.context_len
+                    return req.generated, req.context_len, req.finish_reason or "length"
 
                 fut = asyncio.ensure_future(stepped())
             else:
@@ -254,8 +261,9 @@ class NativeEngineClient:
                 if self._loop is not None and not fut.done():
                     self._loop.cancel(ticket)
                     fut.cancel()
-            gen, prompt_len = await fut  # raises here if the engine failed
+            gen, prompt_len, why = await fut  # raises here if the engine failed
             if len(sent) < len(gen):  # an engine without token callbacks: everything at the end
                 rest = gen[len(sent):]
                 yield {"token_ids": rest, "text": self._detok(gen)[len(text):]}
-        yield {"done": True, "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)}}
+        yield {"done": True, "finish_reason": why,
+               "usage": {"prompt_tokens": prompt_len, "completion_tokens": len(gen)}}

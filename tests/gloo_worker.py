@@ -210,7 +210,7 @@ def scenario_serve() -> int:
 
         def submit(self, req):
             self.calls.append(("submit", tuple(map(tuple, req.chunks)), tuple(req.query), req.max_new_tokens,
-                               req.store_misses, req.temperature, req.seed))
+                               req.store_misses, req.temperature, req.seed, tuple(req.stop_token_ids)))
             return req
 
         def has_work(self):
@@ -239,7 +239,8 @@ def scenario_serve() -> int:
         # the iteration-level calls an engine loop makes
         from daser_b200.engine.request import RagRequest
 
-        lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True, temperature=0.5, seed=42))
+        lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True, temperature=0.5, seed=42,
+                               stop_token_ids=(2,)))
         lead.step()
         lead.step()
         lead.abort("req-7")

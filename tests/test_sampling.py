@@ -68,3 +68,43 @@ def test_engine_and_http_sampling_are_reproducible_per_seed(tmp_path):
     finally:
         eng.close()
         lp.stop()
+
+
+def test_generation_stops_at_stop_tokens_and_reports_why(tmp_path):
+    from fastapi.testclient import TestClient
+
+    from daser_b200.service.http_api import ByteTokenizer, ServiceConfig, build_service_app
+    from daser_b200.service.openai_api import mount_openai_routes
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, 16, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    eng = CpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=128)
+    try:
+        query = [3, 1, 4, 1, 5, 9, 2, 6]
+        full = eng.generate([], query, max_new_tokens=10)
+        assert full.finish_reason == "length" and len(full.generated) == 10
+        stop = full.generated[4]
+        first = full.generated.index(stop)
+        cut = eng.generate([], query, max_new_tokens=10, stop_token_ids=[stop])
+        assert cut.finish_reason == "stop" and cut.generated == full.generated[: first + 1]
+        assert eng.blocks.num_free == 128
+        tok = ByteTokenizer()
+        client_obj = NativeEngineClient(eng, tok.decode, eos_token_ids=[stop])      # the "model's" end-of-sequence id
+        app = build_service_app(ServiceConfig("", "toy", "byte", lp.socket_path, block_tokens=16, chunk_blocks=2),
+                                engine_client=client_obj, tokenizer=tok)
+        mount_openai_routes(app, client_obj, tok, lp.socket_path, "toy", "default", 16)
+        with TestClient(app) as client:
+            body = client.post("/v1/completions", json={"prompt": query, "max_tokens": 10}).json()
+            assert body["choices"][0]["finish_reason"] == "stop"
+            assert body["choices"][0]["token_ids"] == cut.generated and body["usage"]["completion_tokens"] == first + 1
+            body = client.post("/v1/completions", json={"prompt": query, "max_tokens": 10, "ignore_eos": True}).json()
+            assert body["choices"][0]["finish_reason"] == "length" and body["choices"][0]["token_ids"] == full.generated
+            other = full.generated[1]
+            body = client.post("/v1/completions", json={"prompt": query, "max_tokens": 10, "ignore_eos": True,
+                                                        "stop_token_ids": [other]}).json()
+            assert body["choices"][0]["token_ids"] == full.generated[: full.generated.index(other) + 1]
+    finally:
+        eng.close()
+        lp.stop()
