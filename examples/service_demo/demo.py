@@ -1,4 +1,5 @@
-"""Walk through the service API: health, upload two documents, list, get, infer, delete, list.
+"""Walk through the service API: health, upload two documents, list, get, infer, a streamed chat
+completion (in-process engine only), delete, list.
 
     python -m daser_b200.service --engine native --tokenizer byte --store-path /tmp/d.store \
         --index-path /tmp/d.index --port 8080 &
@@ -42,6 +43,15 @@ def main() -> None:
         out = http.post("/infer", json={"doc_ids": [a["doc_id"], b["doc_id"]], "task": "Summarise both notes.",
                                         "gen_params": {"max_tokens": 16, "temperature": 0.0}}).json()
         show("POST /infer", out)
+        if http.get("/v1/models").status_code == 200:  # the in-process engine also speaks vLLM's API
+            print("--- POST /v1/chat/completions (stream): one event per token")
+            body = {"messages": [{"role": "user", "content": "Which memory holds the accumulators?"}],
+                    "max_tokens": 8, "temperature": 0.8, "seed": 7, "stream": True}
+            with http.stream("POST", "/v1/chat/completions", json=body) as resp:
+                for line in resp.iter_lines():
+                    if line.startswith("data: {"):
+                        choice = json.loads(line[6:])["choices"][0]
+                        print(f"    {choice['delta']['content']!r} finish={choice['finish_reason']}")
         show(f"DELETE /documents/{a['doc_id']}", http.delete(f"/documents/{a['doc_id']}").json())
         show("GET /documents", http.get("/documents").json())
         print("--- GET /metrics (first lines)")
