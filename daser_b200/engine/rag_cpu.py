@@ -20,6 +20,7 @@ import torch
 
 from daser_b200.connector.core import ConnectorMeta, SchedulerHalf, TorchKVBackend, WorkerHalf
 from daser_b200.engine.request import RagRequest
+from daser_b200.engine.scheduling import REJECT, START, SchedulingMixin
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.layout import KVGeometry
 from daser_b200.models.llama import LlamaConfig, LlamaWeights, TorchPagedKV, reference_forward
@@ -62,7 +63,7 @@ class RequestResult:
     total_tokens: int
 
 
-class CpuRagEngine:
+class CpuRagEngine(SchedulingMixin):
     # defaults of the optional behaviours, also for subclasses that build themselves differently
     compose_after = 0
     repair_tokens = 0
@@ -230,37 +231,14 @@ class CpuRagEngine:
         self.waiting.append(req)
         return req
 
-    def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
-
-    def abort(self, req_id: str) -> bool:
-        """Drop a waiting or running request between two steps (a client that went away); its blocks
-        go back to the pool.  False when the request is unknown or already finished."""
-        for queue in (self.waiting, self.running):
-            for req in queue:
-                if req.req_id == req_id:
-                    queue.remove(req)
-                    if req.block_table:
-                        self.blocks.free(req.block_table)
-                    req.error, req.done = "aborted", True
-                    return True
-        return False
-
     def step(self) -> None:
         """One engine iteration: the prefill of the oldest waiting request (restore, compute
         what is missing, first token), else one more token for every running request."""
         bt = self.cfg.block_tokens
-        if self.waiting:
-            # admission as in the GPU engine: all blocks of the request up front, or wait for the
-            # running requests to finish, or (idle engine, still too large) give this one up alone
-            req = self.waiting[0]
-            need = req.blocks_needed(bt)
-            if need > self.blocks.num_free and not self.running:
-                self.waiting.pop(0)
-                req.error = f"{need} KV blocks needed, the pool has {self.blocks.num_free} free of {self.blocks.num_blocks}"
-                req.done = True
-                return
-        if self.waiting and self.waiting[0].blocks_needed(bt) <= self.blocks.num_free:
+        verdict = self._admission() if self.waiting else None
+        if verdict == REJECT:
+            return
+        if verdict == START:
             req = self.waiting.pop(0)
             res = self.run_request([], req.chunks, req.query, keep_blocks=True)
             req.block_table, req.context_len = list(res.block_table), res.total_tokens

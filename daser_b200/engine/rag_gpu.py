@@ -26,6 +26,7 @@ from daser_b200 import metrics
 from daser_b200.connector.core import ConnectorMeta, CudaKVBackend, SchedulerHalf, WorkerHalf
 from daser_b200.engine.rag_cpu import BlockAllocator
 from daser_b200.engine.request import RagRequest
+from daser_b200.engine.scheduling import REJECT, START, SchedulingMixin
 from daser_b200.engine.runner import GpuModelRunner
 from daser_b200.hashing import hash_tokens
 from daser_b200.kv.hbm_store import HBMStore
@@ -34,7 +35,7 @@ from daser_b200.ops import gemm as gemm_ops
 from daser_b200.utils import trace
 
 
-class GpuRagEngine:
+class GpuRagEngine(SchedulingMixin):
     def __init__(self, cfg: LlamaConfig, socket_path: str, store_path: str, num_blocks: int = 4096,
                  max_tokens: int = 256, max_seqs: int = 64, hbm_slots: int = 0, host_slots: int = 0,
                  io_backend: str = "auto",
@@ -62,6 +63,7 @@ class GpuRagEngine:
         self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device,
                                      max_blocks=max_blocks, use_graphs=use_graphs)
         self.blocks = BlockAllocator(num_blocks)
+        self.max_blocks_per_seq = max_blocks  # the runner's block tables are this wide
         self.geo = self.runner.geo
         # the restore kernel of the IO owner scatters into every rank's pool
         pool = tp_ctx.global_pool(self.runner) if tp_ctx is not None else self.runner.local_pool
@@ -175,57 +177,18 @@ class GpuRagEngine:
         self.waiting.append(req)
         return req
 
-    def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
-
-    def abort(self, req_id: str) -> bool:
-        """Drop a waiting or running request between two steps (a client that went away); its blocks
-        go back to the pool.  False when the request is unknown or already finished."""
-        for queue in (self.waiting, self.running):
-            for req in queue:
-                if req.req_id == req_id:
-                    queue.remove(req)
-                    if req.block_table:
-                        self.blocks.free(req.block_table)
-                    req.error, req.done = "aborted", True
-                    metrics.inc("engine.requests_aborted")
-                    return True
-        return False
-
     def step(self) -> None:
         if self.tp_ctx is not None:
             self.tp_ctx.check_peers()  # host-side: a lost peer ends the step before any launch
-        if self.waiting and not self._admit():
+        verdict = self._admission() if self.waiting else None
+        if verdict == REJECT:
             return
-        if self.waiting:
+        if verdict == START:
             with trace.span("engine.ttft_step", "engine"):
                 self._ttft_step(self.waiting.pop(0))
-        elif self.running:
+        elif self.running:  # nothing waiting, or the head of the queue waits for blocks
             with trace.span("engine.decode_step", "engine", batch=len(self.running)):
                 self._decode_step()
-
-    def _admit(self) -> bool:
-        """May the oldest waiting request start now?  If the pool lacks the blocks, the running
-        requests get a decode step instead (they free theirs when they finish); a request that
-        cannot fit even an idle engine is given up alone (``error``), the others go on.  The answer
-        depends on queue and pool state only, which every tensor-parallel rank shares."""
-        req = self.waiting[0]
-        need = req.blocks_needed(self.cfg.block_tokens)
-        why = None
-        if need > self.runner.max_blocks:
-            why = f"{need} KV blocks exceed the runner's limit of {self.runner.max_blocks} per sequence"
-        elif need > self.blocks.num_free and not self.running:
-            why = f"{need} KV blocks needed, the pool has {self.blocks.num_free} free of {self.blocks.num_blocks}"
-        if why is not None:
-            self.waiting.pop(0)
-            req.error, req.done = why, True
-            metrics.inc("engine.requests_rejected")
-            return False
-        if need > self.blocks.num_free:
-            with trace.span("engine.decode_step", "engine", batch=len(self.running)):
-                self._decode_step()
-            return False
-        return True
 
     def _ttft_step(self, req: RagRequest) -> None:
         cfg, bt = self.cfg, self.cfg.block_tokens

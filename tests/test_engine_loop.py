@@ -193,3 +193,15 @@ def test_cancelled_requests_leave_the_engine_and_return_their_blocks(engine):
 
     seen = asyncio.run(read_three())
     assert len(seen) == 3 and not engine.has_work() and engine.blocks.num_free == free
+
+
+def test_per_sequence_block_limit_rejects_alone(engine):
+    """The CUDA engine's runner has block tables of a fixed width; the shared admission code turns a
+    request beyond it away (here with the limit set on the oracle engine)."""
+    engine.max_blocks_per_seq = 4
+    try:
+        with pytest.raises(MemoryError, match="per sequence"):
+            engine.generate([], list(range(1, 70)), max_new_tokens=10)     # 79 tokens: 5 blocks
+        assert len(engine.generate([], list(range(1, 40)), max_new_tokens=10).generated) == 10
+    finally:
+        engine.max_blocks_per_seq = None
