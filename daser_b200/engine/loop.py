@@ -150,6 +150,11 @@ class EngineLoop:
 
     def _run(self) -> None:
         try:
+            dev = getattr(self.engine, "device", None)
+            if dev is not None and getattr(dev, "type", "") == "cuda":
+                import torch
+
+                torch.cuda.set_device(dev)  # the current device is per thread; the engine was built elsewhere
             while True:
                 while self._take(block=False):  # everything that arrived since the last step
                     pass

@@ -54,6 +54,10 @@ class TPLeaderEngine:
     def cfg(self):
         return self._engine.cfg
 
+    @property
+    def device(self):
+        return getattr(self._engine, "device", None)
+
     def _announce(self, *cmd: Any) -> None:
         if self._stopped:
             raise RuntimeError("the tensor-parallel engine was shut down")
