@@ -141,6 +141,11 @@ class NativeEngineClient:
     def _guard(self, fn, *args):
         if self._failed is not None:
             raise RuntimeError(f"engine unavailable: {self._failed}")
+        dev = getattr(self._engine, "device", None)
+        if dev is not None and getattr(dev, "type", "") == "cuda":
+            import torch
+
+            torch.cuda.set_device(dev)  # worker threads start on device 0: use the engine's
         try:
             return fn(*args)
         except Exception as exc:
