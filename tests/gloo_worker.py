@@ -13,6 +13,8 @@ Scenarios, chosen by ``argv[1]``; RANK / WORLD_SIZE / MASTER_PORT come from the 
 ``serve``   the leader / follower layer that puts a tensor-parallel engine behind one HTTP front
             end: rank 0 announces every engine call, the other ranks replay it; all ranks must
             have executed the same calls with the same arguments, in the same order.
+``serve_loop`` the engine loop on the leader over a real engine on every rank (concurrent requests,
+            a cancellation, a chunk store between steps): followers must replay to the same tokens.
 ``pipeline`` every rank one pipeline stage of the oracle engine (layer ranges, per-stage store
             files, multi-part commits, activations over point-to-point sends); tokens and logits must
             equal those of a single process with all layers.
@@ -262,6 +264,66 @@ def scenario_serve() -> int:
     return 0 if good else 1
 
 
+def scenario_serve_loop() -> int:
+    """The engine loop on the leader over real (oracle) engines on every rank: requests arrive from
+    several threads, one is cancelled, a chunk is stored between steps.  Every follower must end up
+    having served the same requests to the same tokens, with all blocks returned."""
+    import random
+    from concurrent.futures import ThreadPoolExecutor
+
+    from daser_b200.engine.loop import EngineLoop
+    from daser_b200.engine.rag_cpu import CpuRagEngine
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.service.tp_serving import TPLeaderEngine, follower_loop
+
+    rank, world = _init()
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    tmp = _bcast(tempfile.mkdtemp(prefix="daser_loop_") if rank == 0 else None)
+    planes = [_start_plane(tmp, "cp", geo.slot_size)] if rank == 0 else []
+    dist.barrier()
+    # every rank is a whole replica here (the protocol under test does not care how a rank computes)
+    eng = CpuRagEngine(cfg, f"{tmp}/cp.sock", f"{tmp}/r{rank}.store", num_blocks=24, io_backend="posix")
+    served = []
+    real_submit = eng.submit
+    eng.submit = lambda req: served.append(req) or real_submit(req)
+    rng = random.Random(1)
+    prompts = [[rng.randrange(cfg.vocab_size) for _ in range(20 + 7 * i)] for i in range(5)]
+    if rank == 0:
+        loop = EngineLoop(TPLeaderEngine(eng, _bcast))
+        with ThreadPoolExecutor(5) as pool:
+            futs = list(pool.map(lambda p: loop.submit([], p, 12, temperature=0.9, seed=len(p)), prompts))
+        long_one = loop.submit([], prompts[0], 200)
+        loop.call("store_chunk", list(range(32))).result(60)
+        time.sleep(0.2)
+        loop.cancel(long_one)
+        done = [f.result(120) for f in futs]
+        try:
+            long_one.result(60)
+            cancelled = False
+        except RuntimeError:
+            cancelled = True
+        loop.close()
+        loop.engine.close()                                   # tells the followers to stop
+        ok = cancelled and all(len(r.generated) == 12 for r in done)
+    else:
+        follower_loop(eng, _bcast)
+        ok = True
+    mine = sorted((r.req_id, tuple(r.generated) if r.error is None else r.error) for r in served)
+    # the cancelled request stops at a step that is the same on every rank
+    ok = ok and eng.blocks.num_free == 24 and not eng.has_work()
+    logs = [None] * world
+    dist.all_gather_object(logs, (mine, bool(ok)))
+    good = all(o for _, o in logs) and all(m == logs[0][0] for m, _ in logs) and len(logs[0][0]) == 6
+    if rank == 0:
+        for plane, lp in planes:
+            asyncio.run_coroutine_threadsafe(plane.stop(save=False), lp).result(10)
+            lp.call_soon_threadsafe(lp.stop)
+        print("SERVE_LOOP_OK" if good else f"SERVE_LOOP_FAIL {logs}", flush=True)
+    dist.destroy_process_group()
+    return 0 if good else 1
+
+
 def scenario_late() -> int:
     t0 = time.time()
     try:
@@ -365,4 +427,4 @@ def scenario_pipeline() -> int:
 
 if __name__ == "__main__":
     sys.exit({"parts": scenario_parts, "health": scenario_health, "serve": scenario_serve,
-              "late": scenario_late, "pipeline": scenario_pipeline}[sys.argv[1]]())
+              "late": scenario_late, "pipeline": scenario_pipeline, "serve_loop": scenario_serve_loop}[sys.argv[1]]())

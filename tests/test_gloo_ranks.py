@@ -53,6 +53,12 @@ def test_followers_replay_the_leaders_engine_calls():
     assert "SERVE_OK" in outs[0][1]
 
 
+def test_engine_loop_on_the_leader_is_replayed_exactly_by_real_follower_engines():
+    outs = _launch("serve_loop", 3, timeout=180)
+    assert all(rc == 0 for rc, _ in outs), "\n".join(o[-2000:] for _, o in outs)
+    assert "SERVE_LOOP_OK" in outs[0][1]
+
+
 def test_pipeline_stages_match_a_single_process():
     for world in (2, 3):
         outs = _launch("pipeline", world, timeout=180)
