@@ -169,6 +169,18 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             tokens = list(prompt)
         elif isinstance(prompt, list) and len(prompt) == 1 and isinstance(prompt[0], list):
             tokens = [int(t) for t in prompt[0]]
+        elif isinstance(prompt, list) and len(prompt) > 1 and all(isinstance(p, (str, list)) for p in prompt):
+            # several prompts in one call (vLLM's batch form): served side by side, which the engine
+            # loop turns into shared steps; one choice per prompt, in order
+            if req.stream:
+                raise HTTPException(400, "streaming takes one prompt per request")
+            import asyncio
+
+            singles = [req.model_copy(update={"prompt": p if isinstance(p, str) else [int(t) for t in p]})
+                       for p in prompt]
+            parts = await asyncio.gather(*(completions(r) for r in singles))
+            usage = {k: sum(p["usage"][k] for p in parts) for k in ("prompt_tokens", "completion_tokens", "total_tokens")}
+            return dict(parts[0], choices=[dict(p["choices"][0], index=i) for i, p in enumerate(parts)], usage=usage)
         else:
             raise HTTPException(400, "prompt must be a string or a list of token ids")
         return await serve(req, tokens, chat=False)

@@ -300,6 +300,13 @@ def test_batching_engine_client_serves_concurrent_and_streamed_requests(tmp_path
             alone = [post(p) for p in prompts]
             assert [r["choices"][0]["token_ids"] for r in together] == [r["choices"][0]["token_ids"] for r in alone]
             assert client_obj._loop.max_batch > 1
+            # several prompts in one call: one choice per prompt, in order, usage summed
+            many = client.post("/v1/completions", json={"prompt": prompts[:3], "max_tokens": 6}).json()
+            assert [c["index"] for c in many["choices"]] == [0, 1, 2]
+            assert [c["token_ids"] for c in many["choices"]] == [r["choices"][0]["token_ids"] for r in alone[:3]]
+            assert many["usage"]["completion_tokens"] == 18
+            assert many["usage"]["prompt_tokens"] == sum(len(p) for p in prompts[:3])
+            assert client.post("/v1/completions", json={"prompt": prompts[:2], "stream": True}).status_code == 400
             with client.stream("POST", "/v1/completions", json={"prompt": prompts[0], "max_tokens": 6, "stream": True}) as sr:
                 events = [json.loads(l[6:]) for l in sr.iter_lines() if l.startswith("data: {")]
             assert [t for e in events for t in e["choices"][0]["token_ids"]] == alone[0]["choices"][0]["token_ids"]
