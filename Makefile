@@ -16,7 +16,7 @@ bench: build      ## headline benchmark on one GPU
 	$(PY) bench.py
 
 bench-cpu: build  ## benchmarks that need no GPU
-	cd benchmarks && $(PY) bench_control_plane.py && $(PY) bench_storage.py --device cpu
+	cd benchmarks && $(PY) bench_control_plane.py && $(PY) bench_storage.py --device cpu && $(PY) bench_frontend.py
 
 clean:
 	rm -rf build daser_b200/ops/libdaser_ops.so daser_b200/io/libdaser_io.so daser_b200/server/libdaser_index.so
