@@ -1,0 +1,148 @@
+"""The CUDA engine's host-side control flow, run without a GPU.
+
+``GpuRagEngine`` is Python around a model runner and a KV backend.  Here the runner is replaced by a
+recorder that "samples" a deterministic function of what it was asked to compute, the KV backend by
+the PyTorch one on a host pool, and the CUDA events by stubs; scheduler half, worker half, block
+allocator, store file and control plane are the real ones.  What is checked is which work the
+engine asks for: what is restored and what is computed, where, with which sampling fields, and what
+happens to queues and blocks.  (Numerics of the real runner: ``tests/test_gpu_engine.py``.)"""
+
+import random
+
+import pytest
+import torch
+
+from conftest import LiveControlPlane
+from daser_b200.connector.core import SchedulerHalf, TorchKVBackend, WorkerHalf
+from daser_b200.engine.loop import EngineLoop
+from daser_b200.engine.rag_cpu import BlockAllocator
+from daser_b200.engine.rag_gpu import GpuRagEngine
+from daser_b200.engine.request import RagRequest
+from daser_b200.kv.layout import KVGeometry
+from daser_b200.models.llama import PRESETS, TorchPagedKV
+
+
+class _Event:
+    def record(self):
+        pass
+
+    def elapsed_time(self, other):
+        return 0.0
+
+
+class _Runner:
+    """Records every forward; the "sampled" token of a sequence is a hash of its last token and position."""
+
+    max_tokens, max_seqs, max_blocks = 64, 4, 32
+
+    def __init__(self):
+        self.calls = []
+
+    def stage_inputs(self, seqs):
+        return [dict(s, tokens=list(s["tokens"]), block_table=list(s["block_table"])) for s in seqs]
+
+    def forward(self, seqs):
+        self.calls.append(seqs)
+        return torch.tensor([(s["tokens"][-1] * 31 + s["start_pos"] + len(s["tokens"])) % 1000 for s in seqs])
+
+    def check_status(self):
+        pass
+
+
+@pytest.fixture
+def engine(tmp_path):
+    cfg = PRESETS["toy"]
+    geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
+    lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
+    eng = GpuRagEngine.__new__(GpuRagEngine)                 # not __init__: that needs a GPU
+    eng.cfg, eng.geo, eng.tp, eng.rank, eng.tp_ctx = cfg, geo, 1, 0, None
+    eng.compose_after = eng.repair_tokens = 0
+    eng.runner = _Runner()
+    eng.blocks = BlockAllocator(32)
+    eng.max_blocks_per_seq = eng.runner.max_blocks
+    pool = TorchPagedKV(cfg, 32)
+    eng.sched = SchedulerHalf(lp.socket_path, cfg.block_tokens, "default")
+    eng.worker = WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool.data, cfg.inv_freq()),
+                            io_backend="posix")
+    eng.hbm = eng.host = None
+    eng.waiting, eng.running, eng._n = [], [], 0
+    eng._ev = [_Event() for _ in range(4)]
+    yield eng
+    eng.worker.shutdown()
+    eng.sched.close()
+    lp.stop()
+
+
+def _computed(calls):
+    """(start_pos, number of tokens) of every sequence of every forward, in order."""
+    return [(s["start_pos"], len(s["tokens"])) for seqs in calls for s in seqs]
+
+
+def test_restore_compute_repair_and_sampling_fields(engine):
+    rng = random.Random(0)
+    a, b = ([rng.randrange(1000) for _ in range(32)] for _ in range(2))
+    engine.store_chunk(a)
+    assert _computed(engine.runner.calls) == [(0, 32)] and engine.blocks.num_free == 32
+    engine.runner.calls.clear()
+    seen = []
+    req = engine.generate([a, b], [5, 6, 7], max_new_tokens=3, temperature=0.7, seed=9, on_token=seen.append)
+    # chunk a restored (no forward), chunk b computed at its offset, then the query, then two decode steps
+    assert req.restored_chunks == 1 and _computed(engine.runner.calls) == [(32, 32), (64, 3), (67, 1), (68, 1)]
+    assert seen == req.generated and len(seen) == 3 and req.finish_reason == "length"
+    sampled = [s for seqs in engine.runner.calls[1:] for s in seqs]
+    assert all(s["temperature"] == 0.7 for s in sampled)
+    assert len({s["seed"] for s in sampled}) == 3            # a fresh seed per step, derived from the request's
+    assert "temperature" not in engine.runner.calls[0][0]    # computing a chunk samples nothing
+    assert engine.blocks.num_free == 32 and not engine.has_work()
+    # head repair: the restored chunk behind other context gets its first tokens recomputed in place
+    engine.store_chunk(b)
+    engine.runner.calls.clear()
+    engine.repair_tokens = 8
+    req = engine.generate([b, a], [1], max_new_tokens=1)
+    assert req.restored_chunks == 2 and _computed(engine.runner.calls) == [(32, 8), (64, 1)]
+    engine.repair_tokens = 0
+    # stop tokens end the request early and free its blocks
+    first = engine.generate([], [9, 9], max_new_tokens=4).generated
+    cut = engine.generate([], [9, 9], max_new_tokens=4, stop_token_ids=[first[1]])
+    assert cut.generated == first[:2] and cut.finish_reason == "stop" and engine.blocks.num_free == 32
+
+
+def test_composed_chunks_admission_abort_and_the_engine_loop(engine):
+    rng = random.Random(1)
+    a, b = ([rng.randrange(1000) for _ in range(16)] for _ in range(2))
+    engine.compose_after = 2
+    engine.generate([a, b], [3], max_new_tokens=1)
+    engine.generate([a, b], [3], max_new_tokens=1)            # second sighting: [a, b] stored as one chunk
+    engine.runner.calls.clear()
+    req = engine.generate([a, b], [3], max_new_tokens=1)
+    assert req.restored_chunks == 1 and _computed(engine.runner.calls) == [(32, 1)]
+    engine.compose_after = 0
+    # admission: 32 blocks of 16 tokens in the pool, 32 per sequence at most
+    with pytest.raises(MemoryError, match="per sequence"):
+        engine.generate([], [1] * 600, max_new_tokens=1)
+    engine.max_blocks_per_seq = 64
+    with pytest.raises(MemoryError, match="pool has 32 free"):
+        engine.generate([], [1] * 600, max_new_tokens=1)
+    assert engine.blocks.num_free == 32
+    # two requests that do not fit side by side: the second waits, is aborted while waiting
+    r1 = engine.submit(RagRequest([], [1] * 300, 4))
+    r2 = engine.submit(RagRequest([], [2] * 300, 4))
+    engine.step()
+    assert r1 in engine.running and r2 in engine.waiting
+    engine.step()                                              # r2 still lacks blocks: r1 decodes instead
+    assert len(r1.generated) == 2 and not r2.generated
+    assert engine.abort(r2.req_id) and r2.error == "aborted" and r2.done
+    while not r1.done:
+        engine.step()
+    assert engine.blocks.num_free == 32 and not engine.has_work()
+    # and under the engine loop: decode steps carry every running request together
+    engine.runner.calls.clear()
+    loop = EngineLoop(engine)
+    try:
+        futs = [loop.submit([], [i + 1] * 10, 6) for i in range(3)]
+        done = [f.result(30) for f in futs]
+    finally:
+        loop.close()
+    assert all(len(r.generated) == 6 for r in done)
+    assert max(len(seqs) for seqs in engine.runner.calls) == 3   # one forward for the three of them
+    assert engine.blocks.num_free == 32
