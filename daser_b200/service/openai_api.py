@@ -198,8 +198,12 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
             raise HTTPException(400, "max_tokens must be at least 1")  # as vLLM
         t0 = time.time()
         try:
-            reply = await ipc.call({"op": "lookup_chunks", "tokens": tokens, "model_id": model_id,
-                                    "any_offset": True})
+            # token ids as one packed int32 field (a control plane of this package takes them; a list
+            # of n msgpack integers costs several times as much on both ends)
+            from array import array
+
+            reply = await ipc.call({"op": "lookup_chunks", "tokens_bin": array("i", tokens).tobytes(),
+                                    "model_id": model_id, "any_offset": True})
             hits = reply.get("hits", [])
         except RuntimeError as exc:  # the control plane is optional for correctness: compute everything
             logger.warning("[SERVICE] scan failed (%s): computing the whole prompt", exc)
