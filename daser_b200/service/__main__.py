@@ -53,6 +53,11 @@ def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
                    help="directory of a Hugging Face checkpoint (config.json + *.safetensors; Llama-3 and Qwen3 "
                         "families): architecture and weights of the native engine instead of --native-model "
                         "with random weights")
+    p.add_argument("--native-compose-after", type=int, default=0,
+                   help="store an ordered chunk combination whole after this many sightings and restore it as "
+                        "one exact chunk later (0 = off)")
+    p.add_argument("--native-repair-tokens", type=int, default=0,
+                   help="recompute the first N tokens of every chunk restored behind other context (0 = off)")
     p.add_argument("--native-batching", action="store_true",
                    help="one thread keeps the native engine stepping and concurrent requests share its steps "
                         "(continuous batching); without it requests are served one after the other")
@@ -126,6 +131,11 @@ def _model_weights(args: argparse.Namespace, device, dtype, tp: int = 1, rank: i
                            block_tokens=args.block_tokens)
 
 
+def _engine_options(args: argparse.Namespace) -> dict:
+    return {"compose_after": int(getattr(args, "native_compose_after", 0) or 0),
+            "repair_tokens": int(getattr(args, "native_repair_tokens", 0) or 0)}
+
+
 def _eos_ids(args: argparse.Namespace) -> tuple:
     """End-of-sequence ids of a checkpoint (``generation_config.json``, else ``config.json``); none for
     the presets with random weights, whose generations run to ``max_tokens``."""
@@ -158,7 +168,8 @@ def _run_follower(args: argparse.Namespace) -> None:
     tp_ctx.barrier()  # the leader's control plane is up
     engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
                           hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx,
-                          weights=_model_weights(args, "cuda", torch.bfloat16, tp_ctx.tp, tp_ctx.rank))
+                          weights=_model_weights(args, "cuda", torch.bfloat16, tp_ctx.tp, tp_ctx.rank),
+                          **_engine_options(args))
     steps = follower_loop(engine, tp_ctx.broadcast_object)
     logger.info("[SERVICE] follower rank %d leaves after %d engine calls", tp_ctx.rank, steps)
 
@@ -176,7 +187,7 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
         shard = (tp_ctx.tp, tp_ctx.rank) if tp_ctx is not None else (1, 0)
         engine = GpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
                               hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx,
-                              weights=_model_weights(args, "cuda", torch.bfloat16, *shard))
+                              weights=_model_weights(args, "cuda", torch.bfloat16, *shard), **_engine_options(args))
         if tp_ctx is not None:
             from daser_b200.service.tp_serving import TPLeaderEngine
 
@@ -186,7 +197,7 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
         from daser_b200.engine.rag_cpu import CpuRagEngine
 
         engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
-                              weights=_model_weights(args, "cpu", torch.float32))
+                              weights=_model_weights(args, "cpu", torch.float32), **_engine_options(args))
     return NativeEngineClient(engine, tokenizer.decode, model=args.native_model,
                               batching=bool(getattr(args, "native_batching", False)), eos_token_ids=_eos_ids(args)), engine
 
