@@ -204,9 +204,6 @@ class CpuRagEngine(SchedulingMixin):
         offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
         for signature parity; chunks are only stored through :meth:`store_chunk` here.
         ``on_token(token_id)`` is called as each token is sampled (streaming front ends)."""
-        asked = [list(c) for c in chunks]
-        if self.compose_after > 0:
-            chunks = self._lead(lambda: self.sched.merge_composed(asked))
         req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens,
                                      temperature=float(temperature), seed=int(seed),
                                      stop_token_ids=tuple(int(t) for t in stop_token_ids)))
@@ -219,17 +216,25 @@ class CpuRagEngine(SchedulingMixin):
                 sent = len(req.generated)
         if req.error is not None:
             raise MemoryError(req.error)
-        if self.compose_after > 0:
-            combo = self._lead(lambda: self.sched.note_composition(asked, self.compose_after))
-            if combo is not None:
-                self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
         return GenerateResult(req.generated, req.context_len, req.restored_chunks, req.finish_reason)
 
     # -- iteration-level scheduling: the calls GpuRagEngine offers, on the oracle model ----------
     def submit(self, req: RagRequest) -> RagRequest:
         req.req_id = req.req_id or self._next_id()
+        if self.compose_after > 0 and not req.asked:
+            req.asked = [list(c) for c in req.chunks]
+            req.chunks = self._lead(lambda: self.sched.merge_composed(req.asked))
         self.waiting.append(req)
         return req
+
+    def _after_finish(self, req: RagRequest) -> None:
+        """Between two steps, once a request has ended: a chunk combination seen often enough is
+        computed from scratch (its chunks attending to one another) and stored whole."""
+        room = sum(len(c) for c in req.asked) // self.cfg.block_tokens <= self.blocks.num_free
+        if self.compose_after > 0 and req.asked and req.error is None and room:  # (no room: next sighting)
+            combo = self._lead(lambda: self.sched.note_composition(req.asked, self.compose_after))
+            if combo is not None:
+                self.store_chunk(combo)
 
     def step(self) -> None:
         """One engine iteration: the prefill of the oldest waiting request (restore, compute
@@ -256,6 +261,7 @@ class CpuRagEngine(SchedulingMixin):
                 req.done = True
                 self.running.remove(req)
                 self.blocks.free(req.block_table)
+                self._after_finish(req)
 
     def recompute_chunk_alone(self, chunk: Sequence[int], offset: int) -> tuple[list[int], int]:
         """Run ``chunk`` alone at positions ``offset..``; returns its (fresh) blocks and length.

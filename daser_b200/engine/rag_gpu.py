@@ -174,6 +174,10 @@ class GpuRagEngine(SchedulingMixin):
     def submit(self, req: RagRequest) -> RagRequest:
         req.req_id = req.req_id or self._next_id()
         req.arrival = req.arrival or time.perf_counter()
+        if self.compose_after > 0 and not req.asked:
+            # the rank that owns the scheduler half decides; every rank must serve the same list
+            req.asked = [list(c) for c in req.chunks]
+            req.chunks = self._bcast(self.sched.merge_composed(req.asked) if self.sched is not None else None)
         self.waiting.append(req)
         return req
 
@@ -287,6 +291,14 @@ class GpuRagEngine(SchedulingMixin):
         if req in self.running:
             self.running.remove(req)
         self.blocks.free(req.block_table)
+        room = sum(len(c) for c in req.asked) // self.cfg.block_tokens <= self.blocks.num_free
+        if self.compose_after > 0 and req.asked and room:  # (no room for the prefill now: next sighting)
+            # a chunk combination seen often enough is computed from scratch (its chunks attending to
+            # one another) and stored whole, here between two steps
+            combo = self._bcast(self.sched.note_composition(req.asked, self.compose_after)
+                                if self.sched is not None else None)
+            if combo is not None:
+                self.store_chunk(combo)
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
                  store_misses: bool = False, on_token=None, temperature: float = 0.0, seed: int = 0,
@@ -295,12 +307,7 @@ class GpuRagEngine(SchedulingMixin):
 
         ``on_token(token_id)`` is called after each engine step with every token the step added
         (a streaming front end sends the first one on as soon as the prefill step has ended)."""
-        asked = [list(c) for c in chunks]
-        merged = asked
-        if self.compose_after > 0:
-            # the rank that owns the scheduler half decides; every rank must serve the same list
-            merged = self._bcast(self.sched.merge_composed(asked) if self.sched is not None else None)
-        req = self.submit(RagRequest(merged, list(query), max_new_tokens, store_misses=store_misses,
+        req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens, store_misses=store_misses,
                                      temperature=float(temperature), seed=int(seed),
                                      stop_token_ids=tuple(int(t) for t in stop_token_ids)))
         sent = 0
@@ -312,10 +319,6 @@ class GpuRagEngine(SchedulingMixin):
                 sent = len(req.generated)
         if req.error is not None:
             raise MemoryError(req.error)
-        if self.compose_after > 0:
-            combo = self._bcast(self.sched.note_composition(asked, self.compose_after) if self.sched is not None else None)
-            if combo is not None:
-                self.store_chunk(combo)  # computed from scratch, the chunks attending to one another
         return req
 
     def close(self) -> None:

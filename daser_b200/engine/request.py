@@ -34,6 +34,9 @@ class RagRequest:
     # `generated`, as in vLLM's token_ids
     stop_token_ids: tuple = ()
     finish_reason: str = ""  # "length" | "stop", set when generation ends
+    # the chunks as the caller gave them, when the engine replaced a stored combination of them by
+    # one chunk (composed-chunk reuse); empty otherwise
+    asked: list = field(default_factory=list)
 
     def finished(self) -> bool:
         """Has the token just appended ended the generation?  Records why."""

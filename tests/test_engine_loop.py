@@ -205,3 +205,22 @@ def test_per_sequence_block_limit_rejects_alone(engine):
         assert len(engine.generate([], list(range(1, 40)), max_new_tokens=10).generated) == 10
     finally:
         engine.max_blocks_per_seq = None
+
+
+def test_composed_chunks_also_work_through_the_engine_loop(engine):
+    from daser_b200 import metrics
+
+    engine.compose_after = 2
+    rng = random.Random(3)
+    a, b = ([rng.randrange(engine.cfg.vocab_size) for _ in range(32)] for _ in range(2))
+    loop = EngineLoop(engine)
+    try:
+        first = loop.submit([a, b], [1, 2, 3], 3).result(60)
+        loop.submit([a, b], [1, 2, 3], 3).result(60)              # second sighting: [a, b] gets stored
+        hits0 = metrics.snapshot().get("connector.composed_hits", 0)
+        third = loop.submit([a, b], [1, 2, 3], 3).result(60)
+    finally:
+        loop.close()
+        engine.compose_after = 0
+    assert metrics.snapshot().get("connector.composed_hits", 0) == hits0 + 1
+    assert third.restored_chunks == 1 and third.generated == first.generated and third.asked == [a, b]
