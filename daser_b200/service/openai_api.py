@@ -20,7 +20,8 @@ control plane (``lookup_chunks`` with tokens: every stored chunk that appears at
 offset), the prompt is cut at the hits, and the pieces go to the engine as segments: hits are
 restored (keys re-rotated to their new positions), the gaps and the tail are computed.  Sampling is
 greedy by default (``temperature`` 0); a positive ``temperature`` draws from the softmax, reproducibly
-when ``seed`` is given.  ``top_p`` / ``top_k`` and the other sampling fields are accepted and ignored.
+when ``seed`` is given.  ``top_p`` / ``top_k`` and penalties are accepted and ignored; ``n`` or
+``best_of`` above 1, ``logprobs`` and ``echo`` are refused (400) rather than silently dropped.
 
 ``"stream": true`` answers with server-sent events, one per sampled token (vLLM's shape), so a
 client sees the first token when the prefill step ends rather than when the request does.
@@ -192,6 +193,12 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
         return await serve(req, chat_prompt_tokens(tokenizer, req.messages), chat=True)
 
     async def serve(req: Any, tokens: list[int], chat: bool) -> Any:
+        extra = getattr(req, "model_extra", None) or {}
+        for name, limit in (("n", 1), ("best_of", 1)):
+            if extra.get(name) not in (None, limit):
+                raise HTTPException(400, f"{name} other than {limit} is not supported")
+        if extra.get("logprobs") or extra.get("top_logprobs") or extra.get("echo"):
+            raise HTTPException(400, "logprobs / echo are not supported")
         if not tokens:
             raise HTTPException(400, "empty prompt")
         if req.max_tokens < 1:
