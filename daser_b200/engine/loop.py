@@ -38,14 +38,23 @@ class _Tracked:
         self.req, self.future, self.on_token, self.sent = req, future, on_token, 0
 
 
+class QueueFull(RuntimeError):
+    """More requests in flight than the loop was told to take: the caller should come back later."""
+
+
 class EngineLoop:
-    def __init__(self, engine: Any, idle_wait_s: float = 0.05) -> None:
+    def __init__(self, engine: Any, idle_wait_s: float = 0.05, max_in_flight: int = 0) -> None:
         if not (hasattr(engine, "submit") and hasattr(engine, "step") and hasattr(engine, "has_work")):
             raise TypeError("the engine has no submit / step / has_work: it cannot be stepped by a loop")
         self.engine = engine
         self._idle_wait = idle_wait_s
         self._inbox: queue.Queue = queue.Queue()
         self._tracked: list[_Tracked] = []
+        # back-pressure: requests submitted and not yet finished (queued, waiting, running); above
+        # `max_in_flight` (0 = no limit) a submit fails at once instead of queueing without bound
+        self._max_in_flight = max_in_flight
+        self._in_flight = 0
+        self._count_lock = threading.Lock()
         self._stop = False
         self.failed: Optional[BaseException] = None
         self.steps = 0
@@ -60,9 +69,19 @@ class EngineLoop:
         if self._stop or self.failed is not None:
             fut.set_exception(RuntimeError(f"engine loop is not running: {self.failed or 'closed'}"))
             return fut
+        with self._count_lock:
+            if self._max_in_flight and self._in_flight >= self._max_in_flight:
+                fut.set_exception(QueueFull(f"{self._in_flight} requests in flight (limit {self._max_in_flight})"))
+                return fut
+            self._in_flight += 1
+        fut.add_done_callback(self._one_less)
         req = RagRequest([list(c) for c in chunks], list(query), int(max_new_tokens), **fields)
         self._inbox.put(("submit", _Tracked(req, fut, on_token)))
         return fut
+
+    def _one_less(self, _fut: Future) -> None:
+        with self._count_lock:
+            self._in_flight -= 1
 
     def cancel(self, fut: Future) -> None:
         """Stop working on the request behind ``fut`` (as returned by :meth:`submit`): it leaves the

@@ -49,6 +49,8 @@ def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
     p.add_argument("--model-id", default="default")
     p.add_argument("--native-model", default="toy")
     p.add_argument("--native-device", choices=("cpu", "cuda"), default="cpu")
+    p.add_argument("--native-max-in-flight", type=int, default=0,
+                   help="with --native-batching: answer 429 above this many unfinished requests (0 = no limit)")
     p.add_argument("--native-checkpoint", default=None,
                    help="directory of a Hugging Face checkpoint (config.json + *.safetensors; Llama-3 and Qwen3 "
                         "families): architecture and weights of the native engine instead of --native-model "
@@ -199,7 +201,8 @@ def _native_engine(args: argparse.Namespace, cfg: DaserConfig, tokenizer):
         engine = CpuRagEngine(mcfg, cfg.ipc_socket_path, cfg.store_path, model_id=cfg.model_id,
                               weights=_model_weights(args, "cpu", torch.float32), **_engine_options(args))
     return NativeEngineClient(engine, tokenizer.decode, model=args.native_model,
-                              batching=bool(getattr(args, "native_batching", False)), eos_token_ids=_eos_ids(args)), engine
+                              batching=bool(getattr(args, "native_batching", False)), eos_token_ids=_eos_ids(args),
+                              max_in_flight=int(getattr(args, "native_max_in_flight", 0) or 0)), engine
 
 
 async def _run(args: argparse.Namespace) -> None:

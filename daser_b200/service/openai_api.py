@@ -230,6 +230,10 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
                 metrics.inc("service.completion_stores")
         except MemoryError as exc:  # the request can never fit the KV pool: the caller's problem, as in vLLM
             raise HTTPException(400, f"request too large: {exc}") from exc
+        except RuntimeError as exc:
+            if type(exc).__name__ == "QueueFull":  # back-pressure of the engine loop
+                raise HTTPException(429, str(exc)) from exc
+            raise HTTPException(502, f"engine failed: {exc}") from exc
         except Exception as exc:
             raise HTTPException(502, f"engine failed: {exc}") from exc
         metrics.observe("service.completion_ms", (time.time() - t0) * 1e3)

@@ -107,7 +107,7 @@ class NativeEngineClient:
     """
 
     def __init__(self, engine: Any, detokenize, model: str = "native", pad_token: int = 0,
-                 batching: bool = False, eos_token_ids: Sequence[int] = ()) -> None:
+                 batching: bool = False, eos_token_ids: Sequence[int] = (), max_in_flight: int = 0) -> None:
         self._engine = engine
         self.eos_token_ids = tuple(int(t) for t in eos_token_ids)  # generation stops at these
         self._detok = detokenize
@@ -121,7 +121,7 @@ class NativeEngineClient:
         if batching:
             from daser_b200.engine.loop import EngineLoop
 
-            self._loop = EngineLoop(engine)
+            self._loop = EngineLoop(engine, max_in_flight=max_in_flight)
 
     @property
     def model(self) -> str:

@@ -224,3 +224,19 @@ def test_composed_chunks_also_work_through_the_engine_loop(engine):
         engine.compose_after = 0
     assert metrics.snapshot().get("connector.composed_hits", 0) == hits0 + 1
     assert third.restored_chunks == 1 and third.generated == first.generated and third.asked == [a, b]
+
+
+def test_back_pressure_refuses_at_once_above_the_limit(engine):
+    from daser_b200.engine.loop import QueueFull
+
+    loop = EngineLoop(engine, max_in_flight=2)
+    try:
+        a = loop.submit([], [1, 2, 3], 60)
+        b = loop.submit([], [4, 5, 6], 60)
+        c = loop.submit([], [7, 8, 9], 2)
+        with pytest.raises(QueueFull, match="limit 2"):
+            c.result(1)
+        a.result(60), b.result(60)
+        assert len(loop.submit([], [7, 8, 9], 2).result(60).generated) == 2      # room again
+    finally:
+        loop.close()
