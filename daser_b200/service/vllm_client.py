@@ -266,6 +266,13 @@ class NativeEngineClient:
                 if self._loop is not None and not fut.done():
                     self._loop.cancel(ticket)
                     fut.cancel()
+                elif not fut.done():
+                    # one request at a time: the worker thread still owns the engine, so the lock must
+                    # not be released before it is through (the tokens it still makes go nowhere)
+                    try:
+                        await asyncio.shield(fut)
+                    except BaseException:
+                        pass
             gen, prompt_len, why = await fut  # raises here if the engine failed
             if len(sent) < len(gen):  # an engine without token callbacks: everything at the end
                 rest = gen[len(sent):]

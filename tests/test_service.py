@@ -364,3 +364,47 @@ def test_chat_completions_route(tmp_path):
     finally:
         engine.close()
         lp.stop()
+
+
+def test_abandoned_stream_keeps_the_lock_until_the_engine_is_through(tmp_path):
+    """Without the engine loop one worker thread at a time owns the engine: a consumer that stops
+    reading must not let the next request in while that thread is still generating."""
+    import threading
+    import time
+
+    from daser_b200.service.vllm_client import NativeEngineClient
+
+    class SlowEngine:
+        class cfg:
+            block_tokens = 16
+
+        def __init__(self):
+            self.inside = 0
+            self.overlap = False
+
+        def generate(self, chunks, query, max_new_tokens=1, on_token=None, **kw):
+            self.inside += 1
+            self.overlap = self.overlap or self.inside > 1
+            out = []
+            for i in range(max_new_tokens):
+                time.sleep(0.01)
+                out.append(65 + i % 26)
+                if on_token:
+                    on_token(out[-1])
+            self.inside -= 1
+            return type("R", (), {"generated": out, "context_len": len(query), "finish_reason": "length"})()
+
+    eng = SlowEngine()
+    client = NativeEngineClient(eng, lambda ids: "".join(map(chr, ids)))
+
+    async def scenario():
+        agen = client.completion_stream([1, 2, 3], {"max_tokens": 30})
+        async for _ in agen:
+            break                                              # the consumer goes away after one token
+        closing = asyncio.ensure_future(agen.aclose())
+        nxt = await client.completion([4, 5], {"max_tokens": 3})   # must wait for the first to end
+        await closing
+        return nxt
+
+    out = asyncio.run(scenario())
+    assert out["choices"][0]["token_ids"] == [65, 66, 67] and not eng.overlap and threading.active_count() >= 1
