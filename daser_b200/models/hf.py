@@ -162,8 +162,15 @@ def load_checkpoint(path: str, tp: int = 1, rank: int = 0, dtype: torch.dtype = 
             raise KeyError(name)
         fname = where[name]
         if fname not in handles:
-            handles[fname] = safe_open(os.path.join(path, fname), framework="pt")
+            handles[fname] = safe_open(os.path.join(path, fname), framework="pt").__enter__()
         sl = handles[fname].get_slice(name)
         return sl[:] if rows is None else sl[rows.start : rows.stop]
 
-    return weights_from_state_dict(cfg, get, tp=tp, rank=rank, dtype=dtype, device=device)
+    try:
+        return weights_from_state_dict(cfg, get, tp=tp, rank=rank, dtype=dtype, device=device)
+    finally:
+        for handle in handles.values():  # the shards were opened lazily and stayed open for the slices
+            try:
+                handle.__exit__(None, None, None)
+            except Exception:
+                pass
