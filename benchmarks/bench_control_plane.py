@@ -100,6 +100,15 @@ def main():
         lat = _timed(plan, args.iters)
         emit({"bench": "control_plane", "what": "lookup_chunks RPC, 8 keys", "p50_us": percentile(lat, 50),
               "p99_us": percentile(lat, 99)})
+        scan = IPCClientSync(sock)
+        scan.negotiate()
+        for label, extra in (("block-aligned offsets", {}), ("every token offset", {"any_offset": True})):
+            msg = {"op": "lookup_chunks", **scan._tok(prompt), "model_id": "m", **extra}
+            lat = _timed(lambda: scan.call(msg), max(20, args.iters // 5))
+            emit({"bench": "control_plane", "what": f"lookup_chunks scan RPC, {args.prompt_tokens}-token prompt, "
+                  f"{label} (the completions route runs the second per request)", "p50_us": percentile(lat, 50),
+                  "p99_us": percentile(lat, 99)})
+        scan.close()
         native = IPCClientSync(sock)
         native.negotiate()
         has_native = getattr(native, "_fast", None) is not None
