@@ -144,3 +144,23 @@ def test_other_operations_and_bad_frames_on_the_native_socket(tmp_path):
         c.close()
     finally:
         lp.stop()
+
+
+def test_wide_requests_cover_the_longer_msgpack_forms(tmp_path):
+    """More than 15 keys (array16), keys longer than 31 bytes (str8) and than 255 (str16), slots
+    beyond 32 bits of file offset: the native encoder and decoder against msgpack's own."""
+    lp = LiveControlPlane(tmp_path, total_slots=64, slot_size=1 << 28).start()     # 256 MiB slots: offsets > 4 GiB
+    plain, fast = _pair(lp)
+    try:
+        keys = [f"key-{i:03d}-" + "x" * (10 + 9 * i) for i in range(40)]          # 17 .. 368 characters
+        for i, k in enumerate(keys[:30]):
+            plain.alloc_chunk(k, 16, "m")
+            plain.commit_chunk(k)
+        got = fast.lookup_chunks(keys, "m")
+        assert got == plain.lookup_chunks(keys, "m")
+        assert sum(g is not None for g in got) == 30 and got[29]["file_offset"] == 29 * (1 << 28) > 2**32
+        assert fast.lookup_chunks([], "m") == []
+    finally:
+        plain.close()
+        fast.close()
+        lp.stop()
