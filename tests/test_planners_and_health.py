@@ -85,3 +85,20 @@ def test_peer_monitor_single_rank_is_a_no_op():
     m.check()
     m.leave()
     m.close()
+
+
+def test_pipeline_partition_and_stage_geometry():
+    from daser_b200.models.llama import PRESETS
+    from daser_b200.parallel.pp import partition_layers, stage_geometry, stage_store_path
+
+    assert partition_layers(80, 8) == [range(10 * i, 10 * i + 10) for i in range(8)]
+    parts = partition_layers(36, 5)                          # Qwen3-8B over five stages: 8, 7, 7, 7, 7
+    assert [len(p) for p in parts] == [8, 7, 7, 7, 7] and parts[0].start == 0 and parts[-1].stop == 36
+    assert all(a.stop == b.start for a, b in zip(parts, parts[1:]))
+    for bad in (0, 37):
+        with pytest.raises(ValueError):
+            partition_layers(36, bad)
+    cfg = PRESETS["qwen3-8b"]
+    geo = stage_geometry(cfg, 5, dtype_bytes=2)
+    assert geo.num_layers == 8 and geo.slot_size == 8 * 2 * 16 * 8 * 128 * 2    # the widest stage sizes the slots
+    assert stage_store_path("/mnt/kv/daser.store", 2, 5) == "/mnt/kv/daser.store.pp2of5"
