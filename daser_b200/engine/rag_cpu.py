@@ -240,10 +240,10 @@ class CpuRagEngine(SchedulingMixin):
         """One engine iteration: the prefill of the oldest waiting request (restore, compute
         what is missing, first token), else one more token for every running request."""
         bt = self.cfg.block_tokens
-        verdict = self._admission() if self.waiting else None
-        if verdict == REJECT:
+        decision = self._admission() if self.waiting else None
+        if decision == REJECT:
             return
-        if verdict == START:
+        if decision == START:
             req = self.waiting.pop(0)
             res = self.run_request([], req.chunks, req.query, keep_blocks=True)
             req.block_table, req.context_len = list(res.block_table), res.total_tokens

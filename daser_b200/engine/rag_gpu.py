@@ -184,10 +184,10 @@ class GpuRagEngine(SchedulingMixin):
     def step(self) -> None:
         if self.tp_ctx is not None:
             self.tp_ctx.check_peers()  # host-side: a lost peer ends the step before any launch
-        verdict = self._admission() if self.waiting else None
-        if verdict == REJECT:
+        decision = self._admission() if self.waiting else None
+        if decision == REJECT:
             return
-        if verdict == START:
+        if decision == START:
             with trace.span("engine.ttft_step", "engine"):
                 self._ttft_step(self.waiting.pop(0))
         elif self.running:  # nothing waiting, or the head of the queue waits for blocks

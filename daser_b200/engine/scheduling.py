@@ -25,7 +25,7 @@ class SchedulingMixin:
         generation, reserved up front so that a running request is never starved) are free.
         ``wait``: they are not, but running requests will free theirs: decode instead.  ``reject``:
         it cannot fit even an idle engine, or exceeds the runner's blocks per sequence; it has been
-        taken off the queue and marked (``error``, ``done``), the others go on.  The verdict depends
+        taken off the queue and marked (``error``, ``done``), the others go on.  The decision depends
         on queue and pool state only, which every tensor-parallel rank shares."""
         req = self.waiting[0]
         need = req.blocks_needed(self.cfg.block_tokens)
