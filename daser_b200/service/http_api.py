@@ -25,6 +25,7 @@ from __future__ import annotations
 import asyncio
 import time
 import uuid
+from contextlib import asynccontextmanager
 from dataclasses import dataclass
 from typing import Any, Optional
 
@@ -88,7 +89,6 @@ def _tokenize(tokenizer, text: str) -> list[int]:
 
 
 def build_service_app(cfg: ServiceConfig, engine_client: Any = None, tokenizer: Any = None) -> FastAPI:
-    app = FastAPI(title="daser_b200 service", version="0.1.0")
     tok = tokenizer or load_tokenizer(cfg.tokenizer)
     chunker = Chunker(cfg.block_tokens, cfg.chunk_blocks)
     ipc = IPCClientAsync(cfg.socket_path)
@@ -98,10 +98,13 @@ def build_service_app(cfg: ServiceConfig, engine_client: Any = None, tokenizer: 
         engine_client = VLLMClient(cfg.vllm_base_url, cfg.model)
     engine = engine_client
 
-    @app.on_event("shutdown")
-    async def _shutdown() -> None:
+    @asynccontextmanager
+    async def lifespan(_app: FastAPI):
+        yield
         await engine.close()
         await ipc.close()
+
+    app = FastAPI(title="daser_b200 service", version="0.1.0", lifespan=lifespan)
 
     @app.get("/health")
     async def health() -> dict[str, Any]:
