@@ -1,6 +1,10 @@
 """Queue handling shared by the CUDA engine and the oracle engine: admission against the KV pool,
 and dropping a request between two steps.  (One implementation, so that the CPU tests of the oracle
-engine also cover what the CUDA engine does.)"""
+engine also cover what the CUDA engine does.)
+
+The reference has no scheduler of its own: requests are queued, admitted and preempted inside the
+remote vLLM (``vllm/v1/core/sched/scheduler.py``), which its service reaches over HTTP
+(``daser/service/vllm_client.py:62-126``)."""
 
 from __future__ import annotations
 
