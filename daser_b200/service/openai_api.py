@@ -21,7 +21,8 @@ offset), the prompt is cut at the hits, and the pieces go to the engine as segme
 restored (keys re-rotated to their new positions), the gaps and the tail are computed.  Sampling is
 greedy by default (``temperature`` 0); a positive ``temperature`` draws from the softmax, reproducibly
 when ``seed`` is given.  ``top_p`` / ``top_k`` and penalties are accepted and ignored; ``n`` or
-``best_of`` above 1, ``logprobs`` and ``echo`` are refused (400) rather than silently dropped.
+``best_of`` above 1, ``logprobs``, ``echo`` and ``stop`` strings are refused (400) rather than silently
+dropped (``stop_token_ids`` work).
 
 ``"stream": true`` answers with server-sent events, one per sampled token (vLLM's shape), so a
 client sees the first token when the prefill step ends rather than when the request does.
@@ -199,6 +200,8 @@ def mount_openai_routes(app: FastAPI, engine_client: Any, tokenizer: Any, socket
                 raise HTTPException(400, f"{name} other than {limit} is not supported")
         if extra.get("logprobs") or extra.get("top_logprobs") or extra.get("echo"):
             raise HTTPException(400, "logprobs / echo are not supported")
+        if extra.get("stop"):
+            raise HTTPException(400, "stop strings are not supported (stop_token_ids are)")
         if not tokens:
             raise HTTPException(400, "empty prompt")
         if req.max_tokens < 1:

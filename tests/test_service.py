@@ -357,7 +357,7 @@ def test_chat_completions_route(tmp_path):
             assert "".join(e["choices"][0]["delta"]["content"] for e in events) == msg["content"]
             assert events[-1]["choices"][0]["finish_reason"] == "length"
             assert client.post("/v1/chat/completions", json={"messages": [], "max_tokens": 1}).status_code == 400
-            for unsupported in ({"n": 2}, {"best_of": 3}, {"logprobs": 5}, {"echo": True}):
+            for unsupported in ({"n": 2}, {"best_of": 3}, {"logprobs": 5}, {"echo": True}, {"stop": ["\n\n"]}):
                 r = client.post("/v1/completions", json={"prompt": ids, "max_tokens": 1, **unsupported})
                 assert r.status_code == 400 and "not supported" in r.json()["detail"]
             assert client.post("/v1/completions", json={"prompt": ids, "max_tokens": 1, "n": 1, "top_p": 0.9}).status_code == 200
