@@ -110,6 +110,13 @@ class CpuRagEngine(SchedulingMixin):
         """Greedy, or (request with a temperature) a draw from softmax(logits / T) by the Gumbel-max
         rule, reproducible from the request's seed and the step."""
         row = logits[-1].float()
+        if req is not None and req.truncated():
+            from daser_b200.engine.sampling import apply_truncation
+
+            row = row.clone()[None]
+            apply_truncation(row, torch.tensor([1.0 / req.temperature]), torch.tensor([req.top_k]),
+                             torch.tensor([req.top_p]))
+            row = row[0]
         if req is not None and req.temperature > 0:
             gen = torch.Generator().manual_seed(req.step_seed())
             u = torch.rand(row.shape, generator=gen).clamp_(1e-9, 1.0 - 1e-9)
@@ -199,14 +206,15 @@ class CpuRagEngine(SchedulingMixin):
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
                  store_misses: bool = False, on_token=None, temperature: float = 0.0,
-                 seed: int = 0, stop_token_ids: Sequence[int] = ()) -> "GenerateResult":
+                 seed: int = 0, stop_token_ids: Sequence[int] = (), top_k: int = 0,
+                 top_p: float = 1.0) -> "GenerateResult":
         """Serve one request to completion with greedy sampling: the same call the GPU engine
         offers (``GpuRagEngine.generate``), on the oracle model.  ``store_misses`` is accepted
         for signature parity; chunks are only stored through :meth:`store_chunk` here.
         ``on_token(token_id)`` is called as each token is sampled (streaming front ends)."""
         req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens,
-                                     temperature=float(temperature), seed=int(seed),
-                                     stop_token_ids=tuple(int(t) for t in stop_token_ids)))
+                                     temperature=float(temperature), seed=int(seed), top_k=int(top_k),
+                                     top_p=float(top_p), stop_token_ids=tuple(int(t) for t in stop_token_ids)))
         sent = 0
         while not req.done:
             self.step()

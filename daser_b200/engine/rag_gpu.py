@@ -238,7 +238,8 @@ class GpuRagEngine(SchedulingMixin):
                 if self.repair_tokens > 0 and off > 0:
                     self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table)
             ctx = off + len(c)
-        sample = {"temperature": req.temperature, "seed": req.step_seed()} if req.temperature > 0 else None
+        sample = ({"temperature": req.temperature, "seed": req.step_seed(), "top_k": req.top_k, "top_p": req.top_p}
+                  if req.temperature > 0 else None)
         first = self._prefill_tokens(req.query, ctx, req.block_table, sample)
         self._ev[3].record()
         token = int(first[0].item())  # device -> host read of the step's result
@@ -278,7 +279,8 @@ class GpuRagEngine(SchedulingMixin):
     def _decode_step(self) -> None:
         batch = self.running[: self.runner.max_seqs]
         seqs = [{"tokens": [r.generated[-1]], "start_pos": r.context_len + len(r.generated) - 1,
-                 "block_table": r.block_table, "temperature": r.temperature, "seed": r.step_seed()} for r in batch]
+                 "block_table": r.block_table, "temperature": r.temperature, "seed": r.step_seed(),
+                 "top_k": r.top_k, "top_p": r.top_p} for r in batch]
         inp = self.runner.stage_inputs(seqs)
         out = self.runner.forward(inp).tolist()
         for r, tok in zip(batch, out):
@@ -302,14 +304,14 @@ class GpuRagEngine(SchedulingMixin):
 
     def generate(self, chunks: Sequence[Sequence[int]], query: Sequence[int], max_new_tokens: int = 1,
                  store_misses: bool = False, on_token=None, temperature: float = 0.0, seed: int = 0,
-                 stop_token_ids: Sequence[int] = ()) -> RagRequest:
+                 stop_token_ids: Sequence[int] = (), top_k: int = 0, top_p: float = 1.0) -> RagRequest:
         """Serve one request to completion (the call a user of the engine makes).
 
         ``on_token(token_id)`` is called after each engine step with every token the step added
         (a streaming front end sends the first one on as soon as the prefill step has ended)."""
         req = self.submit(RagRequest([list(c) for c in chunks], list(query), max_new_tokens, store_misses=store_misses,
-                                     temperature=float(temperature), seed=int(seed),
-                                     stop_token_ids=tuple(int(t) for t in stop_token_ids)))
+                                     temperature=float(temperature), seed=int(seed), top_k=int(top_k),
+                                     top_p=float(top_p), stop_token_ids=tuple(int(t) for t in stop_token_ids)))
         sent = 0
         while not req.done:
             self.step()

@@ -27,6 +27,8 @@ class RagRequest:
     # sampling: 0 = greedy; > 0 draws from softmax(logits / temperature), reproducibly from `seed`
     temperature: float = 0.0
     seed: int = 0
+    top_k: int = 0  # with a temperature: sample among the k largest logits only (0 = all)
+    top_p: float = 1.0  # ... and among the smallest set of them whose probability reaches p (1 = all)
     # set (with done) when the engine gave the request up without touching the others: it can never
     # fit the KV pool or the runner's buffers
     error: Optional[str] = None
@@ -37,6 +39,9 @@ class RagRequest:
     # the chunks as the caller gave them, when the engine replaced a stored combination of them by
     # one chunk (composed-chunk reuse); empty otherwise
     asked: list = field(default_factory=list)
+
+    def truncated(self) -> bool:
+        return self.temperature > 0 and (self.top_k > 0 or self.top_p < 1.0)
 
     def finished(self) -> bool:
         """Has the token just appended ended the generation?  Records why."""

@@ -53,6 +53,8 @@ class StepInputs:
     # (inv_temp float32[num_seqs], seeds int64[num_seqs]) when a sequence of the step samples with a
     # temperature; None = every sequence is greedy
     sampling: Optional[tuple] = None
+    # (top_k int64[num_seqs], top_p float32[num_seqs]) when a sampling sequence also truncates
+    truncation: Optional[tuple] = None
 
 
 class GpuModelRunner:
@@ -199,7 +201,7 @@ class GpuModelRunner:
             self._in_event = torch.cuda.Event()
         self._in_event.record()
         self.h2d_bytes = t * 16 + ns * (self.max_blocks * 4 + 20) + 4
-        sampling = None
+        sampling = truncation = None
         if any(s.get("temperature", 0.0) > 0.0 for s in seqs):
             # sampling runs outside the captured layer loop, so these need no fixed buffers
             inv = torch.tensor([1.0 / s["temperature"] if s.get("temperature", 0.0) > 0.0 else 0.0 for s in seqs],
@@ -207,9 +209,14 @@ class GpuModelRunner:
             seeds = torch.tensor([int(s.get("seed", 0)) & 0x7FFFFFFFFFFFFFFF for s in seqs], dtype=torch.int64)
             sampling = (inv.to(self.device), seeds.to(self.device))
             self.h2d_bytes += ns * 12
+            if any(s.get("temperature", 0.0) > 0.0 and (s.get("top_k", 0) > 0 or s.get("top_p", 1.0) < 1.0)
+                   for s in seqs):
+                truncation = (torch.tensor([int(s.get("top_k", 0)) for s in seqs], dtype=torch.int64).to(self.device),
+                              torch.tensor([float(s.get("top_p", 1.0)) for s in seqs]).to(self.device))
+                self.h2d_bytes += ns * 12
         return StepInputs(d["tokens"][:t], d["positions"][:t], d["slot_mapping"][:t], d["block_tables"][:ns],
                           d["q_start"][: ns + 1], d["ctx_lens"][:ns], d["sample_rows"][:ns], t, ns, max_q, max_ctx,
-                          persistent=True, sampling=sampling)
+                          persistent=True, sampling=sampling, truncation=truncation)
 
     # -- one step -----------------------------------------------------------------------------------
     @torch.no_grad()
@@ -281,6 +288,10 @@ class GpuModelRunner:
         n = inp.num_seqs
         torch.index_select(normed, 0, inp.sample_rows[:n], out=self.last_rows[:n])
         gemm.linear(self.last_rows[:n], self.w.lm_head, acc=self.logits_acc[:n], status=self.status)
+        if inp.truncation is not None:  # top-k / top-p: a value threshold per row, then sample as usual
+            from daser_b200.engine.sampling import apply_truncation
+
+            apply_truncation(self.logits_acc[:n], inp.sampling[0], *inp.truncation)
         ew.argmax(self.logits_acc[:n], self.best_val[:n], self.best_idx[:n],
                   index_offset=self.rank * self.w.vocab_local, zero_after=True, sampling=inp.sampling)
         return self.best_idx[:n]

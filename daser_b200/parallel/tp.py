@@ -461,6 +461,16 @@ class TPContext:
                       base_ptr=self.epochs.data_ptr() + 4)
         torch.index_select(self.gathered, 0, inp.sample_rows[:n], out=runner.last_rows[:n])
         gemm.linear(runner.last_rows[:n], runner.w.lm_head, acc=runner.logits_acc[:n], status=runner.status)
+        if inp.truncation is not None:
+            # top-k / top-p: the threshold needs whole rows (gathered here, for the requests that ask
+            # for it only); every rank then masks its own shard, and sampling goes on as below
+            from daser_b200.engine.sampling import apply_truncation
+
+            local = runner.logits_acc[:n]
+            parts = torch.empty(self.tp, n, local.shape[1], dtype=local.dtype, device=self.device)
+            dist.all_gather_into_tensor(parts, local.contiguous(), group=self.group)
+            whole = parts.permute(1, 0, 2).reshape(n, -1)
+            apply_truncation(local, inp.sampling[0], *inp.truncation, whole_rows=whole)
         # (with a temperature the values are Gumbel-perturbed: their maximum over the ranks' shards
         # is the sample, the noise being a function of the seed and the global vocabulary index)
         ew.argmax(runner.logits_acc[:n], runner.best_val[:n], runner.best_idx[:n],

@@ -20,7 +20,8 @@ control plane (``lookup_chunks`` with tokens: every stored chunk that appears at
 offset), the prompt is cut at the hits, and the pieces go to the engine as segments: hits are
 restored (keys re-rotated to their new positions), the gaps and the tail are computed.  Sampling is
 greedy by default (``temperature`` 0); a positive ``temperature`` draws from the softmax, reproducibly
-when ``seed`` is given.  ``top_p`` / ``top_k`` and penalties are accepted and ignored; ``n`` or
+when ``seed`` is given, optionally truncated by ``top_k`` / ``top_p``.  Penalties are accepted and
+ignored; ``n`` or
 ``best_of`` above 1, ``logprobs``, ``echo`` and ``stop`` strings are refused (400) rather than silently
 dropped (``stop_token_ids`` work).
 
@@ -108,7 +109,7 @@ def _gen_params(req: Any) -> dict[str, Any]:
     if req.seed is not None:
         params["seed"] = req.seed
     extra = getattr(req, "model_extra", None) or {}  # vLLM's extensions, passed as plain fields
-    for name in ("stop_token_ids", "ignore_eos"):
+    for name in ("stop_token_ids", "ignore_eos", "top_k", "top_p"):
         if extra.get(name) is not None:
             params[name] = extra[name]
     return params

@@ -80,7 +80,8 @@ class TPLeaderEngine:
     # iteration-level calls (an engine loop drives these instead of `generate`)
     def submit(self, req: Any) -> Any:
         self._announce(CMD_SUBMIT, [list(c) for c in req.chunks], list(req.query), int(req.max_new_tokens),
-                       bool(req.store_misses), float(req.temperature), int(req.seed), tuple(req.stop_token_ids))
+                       bool(req.store_misses), float(req.temperature), int(req.seed), tuple(req.stop_token_ids),
+                       int(req.top_k), float(req.top_p))
         return self._engine.submit(req)
 
     def has_work(self) -> bool:
@@ -130,9 +131,9 @@ def follower_loop(engine: Any, broadcast: Broadcast, on_step: Optional[Callable[
         elif op == CMD_SUBMIT:
             from daser_b200.engine.request import RagRequest
 
-            _, chunks, query, max_new, store_misses, temperature, seed, stops = cmd
+            _, chunks, query, max_new, store_misses, temperature, seed, stops, top_k, top_p = cmd
             engine.submit(RagRequest(chunks, query, max_new, store_misses=store_misses, temperature=temperature,
-                                     seed=seed, stop_token_ids=tuple(stops)))
+                                     seed=seed, stop_token_ids=tuple(stops), top_k=top_k, top_p=top_p))
         elif op == CMD_STEP:
             engine.step()
         elif op == CMD_ABORT:

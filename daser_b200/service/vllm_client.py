@@ -180,6 +180,11 @@ class NativeEngineClient:
         if t > 0.0:
             seed = params.get("seed")
             out.update(temperature=t, seed=int(seed) if seed is not None else random.getrandbits(62))
+            top_k, top_p = int(params.get("top_k") or 0), params.get("top_p")
+            if top_k > 0:
+                out["top_k"] = top_k
+            if top_p is not None and 0.0 < float(top_p) < 1.0:
+                out["top_p"] = float(top_p)
         return out
 
     def _generate(self, segments, query, max_new, on_token=None, sampling=None):

@@ -212,7 +212,8 @@ def scenario_serve() -> int:
 
         def submit(self, req):
             self.calls.append(("submit", tuple(map(tuple, req.chunks)), tuple(req.query), req.max_new_tokens,
-                               req.store_misses, req.temperature, req.seed, tuple(req.stop_token_ids)))
+                               req.store_misses, req.temperature, req.seed, tuple(req.stop_token_ids),
+                               req.top_k, req.top_p))
             return req
 
         def has_work(self):
@@ -242,7 +243,7 @@ def scenario_serve() -> int:
         from daser_b200.engine.request import RagRequest
 
         lead.submit(RagRequest([[5] * 16], [6, 7], 3, store_misses=True, temperature=0.5, seed=42,
-                               stop_token_ids=(2,)))
+                               stop_token_ids=(2,), top_k=40, top_p=0.9))
         lead.step()
         lead.step()
         lead.abort("req-7")

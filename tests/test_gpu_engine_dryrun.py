@@ -93,6 +93,9 @@ def test_restore_compute_repair_and_sampling_fields(engine):
     assert all(s["temperature"] == 0.7 for s in sampled)
     assert len({s["seed"] for s in sampled}) == 3            # a fresh seed per step, derived from the request's
     assert "temperature" not in engine.runner.calls[0][0]    # computing a chunk samples nothing
+    engine.runner.calls.clear()
+    engine.generate([], [5, 6], max_new_tokens=2, temperature=0.7, seed=1, top_k=40, top_p=0.9)
+    assert all(s["top_k"] == 40 and s["top_p"] == 0.9 for seqs in engine.runner.calls for s in seqs)
     assert engine.blocks.num_free == 32 and not engine.has_work()
     # head repair: the restored chunk behind other context gets its first tokens recomputed in place
     engine.store_chunk(b)

@@ -65,6 +65,9 @@ def test_engine_and_http_sampling_are_reproducible_per_seed(tmp_path):
             assert post(temperature=1.5, seed=3) == post(temperature=1.5, seed=3)
             draws = {tuple(post(temperature=1.5)) for _ in range(4)}        # unseeded: a fresh seed per request
             assert len(draws) > 1
+            assert post(temperature=1.5, seed=3, top_k=1) == greedy         # top_k = 1 is greedy whatever the noise
+            assert post(temperature=1.5, seed=3, top_p=0.9) == eng.generate(
+                [], query, max_new_tokens=8, temperature=1.5, seed=3, top_p=0.9).generated
     finally:
         eng.close()
         lp.stop()
@@ -108,3 +111,40 @@ def test_generation_stops_at_stop_tokens_and_reports_why(tmp_path):
     finally:
         eng.close()
         lp.stop()
+
+
+def test_top_k_and_top_p_thresholds():
+    from daser_b200.engine.sampling import apply_truncation, sampling_threshold
+
+    torch.manual_seed(0)
+    logits = torch.randn(5, 200) * 2
+    inv = torch.tensor([1.0, 1.25, 0.0, 2.0, 1.0])
+    k = torch.tensor([5, 0, 5, 50, 0])
+    p = torch.tensor([1.0, 0.5, 0.5, 0.3, 1.0])
+    tau = sampling_threshold(logits, inv, k, p)
+    kept = (logits >= tau[:, None]).sum(-1)
+    assert int(kept[0]) == 5 and int(kept[2]) == 200 and int(kept[4]) == 200        # top-k; greedy row and plain row untouched
+    for row in (1, 3):                                                              # top-p (after top-k): smallest covering set
+        order = logits[row].sort(descending=True).values[: int(k[row]) or 200]
+        probs = torch.softmax(order * inv[row], 0)
+        want = int(((probs.cumsum(0) - probs) < p[row]).sum())
+        assert int(kept[row]) == want >= 1
+    # a shard masked with the threshold of the whole row keeps exactly its part of the kept set
+    shard = logits[:, 50:120].clone()
+    apply_truncation(shard, inv, k, p, whole_rows=logits)
+    assert torch.equal(torch.isfinite(shard), logits[:, 50:120] >= tau[:, None])
+
+
+def test_truncated_draws_stay_inside_the_nucleus_and_follow_it():
+    logits = torch.tensor([[2.0, 1.5, 1.0, 0.0, -1.0, -3.0]])
+    eng = CpuRagEngine.__new__(CpuRagEngine)
+    counts = torch.zeros(6)
+    for seed in range(4000):
+        counts[eng._sample(logits, RagRequest([], [1], 4, temperature=1.0, seed=seed, top_k=3))] += 1
+    want = torch.softmax(logits[0, :3], 0)
+    assert counts[3:].sum() == 0 and (counts[:3] / counts.sum() - want).abs().max().item() < 0.03
+    counts.zero_()
+    for seed in range(4000):
+        counts[eng._sample(logits, RagRequest([], [1], 4, temperature=1.0, seed=seed, top_p=0.6))] += 1
+    # probabilities .42 .26 .16 ...: the first two reach 0.6
+    assert counts[2:].sum() == 0 and counts[0] > counts[1] > 0
