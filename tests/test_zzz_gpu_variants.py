@@ -83,3 +83,32 @@ def test_gumbel_max_sampling_kernel_is_exact_across_vocabulary_shards_and_follow
     ew.argmax(logits, val, idx3, sampling=(inv, seeds + 1))
     torch.cuda.synchronize()
     assert torch.equal(idx2, idx) and not torch.equal(idx3, idx)
+
+
+def test_truncated_sampling_on_the_device():
+    """top-k / top-p masking (PyTorch on the device) followed by the Gumbel-max kernel: ``top_k = 1``
+    is greedy whatever the noise, and draws never leave the kept set."""
+    from daser_b200.engine.sampling import apply_truncation
+    from daser_b200.ops import elementwise as ew
+
+    torch.manual_seed(1)
+    rows, n = 512, 256
+    logits = (torch.randn(rows, n) * 2).to("cuda", torch.float32).contiguous()
+    greedy = logits.argmax(-1).to(torch.int32)
+    inv = torch.full((rows,), 1.25, dtype=torch.float32, device="cuda")
+    seeds = torch.arange(rows, dtype=torch.int64, device="cuda") + 99
+    val = torch.empty(rows, dtype=torch.float32, device="cuda")
+    idx = torch.empty(rows, dtype=torch.int32, device="cuda")
+    one = logits.clone()
+    apply_truncation(one, inv, torch.ones(rows, dtype=torch.int64, device="cuda"), torch.ones(rows, device="cuda"))
+    ew.argmax(one, val, idx, sampling=(inv, seeds))
+    torch.cuda.synchronize()
+    assert torch.equal(idx, greedy)
+    nucleus = logits.clone()
+    apply_truncation(nucleus, inv, torch.full((rows,), 20, dtype=torch.int64, device="cuda"),
+                     torch.full((rows,), 0.8, device="cuda"))
+    kept = torch.isfinite(nucleus)
+    assert int(kept.sum(-1).max()) <= 20 and int(kept.sum(-1).min()) >= 1
+    ew.argmax(nucleus, val, idx, sampling=(inv, seeds))
+    torch.cuda.synchronize()
+    assert bool(kept.gather(1, idx.long()[:, None]).all())
