@@ -38,6 +38,20 @@ class _Tracked:
         self.req, self.future, self.on_token, self.sent = req, future, on_token, 0
 
 
+def _settle(fut: Future, result: Any = None, exc: Optional[BaseException] = None) -> None:
+    """Complete ``fut`` unless its owner got there first (an asyncio wrapper that was cancelled
+    cancels the future underneath it at once, before the loop thread hears of it)."""
+    try:
+        if fut.done():
+            return
+        if exc is not None:
+            fut.set_exception(exc)
+        else:
+            fut.set_result(result)
+    except Exception:  # InvalidStateError: cancelled between the check and the call
+        pass
+
+
 class QueueFull(RuntimeError):
     """More requests in flight than the loop was told to take: the caller should come back later."""
 
@@ -123,15 +137,14 @@ class EngineLoop:
                         t.on_token = None  # an engine without abort runs the request out, unobserved
                         break
                     self._tracked.remove(t)
-                    if not t.future.done():
-                        t.future.set_exception(RuntimeError("request cancelled"))
+                    _settle(t.future, exc=RuntimeError("request cancelled"))
                     break
         elif kind == "call":
             fut, method, args, kw = item
             try:
-                fut.set_result(getattr(self.engine, method)(*args, **kw))
+                _settle(fut, result=getattr(self.engine, method)(*args, **kw))
             except Exception as exc:  # the caller's error, not the loop's
-                fut.set_exception(exc)
+                _settle(fut, exc=exc)
         return True
 
     def _report(self) -> None:
@@ -148,15 +161,14 @@ class EngineLoop:
             if t.req.done:
                 self._tracked.remove(t)
                 if t.req.error is not None:  # given up alone (it can never fit): the others go on
-                    t.future.set_exception(MemoryError(t.req.error))
+                    _settle(t.future, exc=MemoryError(t.req.error))
                 else:
-                    t.future.set_result(t.req)
+                    _settle(t.future, result=t.req)
 
     def _fail(self, exc: BaseException) -> None:
         self.failed = exc
         for t in self._tracked:
-            if not t.future.done():
-                t.future.set_exception(exc)
+            _settle(t.future, exc=exc)
         self._tracked.clear()
         while True:  # whoever queued meanwhile
             try:
@@ -164,8 +176,8 @@ class EngineLoop:
             except queue.Empty:
                 break
             fut = item.future if kind == "submit" else (item[0] if kind == "call" else None)  # cancels: nothing to tell
-            if fut is not None and not fut.done():
-                fut.set_exception(exc)
+            if fut is not None:
+                _settle(fut, exc=exc)
 
     def _run(self) -> None:
         try:

@@ -240,3 +240,23 @@ def test_back_pressure_refuses_at_once_above_the_limit(engine):
         assert len(loop.submit([], [7, 8, 9], 2).result(60).generated) == 2      # room again
     finally:
         loop.close()
+
+
+def test_a_future_cancelled_by_its_owner_does_not_stop_the_loop(engine):
+    """An asyncio wrapper that is cancelled cancels the future underneath it at once; when the
+    request then finishes (or is aborted) the loop must shrug, not die on the dead future."""
+    loop = EngineLoop(engine)
+    try:
+        doomed = loop.submit([], [1, 2, 3], 4)
+        assert doomed.cancel()                                # still pending: the owner wins
+        other = loop.submit([], [4, 5, 6], 3)
+        assert len(other.result(60).generated) == 3
+        time.sleep(0.2)                                       # the doomed request runs out meanwhile
+        assert loop.failed is None
+        assert len(loop.submit([], [7, 8], 2).result(60).generated) == 2
+        late = loop.call("has_work")
+        late.cancel()
+        assert loop.call("has_work").result(10) in (True, False) and loop.failed is None
+    finally:
+        loop.close()
+    assert engine.blocks.num_free == 256
