@@ -114,10 +114,14 @@ class EngineLoop:
         return fut
 
     def close(self, timeout_s: float = 60.0) -> None:
-        """Finish what is in flight, then stop the thread (the engine is left open)."""
+        """Finish what is in flight, then stop the thread (the engine is left open).  What is still
+        running after ``timeout_s`` is aborted, so that the caller may close the engine after this."""
         self._stop = True
         self._inbox.put(("wake", None))
         self._thread.join(timeout_s)
+        if self._thread.is_alive():
+            self._inbox.put(("abort_all", None))
+            self._thread.join(timeout_s)
 
     # -- the loop thread ---------------------------------------------------------------------------
     def _take(self, block: bool) -> bool:
@@ -128,6 +132,13 @@ class EngineLoop:
         if kind == "submit":
             self.engine.submit(item.req)
             self._tracked.append(item)
+        elif kind == "abort_all":
+            for t in list(self._tracked):
+                if hasattr(self.engine, "abort"):
+                    self.engine.abort(t.req.req_id)
+                _settle(t.future, exc=RuntimeError("engine loop closed"))
+            if hasattr(self.engine, "abort"):
+                self._tracked.clear()
         elif kind == "cancel":
             for t in self._tracked:
                 if t.future is item:

@@ -260,3 +260,15 @@ def test_a_future_cancelled_by_its_owner_does_not_stop_the_loop(engine):
     finally:
         loop.close()
     assert engine.blocks.num_free == 256
+
+
+def test_close_aborts_what_outlives_its_patience(engine):
+    loop = EngineLoop(engine)
+    long_one = loop.submit([], [1, 2, 3], 3000)
+    time.sleep(0.1)
+    t0 = time.time()
+    loop.close(timeout_s=0.3)
+    assert time.time() - t0 < 5 and not loop._thread.is_alive()
+    with pytest.raises(RuntimeError, match="closed"):
+        long_one.result(1)
+    assert not engine.has_work() and engine.blocks.num_free == 256
