@@ -83,6 +83,14 @@ class EngineLoop:
         if self._stop or self.failed is not None:
             fut.set_exception(RuntimeError(f"engine loop is not running: {self.failed or 'closed'}"))
             return fut
+        # what the engine would only find out inside a step (where a failure takes the others down)
+        bt = getattr(getattr(self.engine, "cfg", None), "block_tokens", None)
+        if bt and any(len(c) % bt for c in chunks):
+            fut.set_exception(ValueError(f"cached segments must be whole blocks of {bt} tokens"))
+            return fut
+        if len(query) < 1 or int(max_new_tokens) < 1:
+            fut.set_exception(ValueError("a request needs at least one query token and one token to generate"))
+            return fut
         with self._count_lock:
             if self._max_in_flight and self._in_flight >= self._max_in_flight:
                 fut.set_exception(QueueFull(f"{self._in_flight} requests in flight (limit {self._max_in_flight})"))

@@ -114,6 +114,9 @@ def test_a_failing_step_fails_everything_in_flight_and_later_calls():
 def test_a_callers_error_in_call_does_not_stop_the_loop(engine):
     loop = EngineLoop(engine)
     try:
+        for bad in (([[1, 2, 3]], [4], 1), ([], [], 1), ([], [4], 0)):      # ragged segment, no query, nothing to generate
+            with pytest.raises(ValueError):
+                loop.submit(*bad).result(5)
         with pytest.raises(ValueError):
             loop.call("store_chunk", [1, 2, 3]).result(30)   # not a whole number of blocks
         assert len(loop.submit([], [9, 9], 2).result(60).generated) == 2
