@@ -40,7 +40,9 @@ def test_runner_with_qk_norm_matches_reference_forward():
     assert cos > 0.98, cos
     assert (got - want).abs().max().item() < 0.15 * want.abs().max().item() + 0.05
     # the norm is not a no-op for these weights: the same model without it answers differently
-    plain = LlamaWeights(PRESETS["tiny-gqa"], 1, 0, wf.embed, wf.layers, wf.final_norm, wf.lm_head)
+    import dataclasses
+
+    plain = LlamaWeights(dataclasses.replace(cfg, qk_norm=False), 1, 0, wf.embed, wf.layers, wf.final_norm, wf.lm_head)
     pool2 = TorchPagedKV(cfg, 64)
     reference_forward(plain, torch.tensor(tokens[:33]), torch.arange(33), pool2, torch.tensor(table), 0, return_logits=False)
     other = reference_forward(plain, torch.tensor(tokens[33:]), torch.arange(33, 40), pool2, torch.tensor(table), 33)[-1]
