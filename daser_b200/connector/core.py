@@ -165,9 +165,12 @@ class SchedulerHalf:
     def _negotiate_once(self) -> None:
         """First contact: packed token ids and the native lookup socket, if the server has them."""
         if not self._negotiated:
-            self._negotiated = True
             if hasattr(self._ipc, "negotiate"):
                 self._ipc.negotiate()
+                # asked again at the next request if the server could not be reached this time
+                self._negotiated = bool(getattr(self._ipc, "negotiated", True))
+            else:
+                self._negotiated = True
 
     def plan_chunk_loads(self, req_id: str, placements: Sequence[tuple[str, int]]) -> list[Optional[ReqLoadSpec]]:
         """Resolve ``(chunk_key, token offset)`` pairs; returns one spec (or None) per pair.

@@ -38,14 +38,18 @@ class IPCClientSync:
         # a server that also takes them as packed int32 (one bin field instead of n integers)
         self.binary_tokens = False
         self._fast: Optional["IPCClientSync"] = None  # client of the server's native lookup socket
+        self.negotiated = False  # a server has answered `negotiate` (with its features, or with "unknown op")
 
     def negotiate(self) -> bool:
         """Ask the server what it supports; enables packed token ids when it does.  A server
         without the ``hello`` operation (the reference's) leaves everything as it is."""
         try:
             reply = self.call({"op": frames.OP_HELLO, "geometry": {}})
-        except RuntimeError:
+        except RuntimeError as exc:
+            # a server that answered "unknown op" has been asked; one that could not be reached has not
+            self.negotiated = "IPC error from server" in str(exc)
             return False
+        self.negotiated = True
         self.binary_tokens = "tokens_bin" in (reply.get("features") or [])
         # lookups by key may go to the server's native thread, on a socket of its own
         fast = reply.get("fast_lookup")

@@ -164,3 +164,20 @@ def test_wide_requests_cover_the_longer_msgpack_forms(tmp_path):
         plain.close()
         fast.close()
         lp.stop()
+
+
+def test_negotiation_is_retried_until_a_server_answers(tmp_path):
+    """A scheduler half that comes up before the control plane must not settle for the slow path."""
+    from daser_b200.connector.core import SchedulerHalf
+
+    sock = str(tmp_path / "d.sock")
+    half = SchedulerHalf(sock, 16, "m")
+    assert half.plan_chunk_loads("r0", [("k" * 32, 0)]) == [None]         # nobody there: a miss, and not negotiated
+    assert half._negotiated is False
+    lp = LiveControlPlane(tmp_path).start()
+    try:
+        assert half.plan_chunk_loads("r1", [("k" * 32, 0)]) == [None]
+        assert half._negotiated is True and half._ipc._fast is not None and half._ipc.binary_tokens
+    finally:
+        half.close()
+        lp.stop()
