@@ -55,7 +55,12 @@ def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
     p.add_argument("--position", choices=("fixed", "rope"), default="fixed")
     p.add_argument("--rope-theta", type=float, default=10000.0)
     p.add_argument("--snapshot-interval", type=float, default=0.0)
-    return p.parse_args(argv)
+    p.add_argument("--no-fast-lookup", action="store_true",
+                   help="do not start the native thread that answers lookups by key on <socket>.fast")
+    args = p.parse_args(argv)
+    if args.no_fast_lookup:
+        os.environ["DASER_FAST_LOOKUP"] = "0"
+    return args
 
 
 def _build_daser_config(args: argparse.Namespace) -> DaserConfig:

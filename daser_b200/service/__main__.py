@@ -64,7 +64,11 @@ def _parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
                    help="one thread keeps the native engine stepping and concurrent requests share its steps "
                         "(continuous batching); without it requests are served one after the other")
     p.add_argument("--snapshot-interval", type=float, default=0.0)
+    p.add_argument("--no-fast-lookup", action="store_true",
+                   help="do not start the native thread that answers lookups by key on <socket>.fast")
     args = p.parse_args(argv)
+    if args.no_fast_lookup:
+        os.environ["DASER_FAST_LOOKUP"] = "0"
     if args.engine == "vllm" and (not args.vllm_base_url or not args.model):
         p.error("--vllm-base-url and --model are required with --engine vllm")
     return args
