@@ -29,9 +29,7 @@ from __future__ import annotations
 import argparse
 import asyncio
 import json
-import math
 import os
-import random
 import subprocess
 import sys
 import tempfile
@@ -40,104 +38,56 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "baseline"))
+
+from traffic import make_traffic, percentile  # noqa: E402
+from vllm_common import ClockSampler  # noqa: E402
 
 METRIC = "rag_ttft_p50_ms (Llama-3-70B, TP=#GPUs, chunk-KV restore from fp8 store)"
 
 
 def reference_arm(args) -> None:
-    """The unmodified reference needs ``kvikio`` and ``cupy`` at import time
-    (``daser/connector/gds_transfer.py:10-13``, ``daser/connector/daser_connector.py:14``);
-    neither is installed and there is no package index, so its connector cannot be imported."""
-    why = "reference connector imports kvikio and cupy at module scope; neither is installed offline"
-    try:
-        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-        import importlib
+    """Runs ``baseline/reference_arm.py`` (the unmodified reference inside the stock ``vllm.LLM``)
+    in a process of its own and relays its JSON line.
 
-        importlib.import_module("daser.connector.daser_connector")
-        why = "reference imported but its vLLM path was not wired in this build"
-    except Exception as exc:  # noqa: BLE001
-        why = f"reference connector cannot be imported here: {type(exc).__name__}: {str(exc)[:120]}"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    vLLM starts and manages its own tensor-parallel workers, so under a multi-rank launcher only
+    rank 0 acts, with the launcher's variables removed from the child's environment; the other
+    ranks exit at once.  The child imports nothing of this framework: its ``PYTHONPATH`` holds
+    the reference install and the kvikio / cupy stand-ins only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    base = os.path.join(ROOT, "baseline")
+    sys.path.insert(0, base)
+    out = None
+    if not os.path.isdir(os.path.join(base, "_ref", "daser")):
+        out = {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target of the reference)"}
+    else:
+        import vllm_common as vc
 
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int) -> None:
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.path = os.path.join(tempfile.gettempdir(), f"daser_clocks_{os.getpid()}.csv")
-
-    def start(self) -> None:
+        env = vc.clean_env([os.path.join(base, "_ref"), os.path.join(base, "shims")])
+        cmd = [sys.executable, os.path.join(base, "reference_arm.py"), "--gpus", str(args.gpus), "--steps",
+               str(args.steps), "--warmup", str(max(args.warmup, 3)), "--model", args.model, "--pool", str(args.pool),
+               "--k", str(args.k)]
+        if args.store_dir:
+            cmd += ["--store-dir", args.store_dir]
+        if os.environ.get("DASER_REF_EAGER") == "1":
+            cmd.append("--eager")
+        # a session of its own: on a time-out the whole group goes (vLLM's engine and worker processes too)
+        proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=None, text=True, start_new_session=True)
         try:
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=self.out, stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
-        self.proc.terminate()
-        try:
-            self.proc.wait(5)
+            stdout, _ = proc.communicate(timeout=float(os.environ.get("DASER_REF_TIMEOUT", "1500")))
+            for line in stdout.splitlines():
+                if line.startswith("REFERENCE_RESULT "):
+                    out = json.loads(line[len("REFERENCE_RESULT "):])
+            if out is None:
+                out = {"impl": "reference", "unavailable": f"reference process ended with code {proc.returncode} and no result"}
         except subprocess.TimeoutExpired:
-            self.proc.kill()
-        self.out.close()
-        sm, mx, reasons = [], [], set()
-        for line in open(self.path):
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+            import signal
 
-
-def make_traffic(cfg, pool_size: int, k_chunks: int, n_requests: int, seed: int = 0):
-    rng = random.Random(seed)
-    bt = cfg.block_tokens
-    pad = 0
-
-    def tokens(n):
-        return [rng.randrange(1, cfg.vocab_size) for _ in range(n)]
-
-    def padded(n):
-        t = tokens(n)
-        return t + [pad] * (-len(t) % bt)
-
-    prefix = padded(64)
-    pool = []
-    for _ in range(pool_size):
-        n = int(round(math.exp(math.log(300.0) + 0.6 * rng.gauss(0, 1))))
-        pool.append(padded(max(64, min(1024, n))))
-    weights = [1.0 / (r + 1) ** 1.1 for r in range(pool_size)]
-    reqs = []
-    for _ in range(n_requests):
-        picks = rng.choices(range(pool_size), weights=weights, k=k_chunks)
-        reqs.append(([prefix] + [pool[i] for i in picks], tokens(64)))
-    return prefix, pool, reqs
-
-
-def percentile(vals, q):
-    v = sorted(vals)
-    return v[max(0, min(len(v) - 1, int(round(q / 100.0 * (len(v) - 1)))))]
+            os.killpg(proc.pid, signal.SIGKILL)
+            proc.wait()
+            out = {"impl": "reference", "unavailable": "reference process did not finish within its time limit"}
+    print(json.dumps(out))
 
 
 def main() -> None:
@@ -194,7 +144,7 @@ def main() -> None:
     if tp_ctx is not None:
         store_dir = tp_ctx.broadcast_object(store_dir)
     slot = cfg.num_layers * 2 * cfg.block_tokens * cfg.num_kv_heads * cfg.head_dim * 5 // 4
-    prefix, pool, reqs = make_traffic(cfg, args.pool, args.k, args.steps + args.warmup)
+    prefix, pool, reqs = make_traffic(cfg.vocab_size, cfg.block_tokens, args.pool, args.k, args.steps + args.warmup)
     pool_slots = sum(len(c) // cfg.block_tokens for c in pool) + len(prefix) // cfg.block_tokens
     total_slots = pool_slots + 64
     dcfg = DaserConfig(store_path=os.path.join(store_dir, "daser.store"), index_path="", total_slots=total_slots,
@@ -248,7 +198,7 @@ def main() -> None:
         torch.cuda.synchronize()
 
     def run(req_spec):
-        chunks, query = req_spec
+        chunks, query, _ = req_spec
         return eng.generate(chunks, query, max_new_tokens=1)
 
     for spec in reqs[: args.warmup]:

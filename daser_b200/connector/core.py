@@ -562,15 +562,19 @@ class WorkerHalf:
             if n == 0:
                 continue
             skip = spec.skip_slots * g.slot_size
-            hit = self.hbm.lookup(spec.chunk_key) if self.hbm is not None else None
+            need = spec.skip_slots + n
+            hit = self.hbm.lookup(spec.chunk_key, need) if self.hbm is not None else None
             if hit is not None:
                 jobs.append((spec, hit + skip, n, 0, "hbm"))
                 continue
-            hit = self.host.lookup(spec.chunk_key) if self.host is not None else None
+            hit = self.host.lookup(spec.chunk_key, need) if self.host is not None else None
             if hit is not None:
                 jobs.append((spec, hit + skip, n, 0, "host"))
                 continue
-            if self.host is not None and spec.skip_slots == 0:
+            # only whole chunks enter a tier: a trimmed prefix hit (one slot short, so that the
+            # engine has a token left to compute) must not be mistaken for the chunk later
+            whole = spec.skip_slots == 0 and n == spec.num_slots
+            if self.host is not None and whole:
                 off = self.host.reserve(spec.chunk_key, n * g.slot_size)
                 if off is not None:
                     ptr = self.host.arena.data_ptr() + off
@@ -638,7 +642,7 @@ class WorkerHalf:
                 continue
             if kind != "hbm":
                 metrics.inc("connector.bytes_over_pcie", n * g.slot_size)
-                if cuda and self.hbm is not None and spec.skip_slots == 0:
+                if cuda and self.hbm is not None and spec.skip_slots == 0 and n == spec.num_slots:
                     # Promote first, restore from the promoted copy: the images cross PCIe once,
                     # by DMA at full rate, instead of being read by the kernel and copied again.
                     off = self.hbm.reserve(spec.chunk_key, n * g.slot_size)

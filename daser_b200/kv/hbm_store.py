@@ -55,9 +55,16 @@ class HBMStore:
     def used_slots(self) -> int:
         return sum(n for _, n in self._chunks.values())
 
-    def lookup(self, key: str) -> Optional[int]:
-        """Device address of the chunk's first slot image, or None."""
+    def lookup(self, key: str, need_slots: int = 0) -> Optional[int]:
+        """Device address of the chunk's first slot image, or None.
+
+        ``need_slots`` is how many slots from the start of the chunk the caller is going to read;
+        an entry that holds fewer is not a hit (and is dropped, so that the whole chunk can be
+        cached in its place)."""
         hit = self._chunks.get(key)
+        if hit is not None and hit[1] < need_slots:
+            self.evict(key)
+            hit = None
         if hit is None:
             metrics.inc(f"{self.kind}.misses")
             return None
@@ -116,13 +123,17 @@ class HBMStore:
     def reserve(self, key: str, nbytes: int) -> Optional[int]:
         """Claim room for ``key`` and return the arena byte offset to fill (None if it cannot fit
         without evicting an entry that the current step still reads)."""
-        if key in self._chunks:
-            self._chunks.move_to_end(key)
-            self._protected.add(key)
-            return self._chunks[key][0] * self.slot_size
         if nbytes % self.slot_size:
             raise ValueError("chunk size is not a whole number of slots")
         n = nbytes // self.slot_size
+        if key in self._chunks:
+            if self._chunks[key][1] >= n:
+                self._chunks.move_to_end(key)
+                self._protected.add(key)
+                return self._chunks[key][0] * self.slot_size
+            if key in self._protected:
+                return None  # a shorter entry that this step still reads
+            self.evict(key)
         if n > self.capacity:
             return None
         first = self._take(n)

@@ -140,3 +140,67 @@ def test_tier_invariants_under_random_operations():
             assert tier.used_slots == sum(n for _, n in tier._chunks.values()) <= CAP
 
     run()
+
+
+def test_trimmed_prefix_hit_does_not_shadow_the_whole_chunk(tmp_path):
+    """A prompt equal to a stored chunk loads one slot fewer than the chunk has (the engine must
+    compute at least one token).  That short load must not be cached under the chunk's key: a
+    later, longer prompt reads the whole chunk and must get every block right."""
+    from conftest import LiveControlPlane
+    from daser_b200.connector.core import SchedulerHalf, TorchKVBackend, WorkerHalf
+    from daser_b200.kv.hbm_store import HBMStore
+    from daser_b200.kv.layout import KVGeometry
+
+    L, H, D, B = 2, 2, 32, 16
+    geo = KVGeometry(num_layers=L, num_kv_heads=H, head_dim=D, block_tokens=B, dtype_bytes=2, codec="raw")
+    lp = LiveControlPlane(tmp_path, total_slots=64, slot_size=geo.slot_size).start()
+    torch.manual_seed(3)
+    pool = torch.randn(L, 24, 2, H, B, D).to(torch.bfloat16)
+    host = HBMStore(geo.slot_size, 16, torch.device("cpu"))
+    worker = WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool, [1.0] * (D // 2)),
+                        io_backend="posix", staging_slots=8, host_store=host)
+    sched = SchedulerHalf(lp.socket_path, B, "m")
+
+    def step(req, fn):
+        fn()
+        meta = sched.build_connector_meta([req])
+        worker.bind_connector_metadata(meta)
+        worker.start_load_kv()
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+        sched.request_finished(req)
+        return meta
+
+    try:
+        tokens = list(range(500, 500 + 4 * B))
+        # another chunk right behind it in the arena and in the file, so an over-read is visible
+        other = list(range(900, 900 + 4 * B))
+        for rid, toks, blocks in (("s1", tokens, [1, 2, 3, 4]), ("s2", other, [5, 6, 7, 8])):
+            def cold(rid=rid, toks=toks, blocks=blocks):
+                assert sched.get_num_new_matched_tokens(rid, toks + [1], 0) == (0, False)
+                sched.update_state_after_alloc(rid, blocks, 0)
+            step(rid, cold)
+        host.clear()  # cold tier: the next loads come from the file
+        want = pool[:, [1, 2, 3, 4]].clone()
+
+        def trimmed():
+            n, _ = sched.get_num_new_matched_tokens("t1", tokens, 0)  # the prompt IS the chunk
+            assert n == 3 * B
+            sched.update_state_after_alloc("t1", [10, 11, 12], n)
+        meta = step("t1", trimmed)
+        assert len(meta.reqs_to_load[0].block_ids) == 3
+        assert torch.equal(pool[:, [10, 11, 12]], want[:, :3])
+
+        def full():
+            n, _ = sched.get_num_new_matched_tokens("t2", tokens + [7, 8, 9], 0)
+            assert n == 4 * B
+            sched.update_state_after_alloc("t2", [14, 15, 16, 17, 18], n)
+        step("t2", full)
+        assert torch.equal(pool[:, [14, 15, 16, 17]], want)
+        # and the whole chunk is what the tier now holds
+        assert host.lookup(meta.reqs_to_load[0].chunk_key, 4) is not None
+        host.end_step()
+    finally:
+        worker.shutdown()
+        sched.close()
+        lp.stop()
