@@ -226,12 +226,20 @@ class GpuRagEngine(SchedulingMixin):
         # 3. compute what was not restored, then the query
         ctx = 0
         first = None
+        # A missed chunk behind other context was just computed attending to that context; the
+        # store keeps chunks under a key of their own tokens only, so what is stored must be the
+        # chunk computed alone (as `store_chunk` does).  Those are recomputed after the first
+        # token has gone out, between steps.
+        standalone: list[Sequence[int]] = []
         for c, off, ok in zip(req.chunks, offsets, found):
             blocks_of_chunk = set(req.block_table[off // bt : (off + len(c)) // bt])
             if not ok or (blocks_of_chunk & failed_blocks):
                 self._prefill_tokens(c, off, req.block_table)
                 if req.store_misses and not ok:
-                    self._store_in_place(req, c, off)
+                    if off == 0:
+                        self._store_in_place(req, c, off)  # saw no context: this IS the chunk's own KV
+                    else:
+                        standalone.append(c)
             else:
                 req.restored_chunks += 1
                 req.restored_bytes += (len(c) // bt) * self.geo.slot_size
@@ -257,13 +265,17 @@ class GpuRagEngine(SchedulingMixin):
         metrics.observe("engine.ttft_ms", req.ttft_ms)
         if self.sched is not None:
             self.sched.request_finished(req.req_id)
+        for c in standalone:
+            if len(c) // bt <= self.blocks.num_free:
+                self.store_chunk(c)
         if req.finished():
             self._finish(req)
         else:
             self.running.append(req)
 
     def _store_in_place(self, req: RagRequest, chunk: Sequence[int], off: int) -> None:
-        """Save a chunk that was just computed inside the request (its keys sit at ``off``)."""
+        """Save a chunk that was just computed inside the request.  Only valid for ``off == 0``:
+        further back the KV has attended to the request's earlier chunks and is not the chunk's own."""
         bt = self.cfg.block_tokens
         blocks = req.block_table[off // bt : (off + len(chunk)) // bt]
         meta = ConnectorMeta()

@@ -134,6 +134,9 @@ class ControlPlane:
             for meta in self.store.iter_chunks():
                 if self.store.is_committed(meta.chunk_key):
                     await self.index.insert(meta)
+                    anchor = self.store.anchor(meta.chunk_key)
+                    if anchor and hasattr(self.index, "register_anchor"):
+                        self.index.register_anchor(meta.chunk_key, anchor)  # scans find it after a restart
         geometry = {}
         try:
             geometry = self.cfg.geometry()

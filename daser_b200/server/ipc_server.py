@@ -335,10 +335,10 @@ class IPCServer:
             if len(seen) < parts:
                 return {"ok": True, "pending_parts": parts - len(seen)}
             self._parts.pop(chunk_key, None)
-        self._cm.store.mark_committed(chunk_key, msg.get("checksum"))
+        anchor = msg.get("first_block")
+        self._cm.store.mark_committed(chunk_key, msg.get("checksum"), anchor)
         await self._ri.insert(meta)
         self._fast_put(meta)  # visible on the native lookup socket before this commit is acknowledged
-        anchor = msg.get("first_block")
         if anchor and hasattr(self._ri, "register_anchor"):
             self._ri.register_anchor(chunk_key, anchor)  # type: ignore[attr-defined]
         self._dirty = True

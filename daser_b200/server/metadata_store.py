@@ -79,6 +79,7 @@ class MetadataStore:
         self._runs: dict[int, SlotEntry] = {}
         self._uncommitted: set[str] = set()
         self._checksums: dict[str, int] = {}
+        self._anchors: dict[str, str] = {}  # chunk_key -> digest of its first block (chunk-offset scan)
 
     # -- mutation ---------------------------------------------------------
 
@@ -124,17 +125,20 @@ class MetadataStore:
             self._runs[meta.start_slot] = SlotEntry("skip", None, meta.num_slots)
         self._uncommitted.discard(chunk_key)
         self._checksums.pop(chunk_key, None)
+        self._anchors.pop(chunk_key, None)
 
     def clear_run(self, start_slot: int) -> None:
         """Erase the run head at ``start_slot`` (the ring reclaimed these slots)."""
         self._runs.pop(start_slot, None)
 
-    def mark_committed(self, chunk_key: str, checksum: Optional[int] = None) -> None:
+    def mark_committed(self, chunk_key: str, checksum: Optional[int] = None, anchor: Optional[str] = None) -> None:
         if chunk_key not in self._chunks:
             raise KeyError(f"chunk_key not found: {chunk_key}")
         self._uncommitted.discard(chunk_key)
         if checksum is not None:
             self._checksums[chunk_key] = int(checksum)
+        if anchor:
+            self._anchors[chunk_key] = str(anchor)
 
     # -- query ------------------------------------------------------------
 
@@ -150,6 +154,10 @@ class MetadataStore:
 
     def checksum(self, chunk_key: str) -> Optional[int]:
         return self._checksums.get(chunk_key)
+
+    def anchor(self, chunk_key: str) -> Optional[str]:
+        """Digest of the chunk's first block, as given at commit (kept across restarts)."""
+        return self._anchors.get(chunk_key)
 
     def get_slot_entry(self, slot_id: int) -> SlotEntry:
         if not 0 <= slot_id < self._total_slots:
@@ -208,11 +216,13 @@ class MetadataStore:
         self._total_slots, self._chunks, self._runs = total, chunks, runs
         self._uncommitted = set()
         self._checksums = {}
+        self._anchors = {}
 
     def ext_state(self) -> dict:
         return {
             "uncommitted": sorted(self._uncommitted),
             "checksums": dict(self._checksums),
+            "anchors": dict(self._anchors),
         }
 
     def load_ext_state(self, ext: dict) -> None:
@@ -220,6 +230,7 @@ class MetadataStore:
         self._checksums = {
             k: int(v) for k, v in ext.get("checksums", {}).items() if k in self._chunks
         }
+        self._anchors = {k: str(v) for k, v in ext.get("anchors", {}).items() if k in self._chunks}
 
     def save(self, path: str) -> None:
         atomic_write(path, self.to_bytes())

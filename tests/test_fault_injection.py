@@ -140,3 +140,27 @@ def test_worker_refuses_a_control_plane_with_another_geometry(tmp_path):
             WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool, [1.0] * 16))
     finally:
         lp.stop()
+
+
+def test_offset_scan_finds_chunks_again_after_a_restart(tmp_path):
+    """The first-block anchors that the offset scan needs are part of the snapshot: a chunk
+    committed before a restart is still found inside a prompt after it."""
+    lp = LiveControlPlane(tmp_path).start()
+    c = IPCClientSync(lp.socket_path)
+    chunk = list(range(300, 332))
+    key = hash_tokens(chunk)
+    c.alloc_chunk(key, 32, "default")
+    c.commit_chunk(key, first_block=hash_tokens(chunk[:16]))
+    prompt = [9] * 16 + chunk + [4, 5]
+    before = c.scan_chunks(prompt, "default")
+    assert [(h["chunk_key"], h["offset"]) for h in before] == [(key, 16)]
+    c.close()
+    lp.stop(save=True)
+    lp2 = LiveControlPlane(tmp_path).start()
+    try:
+        c = IPCClientSync(lp2.socket_path)
+        after = c.scan_chunks(prompt, "default")
+        assert [(h["chunk_key"], h["offset"]) for h in after] == [(key, 16)]
+        c.close()
+    finally:
+        lp2.stop()

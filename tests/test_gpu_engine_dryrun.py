@@ -149,3 +149,22 @@ def test_composed_chunks_admission_abort_and_the_engine_loop(engine):
     assert all(len(r.generated) == 6 for r in done)
     assert max(len(seqs) for seqs in engine.runner.calls) == 3   # one forward for the three of them
     assert engine.blocks.num_free == 32
+
+
+def test_missed_chunks_are_stored_as_computed_alone(engine):
+    """``store_misses``: a missed chunk at offset 0 is saved from the request's own blocks; a missed
+    chunk behind other context is recomputed alone at position 0 before it is saved, because what
+    the request computed for it has attended to the chunks in front of it."""
+    from daser_b200.hashing import hash_tokens
+
+    rng = random.Random(2)
+    a, b = ([rng.randrange(1000) for _ in range(32)] for _ in range(2))
+    engine.generate([a, b], [4, 5], max_new_tokens=1, store_misses=True)
+    # a at 0 and b at 32 inside the request, the query, then b once more on its own
+    assert _computed(engine.runner.calls) == [(0, 32), (32, 32), (64, 2), (0, 32)]
+    probe = engine.sched._ipc.lookup_chunks([hash_tokens(a), hash_tokens(b)], "default")
+    assert all(m is not None and m["pos_offset"] == 0 for m in probe)
+    engine.runner.calls.clear()
+    req = engine.generate([b, a], [4, 5], max_new_tokens=1, store_misses=True)
+    assert req.restored_chunks == 2 and _computed(engine.runner.calls) == [(64, 2)]
+    assert engine.blocks.num_free == 32
