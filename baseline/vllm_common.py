@@ -31,6 +31,8 @@ def clean_env(extra_pythonpath: list[str]) -> dict[str, str]:
     env.update(HF_HUB_OFFLINE="1", TRANSFORMERS_OFFLINE="1", VLLM_NO_USAGE_STATS="1", DO_NOT_TRACK="1",
                VLLM_WORKER_MULTIPROC_METHOD="spawn", PYTHONHASHSEED="0", TOKENIZERS_PARALLELISM="false")
     env.setdefault("VLLM_LOGGING_LEVEL", "WARNING")
+    # the reference logs every block id of every request at INFO (its own variable: daser/logging.py:31)
+    env.setdefault("DASER_LOG_LEVEL", "WARNING")
     return env
 
 

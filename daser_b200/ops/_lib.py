@@ -54,6 +54,8 @@ class KVJob(C.Structure):
         ("block_tokens", C.c_int32),
         ("image_is_fp8", C.c_int32),
         ("rank", C.c_int32),
+        ("layer_begin", C.c_int32),
+        ("layer_count", C.c_int32),
     ]
 
 

@@ -248,6 +248,7 @@ paged_attn_fp8_kernel(const AttnParams p) {
       vals[16 + j] = o[j][2 * r + 1] * inv;
     }
     const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
+    if (row >= p.total_rows) continue;  // q_start names more rows than the caller's buffers hold
     if (p.nsplit == 1) {
       __nv_bfloat16* dst = p.out + row * ATT_D + 32 * t;
       float lo[16], hi[16];
@@ -488,6 +489,7 @@ paged_attn_fp8_prefill_kernel(const AttnParams p) {
     const int tq = r ? tq1 : tq0, hq = r ? hq1 : hq0;
     const float inv = r ? inv1 : inv0;
     const int64_t row = (int64_t)(q0 + tq) * p.Hq + hq;
+    if (row >= p.total_rows) continue;
     if (p.nsplit == 1) {
       __nv_bfloat16* dst = p.out + row * ATT_D + 2 * t;
 #pragma unroll
@@ -580,16 +582,16 @@ DASER_API int daser_paged_attention_fp8(const void* q, void* out, float* part_o,
   p.row_tiles_max = (max_q_len * G + 15) / 16;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.num_blocks = pool->num_blocks;
+  p.total_rows = (int64_t)total_q * Hq;
   const int items = p.row_tiles_max * nsplit;
   const dim3 grid(Hkv, num_seqs, (items + ATT_WARPS - 1) / ATT_WARPS);
   const size_t smem = ATT_WARPS * ATT_STAGES * ATT_STAGE_BYTES;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[DASER_MAX_DEVICES] = {false};  // per device: the attribute is the device's
+  if (daser_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(paged_attn_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(paged_attn_fp8_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   if (attention_tc_enabled() && max_q_len * G >= 64 && 128 % G == 0) {
     // at least half of a 128-row MMA tile per KV head: the tcgen05 kernel

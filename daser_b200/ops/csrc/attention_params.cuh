@@ -27,6 +27,7 @@ struct AttnParams {
   int nsplit, split_tokens, row_tiles_max;
   float scale_log2;          // softmax scale * log2(e)
   int num_blocks;
+  int64_t total_rows;         // total_q * Hq: rows of out / part_o that exist (writes beyond are skipped)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {

@@ -118,7 +118,8 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
   // this thread's row
   const int tq = grp_tok_first + tid / G;
   const int hq = kvh * G + tid % G;
-  const bool valid = tq < q_len;
+  // rows beyond total_q (a q_start that names more rows than the buffers hold) are computed but never stored
+  const bool valid = tq < q_len && ((int64_t)(q0 + tq) * p.Hq + hq) < p.total_rows;
   const int pos = ctx - q_len + tq;  // last key this row may see
 
   float m = -INFINITY;  // the maximum the accumulated P are relative to
@@ -443,11 +444,10 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
 
 int daser_launch_attention_tc(const daser::AttnParams& p, int max_q_len, cudaStream_t stream) {
   using namespace daser;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[DASER_MAX_DEVICES] = {false};  // per device: the attribute is the device's
+  if (daser_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(paged_attn_fp8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   const int groups = (max_q_len * p.G + 127) / 128;
   const dim3 grid(p.Hkv, p.num_seqs, groups * p.nsplit);

@@ -8,16 +8,24 @@
 
 #define DASER_API extern "C" __attribute__((visibility("default")))
 
-// Error codes returned by the host entry points (0 = ok, >0 = cudaError_t).
-#define DASER_ERR_BAD_ARG (-1)
-#define DASER_ERR_UNSUPPORTED (-2)
-#define DASER_ERR_TOO_LARGE (-3)
+#include "kv_paged.h"  // DASER_ERR_* return codes and the host-visible parameter blocks
+
+// True the first time it is called for the current device with this `flags` array: attributes
+// set with cudaFuncSetAttribute belong to a device, so a process that drives several GPUs has to
+// set them once on each.
+#define DASER_MAX_DEVICES 64
+static inline bool daser_first_use_on_device(bool (&flags)[DASER_MAX_DEVICES]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= DASER_MAX_DEVICES) return true;
+  if (flags[dev]) return false;
+  flags[dev] = true;
+  return true;
+}
 
 // Status words written by kernels whose waits ran out (see signals.cuh).
 #define DASER_STATUS_OK 0u
 #define DASER_STATUS_TIMEOUT 1u
 
-#define DASER_MAX_RANKS 8
 #define FP8_GROUP 16
 #define E4M3_MAX 448.0f
 

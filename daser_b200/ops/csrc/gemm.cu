@@ -436,12 +436,11 @@ static bool pdl_enabled() {
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[DASER_MAX_DEVICES] = {false};  // per device: the attribute is the device's
+  if (daser_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          S::DYNAMIC);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   const dim3 grid((p.N + BN - 1) / BN, (p.M + GEMM_BM - 1) / GEMM_BM, p.k_splits);
   // Programmatic dependent launch: CTAs of this grid may be scheduled while the previous

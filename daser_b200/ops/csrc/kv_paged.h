@@ -5,6 +5,14 @@
 
 #define DASER_MAX_RANKS 8
 
+// Return codes of every host entry point of the library: 0 = ok, a positive value is a
+// cudaError_t, negative values are these.
+#ifndef DASER_ERR_BAD_ARG
+#define DASER_ERR_BAD_ARG (-1)
+#define DASER_ERR_UNSUPPORTED (-2)
+#define DASER_ERR_TOO_LARGE (-3)
+#endif
+
 // A paged KV pool, one base pointer per tensor-parallel rank.  Addresses of peers are
 // peer-mapped device pointers; element (layer, block, kv, tok, head_local, dim) of rank r
 // lives at payload[r] + layer*stride_layer + block*stride_block + kv*stride_kv +
@@ -40,4 +48,6 @@ typedef struct {
   int32_t block_tokens;
   int32_t image_is_fp8;      // slot image codec: 1 fp8b16, 0 raw bf16
   int32_t rank;              // save only: whose heads this launch writes
+  int32_t layer_begin;       // restore only: first layer this launch covers
+  int32_t layer_count;       // restore only: how many layers from layer_begin (0 = all of them)
 } DaserKVJob;
