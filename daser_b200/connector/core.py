@@ -431,11 +431,19 @@ class CudaKVBackend:
         self._d_ptr = torch.empty(max_slots, dtype=torch.int64, device=self.device)
         self._d_blk = torch.empty(max_slots, dtype=torch.int32, device=self.device)
         self._d_dlt = torch.empty(max_slots, dtype=torch.int32, device=self.device)
+        self._uploaded: Optional[torch.cuda.Event] = None  # the mirror's last copy has been read
+        self._consumed: Optional[torch.cuda.Event] = None  # the device list's last launch has run
+        self.h2d_bytes = 0  # bytes of work lists copied to the device (callers read and reset it)
 
-    def _worklist(self, ptrs: Sequence[int], block_ids: Sequence[int], deltas: Optional[Sequence[int]]):
+    def upload_worklist(self, ptrs: Sequence[int], block_ids: Sequence[int], deltas: Optional[Sequence[int]]):
+        """Copy a work list to the device on the current stream; launches that use it follow on
+        the same stream (or after an event recorded there)."""
         n = len(block_ids)
         if n > self.max_slots:
             raise ValueError(f"{n} slots in one step exceeds max_slots={self.max_slots}")
+        for ev in (self._uploaded, self._consumed):
+            if ev is not None:
+                ev.synchronize()  # earlier copies / launches have read what is about to be overwritten
         h = self._h
         h[0, :n] = torch.as_tensor(list(ptrs), dtype=torch.int64)
         h[1, :n] = torch.as_tensor(list(block_ids), dtype=torch.int64)
@@ -443,17 +451,40 @@ class CudaKVBackend:
         self._d_ptr[:n].copy_(h[0, :n], non_blocking=True)
         self._d_blk[:n].copy_(h[1, :n], non_blocking=True)
         self._d_dlt[:n].copy_(h[2, :n], non_blocking=True)
+        if self._uploaded is None:
+            self._uploaded = torch.cuda.Event()
+        self._uploaded.record()
+        self.h2d_bytes += 24 * n
         return self._ops.KVWorkList(self._d_ptr[:n], self._d_blk[:n], self._d_dlt[:n] if deltas is not None else None)
+
+    def _mark_consumed(self) -> None:
+        if self._consumed is None:
+            self._consumed = torch.cuda.Event()
+        self._consumed.record()
+
+    def restore_worklist(self, work, layer_begin: int = 0, layer_count: int = 0) -> None:
+        """One launch over ``work`` for layers ``[layer_begin, layer_begin + layer_count)`` (0 = all)."""
+        if work.n_slots:
+            self._ops.kv_restore(work, self.geo, self.pool, self.cos_sin, self.status, layer_begin=layer_begin,
+                                 layer_count=layer_count)
+            self._mark_consumed()
 
     def restore_ptrs(self, ptrs: Sequence[int], block_ids: Sequence[int], deltas: Sequence[int]) -> None:
         if not block_ids:
             return
-        self._ops.kv_restore(self._worklist(ptrs, block_ids, deltas), self.geo, self.pool, self.cos_sin, self.status)
+        self.restore_worklist(self.upload_worklist(ptrs, block_ids, deltas))
 
     def save_ptrs(self, ptrs: Sequence[int], block_ids: Sequence[int]) -> None:
         if not block_ids:
             return
-        self._ops.kv_save(self._worklist(ptrs, block_ids, None), self.geo, self.pool, self.rank, self.status)
+        self._ops.kv_save(self.upload_worklist(ptrs, block_ids, None), self.geo, self.pool, self.rank, self.status)
+        self._mark_consumed()
+
+    def copy_rows(self, dst_ptr: int, src_ptr: int, pitch: int, width: int, rows: int) -> None:
+        """``rows`` runs of ``width`` bytes, ``pitch`` apart on both sides, by the copy engine on the
+        current stream (some layers of every slot image of a chunk, host tier to HBM tier)."""
+        self._ops.copy_rows(dst_ptr, src_ptr, pitch, width, rows)
+        self.h2d_bytes += width * rows
 
     def check_status(self) -> None:
         code, slot = self.status.tolist()
@@ -465,6 +496,34 @@ class CudaKVBackend:
 # =========================================================================================
 # worker half
 # =========================================================================================
+
+
+@dataclass
+class _LoadJob:
+    """One chunk of a load: where the kernel reads it from and, if it is cold, where IO puts it."""
+
+    spec: ReqLoadSpec
+    n: int  # slots
+    kind: str  # "hbm" | "host" | "host_fill" | "staging"
+    src: int  # address of the first slot image the restore kernel reads
+    io_dst: int = 0  # address the reads land at (0: no IO)
+    promote_from: Optional[int] = None  # host address it is copied into the HBM tier from
+    tickets: list = field(default_factory=list)  # one IO ticket per layer group
+
+
+@dataclass
+class LoadTicket:
+    """A load in progress (see :meth:`WorkerHalf.begin_load`)."""
+
+    jobs: list
+    groups: list
+    failed: set = field(default_factory=set)
+    io_bytes: int = 0
+    io_wait_ms: float = 0.0  # host time spent blocked on reads (what the pipeline could not hide)
+    io_span_ms: float = 0.0  # first submit to last completion: the drive's view of the load
+    t_submit: float = 0.0
+    tier_bytes: dict = field(default_factory=dict)  # bytes restored by source: hbm / host / host_fill / staging
+    work: Any = None
 
 
 class WorkerHalf:
@@ -526,6 +585,7 @@ class WorkerHalf:
         self._lock = threading.Lock()
         self.last_load_bytes = 0
         self.last_load_io_ms = 0.0
+        self._load_done: Optional[Any] = None  # CUDA event: the last load's kernels have run
 
     @property
     def transfer(self):
@@ -550,12 +610,31 @@ class WorkerHalf:
         if meta is None or not meta.reqs_to_load:
             return
         with trace.span("start_load_kv", "connector", chunks=len(meta.reqs_to_load)):
-            self._start_load_kv(meta)
+            ticket = self.begin_load(meta)
+            if ticket is not None:
+                self.restore_group(ticket, 0)
+                self.end_load(ticket, wait=True)
 
-    def _start_load_kv(self, meta: ConnectorMeta) -> None:
+    def begin_load(self, meta: ConnectorMeta, layer_groups: Optional[Sequence[tuple[int, int]]] = None):
+        """Start restoring ``meta.reqs_to_load``; returns a ticket, or None if there is nothing to do.
+
+        ``layer_groups`` = ``[(first layer, count), ...]`` cuts the restore into pieces that
+        :meth:`restore_group` finishes one by one, in order: the storage reads are issued here,
+        all at once and group-major (every chunk's first layers come off the drive first), and
+        piece ``g`` only waits for its own reads.  An engine launches the model's layers of
+        group ``g`` right behind piece ``g``, so reading layers 10.. overlaps restoring and
+        computing layers 0..9.  Without groups the whole chunk is one piece (one contiguous read).
+
+        Chunks that do not fit the staging arena together are restored in waves; every wave
+        but the last completes inside this call.
+        """
+        if meta is None or not meta.reqs_to_load:
+            return None
         g = self.geo
-        # job = (spec, source address, n slots, IO destination address or 0, "hbm" | "host" | "host_fill" | "staging")
-        jobs: list[tuple[ReqLoadSpec, int, int, int, str]] = []
+        groups = [(int(a), int(n)) for a, n in (layer_groups or [(0, g.num_layers)])]
+        if self.kv.device_kind != "cuda" and len(groups) != 1:
+            raise ValueError("layer groups need the CUDA backend")
+        waves: list[list[_LoadJob]] = [[]]
         used = 0
         for spec in meta.reqs_to_load:
             n = len(spec.block_ids)
@@ -565,11 +644,11 @@ class WorkerHalf:
             need = spec.skip_slots + n
             hit = self.hbm.lookup(spec.chunk_key, need) if self.hbm is not None else None
             if hit is not None:
-                jobs.append((spec, hit + skip, n, 0, "hbm"))
+                waves[-1].append(_LoadJob(spec, n, "hbm", hit + skip))
                 continue
             hit = self.host.lookup(spec.chunk_key, need) if self.host is not None else None
             if hit is not None:
-                jobs.append((spec, hit + skip, n, 0, "host"))
+                waves[-1].append(_LoadJob(spec, n, "host", hit + skip))
                 continue
             # only whole chunks enter a tier: a trimmed prefix hit (one slot short, so that the
             # engine has a token left to compute) must not be mistaken for the chunk later
@@ -578,93 +657,173 @@ class WorkerHalf:
                 off = self.host.reserve(spec.chunk_key, n * g.slot_size)
                 if off is not None:
                     ptr = self.host.arena.data_ptr() + off
-                    jobs.append((spec, ptr, n, ptr, "host_fill"))
+                    waves[-1].append(_LoadJob(spec, n, "host_fill", ptr, io_dst=ptr))
                     continue
-            if used + n > self._staging_slots:
-                self._run_loads(jobs)  # staging full: flush what we have, then go on
-                jobs, used = [], 0
             if n > self._staging_slots:
                 raise ValueError(f"chunk of {n} slots exceeds staging capacity {self._staging_slots}")
+            if used + n > self._staging_slots:
+                waves.append([])  # staging full: what we have goes first, to completion
+                used = 0
             ptr = self._staging.data_ptr() + used * g.slot_size
-            jobs.append((spec, ptr, n, ptr, "staging"))
+            waves[-1].append(_LoadJob(spec, n, "staging", ptr, io_dst=ptr))
             used += n
-        self._run_loads(jobs)
-        for tier in (self.hbm, self.host):
-            if tier is not None:
-                tier.end_step()
+        self._wait_sources_free()
+        for wave in waves[:-1]:
+            t = self._issue(wave, [(0, g.num_layers)])
+            self.restore_group(t, 0)
+            self.end_load(t, wait=True, close_step=False)
+        return self._issue(waves[-1], groups)
 
-    def _run_loads(self, jobs) -> None:
-        if not jobs:
-            return
+    def _wait_sources_free(self) -> None:
+        """The previous load's kernels have read the staging arena (about to be refilled)."""
+        if self._load_done is not None:
+            self._load_done.synchronize()
+
+    def _issue(self, jobs: list, groups: list[tuple[int, int]]) -> "LoadTicket":
+        """Reserve HBM-tier room for what crosses PCIe, submit every read, upload the work list."""
         g = self.geo
-        t0 = time.perf_counter()
+        ticket = LoadTicket(jobs, groups)
         eng = self._xfer.engine
+        cuda = self.kv.device_kind == "cuda"
         dev_staging = self._staging.is_cuda
-        tickets = []
-        nbytes_total = 0
-        # reads go out in file order: neighbouring chunks become one sequential sweep of the device
-        for spec, src, n, io_dst, kind in sorted(jobs, key=lambda j: j[0].file_offset):
-            if not io_dst:
-                continue
-            off = spec.file_offset + spec.skip_slots * g.slot_size
-            nbytes = n * g.slot_size
-            try:
-                tickets.append((spec, kind, eng.submit_read(io_dst, off, nbytes, device=dev_staging and kind == "staging")))
-            except OSError as exc:
-                logger.warning("[CONNECTOR] read submit failed for %s: %s", spec.chunk_key, exc)
-                tickets.append((spec, kind, None))
-            nbytes_total += nbytes
-        failed: set[str] = set()
-        trace.instant("io.reads_submitted", n=len(tickets), bytes=nbytes_total)
-        for spec, kind, ticket in tickets:
-            try:
-                if ticket is None:
-                    raise OSError("submit failed")
-                eng.wait(ticket)
-            except (OSError, TimeoutError) as exc:
-                logger.warning("[CONNECTOR] load of %s failed: %s", spec.chunk_key, exc)
-                failed.add(spec.chunk_key)
-                self._load_errors.update(spec.block_ids)
-                metrics.inc("connector.load_errors")
-                if kind == "host_fill":
-                    self.host.evict(spec.chunk_key)  # the reserved slots hold garbage
-        io_ms = (time.perf_counter() - t0) * 1e3
-        self.last_load_bytes, self.last_load_io_ms = nbytes_total, io_ms
-        if nbytes_total:
-            _perf.record("load_io_ms", io_ms, "ms")
-            metrics.inc("connector.bytes_loaded", nbytes_total)
+        for job in jobs:
+            spec = job.spec
+            if job.kind != "hbm":
+                metrics.inc("connector.bytes_over_pcie", job.n * g.slot_size)
+                if cuda and self.hbm is not None and spec.skip_slots == 0 and job.n == spec.num_slots:
+                    # Promote first, restore from the promoted copy: the images cross PCIe once,
+                    # by DMA at full rate, instead of being read by the kernel and copied again.
+                    off = self.hbm.reserve(spec.chunk_key, job.n * g.slot_size)
+                    if off is not None:
+                        job.promote_from, job.src = job.src, self.hbm.arena.data_ptr() + off
+                if cuda and job.promote_from is None and not dev_staging:
+                    self.kv.h2d_bytes += job.n * g.slot_size  # the kernel reads these images over PCIe itself
+            ticket.tier_bytes[job.kind] = ticket.tier_bytes.get(job.kind, 0) + job.n * g.slot_size
+        ticket.t_submit = time.perf_counter()
+        whole = len(groups) == 1 and groups[0] == (0, g.num_layers)
+        layer = g.layer_size
+        # reads go out group-major and, inside a group, in file order: neighbouring chunks
+        # become one sequential sweep of the device
+        for l0, count in groups:
+            for job in sorted((j for j in jobs if j.io_dst), key=lambda j: j.spec.file_offset):
+                spec = job.spec
+                off = spec.file_offset + spec.skip_slots * g.slot_size
+                dev = dev_staging and job.kind == "staging"
+                try:
+                    if whole:
+                        t = eng.submit_read(job.io_dst, off, job.n * g.slot_size, device=dev)
+                    else:
+                        t = eng.submit_read_strided(job.io_dst + l0 * layer, off + l0 * layer, count * layer, job.n,
+                                                    g.slot_size, device=dev)
+                except OSError as exc:
+                    logger.warning("[CONNECTOR] read submit failed for %s: %s", spec.chunk_key, exc)
+                    t = None
+                job.tickets.append(t)
+                ticket.io_bytes += job.n * count * layer
+        trace.instant("io.reads_submitted", n=sum(len(j.tickets) for j in jobs), bytes=ticket.io_bytes)
+        if cuda:
+            ticket.work = self._upload(ticket)
+        return ticket
+
+    def _upload(self, ticket: "LoadTicket"):
+        g = self.geo
         ptrs: list[int] = []
         blocks: list[int] = []
         deltas: list[int] = []
-        cuda = self.kv.device_kind == "cuda"
-        for spec, src, n, io_dst, kind in jobs:
-            if spec.chunk_key in failed:
+        for job in ticket.jobs:
+            if job.spec.chunk_key in ticket.failed:
                 continue
-            if kind != "hbm":
-                metrics.inc("connector.bytes_over_pcie", n * g.slot_size)
-                if cuda and self.hbm is not None and spec.skip_slots == 0 and n == spec.num_slots:
-                    # Promote first, restore from the promoted copy: the images cross PCIe once,
-                    # by DMA at full rate, instead of being read by the kernel and copied again.
-                    off = self.hbm.reserve(spec.chunk_key, n * g.slot_size)
-                    if off is not None:
-                        arena = self.host.arena if kind in ("host", "host_fill") else self._staging
-                        a0 = src - arena.data_ptr()
-                        self.hbm.arena[off : off + n * g.slot_size].copy_(arena[a0 : a0 + n * g.slot_size],
-                                                                         non_blocking=True)
-                        src = self.hbm.arena.data_ptr() + off
-            for i in range(n):
-                ptrs.append(src + i * g.slot_size)
-                blocks.append(spec.block_ids[i])
-                deltas.append(spec.delta)
-        if cuda:
-            self.kv.restore_ptrs(ptrs, blocks, deltas)
-            torch.cuda.current_stream().synchronize()  # sources may be reused by the next step
-            self.kv.check_status()
-        else:
-            images = torch.empty((len(ptrs), g.slot_size), dtype=torch.uint8)
-            for row, ptr in enumerate(ptrs):
-                images[row] = self._image_at(ptr)
+            for i in range(job.n):
+                ptrs.append(job.src + i * g.slot_size)
+                blocks.append(job.spec.block_ids[i])
+                deltas.append(job.spec.delta)
+        return self.kv.upload_worklist(ptrs, blocks, deltas)
+
+    def restore_group(self, ticket: "LoadTicket", index: int) -> None:
+        """Finish piece ``index`` of the load: wait for its reads, then queue its copies into the
+        HBM tier and its restore launch on the current stream.  Pieces are taken in order."""
+        g = self.geo
+        l0, count = ticket.groups[index]
+        eng = self._xfer.engine
+        t0 = time.perf_counter()
+        newly_failed = False
+        for job in ticket.jobs:
+            if not job.io_dst or job.spec.chunk_key in ticket.failed:
+                continue
+            try:
+                t = job.tickets[index]
+                if t is None:
+                    raise OSError("submit failed")
+                eng.wait(t)
+            except (OSError, TimeoutError) as exc:
+                logger.warning("[CONNECTOR] load of %s failed: %s", job.spec.chunk_key, exc)
+                ticket.failed.add(job.spec.chunk_key)
+                newly_failed = True
+                for other in ticket.jobs:  # the same chunk may sit at several offsets of the request
+                    if other.spec.chunk_key == job.spec.chunk_key:
+                        self._load_errors.update(other.spec.block_ids)
+                metrics.inc("connector.load_errors")
+                # the reserved tier slots hold garbage
+                if job.kind == "host_fill":
+                    self.host.evict(job.spec.chunk_key)
+                if job.promote_from is not None:
+                    self.hbm.evict(job.spec.chunk_key)
+                for later in job.tickets[index + 1:]:
+                    try:  # its other reads still land in memory this step owns: let them finish
+                        if later is not None:
+                            eng.wait(later)
+                    except (OSError, TimeoutError):
+                        pass
+        now = time.perf_counter()
+        ticket.io_wait_ms += (now - t0) * 1e3
+        if ticket.io_bytes and index + 1 == len(ticket.groups):
+            ticket.io_span_ms = (now - ticket.t_submit) * 1e3
+        if self.kv.device_kind != "cuda":
+            jobs = [j for j in ticket.jobs if j.spec.chunk_key not in ticket.failed]
+            images = torch.empty((sum(j.n for j in jobs), g.slot_size), dtype=torch.uint8)
+            blocks: list[int] = []
+            deltas: list[int] = []
+            row = 0
+            for job in jobs:
+                for i in range(job.n):
+                    images[row] = self._image_at(job.src + i * g.slot_size)
+                    blocks.append(job.spec.block_ids[i])
+                    deltas.append(job.spec.delta)
+                    row += 1
             self.kv.restore(images, blocks, deltas)
+            return
+        if newly_failed:
+            ticket.work = self._upload(ticket)  # without the failed chunk's slots
+        layer = g.layer_size
+        for job in ticket.jobs:
+            if job.promote_from is not None and job.spec.chunk_key not in ticket.failed:
+                self.kv.copy_rows(job.src + l0 * layer, job.promote_from + l0 * layer, g.slot_size, count * layer, job.n)
+        whole = len(ticket.groups) == 1 and (l0, count) == (0, g.num_layers)
+        self.kv.restore_worklist(ticket.work, 0 if whole else l0, 0 if whole else count)
+
+    def end_load(self, ticket: "LoadTicket", wait: bool = False, close_step: bool = True) -> None:
+        """Every piece has been queued.  ``wait`` blocks until the kernels have run and raises on a
+        kernel-reported error; without it the caller orders later work behind the current stream
+        and checks :meth:`check_load_status` when it next synchronises anyway."""
+        self.last_load_bytes, self.last_load_io_ms = ticket.io_bytes, ticket.io_wait_ms
+        if ticket.io_bytes:
+            _perf.record("load_io_ms", ticket.io_wait_ms, "ms")
+            metrics.inc("connector.bytes_loaded", ticket.io_bytes)
+        if self.kv.device_kind == "cuda":
+            if self._load_done is None:
+                self._load_done = torch.cuda.Event()
+            self._load_done.record()
+            if wait:
+                self._load_done.synchronize()
+                self.kv.check_status()
+        if close_step:
+            for tier in (self.hbm, self.host):
+                if tier is not None:
+                    tier.end_step()
+
+    def check_load_status(self) -> None:
+        if self.kv.device_kind == "cuda":
+            self.kv.check_status()
 
     def _image_at(self, ptr: int) -> torch.Tensor:
         """CPU path: the slot image at host address ``ptr`` (staging or host tier)."""

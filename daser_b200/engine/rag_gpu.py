@@ -11,12 +11,24 @@ The reference relies on a separately launched ``vllm serve`` for this part
   plus the query, sample the first token); otherwise all running sequences decode one token
   as a batch.
 
-With ``tp > 1`` every rank runs the same engine object in lock step; rank 0 additionally
-owns the scheduler half and broadcasts each step's plan.
+A TTFT step is pipelined by layer group (``GpuModelRunner.layer_groups``): the storage reads of
+every cold chunk are issued at once, group-major; restore piece ``g`` (its copies into the HBM
+tier and its fused kernel) runs on a side stream as soon as the reads of its layers are in, and
+the model's layers of group ``g`` are launched behind it.  Reading layers 10.. from the drive
+overlaps restoring and computing layers 0..9, and a step whose chunks are all in memory tiers
+waits for the first piece only.
+
+With ``tp > 1`` every rank runs the same engine object in lock step.  Rank 0 owns the scheduler
+half and publishes each step's plan through a shared-memory mailbox.  Every rank owns the
+chunks whose key hashes to it: it keeps them in its own HBM and host tiers, reads them from the
+store with its own IO ring over its own PCIe link, and its restore kernel scatters each head
+slice into every rank's paged pool over NVLink; a per-source flag per layer group, written
+behind the kernel and awaited (bounded) in front of each rank's layers, replaces a barrier.
 """
 
 from __future__ import annotations
 
+import contextlib
 import time
 from typing import Optional, Sequence
 
@@ -41,7 +53,7 @@ class GpuRagEngine(SchedulingMixin):
                  io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
                  staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True,
-                 compose_after: int = 0, repair_tokens: int = 0) -> None:
+                 compose_after: int = 0, repair_tokens: int = 0, layer_groups: int = 8) -> None:
         self.cfg = cfg
         # > 0: after a chunk was restored behind other context, its first `repair_tokens` tokens are
         # recomputed in place with attention over everything before them (the tokens whose stored KV
@@ -61,7 +73,7 @@ class GpuRagEngine(SchedulingMixin):
         if self.weights.gate_up_block == 0 and self.weights.inter_local % gemm_ops.GATE_UP_BLOCK == 0:
             self.weights.interleave_gate_up_(gemm_ops.GATE_UP_BLOCK)
         self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device,
-                                     max_blocks=max_blocks, use_graphs=use_graphs)
+                                     max_blocks=max_blocks, use_graphs=use_graphs, layer_groups=layer_groups)
         self.blocks = BlockAllocator(num_blocks)
         self.max_blocks_per_seq = max_blocks  # the runner's block tables are this wide
         self.geo = self.runner.geo
@@ -70,21 +82,22 @@ class GpuRagEngine(SchedulingMixin):
         self.kv_backend = CudaKVBackend(self.geo, pool, cfg.inv_freq(), max_pos=self.runner.cos_sin.shape[0],
                                         rank=self.rank, max_slots=max(staging_slots, 1024), device=self.device)
         self.kv_backend.cos_sin = self.runner.cos_sin
+        # tiers and IO are per rank: `hbm_slots` / `host_slots` are this rank's share
         self.hbm = HBMStore(self.geo.slot_size, hbm_slots, self.device) if hbm_slots > 0 else None
-        self.host = (
-            HBMStore(self.geo.slot_size, host_slots, torch.device("cpu")) if host_slots > 0 and self.rank == 0 else None
-        )
-        self.is_io_rank = self.rank == 0
+        self.host = HBMStore(self.geo.slot_size, host_slots, torch.device("cpu")) if host_slots > 0 else None
         self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id) if self.rank == 0 else None
-        self.worker = (
-            WorkerHalf(socket_path, store_path, self.geo, self.kv_backend, io_backend=io_backend, tp=self.tp,
-                       rank=self.rank, hbm_store=self.hbm, host_store=self.host, staging_slots=staging_slots)
-            if self.is_io_rank else None
-        )
+        if self.tp > 1 and self.rank != 0:
+            tp_ctx.wait_for_path(store_path)  # rank 0 creates the store file
+        self.worker = WorkerHalf(socket_path, store_path, self.geo, self.kv_backend, io_backend=io_backend, tp=self.tp,
+                                 rank=self.rank, hbm_store=self.hbm, host_store=self.host, staging_slots=staging_slots)
         self.waiting: list[RagRequest] = []
         self.running: list[RagRequest] = []
         self._n = 0
         self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        self._restore_stream = torch.cuda.Stream(device=self.device)
+        self._group_ev = [torch.cuda.Event() for _ in self.runner.layer_groups]
+        self._kv_epoch = 0  # restore pieces signalled so far (the same on every rank)
+        self.h2d_bytes = 0  # host -> device bytes of the steps so far (inputs, work lists, tier promotions)
 
     # ------------------------------------------------------------------------------------------
     def _next_id(self) -> str:
@@ -98,17 +111,23 @@ class GpuRagEngine(SchedulingMixin):
     def _bcast(self, obj):
         return self.tp_ctx.broadcast_object(obj) if self.tp_ctx is not None else obj
 
+    def owner_of(self, chunk_key: str) -> int:
+        """The rank that keeps ``chunk_key`` in its tiers and moves it between the store and the pools."""
+        return int(chunk_key[:8], 16) % self.tp if self.tp > 1 else 0
+
     def _prefill_tokens(self, tokens: Sequence[int], start_pos: int, table: list[int],
-                        sample: Optional[dict] = None) -> torch.Tensor:
+                        sample: Optional[dict] = None, gate=None) -> torch.Tensor:
         """Run ``tokens`` through the model in pieces of at most ``max_tokens``; returns the last sample
-        (greedy, or drawn with ``sample = {"temperature", "seed"}``)."""
+        (greedy, or drawn with ``sample = {"temperature", "seed"}``).  ``gate`` (see
+        ``GpuModelRunner.forward``) applies to the first piece."""
         out = None
         mt = self.runner.max_tokens
         for i in range(0, len(tokens), mt):
             piece = list(tokens[i : i + mt])
             inp = self.runner.stage_inputs([{"tokens": piece, "start_pos": start_pos + i, "block_table": table,
                                              **(sample or {})}])
-            out = self.runner.forward(inp)
+            self.h2d_bytes += self.runner.h2d_bytes
+            out = self.runner.forward(inp, gate=gate if i == 0 else None)
         return out
 
     def warm_up(self, token_counts: Sequence[int] = (64,), context_lens: Sequence[int] = (2048, 4096, 8192)) -> None:
@@ -161,14 +180,41 @@ class GpuRagEngine(SchedulingMixin):
             return
         self.tp_ctx.save_step(self, meta)
 
-    def _restore(self, meta: ConnectorMeta) -> None:
-        if self.worker is not None:
-            self.worker.bind_connector_metadata(meta)
-            try:
-                self.worker.start_load_kv()
-            finally:
-                self.worker.clear_connector_metadata()
-        self._sync_ranks()  # peers' pools were written by the IO rank
+    def _begin_restore(self, meta: ConnectorMeta):
+        """Issue this rank's share of the step's loads; returns ``(ticket, gate)`` for the first
+        forward of the step (``gate`` is None when no rank restores anything)."""
+        loads = list(meta.reqs_to_load)
+        if not loads:
+            return None, None
+        mine = ConnectorMeta(reqs_to_load=[s for s in loads if self.owner_of(s.chunk_key) == self.rank])
+        groups = self.runner.layer_groups
+        ticket = self.worker.begin_load(mine, groups) if mine.reqs_to_load else None
+        side = self._restore_stream
+        base = self._kv_epoch
+        self._kv_epoch += len(groups)
+        tp = self.tp_ctx
+
+        def on_side():
+            return torch.cuda.stream(side) if side is not None else contextlib.nullcontext()
+
+        def gate(g: int) -> None:
+            # piece g: wait for its reads (host), queue its copies and kernel on the side stream
+            with on_side():
+                if ticket is not None:
+                    self.worker.restore_group(ticket, g)
+                if tp is not None:
+                    tp.signal_kv_landed(base + g + 1)  # behind this rank's scatter into every pool
+                if side is not None:
+                    self._group_ev[g].record(side)
+            if side is not None:
+                torch.cuda.current_stream().wait_event(self._group_ev[g])
+            if tp is not None:
+                tp.wait_kv_landed(base + g + 1, self.runner.status)  # every rank's piece g is in this pool
+            if g + 1 == len(groups) and ticket is not None:
+                with on_side():
+                    self.worker.end_load(ticket)
+
+        return ticket, gate
 
     # -- online ---------------------------------------------------------------------------------------
     def submit(self, req: RagRequest) -> RagRequest:
@@ -198,6 +244,7 @@ class GpuRagEngine(SchedulingMixin):
         cfg, bt = self.cfg, self.cfg.block_tokens
         t_start = time.perf_counter()
         self._ev[0].record()
+        h2d0 = self.h2d_bytes + self.kv_backend.h2d_bytes
         offsets, pos = [], 0
         for c in req.chunks:
             if len(c) % bt:
@@ -216,51 +263,72 @@ class GpuRagEngine(SchedulingMixin):
             plan = (self.sched.build_connector_meta([req.req_id]), [s is not None for s in specs])
         meta, found = self._bcast(plan)
         t_plan = time.perf_counter()
-        # 2. restore cached chunks (IO + one fused kernel)
+        # 2. start restoring the cached chunks: reads go out now, the pieces follow group by group
+        #    in front of the first forward below
         self._ev[1].record()
-        self._restore(meta)
-        self._ev[2].record()
+        ticket, gate = self._begin_restore(meta)
         t_restore = time.perf_counter()
-        failed_blocks = self.worker.take_load_errors() if self.worker is not None else set()
-        failed_blocks = self._bcast(failed_blocks)
-        # 3. compute what was not restored, then the query
-        ctx = 0
-        first = None
+        sample = ({"temperature": req.temperature, "seed": req.step_seed(), "top_k": req.top_k, "top_p": req.top_p}
+                  if req.temperature > 0 else None)
+
+        def compute(failed_blocks: set, gate) -> torch.Tensor:
+            """Prefill whatever is not (validly) restored, then the query; returns the sampled token."""
+            ctx = 0
+            for c, off, ok in zip(req.chunks, offsets, found):
+                blocks_of_chunk = set(req.block_table[off // bt : (off + len(c)) // bt])
+                if not ok or (blocks_of_chunk & failed_blocks):
+                    self._prefill_tokens(c, off, req.block_table, gate=gate)
+                    gate = None
+                    if req.store_misses and not ok:
+                        if off == 0:
+                            self._store_in_place(req, c, off)  # saw no context: this IS the chunk's own KV
+                        elif c not in standalone:
+                            standalone.append(c)
+                    if ok and failed_blocks:  # counted as restored by the first pass
+                        req.restored_chunks -= 1
+                        req.restored_bytes -= (len(c) // bt) * self.geo.slot_size
+                elif not failed_blocks:
+                    req.restored_chunks += 1
+                    req.restored_bytes += (len(c) // bt) * self.geo.slot_size
+                    if self.repair_tokens > 0 and off > 0:
+                        self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table, gate=gate)
+                        gate = None
+                ctx = off + len(c)
+            return self._prefill_tokens(req.query, ctx, req.block_table, sample, gate=gate)
+
         # A missed chunk behind other context was just computed attending to that context; the
         # store keeps chunks under a key of their own tokens only, so what is stored must be the
         # chunk computed alone (as `store_chunk` does).  Those are recomputed after the first
         # token has gone out, between steps.
         standalone: list[Sequence[int]] = []
-        for c, off, ok in zip(req.chunks, offsets, found):
-            blocks_of_chunk = set(req.block_table[off // bt : (off + len(c)) // bt])
-            if not ok or (blocks_of_chunk & failed_blocks):
-                self._prefill_tokens(c, off, req.block_table)
-                if req.store_misses and not ok:
-                    if off == 0:
-                        self._store_in_place(req, c, off)  # saw no context: this IS the chunk's own KV
-                    else:
-                        standalone.append(c)
-            else:
-                req.restored_chunks += 1
-                req.restored_bytes += (len(c) // bt) * self.geo.slot_size
-                if self.repair_tokens > 0 and off > 0:
-                    self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table)
-            ctx = off + len(c)
-        sample = ({"temperature": req.temperature, "seed": req.step_seed(), "top_k": req.top_k, "top_p": req.top_p}
-                  if req.temperature > 0 else None)
-        first = self._prefill_tokens(req.query, ctx, req.block_table, sample)
+        # 3. compute what was not restored, then the query
+        first = compute(set(), gate)
+        if self._restore_stream is not None:
+            self._ev[2].record(self._restore_stream)
+        # a load that failed on any rank (rare): recompute those chunks and the query once more
+        failed_blocks = self.worker.take_load_errors()
+        if self.tp_ctx is not None and meta.reqs_to_load:
+            failed_blocks = set().union(*self.tp_ctx.gather_object(sorted(failed_blocks)))
+        if failed_blocks:
+            first = compute(set(failed_blocks), None)
         self._ev[3].record()
         token = int(first[0].item())  # device -> host read of the step's result
         t_end = time.perf_counter()
+        self.worker.check_load_status()
         req.generated.append(token)
         req.context_len = total
         req.ttft_ms = (t_end - t_start) * 1e3
+        req.first_token_time = t_end
         req.ttft_device_ms = self._ev[0].elapsed_time(self._ev[3])
         req.timings = {
             "plan_ms": (t_plan - t_start) * 1e3,
-            "restore_ms": (t_restore - t_plan) * 1e3,
-            "restore_device_ms": self._ev[1].elapsed_time(self._ev[2]),
+            "restore_ms": (t_restore - t_plan) * 1e3,  # host time to issue the loads (the pieces overlap the forward)
+            "restore_device_ms": (self._ev[1].elapsed_time(self._ev[2])
+                                  if ticket is not None and self._restore_stream is not None else 0.0),
             "compute_ms": (t_end - t_restore) * 1e3,
+            "io_wait_ms": ticket.io_wait_ms if ticket is not None else 0.0,
+            "io_bytes": ticket.io_bytes if ticket is not None else 0,
+            "h2d_bytes": self.h2d_bytes + self.kv_backend.h2d_bytes - h2d0,
         }
         metrics.observe("engine.ttft_ms", req.ttft_ms)
         if self.sched is not None:
@@ -294,6 +362,7 @@ class GpuRagEngine(SchedulingMixin):
                  "block_table": r.block_table, "temperature": r.temperature, "seed": r.step_seed(),
                  "top_k": r.top_k, "top_p": r.top_p} for r in batch]
         inp = self.runner.stage_inputs(seqs)
+        self.h2d_bytes += self.runner.h2d_bytes
         out = self.runner.forward(inp).tolist()
         for r, tok in zip(batch, out):
             r.generated.append(int(tok))

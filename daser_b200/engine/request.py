@@ -19,6 +19,7 @@ class RagRequest:
     context_len: int = 0
     ttft_ms: float = 0.0
     ttft_device_ms: float = 0.0
+    first_token_time: float = 0.0  # time.perf_counter() when the first token was read back
     restored_chunks: int = 0
     restored_bytes: int = 0
     timings: dict = field(default_factory=dict)

@@ -57,10 +57,22 @@ class StepInputs:
     truncation: Optional[tuple] = None
 
 
+def split_layers(num_layers: int, parts: int) -> list[tuple[int, int]]:
+    """``num_layers`` cut into at most ``parts`` consecutive runs of near-equal length."""
+    parts = max(1, min(int(parts), num_layers))
+    base, extra = divmod(num_layers, parts)
+    out, first = [], 0
+    for i in range(parts):
+        n = base + (1 if i < extra else 0)
+        out.append((first, n))
+        first += n
+    return out
+
+
 class GpuModelRunner:
     def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, num_blocks: int, max_tokens: int = 256,
                  max_seqs: int = 64, tp_ctx=None, device: Optional[torch.device] = None,
-                 max_blocks: int = 512, use_graphs: bool = True) -> None:
+                 max_blocks: int = 512, use_graphs: bool = True, layer_groups: int = 8) -> None:
         self.cfg = cfg
         self.w = weights
         self.tp = weights.tp
@@ -131,6 +143,8 @@ class GpuModelRunner:
         self.use_graphs = use_graphs
         self._graphs: dict[tuple, Any] = {}
         self._seen: dict[tuple, int] = {}
+        # consecutive runs of layers a step is launched in (see `forward`): [(first layer, count)]
+        self.layer_groups = split_layers(cfg.num_layers, layer_groups)
 
     # -- helpers ---------------------------------------------------------------------------------
     def _linear(self, x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, out_bf: torch.Tensor):
@@ -220,13 +234,18 @@ class GpuModelRunner:
 
     # -- one step -----------------------------------------------------------------------------------
     @torch.no_grad()
-    def forward(self, inp: StepInputs) -> torch.Tensor:
+    def forward(self, inp: StepInputs, gate=None) -> torch.Tensor:
         """Run the model on the step's tokens; returns the greedy next token of every sequence
         (int32 ``[num_seqs]``, on the device).
 
-        The layer loop of a step shape seen before is replayed from a CUDA graph (captured on
-        the second occurrence): a forward is several hundred short kernels and the host
-        would otherwise be the bottleneck at small token counts.
+        The layers run in ``self.layer_groups`` consecutive groups.  ``gate(g)``, if given, is
+        called on the host right before group ``g`` is launched and queues on the current stream
+        whatever that group has to wait for: this is how a chunk restore that is still reading
+        layers 10.. from storage lets layers 0..9 start (``GpuRagEngine._ttft_step``).
+
+        Each group of a step shape seen before is replayed from a CUDA graph (captured on the
+        second occurrence): a forward is several hundred short kernels and the host would
+        otherwise be the bottleneck at small token counts.
         """
         T = inp.num_tokens
         if T > self.max_tokens or inp.num_seqs > self.max_seqs:
@@ -235,41 +254,49 @@ class GpuModelRunner:
         ctx_bucket = max(2048, 1 << (max(inp.max_ctx, 1) - 1).bit_length())  # powers of two: few graph shapes
         nsplit, split_tokens = attention.plan_splits(inp.num_seqs, self.hkv, inp.max_q_len, group, ctx_bucket,
                                                      self.cfg.block_tokens, rows=T * self.hq)
-        body = self._body if self.tp == 1 else (lambda i, a, b: self.tp_ctx.forward_body(self, i, a, b))
-        key = (T, inp.num_seqs, inp.max_q_len, nsplit, split_tokens)
-        if not (self.use_graphs and inp.persistent):
-            body(inp, nsplit, split_tokens)
-        elif key in self._graphs:
-            graph, n_kernels = self._graphs[key]
-            graph.replay()
-            _lib.launch_count += n_kernels  # kernels of ours that the replay launched
-        else:
-            seen = self._seen.get(key, 0)
-            self._seen[key] = seen + 1
-            if seen == 0 or len(self._graphs) >= 64:
-                body(inp, nsplit, split_tokens)  # first sight: eager (also loads every kernel)
+        body = self._body if self.tp == 1 else (lambda *a: self.tp_ctx.forward_body(self, *a))
+        shape = (T, inp.num_seqs, inp.max_q_len, nsplit, split_tokens)
+        graphs_ok = self.use_graphs and inp.persistent
+        seen = self._seen.get(shape, 0)
+        self._seen[shape] = seen + 1
+        for g, (l0, count) in enumerate(self.layer_groups):
+            if gate is not None:
+                gate(g)
+            key = shape + (g,)
+            if not graphs_ok:
+                body(inp, nsplit, split_tokens, l0, l0 + count)
+            elif key in self._graphs:
+                graph, n_kernels = self._graphs[key]
+                graph.replay()
+                _lib.launch_count += n_kernels  # kernels of ours that the replay launched
+            elif seen == 0 or len(self._graphs) >= 64 * len(self.layer_groups):
+                body(inp, nsplit, split_tokens, l0, l0 + count)  # first sight: eager (also loads every kernel)
             else:
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 before = _lib.launch_count
                 with torch.cuda.graph(graph):
-                    body(inp, nsplit, split_tokens)
+                    body(inp, nsplit, split_tokens, l0, l0 + count)
                 self._graphs[key] = (graph, _lib.launch_count - before)
                 graph.replay()
         if self.tp > 1:
             return self.tp_ctx.sample(self, inp)
         return self.sample(self.normed[:T], inp)
 
-    def _body(self, inp: StepInputs, nsplit: int, split_tokens: int) -> None:
-        """Embedding, all layers and the final norm on one GPU; leaves ``self.normed`` ready to sample."""
+    def _body(self, inp: StepInputs, nsplit: int, split_tokens: int, l0: int = 0, l1: Optional[int] = None) -> None:
+        """Layers ``[l0, l1)`` on one GPU (the embedding in front of layer 0, the final norm behind
+        the last layer); leaves ``self.normed`` ready for the next group or for sampling."""
         cfg, w = self.cfg, self.w
+        l1 = len(w.layers) if l1 is None else l1
         T = inp.num_tokens
         D, B = cfg.head_dim, cfg.block_tokens
         h = self.h[:T]
         normed = self.normed[:T]
-        ew.embedding(inp.tokens, w.embed, out=h)
-        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
-        for li, lw in enumerate(w.layers):
+        if l0 == 0:
+            ew.embedding(inp.tokens, w.embed, out=h)
+            ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li in range(l0, l1):
+            lw = w.layers[li]
             qkv, f32 = self._linear(normed, lw.wqkv, self.qkv_acc, self.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq,
                              self.hkv, D, B, self.local_pool, li, 0, zero_after=f32, qk_norm=self.qk_norm(lw))

@@ -470,37 +470,48 @@ int64_t daser_io_register_buffers(daser_io* io, void* const* bufs, const int64_t
 }
 int64_t daser_io_file_size(const daser_io* io) { return io ? io->file_size : -1; }
 
-int64_t daser_io_submit(daser_io* io, int is_write, void* buf, int device, int64_t file_offset, int64_t nbytes) {
-  if (!io || !buf || file_offset < 0 || nbytes <= 0) return -EINVAL;
+int64_t daser_io_submit_strided(daser_io* io, int is_write, void* buf, int device, int64_t file_offset,
+                                int64_t nbytes, int count, int64_t stride) {
+  if (!io || !buf || file_offset < 0 || nbytes <= 0 || count <= 0 || (count > 1 && stride < nbytes)) return -EINVAL;
   if (device && io->backend != DASER_IO_GDS) return -ENOTSUP;
-  const int npieces = (int)((nbytes + kPieceBytes - 1) / kPieceBytes);
+  const int per_extent = (int)((nbytes + kPieceBytes - 1) / kPieceBytes);
+  const int64_t npieces = (int64_t)per_extent * count;
+  if (npieces > (1 << 24)) return -EINVAL;
   int64_t ticket;
   {
     std::lock_guard<std::mutex> g(io->mu);
     if (io->closing) return -ESHUTDOWN;
     ticket = io->next_ticket++;
-    io->tickets[ticket].pending = npieces;
+    io->tickets[ticket].pending = (int)npieces;
   }
   io->st_pieces += npieces;
-  for (int i = 0; i < npieces; ++i) {
-    Piece p;
-    p.ticket = ticket;
-    p.write = is_write != 0;
-    p.device = device != 0;
-    p.buf = (char*)buf + (int64_t)i * kPieceBytes;
-    p.off = file_offset + (int64_t)i * kPieceBytes;
-    p.len = nbytes - (int64_t)i * kPieceBytes < kPieceBytes ? nbytes - (int64_t)i * kPieceBytes : kPieceBytes;
-    if (io->backend == DASER_IO_URING) {
-      io->ring_enqueue(new Piece(p));
-    } else {
-      {
-        std::lock_guard<std::mutex> g(io->mu);
-        io->queue.push_back(p);
+  for (int e = 0; e < count; ++e) {
+    char* ebuf = (char*)buf + (int64_t)e * stride;
+    const int64_t eoff = file_offset + (int64_t)e * stride;
+    for (int i = 0; i < per_extent; ++i) {
+      Piece p;
+      p.ticket = ticket;
+      p.write = is_write != 0;
+      p.device = device != 0;
+      p.buf = ebuf + (int64_t)i * kPieceBytes;
+      p.off = eoff + (int64_t)i * kPieceBytes;
+      p.len = nbytes - (int64_t)i * kPieceBytes < kPieceBytes ? nbytes - (int64_t)i * kPieceBytes : kPieceBytes;
+      if (io->backend == DASER_IO_URING) {
+        io->ring_enqueue(new Piece(p));
+      } else {
+        {
+          std::lock_guard<std::mutex> g(io->mu);
+          io->queue.push_back(p);
+        }
+        io->queue_cv.notify_one();
       }
-      io->queue_cv.notify_one();
     }
   }
   return ticket;
+}
+
+int64_t daser_io_submit(daser_io* io, int is_write, void* buf, int device, int64_t file_offset, int64_t nbytes) {
+  return daser_io_submit_strided(io, is_write, buf, device, file_offset, nbytes, 1, 0);
 }
 
 int daser_io_wait(daser_io* io, int64_t ticket, int timeout_ms) {

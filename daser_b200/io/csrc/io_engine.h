@@ -51,6 +51,12 @@ DASER_IO_API int64_t daser_io_fixed_pieces(const daser_io* io);
 DASER_IO_API int64_t daser_io_file_size(const daser_io* io);
 
 // `device` != 0: buf is a CUDA device pointer (GDS backend only).
+// `count` extents of `nbytes` each under ONE ticket: extent i moves file bytes
+// [file_offset + i * stride, + nbytes) to or from buf + i * stride (the same stride on both
+// sides: a run of equally spaced slices of a larger image, e.g. some layers of every slot of a
+// chunk).  Completes when every extent has; the first error wins.
+DASER_IO_API int64_t daser_io_submit_strided(daser_io* io, int is_write, void* buf, int device, int64_t file_offset,
+                                             int64_t nbytes, int count, int64_t stride);
 DASER_IO_API int64_t daser_io_submit(daser_io* io, int is_write, void* buf, int device, int64_t file_offset,
                                      int64_t nbytes);
 DASER_IO_API int daser_io_wait(daser_io* io, int64_t ticket, int timeout_ms);

@@ -39,6 +39,9 @@ def lib() -> C.CDLL:
         L.daser_io_file_size.argtypes = [C.c_void_p]
         L.daser_io_submit.restype = C.c_int64
         L.daser_io_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64]
+        L.daser_io_submit_strided.restype = C.c_int64
+        L.daser_io_submit_strided.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
+                                              C.c_int, C.c_int64]
         L.daser_io_wait.argtypes = [C.c_void_p, C.c_int64, C.c_int]
         L.daser_io_close.argtypes = [C.c_void_p]
         L.daser_io_preallocate.argtypes = [C.c_char_p, C.c_int64]
@@ -96,6 +99,17 @@ class IOEngine:
 
     def submit_write(self, ptr: int, offset: int, nbytes: int, device: bool = False) -> int:
         return self._submit(True, ptr, device, offset, nbytes)
+
+    def submit_read_strided(self, ptr: int, offset: int, nbytes: int, count: int, stride: int,
+                            device: bool = False) -> int:
+        """``count`` reads of ``nbytes`` under one ticket: read i fills ``ptr + i * stride`` from file
+        offset ``offset + i * stride`` (equally spaced slices of a larger image)."""
+        if self._h is None:
+            raise ValueError("engine is closed")
+        t = lib().daser_io_submit_strided(self._h, 0, C.c_void_p(ptr), int(device), offset, nbytes, count, stride)
+        if t < 0:
+            raise OSError(-t, os.strerror(-t))
+        return t
 
     def wait(self, ticket: int, timeout_s: Optional[float] = 120.0) -> None:
         ms = -1 if timeout_s is None else int(timeout_s * 1000)

@@ -56,6 +56,10 @@ class KVJob(C.Structure):
         ("rank", C.c_int32),
         ("layer_begin", C.c_int32),
         ("layer_count", C.c_int32),
+        ("lg_heads", C.c_int32),
+        ("lg_tokens", C.c_int32),
+        ("lg_groups", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

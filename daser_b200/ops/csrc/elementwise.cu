@@ -218,6 +218,18 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int n, uint32_t target,
   }
 }
 
+// One thread per target: make everything this stream wrote before (peer memory included) visible
+// system-wide, then publish `value` in the target's flag.  The flags of one writer only ever grow.
+struct SignalTargets {
+  uint32_t* flag[DASER_MAX_RANKS];
+};
+__global__ void signal_flags_kernel(SignalTargets targets, int n, uint32_t value) {
+  const int i = threadIdx.x;
+  if (i >= n || targets.flag[i] == nullptr) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(targets.flag[i]), "r"(value) : "memory");
+}
+
 // RoPE on q and k, then k/v into the paged pool.  qkv row = [Hq*D | Hkv*D | Hkv*D].
 // slot_mapping[t] = block * block_tokens + offset inside the block, or < 0 to skip the write.
 // QKNORM (Qwen3 family): every query and key head is RMS-normalised over head_dim and scaled by
@@ -517,6 +529,16 @@ DASER_API int daser_wait_flags(const uint32_t* flags, int n, uint32_t target, co
                                uint32_t* status, cudaStream_t stream) {
   if (!flags || n <= 0) return DASER_ERR_BAD_ARG;
   daser::wait_flags_kernel<<<1, 1, 0, stream>>>(flags, n, target, base, status);
+  return (int)cudaGetLastError();
+}
+
+// flags[i] <- value for i < n (each possibly in a peer's memory), ordered after all earlier work
+// of the stream: "what I wrote for you has landed".
+DASER_API int daser_signal_flags(const uint64_t* flag_ptrs, int n, uint32_t value, cudaStream_t stream) {
+  if (!flag_ptrs || n <= 0 || n > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
+  daser::SignalTargets t;
+  for (int i = 0; i < DASER_MAX_RANKS; ++i) t.flag[i] = i < n ? reinterpret_cast<uint32_t*>(flag_ptrs[i]) : nullptr;
+  daser::signal_flags_kernel<<<1, 32, 0, stream>>>(t, n, value);
   return (int)cudaGetLastError();
 }
 

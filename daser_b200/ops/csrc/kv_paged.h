@@ -50,4 +50,8 @@ typedef struct {
   int32_t rank;              // save only: whose heads this launch writes
   int32_t layer_begin;       // restore only: first layer this launch covers
   int32_t layer_count;       // restore only: how many layers from layer_begin (0 = all of them)
+  int32_t lg_heads;          // filled in by the launcher: log2 of num_kv_heads, block_tokens and
+  int32_t lg_tokens;         //   head_dim / 16 when all three are powers of two (the kernels then
+  int32_t lg_groups;         //   index with shifts), else -1
+  int32_t reserved;
 } DaserKVJob;

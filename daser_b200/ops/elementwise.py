@@ -39,6 +39,15 @@ def wait_flags(flags_ptr: int, n: int, target: int, status: Optional[torch.Tenso
     )
 
 
+def signal_flags(flag_ptrs: Sequence[int], value: int, stream=None) -> None:
+    """Stream-ordered: after everything queued before it (stores into peers' memory included) is
+    visible system-wide, write ``value`` into each of ``flag_ptrs`` (device addresses, possibly in
+    peers' memory).  The counterpart of :func:`wait_flags`."""
+    arr = (C.c_uint64 * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
+    _lib.check(_lib.lib().daser_signal_flags(arr, len(flag_ptrs), C.c_uint32(value & 0xFFFFFFFF),
+                                             _lib.stream_ptr(stream)), "signal_flags")
+
+
 def advance_epochs(epochs: torch.Tensor, d0: int, d1: int, d2: int) -> None:
     """``epochs[0:3] += (d0, d1, d2)`` on the stream (see ``parallel/tp.py``)."""
     _lib.check(

@@ -151,9 +151,15 @@ def _job(work, geo, image_is_fp8, cos_sin, status, rank=0) -> KVJob:
 
 
 def kv_restore(work: KVWorkList, geo, pool: PagedKVPool, cos_sin: Optional[torch.Tensor],
-               status: Optional[torch.Tensor] = None, stream=None) -> None:
-    """Slot images -> paged pools of every rank: dequantise, rotate keys by ``deltas``, scatter."""
+               status: Optional[torch.Tensor] = None, stream=None, layer_begin: int = 0,
+               layer_count: int = 0) -> None:
+    """Slot images -> paged pools of every rank: dequantise, rotate keys by ``deltas``, scatter.
+
+    ``layer_begin`` / ``layer_count`` restrict the launch to a range of layers (0 = through the
+    last one): a restore can then run group by group while the storage reads of later layers
+    are still in flight and the model already computes on the earlier ones."""
     job = _job(work, geo, geo.codec == "fp8b16", cos_sin, status)
+    job.layer_begin, job.layer_count = int(layer_begin), int(layer_count)
     pool_c = pool.c_struct()
     _lib.check(_lib.lib().daser_kv_restore(C.byref(job), C.byref(pool_c), _lib.stream_ptr(stream)), "kv_restore")
 
@@ -164,6 +170,15 @@ def kv_save(work: KVWorkList, geo, pool: PagedKVPool, rank: int = 0,
     job = _job(work, geo, geo.codec == "fp8b16", None, status, rank)
     pool_c = pool.c_struct()
     _lib.check(_lib.lib().daser_kv_save(C.byref(job), C.byref(pool_c), _lib.stream_ptr(stream)), "kv_save")
+
+
+def copy_rows(dst_ptr: int, src_ptr: int, pitch: int, width: int, rows: int, stream=None) -> None:
+    """``rows`` runs of ``width`` bytes, ``pitch`` bytes apart on both sides, copied by the copy
+    engine on ``stream`` (either side may be pinned host or device memory)."""
+    code = _lib.lib().daser_copy_rows(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), C.c_int64(pitch), C.c_int64(width),
+                                      C.c_int64(rows), _lib.stream_ptr(stream))
+    if code != 0:
+        raise _lib.KernelError(f"copy_rows: CUDA error {code}" if code > 0 else "copy_rows: bad argument")
 
 
 def rope_table(max_pos: int, inv_freq, device) -> torch.Tensor:

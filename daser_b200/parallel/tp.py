@@ -47,6 +47,7 @@ import torch.distributed as dist
 from daser_b200.models.llama import LlamaConfig
 from daser_b200.ops import attention, elementwise as ew, gemm, kv_ops
 from daser_b200.parallel.health import PeerMonitor
+from daser_b200.parallel.mailbox import open_mailbox
 
 FLAG_RS = 0  # arrival counter of reduce-scattered partials
 FLAG_OS = 1  # and 2: arrival counters of the two one-shot all-reduce receive buffers
@@ -57,7 +58,8 @@ FLAG_OS = 1  # and 2: arrival counters of the two one-shot all-reduce receive bu
 ONESHOT_MAX_TP = 2
 FLAG_NV = 3  # and 4: arrival counters of the two in-switch all-reduce buffers
 FLAG_AG = 8  # first of tp per-source "rows landed" flags
-NUM_FLAGS = 16
+FLAG_KV = 16  # first of tp per-source "restore pieces landed in your pool" counters
+NUM_FLAGS = 24
 IMPLS = ("fused", "twoshot", "oneshot", "nvls", "nccl")
 
 
@@ -135,11 +137,15 @@ class TPContext:
                     raise RuntimeError("no NVLink multicast mapping for the symmetric buffers (NVLS unavailable)")
                 self.nv_buf, self.nv_mc = [], []
         self.save_staging: Optional[torch.Tensor] = None
+        self._mail_timeout = float(os.environ.get("DASER_TP_MAIL_TIMEOUT", "120"))
+        self.mailbox = None
         self.health: Optional[PeerMonitor] = None
         if os.environ.get("DASER_TP_HEALTH", "1") != "0":
             store = dist.distributed_c10d._get_default_store()
             self.health = PeerMonitor(dist.PrefixStore(f"daser/{self.group_name}", store), self.rank, self.tp,
                                       timeout_s=float(os.environ.get("DASER_TP_HEALTH_TIMEOUT", "10")))
+        # per-step control messages (plans, load-error reports) go through shared memory, not gloo
+        self.mailbox = open_mailbox(self.rank, self.tp, self._broadcast_gloo)
         torch.cuda.synchronize()
         self.barrier()
 
@@ -175,11 +181,50 @@ class TPContext:
     def close(self) -> None:
         if self.health is not None:
             self.health.close()
+        if self.mailbox is not None:
+            self.mailbox.close()
+            self.mailbox = None
 
-    def broadcast_object(self, obj: Any, src: int = 0) -> Any:
+    def _broadcast_gloo(self, obj: Any, src: int = 0) -> Any:
         box = [obj]
         dist.broadcast_object_list(box, src=src, group=self._cpu_group)
         return box[0]
+
+    def broadcast_object(self, obj: Any, src: int = 0) -> Any:
+        """``obj`` of rank ``src`` on every rank.  Through the shared-memory mailbox (microseconds);
+        a peer that stops publishing surfaces as :class:`~daser_b200.parallel.health.PeerLost` or a
+        time-out instead of a hung collective."""
+        if self.mailbox is None:
+            return self._broadcast_gloo(obj, src)
+        return self.mailbox.broadcast(obj, src, timeout_s=self._mail_timeout, on_wait=self.check_peers)
+
+    def gather_object(self, obj: Any) -> list:
+        """Every rank's ``obj`` in rank order, on every rank."""
+        if self.mailbox is None:
+            out: list = [None] * self.tp
+            dist.all_gather_object(out, obj, group=self._cpu_group)
+            return out
+        return self.mailbox.gather(obj, timeout_s=self._mail_timeout, on_wait=self.check_peers)
+
+    def wait_for_path(self, path: str, timeout_s: float = 60.0) -> None:
+        """Block until ``path`` exists (a file another rank creates)."""
+        import time
+
+        t0 = time.time()
+        while not os.path.exists(path):
+            if time.time() - t0 > timeout_s:
+                raise TimeoutError(f"{path} did not appear")
+            time.sleep(0.01)
+
+    # -- restore hand-shake: "my scatter into your pool has landed" -------------------------------
+    def signal_kv_landed(self, value: int) -> None:
+        """On the current stream, behind this rank's restore kernel: publish ``value`` (a count of
+        finished restore pieces that only grows) in this rank's slot of every rank's counters."""
+        ew.signal_flags([self.flag_ptr(r, FLAG_KV + self.rank) for r in range(self.tp)], value)
+
+    def wait_kv_landed(self, value: int, status: Optional[torch.Tensor]) -> None:
+        """On the current stream: a bounded wait until every rank's counter here has reached ``value``."""
+        ew.wait_flags(self.flag_ptr(self.rank, FLAG_KV), self.tp, value, status)
 
     def global_pool(self, runner) -> kv_ops.PagedKVPool:
         """The paged pool as the restore / save kernels see it: one base pointer per rank."""
@@ -248,8 +293,10 @@ class TPContext:
 
     # -- the model step ---------------------------------------------------------------------------
     @torch.no_grad()
-    def forward_body(self, runner, inp, nsplit: int, split_tokens: int) -> None:
-        """Embedding, all layers and the final norm push; ends by advancing the epoch bases.
+    def forward_body(self, runner, inp, nsplit: int, split_tokens: int, l0: int = 0, l1: Optional[int] = None) -> None:
+        """Layers ``[l0, l1)`` (the embedding in front of layer 0, the final norm push behind the last
+        layer); ends by advancing the epoch bases, so consecutive layer ranges chain: the first
+        wait of a range finds the previous range's last pushes at offset 0 of the new bases.
 
         Every launch depends only on the step's shape (offsets are relative to the bases), so
         the runner may capture this body in a CUDA graph and replay it.  Counter comparisons
@@ -259,24 +306,27 @@ class TPContext:
         T = inp.num_tokens
         if T > self.max_tokens or T > runner.max_tokens:
             raise ValueError("step exceeds the tensor-parallel buffers")
+        l1 = len(w.layers) if l1 is None else l1
         if self.impl == "nccl":
-            return self._forward_body_nccl(runner, inp, nsplit, split_tokens)
+            return self._forward_body_nccl(runner, inp, nsplit, split_tokens, l0, l1)
         if self.impl == "nvls":
-            return self._forward_body_nvls(runner, inp, nsplit, split_tokens)
+            return self._forward_body_nvls(runner, inp, nsplit, split_tokens, l0, l1)
         if self.impl == "oneshot" or (self.impl == "fused" and self.tp <= ONESHOT_MAX_TP and T <= self.os_cap):
-            return self._forward_body_oneshot(runner, inp, nsplit, split_tokens)
+            return self._forward_body_oneshot(runner, inp, nsplit, split_tokens, l0, l1)
         self._rs_off = self._ag_off = self._done_off = 0
         D, B = cfg.head_dim, cfg.block_tokens
         rows = -(-T // self.tp)
         first = self.rank * rows
         mine = max(0, min(rows, T - first))
         h = self.h_local[:rows]
-        if mine < rows:
-            h[mine:].zero_()
-        if mine > 0:
-            ew.embedding(inp.tokens[first : first + mine], w.embed, out=h[:mine])
-        self._norm_push(runner, h, w.layers[0].input_norm, None, rows, wait=False)
-        for li, lw in enumerate(w.layers):
+        if l0 == 0:
+            if mine < rows:
+                h[mine:].zero_()
+            if mine > 0:
+                ew.embedding(inp.tokens[first : first + mine], w.embed, out=h[:mine])
+            self._norm_push(runner, h, w.layers[0].input_norm, None, rows, wait=False)
+        for li in range(l0, l1):
+            lw = w.layers[li]
             qkv, f32 = self._col_gemm(runner, lw.wqkv, runner.qkv_acc, runner.qkv_bf, T, rows)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
                              runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
@@ -320,7 +370,7 @@ class TPContext:
         ew.add_rmsnorm(self.os_buf[which][:T], weight, residual=h, out=out, eps=self.cfg.rms_eps, zero_after=False,
                        tp_sync=sync, n_partials=self.tp, partial_stride=self.os_cap * self.cfg.hidden)
 
-    def _forward_body_oneshot(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+    def _forward_body_oneshot(self, runner, inp, nsplit: int, split_tokens: int, l0: int, l1: int) -> None:
         """The fused forward for steps of few tokens (a RAG query block, a decode batch).
 
         At this size a sync point costs latency, not bandwidth, so each of the two per-layer
@@ -337,9 +387,11 @@ class TPContext:
         D, B = cfg.head_dim, cfg.block_tokens
         h, normed = runner.h[:T], runner.normed[:T]
         offs = [0, 0]
-        ew.embedding(inp.tokens, w.embed, out=h)
-        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
-        for li, lw in enumerate(w.layers):
+        if l0 == 0:
+            ew.embedding(inp.tokens, w.embed, out=h)
+            ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li in range(l0, l1):
+            lw = w.layers[li]
             qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
                              runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
@@ -357,7 +409,7 @@ class TPContext:
         ew.advance_epochs(self.epochs_os, offs[0], offs[1], 0)
 
     # -- in-switch form: partial stays local, the reader sums through the NVLink multicast mapping ----
-    def _forward_body_nvls(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+    def _forward_body_nvls(self, runner, inp, nsplit: int, split_tokens: int, l0: int, l1: int) -> None:
         """The one-shot form with the NVSwitch doing the sum.
 
         Each row-parallel GEMM stores its bf16 partial into this rank's OWN buffer (local stores
@@ -404,9 +456,11 @@ class TPContext:
             ew.add_rmsnorm(self.nv_buf[which][:T], weight, residual=h, out=out, eps=cfg.rms_eps, zero_after=False,
                            tp_sync=sync)
 
-        ew.embedding(inp.tokens, w.embed, out=h)
-        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
-        for li, lw in enumerate(w.layers):
+        if l0 == 0:
+            ew.embedding(inp.tokens, w.embed, out=h)
+            ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li in range(l0, l1):
+            lw = w.layers[li]
             qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
                              runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
@@ -422,7 +476,7 @@ class TPContext:
             norm_sum(1, w.final_norm if last else w.layers[li + 1].input_norm, self.gathered[:T] if last else normed)
         ew.advance_epochs(self.epochs_nv, offs[0], offs[1], 0)
 
-    def _forward_body_nccl(self, runner, inp, nsplit: int, split_tokens: int) -> None:
+    def _forward_body_nccl(self, runner, inp, nsplit: int, split_tokens: int, l0: int, l1: int) -> None:
         """The baseline: what stock tensor parallelism does (``vllm/model_executor/layers/linear.py``,
         ``RowParallelLinear`` with ``reduce_results``): every rank keeps the whole residual stream,
         column- and row-parallel GEMMs run on the local shards (the same tcgen05 kernels as the
@@ -433,9 +487,11 @@ class TPContext:
         T = inp.num_tokens
         D, B = cfg.head_dim, cfg.block_tokens
         h, normed = runner.h[:T], runner.normed[:T]
-        ew.embedding(inp.tokens, w.embed, out=h)
-        ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
-        for li, lw in enumerate(w.layers):
+        if l0 == 0:
+            ew.embedding(inp.tokens, w.embed, out=h)
+            ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        for li in range(l0, l1):
+            lw = w.layers[li]
             qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
                              runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
@@ -451,7 +507,8 @@ class TPContext:
             dist.all_reduce(d, group=self.group)
             nxt = w.layers[li + 1].input_norm if li + 1 < len(w.layers) else w.final_norm
             ew.add_rmsnorm(d, nxt, residual=h, out=normed, eps=cfg.rms_eps, zero_after=f32)
-        self.gathered[:T].copy_(normed)  # where `sample` looks for the last layer's output
+        if l1 == len(w.layers):
+            self.gathered[:T].copy_(normed)  # where `sample` looks for the last layer's output
 
     def sample(self, runner, inp) -> torch.Tensor:
         n = inp.num_seqs
@@ -485,8 +542,11 @@ class TPContext:
         runner.best_idx[:n].copy_(tok)
         return runner.best_idx[:n]
 
-    # -- save: every rank pushes its heads into the IO rank's staging ---------------------------------
+    # -- save: every rank pushes its heads into the owning rank's staging ------------------------------
     def save_step(self, engine, meta) -> None:
+        """Store the step's chunks: each chunk is assembled in the staging buffer of the rank that owns
+        it (every rank's save kernel compresses its own head slice and writes it there over NVLink),
+        and that rank writes the file, fills its tiers and commits."""
         geo = engine.geo
         specs = list(meta.reqs_to_store)
         if not specs:
@@ -494,35 +554,36 @@ class TPContext:
         if self.save_staging is None:
             self.staging_slots = 256
             self.save_staging = self.alloc("save_staging", (self.staging_slots * geo.slot_size,), torch.uint8)
-        base0 = self.ptrs["save_staging"][0]
         while specs:
             batch, used = [], 0
             while specs and used + len(specs[0].block_ids) <= self.staging_slots:
                 s = specs.pop(0)
-                batch.append((s, used))
+                batch.append((s, used, engine.owner_of(s.chunk_key)))
                 used += len(s.block_ids)
             if not batch:
                 raise ValueError("chunk larger than the save staging buffer")
             ptrs, blocks = [], []
-            for s, first in batch:
+            for s, first, owner in batch:
+                base = self.ptrs["save_staging"][owner]
                 for i, b in enumerate(s.block_ids):
-                    ptrs.append(base0 + (first + i) * geo.slot_size)
+                    ptrs.append(base + (first + i) * geo.slot_size)
                     blocks.append(b)
             engine.kv_backend.save_ptrs(ptrs, blocks)
             torch.cuda.synchronize()
             engine.kv_backend.check_status()
-            self.barrier()  # every rank's head slice is in rank 0's staging
-            if self.rank == 0:
-                wk = engine.worker
-                for s, first in batch:
-                    n = len(s.block_ids)
-                    view = self.save_staging[first * geo.slot_size : (first + n) * geo.slot_size]
-                    wk.transfer.write(view, s.file_offset, n * geo.slot_size)
-                    for tier in (engine.hbm, engine.host):
-                        if tier is not None:
-                            tier.admit(s.chunk_key, self.save_staging, first * geo.slot_size, n * geo.slot_size)
-                            tier.end_step()
-                    extra = {"first_block": s.first_block_digest} if s.first_block_digest else {}
-                    wk._ipc.commit_chunk(s.chunk_key, **extra)
-                torch.cuda.synchronize()
-            self.barrier()  # staging may be overwritten again
+            self.barrier()  # every rank's head slice is in the owner's staging
+            wk = engine.worker
+            for s, first, owner in batch:
+                if owner != self.rank:
+                    continue
+                n = len(s.block_ids)
+                view = self.save_staging[first * geo.slot_size : (first + n) * geo.slot_size]
+                wk.transfer.write(view, s.file_offset, n * geo.slot_size)
+                for tier in (engine.hbm, engine.host):
+                    if tier is not None:
+                        tier.admit(s.chunk_key, self.save_staging, first * geo.slot_size, n * geo.slot_size)
+                        tier.end_step()
+                extra = {"first_block": s.first_block_digest} if s.first_block_digest else {}
+                wk._ipc.commit_chunk(s.chunk_key, **extra)
+            torch.cuda.synchronize()
+            self.barrier()  # staging may be overwritten again; every commit is visible

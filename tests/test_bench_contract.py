@@ -15,19 +15,20 @@ def test_traffic_is_deterministic_block_aligned_and_skewed():
     from daser_b200.models.llama import PRESETS
 
     cfg = PRESETS["llama3-70b"]
-    prefix, pool, reqs = bench.make_traffic(cfg, 64, 8, 30)
-    prefix2, pool2, reqs2 = bench.make_traffic(cfg, 64, 8, 30)
+    prefix, pool, reqs = bench.make_traffic(cfg.vocab_size, cfg.block_tokens, 64, 8, 30)
+    prefix2, pool2, reqs2 = bench.make_traffic(cfg.vocab_size, cfg.block_tokens, 64, 8, 30)
     assert (prefix, pool, reqs) == (prefix2, pool2, reqs2)
     bt = cfg.block_tokens
     assert len(prefix) == 64 and all(len(c) % bt == 0 and 64 <= len(c) <= 1024 for c in pool)
-    for chunks, query in reqs:
+    for chunks, query, picked in reqs:
         assert chunks[0] is prefix and len(chunks) == 9 and len(query) == 64
         assert all(0 < t < cfg.vocab_size for t in query)
+        assert [pool[i] for i in picked] == chunks[1:]
     # Zipf 1.1 over the pool: the few most popular chunks take a large share of the picks
-    picks = [id(c) for chunks, _ in reqs for c in chunks[1:]]
+    picks = [id(c) for chunks, _, _ in reqs for c in chunks[1:]]
     top = sorted((picks.count(id(c)) for c in pool), reverse=True)
     assert sum(top[:8]) > 0.4 * len(picks)
-    ctx = [sum(map(len, chunks)) + len(q) for chunks, q in reqs]
+    ctx = [sum(map(len, chunks)) + len(q) for chunks, q, _ in reqs]
     assert 1500 < sum(ctx) / len(ctx) < 6000
 
 

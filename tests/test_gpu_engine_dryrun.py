@@ -34,6 +34,9 @@ class _Runner:
     """Records every forward; the "sampled" token of a sequence is a hash of its last token and position."""
 
     max_tokens, max_seqs, max_blocks = 64, 4, 32
+    layer_groups = [(0, 2)]
+    h2d_bytes = 0
+    status = None
 
     def __init__(self):
         self.calls = []
@@ -41,7 +44,10 @@ class _Runner:
     def stage_inputs(self, seqs):
         return [dict(s, tokens=list(s["tokens"]), block_table=list(s["block_table"])) for s in seqs]
 
-    def forward(self, seqs):
+    def forward(self, seqs, gate=None):
+        if gate is not None:
+            for g in range(len(self.layer_groups)):
+                gate(g)  # the restore pieces, in order, in front of the layers that read them
         self.calls.append(seqs)
         return torch.tensor([(s["tokens"][-1] * 31 + s["start_pos"] + len(s["tokens"])) % 1000 for s in seqs])
 
@@ -65,8 +71,11 @@ def engine(tmp_path):
     eng.worker = WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool.data, cfg.inv_freq()),
                             io_backend="posix")
     eng.hbm = eng.host = None
+    eng.kv_backend = eng.worker.kv
+    eng.kv_backend.h2d_bytes = 0
     eng.waiting, eng.running, eng._n = [], [], 0
     eng._ev = [_Event() for _ in range(4)]
+    eng._restore_stream, eng._group_ev, eng._kv_epoch, eng.h2d_bytes = None, [], 0, 0
     yield eng
     eng.worker.shutdown()
     eng.sched.close()

@@ -162,3 +162,28 @@ def test_registered_buffers_use_fixed_operations(tmp_path):
         eng.wait(eng.submit_read(base, 0, 1 << 20))
         st = eng.stats()
         assert st["fixed_pieces"] > fixed_after_write and st["resubmits"] >= 1
+
+
+@pytest.mark.parametrize("backend", _backends())
+def test_strided_read_fills_equally_spaced_slices_under_one_ticket(store, backend):
+    """Some layers of every slot of a chunk: extent i of the file lands at the same offset of the
+    image in memory; everything between the extents stays untouched."""
+    slot, layer, n_slots = 40960, 10240, 6
+    rng = np.random.default_rng(1)
+    data = rng.integers(0, 256, n_slots * slot, dtype=np.uint8)
+    with _open(store, backend) as io:
+        src = _aligned(n_slots * slot)
+        src[:] = data
+        io.wait(io.submit_write(src.ctypes.data, 8192, n_slots * slot))
+        dst = _aligned(n_slots * slot, fill=0xEE)
+        l0, count = 1, 2  # layers 1 and 2 of every slot
+        io.wait(io.submit_read_strided(dst.ctypes.data + l0 * layer, 8192 + l0 * layer, count * layer, n_slots, slot))
+        got, want = dst.reshape(n_slots, slot), data.reshape(n_slots, slot)
+        assert np.array_equal(got[:, l0 * layer : (l0 + count) * layer], want[:, l0 * layer : (l0 + count) * layer])
+        assert (got[:, : l0 * layer] == 0xEE).all() and (got[:, (l0 + count) * layer :] == 0xEE).all()
+        # an injected error on one extent fails the whole ticket
+        io.inject_fault(1, errno.EIO)
+        with pytest.raises(OSError):
+            io.wait(io.submit_read_strided(dst.ctypes.data, 8192, layer, n_slots, slot))
+        with pytest.raises(OSError):
+            io.submit_read_strided(dst.ctypes.data, 0, 4096, 2, 1024)  # extents would overlap

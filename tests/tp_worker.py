@@ -1,8 +1,10 @@
 """Worker of the multi-GPU tests: run with ``torch.distributed.run --nproc-per-node N``.
 
 Each rank shards the same tiny model, runs the fused tensor-parallel forward and the RAG
-engine (store -> restore with scatter into every rank's pool), and rank 0 compares against a
-single-GPU run of the unsharded model.  Prints ``TP_OK`` when everything agrees.
+engine (store -> restore with scatter into every rank's pool: every rank reads the chunks it
+owns and its kernel writes every rank's head slices), rank 0 compares the forward against a
+single-GPU run of the unsharded model, and every rank compares the restored KV in its own pool
+with a recompute at the same offset.  Prints ``TP_OK`` when everything agrees.
 """
 
 import asyncio
@@ -20,6 +22,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from daser_b200.config import DaserConfig  # noqa: E402
 from daser_b200.engine.rag_gpu import GpuRagEngine  # noqa: E402
 from daser_b200.engine.runner import GpuModelRunner, make_step_inputs  # noqa: E402
+from daser_b200.hashing import hash_tokens  # noqa: E402
 from daser_b200.models.llama import PRESETS, LlamaWeights, shard_weights  # noqa: E402
 from daser_b200.parallel.tp import TPContext  # noqa: E402
 from daser_b200.server.__main__ import ControlPlane  # noqa: E402
@@ -98,19 +101,66 @@ def main() -> None:
     ctx.barrier()
     eng = GpuRagEngine(cfg, dcfg.ipc_socket_path, dcfg.store_path, num_blocks=128, max_tokens=128, max_seqs=8,
                        hbm_slots=32, tp_ctx=ctx, weights=shard_weights(full, tp, rank), staging_slots=64)
-    chunks = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (64, 96)]
+    chunks = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (64, 96, 48)]
     for c in chunks:
         eng.store_chunk(c)
+    owners = sorted({eng.owner_of(hash_tokens(c)) for c in chunks})
     query = [rng.randrange(cfg.vocab_size) for _ in range(12)]
-    cold = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=3)
-    warm = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=3)  # HBM tier on the IO rank
+    for tier in (eng.hbm, eng.host):  # saving admitted the chunks to their owners' tiers: forget them,
+        if tier is not None:          # so that the first request reads the store file, layer group by layer group
+            tier.clear()
+    read0 = eng.worker.transfer.engine.stats()["bytes_read"]
+    cold = eng.generate([chunks[1], chunks[0], chunks[2]], query, max_new_tokens=3)
+    read_cold = eng.worker.transfer.engine.stats()["bytes_read"] - read0
+    warm = eng.generate([chunks[1], chunks[0], chunks[2]], query, max_new_tokens=3)  # each owner's HBM tier
+    read_warm = eng.worker.transfer.engine.stats()["bytes_read"] - read0 - read_cold
     eng.runner.check_status()
     same = ctx.broadcast_object(cold.generated) == cold.generated  # every rank sampled the same tokens
     ok = ok and same and cold.generated == warm.generated
+    ok = ok and cold.restored_chunks == 3 and warm.restored_chunks == 3 and read_warm == 0
+    reads = ctx.gather_object(read_cold)
+    mine = sum(len(c) // 16 for c in chunks if eng.owner_of(hash_tokens(c)) == rank) * slot
+    ok = ok and read_cold == mine  # every rank read exactly the chunks it owns, from the file
     if rank == 0:
-        ok = ok and cold.restored_chunks == 2 and warm.restored_chunks == 2
-        print(f"engine tokens cold={cold.generated} warm={warm.generated} restored={cold.restored_chunks}", flush=True)
-    # the scattered + rotated KV of chunk 0 equals what a recompute at that offset writes (layer 0)
+        print(f"engine tokens cold={cold.generated} warm={warm.generated} restored={cold.restored_chunks} "
+              f"owners={owners} file bytes per rank={reads}", flush=True)
+    # every rank's pool: the scattered + rotated KV of chunk 0 equals what a recompute at that
+    # offset writes (layer 0 depends on the token and its position only; up to fp8 requantisation)
+    from daser_b200.engine.request import RagRequest
+    from daser_b200.kv import codec
+
+    r = eng.submit(RagRequest([chunks[1], chunks[0]], query, 2))  # stays running: its blocks are kept
+    eng._ttft_step(eng.waiting.pop(0))
+    off = len(chunks[1])
+    restored = r.block_table[off // 16 : (off + len(chunks[0])) // 16]
+    fresh = eng.blocks.alloc(len(chunks[0]) // 16)
+    eng._prefill_tokens(chunks[0], off, [0] * (off // 16) + fresh)  # same positions, fresh blocks
+    torch.cuda.synchronize()
+    pay, sc = eng.runner.kv_payload.cpu(), eng.runner.kv_scales.cpu()
+    got = codec.dequantize_fp8b16(pay[:, restored], sc[:, restored])
+    want = codec.dequantize_fp8b16(pay[:, fresh], sc[:, fresh])
+    err0 = (got[0] - want[0]).abs().max().item() / want[0].abs().max().item()
+    errs = ctx.gather_object(round(err0, 4))
+    ok = ok and err0 < 0.15 and float(want[0].abs().max()) > 0
+    if rank == 0:
+        print(f"restored vs recomputed KV, layer 0, relative error per rank: {errs}", flush=True)
+    while not r.done:
+        eng.step()
+    eng.blocks.free(fresh)
+    # engine options that are Python over the same kernels, in lock step on every rank
+    eng.repair_tokens = 8
+    rep = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=2)
+    eng.repair_tokens = 0
+    samp = eng.generate([chunks[2]], query, max_new_tokens=4, temperature=0.8, seed=3, top_k=5, top_p=0.9)
+    ok = ok and rep.restored_chunks == 2 and len(samp.generated) == 4
+    ok = ok and ctx.broadcast_object(samp.generated) == samp.generated and ctx.broadcast_object(rep.generated) == rep.generated
+    eng.compose_after = 2
+    for _ in range(2):
+        eng.generate([chunks[0], chunks[2]], query, max_new_tokens=1)
+    comp = eng.generate([chunks[0], chunks[2]], query, max_new_tokens=1)  # the pair is now one stored chunk
+    eng.compose_after = 0
+    ok = ok and comp.restored_chunks == 1
+    eng.runner.check_status()
     eng.close()
     flags = [None] * tp
     dist.all_gather_object(flags, ok, group=ctx._cpu_group)
