@@ -130,24 +130,30 @@ class GpuRagEngine(SchedulingMixin):
             out = self.runner.forward(inp, gate=gate if i == 0 else None)
         return out
 
-    def warm_up(self, token_counts: Sequence[int] = (64,), context_lens: Sequence[int] = (2048, 4096, 8192)) -> None:
+    def warm_up(self, token_counts: Sequence[int] = (64,), context_lens: Sequence[int] = (2048, 4096, 8192),
+                decode_batches: Sequence[int] = ()) -> None:
         """Run (and capture) the forward for the step shapes a workload will use, on scratch blocks.
 
         A shape's first run is eager and its second run captures a CUDA graph, which costs
         tens of milliseconds; serving code calls this once at start-up so that no request pays it.
+        ``token_counts`` are single-sequence prefill steps, ``decode_batches`` decode steps of that
+        many sequences (see :meth:`decode_bucket`), each at every context length.
         """
         bt = self.cfg.block_tokens
         for ctx in context_lens:
-            for t in token_counts:
-                n_blocks = -(-ctx // bt)
-                if n_blocks > self.blocks.num_free or n_blocks > self.runner.max_blocks or t > self.runner.max_tokens:
-                    continue
-                table = self.blocks.alloc(n_blocks)
+            n_blocks = -(-ctx // bt)
+            if n_blocks > self.blocks.num_free or n_blocks > self.runner.max_blocks:
+                continue
+            table = self.blocks.alloc(n_blocks)
+            shapes = [[{"tokens": [1] * t, "start_pos": ctx - t, "block_table": table}]
+                      for t in token_counts if t <= self.runner.max_tokens]
+            shapes += [[{"tokens": [1], "start_pos": ctx - 1, "block_table": table}] * b
+                       for b in decode_batches if b <= self.runner.max_seqs]
+            for seqs in shapes:
                 for _ in range(3):
-                    inp = self.runner.stage_inputs([{"tokens": [1] * t, "start_pos": ctx - t, "block_table": table}])
-                    self.runner.forward(inp)
+                    self.runner.forward(self.runner.stage_inputs(seqs))
                 torch.cuda.synchronize()
-                self.blocks.free(table)
+            self.blocks.free(table)
 
     # -- offline fill ------------------------------------------------------------------------------
     def store_chunk(self, tokens: Sequence[int]) -> str:
@@ -356,11 +362,24 @@ class GpuRagEngine(SchedulingMixin):
         if self.sched is not None:
             self.sched.request_finished(sub)
 
+    @staticmethod
+    def decode_bucket(n: int, cap: int) -> int:
+        """Batch sizes are rounded up to powers of two so that a handful of captured graphs serve
+        every decode step (a batch that grows and shrinks by one would otherwise meet a new shape,
+        run eagerly and capture, at almost every step)."""
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, cap) if cap >= n else n
+
     def _decode_step(self) -> None:
         batch = self.running[: self.runner.max_seqs]
         seqs = [{"tokens": [r.generated[-1]], "start_pos": r.context_len + len(r.generated) - 1,
                  "block_table": r.block_table, "temperature": r.temperature, "seed": r.step_seed(),
                  "top_k": r.top_k, "top_p": r.top_p} for r in batch]
+        # padding rows repeat the first sequence: they rewrite the same KV entry with the same
+        # value and their samples are dropped
+        seqs += [seqs[0]] * (self.decode_bucket(len(seqs), self.runner.max_seqs) - len(seqs))
         inp = self.runner.stage_inputs(seqs)
         self.h2d_bytes += self.runner.h2d_bytes
         out = self.runner.forward(inp).tolist()
