@@ -53,8 +53,14 @@ class GpuRagEngine(SchedulingMixin):
                  io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
                  staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True,
-                 compose_after: int = 0, repair_tokens: int = 0, layer_groups: int = 8) -> None:
+                 compose_after: int = 0, repair_tokens: int = 0, layer_groups: int = 8, pp_link=None) -> None:
         self.cfg = cfg
+        # pipeline parallelism: this process is one stage (``parallel/pp.py::StageLink``); it runs a
+        # contiguous range of layers, keeps their KV in a pool and a store file of its own, and a
+        # chunk is published once every stage has committed its part
+        self.pp_link = pp_link
+        if pp_link is not None and tp_ctx is not None:
+            raise ValueError("pipeline stages are single-GPU here: pass tp_ctx or pp_link, not both")
         # > 0: after a chunk was restored behind other context, its first `repair_tokens` tokens are
         # recomputed in place with attention over everything before them (the tokens whose stored KV
         # is furthest from what the full context would have produced: they saw nothing when stored)
@@ -66,14 +72,22 @@ class GpuRagEngine(SchedulingMixin):
         self.rank = tp_ctx.rank if tp_ctx is not None else 0
         self.tp_ctx = tp_ctx
         self.device = torch.device("cuda", torch.cuda.current_device())
+        layer_range, pool_layers = None, None
+        if pp_link is not None:
+            from daser_b200.parallel.pp import partition_layers, stage_store_path
+
+            layer_range = partition_layers(cfg.num_layers, pp_link.stages)[pp_link.stage]
+            pool_layers = max(len(r) for r in partition_layers(cfg.num_layers, pp_link.stages))
+            store_path = stage_store_path(store_path, pp_link.stage, pp_link.stages)
         self.weights = weights or LlamaWeights.random(cfg, self.device, torch.bfloat16, tp=self.tp,
-                                                      rank=self.rank, seed=seed)
+                                                      rank=self.rank, seed=seed, layers=layer_range)
         # the engine owns its weights: put gate/up rows in the order that lets SwiGLU run as the
         # GEMM's epilogue (in place, one layer-sized temporary)
         if self.weights.gate_up_block == 0 and self.weights.inter_local % gemm_ops.GATE_UP_BLOCK == 0:
             self.weights.interleave_gate_up_(gemm_ops.GATE_UP_BLOCK)
         self.runner = GpuModelRunner(cfg, self.weights, num_blocks, max_tokens, max_seqs, tp_ctx, self.device,
-                                     max_blocks=max_blocks, use_graphs=use_graphs, layer_groups=layer_groups)
+                                     max_blocks=max_blocks, use_graphs=use_graphs, layer_groups=layer_groups,
+                                     layer_range=layer_range, pool_layers=pool_layers, pp_link=pp_link)
         self.blocks = BlockAllocator(num_blocks)
         self.max_blocks_per_seq = max_blocks  # the runner's block tables are this wide
         self.geo = self.runner.geo
@@ -85,11 +99,24 @@ class GpuRagEngine(SchedulingMixin):
         # tiers and IO are per rank: `hbm_slots` / `host_slots` are this rank's share
         self.hbm = HBMStore(self.geo.slot_size, hbm_slots, self.device) if hbm_slots > 0 else None
         self.host = HBMStore(self.geo.slot_size, host_slots, torch.device("cpu")) if host_slots > 0 else None
-        self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id) if self.rank == 0 else None
+        self.is_lead = self.rank == 0 and (pp_link is None or pp_link.first)  # plans, reserves, finishes
+        self.sched = SchedulerHalf(socket_path, cfg.block_tokens, model_id) if self.is_lead else None
         if self.tp > 1 and self.rank != 0:
             tp_ctx.wait_for_path(store_path)  # rank 0 creates the store file
         self.worker = WorkerHalf(socket_path, store_path, self.geo, self.kv_backend, io_backend=io_backend, tp=self.tp,
                                  rank=self.rank, hbm_store=self.hbm, host_store=self.host, staging_slots=staging_slots)
+        if pp_link is not None and pp_link.stages > 1:
+            self.worker.commit_parts = (pp_link.stage, pp_link.stages)
+        # Every process has now shaken hands with the control plane, which may live on a thread of
+        # the lead process.  Meet here before anyone goes on: collective set-up calls (symmetric
+        # memory rendezvous, communicator creation) can block without releasing the interpreter
+        # lock, and a lead that enters one while a peer still waits for the control plane's answer
+        # would starve the very thread that has to give it.
+        if tp_ctx is not None:
+            tp_ctx.prepare_save_staging(self.geo)
+            tp_ctx.barrier()
+        elif pp_link is not None:
+            pp_link.barrier()
         self.waiting: list[RagRequest] = []
         self.running: list[RagRequest] = []
         self._n = 0
@@ -109,7 +136,19 @@ class GpuRagEngine(SchedulingMixin):
             self.tp_ctx.barrier()
 
     def _bcast(self, obj):
-        return self.tp_ctx.broadcast_object(obj) if self.tp_ctx is not None else obj
+        """``obj`` of the lead process (tensor-parallel rank 0 / pipeline stage 0) everywhere."""
+        if self.tp_ctx is not None:
+            return self.tp_ctx.broadcast_object(obj)
+        if self.pp_link is not None:
+            return self.pp_link.from_stage(obj, 0)
+        return obj
+
+    def _tokens_out(self, sampled: Optional[torch.Tensor], n: int) -> list[int]:
+        """The step's sampled tokens on the host (read back from the device; in a pipeline, sent
+        from the last stage to every stage)."""
+        if self.pp_link is None:
+            return [int(t) for t in sampled[:n].tolist()]
+        return self.pp_link.tokens_from_last(sampled[:n] if sampled is not None else None, n, self.device)
 
     def owner_of(self, chunk_key: str) -> int:
         """The rank that keeps ``chunk_key`` in its tiers and moves it between the store and the pools."""
@@ -193,7 +232,8 @@ class GpuRagEngine(SchedulingMixin):
         if not loads:
             return None, None
         mine = ConnectorMeta(reqs_to_load=[s for s in loads if self.owner_of(s.chunk_key) == self.rank])
-        groups = self.runner.layer_groups
+        # the worker counts layers inside a slot image: from 0 in every pipeline stage
+        groups = [(a - self.runner.layers.start, n) for a, n in self.runner.layer_groups]
         ticket = self.worker.begin_load(mine, groups) if mine.reqs_to_load else None
         side = self._restore_stream
         base = self._kv_epoch
@@ -315,10 +355,12 @@ class GpuRagEngine(SchedulingMixin):
         failed_blocks = self.worker.take_load_errors()
         if self.tp_ctx is not None and meta.reqs_to_load:
             failed_blocks = set().union(*self.tp_ctx.gather_object(sorted(failed_blocks)))
+        elif self.pp_link is not None and meta.reqs_to_load:
+            failed_blocks = set().union(*self.pp_link.gather_object(sorted(failed_blocks)))
         if failed_blocks:
             first = compute(set(failed_blocks), None)
         self._ev[3].record()
-        token = int(first[0].item())  # device -> host read of the step's result
+        token = self._tokens_out(first, 1)[0]  # device -> host read of the step's result
         t_end = time.perf_counter()
         self.worker.check_load_status()
         req.generated.append(token)
@@ -382,7 +424,7 @@ class GpuRagEngine(SchedulingMixin):
         seqs += [seqs[0]] * (self.decode_bucket(len(seqs), self.runner.max_seqs) - len(seqs))
         inp = self.runner.stage_inputs(seqs)
         self.h2d_bytes += self.runner.h2d_bytes
-        out = self.runner.forward(inp).tolist()
+        out = self._tokens_out(self.runner.forward(inp), len(batch))
         for r, tok in zip(batch, out):
             r.generated.append(int(tok))
             if r.finished():

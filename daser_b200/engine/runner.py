@@ -72,9 +72,16 @@ def split_layers(num_layers: int, parts: int) -> list[tuple[int, int]]:
 class GpuModelRunner:
     def __init__(self, cfg: LlamaConfig, weights: LlamaWeights, num_blocks: int, max_tokens: int = 256,
                  max_seqs: int = 64, tp_ctx=None, device: Optional[torch.device] = None,
-                 max_blocks: int = 512, use_graphs: bool = True, layer_groups: int = 8) -> None:
+                 max_blocks: int = 512, use_graphs: bool = True, layer_groups: int = 8,
+                 layer_range: Optional[range] = None, pool_layers: Optional[int] = None, pp_link=None) -> None:
         self.cfg = cfg
         self.w = weights
+        # pipeline stage: the layers this process runs, its links to the neighbouring stages
+        # (``parallel/pp.py::StageLink``) and how many layers its pool and slot images have room for
+        self.layers = layer_range if layer_range is not None else range(cfg.num_layers)
+        self.pp_link = pp_link
+        if pp_link is not None and tp_ctx is not None:
+            raise ValueError("a pipeline stage runs on one GPU here (no tensor parallelism inside a stage)")
         self.tp = weights.tp
         self.rank = weights.rank
         self.tp_ctx = tp_ctx
@@ -88,7 +95,10 @@ class GpuModelRunner:
         dev = self.device
 
         # ---- paged KV pool (this rank's heads) ----
-        shape = (cfg.num_layers, num_blocks, 2, self.hkv, B, D)
+        n_pool_layers = pool_layers if pool_layers is not None else len(self.layers)
+        if n_pool_layers < len(self.layers):
+            raise ValueError("the pool has fewer layers than the stage runs")
+        shape = (n_pool_layers, num_blocks, 2, self.hkv, B, D)
         if tp_ctx is not None:
             self.kv_payload = tp_ctx.alloc("kv_payload", shape, torch.uint8)
             self.kv_scales = tp_ctx.alloc("kv_scales", shape[:-1] + (D // 16,), torch.float32)
@@ -99,7 +109,7 @@ class GpuModelRunner:
             self.kv_scales = torch.ones(shape[:-1] + (D // 16,), dtype=torch.float32, device=dev)
         self.local_pool = kv_ops.PagedKVPool.from_tensors([self.kv_payload], [self.kv_scales], "LNKHTD")
         # geometry of a stored slot: ALL kv heads, fp8b16
-        self.geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, D, B, 2, "fp8b16")
+        self.geo = KVGeometry(n_pool_layers, cfg.num_kv_heads, D, B, 2, "fp8b16")
         self.cos_sin = kv_ops.rope_table(min(cfg.max_position, 32768), cfg.inv_freq(), dev)
 
         # ---- activation buffers ----
@@ -144,7 +154,7 @@ class GpuModelRunner:
         self._graphs: dict[tuple, Any] = {}
         self._seen: dict[tuple, int] = {}
         # consecutive runs of layers a step is launched in (see `forward`): [(first layer, count)]
-        self.layer_groups = split_layers(cfg.num_layers, layer_groups)
+        self.layer_groups = [(self.layers.start + a, n) for a, n in split_layers(len(self.layers), layer_groups)]
 
     # -- helpers ---------------------------------------------------------------------------------
     def _linear(self, x: torch.Tensor, w: torch.Tensor, acc: torch.Tensor, out_bf: torch.Tensor):
@@ -256,6 +266,11 @@ class GpuModelRunner:
                                                      self.cfg.block_tokens, rows=T * self.hq)
         body = self._body if self.tp == 1 else (lambda *a: self.tp_ctx.forward_body(self, *a))
         shape = (T, inp.num_seqs, inp.max_q_len, nsplit, split_tokens)
+        link = self.pp_link
+        if link is not None:
+            link.drain()  # the previous step's hand-over has left `self.h`
+            if not link.first:
+                link.recv_prev_into(self.h[:T])  # the residual stream as the previous stage left it
         graphs_ok = self.use_graphs and inp.persistent
         seen = self._seen.get(shape, 0)
         self._seen[shape] = seen + 1
@@ -279,6 +294,9 @@ class GpuModelRunner:
                     body(inp, nsplit, split_tokens, l0, l0 + count)
                 self._graphs[key] = (graph, _lib.launch_count - before)
                 graph.replay()
+        if link is not None and not link.last:
+            link.send_next(self.h[:T])  # asynchronous; only the last stage samples
+            return None
         if self.tp > 1:
             return self.tp_ctx.sample(self, inp)
         return self.sample(self.normed[:T], inp)
@@ -292,16 +310,20 @@ class GpuModelRunner:
         D, B = cfg.head_dim, cfg.block_tokens
         h = self.h[:T]
         normed = self.normed[:T]
-        if l0 == 0:
-            ew.embedding(inp.tokens, w.embed, out=h)
-            ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
+        first = self.layers.start
+        if l0 == first:
+            if first == 0:
+                ew.embedding(inp.tokens, w.embed, out=h)
+            # (a later pipeline stage finds the residual stream in `h`, received from its predecessor)
+            ew.add_rmsnorm(h, w.layers[first].input_norm, out=normed, eps=cfg.rms_eps)
         for li in range(l0, l1):
             lw = w.layers[li]
+            pl = li - first  # layer index inside this stage's pool
             qkv, f32 = self._linear(normed, lw.wqkv, self.qkv_acc, self.qkv_bf)
             ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq,
-                             self.hkv, D, B, self.local_pool, li, 0, zero_after=f32, qk_norm=self.qk_norm(lw))
+                             self.hkv, D, B, self.local_pool, pl, 0, zero_after=f32, qk_norm=self.qk_norm(lw))
             attn = self.attn_out[:T].view(T, self.hq, D)
-            attention.paged_attention(self.q_rot[:T], attn, self.local_pool, li, inp.block_tables, inp.q_start,
+            attention.paged_attention(self.q_rot[:T], attn, self.local_pool, pl, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, self.hkv, self.softmax_scale,
                                       self.attn_ws, nsplit=nsplit, split_tokens=split_tokens)
             o, f32 = self._linear(self.attn_out[:T], lw.wo, self.hid_acc, self.hid_bf)

@@ -123,6 +123,8 @@ class LlamaWeights:
         if self.gate_up_block != 0 or self.inter_local % block:
             raise ValueError("gate/up rows cannot be interleaved in blocks of %d" % block)
         for lw in self.layers:
+            if lw.w_gate_up is None:  # a layer another pipeline stage runs
+                continue
             two_i, hidden = lw.w_gate_up.shape
             src = lw.w_gate_up.view(2, two_i // 2 // block, block, hidden).transpose(0, 1)
             lw.w_gate_up.copy_(src.reshape(two_i, hidden).clone())
@@ -155,8 +157,13 @@ class LlamaWeights:
 
     @classmethod
     def random(cls, cfg: LlamaConfig, device: str | torch.device = "cpu", dtype: torch.dtype = torch.float32,
-               tp: int = 1, rank: int = 0, seed: int = 0, std: float = 0.02) -> "LlamaWeights":
+               tp: int = 1, rank: int = 0, seed: int = 0, std: float = 0.02,
+               layers: Optional[range] = None) -> "LlamaWeights":
         """Random-init weights for ``rank`` of ``tp``.
+
+        ``layers`` keeps only that range of layers (a pipeline stage): the others get their norm
+        weights and no matrices, and every tensor that IS generated equals the one the full model
+        would hold (seeds are per tensor).
 
         Tensors are filled in place on ``device`` (no full-size temporaries), so the 70B
         model initialises inside one 180 GB GPU.  Every rank seeds per tensor from
@@ -183,7 +190,6 @@ class LlamaWeights:
         hq, hkv = cfg.num_heads // tp, max(1, cfg.num_kv_heads // tp)
         inter = cfg.intermediate // tp
         embed = mat(cfg.vocab_size, cfg.hidden, shard=False)
-        layers = []
 
         def head_norm() -> torch.Tensor:  # near one, not one: a misapplied weight must show in tests
             counter[0] += 1
@@ -192,7 +198,13 @@ class LlamaWeights:
             t.normal_(1.0, 0.1, generator=gen)
             return t
 
-        for _ in range(cfg.num_layers):
+        keep = layers
+        layers = []
+        for li in range(cfg.num_layers):
+            if keep is not None and li not in keep:
+                counter[0] += 4 + (2 if cfg.qk_norm else 0)  # the tensors this layer would have drawn
+                layers.append(LayerWeights(ones(cfg.hidden), None, None, ones(cfg.hidden), None, None))
+                continue
             layers.append(
                 LayerWeights(
                     input_norm=ones(cfg.hidden),

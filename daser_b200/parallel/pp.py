@@ -19,7 +19,11 @@ previous one.  The sampled token goes back from the last stage to all.
 
 :class:`PipelineCpuEngine` runs the oracle model (``models/llama.py::reference_forward`` on a
 layer range) and is what the CPU tests drive; it keeps the public calls of
-:class:`~daser_b200.engine.rag_cpu.CpuRagEngine`.  The CUDA runner has no stage mode yet.
+:class:`~daser_b200.engine.rag_cpu.CpuRagEngine`.  On GPUs the same scheme is a mode of the native
+engine: ``GpuRagEngine(..., pp_link=StageLink(group))`` runs this stage's layers on the sm_100a
+kernels (``GpuModelRunner(layer_range=...)``), receives the residual stream with an NCCL receive
+in front of its first layer group, posts it on behind its last, and the last stage broadcasts
+the sampled tokens (``tests/pp_worker.py``).
 """
 
 from __future__ import annotations
@@ -82,6 +86,11 @@ class StageLink:
         dist.recv(buf, self._global(self.stage - 1), group=self.group)
         return buf
 
+    def recv_prev_into(self, buf: torch.Tensor) -> torch.Tensor:
+        """Receive the previous stage's hand-over into an existing (persistent) buffer."""
+        dist.recv(buf, self._global(self.stage - 1), group=self.group)
+        return buf
+
     def drain(self) -> None:
         for work, _ in self._inflight:
             work.wait()
@@ -92,6 +101,27 @@ class StageLink:
         box = [obj]
         dist.broadcast_object_list(box, src=self._global(stage), group=self.group)
         return box[0]
+
+    def barrier(self) -> None:
+        if dist.get_backend(self.group) == "nccl":
+            dist.barrier(group=self.group, device_ids=[torch.cuda.current_device()])
+        else:
+            dist.barrier(group=self.group)
+
+    def gather_object(self, obj: Any) -> list:
+        """Every stage's ``obj`` in stage order, on every stage."""
+        out: list = [None] * self.stages
+        dist.all_gather_object(out, obj, group=self.group)
+        return out
+
+    def tokens_from_last(self, tokens: Optional[torch.Tensor], n: int, device: Any = "cpu") -> list[int]:
+        """The last stage's ``n`` sampled tokens as a list on every stage (one broadcast, one read)."""
+        buf = torch.empty(n, dtype=torch.int64, device=device)
+        if self.last:
+            buf.copy_(tokens[:n])
+        dist.broadcast(buf, self._global(self.stages - 1), group=self.group)
+        self.drain()  # the tokens exist, so every hand-over that led to them has completed
+        return [int(t) for t in buf.tolist()]
 
     def token_from_last(self, token: Optional[int], device: Any = "cpu") -> int:
         t = torch.tensor([token if token is not None else -1], dtype=torch.int64, device=device)

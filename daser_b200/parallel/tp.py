@@ -542,6 +542,13 @@ class TPContext:
         runner.best_idx[:n].copy_(tok)
         return runner.best_idx[:n]
 
+    def prepare_save_staging(self, geo) -> None:
+        """Allocate the symmetric buffer chunks are assembled in (a collective: every rank calls it
+        at the same point; engines do so once at start-up)."""
+        if self.save_staging is None:
+            self.staging_slots = 256
+            self.save_staging = self.alloc("save_staging", (self.staging_slots * geo.slot_size,), torch.uint8)
+
     # -- save: every rank pushes its heads into the owning rank's staging ------------------------------
     def save_step(self, engine, meta) -> None:
         """Store the step's chunks: each chunk is assembled in the staging buffer of the rank that owns
@@ -551,9 +558,7 @@ class TPContext:
         specs = list(meta.reqs_to_store)
         if not specs:
             return
-        if self.save_staging is None:
-            self.staging_slots = 256
-            self.save_staging = self.alloc("save_staging", (self.staging_slots * geo.slot_size,), torch.uint8)
+        self.prepare_save_staging(geo)
         while specs:
             batch, used = [], 0
             while specs and used + len(specs[0].block_ids) <= self.staging_slots:

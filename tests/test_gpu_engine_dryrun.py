@@ -35,6 +35,7 @@ class _Runner:
 
     max_tokens, max_seqs, max_blocks = 64, 4, 32
     layer_groups = [(0, 2)]
+    layers = range(2)
     h2d_bytes = 0
     status = None
 
@@ -61,7 +62,7 @@ def engine(tmp_path):
     geo = KVGeometry(cfg.num_layers, cfg.num_kv_heads, cfg.head_dim, cfg.block_tokens, 4, "raw")
     lp = LiveControlPlane(tmp_path, total_slots=128, slot_size=geo.slot_size).start()
     eng = GpuRagEngine.__new__(GpuRagEngine)                 # not __init__: that needs a GPU
-    eng.cfg, eng.geo, eng.tp, eng.rank, eng.tp_ctx = cfg, geo, 1, 0, None
+    eng.cfg, eng.geo, eng.tp, eng.rank, eng.tp_ctx, eng.pp_link = cfg, geo, 1, 0, None, None
     eng.compose_after = eng.repair_tokens = 0
     eng.runner = _Runner()
     eng.blocks = BlockAllocator(32)

@@ -32,3 +32,15 @@ def test_tp2_rank_leaves_between_steps_and_the_other_learns_on_the_host():
     if "TP_LEAVE_SKIPPED" in proc.stdout:
         pytest.skip("symmetric buffers carry a multicast mapping on this box")
     assert "TP_LEAVE_OK" in proc.stdout, tail
+
+
+def test_pp2_pipeline_stages_match_a_single_gpu():
+    """Two pipeline stages of the native engine (NCCL point-to-point hand-over, per-stage store
+    files, multi-part commits) produce the tokens of the whole model on one GPU."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29521", os.path.join(here, "pp_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=280)
+    tail = (proc.stdout + proc.stderr)[-3000:]
+    assert proc.returncode == 0, tail
+    assert "PP_OK" in proc.stdout, tail
