@@ -113,8 +113,8 @@ class GpuRagEngine(SchedulingMixin):
         # lock, and a lead that enters one while a peer still waits for the control plane's answer
         # would starve the very thread that has to give it.
         if tp_ctx is not None:
-            tp_ctx.prepare_save_staging(self.geo)
-            tp_ctx.barrier()
+            tp_ctx.barrier()  # (releases the lock while it waits: the control plane keeps answering)
+            tp_ctx.prepare_save_staging(self.geo)  # a rendezvous: only now, with every rank at this line
         elif pp_link is not None:
             pp_link.barrier()
         self.waiting: list[RagRequest] = []

@@ -42,6 +42,7 @@ paged_attn_fp8_kernel(const AttnParams p) {
   const int kvh = blockIdx.x, seq = blockIdx.y;
   const int item = blockIdx.z * ATT_WARPS + warp;
   const int rt = item / p.nsplit, sp = item % p.nsplit;
+  pdl_enter();
   if (rt >= p.row_tiles_max) return;
 
   const int q0 = p.q_start[seq];
@@ -299,6 +300,7 @@ paged_attn_fp8_prefill_kernel(const AttnParams p) {
   const int g = lane >> 2, t = lane & 3;
   const int kvh = blockIdx.x, seq = blockIdx.y;
   const int grp = blockIdx.z / p.nsplit, sp = blockIdx.z % p.nsplit;
+  pdl_enter();
   const int q0 = p.q_start[seq];
   const int q_len = p.q_start[seq + 1] - q0;
   const int ctx = p.ctx_lens[seq];
@@ -514,6 +516,7 @@ attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ pa
                   __nv_bfloat16* __restrict__ out, int64_t rows, int nsplit) {
   const int64_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  pdl_enter();
   if (row >= rows) return;
   float mx = -INFINITY;
   for (int s = 0; s < nsplit; ++s) mx = fmaxf(mx, part_lse[row * nsplit + s]);
@@ -601,15 +604,16 @@ DASER_API int daser_paged_attention_fp8(const void* q, void* out, float* part_o,
     // several row tiles per KV head: the CTA-shared dequantisation pays off
     const int groups = (p.row_tiles_max + 3) / 4;
     const dim3 pgrid(Hkv, num_seqs, groups * nsplit);
-    paged_attn_fp8_prefill_kernel<<<pgrid, 128, PF_SMEM, stream>>>(p);
+    launch_pdl(paged_attn_fp8_prefill_kernel, pgrid, dim3(128), (size_t)PF_SMEM, stream, p);
   } else {
-    paged_attn_fp8_kernel<<<grid, ATT_WARPS * 32, smem, stream>>>(p);
+    launch_pdl(paged_attn_fp8_kernel, grid, dim3(ATT_WARPS * 32), smem, stream, p);
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (nsplit > 1) {
     const int64_t rows = (int64_t)total_q * Hq;
-    attn_merge_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, stream>>>(part_o, part_lse, (__nv_bfloat16*)out, rows, nsplit);
+    launch_pdl(attn_merge_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
+               (const float*)part_lse, (__nv_bfloat16*)out, rows, nsplit);
     e = cudaGetLastError();
   }
   return (int)e;

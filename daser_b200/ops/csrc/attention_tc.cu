@@ -102,6 +102,7 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
   const int tid = threadIdx.x, warp = tid >> 5;
   const int kvh = blockIdx.x, seq = blockIdx.y;
   const int grp = blockIdx.z / p.nsplit, sp = blockIdx.z % p.nsplit;
+  pdl_wait();  // launched ahead of its predecessor's end: nothing is read before this returns
   const int q0 = p.q_start[seq];
   const int q_len = p.q_start[seq + 1] - q0;
   const int ctx = p.ctx_lens[seq];
@@ -222,6 +223,7 @@ paged_attn_fp8_tc_kernel(const AttnParams p) {
     tc_fence_before();
     __syncthreads();  // barriers initialised, TMEM address published
     tc_fence_after();
+    pdl_launch_dependents();  // only now: this CTA holds its tensor memory, a successor cannot take it
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);
     constexpr uint32_t idesc_s = make_idesc_f16(128, TC_NK, 0);
@@ -451,7 +453,7 @@ int daser_launch_attention_tc(const daser::AttnParams& p, int max_q_len, cudaStr
   }
   const int groups = (max_q_len * p.G + 127) / 128;
   const dim3 grid(p.Hkv, p.num_seqs, groups * p.nsplit);
-  paged_attn_fp8_tc_kernel<<<grid, 128, TC_SMEM, stream>>>(p);
+  launch_pdl(paged_attn_fp8_tc_kernel, grid, dim3(128), TC_SMEM, stream, p);
   return (int)cudaGetLastError();
 }
 

@@ -5,6 +5,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define DASER_API extern "C" __attribute__((visibility("default")))
 
@@ -30,6 +31,49 @@ static inline bool daser_first_use_on_device(bool (&flags)[DASER_MAX_DEVICES]) {
 #define E4M3_MAX 448.0f
 
 namespace daser {
+
+// ---- programmatic dependent launch ----------------------------------------------------------
+// A serving step is a few hundred short kernels in one stream.  Launched the plain way, each
+// starts only after its predecessor has drained and the launch latency of every one of them is
+// exposed.  Kernels launched with `launch_pdl` may instead be scheduled while the predecessor
+// still runs: they run their set-up, call `pdl_wait()` (which returns once the predecessor has
+// completed and its writes are visible) and only then touch memory.  `pdl_launch_dependents()`
+// tells the scheduler that the NEXT kernel may be brought in; a kernel that holds tensor memory
+// calls it only after its own allocation, so that a successor can never take the columns a
+// not-yet-started CTA of this kernel still needs.
+// Every kernel that is launched with `launch_pdl` must execute `pdl_wait()` before its first
+// global-memory access.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+  pdl_launch_dependents();
+  pdl_wait();
+}
+
+inline bool pdl_allowed() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DASER_PDL");
+    v = (e == nullptr || e[0] != '0') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_allowed() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }

@@ -110,6 +110,7 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
                    int hidden, float eps, int zero_after, TpSync sync, int n_partials, int64_t partial_stride) {
   __shared__ float s_part[32];
   __shared__ int s_ok;
+  pdl_enter();
   const int64_t row = blockIdx.x;
   if (sync.wait_counter != nullptr) {
     // bounded wait for the other ranks' partial sums (a second or two, never for ever)
@@ -197,6 +198,7 @@ add_rmsnorm_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ residual,
 // epochs[i] += delta[i]: run at the end of a tensor-parallel forward so that the next
 // forward (or the next replay of the same captured graph) waits for fresh arrivals.
 __global__ void advance_epochs_kernel(uint32_t* epochs, uint32_t d0, uint32_t d1, uint32_t d2) {
+  pdl_enter();
   epochs[0] += d0;
   epochs[1] += d1;
   epochs[2] += d2;
@@ -244,6 +246,7 @@ rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* _
                      int block_tokens, DaserKVPool pool, int layer, int rank, int zero_after,
                      const __nv_bfloat16* __restrict__ q_norm_w = nullptr,
                      const __nv_bfloat16* __restrict__ k_norm_w = nullptr, float norm_eps = 0.f) {
+  pdl_enter();
   const int half = D >> 1;
   const int segs = half / FP8_GROUP;
   const int heads = Hq + 2 * Hkv;
@@ -340,6 +343,7 @@ rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* _
 template <typename TIn>
 __global__ void __launch_bounds__(256)
 swiglu_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ y, int64_t T, int inter, int zero_after, int block) {
+  pdl_enter();
   const int64_t total = T * (inter / 8);
   for (int64_t item = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; item < total;
        item += (int64_t)gridDim.x * blockDim.x) {
@@ -359,6 +363,7 @@ swiglu_kernel(TIn* __restrict__ x, __nv_bfloat16* __restrict__ y, int64_t T, int
 __global__ void __launch_bounds__(256)
 embedding_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                  __nv_bfloat16* __restrict__ out, int64_t T, int hidden, int vocab_begin, int vocab_count) {
+  pdl_enter();
   const int64_t total = T * (hidden / 8);
   for (int64_t item = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; item < total;
        item += (int64_t)gridDim.x * blockDim.x) {
@@ -485,7 +490,7 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
     for (int i = 0; i < tp->n_signal; ++i) sync.signal[i] = tp->signal[i];
   }
 #define NORM_LAUNCH(TIN, IT, MAXT)                                                                    \
-  add_rmsnorm_kernel<TIN, IT, MAXT><<<(unsigned)rows, threads, 0, stream>>>(                            \
+  launch_pdl(add_rmsnorm_kernel<TIN, IT, MAXT>, dim3((unsigned)rows), dim3(threads), 0, stream,         \
       (TIN*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, eps, \
       x_is_fp32 ? zero_after : 0, sync, n_partials < 1 ? 1 : n_partials, partial_stride)
 #define NORM_DISPATCH(TIN)                                                  \
@@ -500,9 +505,9 @@ DASER_API int daser_add_rmsnorm_tp(void* x, int x_is_fp32, void* residual, const
     // in-switch sum: bf16 only, and only the shapes a serving step has (rows of up to 16k values)
     if (iters > 2) return DASER_ERR_TOO_LARGE;
 #define NORM_LAUNCH_MC(IT, MAXT)                                                                             \
-  add_rmsnorm_kernel<__nv_bfloat16, IT, MAXT, true><<<(unsigned)rows, threads, 0, stream>>>(                   \
+  launch_pdl(add_rmsnorm_kernel<__nv_bfloat16, IT, MAXT, true>, dim3((unsigned)rows), dim3(threads), 0, stream, \
       (__nv_bfloat16*)x, (__nv_bfloat16*)residual, (const __nv_bfloat16*)weight, out, out_row_offset, hidden, \
-      eps, 0, sync, 1, 0)
+      eps, 0, sync, 1, (int64_t)0)
     if (few_rows && iters <= 1) NORM_LAUNCH_MC(1, 1024);
     else if (few_rows) NORM_LAUNCH_MC(2, 1024);
     else if (iters <= 1) NORM_LAUNCH_MC(1, 256);
@@ -544,8 +549,7 @@ DASER_API int daser_signal_flags(const uint64_t* flag_ptrs, int n, uint32_t valu
 
 DASER_API int daser_advance_epochs(uint32_t* epochs, uint32_t d0, uint32_t d1, uint32_t d2, cudaStream_t stream) {
   if (!epochs) return DASER_ERR_BAD_ARG;
-  daser::advance_epochs_kernel<<<1, 1, 0, stream>>>(epochs, d0, d1, d2);
-  return (int)cudaGetLastError();
+  return (int)daser::launch_pdl(daser::advance_epochs_kernel, dim3(1), dim3(1), 0, stream, epochs, d0, d1, d2);
 }
 
 // The same with RMSNorm over head_dim on every query and key head before the rotation
@@ -565,7 +569,7 @@ DASER_API int daser_rope_kv_write_qknorm(void* qkv, int qkv_is_fp32, int64_t qkv
   const int64_t items = (int64_t)T * (Hq + 2 * Hkv) * segs;
   const int grid = ew_grid(items, 128);
 #define LAUNCH_QK(TIN, FP8)                                                                        \
-  rope_kv_write_kernel<TIN, FP8, true><<<grid, 128, 0, stream>>>(                                  \
+  launch_pdl(rope_kv_write_kernel<TIN, FP8, true>, dim3(grid), dim3(128), 0, stream,               \
       (TIN*)qkv, qkv_stride, positions, slot_mapping, cos_sin, max_pos, (__nv_bfloat16*)q_out, T,  \
       Hq, Hkv, D, block_tokens, *pool, layer, rank, zero_after, (const __nv_bfloat16*)q_norm_w,    \
       (const __nv_bfloat16*)k_norm_w, eps)
@@ -587,9 +591,10 @@ DASER_API int daser_rope_kv_write(void* qkv, int qkv_is_fp32, int64_t qkv_stride
   const int64_t items = (int64_t)T * (Hq + 2 * Hkv) * (D / 32);
   const int grid = ew_grid(items, 128);
 #define LAUNCH(TIN, FP8)                                                                         \
-  rope_kv_write_kernel<TIN, FP8><<<grid, 128, 0, stream>>>(                                      \
+  launch_pdl(rope_kv_write_kernel<TIN, FP8>, dim3(grid), dim3(128), 0, stream,                   \
       (TIN*)qkv, qkv_stride, positions, slot_mapping, cos_sin, max_pos, (__nv_bfloat16*)q_out, T, \
-      Hq, Hkv, D, block_tokens, *pool, layer, rank, zero_after)
+      Hq, Hkv, D, block_tokens, *pool, layer, rank, zero_after, (const __nv_bfloat16*)nullptr,    \
+      (const __nv_bfloat16*)nullptr, 0.f)
   if (qkv_is_fp32) { if (pool->pool_is_fp8) LAUNCH(float, true); else LAUNCH(float, false); }
   else { if (pool->pool_is_fp8) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false); }
 #undef LAUNCH
@@ -603,9 +608,11 @@ DASER_API int daser_swiglu(void* x, int x_is_fp32, void* y, int64_t T, int inter
   if (block < 0 || (block && (block % 8 || inter % block))) return DASER_ERR_BAD_ARG;
   if (T == 0) return 0;
   const int grid = ew_grid(T * (inter / 8), 256);
-  if (x_is_fp32) swiglu_kernel<float><<<grid, 256, 0, stream>>>((float*)x, (__nv_bfloat16*)y, T, inter, zero_after, block);
-  else swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)x, (__nv_bfloat16*)y, T, inter, 0, block);
-  return (int)cudaGetLastError();
+  if (x_is_fp32)
+    return (int)launch_pdl(swiglu_kernel<float>, dim3(grid), dim3(256), 0, stream, (float*)x, (__nv_bfloat16*)y, T, inter,
+                           zero_after, block);
+  return (int)launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (__nv_bfloat16*)x,
+                         (__nv_bfloat16*)y, T, inter, 0, block);
 }
 
 DASER_API int daser_embedding(const int32_t* ids, const void* table, void* out, int64_t T, int hidden,
@@ -613,9 +620,8 @@ DASER_API int daser_embedding(const int32_t* ids, const void* table, void* out, 
   using namespace daser;
   if (T < 0 || hidden <= 0 || hidden % 8) return DASER_ERR_BAD_ARG;
   if (T == 0) return 0;
-  embedding_kernel<<<ew_grid(T * (hidden / 8), 256), 256, 0, stream>>>(
-      ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, hidden, vocab_begin, vocab_count);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(embedding_kernel, dim3(ew_grid(T * (hidden / 8), 256)), dim3(256), 0, stream, ids,
+                         (const __nv_bfloat16*)table, (__nv_bfloat16*)out, T, hidden, vocab_begin, vocab_count);
 }
 
 // Temperature sampling (Gumbel-max): inv_temp[rows] = 1 / temperature (0 = greedy for that row),

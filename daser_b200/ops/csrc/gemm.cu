@@ -153,6 +153,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   sm100::tc_fence_before();
   __syncthreads();
   sm100::tc_fence_after();
+  // This CTA holds its tensor memory: the next kernel of the stream may be scheduled (it parks
+  // in griddepcontrol.wait until this grid has completed).
+  pdl_launch_dependents();
   const uint32_t tmem_base = *tmem_base_slot;
 
   if (warp == 0) {
@@ -424,14 +427,7 @@ static int make_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t c
   return r == CUDA_SUCCESS ? 0 : DASER_ERR_BAD_ARG;
 }
 
-static bool pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("DASER_PDL");
-    v = (e == nullptr || e[0] != '0') ? 1 : 0;
-  }
-  return v == 1;
-}
+static bool pdl_enabled() { return pdl_allowed(); }
 
 template <int BN, int STAGES>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {

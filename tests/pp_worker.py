@@ -63,7 +63,7 @@ def main() -> None:
     rng = random.Random(0)
     chunks = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (64, 96)]
     query = [rng.randrange(cfg.vocab_size) for _ in range(12)]
-    ok = eng.runner.layers == range(rank * cfg.num_layers // stages, (rank + 1) * cfg.num_layers // stages)
+    checks = {"layers": eng.runner.layers == range(rank * cfg.num_layers // stages, (rank + 1) * cfg.num_layers // stages)}
     cold = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=4)  # nothing stored: all computed
     for c in chunks:
         eng.store_chunk(c)  # every stage writes its layers, the chunk appears when both have committed
@@ -73,10 +73,14 @@ def main() -> None:
     filed = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=4)  # from the stages' store files
     warm = eng.generate([chunks[1], chunks[0]], query, max_new_tokens=4)  # from the stages' HBM tiers
     eng.runner.check_status()
-    ok = ok and cold.restored_chunks == 0 and filed.restored_chunks == 2 and warm.restored_chunks == 2
-    ok = ok and filed.generated == warm.generated and len(cold.generated) == 4
+    checks["restored"] = (cold.restored_chunks, filed.restored_chunks, warm.restored_chunks) == (0, 2, 2)
+    checks["file_equals_tier"] = filed.generated == warm.generated and len(cold.generated) == 4
     everyone = link.gather_object((cold.generated, filed.generated))
-    ok = ok and all(e == everyone[0] for e in everyone)  # every stage learned the same tokens
+    checks["same_on_every_stage"] = all(e == everyone[0] for e in everyone)
+    ok = all(checks.values())
+    if not ok:
+        print(f"stage {rank}: {checks} restored={cold.restored_chunks, filed.restored_chunks, warm.restored_chunks} "
+              f"filed={filed.generated} warm={warm.generated}", flush=True)
     eng.close()
     if rank == 0:
         # the whole model on one GPU, same seed: same weights tensor by tensor

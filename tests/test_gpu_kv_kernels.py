@@ -210,3 +210,65 @@ def test_restore_and_save_stay_inside_their_buffers(pool_fp8):
     for buf in (raw_pool, raw_scales, raw_staging):
         assert bool((buf[:guard] == 0xA5).all()) and bool((buf[-guard:] == 0xA5).all())
     assert bool((payload.view(torch.uint8) != 0xA5).any())  # the kernels did write
+
+
+def test_restore_by_layer_groups_equals_one_launch():
+    """The pipelined restore launches the kernel once per group of layers: together the pieces
+    write exactly what one launch over all layers writes, and a piece touches no other layer."""
+    kv_ops = _ops()
+    torch.manual_seed(4)
+    geo = KVGeometry(num_layers=6, num_kv_heads=8, head_dim=128, block_tokens=16, dtype_bytes=2, codec="fp8b16")
+    n_slots, n_blocks = 7, 16
+    staging = torch.randint(0, 256, (n_slots, geo.slot_size), dtype=torch.uint8)
+    # plausible scales (the payload bytes may be anything but NaN patterns: keep exponents small)
+    per_layer = staging.view(n_slots, geo.num_layers, geo.layer_size)
+    per_layer[..., : geo.payload_bytes_per_layer] &= 0x77
+    sc = torch.rand(n_slots, geo.num_layers, (geo.layer_size - geo.payload_bytes_per_layer) // 4) * 0.01 + 0.001
+    per_layer[..., geo.payload_bytes_per_layer :] = sc.view(torch.uint8).view(n_slots, geo.num_layers, -1)
+    staging = staging.cuda()
+    work = kv_ops.KVWorkList(
+        slot_ptrs=torch.tensor([staging.data_ptr() + i * geo.slot_size for i in range(n_slots)], dtype=torch.int64, device="cuda"),
+        block_ids=torch.tensor([3, 9, 0, 15, 7, 1, 12], dtype=torch.int32, device="cuda"),
+        deltas=torch.tensor([0, 40, 0, -3, 7, 0, 100], dtype=torch.int32, device="cuda"),
+    )
+    cos_sin = kv_ops.rope_table(256, inv_freq_table(128, 500000.0), "cuda")
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for tp in (1, 2):
+        pa, sa = _make_pool(geo, n_blocks, tp, True, "LNKHTD")
+        pb, sb = _make_pool(geo, n_blocks, tp, True, "LNKHTD")
+        kv_ops.kv_restore(work, geo, kv_ops.PagedKVPool.from_tensors(pa, sa, "LNKHTD"), cos_sin, status)
+        pool_b = kv_ops.PagedKVPool.from_tensors(pb, sb, "LNKHTD")
+        kv_ops.kv_restore(work, geo, pool_b, cos_sin, status, layer_begin=0, layer_count=1)
+        torch.cuda.synchronize()
+        assert all(bool((t[1:] == 0).all()) for t in pb)  # only layer 0 so far
+        assert all(torch.equal(x[0], y[0]) for x, y in zip(pa, pb))
+        kv_ops.kv_restore(work, geo, pool_b, cos_sin, status, layer_begin=1, layer_count=3)
+        kv_ops.kv_restore(work, geo, pool_b, cos_sin, status, layer_begin=4, layer_count=0)  # 0 = through the last
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0]
+        for x, y in zip(pa + sa, pb + sb):
+            assert torch.equal(x, y)
+        assert any(bool(t.any()) for t in pa)
+    with pytest.raises(Exception):
+        kv_ops.kv_restore(work, geo, pool_b, cos_sin, status, layer_begin=5, layer_count=3)
+
+
+def test_copy_rows_and_flag_signalling():
+    from daser_b200.ops import elementwise as ew
+
+    kv_ops = _ops()
+    src = torch.arange(8 * 64, dtype=torch.int32).view(torch.uint8).clone().pin_memory()
+    dst = torch.zeros(src.numel(), dtype=torch.uint8, device="cuda")
+    pitch = src.numel() // 8
+    kv_ops.copy_rows(dst.data_ptr() + 16, src.data_ptr() + 16, pitch, 48, 8)  # bytes [16, 64) of each of 8 rows
+    torch.cuda.synchronize()
+    got, want = dst.cpu().view(8, pitch), src.view(8, pitch)
+    assert torch.equal(got[:, 16:64], want[:, 16:64]) and not got[:, :16].any() and not got[:, 64:].any()
+    # signal then wait on the same stream: the wait finds the value; a wait for more runs out
+    # (bounded) and reports through the status word, and the stream stays usable
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ew.signal_flags([flags.data_ptr() + 4 * i for i in range(3)], 5)
+    ew.wait_flags(flags.data_ptr(), 3, 5, status)
+    torch.cuda.synchronize()
+    assert flags.tolist() == [5, 5, 5, 0, 0, 0, 0, 0] and status[0].item() == 0
