@@ -119,6 +119,7 @@ def main() -> None:
     ap.add_argument("--max-tokens", type=int, default=1024, help="tokens per forward (chunk fills, missed chunks)")
     ap.add_argument("--extras", type=int, default=1, help="0: skip the untimed extra measurements after the timed region")
     ap.add_argument("--open-loop-requests", type=int, default=16)
+    ap.add_argument("--kv-blocks", type=int, default=6144, help="blocks of 16 tokens in the paged KV pool")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -192,7 +193,9 @@ def main() -> None:
     # each rank holds 1 / world of the tier budget (it owns 1 / world of the chunks)
     hbm_slots = max(64, int(pool_slots * args.hbm_frac / world)) if args.hbm_frac > 0 else 0
     host_slots = max(64, int(pool_slots * args.host_frac / world)) if args.host_frac > 0 else 0
-    eng = GpuRagEngine(cfg, dcfg.ipc_socket_path, dcfg.store_path, num_blocks=2 * blocks_per_req + 256,
+    # the paged pool holds the open-loop phase's concurrent requests (4 req/s x 128 output tokens:
+    # about twenty of ~230 blocks each at TP = 1); 6144 blocks = 20 GB of fp8 KV over all ranks
+    eng = GpuRagEngine(cfg, dcfg.ipc_socket_path, dcfg.store_path, num_blocks=args.kv_blocks,
                        max_tokens=args.max_tokens, max_seqs=32, hbm_slots=hbm_slots, host_slots=host_slots,
                        io_backend=args.io_backend, tp_ctx=tp_ctx, staging_slots=max(blocks_per_req, 128),
                        max_blocks=blocks_per_req + 16, layer_groups=args.layer_groups)

@@ -82,6 +82,8 @@ PRESETS = {
                               1e-5, 16, 131072),
     # small GPU test model with the 70B head geometry
     "tiny-gqa": LlamaConfig("tiny-gqa", 1024, 512, 2, 8, 2, 128, 1024, 500000.0, (), 1e-5, 16, 8192),
+    # the same with 8 KV heads, so that it shards 8 ways (2 query heads + 1 KV head per rank)
+    "tiny-8kv": LlamaConfig("tiny-8kv", 1024, 1024, 2, 16, 8, 128, 2048, 500000.0, (), 1e-5, 16, 8192),
     # the model of the reference's own end-to-end runs (tests/integration/conftest.py:30 there:
     # 36 layers x 8 KV heads x 128 x 16 tokens x bf16 x 2 = 2 359 296 bytes per slot)
     "qwen3-8b": LlamaConfig("qwen3-8b", 151936, 4096, 36, 32, 8, 128, 12288, 1000000.0, (), 1e-6, 16, 40960, True),

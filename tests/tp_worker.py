@@ -33,7 +33,8 @@ def main() -> None:
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     tp = dist.get_world_size()
-    cfg = PRESETS["tiny-gqa"]
+    # tiny-gqa has 2 KV heads; beyond 2 ranks use the model with 8 (DASER_TP_TEST_MODEL overrides)
+    cfg = PRESETS[os.environ.get("DASER_TP_TEST_MODEL", "tiny-gqa" if tp <= 2 else "tiny-8kv")]
     full = LlamaWeights.random(cfg, "cuda", torch.bfloat16, seed=5, std=0.05)  # same on every rank
     ctx = TPContext(cfg, dist.group.WORLD, max_tokens=128)
     rng = random.Random(0)
