@@ -210,6 +210,8 @@ class GpuRagEngine(SchedulingMixin):
         meta = self._bcast(meta)
         self._prefill_tokens(tokens, 0, table)
         self._save(meta)
+        if self.pp_link is not None:
+            self.pp_link.barrier()  # every stage has committed its part: the chunk is visible when this returns
         if self.sched is not None:
             self.sched.request_finished(req)
         self.blocks.free(table)

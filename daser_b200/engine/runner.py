@@ -135,6 +135,11 @@ class GpuModelRunner:
         self.attn_ws = attention.AttentionWorkspace(dev)
         self.attn_ws.ensure(attention.MAX_ROW_SPLITS, 1, D)  # sized once: captured graphs keep its address
         self.status = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=dev)  # split-K "last CTA of a tile" counts
+        import os as _os
+
+        self.fuse_qkv_rope = (gemm.can_fuse_qkv_rope(D, cfg.qk_norm) and _os.environ.get("DASER_FUSE_QKV_ROPE", "1") != "0"
+                              and -(-max_tokens // 128) * -(-qkv_n // 128) <= self.tile_counters.numel())
         self.softmax_scale = D**-0.5
         # ---- persistent step inputs (pinned host mirror + device copy) ----
         self.max_blocks = max_blocks
@@ -173,12 +178,35 @@ class GpuModelRunner:
             return None
         return (lw.q_norm, lw.k_norm, self.cfg.rms_eps)
 
+    def qkv_rope(self, x: torch.Tensor, lw, inp: "StepInputs", T: int, pool_layer: int, **gate) -> None:
+        """QKV projection, RoPE and the KV-cache write: ``self.q_rot[:T]`` holds the rotated queries,
+        the step's keys and values are in the paged pool.  One kernel (the GEMM's epilogue does the
+        rest) when a 128-column tile is a head and the model has no per-head norm, else GEMM + kernel."""
+        D, B = self.cfg.head_dim, self.cfg.block_tokens
+        if self.fuse_qkv_rope:
+            gemm.linear_qkv_rope(x, lw.wqkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq,
+                                 self.hkv, B, self.local_pool, pool_layer, 0, self.qkv_acc, self.tile_counters,
+                                 status=self.status, **gate)
+            return
+        bn, ks = gemm.plan_tiles(T, lw.wqkv.shape[0], lw.wqkv.shape[1], allow_split=True)
+        if ks > 1:
+            gemm.linear(x, lw.wqkv, acc=self.qkv_acc[:T], block_n=bn, k_splits=ks, status=self.status, **gate)
+            qkv, f32 = self.qkv_acc[:T], True
+        else:
+            gemm.linear(x, lw.wqkv, out=self.qkv_bf[:T], block_n=bn, k_splits=1, status=self.status, **gate)
+            qkv, f32 = self.qkv_bf[:T], False
+        ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq, self.hkv, D, B,
+                         self.local_pool, pool_layer, 0, zero_after=f32, qk_norm=self.qk_norm(lw))
+
     def mlp_up(self, x: torch.Tensor, lw, T: int, **gate) -> torch.Tensor:
         """``silu(x Wg^T) * (x Wu^T)`` into ``self.act[:T]``: one GEMM with the activation as its
         epilogue when the weights are interleaved and the shape runs unsplit, else GEMM + kernel."""
         w = self.w
-        if w.gate_up_block == gemm.GATE_UP_BLOCK and gemm.can_fuse_swiglu(T, lw.w_gate_up.shape[0], lw.w_gate_up.shape[1]):
-            return gemm.linear_swiglu(x, lw.w_gate_up, self.act[:T], status=self.status, **gate)
+        n2, k = lw.w_gate_up.shape
+        if w.gate_up_block == gemm.GATE_UP_BLOCK and gemm.can_fuse_swiglu(T, n2, k, split_ok=True):
+            _, ks = gemm.plan_tiles(T, n2, k, allow_split=True)
+            return gemm.linear_swiglu(x, lw.w_gate_up, self.act[:T], status=self.status, k_splits=ks,
+                                      work=self.gu_acc, tile_counters=self.tile_counters, **gate)
         bn, ks = gemm.plan_tiles(T, lw.w_gate_up.shape[0], lw.w_gate_up.shape[1], allow_split=True)
         if ks > 1:
             gemm.linear(x, lw.w_gate_up, acc=self.gu_acc[:T], block_n=bn, k_splits=ks, status=self.status, **gate)
@@ -319,9 +347,7 @@ class GpuModelRunner:
         for li in range(l0, l1):
             lw = w.layers[li]
             pl = li - first  # layer index inside this stage's pool
-            qkv, f32 = self._linear(normed, lw.wqkv, self.qkv_acc, self.qkv_bf)
-            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos_sin, self.q_rot[:T], self.hq,
-                             self.hkv, D, B, self.local_pool, pl, 0, zero_after=f32, qk_norm=self.qk_norm(lw))
+            self.qkv_rope(normed, lw, inp, T, pl)
             attn = self.attn_out[:T].view(T, self.hq, D)
             attention.paged_attention(self.q_rot[:T], attn, self.local_pool, pl, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, self.hkv, self.softmax_scale,

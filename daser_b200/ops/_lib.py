@@ -92,6 +92,17 @@ class Gemm(C.Structure):
         ("work_ld", C.c_int64),
         ("tile_counters", C.c_void_p),
         ("bcast", C.c_int32),
+        ("rope_positions", C.c_void_p),
+        ("rope_slot_mapping", C.c_void_p),
+        ("rope_cos_sin", C.c_void_p),
+        ("rope_q_out", C.c_void_p),
+        ("rope_pool", C.c_void_p),
+        ("rope_max_pos", C.c_int32),
+        ("rope_hq", C.c_int32),
+        ("rope_hkv", C.c_int32),
+        ("rope_block_tokens", C.c_int32),
+        ("rope_layer", C.c_int32),
+        ("rope_rank", C.c_int32),
     ]
 
 

@@ -11,6 +11,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 #include "kv_paged.h"
 
 namespace daser {
@@ -286,55 +287,11 @@ rope_kv_write_kernel(TIn* __restrict__ qkv, int64_t qkv_stride, const int32_t* _
         x2[i] = __bfloat162float(__float2bfloat16(x2[i] * inv * __bfloat162float(w[half + i])));
       }
     }
-    if (!is_v) {
-      int pos = positions[t];
-      pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-      const float* cs = cos_sin + (int64_t)pos * D + j * FP8_GROUP;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float c = cs[i], s = cs[half + i];
-        const float a = x1[i], b = x2[i];
-        x1[i] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-        x2[i] = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
-      }
-    }
-    if (hd < Hq) {
-      __nv_bfloat16* dst = q_out + ((int64_t)t * Hq + hd) * D + j * FP8_GROUP;
-      store_bf16x16(dst, x1);
-      store_bf16x16(dst + half, x2);
-      continue;
-    }
-    const int64_t sm = slot_mapping[t];
-    if (sm < 0) continue;
-    const int block = (int)(sm / block_tokens), tok = (int)(sm % block_tokens);
-    if (block >= pool.num_blocks) continue;
-    const int kv = is_v ? 1 : 0;
-    const int hl = is_v ? hd - Hq - Hkv : hd - Hq;
-    const int64_t d1 = (int64_t)layer * pool.stride_layer + (int64_t)block * pool.stride_block +
-                       (int64_t)kv * pool.stride_kv + (int64_t)tok * pool.stride_tok +
-                       (int64_t)hl * pool.stride_head + j * FP8_GROUP;
-    const int64_t d2 = d1 + half;
-    if (POOL_FP8) {
-      uint4 q1, q2;
-      float s1, s2;
-      // quantise what a bf16 pool would have held, so both pool kinds see the same values
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        x1[i] = __bfloat162float(__float2bfloat16(x1[i]));
-        x2[i] = __bfloat162float(__float2bfloat16(x2[i]));
-      }
-      quant_group16(x1, q1, s1);
-      quant_group16(x2, q2, s2);
-      uint8_t* p = reinterpret_cast<uint8_t*>(pool.payload[rank]);
-      *reinterpret_cast<uint4*>(p + d1) = q1;
-      *reinterpret_cast<uint4*>(p + d2) = q2;
-      pool.scales[rank][d1 / FP8_GROUP] = s1;
-      pool.scales[rank][d2 / FP8_GROUP] = s2;
-    } else {
-      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(pool.payload[rank]);
-      store_bf16x16(p + d1, x1);
-      store_bf16x16(p + d2, x2);
-    }
+    RopeKvWrite r;
+    r.positions = positions; r.slot_mapping = slot_mapping; r.cos_sin = cos_sin; r.max_pos = max_pos;
+    r.q_out = q_out; r.Hq = Hq; r.Hkv = Hkv; r.D = D; r.block_tokens = block_tokens;
+    r.pool = pool; r.layer = layer; r.rank = rank;
+    rope_kv_write_item<POOL_FP8>(r, x1, x2, t, hd, j);
   }
 }
 

@@ -37,7 +37,16 @@
 //   EPI_SWIGLU_BF16  the gate/up projection with its activation: the weight rows of every BN-row
 //                    tile are BN/2 gate rows followed by the BN/2 up rows of the same outputs
 //                    (the loader interleaves them), so one CTA holds both halves in TMEM and
-//                    stores silu(gate) * up as bf16 [M, N/2]; k_splits must be 1.
+//                    stores silu(gate) * up as bf16 [M, N/2].  With split-K the partials are added
+//                    into the fp32 work buffer and the CTA that completes a tile applies the
+//                    activation (and hands the buffer back zeroed).
+//   EPI_QKV_ROPE     the QKV projection with what follows it: BN = head_dim = 128, so a tile is one
+//                    head of up to 128 tokens and an epilogue thread holds one token's head.  Query
+//                    heads are rotated and stored as bf16, key heads rotated, value heads as they
+//                    are, both quantised into the paged KV pool at the token's slot (rope.cuh: the
+//                    same code the stand-alone kernel runs).  Unsplit, the values come straight from
+//                    tensor memory; with split-K the partials are added into the fp32 work buffer
+//                    and the CTA that completes a tile does the rest (and hands the buffer back zeroed).
 //   EPI_SPLITK_SCATTER  split-K and the bf16 scatter in one kernel: every K split adds its
 //                    partial tile into a local fp32 work buffer; the CTA that finishes a tile
 //                    last (per-tile counter) reads the sum back, hands the work buffer back
@@ -48,8 +57,10 @@
 // TMEM and returns.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 #include "tcgen05.cuh"
 
 namespace daser {
@@ -58,7 +69,7 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;  // 64 bf16 = 128 B = one swizzle row
 constexpr int GEMM_THREADS = 192;
 
-enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1, EPI_SPLITK_SCATTER = 2, EPI_SWIGLU_BF16 = 3 };
+enum { EPI_STORE_BF16 = 0, EPI_REDUCE_F32 = 1, EPI_SPLITK_SCATTER = 2, EPI_SWIGLU_BF16 = 3, EPI_QKV_ROPE = 4 };
 
 struct GemmParams {
   int M, N, K;
@@ -85,6 +96,8 @@ struct GemmParams {
   const uint32_t* gate_base;
   uint32_t gate_target;
   int gate_rows;
+  RopeKvWrite rope;   // EPI_QKV_ROPE
+  int rope_pool_fp8;
 };
 
 __device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
@@ -250,7 +263,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < p.M;
       const int owner = row_ok ? row / p.rows_per_owner : 0;
       const int64_t local_row = row_ok ? row - (int64_t)owner * p.rows_per_owner : 0;
-      if (p.epilogue == EPI_SWIGLU_BF16) {
+      const bool swiglu_split = p.epilogue == EPI_SWIGLU_BF16 && p.k_splits > 1;
+      if (p.epilogue == EPI_SWIGLU_BF16 && !swiglu_split) {
         if constexpr (BN >= 64) {
           // columns [0, BN/2) of the tile are gate, [BN/2, BN) the matching up values
 #pragma unroll 1
@@ -280,7 +294,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
-      const int n_chunks = p.epilogue == EPI_SWIGLU_BF16 ? 0 : BN / 32;  // (the activation epilogue is done)
+      const bool rope_split = p.epilogue == EPI_QKV_ROPE && p.k_splits > 1;
+      if (p.epilogue == EPI_QKV_ROPE && !rope_split) {
+        if constexpr (BN == 128) {
+          const int hd = n0 / 128;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            // columns [32c, 32c + 32) and their rotary partners [64 + 32c, 64 + 32c + 32)
+            uint32_t ra[32], rb[32];
+            sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), ra);
+            sm100::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(64 + c * 32), rb);
+            sm100::tmem_ld_wait();
+            if (!row_ok) continue;
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {
+              float x1[16], x2[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                x1[i] = __uint_as_float(ra[16 * jj + i]);
+                x2[i] = __uint_as_float(rb[16 * jj + i]);
+              }
+              if (p.rope_pool_fp8) rope_kv_write_item<true>(p.rope, x1, x2, row, hd, 2 * c + jj);
+              else rope_kv_write_item<false>(p.rope, x1, x2, row, hd, 2 * c + jj);
+            }
+          }
+        }
+      }
+      const bool splitk_tail = p.epilogue == EPI_SPLITK_SCATTER || rope_split || swiglu_split;  // partials meet in `work`
+      const int n_chunks = ((p.epilogue == EPI_SWIGLU_BF16 && !swiglu_split) || (p.epilogue == EPI_QKV_ROPE && !rope_split))
+                               ? 0 : BN / 32;  // (those epilogues are done)
 #pragma unroll 1
       for (int c = 0; c < n_chunks; ++c) {
         uint32_t r[32];
@@ -307,7 +349,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               if (col0 + v * 8 < p.N) *reinterpret_cast<uint4*>(dst + v * 8) = o[v];
           }
         } else {
-          float* dst = p.epilogue == EPI_SPLITK_SCATTER
+          float* dst = splitk_tail
                            ? p.work + (int64_t)row * p.work_ld + col0
                            : reinterpret_cast<float*>(p.c[owner]) + local_row * p.ldc + col0;
 #pragma unroll
@@ -319,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
       bool signal = p.arrive[0] != nullptr;
-      if (p.epilogue == EPI_SPLITK_SCATTER) {
+      if (splitk_tail) {
         // Which CTA completes this tile?  (uniform over the 128 epilogue threads: a named
         // barrier is safe here because `ok` is true for all of them or for none)
         __threadfence();
@@ -335,7 +377,64 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         signal = signal && (*s_last != 0u);
-        if (*s_last != 0u && row_ok) {
+        if (*s_last != 0u && row_ok && rope_split) {
+          __threadfence();
+          if constexpr (BN == 128) {
+            const int hd = n0 / 128;
+#pragma unroll 1
+            for (int j = 0; j < 4; ++j) {
+              float* s1 = p.work + (int64_t)row * p.work_ld + n0 + j * FP8_GROUP;
+              float* s2 = s1 + 64;
+              float x1[16], x2[16];
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(s1 + 4 * v));
+                const float4 b = __ldcg(reinterpret_cast<const float4*>(s2 + 4 * v));
+                x1[4 * v] = a.x; x1[4 * v + 1] = a.y; x1[4 * v + 2] = a.z; x1[4 * v + 3] = a.w;
+                x2[4 * v] = b.x; x2[4 * v + 1] = b.y; x2[4 * v + 2] = b.z; x2[4 * v + 3] = b.w;
+              }
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {  // the work buffer goes back zeroed
+                *reinterpret_cast<float4*>(s1 + 4 * v) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(s2 + 4 * v) = make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+              if (p.rope_pool_fp8) rope_kv_write_item<true>(p.rope, x1, x2, row, hd, j);
+              else rope_kv_write_item<false>(p.rope, x1, x2, row, hd, j);
+            }
+          }
+        } else if (*s_last != 0u && row_ok && swiglu_split) {
+          __threadfence();
+          if constexpr (BN >= 64) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 64; ++c) {
+              float* gs = p.work + (int64_t)row * p.work_ld + n0 + c * 32;  // gate columns of the tile
+              float* us = gs + BN / 2;                                      // the matching up columns
+              const int col0 = (n0 >> 1) + c * 32;                          // output column
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c[0]) + (int64_t)row * p.ldc + col0;
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (2 * (col0 + v * 8) >= p.N) continue;
+                const float4 g0 = __ldcg(reinterpret_cast<const float4*>(gs + v * 8));
+                const float4 g1 = __ldcg(reinterpret_cast<const float4*>(gs + v * 8 + 4));
+                const float4 u0 = __ldcg(reinterpret_cast<const float4*>(us + v * 8));
+                const float4 u1 = __ldcg(reinterpret_cast<const float4*>(us + v * 8 + 4));
+                *reinterpret_cast<float4*>(gs + v * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(gs + v * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(us + v * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4*>(us + v * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = gv[i] / (1.f + __expf(-gv[i])) * uv[i];
+                uint4 w;
+                w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]);
+                w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
+                *reinterpret_cast<uint4*>(dst + v * 8) = w;
+              }
+            }
+          }
+        } else if (*s_last != 0u && row_ok) {
           __threadfence();
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
@@ -482,6 +581,13 @@ typedef struct {
   int32_t bcast;  // 1: the bf16 epilogues store to every c[i] (row + dst_row_offset) and bump every arrive[i];
                   // 2: they store to c[0] only and bump every arrive[i] (the partial stays in this rank's
                   //    memory; peers fetch the sum with multimem.ld_reduce once all counters are up)
+  // epilogue 4 (QKV projection + RoPE + paged KV write); N = (rope_hq + 2 * rope_hkv) * 128, block_n = 128
+  const int32_t* rope_positions;
+  const int64_t* rope_slot_mapping;
+  const float* rope_cos_sin;
+  void* rope_q_out;
+  const DaserKVPool* rope_pool;
+  int32_t rope_max_pos, rope_hq, rope_hkv, rope_block_tokens, rope_layer, rope_rank;
 } DaserGemm;
 
 DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
@@ -490,7 +596,15 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   if (g->K % 8 || g->N % 8) return DASER_ERR_UNSUPPORTED;
   if (g->epilogue == EPI_STORE_BF16 && g->k_splits != 1) return DASER_ERR_BAD_ARG;
   if (g->epilogue == EPI_SWIGLU_BF16 &&
-      (g->k_splits != 1 || g->block_n < 64 || g->N % g->block_n || g->n_owners != 1)) return DASER_ERR_BAD_ARG;
+      (g->block_n < 64 || g->N % g->block_n || g->n_owners != 1 ||
+       (g->k_splits != 1 && (!g->work || !g->tile_counters)))) return DASER_ERR_BAD_ARG;
+  if (g->epilogue == EPI_QKV_ROPE) {
+    if (g->block_n != 128 || !g->rope_pool || !g->rope_positions || !g->rope_slot_mapping || !g->rope_cos_sin ||
+        !g->rope_q_out || g->rope_max_pos <= 0 || g->rope_block_tokens <= 0) return DASER_ERR_BAD_ARG;
+    if (g->N != (g->rope_hq + 2 * g->rope_hkv) * 128 || g->rope_rank < 0 || g->rope_rank >= DASER_MAX_RANKS)
+      return DASER_ERR_BAD_ARG;
+    if (g->k_splits > 1 && (!g->work || !g->tile_counters)) return DASER_ERR_BAD_ARG;
+  }
   if (g->n_owners < 1 || g->n_owners > DASER_MAX_RANKS) return DASER_ERR_BAD_ARG;
   if (g->rows_per_owner <= 0 || (int64_t)g->rows_per_owner * g->n_owners < g->M) return DASER_ERR_BAD_ARG;
   if (g->gate_flags && g->gate_rows <= 0) return DASER_ERR_BAD_ARG;
@@ -514,6 +628,16 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   p.gate_target = g->gate_target;
   p.gate_base = g->gate_base;
   p.gate_rows = g->gate_rows > 0 ? g->gate_rows : 1;
+  memset(&p.rope, 0, sizeof(p.rope));
+  p.rope_pool_fp8 = 0;
+  if (g->epilogue == EPI_QKV_ROPE) {
+    p.rope.positions = g->rope_positions; p.rope.slot_mapping = g->rope_slot_mapping;
+    p.rope.cos_sin = g->rope_cos_sin; p.rope.max_pos = g->rope_max_pos;
+    p.rope.q_out = (__nv_bfloat16*)g->rope_q_out;
+    p.rope.Hq = g->rope_hq; p.rope.Hkv = g->rope_hkv; p.rope.D = 128; p.rope.block_tokens = g->rope_block_tokens;
+    p.rope.pool = *g->rope_pool; p.rope.layer = g->rope_layer; p.rope.rank = g->rope_rank;
+    p.rope_pool_fp8 = g->rope_pool->pool_is_fp8;
+  }
   CUtensorMap ta, tb;
   if (int e = make_tmap(&ta, g->a, g->M, g->K, g->lda, GEMM_BM)) return e;
   if (int e = make_tmap(&tb, g->b, g->N, g->K, g->ldb, g->block_n)) return e;

@@ -27,6 +27,7 @@ EPI_STORE_BF16 = 0
 EPI_REDUCE_F32 = 1
 EPI_SPLITK_SCATTER = 2
 EPI_SWIGLU_BF16 = 3
+EPI_QKV_ROPE = 4
 GATE_UP_BLOCK = 64  # gate/up rows are interleaved in blocks of this many (half of a 128-row tile)
 
 
@@ -165,6 +166,47 @@ def linear(
     return result
 
 
+def can_fuse_qkv_rope(head_dim: int, qk_norm: bool) -> bool:
+    """The QKV projection can end in RoPE + the paged KV write when a 128-column tile is one head
+    and no per-head norm sits between the projection and the rotation."""
+    return head_dim == 128 and not qk_norm
+
+
+def linear_qkv_rope(x: torch.Tensor, wqkv: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor,
+                    cos_sin: torch.Tensor, q_out: torch.Tensor, hq: int, hkv: int, block_tokens: int, pool, layer: int,
+                    rank: int, work: torch.Tensor, tile_counters: torch.Tensor, k_splits: Optional[int] = None,
+                    status: Optional[torch.Tensor] = None, gate_flags: Optional[int] = None, gate_target: int = 0,
+                    gate_rows: int = 0, gate_base: Optional[int] = None, stream=None) -> None:
+    """``x @ wqkv.T`` with RoPE and the KV-cache write as the GEMM's epilogue.
+
+    Query heads land rotated in ``q_out`` (bf16 ``[T, hq, 128]``); key heads are rotated and, like
+    the value heads, quantised into ``pool`` at ``slot_mapping``.  ``work`` (fp32 ``[>= T, N]``,
+    zero) and ``tile_counters`` (int32, zero) serve the split-K case and come back zeroed."""
+    assert x.dtype == torch.bfloat16 and wqkv.dtype == torch.bfloat16 and x.stride(1) == 1 and wqkv.stride(1) == 1
+    M, K = x.shape
+    N = wqkv.shape[0]
+    assert N == (hq + 2 * hkv) * 128 and q_out.dtype == torch.bfloat16 and q_out.is_contiguous()
+    assert work.dtype == torch.float32 and work.shape[1] >= N and work.shape[0] >= M
+    _, ks = plan_tiles(M, N, K, allow_split=True)
+    ks = k_splits or ks
+    g = Gemm()
+    g.a, g.b = x.data_ptr(), wqkv.data_ptr()
+    g.lda, g.ldb, g.ldc = x.stride(0), wqkv.stride(0), N
+    g.M, g.N, g.K = M, N, K
+    g.block_n, g.k_splits, g.epilogue = 128, ks, EPI_QKV_ROPE
+    g.n_owners, g.rows_per_owner = 1, max(M, 1)
+    g.work, g.work_ld, g.tile_counters = work.data_ptr(), work.stride(0), tile_counters.data_ptr()
+    g.status = status.data_ptr() if status is not None else None
+    g.gate_flags, g.gate_target, g.gate_rows, g.gate_base = gate_flags, gate_target, gate_rows, gate_base
+    pool_c = pool.c_struct()
+    g.rope_positions, g.rope_slot_mapping = positions.data_ptr(), slot_mapping.data_ptr()
+    g.rope_cos_sin, g.rope_q_out = cos_sin.data_ptr(), q_out.data_ptr()
+    g.rope_pool = C.addressof(pool_c)
+    g.rope_max_pos, g.rope_hq, g.rope_hkv = int(cos_sin.shape[0]), hq, hkv
+    g.rope_block_tokens, g.rope_layer, g.rope_rank = block_tokens, layer, rank
+    _lib.check(_lib.lib().daser_gemm(C.byref(g), _lib.stream_ptr(stream)), "gemm_qkv_rope")
+
+
 def interleave_gate_up(w_gate_up: torch.Tensor, block: int = GATE_UP_BLOCK) -> torch.Tensor:
     """``[gate rows | up rows]`` -> blocks of ``block`` gate rows followed by the matching up rows.
 
@@ -177,17 +219,20 @@ def interleave_gate_up(w_gate_up: torch.Tensor, block: int = GATE_UP_BLOCK) -> t
     return (w_gate_up.view(2, inter // block, block, hidden).transpose(0, 1).reshape(two_i, hidden).contiguous())
 
 
-def can_fuse_swiglu(M: int, two_i: int, K: int) -> bool:
-    """True when the gate/up GEMM of this shape runs unsplit with 128-row tiles (one CTA per tile
-    sees the whole K range, so a nonlinearity may follow in the epilogue)."""
+def can_fuse_swiglu(M: int, two_i: int, K: int, split_ok: bool = False) -> bool:
+    """True when the gate/up GEMM of this shape can apply the activation itself: 128-row tiles, and
+    either unsplit (one CTA per tile sees the whole K range) or, with ``split_ok``, split-K with the
+    tile's last CTA finishing from the fp32 work buffer."""
     bn, ks = plan_tiles(M, two_i, K, allow_split=True)
-    return ks == 1 and two_i % 128 == 0
+    return (ks == 1 or split_ok) and bn == 128 and two_i % 128 == 0
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up_il: torch.Tensor, out: torch.Tensor,
                   status: Optional[torch.Tensor] = None, gate_flags: Optional[int] = None, gate_target: int = 0,
-                  gate_rows: int = 0, gate_base: Optional[int] = None, stream=None) -> torch.Tensor:
-    """``silu(x @ Wg.T) * (x @ Wu.T)`` in one kernel; ``w_gate_up_il`` is :func:`interleave_gate_up` order."""
+                  gate_rows: int = 0, gate_base: Optional[int] = None, stream=None, k_splits: int = 1,
+                  work: Optional[torch.Tensor] = None, tile_counters: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` in one kernel; ``w_gate_up_il`` is :func:`interleave_gate_up` order.
+    ``k_splits > 1`` needs ``work`` (fp32 ``[>= M, N]``, zero) and ``tile_counters`` (zero); both come back zeroed."""
     assert x.dtype == torch.bfloat16 and w_gate_up_il.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     M, K = x.shape
     N = w_gate_up_il.shape[0]
@@ -196,7 +241,11 @@ def linear_swiglu(x: torch.Tensor, w_gate_up_il: torch.Tensor, out: torch.Tensor
     g.a, g.b = x.data_ptr(), w_gate_up_il.data_ptr()
     g.lda, g.ldb, g.ldc = x.stride(0), w_gate_up_il.stride(0), out.stride(0)
     g.M, g.N, g.K = M, N, K
-    g.block_n, g.k_splits, g.epilogue = 2 * GATE_UP_BLOCK, 1, EPI_SWIGLU_BF16
+    g.block_n, g.k_splits, g.epilogue = 2 * GATE_UP_BLOCK, max(1, k_splits), EPI_SWIGLU_BF16
+    if k_splits > 1:
+        assert work is not None and tile_counters is not None and work.dtype == torch.float32
+        assert work.shape[0] >= M and work.shape[1] >= N
+        g.work, g.work_ld, g.tile_counters = work.data_ptr(), work.stride(0), tile_counters.data_ptr()
     g.n_owners, g.rows_per_owner = 1, max(M, 1)
     g.c[0] = out.data_ptr()
     g.status = status.data_ptr() if status is not None else None

@@ -327,9 +327,9 @@ class TPContext:
             self._norm_push(runner, h, w.layers[0].input_norm, None, rows, wait=False)
         for li in range(l0, l1):
             lw = w.layers[li]
-            qkv, f32 = self._col_gemm(runner, lw.wqkv, runner.qkv_acc, runner.qkv_bf, T, rows)
-            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
+            # all-gather -> QKV GEMM (loads gated on the per-source flags) -> RoPE + KV write in its epilogue
+            runner.qkv_rope(self.gathered[:T], lw, inp, T, li, gate_flags=self.flag_ptr(self.rank, FLAG_AG),
+                            gate_target=self._ag_off, gate_rows=rows, gate_base=self.epochs.data_ptr() + 4)
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
@@ -392,9 +392,7 @@ class TPContext:
             ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
         for li in range(l0, l1):
             lw = w.layers[li]
-            qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
-            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
+            runner.qkv_rope(normed, lw, inp, T, li)
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
@@ -461,9 +459,7 @@ class TPContext:
             ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
         for li in range(l0, l1):
             lw = w.layers[li]
-            qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
-            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
+            runner.qkv_rope(normed, lw, inp, T, li)
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,
@@ -492,9 +488,7 @@ class TPContext:
             ew.add_rmsnorm(h, w.layers[0].input_norm, out=normed, eps=cfg.rms_eps)
         for li in range(l0, l1):
             lw = w.layers[li]
-            qkv, f32 = runner._linear(normed, lw.wqkv, runner.qkv_acc, runner.qkv_bf)
-            ew.rope_kv_write(qkv, inp.positions, inp.slot_mapping, runner.cos_sin, runner.q_rot[:T], runner.hq,
-                             runner.hkv, D, B, runner.local_pool, li, 0, zero_after=f32, qk_norm=runner.qk_norm(lw))
+            runner.qkv_rope(normed, lw, inp, T, li)
             attn = runner.attn_out[:T].view(T, runner.hq, D)
             attention.paged_attention(runner.q_rot[:T], attn, runner.local_pool, li, inp.block_tables, inp.q_start,
                                       inp.ctx_lens, inp.max_q_len, inp.max_ctx, runner.hkv, runner.softmax_scale,

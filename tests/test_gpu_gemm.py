@@ -212,3 +212,86 @@ def test_swiglu_epilogue_matches_gemm_then_activation(M, inter, K):
     y = ew.swiglu(gu_il, block=gemm.GATE_UP_BLOCK)
     torch.cuda.synchronize()
     assert (y.float() - ref).abs().max().item() <= 3e-2 * ref.abs().max().item() + 3e-2
+
+
+@pytest.mark.parametrize("M,inter,K,ks", [(64, 512, 2048, 4), (33, 1024, 1024, 2), (130, 896, 512, 3)])
+def test_swiglu_epilogue_under_split_k(M, inter, K, ks):
+    """Split-K partials meet in the fp32 work buffer; the CTA that completes a tile applies
+    silu(gate) * up and hands the buffer and the counters back zeroed (so a second launch works)."""
+    from daser_b200.ops import gemm
+
+    torch.manual_seed(8)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(2 * inter, K, device="cuda") * 0.1).to(torch.bfloat16)
+    w_il = gemm.interleave_gate_up(w)
+    work = torch.zeros(M, 2 * inter, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(256, dtype=torch.int32, device="cuda")
+    gu = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+    for _ in range(2):
+        out = torch.full((M, inter), 7.0, dtype=torch.bfloat16, device="cuda")
+        gemm.linear_swiglu(x, w_il, out, k_splits=ks, work=work, tile_counters=counters)
+        torch.cuda.synchronize()
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 2e-2
+        assert not work.any() and not counters.any()
+
+
+@pytest.mark.parametrize("T,ks,pool_fp8", [(64, 3, True), (64, 1, True), (300, 2, True), (130, 1, False), (1, 4, True)])
+def test_qkv_epilogue_rope_and_kv_write_matches_gemm_plus_kernel(T, ks, pool_fp8):
+    """QKV projection with RoPE + the paged KV write as its epilogue, against the two-kernel path
+    (GEMM into fp32, then the stand-alone RoPE / KV-write kernel) on the same inputs: same rotated
+    queries, same pool contents, and the split-K work buffer and counters come back zeroed."""
+    from daser_b200.ops import elementwise as ew, gemm, kv_ops
+    from daser_b200.position import inv_freq_table
+
+    torch.manual_seed(7)
+    Hq, Hkv, D, B, K = 4, 2, 128, 16, 1024
+    N = (Hq + 2 * Hkv) * D
+    x = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    n_blocks = T // B + 3
+    positions = (torch.arange(T, device="cuda") + 5).to(torch.int32)
+    perm = torch.randperm(n_blocks, device="cuda")
+    slot_mapping = (perm[torch.arange(T, device="cuda") // B] * B + torch.arange(T, device="cuda") % B).to(torch.int64)
+    if T > 2:
+        slot_mapping[1] = -1  # a token whose KV is not to be written
+    cos_sin = kv_ops.rope_table(T + 16, inv_freq_table(D, 500000.0), "cuda")
+
+    def pools():
+        shape = (2, n_blocks, 2, Hkv, B, D)
+        if pool_fp8:
+            pay = torch.zeros(shape, dtype=torch.uint8, device="cuda")
+            sc = torch.zeros(shape[:-1] + (D // 16,), dtype=torch.float32, device="cuda")
+            return pay, sc, kv_ops.PagedKVPool.from_tensors([pay], [sc], "LNKHTD")
+        pay = torch.zeros(shape, dtype=torch.bfloat16, device="cuda")
+        return pay, None, kv_ops.PagedKVPool.from_tensors([pay], None, "LNKHTD")
+
+    # reference: GEMM into fp32 accumulators, then the kernel
+    pay_a, sc_a, pool_a = pools()
+    acc = torch.zeros(T, N, dtype=torch.float32, device="cuda")
+    gemm.linear(x, w, acc=acc, block_n=128, k_splits=ks)
+    q_a = torch.zeros(T, Hq, D, dtype=torch.bfloat16, device="cuda")
+    ew.rope_kv_write(acc, positions, slot_mapping, cos_sin, q_a, Hq, Hkv, D, B, pool_a, 1, 0, zero_after=True)
+    # fused
+    pay_b, sc_b, pool_b = pools()
+    work = torch.zeros(T, N, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(64, dtype=torch.int32, device="cuda")
+    q_b = torch.zeros(T, Hq, D, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):  # twice: the second launch must find the work buffer and the counters clean
+        gemm.linear_qkv_rope(x, w, positions, slot_mapping, cos_sin, q_b, Hq, Hkv, B, pool_b, 1, 0, work, counters,
+                             k_splits=ks, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and not work.any() and not counters.any()
+    # split-K sums in another order than one accumulator: equal up to fp32 rounding, then bf16 / fp8 rounding
+    assert (q_a.float() - q_b.float()).abs().max().item() <= 2e-2 * q_a.float().abs().max().item()
+    if pool_fp8:
+        from daser_b200.kv import codec
+
+        a = codec.dequantize_fp8b16(pay_a.cpu(), sc_a.cpu())
+        b = codec.dequantize_fp8b16(pay_b.cpu(), sc_b.cpu())
+    else:
+        a, b = pay_a.float().cpu(), pay_b.float().cpu()
+    assert float(a[1].abs().max()) > 0 and not a[0].any() and not b[0].any()  # layer 1 only
+    assert (a - b).abs().max().item() <= 0.08 * a.abs().max().item()
+    assert ((a - b).abs() > 1e-6).float().mean().item() < 0.05  # rounding flips are rare
