@@ -138,8 +138,14 @@ class GpuModelRunner:
         self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=dev)  # split-K "last CTA of a tile" counts
         import os as _os
 
-        self.fuse_qkv_rope = (gemm.can_fuse_qkv_rope(D, cfg.qk_norm) and _os.environ.get("DASER_FUSE_QKV_ROPE", "1") != "0"
+        # Fused epilogues that finish another operator's work inside the GEMM (RoPE + KV write behind
+        # the QKV projection, SwiGLU under split-K).  Both are correct and tested, and both are OFF by
+        # default: at serving shapes these GEMMs run split-K, the fused work then falls to the one CTA
+        # that completes a tile, and measured on the 70B 64-token step that serial tail costs more
+        # than the launch it saves (all-warm TTFT 30.8 ms fused against 30.3 ms with the two kernels).
+        self.fuse_qkv_rope = (gemm.can_fuse_qkv_rope(D, cfg.qk_norm) and _os.environ.get("DASER_FUSE_QKV_ROPE", "0") == "1"
                               and -(-max_tokens // 128) * -(-qkv_n // 128) <= self.tile_counters.numel())
+        self.fuse_swiglu_split = _os.environ.get("DASER_FUSE_SWIGLU_SPLIT", "0") == "1"
         self.softmax_scale = D**-0.5
         # ---- persistent step inputs (pinned host mirror + device copy) ----
         self.max_blocks = max_blocks
@@ -203,7 +209,7 @@ class GpuModelRunner:
         epilogue when the weights are interleaved and the shape runs unsplit, else GEMM + kernel."""
         w = self.w
         n2, k = lw.w_gate_up.shape
-        if w.gate_up_block == gemm.GATE_UP_BLOCK and gemm.can_fuse_swiglu(T, n2, k, split_ok=True):
+        if w.gate_up_block == gemm.GATE_UP_BLOCK and gemm.can_fuse_swiglu(T, n2, k, split_ok=self.fuse_swiglu_split):
             _, ks = gemm.plan_tiles(T, n2, k, allow_split=True)
             return gemm.linear_swiglu(x, lw.w_gate_up, self.act[:T], status=self.status, k_splits=ks,
                                       work=self.gu_acc, tile_counters=self.tile_counters, **gate)

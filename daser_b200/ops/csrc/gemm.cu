@@ -121,7 +121,9 @@ struct GemmSmem {
   static constexpr int DYNAMIC = TOTAL + 1024;  // slack to align the tiles to 1024 B
 };
 
-template <int BN, int STAGES>
+// FUSED: compiled with the epilogues that finish another operator's work (EPI_QKV_ROPE, and
+// EPI_SWIGLU_BF16 under split-K).  They cost registers, so the plain GEMM is a separate instance.
+template <int BN, int STAGES, bool FUSED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, (BN <= 128 ? 2 : 1))
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -263,7 +265,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool row_ok = row < p.M;
       const int owner = row_ok ? row / p.rows_per_owner : 0;
       const int64_t local_row = row_ok ? row - (int64_t)owner * p.rows_per_owner : 0;
-      const bool swiglu_split = p.epilogue == EPI_SWIGLU_BF16 && p.k_splits > 1;
+      const bool swiglu_split = FUSED && p.epilogue == EPI_SWIGLU_BF16 && p.k_splits > 1;
       if (p.epilogue == EPI_SWIGLU_BF16 && !swiglu_split) {
         if constexpr (BN >= 64) {
           // columns [0, BN/2) of the tile are gate, [BN/2, BN) the matching up values
@@ -294,9 +296,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
-      const bool rope_split = p.epilogue == EPI_QKV_ROPE && p.k_splits > 1;
-      if (p.epilogue == EPI_QKV_ROPE && !rope_split) {
-        if constexpr (BN == 128) {
+      const bool rope_split = FUSED && p.epilogue == EPI_QKV_ROPE && p.k_splits > 1;
+      if (FUSED && p.epilogue == EPI_QKV_ROPE && !rope_split) {
+        if constexpr (BN == 128 && FUSED) {
           const int hd = n0 / 128;
 #pragma unroll 1
           for (int c = 0; c < 2; ++c) {
@@ -377,13 +379,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         signal = signal && (*s_last != 0u);
-        if (*s_last != 0u && row_ok && rope_split) {
+        if (*s_last != 0u && rope_split) {
           __threadfence();
-          if constexpr (BN == 128) {
+          if constexpr (BN == 128 && FUSED) {
+            // the tile's sum is in `work` (L2): any thread may take any row, so the (row, group
+            // pair) items are dealt over all 128 epilogue threads, not one row per thread
             const int hd = n0 / 128;
+            const int rows_here = min(GEMM_BM, p.M - m0);
+            const int et = threadIdx.x - 64;  // 0..127
 #pragma unroll 1
-            for (int j = 0; j < 4; ++j) {
-              float* s1 = p.work + (int64_t)row * p.work_ld + n0 + j * FP8_GROUP;
+            for (int item = et; item < rows_here * 4; item += 128) {
+              const int r = m0 + (item >> 2), j = item & 3;
+              float* s1 = p.work + (int64_t)r * p.work_ld + n0 + j * FP8_GROUP;
               float* s2 = s1 + 64;
               float x1[16], x2[16];
 #pragma unroll
@@ -398,13 +405,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 *reinterpret_cast<float4*>(s1 + 4 * v) = make_float4(0.f, 0.f, 0.f, 0.f);
                 *reinterpret_cast<float4*>(s2 + 4 * v) = make_float4(0.f, 0.f, 0.f, 0.f);
               }
-              if (p.rope_pool_fp8) rope_kv_write_item<true>(p.rope, x1, x2, row, hd, j);
-              else rope_kv_write_item<false>(p.rope, x1, x2, row, hd, j);
+              if (p.rope_pool_fp8) rope_kv_write_item<true>(p.rope, x1, x2, r, hd, j);
+              else rope_kv_write_item<false>(p.rope, x1, x2, r, hd, j);
             }
           }
         } else if (*s_last != 0u && row_ok && swiglu_split) {
           __threadfence();
-          if constexpr (BN >= 64) {
+          if constexpr (BN >= 64 && FUSED) {
 #pragma unroll 1
             for (int c = 0; c < BN / 64; ++c) {
               float* gs = p.work + (int64_t)row * p.work_ld + n0 + c * 32;  // gate columns of the tile
@@ -528,13 +535,13 @@ static int make_tmap(CUtensorMap* out, const void* base, int64_t rows, int64_t c
 
 static bool pdl_enabled() { return pdl_allowed(); }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool FUSED = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
   static bool configured[DASER_MAX_DEVICES] = {false};  // per device: the attribute is the device's
   if (daser_first_use_on_device(configured)) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         S::DYNAMIC);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, FUSED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYNAMIC);
     if (e != cudaSuccess) return (int)e;
   }
   const dim3 grid((p.N + BN - 1) / BN, (p.M + GEMM_BM - 1) / GEMM_BM, p.k_splits);
@@ -551,7 +558,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, STAGES>, ta, tb, p);
+  return (int)cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<BN, STAGES, FUSED>, ta, tb, p);
 }
 
 }  // namespace daser
@@ -641,6 +648,11 @@ DASER_API int daser_gemm(const DaserGemm* g, cudaStream_t stream) {
   CUtensorMap ta, tb;
   if (int e = make_tmap(&ta, g->a, g->M, g->K, g->lda, GEMM_BM)) return e;
   if (int e = make_tmap(&tb, g->b, g->N, g->K, g->ldb, g->block_n)) return e;
+  const bool fused = g->epilogue == EPI_QKV_ROPE || (g->epilogue == EPI_SWIGLU_BF16 && g->k_splits > 1);
+  if (fused) {
+    if (g->block_n != 128) return DASER_ERR_UNSUPPORTED;
+    return launch<128, 3, true>(ta, tb, p, stream);
+  }
   switch (g->block_n) {
     // stage counts keep two CTAs resident per SM for BN <= 128 (<= ~100 KB each)
     case 32: return launch<32, 5>(ta, tb, p, stream);

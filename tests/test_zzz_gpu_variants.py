@@ -114,3 +114,37 @@ def test_truncated_sampling_on_the_device():
     ew.argmax(nucleus, val, idx, sampling=(inv, seeds))
     torch.cuda.synchronize()
     assert bool(kept.gather(1, idx.long()[:, None]).all())
+
+
+def test_runner_with_fused_epilogues_matches_the_two_kernel_path(monkeypatch):
+    """The opt-in fused epilogues (RoPE + KV write behind the QKV projection, SwiGLU under split-K)
+    through the whole runner: same hidden states and the same greedy tokens as the default path, for
+    a decode-sized step (split-K, the tile's last CTA finishes) and a prefill-sized one (unsplit)."""
+    from daser_b200.engine.runner import GpuModelRunner, make_step_inputs
+    from daser_b200.ops import gemm
+
+    cfg = PRESETS["tiny-gqa"]
+    rng = random.Random(1)
+    tokens = [rng.randrange(cfg.vocab_size) for _ in range(200)]
+    table = list(range(3, 3 + 14))
+    results = {}
+    for name, on in (("plain", "0"), ("fused", "1")):
+        monkeypatch.setenv("DASER_FUSE_QKV_ROPE", on)
+        monkeypatch.setenv("DASER_FUSE_SWIGLU_SPLIT", on)
+        w = LlamaWeights.random(cfg, "cuda", torch.bfloat16, seed=3, std=0.05)
+        w.interleave_gate_up_(gemm.GATE_UP_BLOCK)
+        runner = GpuModelRunner(cfg, w, num_blocks=64, max_tokens=256, use_graphs=False)
+        assert runner.fuse_qkv_rope == (on == "1")
+        out = []
+        for lo, hi in ((0, 150), (150, 199), (199, 200)):
+            inp = make_step_inputs([{"tokens": tokens[lo:hi], "start_pos": lo, "block_table": table}], 16, "cuda")
+            out.append(int(runner.forward(inp)[0].item()))
+            hidden = runner.normed[: hi - lo].float().clone()
+        runner.check_status()
+        results[name] = (out, hidden, runner.kv_payload.clone())
+    assert results["plain"][0] == results["fused"][0]
+    a, b = results["plain"][1], results["fused"][1]
+    assert (a - b).abs().max().item() <= 0.03 * a.abs().max().item()
+    # the pools agree except for rare fp8 rounding flips (split-K sums in another order)
+    same = (results["plain"][2] == results["fused"][2]).float().mean().item()
+    assert same > 0.97, same
