@@ -82,7 +82,7 @@ def reference_arm(args) -> None:
         # a session of its own: on a time-out the whole group goes (vLLM's engine and worker processes too)
         proc = subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=None, text=True, start_new_session=True)
         try:
-            stdout, _ = proc.communicate(timeout=float(os.environ.get("DASER_REF_TIMEOUT", "1500")))
+            stdout, _ = proc.communicate(timeout=float(os.environ.get("DASER_REF_TIMEOUT", "1700")))
             for line in stdout.splitlines():
                 if line.startswith("REFERENCE_RESULT "):
                     out = json.loads(line[len("REFERENCE_RESULT "):])

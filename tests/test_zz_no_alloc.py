@@ -4,9 +4,9 @@ Some users of the library cannot call cudaMalloc: a server that froze its device
 layout at start-up, a latency-critical loop that must not hit an allocation's implicit
 synchronisation, or a foreign runtime that only passes raw pointers through the C ABI.  For
 them ``daser_paged_attention_fp8_noalloc`` keeps the split-KV scratch inside the library.
-This test calls it twice in a row (the second call finds the first call's leftovers in the
-shared scratch) and compares each result with the regular entry point, which works in
-caller-provided scratch.  It lives in a file of its own that sorts last, so a run that
+This test calls it on two different cases, each twice in a row (every call after the first
+finds an earlier call's leftovers in the shared scratch, its own shape's or another's), and
+compares each result with the regular entry point, which works in caller-provided scratch.  It lives in a file of its own that sorts last, so a run that
 stops at the first failure has already run everything else.
 """
 
@@ -66,14 +66,15 @@ def test_noalloc_entry_matches_regular_entry_twice_in_a_row():
         attention.paged_attention(q, ref, pool, 0, tables, q_start, ctx, max(q_lens), max(ctx_lens), Hkv,
                                   128**-0.5, attention.AttentionWorkspace("cuda"), nsplit=nsplit,
                                   split_tokens=split_tokens)
-        out = torch.zeros_like(q)
-        before = torch.cuda.memory_allocated()
-        rc = _call_noalloc(lib, out, pool, tables, q, q_start, ctx, q_lens, Hq, Hkv, nsplit, split_tokens)
-        torch.cuda.synchronize()
-        assert rc == 0
-        assert torch.cuda.memory_allocated() == before  # torch's allocator was not touched by the call
-        err = (out.float() - ref.float()).abs().max().item()
-        assert err < 3e-2, err
+        for _ in range(2):  # the same call again: the scratch now holds this very shape's leftovers
+            out = torch.zeros_like(q)
+            before = torch.cuda.memory_allocated()
+            rc = _call_noalloc(lib, out, pool, tables, q, q_start, ctx, q_lens, Hq, Hkv, nsplit, split_tokens)
+            torch.cuda.synchronize()
+            assert rc == 0
+            assert torch.cuda.memory_allocated() == before  # torch's allocator was not touched by the call
+            err = (out.float() - ref.float()).abs().max().item()
+            assert err < 3e-2, err
         assert ref.float().abs().max().item() > 0.01  # the comparison is not vacuous
 
 
