@@ -111,3 +111,48 @@ def test_batched_decode_matches_one_at_a_time(tmp_path):
     finally:
         eng.close()
         lp.stop()
+
+
+def test_engine_loop_on_the_gpu_engine_matches_one_request_at_a_time(tmp_path):
+    """The serving loop (one thread steps the engine, callers on other threads share its steps)
+    around the CUDA engine: concurrent requests decode as one batch, stream their tokens, and
+    produce what each produces alone; an abort frees the request's blocks."""
+    from daser_b200.engine.loop import EngineLoop
+    from daser_b200.engine.rag_gpu import GpuRagEngine, RagRequest
+
+    cfg = PRESETS["tiny-gqa"]
+    lp = LiveControlPlane(tmp_path, total_slots=256,
+                          slot_size=cfg.num_layers * 2 * 16 * cfg.num_kv_heads * cfg.head_dim * 5 // 4).start()
+    eng = GpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=256, max_tokens=128, max_seqs=8,
+                       hbm_slots=64, host_slots=64)
+    try:
+        rng = random.Random(7)
+        chunks = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (32, 64, 48)]
+        for c in chunks:
+            eng.store_chunk(c)
+        reqs = [([chunks[i % 3], chunks[(i + 1) % 3]], [rng.randrange(cfg.vocab_size) for _ in range(5 + i)])
+                for i in range(5)]
+        want = [eng.generate(c, q, max_new_tokens=6).generated for c, q in reqs]
+        free = eng.blocks.num_free
+        loop = EngineLoop(eng)
+        try:
+            streams = [[] for _ in reqs]
+            futs = [loop.submit(c, q, 6, on_token=streams[i].append) for i, (c, q) in enumerate(reqs)]
+            done = [f.result(120) for f in futs]
+        finally:
+            loop.close()
+        eng.runner.check_status()
+        assert [r.generated for r in done] == want
+        assert streams == want and all(r.restored_chunks == 2 for r in done)
+        assert loop.max_batch > 1 and eng.blocks.num_free == free
+        # a temperature changes the draw, reproducibly per seed
+        a = eng.generate(*reqs[0], max_new_tokens=6, temperature=0.9, seed=5, top_k=8, top_p=0.95).generated
+        b = eng.generate(*reqs[0], max_new_tokens=6, temperature=0.9, seed=5, top_k=8, top_p=0.95).generated
+        assert a == b and len(a) == 6
+        # abort of a running request returns its blocks
+        r = eng.submit(RagRequest(reqs[1][0], reqs[1][1], 50))
+        eng.step()
+        assert r in eng.running and eng.abort(r.req_id) and r.done and eng.blocks.num_free == free
+    finally:
+        eng.close()
+        lp.stop()
