@@ -80,6 +80,7 @@ class HostMailbox:
         mm = self._mm
         t0 = time.perf_counter()
         spins = 0
+        slow = False
         while True:
             (seq,) = _U64.unpack_from(mm, base)
             if seq == want:
@@ -93,14 +94,18 @@ class HostMailbox:
             if seq > want:
                 raise RuntimeError(f"mailbox overrun: rank {src} is at message {seq}, message {want} was lost")
             spins += 1
-            if spins & 0x3FF == 0:
-                waited = time.perf_counter() - t0
-                if waited > timeout_s:
-                    raise MailboxTimeout(f"rank {src} published nothing for {timeout_s:.0f} s")
-                if on_wait is not None:
-                    on_wait()
-                if waited > 0.002:
-                    time.sleep(0.0001)
+            if spins & 0x3FF and not slow:
+                continue  # the first milliseconds: a tight poll (a step's plan arrives within microseconds)
+            waited = time.perf_counter() - t0
+            if waited > timeout_s:
+                raise MailboxTimeout(f"rank {src} published nothing for {timeout_s:.0f} s")
+            if on_wait is not None and (not slow or spins & 0x3F == 0):
+                on_wait()
+            if waited > 0.002:
+                # nothing came at once: back off (an idle service's follower costs next to nothing,
+                # and the first request after the pause pays at most the last sleep)
+                slow = True
+                time.sleep(0.005 if waited > 1.0 else 0.001 if waited > 0.05 else 0.0001)
 
     def broadcast(self, obj: Any, src: int = 0, timeout_s: float = 30.0, on_wait=None) -> Any:
         """``obj`` of rank ``src`` on every rank (the others pass anything)."""

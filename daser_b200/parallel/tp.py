@@ -190,13 +190,19 @@ class TPContext:
         dist.broadcast_object_list(box, src=src, group=self._cpu_group)
         return box[0]
 
-    def broadcast_object(self, obj: Any, src: int = 0) -> Any:
+    def broadcast_object(self, obj: Any, src: int = 0, timeout_s: Optional[float] = None) -> Any:
         """``obj`` of rank ``src`` on every rank.  Through the shared-memory mailbox (microseconds);
         a peer that stops publishing surfaces as :class:`~daser_b200.parallel.health.PeerLost` or a
-        time-out instead of a hung collective."""
+        time-out instead of a hung collective.  ``timeout_s=float("inf")`` waits as long as the
+        peers stay alive (a follower of an idle service waiting for the leader's next call)."""
         if self.mailbox is None:
             return self._broadcast_gloo(obj, src)
-        return self.mailbox.broadcast(obj, src, timeout_s=self._mail_timeout, on_wait=self.check_peers)
+        return self.mailbox.broadcast(obj, src, timeout_s=self._mail_timeout if timeout_s is None else timeout_s,
+                                      on_wait=self.check_peers)
+
+    def await_announcement(self, obj: Any = None, src: int = 0) -> Any:
+        """:meth:`broadcast_object` without a time limit: what a follower waits for between requests."""
+        return self.broadcast_object(obj, src, timeout_s=float("inf"))
 
     def gather_object(self, obj: Any) -> list:
         """Every rank's ``obj`` in rank order, on every rank."""

@@ -176,7 +176,7 @@ def _run_follower(args: argparse.Namespace) -> None:
                           hbm_slots=min(cfg.total_slots, 4096), tp_ctx=tp_ctx,
                           weights=_model_weights(args, "cuda", torch.bfloat16, tp_ctx.tp, tp_ctx.rank),
                           **_engine_options(args))
-    steps = follower_loop(engine, tp_ctx.broadcast_object)
+    steps = follower_loop(engine, tp_ctx.await_announcement)  # idle between requests: no time limit, peers watched
     logger.info("[SERVICE] follower rank %d leaves after %d engine calls", tp_ctx.rank, steps)
 
 
