@@ -30,6 +30,7 @@ import os
 from collections import OrderedDict
 import threading
 import time
+import dataclasses
 from dataclasses import dataclass, field
 from typing import Any, Callable, Optional, Sequence
 
@@ -659,14 +660,19 @@ class WorkerHalf:
                     ptr = self.host.arena.data_ptr() + off
                     waves[-1].append(_LoadJob(spec, n, "host_fill", ptr, io_dst=ptr))
                     continue
-            if n > self._staging_slots:
-                raise ValueError(f"chunk of {n} slots exceeds staging capacity {self._staging_slots}")
-            if used + n > self._staging_slots:
-                waves.append([])  # staging full: what we have goes first, to completion
-                used = 0
-            ptr = self._staging.data_ptr() + used * g.slot_size
-            waves[-1].append(_LoadJob(spec, n, "staging", ptr, io_dst=ptr))
-            used += n
+            # a chunk longer than the arena goes through it in pieces (each a run of its slots)
+            cap = self._staging_slots
+            pieces = [spec] if n <= cap else [
+                dataclasses.replace(spec, block_ids=spec.block_ids[i:i + cap], skip_slots=spec.skip_slots + i)
+                for i in range(0, n, cap)]
+            for piece in pieces:
+                m = len(piece.block_ids)
+                if used + m > cap:
+                    waves.append([])  # staging full: what we have goes first, to completion
+                    used = 0
+                ptr = self._staging.data_ptr() + used * g.slot_size
+                waves[-1].append(_LoadJob(piece, m, "staging", ptr, io_dst=ptr))
+                used += m
         self._wait_sources_free()
         for wave in waves[:-1]:
             t = self._issue(wave, [(0, g.num_layers)])
@@ -857,23 +863,26 @@ class WorkerHalf:
             self._wait_for_save(meta, barrier)
 
     def _wait_for_save(self, meta: ConnectorMeta, barrier: Optional[Callable[[], None]]) -> None:
-        g = self.geo
-        pending = list(meta.reqs_to_store)
+        """Pieces ``(spec, first staging slot, b0, b1)`` = blocks ``[b0, b1)`` of a chunk; as many as
+        fit the staging arena go out together, and a chunk longer than the arena takes several
+        rounds.  A chunk is committed once its last piece is on the drive and none failed."""
+        cap = self._staging_slots
+        pending = [(spec, b0, min(b0 + cap, len(spec.block_ids)))
+                   for spec in meta.reqs_to_store for b0 in range(0, len(spec.block_ids), cap)]
+        failed: set[str] = set()
         while pending:
             batch, used = [], 0
-            while pending and used + len(pending[0].block_ids) <= self._staging_slots:
-                spec = pending.pop(0)
-                batch.append((spec, used))
-                used += len(spec.block_ids)
-            if not batch:
-                raise ValueError("chunk larger than the staging arena")
-            self._store_batch(batch, barrier)
+            while pending and used + (pending[0][2] - pending[0][1]) <= cap:
+                spec, b0, b1 = pending.pop(0)
+                batch.append((spec, used, b0, b1))
+                used += b1 - b0
+            self._store_batch(batch, barrier, failed)
 
-    def _store_batch(self, batch, barrier) -> None:
+    def _store_batch(self, batch, barrier, failed: set) -> None:
         g = self.geo
         ptrs, blocks = [], []
-        for spec, first in batch:
-            for i, b in enumerate(spec.block_ids):
+        for spec, first, b0, b1 in batch:
+            for i, b in enumerate(spec.block_ids[b0:b1]):
                 ptrs.append(self._staging.data_ptr() + (first + i) * g.slot_size)
                 blocks.append(b)
         if self.kv.device_kind == "cuda":
@@ -891,28 +900,34 @@ class WorkerHalf:
         eng = self._xfer.engine
         dev_staging = self._staging.is_cuda
         tickets = []
-        for spec, first in batch:
-            n = len(spec.block_ids)
+        for spec, first, b0, b1 in batch:
             ptr = self._staging.data_ptr() + first * g.slot_size
-            tickets.append((spec, first, n, eng.submit_write(ptr, spec.file_offset, n * g.slot_size, device=dev_staging)))
-        for spec, first, n, ticket in tickets:
+            tickets.append((spec, first, b0, b1, eng.submit_write(ptr, spec.file_offset + b0 * g.slot_size,
+                                                                  (b1 - b0) * g.slot_size, device=dev_staging)))
+        for spec, first, b0, b1, ticket in tickets:
+            n = b1 - b0
             try:
                 eng.wait(ticket)
             except (OSError, TimeoutError) as exc:
                 logger.error("[CONNECTOR] store of %s failed: %s (reservation aborted)", spec.chunk_key, exc)
                 metrics.inc("connector.store_errors")
-                try:
-                    self._ipc.abort_chunk(spec.chunk_key)
-                except RuntimeError:
-                    pass
+                if spec.chunk_key not in failed:
+                    failed.add(spec.chunk_key)
+                    try:
+                        self._ipc.abort_chunk(spec.chunk_key)
+                    except RuntimeError:
+                        pass
                 continue
             metrics.inc("connector.bytes_stored", n * g.slot_size)
-            if self.hbm is not None and self.kv.device_kind == "cuda":
-                self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
-                self.hbm.end_step()
-            if self.host is not None:
-                self.host.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
-                self.host.end_step()
+            if b1 < len(spec.block_ids) or spec.chunk_key in failed:
+                continue  # more pieces to come, or an earlier piece was lost
+            if b0 == 0:  # the whole chunk is in the arena: the tiers take it from there
+                if self.hbm is not None and self.kv.device_kind == "cuda":
+                    self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+                    self.hbm.end_step()
+                if self.host is not None:
+                    self.host.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+                    self.host.end_step()
             try:
                 extra = {"first_block": spec.first_block_digest} if spec.first_block_digest else {}
                 if self.commit_parts is not None:

@@ -315,7 +315,8 @@ class TPContext:
         l1 = len(w.layers) if l1 is None else l1
         if self.impl == "nccl":
             return self._forward_body_nccl(runner, inp, nsplit, split_tokens, l0, l1)
-        if self.impl == "nvls":
+        if self.impl == "nvls" and T <= self.os_cap:
+            # (longer steps, the prefill pieces, take the two-hop form below: its buffers hold max_tokens)
             return self._forward_body_nvls(runner, inp, nsplit, split_tokens, l0, l1)
         if self.impl == "oneshot" or (self.impl == "fused" and self.tp <= ONESHOT_MAX_TP and T <= self.os_cap):
             return self._forward_body_oneshot(runner, inp, nsplit, split_tokens, l0, l1)

@@ -204,3 +204,61 @@ def test_trimmed_prefix_hit_does_not_shadow_the_whole_chunk(tmp_path):
         worker.shutdown()
         sched.close()
         lp.stop()
+
+
+def test_a_chunk_longer_than_the_staging_arena_is_stored_and_restored_in_pieces(tmp_path):
+    """Ten blocks through an arena of four slots: three rounds on the way out, three waves on the
+    way back, every block exact; a second, short chunk shares the step."""
+    from conftest import LiveControlPlane
+    from daser_b200.connector.core import SchedulerHalf, TorchKVBackend, WorkerHalf
+    from daser_b200.kv.layout import KVGeometry
+
+    L, H, D, B = 2, 2, 32, 16
+    geo = KVGeometry(num_layers=L, num_kv_heads=H, head_dim=D, block_tokens=B, dtype_bytes=2, codec="raw")
+    lp = LiveControlPlane(tmp_path, total_slots=64, slot_size=geo.slot_size).start()
+    torch.manual_seed(5)
+    pool = torch.randn(L, 40, 2, H, B, D).to(torch.bfloat16)
+    worker = WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool, [1.0] * (D // 2)),
+                        io_backend="posix", staging_slots=4)
+    sched = SchedulerHalf(lp.socket_path, B, "m")
+
+    def step(reqs, fn):
+        fn()
+        meta = sched.build_connector_meta(reqs)
+        worker.bind_connector_metadata(meta)
+        worker.start_load_kv()
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+        for r in reqs:
+            sched.request_finished(r)
+        return meta
+
+    try:
+        long_toks = list(range(100, 100 + 10 * B))
+        short_toks = list(range(700, 700 + 2 * B))
+        src_long, src_short = list(range(1, 11)), [11, 12]
+
+        def cold():
+            assert sched.get_num_new_matched_tokens("a", long_toks + [1], 0) == (0, False)
+            sched.update_state_after_alloc("a", src_long + [13], 0)
+            assert sched.get_num_new_matched_tokens("b", short_toks + [1], 0) == (0, False)
+            sched.update_state_after_alloc("b", src_short + [14], 0)
+        step(["a", "b"], cold)
+        want_long, want_short = pool[:, src_long].clone(), pool[:, src_short].clone()
+        dst_long, dst_short = list(range(20, 30)), [30, 31]
+
+        def warm():
+            n, _ = sched.get_num_new_matched_tokens("c", long_toks + [1, 2], 0)
+            assert n == 10 * B
+            sched.update_state_after_alloc("c", dst_long + [32], n)
+            n, _ = sched.get_num_new_matched_tokens("d", short_toks + [1, 2], 0)
+            assert n == 2 * B
+            sched.update_state_after_alloc("d", dst_short + [33], n)
+        step(["c", "d"], warm)
+        assert torch.equal(pool[:, dst_long], want_long)
+        assert torch.equal(pool[:, dst_short], want_short)
+        assert not worker.take_load_errors()
+    finally:
+        worker.shutdown()
+        sched.close()
+        lp.stop()
