@@ -105,8 +105,9 @@ def main() -> None:
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default="llama3-70b")
     ap.add_argument("--pool", type=int, default=512, help="chunks in the synthetic pool")
-    ap.add_argument("--tp-impl", choices=("fused", "twoshot", "oneshot", "nvls", "nccl"), default="fused",
-                    help="fused: GEMM-epilogue reduction over peer memory (one-shot all-reduce for few tokens at "
+    ap.add_argument("--tp-impl", choices=("auto", "fused", "twoshot", "oneshot", "nvls", "nccl"), default="auto",
+                    help="auto: nvls above two GPUs where the buffers get an NVLink multicast mapping, else fused; "
+                         "fused: GEMM-epilogue reduction over peer memory (one-shot all-reduce for few tokens at "
                          "tp <= 2, reduce-scatter + gated all-gather otherwise); twoshot / oneshot: force one form; "
                          "nvls: partials stay local, each rank reads the sum through the NVLink multicast mapping; "
                          "nccl: the unfused baseline (same kernels, NCCL all-reduce)")
@@ -152,7 +153,15 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         from daser_b200.parallel.tp import TPContext
 
-        tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=args.max_tokens, impl=args.tp_impl)
+        if args.tp_impl == "auto":
+            # measured on the 64-token step of this model (ms, max over ranks): 2 GPUs one-shot 20.9,
+            # in-switch 20.7, two-hop 22.1, NCCL 21.1; 8 GPUs in-switch 12.0, two-hop 13.1, NCCL 13.2
+            tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=args.max_tokens, impl="fused", multicast=world > 2)
+            if world > 2 and tp_ctx.nv_mc:
+                tp_ctx.impl = "nvls"
+            args.tp_impl = tp_ctx.impl
+        else:
+            tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=args.max_tokens, impl=args.tp_impl)
 
     store_dir = args.store_dir or tempfile.mkdtemp(prefix="daser_bench_")
     if tp_ctx is not None:
@@ -384,23 +393,30 @@ def measure_extras(args, eng, tp_ctx, reqs, barrier, rank) -> dict:
         nbytes = sum(len(s.block_ids) for s in mine.reqs_to_load) * eng.geo.slot_size
         barrier()
         ev[0].record()
-        eng.worker.bind_connector_metadata(mine)
-        eng.worker.start_load_kv()
-        eng.worker.clear_connector_metadata()
+        ticket = eng.worker.begin_load(mine)
+        if ticket is not None:
+            eng.worker.restore_group(ticket, 0)
+            eng.worker.end_load(ticket, wait=True)
         ev[1].record()
         torch.cuda.synchronize()
         ms = ev[0].elapsed_time(ev[1])  # spans the host's wait for the reads too: the GPU idles meanwhile
         barrier()
-        agg = torch.tensor([float(nbytes), ms], dtype=torch.float64, device="cuda")
+        tb = ticket.tier_bytes if ticket is not None else {}
+        src = [tb.get("hbm", 0), tb.get("host", 0), tb.get("host_fill", 0) + tb.get("staging", 0)]
+        agg = torch.tensor([float(nbytes), ms] + [float(b) for b in src], dtype=torch.float64, device="cuda")
         if tp_ctx is not None:
             parts = [torch.zeros_like(agg) for _ in range(world)]
             dist.all_gather(parts, agg)
             total_bytes = sum(p[0].item() for p in parts)
             slowest = max(p[1].item() for p in parts)
+            src = [sum(p[2 + i].item() for p in parts) for i in range(3)]
         else:
             total_bytes, slowest = nbytes, ms
         rates[f"restore_{name}_gbs"] = round(total_bytes / max(slowest, 1e-6) / 1e6, 2)
         rates[f"restore_{name}_ms"] = round(slowest, 3)
+        # where the bytes really came from (a rank whose tier is smaller than its share of the
+        # request falls through to the next source)
+        rates[f"restore_{name}_sources_MB"] = {k: round(b / 1e6, 1) for k, b in zip(("hbm", "host", "file"), src)}
     eng.blocks.free(table)
     rates["note"] = ("one request's chunks, all ranks restoring their own at once, no pipelining, device + host timed, "
                      "max over ranks: file = store file -> pinned host tier -> HBM tier -> pools; host = pinned host "

@@ -126,6 +126,9 @@ class TPContext:
         # peers read the sum of all ranks' buffers through the multicast alias of the same range
         self.nv_buf: list[torch.Tensor] = []
         self.nv_mc: list[int] = []
+        # steps of up to this many tokens take the in-switch form (its add + norm kernel handles one
+        # wave of rows: one CTA per row, 148 SMs); longer ones take the two-hop form
+        self.nv_cap = min(self.os_cap, int(os.environ.get("DASER_TP_NVLS_MAX", "128")))
         self.epochs_nv = torch.zeros(4, dtype=torch.int32, device=self.device)
         if self.multicast:
             for i in range(2):
@@ -315,7 +318,7 @@ class TPContext:
         l1 = len(w.layers) if l1 is None else l1
         if self.impl == "nccl":
             return self._forward_body_nccl(runner, inp, nsplit, split_tokens, l0, l1)
-        if self.impl == "nvls" and T <= self.os_cap:
+        if self.impl == "nvls" and T <= self.nv_cap:
             # (longer steps, the prefill pieces, take the two-hop form below: its buffers hold max_tokens)
             return self._forward_body_nvls(runner, inp, nsplit, split_tokens, l0, l1)
         if self.impl == "oneshot" or (self.impl == "fused" and self.tp <= ONESHOT_MAX_TP and T <= self.os_cap):
@@ -434,7 +437,7 @@ class TPContext:
             raise RuntimeError("the in-switch form needs a context built with multicast=True")
         cfg, w = self.cfg, runner.w
         T = inp.num_tokens
-        if T > self.os_cap:
+        if T > self.nv_cap:
             raise ValueError("step exceeds the in-switch all-reduce buffers")
         D, B = cfg.head_dim, cfg.block_tokens
         h, normed = runner.h[:T], runner.normed[:T]
