@@ -233,6 +233,67 @@ __global__ void signal_flags_kernel(SignalTargets targets, int n, uint32_t value
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(targets.flag[i]), "r"(value) : "memory");
 }
 
+// Tensor-parallel sampling in one kernel.  Every rank holds, per row, the best (value, global
+// vocabulary index) of its shard; the sample is the best over the ranks.  This rank's candidates
+// go into every rank's table by peer stores, an arrival is published in every rank's counter, the
+// kernel waits (bounded) until its own counter shows all `tp` arrivals of this round and picks.
+// Table of a rank: [2 rounds][tp sources][2: value, index bits][cap] floats; rounds alternate so
+// that a fast rank's next push cannot land on candidates a slow rank has not read yet.  `epoch`
+// (device word, local) counts the arrivals consumed so far: the kernel can be replayed.
+struct CandTargets {
+  float* table[DASER_MAX_RANKS];
+  uint32_t* counter[DASER_MAX_RANKS];
+};
+__global__ void __launch_bounds__(256)
+tp_pick_token_kernel(const float* best_val, const int32_t* best_idx, int n, int rank,
+                     int tp, int cap, CandTargets tg, uint32_t* epoch, uint32_t* status, int32_t* out_idx) {
+  __shared__ uint32_t base_s;
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) { base_s = *epoch; ok_s = 1; }
+  __syncthreads();
+  const uint32_t base = base_s;
+  const int round = (base / (uint32_t)tp) & 1;
+  for (int i = threadIdx.x; i < n * tp; i += blockDim.x) {
+    const int r = i / n, j = i - r * n;
+    float* dst = tg.table[r] + (size_t)(round * tp + rank) * 2 * cap;
+    dst[j] = best_val[j];
+    dst[cap + j] = __int_as_float(best_idx[j]);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < tp)
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(tg.counter[threadIdx.x]) : "memory");
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = ew_timer_ns();
+    const uint32_t want = base + (uint32_t)tp;
+    while ((int32_t)(ew_ld_acquire_sys(tg.counter[rank]) - want) < 0) {
+      if (ew_timer_ns() - t0 > DASER_WAIT_NS) {
+        if (status) atomicExch(status, DASER_STATUS_TIMEOUT);
+        ok_s = 0;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  if (ok_s) {
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+      float best = 0.f;
+      int idx = 0;
+      for (int r = 0; r < tp; ++r) {
+        const float* src = tg.table[rank] + (size_t)(round * tp + r) * 2 * cap;
+        float v, ib;
+        asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(src + j) : "memory");
+        asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(ib) : "l"(src + cap + j) : "memory");
+        if (r == 0 || v > best) { best = v; idx = __float_as_int(ib); }  // ties: the lowest rank
+      }
+      out_idx[j] = idx;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *epoch = base + (uint32_t)tp;
+}
+
 // RoPE on q and k, then k/v into the paged pool.  qkv row = [Hq*D | Hkv*D | Hkv*D].
 // slot_mapping[t] = block * block_tokens + offset inside the block, or < 0 to skip the write.
 // QKNORM (Qwen3 family): every query and key head is RMS-normalised over head_dim and scaled by
@@ -501,6 +562,24 @@ DASER_API int daser_signal_flags(const uint64_t* flag_ptrs, int n, uint32_t valu
   daser::SignalTargets t;
   for (int i = 0; i < DASER_MAX_RANKS; ++i) t.flag[i] = i < n ? reinterpret_cast<uint32_t*>(flag_ptrs[i]) : nullptr;
   daser::signal_flags_kernel<<<1, 32, 0, stream>>>(t, n, value);
+  return (int)cudaGetLastError();
+}
+
+// table_ptrs[r], counter_ptrs[r]: rank r's candidate table and arrival counter (peer memory for
+// r != rank).  best_val / best_idx: this rank's per-row candidates (n <= cap rows).
+DASER_API int daser_tp_pick_token(const float* best_val, const int32_t* best_idx, int n, int rank, int tp, int cap,
+                                  const uint64_t* table_ptrs, const uint64_t* counter_ptrs, uint32_t* epoch,
+                                  uint32_t* status, int32_t* out_idx, cudaStream_t stream) {
+  if (!best_val || !best_idx || !table_ptrs || !counter_ptrs || !epoch || !out_idx) return DASER_ERR_BAD_ARG;
+  if (tp < 1 || tp > DASER_MAX_RANKS || rank < 0 || rank >= tp || n < 0 || n > cap) return DASER_ERR_BAD_ARG;
+  if (n == 0) return 0;
+  daser::CandTargets tg;
+  for (int r = 0; r < DASER_MAX_RANKS; ++r) {
+    tg.table[r] = r < tp ? reinterpret_cast<float*>(table_ptrs[r]) : nullptr;
+    tg.counter[r] = r < tp ? reinterpret_cast<uint32_t*>(counter_ptrs[r]) : nullptr;
+    if (r < tp && (!tg.table[r] || !tg.counter[r])) return DASER_ERR_BAD_ARG;
+  }
+  daser::tp_pick_token_kernel<<<1, 256, 0, stream>>>(best_val, best_idx, n, rank, tp, cap, tg, epoch, status, out_idx);
   return (int)cudaGetLastError();
 }
 

@@ -48,6 +48,27 @@ def signal_flags(flag_ptrs: Sequence[int], value: int, stream=None) -> None:
                                              _lib.stream_ptr(stream)), "signal_flags")
 
 
+def tp_pick_token(best_val: torch.Tensor, best_idx: torch.Tensor, n: int, rank: int, tp: int, cap: int,
+                  table_ptrs: Sequence[int], counter_ptrs: Sequence[int], epoch: torch.Tensor,
+                  status: Optional[torch.Tensor], out_idx: torch.Tensor) -> None:
+    """The tensor-parallel sample in one kernel: push this rank's per-row candidates (``best_val``
+    float32, ``best_idx`` int32: the best of its vocabulary shard) into every rank's table, publish
+    an arrival in every rank's counter, wait (bounded) for all ``tp`` arrivals here, and write the
+    winning index per row into ``out_idx``.  ``table_ptrs[r]`` = rank r's table of
+    ``2 * tp * 2 * cap`` floats, ``counter_ptrs[r]`` its arrival counter, ``epoch`` this rank's
+    count of consumed arrivals (int32[1], device)."""
+    assert best_val.dtype == torch.float32 and best_idx.dtype == torch.int32 and out_idx.dtype == torch.int32
+    tables = (C.c_uint64 * tp)(*[int(x) for x in table_ptrs])
+    counters = (C.c_uint64 * tp)(*[int(x) for x in counter_ptrs])
+    _lib.check(
+        _lib.lib().daser_tp_pick_token(C.c_void_p(best_val.data_ptr()), C.c_void_p(best_idx.data_ptr()), n, rank, tp,
+                                       cap, tables, counters, C.c_void_p(epoch.data_ptr()),
+                                       C.c_void_p(status.data_ptr()) if status is not None else None,
+                                       C.c_void_p(out_idx.data_ptr()), _lib.stream_ptr()),
+        "tp_pick_token",
+    )
+
+
 def advance_epochs(epochs: torch.Tensor, d0: int, d1: int, d2: int) -> None:
     """``epochs[0:3] += (d0, d1, d2)`` on the stream (see ``parallel/tp.py``)."""
     _lib.check(

@@ -57,6 +57,7 @@ FLAG_OS = 1  # and 2: arrival counters of the two one-shot all-reduce receive bu
 # ranks those stores dominate the GEMM's epilogue.
 ONESHOT_MAX_TP = 2
 FLAG_NV = 3  # and 4: arrival counters of the two in-switch all-reduce buffers
+FLAG_CAND = 5  # arrival counter of the sampling candidates
 FLAG_AG = 8  # first of tp per-source "rows landed" flags
 FLAG_KV = 16  # first of tp per-source "restore pieces landed in your pool" counters
 NUM_FLAGS = 24
@@ -111,7 +112,12 @@ class TPContext:
         self.h_local = torch.zeros(self.rows_max, H, dtype=torch.bfloat16, device=self.device)
         self.done = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.tile_counters = torch.zeros(4096, dtype=torch.int32, device=self.device)
-        self.cand = torch.zeros(2, 64, dtype=torch.float32, device=self.device)
+        # sampling: every rank's best (value, index) per row lands in every rank's table
+        # ([2 rounds][tp sources][value, index][CAND_CAP rows]); `epoch_cand` counts consumed arrivals
+        self.cand_cap = 64
+        self.cand = self.alloc("cand", (2 * self.tp * 2 * self.cand_cap,), torch.float32)
+        self.cand.zero_()
+        self.epoch_cand = torch.zeros(1, dtype=torch.int32, device=self.device)
         # device-resident bases of the three growing counters (reduce-scatter arrivals, pushes
         # per source rank, finished norm CTAs): kernels wait for base + offset, and the last
         # kernel of a forward advances the bases, so a captured forward can be replayed
@@ -536,14 +542,12 @@ class TPContext:
         # is the sample, the noise being a function of the seed and the global vocabulary index)
         ew.argmax(runner.logits_acc[:n], runner.best_val[:n], runner.best_idx[:n],
                   index_offset=self.rank * runner.w.vocab_local, zero_after=True, sampling=inp.sampling)
-        cand = self.cand[:, :n]
-        cand[0].copy_(runner.best_val[:n])
-        cand[1].copy_(runner.best_idx[:n].to(torch.float32))
-        allc = torch.empty(self.tp, 2, n, dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(allc, cand.contiguous(), group=self.group)
-        winner = allc[:, 0].argmax(dim=0)
-        tok = allc[:, 1].gather(0, winner.unsqueeze(0)).squeeze(0).to(torch.int32)
-        runner.best_idx[:n].copy_(tok)
+        # one kernel: candidates to every rank by peer stores, arrival counters, bounded wait, pick
+        if n > self.cand_cap:
+            raise ValueError(f"{n} sequences in one step exceed the sampling table ({self.cand_cap})")
+        ew.tp_pick_token(runner.best_val, runner.best_idx, n, self.rank, self.tp, self.cand_cap, self.ptrs["cand"],
+                         [self.flag_ptr(r, FLAG_CAND) for r in range(self.tp)], self.epoch_cand, runner.status,
+                         runner.best_idx)
         return runner.best_idx[:n]
 
     def prepare_save_staging(self, geo) -> None:

@@ -56,3 +56,40 @@ def test_norm_arrival_timeout_and_flag_wait_timeout():
     ew.wait_flags(counter.data_ptr(), 1, 3, status)
     torch.cuda.synchronize()
     assert status.item() == 0
+
+
+def test_tp_pick_token_with_the_peers_arrival_posted_and_with_it_missing():
+    """The sampling exchange as rank 0 of 2 on one GPU: the peer's candidates and arrival are
+    written by hand before the launch (two kernels that wait for each other never share a GPU).
+    Two rounds, so that both halves of the table and the replay through `epoch` are used; then a
+    round in which the peer never arrives: the wait runs out, the status word says so."""
+    from daser_b200.ops import elementwise as ew
+
+    tp, cap, n = 2, 64, 5
+    mine = torch.zeros(2 * tp * 2 * cap, dtype=torch.float32, device="cuda")   # rank 0's table
+    theirs = torch.zeros_like(mine)                                           # stands in for rank 1's table
+    counters = torch.zeros(2, dtype=torch.int32, device="cuda")                # [0]: rank 0's, [1]: rank 1's
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(n, dtype=torch.int32, device="cuda")
+    view = mine.view(2, tp, 2, cap)
+    for rnd in range(2):
+        my_val = torch.tensor([1.0, 5.0, -2.0, 0.5, 3.0], device="cuda") + rnd
+        my_idx = torch.tensor([10, 11, 12, 13, 14], dtype=torch.int32, device="cuda")
+        peer_val = torch.tensor([2.0, 4.0, -1.0, 0.5, 9.0], device="cuda")
+        peer_idx = torch.tensor([110, 111, 112, 113, 114], dtype=torch.int32, device="cuda")
+        view[rnd, 1, 0, :n] = peer_val                       # what rank 1's kernel would have stored here
+        view[rnd, 1, 1, :n] = peer_idx.view(torch.float32)
+        counters[0] += 1                                     # ... and its arrival
+        ew.tp_pick_token(my_val, my_idx, n, 0, tp, cap, [mine.data_ptr(), theirs.data_ptr()],
+                         [counters[0:].data_ptr(), counters[1:].data_ptr()], epoch, status, out)
+        torch.cuda.synchronize()
+        want = torch.where(my_val >= peer_val, my_idx, peer_idx)  # ties go to the lower rank
+        assert status.item() == 0 and out.tolist() == want.tolist()
+        assert epoch.item() == tp * (rnd + 1) and counters.tolist() == [tp * (rnd + 1), rnd + 1]
+        # this rank's candidates reached the peer's table, in the round's half
+        assert theirs.view(2, tp, 2, cap)[rnd, 0, 0, :n].tolist() == my_val.tolist()
+    ew.tp_pick_token(my_val, my_idx, n, 0, tp, cap, [mine.data_ptr(), theirs.data_ptr()],
+                     [counters[0:].data_ptr(), counters[1:].data_ptr()], epoch, status, out)
+    torch.cuda.synchronize()
+    assert status.item() == 1
