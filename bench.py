@@ -121,6 +121,9 @@ def main() -> None:
     ap.add_argument("--extras", type=int, default=1, help="0: skip the untimed extra measurements after the timed region")
     ap.add_argument("--open-loop-requests", type=int, default=16)
     ap.add_argument("--kv-blocks", type=int, default=6144, help="blocks of 16 tokens in the paged KV pool")
+    ap.add_argument("--precondition", type=int, default=64,
+                    help="untimed requests of the same traffic served before the warm-up, so that the tiers hold what "
+                         "a running service's would (LRU over the Zipf traffic) instead of starting empty")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -167,7 +170,9 @@ def main() -> None:
     if tp_ctx is not None:
         store_dir = tp_ctx.broadcast_object(store_dir)
     slot = cfg.num_layers * 2 * cfg.block_tokens * cfg.num_kv_heads * cfg.head_dim * 5 // 4
-    prefix, pool, reqs = make_traffic(cfg.vocab_size, cfg.block_tokens, args.pool, args.k, args.steps + args.warmup)
+    # (requests are drawn one after the other: asking for more leaves the first ones as they were)
+    prefix, pool, reqs = make_traffic(cfg.vocab_size, cfg.block_tokens, args.pool, args.k,
+                                      args.steps + args.warmup + args.precondition)
     pool_slots = sum(len(c) // cfg.block_tokens for c in pool) + len(prefix) // cfg.block_tokens
     total_slots = pool_slots + 64
     dcfg = DaserConfig(store_path=os.path.join(store_dir, "daser.store"), index_path="", total_slots=total_slots,
@@ -233,6 +238,10 @@ def main() -> None:
         chunks, query, _ = req_spec
         return eng.generate(chunks, query, max_new_tokens=1)
 
+    t0 = time.time()
+    for spec in reqs[args.warmup + args.steps:]:
+        run(spec)
+    t_precondition = time.time() - t0
     for spec in reqs[: args.warmup]:
         run(spec)
     eng.runner.check_status()
@@ -321,6 +330,9 @@ def main() -> None:
                 "open_loop": extras.get("open_loop", {}),
                 "l2": "inputs larger than L2 (weights stream from HBM every step)",
                 "init_s": round(t_init, 1), "fill_s": round(t_fill, 1),
+                "tier_precondition": f"{args.precondition} untimed requests of the same traffic served after the fill "
+                                     f"(tiers emptied first) and before the warm-up, {round(t_precondition, 1)} s: the "
+                                     "tiers hold what LRU makes of the Zipf traffic, not an empty cache",
                 "io_direct_pieces": io1["direct_pieces"],
             },
         }
@@ -439,9 +451,15 @@ def measure_extras(args, eng, tp_ctx, reqs, barrier, rank) -> dict:
     if n_open > 0:
         import random
 
+        # the probes above emptied the tiers: bring them back to what the traffic makes of them
+        for t in tiers:
+            t.clear()
+        for chunks, query, _ in reqs[args.warmup + args.steps:]:
+            eng.generate(chunks, query, max_new_tokens=1)
+
         rng = random.Random(7)
         gaps = [rng.expovariate(4.0) for _ in range(n_open)]
-        picks = [reqs[(args.warmup + i) % len(reqs)] for i in range(n_open)]
+        picks = [reqs[args.warmup + i % args.steps] for i in range(n_open)]
         barrier()
         t_begin = time.perf_counter()
         arrivals, t = [], 0.0
