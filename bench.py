@@ -112,8 +112,10 @@ def main() -> None:
                          "nvls: partials stay local, each rank reads the sum through the NVLink multicast mapping; "
                          "nccl: the unfused baseline (same kernels, NCCL all-reduce)")
     ap.add_argument("--k", type=int, default=8, help="chunks per request")
-    ap.add_argument("--hbm-frac", type=float, default=0.125, help="fraction of the pool the HBM tiers hold (all ranks together)")
-    ap.add_argument("--host-frac", type=float, default=0.25, help="fraction of the pool the pinned host tiers hold")
+    ap.add_argument("--hbm-frac", type=float, default=0.125,
+                    help="HBM tier of ONE rank as a fraction of the pool (the same bytes per GPU at every --gpus)")
+    ap.add_argument("--host-frac", type=float, default=0.25,
+                    help="pinned host tier of ONE rank as a fraction of the pool")
     ap.add_argument("--store-dir", default="")
     ap.add_argument("--io-backend", default="auto")
     ap.add_argument("--layer-groups", type=int, default=8, help="pieces the restore and the forward are pipelined in")
@@ -204,9 +206,13 @@ def main() -> None:
     max_ctx_tokens = (args.k * 1024 + 64 + 64 + 16)
     blocks_per_req = -(-max_ctx_tokens // cfg.block_tokens)
     t0 = time.time()
-    # each rank holds 1 / world of the tier budget (it owns 1 / world of the chunks)
-    hbm_slots = max(64, int(pool_slots * args.hbm_frac / world)) if args.hbm_frac > 0 else 0
-    host_slots = max(64, int(pool_slots * args.host_frac / world)) if args.host_frac > 0 else 0
+    # Every GPU gives the same HBM to its tier and every rank the same pinned host memory, whatever
+    # the number of ranks: a rank owns 1 / world of the chunks, so the share of the pool that fits a
+    # memory tier grows with the ranks (that is what adding GPUs buys a cache).  Capped at what the
+    # rank's own chunks can fill.
+    own = int(pool_slots / world * 1.25) + 64
+    hbm_slots = max(64, min(int(pool_slots * args.hbm_frac), own)) if args.hbm_frac > 0 else 0
+    host_slots = max(64, min(int(pool_slots * args.host_frac), own)) if args.host_frac > 0 else 0
     # the paged pool holds the open-loop phase's concurrent requests (4 req/s x 128 output tokens:
     # about twenty of ~230 blocks each at TP = 1); 6144 blocks = 20 GB of fp8 KV over all ranks
     eng = GpuRagEngine(cfg, dcfg.ipc_socket_path, dcfg.store_path, num_blocks=args.kv_blocks,
@@ -317,7 +323,11 @@ def main() -> None:
                 "kv_codec": "fp8b16 (e4m3 + fp32 scale / 16)",
                 "io_backend": eng.worker.transfer.backend.name, "store": dcfg.store_path,
                 "tiers": {"hbm_slots_per_rank": hbm_slots, "host_slots_per_rank": host_slots, "pool_slots": pool_slots,
-                          "owner": "hash(chunk_key) mod tp"},
+                          "owner": "hash(chunk_key) mod tp",
+                          "sizing": "the same bytes per rank at every N (a rank owns 1/N of the chunks, so the "
+                                    "tiers of N ranks together hold N times the share of the pool)",
+                          "share_of_pool": {"hbm": round(min(1.0, hbm_slots * world / pool_slots), 3),
+                                            "host": round(min(1.0, host_slots * world / pool_slots), 3)}},
                 "tier_hits": {"hbm": int(hbm_hits), "host": int(host_hits),
                               "file": int(delta("connector.chunk_hits") - hbm_hits - host_hits),
                               "file_reads_MB": round(file_bytes / 1e6, 1),

@@ -84,6 +84,7 @@ def main() -> None:
     ap.add_argument("--backend", default="FLASH_ATTN")
     ap.add_argument("--gpu-util", type=float, default=0.92)
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--write-behind", type=int, default=1, help="0: wait for the file write inside wait_for_save")
     args = ap.parse_args()
 
     import vllm_common as vc
@@ -112,7 +113,9 @@ def main() -> None:
                                       "slot_size": slot, "block_tokens": BLOCK_TOKENS, "model_id": args.model,
                                       "codec": args.codec, "hbm_slots": args.hbm_slots, "host_slots": host_slots,
                                       # one prompt's blocks fit the pinned arena (longer ones would go in pieces)
-                                      "staging_slots": max(-(-len(p) // BLOCK_TOKENS) for p in prompts)},
+                                      "staging_slots": (2 if args.write_behind else 1)
+                                      * max(-(-len(p) // BLOCK_TOKENS) for p in prompts),
+                                      "write_behind": bool(args.write_behind)},
     }
     env = vc.clean_env([ROOT, os.path.join(ROOT, "baseline")])  # the engine's children inherit it
     for k in [k for k in os.environ if k not in env]:
@@ -142,7 +145,7 @@ def main() -> None:
     restored = sum((len(p) // BLOCK_TOKENS) * slot * tp for p in timed)
     print(json.dumps({
         "bench": "vllm_connector", "model": args.model, "n_gpus": tp, "codec": args.codec,
-        "attention_backend": args.backend, "host_slots": host_slots, "hbm_slots": args.hbm_slots,
+        "attention_backend": args.backend, "host_slots": host_slots, "hbm_slots": args.hbm_slots, "write_behind": bool(args.write_behind),
         "warm_ttft_ms": {"p50": round(percentile(warm_ms, 50), 3), "p99": round(percentile(warm_ms, 99), 3)},
         "cold_ttft_ms": {"p50": round(percentile(cold_ms, 50), 3), "p99": round(percentile(cold_ms, 99), 3)},
         "kv_restore_gbs": round(restored / (sum(warm_ms) / 1e3) / 1e9, 3),

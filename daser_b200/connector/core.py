@@ -499,6 +499,10 @@ class CudaKVBackend:
 # =========================================================================================
 
 
+# a layer group's share of one slot image below which the chunk is read in one piece instead
+MIN_STRIDED_READ = 128 << 10
+
+
 @dataclass
 class _LoadJob:
     """One chunk of a load: where the kernel reads it from and, if it is cold, where IO puts it."""
@@ -525,6 +529,7 @@ class LoadTicket:
     t_submit: float = 0.0
     tier_bytes: dict = field(default_factory=dict)  # bytes restored by source: hbm / host / host_fill / staging
     work: Any = None
+    waited: set = field(default_factory=set)  # (job, IO ticket) pairs already waited for
 
 
 class WorkerHalf:
@@ -533,8 +538,18 @@ class WorkerHalf:
     def __init__(self, socket_path: str, store_path: str, geo: KVGeometry, backend: Any,
                  io_backend: str = "auto", tp: int = 1, rank: int = 0, hbm_store: Any = None,
                  host_store: Any = None, client: Optional[IPCClientSync] = None, staging_slots: int = 256,
-                 create_store_slots: int = 1024, commit: bool = True) -> None:
+                 create_store_slots: int = 1024, commit: bool = True, write_behind: bool = False) -> None:
         from daser_b200.connector.transfer import TransferLayer
+
+        # write_behind: `wait_for_save` returns once the blocks are copied into the staging arena
+        # and their writes are submitted; the writes complete, and the chunks are committed, when
+        # that half of the arena is needed again, before the next load that uses the arena, at
+        # `flush_stores` or at shutdown.  The blocks may be reused at once either way; what changes
+        # is the moment a chunk becomes visible to lookups.
+        self._write_behind = bool(write_behind) and staging_slots >= 2
+        self._pending_stores: dict = {}
+        self._store_failed: set = set()
+        self._next_half = 0
 
         self.geo = geo
         self.kv = backend
@@ -681,7 +696,9 @@ class WorkerHalf:
         return self._issue(waves[-1], groups)
 
     def _wait_sources_free(self) -> None:
-        """The previous load's kernels have read the staging arena (about to be refilled)."""
+        """The previous load's kernels have read the staging arena (about to be refilled), and no
+        store still writes from it."""
+        self._complete_stores(None)
         if self._load_done is not None:
             self._load_done.synchronize()
 
@@ -708,9 +725,14 @@ class WorkerHalf:
         ticket.t_submit = time.perf_counter()
         whole = len(groups) == 1 and groups[0] == (0, g.num_layers)
         layer = g.layer_size
+        # A group's share of one slot image is one read.  Where that is small (a small model's
+        # slots), many short reads cost more than the overlap buys: the chunk is then read in one
+        # piece, which the first group waits for and the others find done.
+        if not whole and min(count for _, count in groups) * layer < MIN_STRIDED_READ:
+            whole = True
         # reads go out group-major and, inside a group, in file order: neighbouring chunks
         # become one sequential sweep of the device
-        for l0, count in groups:
+        for l0, count in ([(0, g.num_layers)] if whole else groups):
             for job in sorted((j for j in jobs if j.io_dst), key=lambda j: j.spec.file_offset):
                 spec = job.spec
                 off = spec.file_offset + spec.skip_slots * g.slot_size
@@ -724,7 +746,7 @@ class WorkerHalf:
                 except OSError as exc:
                     logger.warning("[CONNECTOR] read submit failed for %s: %s", spec.chunk_key, exc)
                     t = None
-                job.tickets.append(t)
+                job.tickets.extend([t] * (len(groups) if whole else 1))
                 ticket.io_bytes += job.n * count * layer
         trace.instant("io.reads_submitted", n=sum(len(j.tickets) for j in jobs), bytes=ticket.io_bytes)
         if cuda:
@@ -760,6 +782,9 @@ class WorkerHalf:
                 t = job.tickets[index]
                 if t is None:
                     raise OSError("submit failed")
+                if (id(job), t) in ticket.waited:
+                    continue  # one read served several groups: an earlier group has waited for it
+                ticket.waited.add((id(job), t))
                 eng.wait(t)
             except (OSError, TimeoutError) as exc:
                 logger.warning("[CONNECTOR] load of %s failed: %s", job.spec.chunk_key, exc)
@@ -776,7 +801,8 @@ class WorkerHalf:
                     self.hbm.evict(job.spec.chunk_key)
                 for later in job.tickets[index + 1:]:
                     try:  # its other reads still land in memory this step owns: let them finish
-                        if later is not None:
+                        if later is not None and (id(job), later) not in ticket.waited:
+                            ticket.waited.add((id(job), later))
                             eng.wait(later)
                     except (OSError, TimeoutError):
                         pass
@@ -864,21 +890,33 @@ class WorkerHalf:
 
     def _wait_for_save(self, meta: ConnectorMeta, barrier: Optional[Callable[[], None]]) -> None:
         """Pieces ``(spec, first staging slot, b0, b1)`` = blocks ``[b0, b1)`` of a chunk; as many as
-        fit the staging arena go out together, and a chunk longer than the arena takes several
-        rounds.  A chunk is committed once its last piece is on the drive and none failed."""
-        cap = self._staging_slots
+        fit the staging arena (one half of it with ``write_behind``) go out together, and a longer
+        chunk takes several rounds.  A chunk is committed once its last piece is on the drive and
+        none failed."""
+        halves = 2 if self._write_behind else 1
+        cap = self._staging_slots // halves
         pending = [(spec, b0, min(b0 + cap, len(spec.block_ids)))
                    for spec in meta.reqs_to_store for b0 in range(0, len(spec.block_ids), cap)]
-        failed: set[str] = set()
+        failed = self._store_failed if self._write_behind else set()
         while pending:
+            half = self._next_half if self._write_behind else 0
+            self._complete_stores(half)  # the writes that still read this part of the arena
             batch, used = [], 0
             while pending and used + (pending[0][2] - pending[0][1]) <= cap:
                 spec, b0, b1 = pending.pop(0)
-                batch.append((spec, used, b0, b1))
+                batch.append((spec, half * cap + used, b0, b1))
                 used += b1 - b0
-            self._store_batch(batch, barrier, failed)
+            tickets = self._store_batch(batch, barrier)
+            if tickets is None:
+                continue
+            self._pending_stores[half] = (tickets, failed)
+            if self._write_behind:
+                self._next_half ^= 1  # returns with the writes in flight: the other half takes the next batch
+            else:
+                self._complete_stores(half)
 
-    def _store_batch(self, batch, barrier, failed: set) -> None:
+    def _store_batch(self, batch, barrier):
+        """Gather the batch's blocks into the arena (one launch) and submit its writes."""
         g = self.geo
         ptrs, blocks = [], []
         for spec, first, b0, b1 in batch:
@@ -891,12 +929,14 @@ class WorkerHalf:
             self.kv.check_status()
         else:
             n = len(blocks)
-            images = self._staging.view(-1, g.slot_size)[:n]
-            self.kv.save(blocks, images)
+            if n:
+                first = batch[0][1]
+                images = self._staging.view(-1, g.slot_size)[first : first + n]
+                self.kv.save(blocks, images)
         if barrier is not None:
             barrier()  # every rank's head slice is in the owner's staging
         if not self._commit:
-            return
+            return None
         eng = self._xfer.engine
         dev_staging = self._staging.is_cuda
         tickets = []
@@ -904,43 +944,69 @@ class WorkerHalf:
             ptr = self._staging.data_ptr() + first * g.slot_size
             tickets.append((spec, first, b0, b1, eng.submit_write(ptr, spec.file_offset + b0 * g.slot_size,
                                                                   (b1 - b0) * g.slot_size, device=dev_staging)))
-        for spec, first, b0, b1, ticket in tickets:
-            n = b1 - b0
-            try:
-                eng.wait(ticket)
-            except (OSError, TimeoutError) as exc:
-                logger.error("[CONNECTOR] store of %s failed: %s (reservation aborted)", spec.chunk_key, exc)
-                metrics.inc("connector.store_errors")
-                if spec.chunk_key not in failed:
-                    failed.add(spec.chunk_key)
-                    try:
-                        self._ipc.abort_chunk(spec.chunk_key)
-                    except RuntimeError:
-                        pass
+        return tickets
+
+    def _complete_stores(self, half: Optional[int] = None) -> None:
+        """Finish the writes submitted from one half of the arena (all of it: ``None``): wait for
+        them, hand whole chunks to the tiers, commit."""
+        g = self.geo
+        eng = self._xfer.engine
+        for h in ([half] if half is not None else list(self._pending_stores)):
+            entry = self._pending_stores.pop(h, None)
+            if entry is None:
                 continue
-            metrics.inc("connector.bytes_stored", n * g.slot_size)
-            if b1 < len(spec.block_ids) or spec.chunk_key in failed:
-                continue  # more pieces to come, or an earlier piece was lost
-            if b0 == 0:  # the whole chunk is in the arena: the tiers take it from there
-                if self.hbm is not None and self.kv.device_kind == "cuda":
-                    self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
-                    self.hbm.end_step()
-                if self.host is not None:
-                    self.host.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
-                    self.host.end_step()
-            try:
-                extra = {"first_block": spec.first_block_digest} if spec.first_block_digest else {}
-                if self.commit_parts is not None:
-                    extra.update(part=self.commit_parts[0], parts=self.commit_parts[1])
-                self._ipc.commit_chunk(spec.chunk_key, **extra)
-            except RuntimeError as exc:
-                logger.error("[CONNECTOR] commit of %s failed: %s", spec.chunk_key, exc)
+            tickets, failed = entry
+            for spec, first, b0, b1, ticket in tickets:
+                n = b1 - b0
+                try:
+                    eng.wait(ticket)
+                except (OSError, TimeoutError) as exc:
+                    logger.error("[CONNECTOR] store of %s failed: %s (reservation aborted)", spec.chunk_key, exc)
+                    metrics.inc("connector.store_errors")
+                    if spec.chunk_key not in failed:
+                        failed.add(spec.chunk_key)
+                        try:
+                            self._ipc.abort_chunk(spec.chunk_key)
+                        except RuntimeError:
+                            pass
+                    continue
+                metrics.inc("connector.bytes_stored", n * g.slot_size)
+                if b1 < len(spec.block_ids) or spec.chunk_key in failed:
+                    continue  # more pieces to come, or an earlier piece was lost
+                if b0 == 0:  # the whole chunk is in the arena: the tiers take it from there
+                    if self.hbm is not None and self.kv.device_kind == "cuda":
+                        self.hbm.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+                        self.hbm.end_step()
+                    if self.host is not None:
+                        self.host.admit(spec.chunk_key, self._staging, first * g.slot_size, n * g.slot_size)
+                        self.host.end_step()
+                try:
+                    extra = {"first_block": spec.first_block_digest} if spec.first_block_digest else {}
+                    if self.commit_parts is not None:
+                        extra.update(part=self.commit_parts[0], parts=self.commit_parts[1])
+                    self._ipc.commit_chunk(spec.chunk_key, **extra)
+                except RuntimeError as exc:
+                    logger.error("[CONNECTOR] commit of %s failed: %s", spec.chunk_key, exc)
+        if not self._pending_stores:
+            self._store_failed = set()
+
+    def pending_store_keys(self) -> set:
+        """Chunk keys whose writes are submitted but not yet committed (``write_behind``)."""
+        return {t[0].chunk_key for tickets, _ in self._pending_stores.values() for t in tickets}
+
+    def flush_stores(self) -> None:
+        """With ``write_behind``: block until every submitted store is on the drive and committed."""
+        self._complete_stores(None)
 
     def get_stats(self) -> dict[str, float]:
         return {k: v for k, v in metrics.snapshot().items() if k.startswith(("connector.", "transfer."))}
 
     def shutdown(self) -> None:
         try:
+            try:
+                self._complete_stores(None)
+            except Exception as exc:  # noqa: BLE001
+                logger.error("[CONNECTOR] pending stores lost at shutdown: %s", exc)
             self._xfer.close()
         finally:
             self._ipc.close()

@@ -19,7 +19,9 @@ Differences from the reference adapter:
   ``kv[:, block_id]`` and breaks on the FlashInfer layout that compute capability 10.x selects.
 * Additional extra-config keys: ``codec`` (``raw`` keeps the reference's container byte for
   byte, ``fp8b16`` compresses), ``io_backend``, ``hbm_slots``, ``host_slots``, ``staging_slots``
-  (the pinned arena between the kernels and the file; longer chunks pass through it in pieces).
+  (the pinned arena between the kernels and the file; longer chunks pass through it in pieces),
+  ``write_behind`` (``wait_for_save`` returns with the file writes in flight; the chunk is committed
+  when they are done, at the latest before the next load or save that needs the arena).
 * Hooks the reference leaves at their defaults are implemented: ``register_cross_layers_kv_cache``,
   ``reset_cache``, ``get_block_ids_with_load_errors``,
   ``get_kv_connector_stats``, ``prefer_cross_layer_blocks``.
@@ -218,6 +220,7 @@ class DaserConnector(KVConnectorBase_V1):
         self._hbm_slots = int(extra.get("hbm_slots", 0))
         self._host_slots = int(extra.get("host_slots", 0))
         self._staging_slots = int(extra.get("staging_slots", 256))
+        self._write_behind = str(extra.get("write_behind", "0")).lower() in ("1", "true", "yes")
         par = getattr(vllm_config, "parallel_config", None)
         self._tp = int(getattr(par, "tensor_parallel_size", 1) or 1)
         self._rank = int(extra.get("tp_rank", getattr(par, "rank", 0) or 0)) % max(self._tp, 1)
@@ -313,7 +316,7 @@ class DaserConnector(KVConnectorBase_V1):
             hbm = host = None
         self._worker = WorkerHalf(self._socket_path, store_path, geo, backend, io_backend=self._io_backend,
                                   tp=1, rank=0, hbm_store=hbm, host_store=host,
-                                  staging_slots=self._staging_slots)
+                                  staging_slots=self._staging_slots, write_behind=self._write_behind)
         if self._tp > 1:
             self._worker.commit_parts = (self._rank, self._tp)
         logger.info("[CONNECTOR] registered %d KV layers, layout %s, slot_size=%d, backend=%s",

@@ -53,7 +53,8 @@ class GpuRagEngine(SchedulingMixin):
                  io_backend: str = "auto",
                  seed: int = 0, model_id: str = "default", tp_ctx=None, weights: Optional[LlamaWeights] = None,
                  staging_slots: int = 512, max_blocks: int = 512, use_graphs: bool = True,
-                 compose_after: int = 0, repair_tokens: int = 0, layer_groups: int = 8, pp_link=None) -> None:
+                 compose_after: int = 0, repair_tokens: int = 0, layer_groups: int = 8, pp_link=None,
+                 write_behind: bool = False) -> None:
         self.cfg = cfg
         # pipeline parallelism: this process is one stage (``parallel/pp.py::StageLink``); it runs a
         # contiguous range of layers, keeps their KV in a pool and a store file of its own, and a
@@ -104,7 +105,8 @@ class GpuRagEngine(SchedulingMixin):
         if self.tp > 1 and self.rank != 0:
             tp_ctx.wait_for_path(store_path)  # rank 0 creates the store file
         self.worker = WorkerHalf(socket_path, store_path, self.geo, self.kv_backend, io_backend=io_backend, tp=self.tp,
-                                 rank=self.rank, hbm_store=self.hbm, host_store=self.host, staging_slots=staging_slots)
+                                 rank=self.rank, hbm_store=self.hbm, host_store=self.host, staging_slots=staging_slots,
+                                 write_behind=write_behind and self.tp == 1 and pp_link is None)
         if pp_link is not None and pp_link.stages > 1:
             self.worker.commit_parts = (pp_link.stage, pp_link.stages)
         # Every process has now shaken hands with the control plane, which may live on a thread of
@@ -210,6 +212,7 @@ class GpuRagEngine(SchedulingMixin):
         meta = self._bcast(meta)
         self._prefill_tokens(tokens, 0, table)
         self._save(meta)
+        self.worker.flush_stores()  # an explicit store is visible when this returns
         if self.pp_link is not None:
             self.pp_link.barrier()  # every stage has committed its part: the chunk is visible when this returns
         if self.sched is not None:
@@ -306,6 +309,8 @@ class GpuRagEngine(SchedulingMixin):
         plan = None
         if self.sched is not None:
             placements = [(hash_tokens(c), off) for c, off in zip(req.chunks, offsets)]
+            if self.worker.pending_store_keys() & {k for k, _ in placements}:
+                self.worker.flush_stores()  # a chunk this request asks for is still on its way to the drive
             specs = self.sched.plan_chunk_loads(req.req_id, placements)
             self.sched.assign_chunk_blocks(req.req_id, req.block_table)
             plan = (self.sched.build_connector_meta([req.req_id]), [s is not None for s in specs])
@@ -320,35 +325,63 @@ class GpuRagEngine(SchedulingMixin):
                   if req.temperature > 0 else None)
 
         def compute(failed_blocks: set, gate) -> torch.Tensor:
-            """Prefill whatever is not (validly) restored, then the query; returns the sampled token."""
+            """Prefill whatever is not (validly) restored, then the query; returns the sampled token.
+            Neighbouring pieces that must be computed (missed chunks, and the query behind them) go
+            through the model as ONE run of tokens: every forward streams all the weights, so a
+            request whose chunks all miss costs ceil(tokens / max_tokens) passes, not one per chunk."""
+            run: list[int] = []
+            run_start = 0
+
+            def flush(sample_with=None):
+                nonlocal gate, run
+                out = None
+                if run:
+                    out = self._prefill_tokens(run, run_start, req.block_table, sample_with, gate=gate)
+                    gate = None
+                    run = []
+                return out
+
             ctx = 0
             for c, off, ok in zip(req.chunks, offsets, found):
                 blocks_of_chunk = set(req.block_table[off // bt : (off + len(c)) // bt])
                 if not ok or (blocks_of_chunk & failed_blocks):
-                    self._prefill_tokens(c, off, req.block_table, gate=gate)
-                    gate = None
+                    if run and run_start + len(run) != off:
+                        flush()
+                    if not run:
+                        run_start = off
+                    run.extend(c)
                     if req.store_misses and not ok:
                         if off == 0:
-                            self._store_in_place(req, c, off)  # saw no context: this IS the chunk's own KV
+                            if (c, off) not in in_place:
+                                in_place.append((c, off))  # saw no context: this IS the chunk's own KV
                         elif c not in standalone:
                             standalone.append(c)
                     if ok and failed_blocks:  # counted as restored by the first pass
                         req.restored_chunks -= 1
                         req.restored_bytes -= (len(c) // bt) * self.geo.slot_size
-                elif not failed_blocks:
-                    req.restored_chunks += 1
-                    req.restored_bytes += (len(c) // bt) * self.geo.slot_size
-                    if self.repair_tokens > 0 and off > 0:
-                        self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table, gate=gate)
-                        gate = None
+                else:
+                    flush()
+                    if not failed_blocks:
+                        req.restored_chunks += 1
+                        req.restored_bytes += (len(c) // bt) * self.geo.slot_size
+                        if self.repair_tokens > 0 and off > 0:
+                            self._prefill_tokens(c[: min(self.repair_tokens, len(c))], off, req.block_table, gate=gate)
+                            gate = None
                 ctx = off + len(c)
-            return self._prefill_tokens(req.query, ctx, req.block_table, sample, gate=gate)
+            if run and run_start + len(run) != ctx:
+                flush()
+            if not run:
+                run_start = ctx
+            run.extend(req.query)
+            return flush(sample)
 
         # A missed chunk behind other context was just computed attending to that context; the
         # store keeps chunks under a key of their own tokens only, so what is stored must be the
         # chunk computed alone (as `store_chunk` does).  Those are recomputed after the first
         # token has gone out, between steps.
         standalone: list[Sequence[int]] = []
+        # A missed chunk at offset 0 is stored from the request's own blocks, once the first token is out.
+        in_place: list[tuple[Sequence[int], int]] = []
         # 3. compute what was not restored, then the query
         first = compute(set(), gate)
         if self._restore_stream is not None:
@@ -381,6 +414,8 @@ class GpuRagEngine(SchedulingMixin):
             "h2d_bytes": self.h2d_bytes + self.kv_backend.h2d_bytes - h2d0,
         }
         metrics.observe("engine.ttft_ms", req.ttft_ms)
+        for c, off in in_place:
+            self._store_in_place(req, c, off)
         if self.sched is not None:
             self.sched.request_finished(req.req_id)
         for c in standalone:

@@ -24,6 +24,8 @@ is made on that path (:mod:`daser_b200.parallel.tp` holds the symmetric buffers 
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Any, Optional
 
@@ -67,6 +69,9 @@ def split_layers(num_layers: int, parts: int) -> list[tuple[int, int]]:
         out.append((first, n))
         first += n
     return out
+
+
+_BUCKET_ROWS = os.environ.get("DASER_BUCKET_ROWS", "1") != "0"
 
 
 class GpuModelRunner:
@@ -222,7 +227,16 @@ class GpuModelRunner:
             gu, f32 = self.gu_bf[:T], False
         return ew.swiglu(gu, out=self.act[:T], zero_after=f32, block=w.gate_up_block)
 
-    # -- one step -----------------------------------------------------------------------------------
+    @staticmethod
+    def bucket_rows(n: int) -> int:
+        """Rows a step of ``n`` tokens is launched with: exact up to 16 (decode batches, prompt
+        tails: few shapes, soon all captured), then multiples of 16 up to 128, of 64 up to 512, of
+        128 beyond."""
+        if n <= 16 or not _BUCKET_ROWS:
+            return n
+        step = 16 if n <= 128 else 64 if n <= 512 else 128
+        return -(-n // step) * step
+
     # -- step inputs ---------------------------------------------------------------------------------
     def stage_inputs(self, seqs: list[dict]) -> StepInputs:
         """Write one step's inputs into the runner's fixed buffers (pinned host -> device, one
@@ -250,6 +264,17 @@ class GpuModelRunner:
             h["sample_rows"][i] = t - 1
             max_q, max_ctx = max(max_q, n), max(max_ctx, p0 + n)
         ns = len(seqs)
+        # Round the step up to a bucket of rows so that steps of nearby sizes share their CUDA graphs
+        # (a prompt tail or a missed chunk can have any length; an unseen shape runs eagerly, several
+        # hundred launches from the host).  The extra rows belong to no sequence: they write no KV
+        # (slot -1), the attention kernels take their row ranges from `q_start`, nothing samples them.
+        real = t
+        t = min(self.bucket_rows(t), self.max_tokens)
+        if t > real:
+            h["tokens"][real:t] = 0
+            h["positions"][real:t] = 0
+            h["slot_mapping"][real:t] = -1
+            max_q = min(self.bucket_rows(max_q), t)
         d = self._in_dev
         for name, count in (("tokens", t), ("positions", t), ("slot_mapping", t), ("q_start", ns + 1),
                             ("ctx_lens", ns), ("sample_rows", ns)):

@@ -96,13 +96,19 @@ def test_restore_compute_repair_and_sampling_fields(engine):
     engine.runner.calls.clear()
     seen = []
     req = engine.generate([a, b], [5, 6, 7], max_new_tokens=3, temperature=0.7, seed=9, on_token=seen.append)
-    # chunk a restored (no forward), chunk b computed at its offset, then the query, then two decode steps
-    assert req.restored_chunks == 1 and _computed(engine.runner.calls) == [(32, 32), (64, 3), (67, 1), (68, 1)]
+    # chunk a restored (no forward); chunk b and the query behind it go through the model as one run
+    # of 35 tokens at b's offset (one pass over the weights, not two), then two decode steps
+    assert req.restored_chunks == 1 and _computed(engine.runner.calls) == [(32, 35), (67, 1), (68, 1)]
     assert seen == req.generated and len(seen) == 3 and req.finish_reason == "length"
-    sampled = [s for seqs in engine.runner.calls[1:] for s in seqs]
+    sampled = [s for seqs in engine.runner.calls for s in seqs]
     assert all(s["temperature"] == 0.7 for s in sampled)
     assert len({s["seed"] for s in sampled}) == 3            # a fresh seed per step, derived from the request's
-    assert "temperature" not in engine.runner.calls[0][0]    # computing a chunk samples nothing
+    # a missed chunk in FRONT of a restored one is a run of its own, and samples nothing
+    engine.runner.calls.clear()
+    c = [rng.randrange(1000) for _ in range(32)]
+    req = engine.generate([c, a], [5, 6, 7], max_new_tokens=1, temperature=0.7, seed=9)
+    assert req.restored_chunks == 1 and _computed(engine.runner.calls) == [(0, 32), (64, 3)]
+    assert "temperature" not in engine.runner.calls[0][0] and engine.runner.calls[1][0]["temperature"] == 0.7
     engine.runner.calls.clear()
     engine.generate([], [5, 6], max_new_tokens=2, temperature=0.7, seed=1, top_k=40, top_p=0.9)
     assert all(s["top_k"] == 40 and s["top_p"] == 0.9 for seqs in engine.runner.calls for s in seqs)
@@ -172,8 +178,9 @@ def test_missed_chunks_are_stored_as_computed_alone(engine):
     rng = random.Random(2)
     a, b = ([rng.randrange(1000) for _ in range(32)] for _ in range(2))
     engine.generate([a, b], [4, 5], max_new_tokens=1, store_misses=True)
-    # a at 0 and b at 32 inside the request, the query, then b once more on its own
-    assert _computed(engine.runner.calls) == [(0, 32), (32, 32), (64, 2), (0, 32)]
+    # a, b and the query are one run of 66 tokens (in pieces of the runner's 64 tokens per forward);
+    # then b once more on its own
+    assert _computed(engine.runner.calls) == [(0, 64), (64, 2), (0, 32)]
     probe = engine.sched._ipc.lookup_chunks([hash_tokens(a), hash_tokens(b)], "default")
     assert all(m is not None and m["pos_offset"] == 0 for m in probe)
     engine.runner.calls.clear()

@@ -262,3 +262,68 @@ def test_a_chunk_longer_than_the_staging_arena_is_stored_and_restored_in_pieces(
         worker.shutdown()
         sched.close()
         lp.stop()
+
+
+def test_write_behind_stores_commit_later_and_survive_a_failed_write(tmp_path):
+    """``write_behind``: ``wait_for_save`` returns with the file write in flight; the chunk is
+    committed when its half of the arena is needed again, before a load that uses the arena, or at
+    ``flush_stores``.  A write that fails aborts that chunk only."""
+    from conftest import LiveControlPlane
+    from daser_b200.connector.core import SchedulerHalf, TorchKVBackend, WorkerHalf
+    from daser_b200.kv.layout import KVGeometry
+
+    L, H, D, B = 2, 2, 32, 16
+    geo = KVGeometry(num_layers=L, num_kv_heads=H, head_dim=D, block_tokens=B, dtype_bytes=2, codec="raw")
+    lp = LiveControlPlane(tmp_path, total_slots=64, slot_size=geo.slot_size).start()
+    torch.manual_seed(7)
+    pool = torch.randn(L, 40, 2, H, B, D).to(torch.bfloat16)
+    worker = WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool, [1.0] * (D // 2)),
+                        io_backend="posix", staging_slots=8, write_behind=True)
+    sched = SchedulerHalf(lp.socket_path, B, "m")
+
+    def store(rid, toks, blocks):
+        assert sched.get_num_new_matched_tokens(rid, toks + [1], 0) == (0, False)
+        sched.update_state_after_alloc(rid, blocks + [39], 0)
+        meta = sched.build_connector_meta([rid])
+        worker.bind_connector_metadata(meta)
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+        sched.request_finished(rid)
+        return meta.reqs_to_store[0].chunk_key
+
+    def visible(toks):
+        n, _ = sched.get_num_new_matched_tokens("probe", toks + [1, 2], 0)
+        sched.request_finished("probe")
+        return n == len(toks)
+
+    try:
+        chunks = [list(range(100 * (i + 1), 100 * (i + 1) + 3 * B)) for i in range(4)]
+        blocks = [[1, 2, 3], [4, 5, 6], [7, 8, 9], [10, 11, 12]]
+        ka = store("a", chunks[0], blocks[0])
+        assert worker.pending_store_keys() == {ka} and not visible(chunks[0])
+        kb = store("b", chunks[1], blocks[1])            # the other half of the arena: a is still in flight
+        assert worker.pending_store_keys() == {ka, kb}
+        worker.flush_stores()
+        assert not worker.pending_store_keys() and visible(chunks[0]) and visible(chunks[1])
+        worker._xfer.engine.inject_fault(1, err_no=5)     # the next write fails
+        kc = store("c", chunks[2], blocks[2])
+        kd = store("d", chunks[3], blocks[3])
+        assert worker.pending_store_keys() == {kc, kd}
+        worker.flush_stores()
+        assert not visible(chunks[2]) and visible(chunks[3])  # c's write failed: aborted, never visible
+        store("c2", chunks[2], blocks[2])                # and can be stored again; stays pending for now
+        # a load that uses the arena completes what is pending first
+        want = pool[:, blocks[0]].clone()
+        n, _ = sched.get_num_new_matched_tokens("r", chunks[0] + [1, 2], 0)
+        assert n == 3 * B
+        sched.update_state_after_alloc("r", [20, 21, 22, 23], n)
+        worker.bind_connector_metadata(sched.build_connector_meta(["r"]))
+        worker.start_load_kv()
+        worker.clear_connector_metadata()
+        sched.request_finished("r")
+        assert not worker.pending_store_keys() and visible(chunks[2])
+        assert torch.equal(pool[:, [20, 21, 22]], want)
+    finally:
+        worker.shutdown()
+        sched.close()
+        lp.stop()
