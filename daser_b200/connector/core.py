@@ -833,6 +833,16 @@ class WorkerHalf:
         whole = len(ticket.groups) == 1 and (l0, count) == (0, g.num_layers)
         self.kv.restore_worklist(ticket.work, 0 if whole else l0, 0 if whole else count)
 
+    def reads_done(self, ticket: "LoadTicket") -> bool:
+        """True once every storage read of the load has completed (nothing is waited for or consumed):
+        an engine with other work, a decode batch, does that first while this is False."""
+        eng = self._xfer.engine
+        for job in ticket.jobs:
+            for t in job.tickets:
+                if t is not None and (id(job), t) not in ticket.waited and not eng.done(t):
+                    return False
+        return True
+
     def end_load(self, ticket: "LoadTicket", wait: bool = False, close_step: bool = True) -> None:
         """Every piece has been queued.  ``wait`` blocks until the kernels have run and raises on a
         kernel-reported error; without it the caller orders later work behind the current stream

@@ -29,6 +29,7 @@ behind the kernel and awaited (bounded) in front of each rank's layers, replaces
 from __future__ import annotations
 
 import contextlib
+import os
 import time
 from typing import Optional, Sequence
 
@@ -98,6 +99,9 @@ class GpuRagEngine(SchedulingMixin):
                                         rank=self.rank, max_slots=max(staging_slots, 1024), device=self.device)
         self.kv_backend.cos_sin = self.runner.cos_sin
         # tiers and IO are per rank: `hbm_slots` / `host_slots` are this rank's share
+        # decode batches run inside a starting request's wait for the drive (not with composed-chunk
+        # stores, which a finishing request would start inside that wait)
+        self.interleave_decode = os.environ.get("DASER_INTERLEAVE_DECODE", "1") != "0" and compose_after == 0
         self.hbm = HBMStore(self.geo.slot_size, hbm_slots, self.device) if hbm_slots > 0 else None
         self.host = HBMStore(self.geo.slot_size, host_slots, torch.device("cpu")) if host_slots > 0 else None
         self.is_lead = self.rank == 0 and (pp_link is None or pp_link.first)  # plans, reserves, finishes
@@ -321,6 +325,15 @@ class GpuRagEngine(SchedulingMixin):
         self._ev[1].record()
         ticket, gate = self._begin_restore(meta)
         t_restore = time.perf_counter()
+        # While this request's chunks are still coming off the drive, the requests that are already
+        # decoding go on: a decode batch per look at the reads (every rank takes the same decision).
+        while self.interleave_decode and self.running and meta.reqs_to_load and self.pp_link is None:
+            done = ticket is None or self.worker.reads_done(ticket)
+            if self.tp_ctx is not None:
+                done = all(self.tp_ctx.gather_object(bool(done)))
+            if done:
+                break
+            self._decode_step()
         sample = ({"temperature": req.temperature, "seed": req.step_seed(), "top_k": req.top_k, "top_p": req.top_p}
                   if req.temperature > 0 else None)
 

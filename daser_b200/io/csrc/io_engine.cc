@@ -530,6 +530,14 @@ int daser_io_wait(daser_io* io, int64_t ticket, int timeout_ms) {
   return e;
 }
 
+int daser_io_poll(daser_io* io, int64_t ticket) {
+  if (!io) return -EINVAL;
+  std::lock_guard<std::mutex> g(io->mu);
+  auto it = io->tickets.find(ticket);
+  if (it == io->tickets.end()) return -ENOENT;
+  return it->second.pending <= 0 ? 1 : 0;
+}
+
 int daser_io_close(daser_io* io) {
   if (!io) return 0;
   {

@@ -60,6 +60,9 @@ DASER_IO_API int64_t daser_io_submit_strided(daser_io* io, int is_write, void* b
 DASER_IO_API int64_t daser_io_submit(daser_io* io, int is_write, void* buf, int device, int64_t file_offset,
                                      int64_t nbytes);
 DASER_IO_API int daser_io_wait(daser_io* io, int64_t ticket, int timeout_ms);
+// 1 if every piece of the ticket has completed, 0 if some are pending, -ENOENT for an unknown (or
+// already waited-for) ticket.  Does not consume the ticket: daser_io_wait still reports its outcome.
+DASER_IO_API int daser_io_poll(daser_io* io, int64_t ticket);
 DASER_IO_API int daser_io_close(daser_io* io);
 
 // Creates (or extends) a file of `size` bytes without writing zeros through user space.

@@ -43,6 +43,7 @@ def lib() -> C.CDLL:
         L.daser_io_submit_strided.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                               C.c_int, C.c_int64]
         L.daser_io_wait.argtypes = [C.c_void_p, C.c_int64, C.c_int]
+        L.daser_io_poll.argtypes = [C.c_void_p, C.c_int64]
         L.daser_io_close.argtypes = [C.c_void_p]
         L.daser_io_preallocate.argtypes = [C.c_char_p, C.c_int64]
         L.daser_io_inject.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64]
@@ -118,6 +119,14 @@ class IOEngine:
             raise IOTimeout(f"IO ticket {ticket} still pending after {timeout_s}s")
         if rc < 0:
             raise OSError(-rc, os.strerror(-rc), self.path)
+
+    def done(self, ticket: int) -> bool:
+        """True once every piece of ``ticket`` has completed (successfully or not); :meth:`wait` still
+        has to be called to learn the outcome and release the ticket."""
+        rc = lib().daser_io_poll(self._h, ticket)
+        if rc < 0:
+            raise OSError(-rc, os.strerror(-rc), self.path)
+        return rc == 1
 
     def inject_fault(self, count: int, err_no: int = 0, short_bytes: int = -1) -> None:
         lib().daser_io_inject(self._h, count, err_no, short_bytes)

@@ -64,6 +64,7 @@ def engine(tmp_path):
     eng = GpuRagEngine.__new__(GpuRagEngine)                 # not __init__: that needs a GPU
     eng.cfg, eng.geo, eng.tp, eng.rank, eng.tp_ctx, eng.pp_link = cfg, geo, 1, 0, None, None
     eng.compose_after = eng.repair_tokens = 0
+    eng.interleave_decode = True
     eng.runner = _Runner()
     eng.blocks = BlockAllocator(32)
     eng.max_blocks_per_seq = eng.runner.max_blocks
@@ -186,4 +187,37 @@ def test_missed_chunks_are_stored_as_computed_alone(engine):
     engine.runner.calls.clear()
     req = engine.generate([b, a], [4, 5], max_new_tokens=1, store_misses=True)
     assert req.restored_chunks == 2 and _computed(engine.runner.calls) == [(64, 2)]
+    assert engine.blocks.num_free == 32
+
+
+def test_decode_batches_run_while_a_starting_request_waits_for_the_drive(engine, monkeypatch):
+    """A request whose chunk is still being read does not hold up the requests that are decoding:
+    they get a decode step per look at the reads, and the new request starts when the reads are in."""
+    rng = random.Random(3)
+    a = [rng.randrange(1000) for _ in range(32)]
+    engine.store_chunk(a)
+    old = engine.submit(RagRequest([], [1, 2, 3], 8))
+    engine.step()                                   # its first token; it now decodes
+    assert len(old.generated) == 1 and engine.running == [old]
+    looks = []
+
+    def reads_done(ticket):
+        looks.append(len(old.generated))
+        return len(looks) > 3                       # "in flight" for three looks
+
+    monkeypatch.setattr(engine.worker, "reads_done", reads_done)
+    engine.runner.calls.clear()
+    new = engine.submit(RagRequest([a], [7], 1))
+    engine.step()                                   # the new request's step: three decode steps inside it
+    assert new.done and new.restored_chunks == 1
+    assert looks == [1, 2, 3, 4] and len(old.generated) == 4
+    # the three decode forwards of the old request, then the new request's query
+    assert _computed(engine.runner.calls) == [(3, 1), (4, 1), (5, 1), (32, 1)]
+    engine.interleave_decode = False
+    looks.clear()
+    engine.submit(RagRequest([a], [7], 1))
+    engine.step()
+    assert looks == [] and len(old.generated) == 4  # switched off: the step waits for its reads itself
+    while engine.has_work():
+        engine.step()
     assert engine.blocks.num_free == 32

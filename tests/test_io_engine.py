@@ -187,3 +187,24 @@ def test_strided_read_fills_equally_spaced_slices_under_one_ticket(store, backen
             io.wait(io.submit_read_strided(dst.ctypes.data, 8192, layer, n_slots, slot))
         with pytest.raises(OSError):
             io.submit_read_strided(dst.ctypes.data, 0, 4096, 2, 1024)  # extents would overlap
+
+
+@pytest.mark.parametrize("backend", _backends())
+def test_done_polls_without_consuming_the_ticket(store, backend):
+    import time
+
+    with _open(store, backend) as eng:
+        buf = _aligned(1 << 20, fill=7)
+        eng.wait(eng.submit_write(buf.ctypes.data, 0, 1 << 20))
+        dst = _aligned(1 << 20, fill=0)
+        t = eng.submit_read(dst.ctypes.data, 0, 1 << 20)
+        deadline = time.time() + 10
+        while not eng.done(t):
+            assert time.time() < deadline
+            time.sleep(0.001)
+        assert eng.done(t)      # still there: polling releases nothing
+        eng.wait(t)             # the outcome is collected by wait, once
+        assert (dst == 7).all()
+        with pytest.raises(OSError) as exc:
+            eng.done(t)
+        assert exc.value.errno == errno.ENOENT
