@@ -174,7 +174,9 @@ def main() -> None:
     slot = cfg.num_layers * 2 * cfg.block_tokens * cfg.num_kv_heads * cfg.head_dim * 5 // 4
     # (requests are drawn one after the other: asking for more leaves the first ones as they were)
     prefix, pool, reqs = make_traffic(cfg.vocab_size, cfg.block_tokens, args.pool, args.k,
-                                      args.steps + args.warmup + args.precondition)
+                                      args.steps + args.warmup + args.precondition
+                                      + (args.open_loop_requests if args.extras else 0))
+    n_timed_pre = args.steps + args.warmup + args.precondition  # then: the open-loop phase's own requests
     pool_slots = sum(len(c) // cfg.block_tokens for c in pool) + len(prefix) // cfg.block_tokens
     total_slots = pool_slots + 64
     dcfg = DaserConfig(store_path=os.path.join(store_dir, "daser.store"), index_path="", total_slots=total_slots,
@@ -245,7 +247,7 @@ def main() -> None:
         return eng.generate(chunks, query, max_new_tokens=1)
 
     t0 = time.time()
-    for spec in reqs[args.warmup + args.steps:]:
+    for spec in reqs[args.warmup + args.steps : n_timed_pre]:
         run(spec)
     t_precondition = time.time() - t0
     for spec in reqs[: args.warmup]:
@@ -464,12 +466,13 @@ def measure_extras(args, eng, tp_ctx, reqs, barrier, rank) -> dict:
         # the probes above emptied the tiers: bring them back to what the traffic makes of them
         for t in tiers:
             t.clear()
-        for chunks, query, _ in reqs[args.warmup + args.steps:]:
+        n_pre = args.warmup + args.steps + args.precondition
+        for chunks, query, _ in reqs[args.warmup + args.steps : n_pre]:
             eng.generate(chunks, query, max_new_tokens=1)
 
         rng = random.Random(7)
         gaps = [rng.expovariate(4.0) for _ in range(n_open)]
-        picks = [reqs[args.warmup + i % args.steps] for i in range(n_open)]
+        picks = reqs[n_pre : n_pre + n_open]  # requests nobody has served yet: the tier mix of the headline
         barrier()
         t_begin = time.perf_counter()
         arrivals, t = [], 0.0
