@@ -156,3 +156,35 @@ def test_engine_loop_on_the_gpu_engine_matches_one_request_at_a_time(tmp_path):
     finally:
         eng.close()
         lp.stop()
+
+
+def test_missed_chunks_stored_write_behind_are_restored_by_later_requests(tmp_path):
+    """``store_misses`` with write-behind stores: a request's missed chunks and its query go through
+    the model as one run, the chunk at offset 0 is stored from the request's blocks with the file
+    write in flight when the call returns, and a later request that asks for it finds it (the
+    engine completes a pending store of a chunk it is asked for before it plans)."""
+    from daser_b200.engine.rag_gpu import GpuRagEngine
+
+    cfg = PRESETS["tiny-gqa"]
+    lp = LiveControlPlane(tmp_path, total_slots=256,
+                          slot_size=cfg.num_layers * 2 * 16 * cfg.num_kv_heads * cfg.head_dim * 5 // 4).start()
+    eng = GpuRagEngine(cfg, lp.socket_path, lp.cfg.store_path, num_blocks=256, max_tokens=128, host_slots=64,
+                       write_behind=True)
+    try:
+        rng = random.Random(4)
+        a, b = ([rng.randrange(cfg.vocab_size) for _ in range(n)] for n in (64, 48))
+        query = [rng.randrange(cfg.vocab_size) for _ in range(7)]
+        cold = eng.generate([a, b], query, max_new_tokens=3, store_misses=True)
+        assert cold.restored_chunks == 0
+        # a (offset 0) was stored in place and may still be in flight; b was recomputed alone and
+        # stored through store_chunk, which returns with the chunk visible
+        warm = eng.generate([a, b], query, max_new_tokens=3, store_misses=True)
+        assert warm.restored_chunks == 2 and not eng.worker.pending_store_keys()
+        assert len(warm.generated) == 3
+        other = eng.generate([b, a], query, max_new_tokens=2)
+        assert other.restored_chunks == 2
+        eng.runner.check_status()
+        assert eng.blocks.num_free == 256
+    finally:
+        eng.close()
+        lp.stop()
