@@ -26,8 +26,9 @@ GPU and the hot path makes no NCCL call:
   (``ops/csrc/kv_paged.cu``); **save** has every rank compress and push its head slice into
   the IO rank's staging buffer.
 
-NCCL is used for bootstrap, barriers between engine steps and the 8-byte-per-sequence
-exchange of greedy-sampling candidates.  Only the opt-in in-switch form uses ``multimem``, so by
+NCCL is used for bootstrap, barriers between engine steps and the gathered logits rows of
+top-k / top-p requests; the sampling candidates (8 bytes per sequence and rank) are exchanged by
+``tp_pick_token_kernel`` over peer memory.  Only the opt-in in-switch form uses ``multimem``, so by
 default the symmetric allocations are made without an NVLink multicast object bound to them
 (``TORCH_SYMM_MEM_DISABLE_MULTICAST=1`` unless the caller set it, or asked for ``multicast``): a
 process that dies while its memory is bound to one raises NVLink faults on its peers' GPUs.  Peer liveness is checked on the
