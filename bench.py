@@ -169,6 +169,14 @@ def main() -> None:
             tp_ctx = TPContext(cfg, dist.group.WORLD, max_tokens=args.max_tokens, impl=args.tp_impl)
 
     store_dir = args.store_dir or tempfile.mkdtemp(prefix="daser_bench_")
+    if not args.store_dir and rank == 0:
+        # the store file is tens of GB: it must not outlive the run, however the run ends
+        import atexit
+        import shutil
+
+        atexit.register(shutil.rmtree, store_dir, ignore_errors=True)
+    elif not args.store_dir:
+        os.rmdir(store_dir)  # only rank 0's directory is used
     if tp_ctx is not None:
         store_dir = tp_ctx.broadcast_object(store_dir)
     slot = cfg.num_layers * 2 * cfg.block_tokens * cfg.num_kv_heads * cfg.head_dim * 5 // 4
