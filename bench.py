@@ -75,8 +75,12 @@ def reference_arm(args) -> None:
         cmd = [sys.executable, os.path.join(base, "reference_arm.py"), "--gpus", str(args.gpus), "--steps",
                str(args.steps), "--warmup", str(max(args.warmup, 3)), "--model", args.model, "--pool", str(args.pool),
                "--k", str(args.k)]
-        if args.store_dir:
-            cmd += ["--store-dir", args.store_dir]
+        # the store (tens of GB of raw bf16 KV) lives in a directory that this process removes
+        # afterwards, also when the child had to be killed
+        import shutil
+
+        made = None if args.store_dir else tempfile.mkdtemp(prefix="daser_ref_")
+        cmd += ["--store-dir", args.store_dir or made]
         if os.environ.get("DASER_REF_EAGER") == "1":
             cmd.append("--eager")
         # a session of its own: on a time-out the whole group goes (vLLM's engine and worker processes too)
@@ -94,6 +98,9 @@ def reference_arm(args) -> None:
             os.killpg(proc.pid, signal.SIGKILL)
             proc.wait()
             out = {"impl": "reference", "unavailable": "reference process did not finish within its time limit"}
+        finally:
+            if made:
+                shutil.rmtree(made, ignore_errors=True)
     print(json.dumps(out))
 
 
