@@ -1,6 +1,6 @@
 """One small, self-terminating launch of a hot kernel, sized for an ``ncu`` capture.
 
-    python benchmarks/profile_case.py --case restore|save|gemm|gemm_rs|attn_decode|attn_prefill|rmsnorm
+    python benchmarks/profile_case.py --case restore|save|gemm|gemm_rs|gemm_qkv_rope|attn_decode|attn_prefill|rmsnorm
 
 Each case touches a few hundred MB at most (larger than L2, far from the GPU's capacity),
 runs two warm-up launches and three measured ones, and prints the CUDA-event time of the
@@ -54,6 +54,30 @@ def case_gemm(reduce_scatter=False):
     return fn, 2 * (N * K + M * K) + 4 * M * N
 
 
+def case_gemm_qkv_rope():
+    """The QKV projection of Llama-3-70B for a 64-token step with RoPE + fp8 quantise + the paged KV
+    write as its epilogue (opt-in in the engine: `DASER_FUSE_QKV_ROPE=1`); 168 MB of weights."""
+    T, K, Hq, Hkv, D, B = 64, 8192, 64, 8, 128, 16
+    N = (Hq + 2 * Hkv) * D
+    x = (torch.randn(T, K, device="cuda") * 0.1).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    n_blocks = T // B + 4
+    positions = (torch.arange(T, device="cuda") + 3328).to(torch.int32)
+    slot_mapping = (torch.randperm(n_blocks, device="cuda")[torch.arange(T, device="cuda") // B] * B
+                    + torch.arange(T, device="cuda") % B).to(torch.int64)
+    cos_sin = kv_ops.rope_table(8192, inv_freq_table(D, 500000.0), "cuda")
+    pay = torch.zeros(1, n_blocks, 2, Hkv, B, D, dtype=torch.uint8, device="cuda")
+    sc = torch.zeros(1, n_blocks, 2, Hkv, B, D // 16, dtype=torch.float32, device="cuda")
+    pool = kv_ops.PagedKVPool.from_tensors([pay], [sc], "LNKHTD")
+    work = torch.zeros(T, N, dtype=torch.float32, device="cuda")
+    counters = torch.zeros(256, dtype=torch.int32, device="cuda")
+    q_out = torch.zeros(T, Hq, D, dtype=torch.bfloat16, device="cuda")
+    _, ks = gemm.plan_tiles(T, N, K, True)
+    fn = lambda: gemm.linear_qkv_rope(x, w, positions, slot_mapping, cos_sin, q_out, Hq, Hkv, B, pool, 0, 0, work,
+                                      counters, k_splits=ks)
+    return fn, 2 * (N * K + T * K) + 2 * T * Hq * D
+
+
 def case_attn(prefill=False):
     Hq, Hkv, D, B = 64, 8, 128, 16
     batch, ctx = (1, 4096) if prefill else (16, 8192)
@@ -89,7 +113,7 @@ def main():
     args = ap.parse_args()
     table = {
         "restore": lambda: case_restore(False), "save": lambda: case_restore(True),
-        "gemm": lambda: case_gemm(False), "gemm_rs": lambda: case_gemm(True),
+        "gemm": lambda: case_gemm(False), "gemm_rs": lambda: case_gemm(True), "gemm_qkv_rope": case_gemm_qkv_rope,
         "attn_decode": lambda: case_attn(False), "attn_prefill": lambda: case_attn(True),
         "rmsnorm": case_rmsnorm,
     }
