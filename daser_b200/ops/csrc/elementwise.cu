@@ -236,7 +236,7 @@ __global__ void signal_flags_kernel(SignalTargets targets, int n, uint32_t value
 // Tensor-parallel sampling in one kernel.  Every rank holds, per row, the best (value, global
 // vocabulary index) of its shard; the sample is the best over the ranks.  This rank's candidates
 // go into every rank's table by peer stores, an arrival is published in every rank's counter, the
-// kernel waits (bounded) until its own counter shows all `tp` arrivals of this round and picks.
+// kernel waits (bounded) until its own counter shows all `tp` arrivals of this exchange and picks.
 // Table of a rank: [2 rounds][tp sources][2: value, index bits][cap] floats; rounds alternate so
 // that a fast rank's next push cannot land on candidates a slow rank has not read yet.  `epoch`
 // (device word, local) counts the arrivals consumed so far: the kernel can be replayed.
