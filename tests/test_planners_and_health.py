@@ -102,3 +102,16 @@ def test_pipeline_partition_and_stage_geometry():
     geo = stage_geometry(cfg, 5, dtype_bytes=2)
     assert geo.num_layers == 8 and geo.slot_size == 8 * 2 * 16 * 8 * 128 * 2    # the widest stage sizes the slots
     assert stage_store_path("/mnt/kv/daser.store", 2, 5) == "/mnt/kv/daser.store.pp2of5"
+
+
+def test_row_buckets_are_few_idempotent_and_never_smaller_than_the_step():
+    from daser_b200.engine.runner import GpuModelRunner
+
+    b = GpuModelRunner.bucket_rows
+    assert [b(n) for n in (1, 5, 16)] == [1, 5, 16]              # decode batches, prompt tails: exact
+    assert [b(n) for n in (17, 64, 65, 128)] == [32, 64, 80, 128]
+    assert [b(n) for n in (129, 303, 512, 513, 1000)] == [192, 320, 512, 640, 1024]
+    for n in range(1, 2049):
+        assert b(n) >= n and b(b(n)) == b(n)
+        assert b(n) - n < (16 if n <= 128 else 64 if n <= 512 else 128)
+    assert len({b(n) for n in range(1, 1025)}) <= 16 + 7 + 6 + 4  # the graphs a runner can end up holding
