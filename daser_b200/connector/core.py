@@ -20,8 +20,16 @@ What changed relative to the reference:
 * Partial prefix hits honour ``num_computed_tokens`` (``skip_slots``) instead of assuming 0.
 * A failed load is reported through ``take_load_errors`` so the engine recomputes; a
   reservation whose request finishes without a store is aborted.
-* Staging memory is persistent (pinned host or device arena), never allocated per step.
-* An optional HBM tier (:mod:`daser_b200.kv.hbm_store`) serves hot chunks without IO.
+* Staging memory is persistent (pinned host or device arena), never allocated per step; a chunk
+  longer than the arena passes through it in pieces, on the way out and on the way back.
+* An optional HBM tier (:mod:`daser_b200.kv.hbm_store`) serves hot chunks without IO; a pinned host
+  tier of the same class sits between it and the file.
+* A load can be cut by layer group (``begin_load / restore_group / end_load``): reads go out at once,
+  group-major, and piece g is restored when ITS reads are in (``reads_done`` tells an engine whether
+  anything is still in flight without waiting for it).
+* ``write_behind`` (opt-in): ``wait_for_save`` returns with the file writes in flight; the chunk is
+  committed when they are done (the reference writes and commits inside ``wait_for_save``,
+  ``daser/connector/daser_connector.py:560-700``).
 """
 
 from __future__ import annotations
