@@ -29,7 +29,7 @@ What changed relative to the reference:
   anything is still in flight without waiting for it).
 * ``write_behind`` (opt-in): ``wait_for_save`` returns with the file writes in flight; the chunk is
   committed when they are done (the reference writes and commits inside ``wait_for_save``,
-  ``daser/connector/daser_connector.py:560-700``).
+  ``daser/connector/daser_connector.py:634-700``).
 """
 
 from __future__ import annotations
