@@ -327,3 +327,66 @@ def test_write_behind_stores_commit_later_and_survive_a_failed_write(tmp_path):
         worker.shutdown()
         sched.close()
         lp.stop()
+
+
+@pytest.mark.parametrize("staging_slots,write_behind", [(2, False), (3, True), (5, False), (8, True)])
+def test_random_chunks_through_small_arenas_come_back_exact(tmp_path, staging_slots, write_behind):
+    """Chunks of 1..12 blocks, several per step, through arenas smaller than most of them, with and
+    without write-behind: every chunk is restored bit for bit into other blocks."""
+    import random
+
+    from conftest import LiveControlPlane
+    from daser_b200.connector.core import SchedulerHalf, TorchKVBackend, WorkerHalf
+    from daser_b200.kv.layout import KVGeometry
+
+    L, H, D, B = 2, 1, 32, 16
+    geo = KVGeometry(num_layers=L, num_kv_heads=H, head_dim=D, block_tokens=B, dtype_bytes=2, codec="raw")
+    lp = LiveControlPlane(tmp_path, total_slots=256, slot_size=geo.slot_size).start()
+    rng = random.Random(staging_slots * 7 + write_behind)
+    torch.manual_seed(staging_slots)
+    n_blocks = 160
+    pool = torch.randn(L, n_blocks, 2, H, B, D).to(torch.bfloat16)
+    worker = WorkerHalf(lp.socket_path, lp.cfg.store_path, geo, TorchKVBackend(geo, pool, [1.0] * (D // 2)),
+                        io_backend="posix", staging_slots=staging_slots, write_behind=write_behind)
+    sched = SchedulerHalf(lp.socket_path, B, "m")
+
+    def step(reqs):
+        meta = sched.build_connector_meta(reqs)
+        worker.bind_connector_metadata(meta)
+        worker.start_load_kv()
+        worker.wait_for_save()
+        worker.clear_connector_metadata()
+        for r in reqs:
+            sched.request_finished(r)
+
+    try:
+        free = list(range(1, n_blocks))
+        chunks = []
+        for i in range(9):
+            nb = rng.randint(1, 12)
+            toks = [rng.randrange(1, 30000) for _ in range(nb * B)]
+            blocks = [free.pop() for _ in range(nb)]
+            chunks.append((f"s{i}", toks, blocks, pool[:, blocks].clone()))
+        for group in (chunks[:4], chunks[4:7], chunks[7:]):
+            for rid, toks, blocks, _ in group:
+                assert sched.get_num_new_matched_tokens(rid, toks + [1], 0) == (0, False)
+                sched.update_state_after_alloc(rid, blocks + [0], 0)
+            step([rid for rid, *_ in group])
+        worker.flush_stores()
+        loads = []
+        for i, (rid, toks, _, want) in enumerate(chunks):
+            nb = len(toks) // B
+            dst = [free.pop() for _ in range(nb)]
+            n, _ = sched.get_num_new_matched_tokens(f"l{i}", toks + [1, 2], 0)
+            assert n == nb * B
+            sched.update_state_after_alloc(f"l{i}", dst + [0], n)
+            loads.append((f"l{i}", dst, want))
+        step([rid for rid, *_ in loads[:5]])
+        step([rid for rid, *_ in loads[5:]])
+        for rid, dst, want in loads:
+            assert torch.equal(pool[:, dst], want), rid
+        assert not worker.take_load_errors()
+    finally:
+        worker.shutdown()
+        sched.close()
+        lp.stop()
